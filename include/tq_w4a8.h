@@ -1,0 +1,238 @@
+/*
+ * tq_w4a8.h — boundary of the B200 W4A8 projection library (libforward_qwen_xpu.so).
+ *
+ * The library is a drop-in for the projection path of knivesysl-xe: the packed
+ * weight record, the C++ projection functions and the flat C entry points below
+ * keep the reference's names, argument meaning and return codes. Every pointer
+ * named d_* is CUDA device memory on the current device; all calls are
+ * asynchronous on ONE in-order stream per device (tq_stream()) and are not
+ * thread-safe, exactly like the reference's single in-order queue
+ * (xpu/src/decode.cpp:74-75, xpu/src/tq_common.hpp:407-409).
+ *
+ * Each declaration cites the reference interface it replaces.
+ */
+#ifndef TQ_W4A8_H
+#define TQ_W4A8_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Packed weight record. Field order, names and meaning follow
+ * xpu/src/tq_common.hpp:49-76 so that a caller's struct can be passed as is.
+ * Only the W4 members are read by this library:
+ *   M, K, Mt = M/16, Kt = K/32
+ *   d_s4        [Mt][Kt][16 rows][16 B]; byte b of a row holds k = 2b (low
+ *               nibble) and k = 2b+1 (high nibble), two's-complement int4
+ *   d_s4_scale  uint16 [Mt][Kt >> s4_k64][16] (k16 tier: [Mt][2*Kt][16]);
+ *               FP16 scale with its low 4 mantissa bits replaced by a signed
+ *               4-bit zero point z: weight ~= scale * (q - z)
+ *   s4_ready / s4_k16 / s4_k64 select the tier
+ * The E2M3 source members (d_A, d_block_scale_inv, block_scaled, e2m3,
+ * scale_rows, scale_cols) are read only by the repack entry points. */
+typedef struct {
+    int M, K, Mt, Kt;
+    float inv_scale;
+    uint8_t *d_A;
+    float *d_block_scale_inv;
+    int block_scaled;
+    int row_major;
+    int word_major;
+    int e2m3;
+    int e2m1;
+    int e2m3_byte;
+    int scale_rows;
+    int scale_cols;
+    uint8_t *d_s4;
+    uint16_t *d_s4_scale;
+    int s4_ready;
+    int s4_k16;
+    int s4_k64;
+    uint8_t *d_s8;
+    uint16_t *d_s8_scale;
+    int s8_ready;
+} tq_qmma_weight_t;
+
+/* ---- device runtime: replaces tq_q()/tq_dev_* of xpu/src/decode.cpp:86-130 and
+ * xpu/src/tq_common.hpp:200-216. Allocation failure aborts with a message, like
+ * the reference. tq_stream() returns the cudaStream_t every call is ordered on. */
+int tq_set_device(int device);            /* one process per GPU: pick it once */
+int tq_device(void);
+void *tq_stream(void);
+void *tq_dev_alloc(size_t bytes, const char *what);
+void tq_dev_free(void *p);
+void tq_h2d(void *dst, const void *src, size_t bytes);   /* blocking */
+void tq_d2h(void *dst, const void *src, size_t bytes);   /* blocking */
+void tq_dev_zero(void *dst, size_t bytes);
+void tq_dev_fill(void *dst, int byte, size_t bytes);
+void tq_sync(void);                        /* wait for the stream; returns after errors are read */
+int tq_last_error(void);                   /* sticky: cudaError of the last failed call, or a
+                                              device-side wait status (>= 10000); 0 = clean */
+void *tq_host_alloc_pinned(size_t bytes);
+void tq_host_free_pinned(void *p);
+void tq_h2d_async(void *dst, const void *src, size_t bytes);
+void tq_d2h_async(void *dst, const void *src, size_t bytes);
+void tq_d2d_async(void *dst, const void *src, size_t bytes);
+/* CUDA events on tq_stream() for device-side timing. */
+void *tq_event_create(void);
+void tq_event_destroy(void *ev);
+void tq_event_record(void *ev);
+float tq_event_elapsed_ms(void *start, void *stop);     /* synchronises on stop */
+
+/* ---- flat C entry points (for ctypes / cgo / JNI style bindings). Each forwards
+ * to the C++ function of the same name without the qwn_ prefix. */
+
+/* xpu/src/kernels_dpas.cpp:403-428 (x_w4_repack_weight_mode, x_w4_repack_weight):
+ * E2M3 fragment payload -> packed int4 + FP16 scale/zero-point per group.
+ * mode 0 = one scale per K32, 1 = per K16, 2 = per K64. Allocates d_s4/d_s4_scale,
+ * frees d_A/d_block_scale_inv. Returns 0, -1 (bad record), -2 (M%16 or K%128),
+ * -3 (mode 2 with odd Kt). */
+int qwn_x_w4_repack_weight(tq_qmma_weight_t *w);
+int qwn_x_w4_repack_weight_mode(tq_qmma_weight_t *w, int mode);
+
+/* xpu/src/kernels_dpas.cpp:188-223: fp32[K] -> s8[K], one fp32 scale per K32,
+ * one int32 code sum per K16 (d_sum may be NULL). */
+void qwn_x_quantize_act_s8(const float *d_x, int K, int8_t *d_q, float *d_scale, int32_t *d_sum);
+/* xpu/src/kernels_dpas.cpp:846-849: quantise into the library's prepared scratch. */
+void qwn_x_prepare_gemv_act_s8(const float *d_x, int K);
+/* xpu/src/kernels_dpas.cpp:851-855: hidden = silu(gate)*up stored to d_out, then
+ * staged like x_prepare_gemv_act_s8. Silently returns on bad arguments. */
+void qwn_x_silu_mul_quant(float *d_out, const float *d_gate, const float *d_up, int K);
+/* xpu/src/kernels_dpas.cpp:866-929: (1+w) RMSNorm stored to d_out plus staging. */
+void qwn_x_rmsnorm_quant(float *d_out, const float *d_in, const uint16_t *d_w, int H, float eps);
+
+/* xpu/src/kernels_dpas.cpp:1664-1680 and 586-675: single-row GEMV. The split
+ * count follows choose_gemv_splits; y = sum over splits (+ residual).
+ * Returns 0, -1 (bad record/pointers), -2 (scratch not prepared for this K). */
+int qwn_x_gemv_w4a8(const tq_qmma_weight_t *w, const float *d_x, float *d_y);
+int qwn_x_gemv_w4a8_add(const tq_qmma_weight_t *w, const float *d_x, const float *d_residual,
+                        float *d_y);
+int qwn_x_gemv_w4a8_prepared(const tq_qmma_weight_t *w, float *d_y, const float *d_residual);
+/* xpu/src/kernels_dpas.cpp:945-1102: up to 4 weights sharing K, tier and the prepared
+ * activation in one launch. Returns 0, -1, -2 (tier/K mismatch), -3 (not prepared). */
+int qwn_x_gemv_w4a8_fanout(const tq_qmma_weight_t *const *ws, float *const *ys, int count);
+
+/* xpu/src/kernels_core.cpp:164-252: tier dispatchers used by the layer bodies. Only the
+ * W4 K32/K64 tiers exist here; other tiers return -20. */
+int qwn_x_gemv_qmma(const tq_qmma_weight_t *w, const float *d_x, float *d_y);
+int qwn_x_gemv_qmma_add(const tq_qmma_weight_t *w, const float *d_x, const float *d_residual,
+                        float *d_y);
+int qwn_x_gemv_qmma_prepared(const tq_qmma_weight_t *w, const float *d_x, float *d_y,
+                             const float *d_residual);
+/* xpu/src/kernels_core.cpp:254-281: the fp32 glue either side of a projection. */
+void qwn_x_silu_mul(float *d_out, const float *d_gate, const float *d_up, int N);
+void qwn_x_add_inplace(float *d_x, const float *d_y, int N);
+
+/* xpu/src/kernels_dpas.cpp:1149-1207: fp32 [T][K] -> aq[kt][tok][32], as[kt][tok],
+ * asum[kt][tok]. */
+void qwn_x_quantize_act_chunk(const float *d_x, int K, int T, int8_t *d_aq, float *d_as,
+                              int32_t *d_asum);
+/* xpu/src/kernels_dpas.cpp:1334-1490: Y[T][M] for T % 8 == 0; offsets is HOST memory
+ * (segments+1 entries, <= 8 segments, 8-aligned) and keeps each segment's own split-K
+ * count. Returns 0, -1 (bad record), -2 (bad arguments). */
+int qwn_x_gemm_w4a8(const tq_qmma_weight_t *w, const int8_t *d_aq, const float *d_as,
+                    const int32_t *d_asum, float *d_y, int T, const int *offsets, int segments);
+
+/* xpu/src/kernels_dpas.cpp:450-499, 549-556: column (mode 0) shard of a packed weight.
+ * Returns 0, -1..-6 as the reference; modes 1 and 2 return -9 (not built). */
+int qwn_x_w4_shard(tq_qmma_weight_t *dst, const tq_qmma_weight_t *src, int rank, int tp, int mode,
+                   const int *groups, int ngroups);
+void qwn_x_w4_shard_free(tq_qmma_weight_t *w);
+
+/* xpu/src/kernels_dpas.cpp:170-173 and 1226-1250: the split heuristics, exported so
+ * callers and tests can see the order a result was summed in. */
+int qwn_choose_gemv_splits(int groups);
+int qwn_choose_gemm_splits(int rgroups, int tgroups, int ktiles);
+
+/* ---- additions without a counterpart in the reference ----------------------- */
+
+/* Several weights that share K, tier and one staged activation chunk, as ONE launch
+ * (the reference issues one x_gemm_w4a8 per weight, xpu/src/decode.cpp:1859-1862).
+ * Each weight keeps the split count it would get alone, so results are bit-identical
+ * to per-weight calls. */
+int qwn_x_gemm_w4a8_fanout(const tq_qmma_weight_t *const *ws, float *const *ys, int count,
+                           const int8_t *d_aq, const float *d_as, const int32_t *d_asum, int T,
+                           const int *offsets, int segments);
+/* Per-token activation scale (absmax/127 over the whole row): same staging layout as
+ * x_quantize_act_chunk with the scale replicated into every as[kt][tok], plus the
+ * per-token vector d_as_tok[T]. */
+void qwn_x_quantize_act_chunk_pertoken(const float *d_x, int K, int T, int8_t *d_aq, float *d_as,
+                                       int32_t *d_asum, float *d_as_tok);
+/* GEMM for per-token scales: the int32 dot runs over a whole weight-scale group before
+ * the fp32 promote; y = (sum_g (d_g - z*asum_g) * ws_g) * as_tok. out_bf16 != 0 stores
+ * bfloat16 instead of fp32. Returns like x_gemm_w4a8. */
+int qwn_x_gemm_w4a8_pertoken(const tq_qmma_weight_t *w, const int8_t *d_aq, const float *d_as_tok,
+                             const int32_t *d_asum, void *d_y, int T, int out_bf16);
+
+/* int32 layer exposed for bit-exact checks: the dot of every (row, k-tile) with the
+ * staged activation, produced by the same unpack/dot code as the kernels above.
+ * gemv: d[(g*Kt+kt)*16+n] from the prepared scratch; gemm: d[(kt*T+tok)*M+row]. */
+int qwn_dbg_tile_dots_gemv(const tq_qmma_weight_t *w, int32_t *d_out);
+int qwn_dbg_tile_dots_gemm(const tq_qmma_weight_t *w, const int8_t *d_aq, int T, int32_t *d_out);
+/* Copies of the prepared scratch (device->device), for tests: any pointer may be NULL. */
+int qwn_dbg_prepared_act(int K, int8_t *d_q, float *d_scale, int32_t *d_sum);
+
+/* Model-free forms of the reference's self-checks and micro-benches
+ * (xpu/src/kernels_dpas.cpp:2146-2333, 2613-2693): they take a weight record instead of
+ * a layer index of a loaded model. Checks return 0 on pass. */
+double qwn_gemv_bench(const tq_qmma_weight_t *w, int iters);              /* us per call */
+double qwn_gemm_bench(const tq_qmma_weight_t *w, int tokens, int iters);  /* us per call */
+int qwn_gemm_check(const tq_qmma_weight_t *w, int tokens, double *worst_cos, double *worst_rel);
+int qwn_specwave_check(const tq_qmma_weight_t *w);
+int qwn_shard_check(const tq_qmma_weight_t *w, int tp);
+
+/* ---- tensor-parallel exchange: one process per GPU, NCCL loaded at run time.
+ * Replaces tq_allreduce's role as the only collective (xpu/src/decode.cpp:133-154) with
+ * the all-gather a column shard needs. */
+int tq_comm_unique_id(void *id128);                       /* rank 0 fills 128 bytes */
+int tq_comm_init(const void *id128, int rank, int world);
+int tq_comm_allgather(const void *d_send, void *d_recv, size_t bytes_per_rank);
+int tq_comm_rank(void);
+int tq_comm_world(void);
+void tq_comm_destroy(void);
+
+#ifdef __cplusplus
+}  /* extern "C" */
+
+/* C++ projection contract, same signatures as xpu/src/tq_common.hpp:386-461. */
+int x_w4_repack_weight(tq_qmma_weight_t *w);
+int x_w4_repack_weight_mode(tq_qmma_weight_t *w, int mode);
+void x_quantize_act_s8(const float *d_x, int K, int8_t *d_q, float *d_scale, int32_t *d_sum);
+int x_gemv_w4a8(const tq_qmma_weight_t *w, const float *d_x, float *d_y);
+int x_gemv_w4a8_add(const tq_qmma_weight_t *w, const float *d_x, const float *d_residual,
+                    float *d_y);
+int x_gemv_qmma(const tq_qmma_weight_t *w, const float *d_x, float *d_y);
+int x_gemv_qmma_add(const tq_qmma_weight_t *w, const float *d_x, const float *d_residual,
+                    float *d_y);
+void x_prepare_gemv_act_s8(const float *d_x, int K);
+void x_silu_mul_quant(float *d_out, const float *d_gate, const float *d_up, int K);
+void x_silu_mul(float *d_out, const float *d_gate, const float *d_up, int N);
+void x_add_inplace(float *d_x, const float *d_y, int N);
+void x_rmsnorm_quant(float *d_out, const float *d_in, const uint16_t *d_w, int H, float eps);
+int x_gemv_w4a8_fanout(const tq_qmma_weight_t *const *ws, float *const *ys, int count);
+void x_quantize_act_chunk(const float *d_x, int K, int T, int8_t *d_aq, float *d_as,
+                          int32_t *d_asum);
+int x_gemm_w4a8(const tq_qmma_weight_t *w, const int8_t *d_aq, const float *d_as,
+                const int32_t *d_asum, float *d_y, int T, const int *offsets = nullptr,
+                int segments = 0);
+int x_gemv_w4a8_prepared(const tq_qmma_weight_t *w, float *d_y,
+                         const float *d_residual = nullptr);
+int x_gemv_qmma_prepared(const tq_qmma_weight_t *w, const float *d_x, float *d_y,
+                         const float *d_residual = nullptr);
+int x_w4_shard(tq_qmma_weight_t *dst, const tq_qmma_weight_t *src, int rank, int tp, int mode,
+               const int *groups, int ngroups);
+void x_w4_shard_free(tq_qmma_weight_t *w);
+/* additions (see the C section) */
+int x_gemm_w4a8_fanout(const tq_qmma_weight_t *const *ws, float *const *ys, int count,
+                       const int8_t *d_aq, const float *d_as, const int32_t *d_asum, int T,
+                       const int *offsets = nullptr, int segments = 0);
+void x_quantize_act_chunk_pertoken(const float *d_x, int K, int T, int8_t *d_aq, float *d_as,
+                                   int32_t *d_asum, float *d_as_tok);
+int x_gemm_w4a8_pertoken(const tq_qmma_weight_t *w, const int8_t *d_aq, const float *d_as_tok,
+                         const int32_t *d_asum, void *d_y, int T, int out_bf16 = 0);
+#endif /* __cplusplus */
+
+#endif /* TQ_W4A8_H */

@@ -1,0 +1,116 @@
+// comm.cu — the exchange step of a column-sharded projection: an all-gather of the
+// ranks' output slices over NVLink. One process per GPU; NCCL is loaded at run time
+// (dlopen) so a single-GPU user needs no NCCL at all. The reference's only collective
+// is a 2-rank peer-copy all-reduce (xpu/src/decode.cpp:133-154); a column shard needs
+// an all-gather instead, and no K-split all-reduce is built.
+#include "common.cuh"
+
+#include <dlfcn.h>
+#include <string.h>
+
+namespace {
+
+typedef struct ncclComm *ncclComm_t;
+typedef struct { char internal[128]; } ncclUniqueId;
+typedef int ncclResult_t;
+enum { kNcclInt8 = 0 };   // ncclInt8 / ncclChar
+
+struct NcclApi {
+    void *handle = nullptr;
+    ncclResult_t (*GetUniqueId)(ncclUniqueId *) = nullptr;
+    ncclResult_t (*CommInitRank)(ncclComm_t *, int, ncclUniqueId, int) = nullptr;
+    ncclResult_t (*AllGather)(const void *, void *, size_t, int, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+    const char *(*GetErrorString)(ncclResult_t) = nullptr;
+} g_api;
+
+ncclComm_t g_comm = nullptr;
+int g_rank = 0, g_world = 1;
+
+bool load_nccl() {
+    if (g_api.handle) return true;
+    const char *names[] = {"libnccl.so.2", "libnccl.so"};
+    for (const char *n : names) {
+        g_api.handle = dlopen(n, RTLD_NOW | RTLD_GLOBAL);
+        if (g_api.handle) break;
+    }
+    if (!g_api.handle) {
+        fprintf(stderr, "forward_qwen_xpu(b200): cannot load NCCL: %s\n", dlerror());
+        return false;
+    }
+    g_api.GetUniqueId = (decltype(g_api.GetUniqueId))dlsym(g_api.handle, "ncclGetUniqueId");
+    g_api.CommInitRank = (decltype(g_api.CommInitRank))dlsym(g_api.handle, "ncclCommInitRank");
+    g_api.AllGather = (decltype(g_api.AllGather))dlsym(g_api.handle, "ncclAllGather");
+    g_api.CommDestroy = (decltype(g_api.CommDestroy))dlsym(g_api.handle, "ncclCommDestroy");
+    g_api.GetErrorString = (decltype(g_api.GetErrorString))dlsym(g_api.handle, "ncclGetErrorString");
+    if (!g_api.GetUniqueId || !g_api.CommInitRank || !g_api.AllGather || !g_api.CommDestroy) {
+        fprintf(stderr, "forward_qwen_xpu(b200): NCCL symbols missing\n");
+        dlclose(g_api.handle);
+        g_api.handle = nullptr;
+        return false;
+    }
+    return true;
+}
+
+int nccl_fail(ncclResult_t r, const char *where) {
+    fprintf(stderr, "forward_qwen_xpu(b200): NCCL error %d at %s: %s\n", r, where,
+            g_api.GetErrorString ? g_api.GetErrorString(r) : "?");
+    return -10;
+}
+
+}  // namespace
+
+extern "C" {
+
+int tq_comm_unique_id(void *id128) {
+    if (!id128 || !load_nccl()) return -1;
+    ncclUniqueId id;
+    const ncclResult_t r = g_api.GetUniqueId(&id);
+    if (r != 0) return nccl_fail(r, "ncclGetUniqueId");
+    memcpy(id128, &id, sizeof id);
+    return 0;
+}
+
+int tq_comm_init(const void *id128, int rank, int world) {
+    if (world < 1 || rank < 0 || rank >= world) return -2;
+    if (g_comm) return -3;
+    g_rank = rank;
+    g_world = world;
+    if (world == 1) return 0;
+    if (!id128 || !load_nccl()) return -1;
+    tq::stream();   // binds the device before the communicator is created
+    ncclUniqueId id;
+    memcpy(&id, id128, sizeof id);
+    const ncclResult_t r = g_api.CommInitRank(&g_comm, world, id, rank);
+    if (r != 0) return nccl_fail(r, "ncclCommInitRank");
+    return 0;
+}
+
+// Every rank contributes bytes_per_rank; d_recv holds world * bytes_per_rank, rank-major.
+int tq_comm_allgather(const void *d_send, void *d_recv, size_t bytes_per_rank) {
+    if (!d_send || !d_recv) return -1;
+    if (g_world == 1) {
+        if (d_send != d_recv) tq_d2d_async(d_recv, d_send, bytes_per_rank);
+        return 0;
+    }
+    if (!g_comm) return -3;
+    const ncclResult_t r =
+        g_api.AllGather(d_send, d_recv, bytes_per_rank, kNcclInt8, g_comm, tq::stream());
+    if (r != 0) return nccl_fail(r, "ncclAllGather");
+    return 0;
+}
+
+int tq_comm_rank(void) { return g_rank; }
+int tq_comm_world(void) { return g_world; }
+
+void tq_comm_destroy(void) {
+    if (g_comm) {
+        tq_sync();
+        g_api.CommDestroy(g_comm);
+        g_comm = nullptr;
+    }
+    g_rank = 0;
+    g_world = 1;
+}
+
+}  // extern "C"

@@ -1,0 +1,178 @@
+// common.cuh — shared host/device helpers of the W4A8 projection library.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <stdlib.h>
+
+#include "tq_w4a8.h"
+
+namespace tq {
+
+// ---- host runtime (runtime.cu) ------------------------------------------------
+cudaStream_t stream();
+void note_error(cudaError_t e, const char *where);
+#define TQ_CHECK(expr)                                   \
+    do {                                                 \
+        cudaError_t e__ = (expr);                        \
+        if (e__ != cudaSuccess) ::tq::note_error(e__, #expr); \
+    } while (0)
+#define TQ_LAUNCH_CHECK(name) ::tq::note_error(cudaGetLastError(), name)
+
+// Prepared activation scratch consumed by the "*_prepared" GEMV and the fan-out
+// (the reference's g_act_q / g_act_scale / g_act_sum, kernels_dpas.cpp:130-149).
+// qp holds the same codes permuted for the dp4a unpack: inside each 32-byte tile
+// the even-k codes come first (position (k>>3)*4 + ((k&7)>>1)), then the odd-k
+// codes at +16. sum32 is the K32 sum (both K16 halves added).
+struct ActScratch {
+    int8_t *q = nullptr;
+    int8_t *qp = nullptr;
+    float *scale = nullptr;
+    int32_t *sum16 = nullptr;
+    int32_t *sum32 = nullptr;
+    float *norm_partial = nullptr;
+    int cap = 0;          // capacity in elements of K
+    int prepared_K = 0;   // K of the last prepare (0 = nothing staged)
+};
+ActScratch &act_scratch();
+void ensure_act_scratch(int K);
+
+// Device status word for bounded waits inside kernels (0 = clean).
+int *device_status_word();
+
+// ---- split heuristics (dispatch.cu) --------------------------------------------
+int choose_gemv_splits(int groups);
+int choose_gemm_splits(int rgroups, int tgroups, int ktiles);
+
+// ---- kernel launchers -----------------------------------------------------------
+// quant.cu
+void launch_quant_s8(const float *d_x, const float *d_up, float *d_hidden, int K, int8_t *d_q,
+                     int8_t *d_qp, float *d_scale, int32_t *d_sum16, int32_t *d_sum32, bool silu);
+void launch_rmsnorm_quant(float *d_out, const float *d_in, const uint16_t *d_w, int H, float eps,
+                          float *d_partial, int8_t *d_q, int8_t *d_qp, float *d_scale,
+                          int32_t *d_sum16, int32_t *d_sum32);
+void launch_quant_chunk(const float *d_x, int K, int T, int8_t *d_aq, float *d_as, int32_t *d_asum);
+void launch_quant_chunk_pertoken(const float *d_x, int K, int T, int8_t *d_aq, float *d_as,
+                                 int32_t *d_asum, float *d_as_tok);
+void launch_code_sums(const int8_t *d_aq, size_t blocks, int32_t *d_asum);
+void launch_silu_mul(float *d_out, const float *d_gate, const float *d_up, int N);
+void launch_add_inplace(float *d_x, const float *d_y, int N);
+
+// gemv.cu
+struct GemvArgs {
+    const uint8_t *codes[4];
+    const uint16_t *scales[4];
+    float *y[4];
+    int goff[5];             // row-group prefix over the set
+    int count;
+    const int8_t *qp;        // permuted codes
+    const float *as;
+    const int32_t *sum32;
+    const float *residual;   // single-weight only
+    int K, ksh, splits;
+    int serial;              // 1 = one serial accumulator (fan-out order), 0 = two accumulators
+    int32_t *dump;           // non-null: write int32 tile dots instead of y
+};
+void launch_gemv(const GemvArgs &a);
+
+// gemm_mma.cu
+struct GemmSegments {
+    int count;
+    int end[8];     // in 8-token groups
+    int split[8];
+};
+struct GemmArgs {
+    const uint8_t *codes[4];
+    const uint16_t *scales[4];
+    float *y[4];
+    int M[4];
+    int goff[5];
+    int count;
+    const int8_t *aq;
+    const float *as;
+    const int32_t *asum;
+    int K, ksh, T;
+    GemmSegments seg[4];     // per weight (each keeps the splits it would get alone)
+    int max_splits;
+    int32_t *dump;           // non-null: write int32 tile dots (single weight)
+};
+void launch_gemm_mma(const GemmArgs &a);
+
+// gemm_tc.cu (tcgen05 path, unsplit, per-token or per-block scales)
+struct GemmTcArgs {
+    const uint8_t *codes;
+    const uint16_t *scales;
+    const int8_t *aq;
+    const float *as;         // per (kt, tok) scales, or nullptr in per-token mode
+    const float *as_tok;     // per-token scales, or nullptr
+    const int32_t *asum;
+    void *y;
+    int M, K, ksh, T;
+    int out_bf16;
+};
+int launch_gemm_tc(const GemmTcArgs &a);   // returns 0, or <0 when the shape is not covered
+
+// repack.cu
+void launch_w4_repack(const uint8_t *d_payload, const float *d_bs, int scale_cols, int M, int K,
+                      int mode, uint8_t *d_codes, uint16_t *d_scales);
+
+// ---- device helpers ---------------------------------------------------------------
+#ifdef __CUDACC__
+
+// exp() built only from IEEE add/mul/fma so that host and device agree bit-for-bit
+// (the reference's sycl::exp is implementation-defined within 3 ulp).
+__device__ __forceinline__ float det_expf(float x) {
+    if (x != x) return x;
+    if (x > 88.72283935546875f) return __int_as_float(0x7F800000);
+    if (x < -103.97208404541015625f) return 0.0f;
+    const float n = rintf(__fmul_rn(x, 1.44269502162933349609375f));
+    float r = fmaf(n, -0.693145751953125f, x);
+    r = fmaf(n, -1.428606765330187045e-06f, r);
+    float p = 1.9875691500e-4f;
+    p = fmaf(p, r, 1.3981999507e-3f);
+    p = fmaf(p, r, 8.3334519073e-3f);
+    p = fmaf(p, r, 4.1665795894e-2f);
+    p = fmaf(p, r, 1.6666665459e-1f);
+    p = fmaf(p, r, 5.0000001201e-1f);
+    p = fmaf(__fmul_rn(p, r), r, r);
+    p = __fadd_rn(p, 1.0f);
+    const int ni = (int)n;
+    const int n1 = ni / 2, n2 = ni - n1;
+    const float s1 = __int_as_float((n1 + 127) << 23);
+    const float s2 = __int_as_float((n2 + 127) << 23);
+    return __fmul_rn(__fmul_rn(p, s1), s2);
+}
+
+__device__ __forceinline__ float silu_mul_f(float g, float up) {
+    return __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, det_expf(-g))), up);
+}
+
+__device__ __forceinline__ float clampf(float x, float lo, float hi) {
+    return fminf(fmaxf(x, lo), hi);   // NaN clamps to lo, as sycl::clamp does on the device
+}
+
+// Packed scale word -> fp32 scale and signed 4-bit zero point
+// (kernels_dpas.cpp:629-634).
+__device__ __forceinline__ void unpack_scale(uint32_t packed, int &zp, float &ws) {
+    zp = ((int)(packed << 28)) >> 28;
+    ws = __half2float(__ushort_as_half((unsigned short)(packed & 0xFFF0u)));
+}
+
+__device__ __forceinline__ uint4 ldg_stream_v4(const void *p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint32_t ldg_stream_u32(const void *p) {
+    uint32_t v;
+    asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v) : "l"(p));
+    return v;
+}
+
+#endif  // __CUDACC__
+
+}  // namespace tq

@@ -1,0 +1,520 @@
+// dispatch.cu — the projection API of the library: argument checks, split heuristics,
+// tier routing and launches. Same names, argument meaning and return codes as
+// xpu/src/kernels_dpas.cpp (x_* functions) and xpu/src/kernels_core.cpp:164-252.
+#include "common.cuh"
+
+#include <algorithm>
+#include <string.h>
+
+namespace tq {
+
+// xpu/src/kernels_dpas.cpp:170-173
+int choose_gemv_splits(int groups) {
+    if (groups <= 4) return 16;
+    return groups >= 4096 ? 1 : 8;
+}
+
+// xpu/src/kernels_dpas.cpp:1226-1250, TQ_XPU_GEMM_SPLITS read once like the reference.
+int choose_gemm_splits(int rgroups, int tgroups, int ktiles) {
+    static const int forced = [] {
+        const char *e = getenv("TQ_XPU_GEMM_SPLITS");
+        if (!e || !*e) return 0;
+        const int v = atoi(e);
+        return (v == 1 || v == 2 || v == 4 || v == 8 || v == 16) ? v : 0;
+    }();
+    const long tasks = (long)rgroups * tgroups;
+    if (tasks <= 0) return 1;
+    if (forced) {
+        int s = forced;
+        while (s > 1 && s > ktiles) s >>= 1;
+        return s;
+    }
+    const long want = 128L * 16;
+    if (tasks >= want) return 1;
+    for (int s = 2; s <= 16; s <<= 1) {
+        if (s > ktiles) break;
+        if (tasks * s >= want) return s;
+    }
+    int s = 16;
+    while (s > 1 && s > ktiles) s >>= 1;
+    return s;
+}
+
+namespace {
+
+bool w4_usable(const tq_qmma_weight_t *w) {
+    return w && w->s4_ready && w->d_s4 && w->d_s4_scale;
+}
+
+int gemv_prepared_impl(const tq_qmma_weight_t *w, float *d_y, const float *d_residual,
+                       int32_t *dump) {
+    if (!w4_usable(w) || (!d_y && !dump)) return -1;
+    ActScratch &s = act_scratch();
+    if (s.cap < w->K || !s.q || !s.scale || s.prepared_K < w->K) return -2;
+    if (w->s4_k16) return -20;   // K16 tier is not built
+    if (w->M % 16 || w->K % 32) return -1;
+    GemvArgs a{};
+    a.codes[0] = w->d_s4;
+    a.scales[0] = w->d_s4_scale;
+    a.y[0] = d_y;
+    a.goff[0] = 0;
+    a.goff[1] = w->M / 16;
+    a.count = 1;
+    a.qp = s.qp;
+    a.as = s.scale;
+    a.sum32 = s.sum32;
+    a.residual = d_residual;
+    a.K = w->K;
+    a.ksh = w->s4_k64 ? 1 : 0;
+    a.splits = choose_gemv_splits(w->M / 16);
+    a.serial = 0;
+    a.dump = dump;
+    launch_gemv(a);
+    return 0;
+}
+
+// Segment table + per-weight split counts (kernels_dpas.cpp:1343-1367).
+int build_segments(int rgroups, int Kt, int T, const int *offsets, int segments,
+                   GemmSegments &out, int &max_splits) {
+    const int tgroups = T / 8;
+    max_splits = 1;
+    if (offsets) {
+        if (segments < 1 || segments > 8 || offsets[0] != 0 || offsets[segments] != T) return -2;
+        out.count = segments;
+        for (int i = 0; i < segments; ++i) {
+            if (offsets[i] < 0 || offsets[i + 1] <= offsets[i] || offsets[i + 1] > T ||
+                offsets[i] % 8 || offsets[i + 1] % 8)
+                return -2;
+            out.end[i] = offsets[i + 1] / 8;
+            out.split[i] = choose_gemm_splits(rgroups, (offsets[i + 1] - offsets[i]) / 8, Kt);
+            max_splits = std::max(max_splits, out.split[i]);
+        }
+    } else {
+        if (segments != 0) return -2;
+        out.count = 1;
+        out.end[0] = tgroups;
+        out.split[0] = max_splits = choose_gemm_splits(rgroups, tgroups, Kt);
+    }
+    return 0;
+}
+
+}  // namespace
+}  // namespace tq
+
+using namespace tq;
+
+// ---- repack -------------------------------------------------------------------------
+int x_w4_repack_weight_mode(tq_qmma_weight_t *w, int mode) {
+    if (!w || !w->d_A || !w->d_block_scale_inv || !w->block_scaled || !w->e2m3) return -1;
+    if (w->M % 16 || w->K % 128) return -2;
+    if (mode == 2 && (w->Kt & 1)) return -3;
+    const size_t code_bytes = (size_t)w->Mt * w->Kt * 256u;
+    const size_t scale_groups = (mode == 1) ? (size_t)w->Kt * 2u
+                              : (mode == 2) ? (size_t)w->Kt / 2u : (size_t)w->Kt;
+    const size_t scale_bytes = (size_t)w->M * scale_groups * sizeof(uint16_t);
+    w->d_s4 = static_cast<uint8_t *>(tq_dev_alloc(code_bytes, "w4.codes"));
+    w->d_s4_scale = static_cast<uint16_t *>(tq_dev_alloc(scale_bytes, "w4.scales"));
+    launch_w4_repack(w->d_A, w->d_block_scale_inv, w->scale_cols, w->M, w->K, mode, w->d_s4,
+                     w->d_s4_scale);
+    tq_sync();
+    tq_dev_free(w->d_A);
+    tq_dev_free(w->d_block_scale_inv);
+    w->d_A = nullptr;
+    w->d_block_scale_inv = nullptr;
+    w->s4_k16 = (mode == 1) ? 1 : 0;
+    w->s4_k64 = (mode == 2) ? 1 : 0;
+    w->s4_ready = 1;
+    return 0;
+}
+
+int x_w4_repack_weight(tq_qmma_weight_t *w) { return x_w4_repack_weight_mode(w, 0); }
+
+// ---- decode staging -------------------------------------------------------------------
+void x_quantize_act_s8(const float *d_x, int K, int8_t *d_q, float *d_scale, int32_t *d_sum) {
+    if (!d_x || !d_q || !d_scale || K <= 0) return;
+    launch_quant_s8(d_x, nullptr, nullptr, K, d_q, nullptr, d_scale, d_sum, nullptr, false);
+}
+
+void x_prepare_gemv_act_s8(const float *d_x, int K) {
+    if (!d_x || K <= 0 || (K % 32) != 0) return;
+    ensure_act_scratch(K);
+    ActScratch &s = act_scratch();
+    launch_quant_s8(d_x, nullptr, nullptr, K, s.q, s.qp, s.scale, s.sum16, s.sum32, false);
+    s.prepared_K = K;
+}
+
+void x_silu_mul_quant(float *d_out, const float *d_gate, const float *d_up, int K) {
+    if (!d_out || !d_gate || !d_up || K <= 0 || (K % 32) != 0) return;
+    ensure_act_scratch(K);
+    ActScratch &s = act_scratch();
+    launch_quant_s8(d_gate, d_up, d_out, K, s.q, s.qp, s.scale, s.sum16, s.sum32, true);
+    s.prepared_K = K;
+}
+
+void x_rmsnorm_quant(float *d_out, const float *d_in, const uint16_t *d_w, int H, float eps) {
+    if (!d_out || !d_in || !d_w || H <= 0 || (H % 32) != 0) return;
+    ensure_act_scratch(H);
+    ActScratch &s = act_scratch();
+    launch_rmsnorm_quant(d_out, d_in, d_w, H, eps, s.norm_partial, s.q, s.qp, s.scale, s.sum16,
+                         s.sum32);
+    s.prepared_K = H;
+}
+
+void x_silu_mul(float *d_out, const float *d_gate, const float *d_up, int N) {
+    if (!d_out || !d_gate || !d_up || N <= 0) return;
+    launch_silu_mul(d_out, d_gate, d_up, N);
+}
+
+void x_add_inplace(float *d_x, const float *d_y, int N) {
+    if (!d_x || !d_y || N <= 0) return;
+    launch_add_inplace(d_x, d_y, N);
+}
+
+// ---- GEMV ---------------------------------------------------------------------------
+int x_gemv_w4a8_prepared(const tq_qmma_weight_t *w, float *d_y, const float *d_residual) {
+    return gemv_prepared_impl(w, d_y, d_residual, nullptr);
+}
+
+int x_gemv_w4a8(const tq_qmma_weight_t *w, const float *d_x, float *d_y) {
+    if (!w || !d_x) return -1;
+    x_prepare_gemv_act_s8(d_x, w->K);
+    return gemv_prepared_impl(w, d_y, nullptr, nullptr);
+}
+
+int x_gemv_w4a8_add(const tq_qmma_weight_t *w, const float *d_x, const float *d_residual,
+                    float *d_y) {
+    if (!w || !d_x || !d_residual) return -1;
+    x_prepare_gemv_act_s8(d_x, w->K);
+    return gemv_prepared_impl(w, d_y, d_residual, nullptr);
+}
+
+int x_gemv_w4a8_fanout(const tq_qmma_weight_t *const *ws, float *const *ys, int count) {
+    if (!ws || !ys || count <= 0 || count > 4) return -1;
+    if (!ws[0]) return -2;
+    GemvArgs a{};
+    const int K = ws[0]->K;
+    const int ksh = ws[0]->s4_k64 ? 1 : 0;
+    a.goff[0] = 0;
+    for (int i = 0; i < count; ++i) {
+        const tq_qmma_weight_t *w = ws[i];
+        if (!w || !w->s4_ready || w->s4_k16 || !w->d_s4 || !w->d_s4_scale || !ys[i] ||
+            w->K != K || (w->M % 16) || (w->s4_k64 ? 1 : 0) != ksh)
+            return -2;
+        a.codes[i] = w->d_s4;
+        a.scales[i] = w->d_s4_scale;
+        a.y[i] = ys[i];
+        a.goff[i + 1] = a.goff[i] + w->M / 16;
+    }
+    ActScratch &s = act_scratch();
+    if (s.cap < K || !s.q || !s.scale || s.prepared_K < K) return -3;
+    a.count = count;
+    a.qp = s.qp;
+    a.as = s.scale;
+    a.sum32 = s.sum32;
+    a.residual = nullptr;
+    a.K = K;
+    a.ksh = ksh;
+    a.splits = choose_gemv_splits(a.goff[count]);
+    a.serial = 1;
+    a.dump = nullptr;
+    launch_gemv(a);
+    return 0;
+}
+
+// ---- tier dispatchers (xpu/src/kernels_core.cpp:164-252) -------------------------------
+int x_gemv_qmma(const tq_qmma_weight_t *w, const float *d_x, float *d_y) {
+    if (!w || !d_x || !d_y) return -1;
+    if (w->M <= 0 || w->K <= 0 || w->Mt <= 0 || w->Kt <= 0) return -2;
+    if (w->s8_ready) return -20;              // W8A8 tier is not built
+    if (w->s4_ready) return x_gemv_w4a8(w, d_x, d_y);
+    return -20;                               // scalar E2M3 tier is not built
+}
+
+int x_gemv_qmma_add(const tq_qmma_weight_t *w, const float *d_x, const float *d_residual,
+                    float *d_y) {
+    if (!w || !d_x || !d_residual || !d_y) return -1;
+    if (w->s8_ready) return -20;
+    if (w->s4_ready) return x_gemv_w4a8_add(w, d_x, d_residual, d_y);
+    return -20;
+}
+
+int x_gemv_qmma_prepared(const tq_qmma_weight_t *w, const float *d_x, float *d_y,
+                         const float *d_residual) {
+    if (!w || !d_x || !d_y) return -1;
+    if (w->s8_ready) return -20;
+    if (w->s4_ready) return x_gemv_w4a8_prepared(w, d_y, d_residual);
+    return -20;
+}
+
+// ---- chunk staging + GEMM ------------------------------------------------------------------
+void x_quantize_act_chunk(const float *d_x, int K, int T, int8_t *d_aq, float *d_as,
+                          int32_t *d_asum) {
+    if (!d_x || !d_aq || !d_as || !d_asum || K <= 0 || T <= 0 || (K % 32) != 0) return;
+    launch_quant_chunk(d_x, K, T, d_aq, d_as, d_asum);
+}
+
+void x_quantize_act_chunk_pertoken(const float *d_x, int K, int T, int8_t *d_aq, float *d_as,
+                                   int32_t *d_asum, float *d_as_tok) {
+    if (!d_x || !d_aq || !d_as || !d_asum || !d_as_tok || K <= 0 || T <= 0 || (K % 32) != 0)
+        return;
+    launch_quant_chunk_pertoken(d_x, K, T, d_aq, d_as, d_asum, d_as_tok);
+}
+
+int x_gemm_w4a8_fanout(const tq_qmma_weight_t *const *ws, float *const *ys, int count,
+                       const int8_t *d_aq, const float *d_as, const int32_t *d_asum, int T,
+                       const int *offsets, int segments) {
+    if (!ws || !ys || count <= 0 || count > 4 || !ws[0]) return -1;
+    GemmArgs a{};
+    const int K = ws[0]->K;
+    const int ksh = ws[0]->s4_k64 ? 1 : 0;
+    for (int i = 0; i < count; ++i) {
+        const tq_qmma_weight_t *w = ws[i];
+        if (!w || !w->s4_ready || w->s4_k16 || !w->d_s4 || !w->d_s4_scale) return -1;
+        if (w->K != K || (w->s4_k64 ? 1 : 0) != ksh || (w->M % 16) || (K % 32)) return -1;
+    }
+    if (!d_aq || !d_as || !d_asum || T <= 0 || (T % 8) != 0) return -2;
+    a.goff[0] = 0;
+    a.max_splits = 1;
+    for (int i = 0; i < count; ++i) {
+        if (!ys[i]) return -2;
+        const tq_qmma_weight_t *w = ws[i];
+        a.codes[i] = w->d_s4;
+        a.scales[i] = w->d_s4_scale;
+        a.y[i] = ys[i];
+        a.M[i] = w->M;
+        a.goff[i + 1] = a.goff[i] + w->M / 16;
+        int ms = 1;
+        const int rc = build_segments(w->M / 16, K / 32, T, offsets, segments, a.seg[i], ms);
+        if (rc) return rc;
+        a.max_splits = std::max(a.max_splits, ms);
+    }
+    a.count = count;
+    a.aq = d_aq;
+    a.as = d_as;
+    a.asum = d_asum;
+    a.K = K;
+    a.ksh = ksh;
+    a.T = T;
+    a.dump = nullptr;
+    launch_gemm_mma(a);
+    return 0;
+}
+
+int x_gemm_w4a8(const tq_qmma_weight_t *w, const int8_t *d_aq, const float *d_as,
+                const int32_t *d_asum, float *d_y, int T, const int *offsets, int segments) {
+    if (!w || !w->s4_ready || w->s4_k16 || !w->d_s4 || !w->d_s4_scale) return -1;
+    if (!d_aq || !d_as || !d_asum || !d_y || T <= 0 || (T % 8) != 0) return -2;
+    // Unsplit large-T calls go to the tcgen05 kernel when it covers the shape.
+    if (offsets == nullptr || segments >= 1) {
+        GemmSegments seg{};
+        int ms = 1;
+        const int rc = build_segments(w->M / 16, w->K / 32, T, offsets, segments, seg, ms);
+        if (rc) return rc;
+        if (ms == 1) {
+            GemmTcArgs t{};
+            t.codes = w->d_s4; t.scales = w->d_s4_scale; t.aq = d_aq; t.as = d_as;
+            t.as_tok = nullptr; t.asum = d_asum; t.y = d_y; t.M = w->M; t.K = w->K;
+            t.ksh = w->s4_k64 ? 1 : 0; t.T = T; t.out_bf16 = 0;
+            if (launch_gemm_tc(t) == 0) return 0;
+        }
+    }
+    const tq_qmma_weight_t *ws[1] = {w};
+    float *ys[1] = {d_y};
+    return x_gemm_w4a8_fanout(ws, ys, 1, d_aq, d_as, d_asum, T, offsets, segments);
+}
+
+int x_gemm_w4a8_pertoken(const tq_qmma_weight_t *w, const int8_t *d_aq, const float *d_as_tok,
+                         const int32_t *d_asum, void *d_y, int T, int out_bf16) {
+    if (!w || !w->s4_ready || w->s4_k16 || !w->d_s4 || !w->d_s4_scale) return -1;
+    if (!d_aq || !d_as_tok || !d_asum || !d_y || T <= 0 || (T % 8) != 0) return -2;
+    GemmTcArgs t{};
+    t.codes = w->d_s4; t.scales = w->d_s4_scale; t.aq = d_aq; t.as = nullptr;
+    t.as_tok = d_as_tok; t.asum = d_asum; t.y = d_y; t.M = w->M; t.K = w->K;
+    t.ksh = w->s4_k64 ? 1 : 0; t.T = T; t.out_bf16 = out_bf16;
+    const int rc = launch_gemm_tc(t);
+    return rc == 0 ? 0 : -3;   // -3: shape not covered by the per-token kernel
+}
+
+// ---- tensor-parallel column shard (xpu/src/kernels_dpas.cpp:450-499, 549-556) ------------
+int x_w4_shard(tq_qmma_weight_t *dst, const tq_qmma_weight_t *src, int rank, int tp, int mode,
+               const int *groups, int ngroups) {
+    if (!dst || !src || !src->s4_ready || !src->d_s4 || !src->d_s4_scale) return -1;
+    if (tp < 1 || rank < 0 || rank >= tp) return -2;
+    const int ksh = src->s4_k64 ? 1 : 0;
+    if (src->s4_k16) return -3;
+    if (mode != 0) return -9;   // row-parallel and replicate shards are not built
+    const int Kt = src->Kt;
+    const int sg = Kt >> ksh;
+    int gs[8];
+    const int ng = (groups && ngroups > 0) ? ngroups : 1;
+    if (ng > 8) return -4;
+    if (groups && ngroups > 0) {
+        int total = 0;
+        for (int i = 0; i < ng; ++i) { gs[i] = groups[i]; total += gs[i]; }
+        if (total != src->M) return -5;
+    } else {
+        gs[0] = src->M;
+    }
+    for (int i = 0; i < ng; ++i)
+        if (gs[i] % (16 * tp)) return -6;
+    *dst = *src;
+    dst->d_A = nullptr;
+    dst->d_block_scale_inv = nullptr;
+    const int Mnew = src->M / tp;
+    dst->M = Mnew;
+    dst->Mt = Mnew / 16;
+    dst->d_s4 = static_cast<uint8_t *>(tq_dev_alloc((size_t)dst->Mt * Kt * 256u, "shard.codes"));
+    dst->d_s4_scale =
+        static_cast<uint16_t *>(tq_dev_alloc((size_t)Mnew * sg * 2u, "shard.scales"));
+    size_t src_g = 0, dst_g = 0;
+    for (int i = 0; i < ng; ++i) {
+        const size_t gtot = (size_t)gs[i] / 16;
+        const size_t gper = gtot / (size_t)tp;
+        const size_t from = src_g + gper * (size_t)rank;
+        tq_d2d_async(dst->d_s4 + dst_g * Kt * 256u, src->d_s4 + from * Kt * 256u,
+                     gper * Kt * 256u);
+        tq_d2d_async(dst->d_s4_scale + dst_g * (size_t)sg * 16u,
+                     src->d_s4_scale + from * (size_t)sg * 16u,
+                     gper * (size_t)sg * 16u * sizeof(uint16_t));
+        src_g += gtot;
+        dst_g += gper;
+    }
+    tq_sync();
+    return 0;
+}
+
+void x_w4_shard_free(tq_qmma_weight_t *w) {
+    if (!w) return;
+    tq_dev_free(w->d_s4);
+    tq_dev_free(w->d_s4_scale);
+    w->d_s4 = nullptr;
+    w->d_s4_scale = nullptr;
+    w->s4_ready = 0;
+}
+
+// ---- flat C entry points ---------------------------------------------------------------
+extern "C" {
+
+int qwn_x_w4_repack_weight(tq_qmma_weight_t *w) { return x_w4_repack_weight(w); }
+int qwn_x_w4_repack_weight_mode(tq_qmma_weight_t *w, int mode) {
+    return x_w4_repack_weight_mode(w, mode);
+}
+void qwn_x_quantize_act_s8(const float *d_x, int K, int8_t *d_q, float *d_scale, int32_t *d_sum) {
+    x_quantize_act_s8(d_x, K, d_q, d_scale, d_sum);
+}
+void qwn_x_prepare_gemv_act_s8(const float *d_x, int K) { x_prepare_gemv_act_s8(d_x, K); }
+void qwn_x_silu_mul_quant(float *d_out, const float *d_gate, const float *d_up, int K) {
+    x_silu_mul_quant(d_out, d_gate, d_up, K);
+}
+void qwn_x_rmsnorm_quant(float *d_out, const float *d_in, const uint16_t *d_w, int H, float eps) {
+    x_rmsnorm_quant(d_out, d_in, d_w, H, eps);
+}
+int qwn_x_gemv_w4a8(const tq_qmma_weight_t *w, const float *d_x, float *d_y) {
+    return x_gemv_w4a8(w, d_x, d_y);
+}
+int qwn_x_gemv_w4a8_add(const tq_qmma_weight_t *w, const float *d_x, const float *d_residual,
+                        float *d_y) {
+    return x_gemv_w4a8_add(w, d_x, d_residual, d_y);
+}
+int qwn_x_gemv_w4a8_prepared(const tq_qmma_weight_t *w, float *d_y, const float *d_residual) {
+    return x_gemv_w4a8_prepared(w, d_y, d_residual);
+}
+int qwn_x_gemv_w4a8_fanout(const tq_qmma_weight_t *const *ws, float *const *ys, int count) {
+    return x_gemv_w4a8_fanout(ws, ys, count);
+}
+int qwn_x_gemv_qmma(const tq_qmma_weight_t *w, const float *d_x, float *d_y) {
+    return x_gemv_qmma(w, d_x, d_y);
+}
+int qwn_x_gemv_qmma_add(const tq_qmma_weight_t *w, const float *d_x, const float *d_residual,
+                        float *d_y) {
+    return x_gemv_qmma_add(w, d_x, d_residual, d_y);
+}
+int qwn_x_gemv_qmma_prepared(const tq_qmma_weight_t *w, const float *d_x, float *d_y,
+                             const float *d_residual) {
+    return x_gemv_qmma_prepared(w, d_x, d_y, d_residual);
+}
+void qwn_x_silu_mul(float *d_out, const float *d_gate, const float *d_up, int N) {
+    x_silu_mul(d_out, d_gate, d_up, N);
+}
+void qwn_x_add_inplace(float *d_x, const float *d_y, int N) { x_add_inplace(d_x, d_y, N); }
+void qwn_x_quantize_act_chunk(const float *d_x, int K, int T, int8_t *d_aq, float *d_as,
+                              int32_t *d_asum) {
+    x_quantize_act_chunk(d_x, K, T, d_aq, d_as, d_asum);
+}
+int qwn_x_gemm_w4a8(const tq_qmma_weight_t *w, const int8_t *d_aq, const float *d_as,
+                    const int32_t *d_asum, float *d_y, int T, const int *offsets, int segments) {
+    return x_gemm_w4a8(w, d_aq, d_as, d_asum, d_y, T, offsets, segments);
+}
+int qwn_x_w4_shard(tq_qmma_weight_t *dst, const tq_qmma_weight_t *src, int rank, int tp, int mode,
+                   const int *groups, int ngroups) {
+    return x_w4_shard(dst, src, rank, tp, mode, groups, ngroups);
+}
+void qwn_x_w4_shard_free(tq_qmma_weight_t *w) { x_w4_shard_free(w); }
+int qwn_choose_gemv_splits(int groups) { return tq::choose_gemv_splits(groups); }
+int qwn_choose_gemm_splits(int rgroups, int tgroups, int ktiles) {
+    return tq::choose_gemm_splits(rgroups, tgroups, ktiles);
+}
+int qwn_x_gemm_w4a8_fanout(const tq_qmma_weight_t *const *ws, float *const *ys, int count,
+                           const int8_t *d_aq, const float *d_as, const int32_t *d_asum, int T,
+                           const int *offsets, int segments) {
+    return x_gemm_w4a8_fanout(ws, ys, count, d_aq, d_as, d_asum, T, offsets, segments);
+}
+void qwn_x_quantize_act_chunk_pertoken(const float *d_x, int K, int T, int8_t *d_aq, float *d_as,
+                                       int32_t *d_asum, float *d_as_tok) {
+    x_quantize_act_chunk_pertoken(d_x, K, T, d_aq, d_as, d_asum, d_as_tok);
+}
+int qwn_x_gemm_w4a8_pertoken(const tq_qmma_weight_t *w, const int8_t *d_aq, const float *d_as_tok,
+                             const int32_t *d_asum, void *d_y, int T, int out_bf16) {
+    return x_gemm_w4a8_pertoken(w, d_aq, d_as_tok, d_asum, d_y, T, out_bf16);
+}
+
+int qwn_dbg_tile_dots_gemv(const tq_qmma_weight_t *w, int32_t *d_out) {
+    if (!d_out) return -1;
+    return tq::gemv_prepared_impl(w, nullptr, nullptr, d_out);
+}
+
+int qwn_dbg_tile_dots_gemm(const tq_qmma_weight_t *w, const int8_t *d_aq, int T, int32_t *d_out) {
+    if (!w || !w->s4_ready || w->s4_k16 || !w->d_s4 || !w->d_s4_scale) return -1;
+    if (!d_aq || !d_out || T <= 0 || (T % 8) != 0) return -2;
+    tq::GemmArgs a{};
+    a.codes[0] = w->d_s4;
+    a.scales[0] = w->d_s4_scale;
+    a.M[0] = w->M;
+    a.goff[0] = 0;
+    a.goff[1] = w->M / 16;
+    a.count = 1;
+    a.aq = d_aq;
+    // The dot does not depend on scales or sums; the -8*asum correction does, so the
+    // debug launch needs true K32 sums: they are recomputed from the codes below.
+    a.K = w->K;
+    a.ksh = w->s4_k64 ? 1 : 0;
+    a.T = T;
+    a.seg[0].count = 1;
+    a.seg[0].end[0] = T / 8;
+    a.seg[0].split[0] = 1;
+    a.max_splits = 1;
+    a.dump = d_out;
+    const size_t nblk = (size_t)(w->K / 32) * T;
+    float *d_as = static_cast<float *>(tq_dev_alloc(nblk * 4, "dbg.as"));
+    int32_t *d_asum = static_cast<int32_t *>(tq_dev_alloc(nblk * 4, "dbg.asum"));
+    tq_dev_zero(d_as, nblk * 4);
+    tq::launch_code_sums(d_aq, nblk, d_asum);
+    a.as = d_as;
+    a.asum = d_asum;
+    tq::launch_gemm_mma(a);
+    tq_sync();
+    tq_dev_free(d_as);
+    tq_dev_free(d_asum);
+    return 0;
+}
+
+int qwn_dbg_prepared_act(int K, int8_t *d_q, float *d_scale, int32_t *d_sum) {
+    tq::ActScratch &s = tq::act_scratch();
+    if (K <= 0 || s.prepared_K < K) return -2;
+    if (d_q) tq_d2d_async(d_q, s.q, (size_t)K);
+    if (d_scale) tq_d2d_async(d_scale, s.scale, (size_t)(K / 32) * 4);
+    if (d_sum) tq_d2d_async(d_sum, s.sum16, (size_t)(K / 16) * 4);
+    return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,257 @@
+// quant.cu — activation quantisers of the W4A8 path and the fp32 glue beside them.
+//
+// All four follow the same per-block rule (xpu/src/kernels_dpas.cpp:203-206,
+// 1173-1178): mx = max |v| over a 32-element K block, s = mx > 0 ? mx/127 : 1,
+// q = clamp(rint(v / s), -127, 127) with a true division and round-half-even.
+// One 32-lane warp owns one K32 block, so the block maximum and the code sums
+// are warp shuffles. HBM traffic per block: 128 B in, 32 B codes + 8..16 B
+// scale/sums out.
+#include "common.cuh"
+
+namespace tq {
+
+namespace {
+
+constexpr int kWarpsPerBlock = 8;
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, off));
+    return v;
+}
+
+// Sum inside each 16-lane half (the K16 sums).
+__device__ __forceinline__ int half_sum16(int v) {
+#pragma unroll
+    for (int off = 8; off >= 1; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+    return v;
+}
+
+// Position of code k inside the permuted 32-byte tile (even-k codes, then odd-k).
+__device__ __forceinline__ int permuted_pos(int k) {
+    return ((k & 1) << 4) + ((k >> 3) << 2) + ((k & 7) >> 1);
+}
+
+__device__ __forceinline__ int quantise_one(float v, float s) {
+    return (int)clampf(rintf(__fdiv_rn(v, s)), -127.0f, 127.0f);
+}
+
+// Decode staging (x_quantize_act_s8 / x_prepare_gemv_act_s8 / x_silu_mul_quant).
+template <bool SILU>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+quant_s8_kernel(const float *__restrict__ x, const float *__restrict__ up,
+                float *__restrict__ hidden, int blocks, int8_t *__restrict__ q,
+                int8_t *__restrict__ qp, float *__restrict__ scale, int32_t *__restrict__ sum16,
+                int32_t *__restrict__ sum32) {
+    const int b = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (b >= blocks) return;
+    float v = x[b * 32 + lane];
+    if (SILU) {
+        v = silu_mul_f(v, up[b * 32 + lane]);
+        hidden[b * 32 + lane] = v;
+    }
+    const float mx = warp_max(fabsf(v));
+    const float s = (mx > 0.0f) ? __fdiv_rn(mx, 127.0f) : 1.0f;
+    const int qv = quantise_one(v, s);
+    const int hs = half_sum16(qv);
+    if (lane == 0) scale[b] = s;
+    if (sum16 && (lane & 15) == 0) sum16[b * 2 + (lane >> 4)] = hs;
+    if (sum32) {
+        const int other = __shfl_xor_sync(0xffffffffu, hs, 16);
+        if (lane == 0) sum32[b] = hs + other;
+    }
+    if (q) q[b * 32 + lane] = (int8_t)qv;
+    if (qp) qp[b * 32 + permuted_pos(lane)] = (int8_t)qv;
+}
+
+// Sum of squares per 256 elements: xor-butterfly in each warp, then the eight
+// warp sums added 0..7 (the order the CPU oracle restates).
+__global__ void __launch_bounds__(256)
+sumsq_partial_kernel(const float *__restrict__ in, int H, float *__restrict__ part) {
+    __shared__ float wsum[8];
+    const int i = blockIdx.x * 256 + threadIdx.x;
+    const float v = (i < H) ? in[i] : 0.0f;
+    float s = __fmul_rn(v, v);
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) s = __fadd_rn(s, __shfl_xor_sync(0xffffffffu, s, off));
+    if ((threadIdx.x & 31) == 0) wsum[threadIdx.x >> 5] = s;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) t = __fadd_rn(t, wsum[w]);
+        part[blockIdx.x] = t;
+    }
+}
+
+// Normalise + quantise in one pass (x_rmsnorm_quant, kernels_dpas.cpp:893-928).
+__global__ void __launch_bounds__(256)
+rmsnorm_quant_kernel(float *__restrict__ out, const float *__restrict__ in,
+                     const uint16_t *__restrict__ w, int H, float eps,
+                     const float *__restrict__ part, int nblk, int8_t *__restrict__ q,
+                     int8_t *__restrict__ qp, float *__restrict__ scale,
+                     int32_t *__restrict__ sum16, int32_t *__restrict__ sum32) {
+    __shared__ float s_rms;
+    if (threadIdx.x == 0) {
+        float sum_sq = 0.0f;
+        for (int b = 0; b < nblk; ++b) sum_sq = __fadd_rn(sum_sq, part[b]);
+        s_rms = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(sum_sq, (float)H), eps)));
+    }
+    __syncthreads();
+    const float rms_inv = s_rms;
+    const int i = blockIdx.x * 256 + threadIdx.x;
+    if (i >= H) return;   // H % 32 == 0, so whole warps leave together
+    const int lane = threadIdx.x & 31;
+    const float wf = __uint_as_float((uint32_t)w[i] << 16);
+    const float v = __fmul_rn(__fmul_rn(in[i], rms_inv), __fadd_rn(1.0f, wf));
+    out[i] = v;
+    const float mx = warp_max(fabsf(v));
+    const float s = (mx > 0.0f) ? __fdiv_rn(mx, 127.0f) : 1.0f;
+    const int qv = quantise_one(v, s);
+    const int hs = half_sum16(qv);
+    const int b = i >> 5;
+    if (lane == 0) scale[b] = s;
+    if ((lane & 15) == 0) sum16[b * 2 + (lane >> 4)] = hs;
+    const int other = __shfl_xor_sync(0xffffffffu, hs, 16);
+    if (lane == 0) sum32[b] = hs + other;
+    q[i] = (int8_t)qv;
+    qp[b * 32 + permuted_pos(lane)] = (int8_t)qv;
+}
+
+// Chunk staging (x_quantize_act_chunk): block index blk = kt*T + tok.
+// PER_TOKEN: the scale comes from as_tok[tok] instead of the block maximum.
+template <bool PER_TOKEN>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+quant_chunk_kernel(const float *__restrict__ x, int K, int T, size_t blocks,
+                   int8_t *__restrict__ aq, float *__restrict__ as, int32_t *__restrict__ asum,
+                   const float *__restrict__ as_tok) {
+    const size_t blk = (size_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (blk >= blocks) return;
+    const size_t kt = blk / (size_t)T, tok = blk % (size_t)T;
+    const float v = x[tok * (size_t)K + kt * 32 + lane];
+    float s;
+    if (PER_TOKEN) {
+        s = as_tok[tok];
+    } else {
+        const float mx = warp_max(fmaxf(-INFINITY, fabsf(v)));
+        s = (mx > 0.0f) ? __fdiv_rn(mx, 127.0f) : 1.0f;
+    }
+    const int qv = quantise_one(v, s);
+    int sum = half_sum16(qv);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 16);
+    aq[blk * 32 + lane] = (int8_t)qv;
+    if (lane == 0) {
+        as[blk] = s;
+        asum[blk] = sum;
+    }
+}
+
+// Per-token absmax -> scale (one block per token row).
+__global__ void __launch_bounds__(256)
+token_scale_kernel(const float *__restrict__ x, int K, float *__restrict__ as_tok) {
+    __shared__ float wmax[8];
+    const float *row = x + (size_t)blockIdx.x * K;
+    float m = -INFINITY;
+    for (int i = threadIdx.x; i < K; i += 256) m = fmaxf(m, fabsf(row[i]));
+    m = warp_max(m);
+    if ((threadIdx.x & 31) == 0) wmax[threadIdx.x >> 5] = m;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = wmax[0];
+#pragma unroll
+        for (int w = 1; w < 8; ++w) t = fmaxf(t, wmax[w]);
+        as_tok[blockIdx.x] = (t > 0.0f) ? __fdiv_rn(t, 127.0f) : 1.0f;
+    }
+}
+
+// K32 code sums of already staged codes (debug helper for the int32 dump).
+__global__ void code_sums_kernel(const int8_t *__restrict__ aq, size_t blocks,
+                                 int32_t *__restrict__ asum) {
+    const size_t blk = (size_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+    if (blk >= blocks) return;
+    int v = aq[blk * 32 + (threadIdx.x & 31)];
+    v = half_sum16(v);
+    v += __shfl_xor_sync(0xffffffffu, v, 16);
+    if ((threadIdx.x & 31) == 0) asum[blk] = v;
+}
+
+__global__ void silu_mul_kernel(float *__restrict__ out, const float *__restrict__ gate,
+                                const float *__restrict__ up, int N) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < N) out[i] = silu_mul_f(gate[i], up[i]);
+}
+
+__global__ void add_inplace_kernel(float *__restrict__ x, const float *__restrict__ y, int N) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < N) x[i] = __fadd_rn(x[i], y[i]);
+}
+
+}  // namespace
+
+void launch_quant_s8(const float *d_x, const float *d_up, float *d_hidden, int K, int8_t *d_q,
+                     int8_t *d_qp, float *d_scale, int32_t *d_sum16, int32_t *d_sum32, bool silu) {
+    const int blocks = K / 32;
+    if (blocks <= 0) return;
+    const int grid = (blocks + kWarpsPerBlock - 1) / kWarpsPerBlock;
+    if (silu)
+        quant_s8_kernel<true><<<grid, kWarpsPerBlock * 32, 0, stream()>>>(
+            d_x, d_up, d_hidden, blocks, d_q, d_qp, d_scale, d_sum16, d_sum32);
+    else
+        quant_s8_kernel<false><<<grid, kWarpsPerBlock * 32, 0, stream()>>>(
+            d_x, nullptr, nullptr, blocks, d_q, d_qp, d_scale, d_sum16, d_sum32);
+    TQ_LAUNCH_CHECK("quant_s8_kernel");
+}
+
+void launch_rmsnorm_quant(float *d_out, const float *d_in, const uint16_t *d_w, int H, float eps,
+                          float *d_partial, int8_t *d_q, int8_t *d_qp, float *d_scale,
+                          int32_t *d_sum16, int32_t *d_sum32) {
+    const int nblk = (H + 255) / 256;
+    sumsq_partial_kernel<<<nblk, 256, 0, stream()>>>(d_in, H, d_partial);
+    TQ_LAUNCH_CHECK("sumsq_partial_kernel");
+    rmsnorm_quant_kernel<<<nblk, 256, 0, stream()>>>(d_out, d_in, d_w, H, eps, d_partial, nblk,
+                                                      d_q, d_qp, d_scale, d_sum16, d_sum32);
+    TQ_LAUNCH_CHECK("rmsnorm_quant_kernel");
+}
+
+void launch_quant_chunk(const float *d_x, int K, int T, int8_t *d_aq, float *d_as,
+                        int32_t *d_asum) {
+    const size_t blocks = (size_t)(K / 32) * (size_t)T;
+    if (!blocks) return;
+    const unsigned grid = (unsigned)((blocks + kWarpsPerBlock - 1) / kWarpsPerBlock);
+    quant_chunk_kernel<false><<<grid, kWarpsPerBlock * 32, 0, stream()>>>(d_x, K, T, blocks, d_aq,
+                                                                          d_as, d_asum, nullptr);
+    TQ_LAUNCH_CHECK("quant_chunk_kernel");
+}
+
+void launch_quant_chunk_pertoken(const float *d_x, int K, int T, int8_t *d_aq, float *d_as,
+                                 int32_t *d_asum, float *d_as_tok) {
+    const size_t blocks = (size_t)(K / 32) * (size_t)T;
+    if (!blocks) return;
+    token_scale_kernel<<<T, 256, 0, stream()>>>(d_x, K, d_as_tok);
+    TQ_LAUNCH_CHECK("token_scale_kernel");
+    const unsigned grid = (unsigned)((blocks + kWarpsPerBlock - 1) / kWarpsPerBlock);
+    quant_chunk_kernel<true><<<grid, kWarpsPerBlock * 32, 0, stream()>>>(d_x, K, T, blocks, d_aq,
+                                                                         d_as, d_asum, d_as_tok);
+    TQ_LAUNCH_CHECK("quant_chunk_kernel<pertoken>");
+}
+
+void launch_code_sums(const int8_t *d_aq, size_t blocks, int32_t *d_asum) {
+    if (!blocks) return;
+    const unsigned grid = (unsigned)((blocks + kWarpsPerBlock - 1) / kWarpsPerBlock);
+    code_sums_kernel<<<grid, kWarpsPerBlock * 32, 0, stream()>>>(d_aq, blocks, d_asum);
+    TQ_LAUNCH_CHECK("code_sums_kernel");
+}
+
+void launch_silu_mul(float *d_out, const float *d_gate, const float *d_up, int N) {
+    silu_mul_kernel<<<(N + 255) / 256, 256, 0, stream()>>>(d_out, d_gate, d_up, N);
+    TQ_LAUNCH_CHECK("silu_mul_kernel");
+}
+
+void launch_add_inplace(float *d_x, const float *d_y, int N) {
+    add_inplace_kernel<<<(N + 255) / 256, 256, 0, stream()>>>(d_x, d_y, N);
+    TQ_LAUNCH_CHECK("add_inplace_kernel");
+}
+
+}  // namespace tq

@@ -1,0 +1,197 @@
+// runtime.cu — device runtime of the projection library: one in-order CUDA stream
+// per process/device, checked allocation and copies, the prepared-activation
+// scratch, events. Replaces the SYCL queue layer of xpu/src/decode.cpp:40-130.
+#include "common.cuh"
+
+#include <string.h>
+
+namespace tq {
+
+namespace {
+cudaStream_t g_stream = nullptr;
+int g_device = -1;
+int g_sticky_error = 0;
+ActScratch g_act;
+int *g_status_dev = nullptr;
+
+void init_device_once() {
+    if (g_stream) return;
+    if (g_device < 0) {
+        int dev = 0;
+        if (const char *e = getenv("TQ_XPU_DEV")) dev = atoi(e);   // same selector name
+        int n = 0;
+        if (cudaGetDeviceCount(&n) != cudaSuccess || n <= 0) {
+            fprintf(stderr, "forward_qwen_xpu(b200): no CUDA device found\n");
+            abort();
+        }
+        if (dev < 0 || dev >= n) dev = 0;
+        g_device = dev;
+    }
+    cudaError_t e = cudaSetDevice(g_device);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&g_stream, cudaStreamNonBlocking);
+    if (e != cudaSuccess) {
+        fprintf(stderr, "forward_qwen_xpu(b200): cannot create stream on device %d: %s\n",
+                g_device, cudaGetErrorString(e));
+        abort();
+    }
+}
+}  // namespace
+
+cudaStream_t stream() {
+    init_device_once();
+    return g_stream;
+}
+
+void note_error(cudaError_t e, const char *where) {
+    if (e == cudaSuccess) return;
+    if (!g_sticky_error) {
+        g_sticky_error = (int)e;
+        fprintf(stderr, "forward_qwen_xpu(b200): CUDA error %d (%s) at %s\n", (int)e,
+                cudaGetErrorString(e), where);
+    }
+}
+
+ActScratch &act_scratch() { return g_act; }
+
+void ensure_act_scratch(int K) {
+    ActScratch &s = g_act;
+    if (s.cap >= K) return;
+    // Stream order makes freeing safe: cudaFree waits for outstanding work.
+    if (s.q) tq_dev_free(s.q);
+    if (s.qp) tq_dev_free(s.qp);
+    if (s.scale) tq_dev_free(s.scale);
+    if (s.sum16) tq_dev_free(s.sum16);
+    if (s.sum32) tq_dev_free(s.sum32);
+    if (s.norm_partial) tq_dev_free(s.norm_partial);
+    s.q = static_cast<int8_t *>(tq_dev_alloc((size_t)K, "act.q8"));
+    s.qp = static_cast<int8_t *>(tq_dev_alloc((size_t)K, "act.q8.permuted"));
+    s.scale = static_cast<float *>(tq_dev_alloc((size_t)(K / 32) * sizeof(float), "act.scale"));
+    s.sum16 = static_cast<int32_t *>(tq_dev_alloc((size_t)(K / 16) * sizeof(int32_t), "act.sum16"));
+    s.sum32 = static_cast<int32_t *>(tq_dev_alloc((size_t)(K / 32) * sizeof(int32_t), "act.sum32"));
+    s.norm_partial = static_cast<float *>(
+        tq_dev_alloc((size_t)((K + 255) / 256) * sizeof(float), "norm.partial"));
+    s.cap = K;
+    s.prepared_K = 0;
+}
+
+int *device_status_word() {
+    if (!g_status_dev) {
+        g_status_dev = static_cast<int *>(tq_dev_alloc(sizeof(int), "status"));
+        TQ_CHECK(cudaMemsetAsync(g_status_dev, 0, sizeof(int), stream()));
+    }
+    return g_status_dev;
+}
+
+}  // namespace tq
+
+extern "C" {
+
+int tq_set_device(int device) {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess || device < 0 || device >= n) return -1;
+    if (tq::g_stream && device != tq::g_device) return -2;   // one device per process
+    tq::g_device = device;
+    tq::init_device_once();
+    return 0;
+}
+
+int tq_device(void) {
+    tq::init_device_once();
+    return tq::g_device;
+}
+
+void *tq_stream(void) { return (void *)tq::stream(); }
+
+void *tq_dev_alloc(size_t bytes, const char *what) {
+    tq::init_device_once();
+    void *p = nullptr;
+    cudaError_t e = cudaMalloc(&p, bytes ? bytes : 1);
+    if (e != cudaSuccess || !p) {
+        fprintf(stderr, "forward_qwen_xpu(b200): device alloc of %zu bytes failed (%s): %s\n",
+                bytes, what ? what : "?", cudaGetErrorString(e));
+        abort();
+    }
+    return p;
+}
+
+void tq_dev_free(void *p) {
+    if (p) TQ_CHECK(cudaFree(p));
+}
+
+void tq_h2d(void *dst, const void *src, size_t bytes) {
+    TQ_CHECK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, tq::stream()));
+    TQ_CHECK(cudaStreamSynchronize(tq::stream()));
+}
+
+void tq_d2h(void *dst, const void *src, size_t bytes) {
+    TQ_CHECK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, tq::stream()));
+    TQ_CHECK(cudaStreamSynchronize(tq::stream()));
+}
+
+void tq_dev_zero(void *dst, size_t bytes) {
+    TQ_CHECK(cudaMemsetAsync(dst, 0, bytes, tq::stream()));
+    TQ_CHECK(cudaStreamSynchronize(tq::stream()));
+}
+
+void tq_dev_fill(void *dst, int byte, size_t bytes) {
+    TQ_CHECK(cudaMemsetAsync(dst, byte, bytes, tq::stream()));
+}
+
+void tq_sync(void) {
+    TQ_CHECK(cudaStreamSynchronize(tq::stream()));
+    if (tq::g_status_dev && !tq::g_sticky_error) {
+        int st = 0;
+        if (cudaMemcpy(&st, tq::g_status_dev, sizeof(int), cudaMemcpyDeviceToHost) == cudaSuccess &&
+            st != 0) {
+            tq::g_sticky_error = 10000 + st;
+            fprintf(stderr, "forward_qwen_xpu(b200): device wait gave up, status %d\n", st);
+        }
+    }
+}
+
+int tq_last_error(void) { return tq::g_sticky_error; }
+
+void *tq_host_alloc_pinned(size_t bytes) {
+    tq::init_device_once();
+    void *p = nullptr;
+    if (cudaMallocHost(&p, bytes ? bytes : 1) != cudaSuccess) return nullptr;
+    return p;
+}
+
+void tq_host_free_pinned(void *p) {
+    if (p) TQ_CHECK(cudaFreeHost(p));
+}
+
+void tq_h2d_async(void *dst, const void *src, size_t bytes) {
+    TQ_CHECK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, tq::stream()));
+}
+
+void tq_d2h_async(void *dst, const void *src, size_t bytes) {
+    TQ_CHECK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, tq::stream()));
+}
+
+void tq_d2d_async(void *dst, const void *src, size_t bytes) {
+    TQ_CHECK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, tq::stream()));
+}
+
+void *tq_event_create(void) {
+    tq::init_device_once();
+    cudaEvent_t ev = nullptr;
+    TQ_CHECK(cudaEventCreate(&ev));
+    return (void *)ev;
+}
+
+void tq_event_destroy(void *ev) {
+    if (ev) TQ_CHECK(cudaEventDestroy((cudaEvent_t)ev));
+}
+
+void tq_event_record(void *ev) { TQ_CHECK(cudaEventRecord((cudaEvent_t)ev, tq::stream())); }
+
+float tq_event_elapsed_ms(void *start, void *stop) {
+    float ms = -1.0f;
+    TQ_CHECK(cudaEventSynchronize((cudaEvent_t)stop));
+    TQ_CHECK(cudaEventElapsedTime(&ms, (cudaEvent_t)start, (cudaEvent_t)stop));
+    return ms;
+}
+
+}  // extern "C"

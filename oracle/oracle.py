@@ -1,0 +1,301 @@
+"""numpy front-end to the CPU oracle (oracle/w4a8_oracle.c).
+
+Test infrastructure only: imported by tests/, by the smoke check and by the
+benchmark's CPU-baseline leg. The shipped library never loads it.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_SO = os.path.join(_HERE, "_build", "liboracle_w4a8.so")
+
+
+def build(force: bool = False) -> str:
+    src = os.path.join(_HERE, "w4a8_oracle.c")
+    if force or not os.path.exists(_SO) or os.path.getmtime(_SO) < os.path.getmtime(src):
+        subprocess.check_call(["make", "-C", _HERE], stdout=subprocess.DEVNULL)
+    return _SO
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        _lib = C.CDLL(build())
+        _lib.orc_e2m3f.restype = C.c_float
+        _lib.orc_e2m3f.argtypes = [C.c_uint32]
+        _lib.orc_f16_to_f32.restype = C.c_float
+        _lib.orc_f16_to_f32.argtypes = [C.c_uint16]
+        _lib.orc_f32_to_f16.restype = C.c_uint16
+        _lib.orc_f32_to_f16.argtypes = [C.c_float]
+        _lib.orc_expf.restype = C.c_float
+        _lib.orc_expf.argtypes = [C.c_float]
+        _lib.orc_fit_int4_asym.restype = C.c_uint16
+        _lib.orc_e2m3_code_at.restype = C.c_uint32
+    return _lib
+
+
+def _p(a):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+def _c(a, dt):
+    return np.ascontiguousarray(a, dtype=dt)
+
+
+# ------------------------------------------------------------------ scalars
+def f32_to_f16(x: float) -> int:
+    return int(lib().orc_f32_to_f16(C.c_float(x)))
+
+
+def f16_to_f32(h: int) -> float:
+    return float(lib().orc_f16_to_f32(C.c_uint16(h)))
+
+
+def expf(x: float) -> float:
+    return float(lib().orc_expf(C.c_float(x)))
+
+
+def e2m3f(code: int) -> float:
+    return float(lib().orc_e2m3f(C.c_uint32(code)))
+
+
+def choose_gemv_splits(groups: int) -> int:
+    return int(lib().orc_choose_gemv_splits(C.c_int(groups)))
+
+
+def choose_gemm_splits(rgroups: int, tgroups: int, ktiles: int, forced: int = 0) -> int:
+    return int(lib().orc_choose_gemm_splits(C.c_int(rgroups), C.c_int(tgroups),
+                                            C.c_int(ktiles), C.c_int(forced)))
+
+
+def fit_int4_asym(wf, reserve_nibble: bool = True):
+    wf = _c(wf, np.float32)
+    z = C.c_int(0)
+    sh = lib().orc_fit_int4_asym(_p(wf), C.c_int(wf.size), C.c_int(int(reserve_nibble)),
+                                 C.byref(z))
+    return int(sh), int(z.value)
+
+
+# --------------------------------------------------------- E2M3 payload
+def e2m3_payload_from_codes(codes6: np.ndarray) -> np.ndarray:
+    """codes6[M][K] (values 0..63) -> dense fragment payload [Mt*Kt*384] bytes."""
+    codes6 = _c(codes6, np.uint8)
+    M, K = codes6.shape
+    Kt = K // 32
+    payload = np.zeros((M // 16) * Kt * 384, dtype=np.uint8)
+    L = lib()
+    for r in range(M):
+        for c in range(K):
+            L.orc_e2m3_set_code(_p(payload), C.c_int(Kt), C.c_int(r), C.c_int(c),
+                                C.c_uint32(int(codes6[r, c])))
+    return payload
+
+
+def e2m3_payload_from_codes_fast(codes6: np.ndarray) -> np.ndarray:
+    """Vectorised form of e2m3_payload_from_codes (same closed-form map)."""
+    codes6 = _c(codes6, np.uint8).astype(np.uint32)
+    M, K = codes6.shape
+    Kt = K // 32
+    row = np.arange(M)[:, None]
+    col = np.arange(K)[None, :]
+    mt, kt = row >> 4, col >> 5
+    lane = (((row & 15) >> 1) << 2) | ((col & 31) >> 3)
+    idx = (((col >> 2) & 1) << 3) | ((row & 1) << 2) | (col & 3)
+    bit = 6 * idx
+    base = (mt * Kt + kt) * 384 + lane * 12
+    nbits = (Mt_ := M // 16) * Kt * 384 * 8
+    bitpos = (base * 8 + bit).astype(np.int64)
+    bits = np.zeros(nbits, dtype=np.uint8)
+    for b in range(6):
+        bits[(bitpos + b).ravel()] = ((codes6 >> b) & 1).astype(np.uint8).ravel()
+    return np.packbits(bits, bitorder="little")
+
+
+def e2m3_decode(payload, bs, scale_cols, M, K):
+    payload = _c(payload, np.uint8)
+    bs = _c(bs, np.float32)
+    W = np.empty((M, K), dtype=np.float32)
+    lib().orc_e2m3_decode(_p(payload), _p(bs), C.c_int(scale_cols), C.c_int(M), C.c_int(K), _p(W))
+    return W
+
+
+def scale_groups(K: int, mode: int) -> int:
+    Kt = K // 32
+    return Kt * 2 if mode == 1 else (Kt // 2 if mode == 2 else Kt)
+
+
+def w4_pack_from_f32(W, mode: int = 0):
+    W = _c(W, np.float32)
+    M, K = W.shape
+    codes = np.zeros(M * K // 2, dtype=np.uint8)
+    scales = np.zeros(M * scale_groups(K, mode), dtype=np.uint16)
+    rc = lib().orc_w4_pack_from_f32(_p(W), C.c_int(M), C.c_int(K), C.c_int(mode), _p(codes), _p(scales))
+    return rc, codes, scales
+
+
+def w4_repack(payload, bs, scale_cols, M, K, mode: int = 0):
+    payload = _c(payload, np.uint8)
+    bs = _c(bs, np.float32)
+    codes = np.zeros(M * K // 2, dtype=np.uint8)
+    scales = np.zeros(M * max(scale_groups(K, mode), 1), dtype=np.uint16)
+    rc = lib().orc_w4_repack(_p(payload), _p(bs), C.c_int(scale_cols), C.c_int(M), C.c_int(K),
+                             C.c_int(mode), _p(codes), _p(scales))
+    return rc, codes, scales
+
+
+def gemv_e2m3(payload, bs, scale_cols, M, K, x):
+    payload, bs, x = _c(payload, np.uint8), _c(bs, np.float32), _c(x, np.float32)
+    y = np.empty(M, dtype=np.float32)
+    lib().orc_gemv_e2m3(_p(payload), _p(bs), C.c_int(scale_cols), C.c_int(M), C.c_int(K), _p(x), _p(y))
+    return y
+
+
+# ---------------------------------------------------------- quantisers
+def quantize_act_s8(x):
+    x = _c(x, np.float32)
+    K = x.size
+    q = np.empty(K, dtype=np.int8)
+    s = np.empty(K // 32, dtype=np.float32)
+    sm = np.empty(K // 16, dtype=np.int32)
+    lib().orc_quantize_act_s8(_p(x), C.c_int(K), _p(q), _p(s), _p(sm))
+    return q, s, sm
+
+
+def silu_mul(gate, up):
+    gate, up = _c(gate, np.float32), _c(up, np.float32)
+    out = np.empty_like(gate)
+    lib().orc_silu_mul(_p(out), _p(gate), _p(up), C.c_int(gate.size))
+    return out
+
+
+def silu_mul_quant(gate, up):
+    gate, up = _c(gate, np.float32), _c(up, np.float32)
+    K = gate.size
+    hidden = np.empty(K, dtype=np.float32)
+    q = np.empty(K, dtype=np.int8)
+    s = np.empty(K // 32, dtype=np.float32)
+    sm = np.empty(K // 16, dtype=np.int32)
+    lib().orc_silu_mul_quant(_p(hidden), _p(gate), _p(up), C.c_int(K), _p(q), _p(s), _p(sm))
+    return hidden, q, s, sm
+
+
+def rmsnorm_quant(x, w_bf16, eps):
+    x, w = _c(x, np.float32), _c(w_bf16, np.uint16)
+    H = x.size
+    out = np.empty(H, dtype=np.float32)
+    q = np.empty(H, dtype=np.int8)
+    s = np.empty(H // 32, dtype=np.float32)
+    sm = np.empty(H // 16, dtype=np.int32)
+    lib().orc_rmsnorm_quant(_p(out), _p(x), _p(w), C.c_int(H), C.c_float(eps), _p(q), _p(s), _p(sm))
+    return out, q, s, sm
+
+
+def quantize_act_chunk(x, per_token: bool = False):
+    x = _c(x, np.float32)
+    T, K = x.shape
+    Kt = K // 32
+    aq = np.empty(Kt * T * 32, dtype=np.int8)
+    as_ = np.empty(Kt * T, dtype=np.float32)
+    asum = np.empty(Kt * T, dtype=np.int32)
+    fn = lib().orc_quantize_act_chunk_pertoken if per_token else lib().orc_quantize_act_chunk
+    fn(_p(x), C.c_int(K), C.c_int(T), _p(aq), _p(as_), _p(asum))
+    return aq, as_, asum
+
+
+# ------------------------------------------------------------- dots
+def tile_dots_gemv(codes, M, K, q):
+    codes, q = _c(codes, np.uint8), _c(q, np.int8)
+    d = np.empty((M // 16) * (K // 32) * 16, dtype=np.int32)
+    lib().orc_tile_dots_gemv(_p(codes), C.c_int(M), C.c_int(K), _p(q), _p(d))
+    return d
+
+
+def tile_dots_gemm(codes, M, K, aq, T):
+    codes, aq = _c(codes, np.uint8), _c(aq, np.int8)
+    d = np.empty((K // 32) * T * M, dtype=np.int32)
+    lib().orc_tile_dots_gemm(_p(codes), C.c_int(M), C.c_int(K), _p(aq), C.c_int(T), _p(d))
+    return d
+
+
+# ------------------------------------------------------------- GEMV / GEMM
+def gemv_w4a8(codes, scales, M, K, ksh, q, as_, sum16, residual=None, fma=1):
+    codes, scales = _c(codes, np.uint8), _c(scales, np.uint16)
+    q, as_, sum16 = _c(q, np.int8), _c(as_, np.float32), _c(sum16, np.int32)
+    res = None if residual is None else _c(residual, np.float32)
+    y = np.empty(M, dtype=np.float32)
+    rc = lib().orc_gemv_w4a8(_p(codes), _p(scales), C.c_int(M), C.c_int(K), C.c_int(ksh), _p(q),
+                             _p(as_), _p(sum16), _p(res), _p(y), C.c_int(fma))
+    return rc, y
+
+
+def gemv_w4a8_fanout(weights, K, ksh, q, as_, sum16, fma=1):
+    """weights: list of (codes, scales, M)."""
+    n = len(weights)
+    cs = [_c(w[0], np.uint8) for w in weights]
+    ss = [_c(w[1], np.uint16) for w in weights]
+    Ms = (C.c_int * n)(*[int(w[2]) for w in weights])
+    ys = [np.empty(int(w[2]), dtype=np.float32) for w in weights]
+    cp = (C.c_void_p * n)(*[a.ctypes.data for a in cs])
+    sp = (C.c_void_p * n)(*[a.ctypes.data for a in ss])
+    yp = (C.c_void_p * n)(*[a.ctypes.data for a in ys])
+    q, as_, sum16 = _c(q, np.int8), _c(as_, np.float32), _c(sum16, np.int32)
+    rc = lib().orc_gemv_w4a8_fanout(cp, sp, Ms, C.c_int(n), C.c_int(K), C.c_int(ksh), _p(q), _p(as_),
+                                    _p(sum16), yp, C.c_int(fma))
+    return rc, ys
+
+
+def gemm_w4a8(codes, scales, M, K, ksh, aq, as_, asum, T, offsets=None, forced_splits=0, fma=1):
+    codes, scales = _c(codes, np.uint8), _c(scales, np.uint16)
+    aq, as_, asum = _c(aq, np.int8), _c(as_, np.float32), _c(asum, np.int32)
+    y = np.empty((T, M), dtype=np.float32)
+    if offsets is not None:
+        off = (C.c_int * len(offsets))(*offsets)
+        nseg = len(offsets) - 1
+    else:
+        off, nseg = None, 0
+    rc = lib().orc_gemm_w4a8(_p(codes), _p(scales), C.c_int(M), C.c_int(K), C.c_int(ksh), _p(aq),
+                             _p(as_), _p(asum), _p(y), C.c_int(T), off, C.c_int(nseg),
+                             C.c_int(forced_splits), C.c_int(fma))
+    return rc, y
+
+
+def gemm_w4a8_pertoken(codes, scales, M, K, ksh, aq, as_tok, asum, T):
+    codes, scales = _c(codes, np.uint8), _c(scales, np.uint16)
+    aq, as_tok, asum = _c(aq, np.int8), _c(as_tok, np.float32), _c(asum, np.int32)
+    y = np.empty((T, M), dtype=np.float32)
+    rc = lib().orc_gemm_w4a8_pertoken(_p(codes), _p(scales), C.c_int(M), C.c_int(K), C.c_int(ksh),
+                                      _p(aq), _p(as_tok), _p(asum), _p(y), C.c_int(T))
+    return rc, y
+
+
+def w4_shard_column(codes, scales, M, K, ksh, rank, tp, groups=None, k16=0):
+    codes, scales = _c(codes, np.uint8), _c(scales, np.uint16)
+    Kt = K // 32
+    Mn = M // tp if tp >= 1 else M
+    dc = np.zeros(max(Mn, 16) * K // 2, dtype=np.uint8)
+    ds = np.zeros(max(Mn, 16) * (Kt >> ksh), dtype=np.uint16)
+    if groups:
+        g = (C.c_int * len(groups))(*groups)
+        ng = len(groups)
+    else:
+        g, ng = None, 0
+    rc = lib().orc_w4_shard_column(_p(codes), _p(scales), C.c_int(M), C.c_int(K), C.c_int(ksh),
+                                   C.c_int(k16), C.c_int(rank), C.c_int(tp), g, C.c_int(ng),
+                                   _p(dc), _p(ds))
+    return rc, dc[: Mn * K // 2], ds[: Mn * (Kt >> ksh)]
+
+
+def num_threads() -> int:
+    return int(lib().orc_num_threads())
+
+
+def set_num_threads(n: int) -> None:
+    lib().orc_set_num_threads(C.c_int(n))

@@ -1,0 +1,816 @@
+/*
+ * w4a8_oracle.c — CPU restatement of knivesysl-xe's W4A8 projection arithmetic.
+ *
+ * TEST INFRASTRUCTURE ONLY. Nothing in the shipped library links, loads or calls
+ * this file; it is the checker the CUDA kernels are compared with, and the timed
+ * "scalar projection semantics" CPU baseline of the benchmark.
+ *
+ * PARITY UNPINNED at the fp32 level: the reference (SYCL + inline Intel vISA,
+ * clang-only vector extensions) cannot be compiled or run without Intel's
+ * toolchain and GPU, and it ships no golden vectors or stored expected outputs
+ * for this path. What pins this restatement is (1) the source text it follows,
+ * cited per function as xpu/src/<file>:<lines>, (2) the int32 layer, which the
+ * source determines completely, and (3) the reference's own invariant gates
+ * (column-shard concat bit-identical, spec-wave prefix rows byte-identical,
+ * fused == unfused SiLU staging, GEMM-vs-GEMV cosine >= 0.9999), which the test
+ * suite re-runs against this file.
+ *
+ * Floating point: every expression keeps the reference's association. Where
+ * the reference's compiler was free to contract a*b+c into one FMA, each routine
+ * takes `fma`: 0 = separate multiply and add, 1 = fused. Build with
+ * -ffp-contract=off so only the explicit fmaf() calls fuse.
+ *
+ * Naming follows the reference: M = output rows of a weight, K = reduction,
+ * Mt = M/16 row-groups, Kt = K/32 k-tiles, T = token rows, ksh = 1 for the K64
+ * scale tier (one scale per pair of k-tiles), else 0.
+ */
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+#define ORC_API __attribute__((visibility("default")))
+
+/* ------------------------------------------------------------------ helpers */
+
+static inline float clampf(float x, float lo, float hi) {
+    /* sycl::clamp is fmin(fmax(x, lo), hi); with a NaN x the non-NaN operand
+     * wins, so NaN clamps to lo. */
+    return fminf(fmaxf(x, lo), hi);
+}
+
+static inline float bits_f32(uint32_t u) { float f; memcpy(&f, &u, 4); return f; }
+static inline uint32_t f32_bits(float f) { uint32_t u; memcpy(&u, &f, 4); return u; }
+
+/* IEEE binary16 <-> binary32, round-to-nearest-even, as sycl::half(float). */
+ORC_API uint16_t orc_f32_to_f16(float f) {
+    const uint32_t x = f32_bits(f);
+    const uint32_t sign = (x >> 16) & 0x8000u;
+    const uint32_t absx = x & 0x7FFFFFFFu;
+    if (absx >= 0x7F800000u)                       /* inf / nan */
+        return (uint16_t)(sign | 0x7C00u | ((absx > 0x7F800000u) ? 0x0200u : 0u));
+    if (absx >= 0x477FF000u) return (uint16_t)(sign | 0x7C00u);   /* rounds to inf */
+    if (absx < 0x33000001u) return (uint16_t)sign;                /* rounds to 0 */
+    int e = (int)(absx >> 23) - 127;
+    uint32_t m = (absx & 0x7FFFFFu) | 0x800000u;                  /* 24-bit */
+    int shift;
+    uint32_t he;
+    if (e < -14) { shift = 13 + (-14 - e); he = 0; }              /* subnormal half */
+    else { shift = 13; he = (uint32_t)(e + 15); }
+    uint32_t q = m >> shift;
+    const uint32_t rem = m & ((1u << shift) - 1u);
+    const uint32_t half = 1u << (shift - 1);
+    if (rem > half || (rem == half && (q & 1u))) ++q;
+    uint32_t h;
+    if (he == 0) h = q;                       /* q may carry into exponent 1 */
+    else h = ((he - 1) << 10) + q;            /* q includes the hidden bit */
+    return (uint16_t)(sign | h);
+}
+
+ORC_API float orc_f16_to_f32(uint16_t h) {
+    const uint32_t sign = ((uint32_t)h & 0x8000u) << 16;
+    const uint32_t e = (h >> 10) & 0x1Fu;
+    const uint32_t m = h & 0x3FFu;
+    if (e == 0) {
+        const float v = (float)m * 5.9604644775390625e-8f;   /* m * 2^-24 */
+        return (sign ? -v : v);
+    }
+    if (e == 31) return bits_f32(sign | 0x7F800000u | (m << 13));
+    return bits_f32(sign | ((e + 112u) << 23) | (m << 13));
+}
+
+static inline float bf16f(uint16_t b) { return bits_f32((uint32_t)b << 16); }
+
+/* One concrete exp(): the reference calls sycl::exp, whose bits depend on the
+ * device library (bound: 3 ulp). Fixing an implementation made only of IEEE
+ * add/mul/fma lets the CPU and GPU sides agree bit-for-bit. Error <= 1 ulp on
+ * the tested range. */
+ORC_API float orc_expf(float x) {
+    if (x != x) return x;
+    if (x > 88.72283935546875f) return INFINITY;
+    if (x < -103.97208404541015625f) return 0.0f;
+    const float n = rintf(x * 1.44269502162933349609375f);
+    float r = fmaf(n, -0.693145751953125f, x);             /* ln2 high part */
+    r = fmaf(n, -1.428606765330187045e-06f, r);            /* ln2 low part */
+    float p = 1.9875691500e-4f;
+    p = fmaf(p, r, 1.3981999507e-3f);
+    p = fmaf(p, r, 8.3334519073e-3f);
+    p = fmaf(p, r, 4.1665795894e-2f);
+    p = fmaf(p, r, 1.6666665459e-1f);
+    p = fmaf(p, r, 5.0000001201e-1f);
+    p = fmaf(p * r, r, r);
+    p = p + 1.0f;
+    const int ni = (int)n;
+    const int n1 = ni / 2, n2 = ni - n1;                   /* both within [-75, 64] */
+    const float s1 = bits_f32((uint32_t)(n1 + 127) << 23);
+    const float s2 = bits_f32((uint32_t)(n2 + 127) << 23);
+    return (p * s1) * s2;
+}
+
+/* ------------------------------------------------- E2M3 source payload (A1) */
+
+/* xpu/src/kernels_dpas.cpp:50-55 */
+ORC_API float orc_e2m3f(uint32_t c) {
+    const float m = (float)(c & 7u);
+    const uint32_t e = (c >> 3) & 3u;
+    const float v = (e == 0) ? m * 0.125f
+                             : (1.0f + m * 0.125f) * (float)(1u << (e - 1));
+    return (c & 0x20u) ? -v : v;
+}
+
+/* (row, col) -> byte position and bit offset of its 6-bit code inside the dense
+ * E2M3 fragment payload: xpu/src/kernels_dpas.cpp:59-69. */
+static inline void e2m3_locate(int Kt, int row, int col, size_t *byte, int *bit) {
+    const int mt = row >> 4;
+    const int kt = col >> 5;
+    const int lane = (((row & 15) >> 1) << 2) | ((col & 31) >> 3);
+    const int idx = (((col >> 2) & 1) << 3) | ((row & 1) << 2) | (col & 3);
+    const int b = 6 * idx;
+    *byte = ((size_t)mt * Kt + kt) * 384u + (size_t)lane * 12u + (size_t)(b >> 3);
+    *bit = b & 7;
+}
+
+ORC_API uint32_t orc_e2m3_code_at(const uint8_t *payload, int Kt, int row, int col) {
+    size_t byte; int bit;
+    e2m3_locate(Kt, row, col, &byte, &bit);
+    uint32_t bits = payload[byte];
+    if (bit > 2) bits |= (uint32_t)payload[byte + 1] << 8;
+    return (bits >> bit) & 0x3Fu;
+}
+
+/* Inverse of orc_e2m3_code_at, used by tests to build a source payload. */
+ORC_API void orc_e2m3_set_code(uint8_t *payload, int Kt, int row, int col, uint32_t code) {
+    size_t byte; int bit;
+    e2m3_locate(Kt, row, col, &byte, &bit);
+    uint32_t v = payload[byte];
+    if (bit > 2) v |= (uint32_t)payload[byte + 1] << 8;
+    v = (v & ~(0x3Fu << bit)) | ((code & 0x3Fu) << bit);
+    payload[byte] = (uint8_t)v;
+    if (bit > 2) payload[byte + 1] = (uint8_t)(v >> 8);
+}
+
+/* xpu/src/kernels_dpas.cpp:229-256. Returns the stored FP16 scale bits
+ * (low nibble cleared when reserve_nibble) and the zero point in *out_z. */
+ORC_API uint16_t orc_fit_int4_asym(const float *wf, int n, int reserve_nibble, int *out_z) {
+    float lo = 0.0f, hi = 0.0f;
+    for (int j = 0; j < n; ++j) { lo = fminf(lo, wf[j]); hi = fmaxf(hi, wf[j]); }
+    float s = (hi - lo) / 15.0f;
+    if (!(s > 0.0f)) s = 1.0f;
+    for (int iter = 0; iter < 3; ++iter) {
+        const int zi = (int)clampf(rintf(-lo / s) - 8.0f, -8.0f, 7.0f);
+        float num = 0.0f, den = 0.0f;
+        for (int j = 0; j < n; ++j) {
+            const float q = clampf(rintf(wf[j] / s + (float)zi), -8.0f, 7.0f);
+            const float centered = q - (float)zi;
+            num += wf[j] * centered;
+            den += centered * centered;
+        }
+        if (den > 0.0f) s = num / den;
+    }
+    *out_z = (int)clampf(rintf(-lo / s) - 8.0f, -8.0f, 7.0f);
+    uint16_t sh = orc_f32_to_f16(s);
+    if (reserve_nibble) sh = (uint16_t)((sh + 8u) & 0xFFF0u);
+    return sh;
+}
+
+/* Group fit + pack from fp32 weights W[M][K] (row-major) into the packed W4
+ * record: xpu/src/kernels_dpas.cpp:266-344 with the E2M3 decode factored out.
+ * mode 0: one scale per K32; 1: per K16; 2: per K64 (Kt must be even).
+ * codes: [Mt][Kt][16 rows][16 B]; scales: [Mt][groups][16] u16. */
+ORC_API int orc_w4_pack_from_f32(const float *W, int M, int K, int mode,
+                                 uint8_t *codes, uint16_t *scales) {
+    if (M % 16 || K % 32) return -2;
+    const int Kt = K / 32;
+    if (mode == 2 && (Kt & 1)) return -3;
+#pragma omp parallel for schedule(static)
+    for (int row = 0; row < M; ++row) {
+        for (int kt = 0; kt < Kt; ++kt) {
+            const float *wf = W + (size_t)row * K + (size_t)kt * 32;
+            const int rowgroup = row >> 4, n = row & 15;
+            float gs[2]; int gz[2];
+            if (mode == 1) {
+                for (int h = 0; h < 2; ++h) {
+                    int zh = 0;
+                    const uint16_t shh = orc_fit_int4_asym(wf + h * 16, 16, 1, &zh);
+                    scales[((size_t)rowgroup * (Kt * 2) + kt * 2 + h) * 16u + n] =
+                        (uint16_t)(shh | (zh & 0xF));
+                    gs[h] = orc_f16_to_f32(shh); gz[h] = zh;
+                }
+            } else if (mode == 2) {
+                const int kt0 = kt & ~1;
+                const float *wf64 = W + (size_t)row * K + (size_t)kt0 * 32;
+                int zp = 0;
+                const uint16_t sh = orc_fit_int4_asym(wf64, 64, 1, &zp);
+                if ((kt & 1) == 0)
+                    scales[((size_t)rowgroup * (Kt / 2) + (kt >> 1)) * 16u + n] =
+                        (uint16_t)(sh | (zp & 0xF));
+                gs[0] = gs[1] = orc_f16_to_f32(sh); gz[0] = gz[1] = zp;
+            } else {
+                int zp = 0;
+                const uint16_t sh = orc_fit_int4_asym(wf, 32, 1, &zp);
+                scales[((size_t)rowgroup * Kt + kt) * 16u + n] = (uint16_t)(sh | (zp & 0xF));
+                gs[0] = gs[1] = orc_f16_to_f32(sh); gz[0] = gz[1] = zp;
+            }
+            const size_t base = ((size_t)rowgroup * Kt + kt) * 256u;
+            for (int j = 0; j < 32; j += 2) {
+                uint32_t qq[2];
+                for (int u = 0; u < 2; ++u) {
+                    const int jj = j + u, h = jj >> 4;
+                    const float r = rintf(wf[jj] / gs[h] + (float)gz[h]);
+                    qq[u] = (uint32_t)(((int)clampf(r, -8.0f, 7.0f)) & 0xF);
+                }
+                const size_t byte = base + (size_t)(n * 4 + (j >> 3)) * 4u
+                                  + (size_t)((j & 7) >> 1);
+                codes[byte] = (uint8_t)(qq[0] | (qq[1] << 4));
+            }
+        }
+    }
+    return 0;
+}
+
+/* Decode the E2M3 payload into fp32 W[M][K]: wf = e2m3f(code) * block scale,
+ * xpu/src/kernels_dpas.cpp:278-285 (scale row = (row/16)>>3, scale col = kt or
+ * kt>>2 depending on the container's scale_cols). */
+ORC_API void orc_e2m3_decode(const uint8_t *payload, const float *bs, int scale_cols,
+                             int M, int K, float *W) {
+    const int Kt = K / 32;
+#pragma omp parallel for schedule(static)
+    for (int row = 0; row < M; ++row) {
+        const int mt = row >> 4;
+        for (int col = 0; col < K; ++col) {
+            const int kt = col >> 5;
+            const int sc = (scale_cols == Kt) ? kt : (kt >> 2);
+            const float b = bs[(size_t)(mt >> 3) * scale_cols + sc];
+            W[(size_t)row * K + col] = orc_e2m3f(orc_e2m3_code_at(payload, Kt, row, col)) * b;
+        }
+    }
+}
+
+/* x_w4_repack_weight_mode: xpu/src/kernels_dpas.cpp:403-424 (argument checks
+ * -2/-3 restated; the pointer/flag check -1 belongs to the host record). */
+ORC_API int orc_w4_repack(const uint8_t *payload, const float *bs, int scale_cols,
+                          int M, int K, int mode, uint8_t *codes, uint16_t *scales) {
+    if (M % 16 || K % 128) return -2;
+    const int Kt = K / 32;
+    if (mode == 2 && (Kt & 1)) return -3;
+    /* One work-item per (row, k-tile), kernels_dpas.cpp:272-343. In mode 2 both
+     * tiles of a K64 pair fit all 64 values scaled by the block scale of THEIR
+     * OWN tile, and only the even tile stores the scale; that is kept as is. */
+#pragma omp parallel for schedule(static)
+    for (int row = 0; row < M; ++row) {
+        for (int kt = 0; kt < Kt; ++kt) {
+            const int mt = row >> 4;
+            const int sc = (scale_cols == Kt) ? kt : (kt >> 2);
+            const float b = bs[(size_t)(mt >> 3) * scale_cols + sc];
+            float wf[32];
+            for (int j = 0; j < 32; ++j)
+                wf[j] = orc_e2m3f(orc_e2m3_code_at(payload, Kt, row, kt * 32 + j)) * b;
+            const int rowgroup = row >> 4, n = row & 15;
+            float gs[2]; int gz[2];
+            if (mode == 1) {
+                for (int h = 0; h < 2; ++h) {
+                    int zh = 0;
+                    const uint16_t shh = orc_fit_int4_asym(wf + h * 16, 16, 1, &zh);
+                    scales[((size_t)rowgroup * (Kt * 2) + kt * 2 + h) * 16u + n] =
+                        (uint16_t)(shh | (zh & 0xF));
+                    gs[h] = orc_f16_to_f32(shh); gz[h] = zh;
+                }
+            } else if (mode == 2) {
+                const int kt0 = kt & ~1;
+                float wf64[64];
+                for (int j = 0; j < 64; ++j)
+                    wf64[j] = orc_e2m3f(orc_e2m3_code_at(payload, Kt, row, kt0 * 32 + j)) * b;
+                int zp = 0;
+                const uint16_t sh = orc_fit_int4_asym(wf64, 64, 1, &zp);
+                if ((kt & 1) == 0)
+                    scales[((size_t)rowgroup * (Kt / 2) + (kt >> 1)) * 16u + n] =
+                        (uint16_t)(sh | (zp & 0xF));
+                gs[0] = gs[1] = orc_f16_to_f32(sh); gz[0] = gz[1] = zp;
+            } else {
+                int zp = 0;
+                const uint16_t sh = orc_fit_int4_asym(wf, 32, 1, &zp);
+                scales[((size_t)rowgroup * Kt + kt) * 16u + n] = (uint16_t)(sh | (zp & 0xF));
+                gs[0] = gs[1] = orc_f16_to_f32(sh); gz[0] = gz[1] = zp;
+            }
+            const size_t base = ((size_t)rowgroup * Kt + kt) * 256u;
+            for (int j = 0; j < 32; j += 2) {
+                uint32_t qq[2];
+                for (int u = 0; u < 2; ++u) {
+                    const int jj = j + u, h = jj >> 4;
+                    const float r = rintf(wf[jj] / gs[h] + (float)gz[h]);
+                    qq[u] = (uint32_t)(((int)clampf(r, -8.0f, 7.0f)) & 0xF);
+                }
+                const size_t byte = base + (size_t)(n * 4 + (j >> 3)) * 4u
+                                  + (size_t)((j & 7) >> 1);
+                codes[byte] = (uint8_t)(qq[0] | (qq[1] << 4));
+            }
+        }
+    }
+    return 0;
+}
+
+/* Scalar E2M3 GEMV (the quality anchor), xpu/src/kernels_core.cpp:164-233:
+ * sixteen lanes stride the columns, then a sub-group sum. The group-sum order is
+ * unspecified in the reference; lanes are added 0..15 here. */
+ORC_API void orc_gemv_e2m3(const uint8_t *payload, const float *bs, int scale_cols,
+                           int M, int K, const float *x, float *y) {
+    const int Kt = K / 32;
+#pragma omp parallel for schedule(static)
+    for (int row = 0; row < M; ++row) {
+        const int mt = row >> 4;
+        float lane_sum[16];
+        for (int lane = 0; lane < 16; ++lane) {
+            float sum = 0.0f;
+            for (int col = lane; col < K; col += 16) {
+                const int kt = col >> 5;
+                const float cv = orc_e2m3f(orc_e2m3_code_at(payload, Kt, row, col));
+                const int sc = (scale_cols == Kt) ? kt : (kt >> 2);
+                const float w = cv * bs[(size_t)(mt >> 3) * scale_cols + sc];
+                sum += w * x[col];
+            }
+            lane_sum[lane] = sum;
+        }
+        float s = 0.0f;
+        for (int lane = 0; lane < 16; ++lane) s += lane_sum[lane];
+        y[row] = s;
+    }
+}
+
+/* ------------------------------------------------ activation quantisers */
+
+/* A2. xpu/src/kernels_dpas.cpp:188-218: one scale per K32 block, two K16
+ * code sums per block. NaN inputs make the reference's group max unspecified;
+ * fmaxf (NaN-ignoring) is used here. */
+ORC_API void orc_quantize_act_s8(const float *x, int K, int8_t *q, float *scale,
+                                 int32_t *sum16) {
+    const int blocks = K / 32;
+    for (int b = 0; b < blocks; ++b) {
+        float mx = 0.0f;
+        for (int t = 0; t < 32; ++t) mx = fmaxf(mx, fabsf(x[b * 32 + t]));
+        const float s = (mx > 0.0f) ? (mx / 127.0f) : 1.0f;
+        scale[b] = s;
+        int32_t hs[2] = {0, 0};
+        for (int t = 0; t < 32; ++t) {
+            const int32_t v = (int32_t)clampf(rintf(x[b * 32 + t] / s), -127.0f, 127.0f);
+            q[b * 32 + t] = (int8_t)v;
+            hs[t >> 4] += v;
+        }
+        if (sum16) { sum16[b * 2] = hs[0]; sum16[b * 2 + 1] = hs[1]; }
+    }
+}
+
+/* SiLU(gate)*up exactly as xpu/src/kernels_core.cpp:254-267 / kernels_dpas.cpp:200. */
+ORC_API void orc_silu_mul(float *out, const float *gate, const float *up, int n) {
+    for (int i = 0; i < n; ++i) {
+        const float g = gate[i];
+        out[i] = (g / (1.0f + orc_expf(-g))) * up[i];
+    }
+}
+
+/* A3. xpu/src/kernels_dpas.cpp:199-202, 851-855: hidden = silu(gate)*up is
+ * stored, then quantised like A2. Bad arguments return without writing. */
+ORC_API void orc_silu_mul_quant(float *hidden, const float *gate, const float *up, int K,
+                                int8_t *q, float *scale, int32_t *sum16) {
+    if (!hidden || !gate || !up || K <= 0 || (K % 32) != 0) return;
+    orc_silu_mul(hidden, gate, up, K);
+    orc_quantize_act_s8(hidden, K, q, scale, sum16);
+}
+
+/* Sum of 256 values in the fixed order the CUDA side uses for a 256-thread
+ * block: a xor-butterfly inside each 32-lane warp (offsets 16,8,4,2,1), then
+ * the eight warp sums added 0..7. The reference leaves this order to
+ * sycl::reduce_over_group. */
+static float block256_sum(const float *v) {
+    float w[8];
+    for (int wp = 0; wp < 8; ++wp) {
+        float l[32];
+        memcpy(l, v + wp * 32, sizeof l);
+        for (int off = 16; off >= 1; off >>= 1) {
+            float nx[32];
+            for (int i = 0; i < 32; ++i) nx[i] = l[i] + l[i ^ off];
+            memcpy(l, nx, sizeof l);
+        }
+        w[wp] = l[0];
+    }
+    float s = 0.0f;
+    for (int wp = 0; wp < 8; ++wp) s += w[wp];
+    return s;
+}
+
+/* A4. xpu/src/kernels_dpas.cpp:866-929: sum-of-squares partials per 256
+ * elements added in block order, rms_inv = 1/sqrt(sum/H + eps) (the reference
+ * uses sycl::rsqrt; an IEEE sqrt and divide are used on both sides here),
+ * v = x*rms_inv*(1+bf16(w)), stored, then quantised like A2. */
+ORC_API void orc_rmsnorm_quant(float *out, const float *in, const uint16_t *w, int H,
+                               float eps, int8_t *q, float *scale, int32_t *sum16) {
+    if (!out || !in || !w || H <= 0 || (H % 32) != 0) return;
+    const int nblk = (H + 255) / 256;
+    float sum_sq = 0.0f;
+    for (int b = 0; b < nblk; ++b) {
+        float sq[256];
+        for (int i = 0; i < 256; ++i) {
+            const int idx = b * 256 + i;
+            const float v = (idx < H) ? in[idx] : 0.0f;
+            sq[i] = v * v;
+        }
+        sum_sq += block256_sum(sq);
+    }
+    const float rms_inv = 1.0f / sqrtf(sum_sq / (float)H + eps);
+    for (int i = 0; i < H; ++i) out[i] = in[i] * rms_inv * (1.0f + bf16f(w[i]));
+    orc_quantize_act_s8(out, H, q, scale, sum16);
+}
+
+/* A5. xpu/src/kernels_dpas.cpp:1149-1207: k-tile-major staging
+ * aq[(kt*T+tok)*32+j], as[kt*T+tok], asum[kt*T+tok] (sum over all 32 codes).
+ * The block max starts at -inf and ignores NaN. */
+ORC_API void orc_quantize_act_chunk(const float *x, int K, int T, int8_t *aq, float *as,
+                                    int32_t *asum) {
+    const int Kt = K / 32;
+#pragma omp parallel for schedule(static)
+    for (int kt = 0; kt < Kt; ++kt) {
+        for (int tok = 0; tok < T; ++tok) {
+            const size_t blk = (size_t)kt * T + tok;
+            const float *v = x + (size_t)tok * K + (size_t)kt * 32;
+            float mx = -INFINITY;
+            for (int j = 0; j < 32; ++j) mx = fmaxf(mx, fabsf(v[j]));
+            const float s = (mx > 0.0f) ? (mx / 127.0f) : 1.0f;
+            int32_t sum = 0;
+            for (int j = 0; j < 32; ++j) {
+                const int32_t qv = (int32_t)clampf(rintf(v[j] / s), -127.0f, 127.0f);
+                sum += qv;
+                aq[blk * 32 + j] = (int8_t)qv;
+            }
+            as[blk] = s;
+            asum[blk] = sum;
+        }
+    }
+}
+
+/* Per-token variant of A5 (the benchmark configurations quantise "int8
+ * per-token"): one scale per token row, absmax/127 over the whole row,
+ * replicated into every as[kt*T+tok]. Same layout and rounding as A5. This has
+ * no counterpart in the reference. */
+ORC_API void orc_quantize_act_chunk_pertoken(const float *x, int K, int T, int8_t *aq,
+                                             float *as, int32_t *asum) {
+    const int Kt = K / 32;
+    for (int tok = 0; tok < T; ++tok) {
+        const float *v = x + (size_t)tok * K;
+        float mx = -INFINITY;
+        for (int j = 0; j < K; ++j) mx = fmaxf(mx, fabsf(v[j]));
+        const float s = (mx > 0.0f) ? (mx / 127.0f) : 1.0f;
+        for (int kt = 0; kt < Kt; ++kt) {
+            const size_t blk = (size_t)kt * T + tok;
+            int32_t sum = 0;
+            for (int j = 0; j < 32; ++j) {
+                const int32_t qv =
+                    (int32_t)clampf(rintf(v[kt * 32 + j] / s), -127.0f, 127.0f);
+                sum += qv;
+                aq[blk * 32 + j] = (int8_t)qv;
+            }
+            as[blk] = s;
+            asum[blk] = sum;
+        }
+    }
+}
+
+/* ------------------------------------------------------- split heuristics */
+
+/* A6. xpu/src/kernels_dpas.cpp:170-173 */
+ORC_API int orc_choose_gemv_splits(int groups) {
+    if (groups <= 4) return 16;
+    return groups >= 4096 ? 1 : 8;
+}
+
+/* A9. xpu/src/kernels_dpas.cpp:1226-1250; `forced` stands for the validated
+ * TQ_XPU_GEMM_SPLITS value (0 = heuristic). */
+ORC_API int orc_choose_gemm_splits(int rgroups, int tgroups, int ktiles, int forced) {
+    if (!(forced == 1 || forced == 2 || forced == 4 || forced == 8 || forced == 16)) forced = 0;
+    const long tasks = (long)rgroups * tgroups;
+    if (tasks <= 0) return 1;
+    if (forced) {
+        int s = forced;
+        while (s > 1 && s > ktiles) s >>= 1;
+        return s;
+    }
+    const long want = 128L * 16;
+    if (tasks >= want) return 1;
+    for (int s = 2; s <= 16; s <<= 1) {
+        if (s > ktiles) break;
+        if (tasks * s >= want) return s;
+    }
+    int s = 16;
+    while (s > 1 && s > ktiles) s >>= 1;
+    return s;
+}
+
+/* --------------------------------------------------------- int32 tile dots */
+
+/* Signed 4-bit code k of row n in tile (g, kt): byte n*16 + k/2 of the tile,
+ * low nibble = even k (xpu/src/kernels_dpas.cpp:327-342). */
+static inline int w4_code(const uint8_t *tile, int n, int k) {
+    const uint8_t b = tile[n * 16 + (k >> 1)];
+    int v = (k & 1) ? (b >> 4) : (b & 0xF);
+    return (v >= 8) ? v - 16 : v;
+}
+
+/* The DPAS instruction restated: exact int32 dot of one row's 32 codes with
+ * 32 int8 activations (operand layout facts: xpu/src/kernels_dpas.cpp:9-16). */
+static inline int32_t tile_dot(const uint8_t *tile, int n, const int8_t *a) {
+    int32_t d = 0;
+    for (int k = 0; k < 32; ++k) d += w4_code(tile, n, k) * (int32_t)a[k];
+    return d;
+}
+
+/* d[(g*Kt+kt)*16+n] for a single activation row q[K]. */
+ORC_API void orc_tile_dots_gemv(const uint8_t *codes, int M, int K, const int8_t *q,
+                                int32_t *d) {
+    const int Kt = K / 32, groups = M / 16;
+#pragma omp parallel for schedule(static)
+    for (int g = 0; g < groups; ++g)
+        for (int kt = 0; kt < Kt; ++kt)
+            for (int n = 0; n < 16; ++n)
+                d[((size_t)g * Kt + kt) * 16 + n] =
+                    tile_dot(codes + ((size_t)g * Kt + kt) * 256u, n, q + (size_t)kt * 32);
+}
+
+/* d[((size_t)kt*T+tok)*M + row] for chunk-staged activations aq[kt][tok][32]. */
+ORC_API void orc_tile_dots_gemm(const uint8_t *codes, int M, int K, const int8_t *aq,
+                                int T, int32_t *d) {
+    const int Kt = K / 32;
+#pragma omp parallel for schedule(static)
+    for (int kt = 0; kt < Kt; ++kt)
+        for (int tok = 0; tok < T; ++tok)
+            for (int row = 0; row < M; ++row)
+                d[((size_t)kt * T + tok) * M + row] =
+                    tile_dot(codes + ((size_t)(row >> 4) * Kt + kt) * 256u, row & 15,
+                             aq + ((size_t)kt * T + tok) * 32);
+}
+
+static inline void unpack_scale(uint16_t packed, int *zp, float *ws) {
+    int z = (int)(packed & 0xFu);
+    if (z >= 8) z -= 16;
+    *zp = z;
+    *ws = orc_f16_to_f32((uint16_t)(packed & 0xFFF0u));
+}
+
+/* ------------------------------------------------------------------- GEMV */
+
+/* One split of one row, A7 order (xpu/src/kernels_dpas.cpp:622-652): two
+ * accumulators over tile pairs from kt_begin, leftover to acc0, acc0+acc1.
+ * term = ((float)(d - z*asum) * ws) * as[kt]. */
+static float gemv_split_two_acc(const uint8_t *bbase, const uint16_t *sbase, int n,
+                                const int8_t *q, const float *as, const int32_t *sum16,
+                                int kt_begin, int kt_end, int ksh, int fma) {
+    float acc0 = 0.0f, acc1 = 0.0f;
+    int kt = kt_begin;
+#define ORC_TILE(KT, ACC)                                                           \
+    do {                                                                            \
+        int zp; float ws;                                                           \
+        unpack_scale(sbase[(size_t)((KT) >> ksh) * 16u + n], &zp, &ws);             \
+        const int32_t dd = tile_dot(bbase + (size_t)(KT) * 256u, n, q + (size_t)(KT) * 32); \
+        const int32_t asum = sum16[2 * (KT)] + sum16[2 * (KT) + 1];                 \
+        const float f = (float)(dd - zp * asum);                                    \
+        if (fma) ACC = fmaf(f * ws, as[(KT)], ACC);                                 \
+        else ACC += f * ws * as[(KT)];                                              \
+    } while (0)
+    for (; kt + 1 < kt_end; kt += 2) { ORC_TILE(kt, acc0); ORC_TILE(kt + 1, acc1); }
+    for (; kt < kt_end; ++kt) ORC_TILE(kt, acc0);
+    return acc0 + acc1;
+}
+
+/* One split of one row, A8 order (xpu/src/kernels_dpas.cpp:1029-1074): one
+ * serial accumulator. */
+static float gemv_split_serial(const uint8_t *bbase, const uint16_t *sbase, int n,
+                               const int8_t *q, const float *as, const int32_t *sum16,
+                               int kt_begin, int kt_end, int ksh, int fma) {
+    float acc = 0.0f;
+    for (int kt = kt_begin; kt < kt_end; ++kt) ORC_TILE(kt, acc);
+    return acc;
+}
+#undef ORC_TILE
+
+/* A7. x_gemv_w4a8_prepared_impl + x_gemv_w4a8_core, xpu/src/kernels_dpas.cpp:
+ * 586-675, 1631-1662. residual may be NULL. Returns -1 on bad arguments. */
+ORC_API int orc_gemv_w4a8(const uint8_t *codes, const uint16_t *scales, int M, int K,
+                          int ksh, const int8_t *q, const float *as, const int32_t *sum16,
+                          const float *residual, float *y, int fma) {
+    if (!codes || !scales || !y || M % 16 || K % 32) return -1;
+    const int Kt = K / 32, groups = M / 16;
+    const int splits = orc_choose_gemv_splits(groups);
+#pragma omp parallel for schedule(static)
+    for (int g = 0; g < groups; ++g) {
+        const uint8_t *bbase = codes + (size_t)g * Kt * 256u;
+        const uint16_t *sbase = scales + (size_t)g * (Kt >> ksh) * 16u;
+        for (int n = 0; n < 16; ++n) {
+            const int row = g * 16 + n;
+            if (splits == 1) {
+                float acc = gemv_split_two_acc(bbase, sbase, n, q, as, sum16, 0, Kt, ksh, fma);
+                if (residual) acc = acc + residual[row];   /* x_add_inplace */
+                y[row] = acc;
+            } else {
+                float sum = 0.0f;
+                for (int s = 0; s < splits; ++s)
+                    sum += gemv_split_two_acc(bbase, sbase, n, q, as, sum16,
+                                              Kt * s / splits, Kt * (s + 1) / splits,
+                                              ksh, fma);
+                y[row] = sum + (residual ? residual[row] : 0.0f);
+            }
+        }
+    }
+    return 0;
+}
+
+/* A8. x_gemv_w4a8_fanout, xpu/src/kernels_dpas.cpp:945-1102. Up to four
+ * weights share K, ksh and one quantised activation; the split count comes from
+ * the total row-group count. Returns -1/-2 like the reference (the scratch
+ * checks -3/-4 have no meaning on the host). */
+ORC_API int orc_gemv_w4a8_fanout(const uint8_t *const *codes, const uint16_t *const *scales,
+                                 const int *Ms, int count, int K, int ksh,
+                                 const int8_t *q, const float *as, const int32_t *sum16,
+                                 float *const *ys, int fma) {
+    if (!codes || !ys || count <= 0 || count > 4) return -1;
+    int total = 0;
+    for (int i = 0; i < count; ++i) {
+        if (!codes[i] || !scales[i] || !ys[i] || (Ms[i] % 16)) return -2;
+        total += Ms[i] / 16;
+    }
+    const int Kt = K / 32;
+    const int splits = orc_choose_gemv_splits(total);
+    for (int i = 0; i < count; ++i) {
+        const int groups = Ms[i] / 16;
+#pragma omp parallel for schedule(static)
+        for (int g = 0; g < groups; ++g) {
+            const uint8_t *bbase = codes[i] + (size_t)g * Kt * 256u;
+            const uint16_t *sbase = scales[i] + (size_t)g * (Kt >> ksh) * 16u;
+            for (int n = 0; n < 16; ++n) {
+                if (splits == 1) {
+                    ys[i][g * 16 + n] =
+                        gemv_split_serial(bbase, sbase, n, q, as, sum16, 0, Kt, ksh, fma);
+                } else {
+                    float sum = 0.0f;
+                    for (int s = 0; s < splits; ++s)
+                        sum += gemv_split_serial(bbase, sbase, n, q, as, sum16,
+                                                 Kt * s / splits, Kt * (s + 1) / splits,
+                                                 ksh, fma);
+                    ys[i][g * 16 + n] = sum;
+                }
+            }
+        }
+    }
+    return 0;
+}
+
+/* ------------------------------------------------------------------- GEMM */
+
+/* A10. x_gemm_w4a8 + gemm_rc16, xpu/src/kernels_dpas.cpp:1255-1490.
+ * Y[tok][row] (stride M). term = (float)(d - z*asum[kt][tok]) * (ws*as[kt][tok]),
+ * one accumulator per output, k-tiles ascending inside each split; splits added
+ * 0..S-1 from 0.0f, except S == 1 which stores the accumulator untouched. Each
+ * segment of offsets[] takes the split count it would have had alone; both
+ * unsplit kernels (rc16 and its tail form) share this arithmetic. */
+ORC_API int orc_gemm_w4a8(const uint8_t *codes, const uint16_t *scales, int M, int K,
+                          int ksh, const int8_t *aq, const float *as, const int32_t *asum,
+                          float *y, int T, const int *offsets, int segments,
+                          int forced_splits, int fma) {
+    if (!codes || !scales) return -1;
+    if (!aq || !as || !asum || !y || T <= 0 || (T % 8) != 0) return -2;
+    const int Kt = K / 32, rgroups = M / 16, tgroups = T / 8;
+    int count, end[8], split[8];
+    if (offsets) {
+        if (segments < 1 || segments > 8 || offsets[0] != 0 || offsets[segments] != T)
+            return -2;
+        count = segments;
+        for (int i = 0; i < segments; ++i) {
+            if (offsets[i] < 0 || offsets[i + 1] <= offsets[i] || offsets[i + 1] > T ||
+                offsets[i] % 8 || offsets[i + 1] % 8)
+                return -2;
+            end[i] = offsets[i + 1] / 8;
+            split[i] = orc_choose_gemm_splits(rgroups, (offsets[i + 1] - offsets[i]) / 8,
+                                              Kt, forced_splits);
+        }
+    } else {
+        if (segments != 0) return -2;
+        count = 1;
+        end[0] = tgroups;
+        split[0] = orc_choose_gemm_splits(rgroups, tgroups, Kt, forced_splits);
+    }
+#pragma omp parallel for schedule(static)
+    for (int row = 0; row < M; ++row) {
+        const int rg = row >> 4, n = row & 15;
+        const uint8_t *bbase = codes + (size_t)rg * Kt * 256u;
+        const uint16_t *sbase = scales + (size_t)rg * (Kt >> ksh) * 16u;
+        for (int tok = 0; tok < T; ++tok) {
+            const int tg = tok >> 3;
+            int seg = 0;
+            while (seg + 1 < count && tg >= end[seg]) ++seg;
+            const int S = split[seg];
+            float sum = 0.0f;
+            for (int s = 0; s < S; ++s) {
+                float acc = 0.0f;
+                for (int kt = Kt * s / S; kt < Kt * (s + 1) / S; ++kt) {
+                    int zp; float ws;
+                    unpack_scale(sbase[(size_t)(kt >> ksh) * 16u + n], &zp, &ws);
+                    const size_t a = (size_t)kt * T + tok;
+                    const int32_t d = tile_dot(bbase + (size_t)kt * 256u, n, aq + a * 32);
+                    const float f = (float)(d - zp * asum[a]);
+                    if (fma) acc = fmaf(f, ws * as[a], acc);
+                    else acc += f * (ws * as[a]);
+                }
+                if (S == 1) sum = acc; else sum += acc;
+            }
+            y[(size_t)tok * M + row] = sum;
+        }
+    }
+    return 0;
+}
+
+/* Per-token-scale GEMM (no counterpart in the reference; pairs with
+ * orc_quantize_act_chunk_pertoken). The integer dot runs across one whole
+ * weight-scale group (32 codes, or 64 under ksh) before the fp32 promote:
+ * acc = fma((float)(d_g - z*asum_g), ws_g, acc) over groups ascending, then
+ * y = acc * as_tok. Unsplit only. */
+ORC_API int orc_gemm_w4a8_pertoken(const uint8_t *codes, const uint16_t *scales, int M,
+                                   int K, int ksh, const int8_t *aq, const float *as_tok,
+                                   const int32_t *asum, float *y, int T) {
+    if (!codes || !scales) return -1;
+    if (!aq || !as_tok || !asum || !y || T <= 0 || (T % 8) != 0) return -2;
+    const int Kt = K / 32, gw = 1 << ksh;
+#pragma omp parallel for schedule(static)
+    for (int row = 0; row < M; ++row) {
+        const int rg = row >> 4, n = row & 15;
+        const uint8_t *bbase = codes + (size_t)rg * Kt * 256u;
+        const uint16_t *sbase = scales + (size_t)rg * (Kt >> ksh) * 16u;
+        for (int tok = 0; tok < T; ++tok) {
+            float acc = 0.0f;
+            for (int kg = 0; kg < (Kt >> ksh); ++kg) {
+                int zp; float ws;
+                unpack_scale(sbase[(size_t)kg * 16u + n], &zp, &ws);
+                int32_t d = 0, sa = 0;
+                for (int u = 0; u < gw; ++u) {
+                    const int kt = kg * gw + u;
+                    const size_t a = (size_t)kt * T + tok;
+                    d += tile_dot(bbase + (size_t)kt * 256u, n, aq + a * 32);
+                    sa += asum[a];
+                }
+                acc = fmaf((float)(d - zp * sa), ws, acc);
+            }
+            y[(size_t)tok * M + row] = acc * as_tok[tok];
+        }
+    }
+    return 0;
+}
+
+/* ------------------------------------------------------------------ shard */
+
+/* A12. x_w4_shard mode 0, xpu/src/kernels_dpas.cpp:450-499: every packed
+ * output group is cut into tp runs of whole 16-row groups; rank takes run
+ * `rank` of each. dst buffers hold M/tp rows. Error codes as the reference. */
+ORC_API int orc_w4_shard_column(const uint8_t *codes, const uint16_t *scales, int M, int K,
+                                int ksh, int k16, int rank, int tp, const int *groups,
+                                int ngroups, uint8_t *dst_codes, uint16_t *dst_scales) {
+    if (!codes || !scales || !dst_codes || !dst_scales) return -1;
+    if (tp < 1 || rank < 0 || rank >= tp) return -2;
+    if (k16) return -3;
+    const int Kt = K / 32, sg = Kt >> ksh;
+    int gs[8], ng = (groups && ngroups > 0) ? ngroups : 1;
+    if (ng > 8) return -4;
+    if (groups && ngroups > 0) {
+        int total = 0;
+        for (int i = 0; i < ng; ++i) { gs[i] = groups[i]; total += gs[i]; }
+        if (total != M) return -5;
+    } else {
+        gs[0] = M;
+    }
+    for (int i = 0; i < ng; ++i) if (gs[i] % (16 * tp)) return -6;
+    size_t src_g = 0, dst_g = 0;
+    for (int i = 0; i < ng; ++i) {
+        const size_t gtot = (size_t)gs[i] / 16, gper = gtot / (size_t)tp;
+        const size_t from = src_g + gper * (size_t)rank;
+        memcpy(dst_codes + dst_g * Kt * 256u, codes + from * Kt * 256u, gper * Kt * 256u);
+        memcpy(dst_scales + dst_g * (size_t)sg * 16u, scales + from * (size_t)sg * 16u,
+               gper * (size_t)sg * 16u * sizeof(uint16_t));
+        src_g += gtot;
+        dst_g += gper;
+    }
+    return 0;
+}
+
+ORC_API int orc_num_threads(void) {
+#ifdef _OPENMP
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}
+
+ORC_API void orc_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}

@@ -1,0 +1,55 @@
+"""The C-ABI library loads without a GPU and exports every symbol the header declares."""
+import ctypes
+import importlib
+import os
+import re
+import subprocess
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared_c_symbols():
+    text = open(os.path.join(ROOT, "include", "tq_w4a8.h")).read()
+    c_part = text.split('extern "C" {', 1)[1].split('}  /* extern "C" */', 1)[0]
+    c_part = re.sub(r"/\*.*?\*/", "", c_part, flags=re.S)
+    c_part = re.sub(r"typedef struct \{.*?\} tq_qmma_weight_t;", "", c_part, flags=re.S)
+    return sorted(set(re.findall(r"\b((?:tq|qwn)_[a-z0-9_]+)\s*\(", c_part)))
+
+
+def _declared_cpp_symbols():
+    text = open(os.path.join(ROOT, "include", "tq_w4a8.h")).read()
+    cpp = text.split('}  /* extern "C" */', 1)[1]
+    return sorted(set(re.findall(r"\b(x_[a-z0-9_]+)\s*\(", cpp)))
+
+
+def test_library_builds_and_exports_header_symbols():
+    build = importlib.import_module("knivesysl-xe_b200.build")
+    path = build.build()
+    lib = ctypes.CDLL(path)
+    names = _declared_c_symbols()
+    assert len(names) > 50
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in include/tq_w4a8.h but not exported"
+    pkg = importlib.import_module("knivesysl-xe_b200")
+    assert set(names) == set(pkg.SIGNATURES), set(names) ^ set(pkg.SIGNATURES)
+    pkg.load()
+
+
+def test_cpp_projection_symbols_keep_reference_mangling():
+    build = importlib.import_module("knivesysl-xe_b200.build")
+    out = subprocess.check_output(["nm", "-D", "--defined-only", build.build()], text=True)
+    for n in _declared_cpp_symbols():
+        assert re.search(rf" T _Z\d+{n}P", out), n
+    # spot-check full signatures a reference-side caller would link against
+    assert "_Z11x_gemv_w4a8PK16tq_qmma_weight_tPKfPf" in out
+    assert "_Z11x_gemm_w4a8PK16tq_qmma_weight_tPKaPKfPKiPfiS7_i" in out
+    assert "_Z20x_quantize_act_chunkPKfiiPaPfPi" in out
+
+
+def test_weight_record_layout_matches_header():
+    pkg = importlib.import_module("knivesysl-xe_b200")
+    W = pkg.TqWeight
+    # int M,K,Mt,Kt; float; 2 pointers; 8 ints; 2 pointers; 3 ints; 2 pointers; int (+pad)
+    assert W.M.offset == 0 and W.inv_scale.offset == 16 and W.d_A.offset == 24
+    assert W.block_scaled.offset == 40 and W.d_s4.offset == 72 and W.s4_ready.offset == 88
+    assert W.d_s8.offset == 104 and W.s8_ready.offset == 120 and ctypes.sizeof(W) == 128
