@@ -1,0 +1,366 @@
+#!/usr/bin/env python
+"""Benchmark of the W4A8 projection path.
+
+Workload ("cfg2"): batched decode fused gate+up projection, K64 scale tier, T = 8 tokens,
+K = 5120, N = 2 x 17408; seeded N(0, 0.02) weights symmetric-quantised to int4; N(0, 1)
+activations with 1% of channels scaled x20, quantised to int8 per token. One step = one pass:
+per-token activation staging (2 launches) + ONE fused gate|up GEMM launch over a weight copy
+that rotates through `rotate` distinct copies (> L2 in total), so weights come from HBM.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+N > 1 (torchrun, one rank per GPU): gate and up are column-sharded (x_w4_shard), each rank
+computes its slice of every step and the slices are all-gathered over NCCL ("strong").
+Prints ONE JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import importlib
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+T, K, N_EACH, GROUP = 8, 5120, 17408, 64
+METRIC = "decode_gemv_weight_GBps"
+UNIT = "GB/s"
+# dram__bytes_read.sum + dram__bytes_write.sum of one GEMM launch of this workload, from the
+# ncu capture summarised in profiles/ (None until a capture exists)
+NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def measured_peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons while the GPU is under the benchmark's load."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.rows, self.proc = [], None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                 "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), line.strip()))
+
+    def stop(self, t0: float, t1: float):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ts, line in self.rows:
+            if ts < t0 or ts > t1 + 0.06:
+                continue
+            f = [c.strip() for c in line.split(",")]
+            try:
+                sm.append(float(f[0]))
+                mx = float(f[1])
+            except Exception:
+                continue
+            for n, v in zip(names, f[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def dist_env():
+    return (int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)),
+            int(os.environ.get("WORLD_SIZE", 1)))
+
+
+def cpu_pass(orc, host_w, aq, as_, asum, rows=None):
+    """One pass of the workload on the CPU oracle (all OpenMP threads); rows limits each
+    matrix to its first `rows` output rows."""
+    for codes, scales in host_w:
+        M = N_EACH if rows is None else rows
+        orc.gemm_w4a8(codes[: M * K // 2], scales[: M * (K // GROUP)], M, K, 1, aq, as_, asum, T)
+
+
+def run_reference(args, rank):
+    """The reference's scalar projection semantics (the CPU oracle; the reference's SYCL
+    sources cannot be built without Intel's toolchain) on the host cores."""
+    if rank != 0:
+        return
+    from oracle import oracle as orc
+    wl = importlib.import_module("knivesysl-xe_b200.workloads")
+    host_w = [wl.make_weight_w4(N_EACH, K, seed=11 + i, group=GROUP) for i in range(2)]
+    x = wl.activations_normal(T, K, seed=5, outlier_frac=0.01)
+    aq, as_, asum = orc.quantize_act_chunk(x, per_token=True)
+    t0 = time.perf_counter()
+    cpu_pass(orc, host_w, aq, as_, asum, rows=1088)
+    t_probe = (time.perf_counter() - t0) * 16.0
+    budget = 150.0
+    frac_rows = N_EACH
+    total = args.steps + args.warmup
+    if t_probe * total > budget:
+        frac_rows = max(16, int(N_EACH * budget / (t_probe * total)) // 16 * 16)
+    for _ in range(args.warmup):
+        orc.quantize_act_chunk(x, per_token=True)
+        cpu_pass(orc, host_w, aq, as_, asum, rows=frac_rows)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        orc.quantize_act_chunk(x, per_token=True)
+        cpu_pass(orc, host_w, aq, as_, asum, rows=frac_rows)
+    dt = time.perf_counter() - t0
+    wl_bytes = 2 * wl.weight_bytes(frac_rows, K, GROUP)
+    val = wl_bytes * args.steps / dt / 1e9
+    sample = f"{frac_rows} of {N_EACH} rows of gate and up per step, T={T}, K={K}"
+    out = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "s8xs4->s32",
+        "data": "synthetic",
+        "config": {"workload": "cfg2: fused gate+up, K64 tier, T=8, K=5120, N=2x17408 (CPU oracle)"},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": orc.num_threads(), "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(out), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--rotate", type=int, default=4)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    rank, local_rank, world = dist_env()
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    pkg = importlib.import_module("knivesysl-xe_b200")
+    wl = importlib.import_module("knivesysl-xe_b200.workloads")
+    lib = pkg.load()                      # raises if the CUDA library is missing
+    assert lib.tq_set_device(local_rank) == 0
+    dist = None
+    if world > 1:
+        import torch.distributed as dist   # control plane only: barrier and max-over-ranks
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        idbuf = (C.c_char * 128)()
+        if rank == 0:
+            assert lib.tq_comm_unique_id(idbuf) == 0
+        obj = [bytes(idbuf.raw)]
+        dist.broadcast_object_list(obj, src=0)
+        idbuf = C.create_string_buffer(obj[0], 128)
+        assert lib.tq_comm_init(idbuf, rank, world) == 0
+
+    # ---- inputs (same seeds on every rank; a rank keeps only its column shard) ----------
+    host_w = [wl.make_weight_w4(N_EACH, K, seed=11 + i, group=GROUP) for i in range(2)]
+    n_shard = N_EACH // world
+    copies = []                      # rotate x [gate, up] PackedWeight (this rank's shard)
+    for c in range(args.rotate):
+        pair = []
+        for codes, scales in host_w:
+            cc = np.roll(codes.reshape(N_EACH // 16, -1), c, axis=0).reshape(-1)
+            ss = np.roll(scales.reshape(N_EACH // 16, -1), c, axis=0).reshape(-1)
+            full = pkg.PackedWeight(cc, ss, N_EACH, K, k64=True)
+            if world > 1:
+                sh = pkg.TqWeight()
+                assert lib.qwn_x_w4_shard(C.byref(sh), full.ref, rank, world, 0, None, 0) == 0
+                full.codes.free()
+                full.scales.free()
+                full.rec = sh
+            pair.append(full)
+        copies.append(pair)
+    warr = [pkg.weight_array(p) for p in copies]
+    x = wl.activations_normal(T, K, seed=5, outlier_frac=0.01)
+    dx = pkg.DevBuf.from_numpy(x)
+    nblk = K // 32 * T
+    aq, as_, asum, as_tok = (pkg.DevBuf(nblk * 32), pkg.DevBuf(nblk * 4), pkg.DevBuf(nblk * 4),
+                             pkg.DevBuf(T * 4))
+    y = [pkg.DevBuf(T * n_shard * 4) for _ in range(2)]
+    yarr = pkg.ptr_array(y)
+    # gathered outputs: [world][gate|up][T][n_shard]
+    ycat = pkg.DevBuf(2 * T * n_shard * 4)
+    gathered = pkg.DevBuf(world * 2 * T * n_shard * 4) if world > 1 else None
+
+    def stage():
+        lib.qwn_x_quantize_act_chunk_pertoken(dx.ptr, K, T, aq.ptr, as_.ptr, asum.ptr, as_tok.ptr)
+
+    def gemm(i):
+        rc = lib.qwn_x_gemm_w4a8_fanout(warr[i % args.rotate], yarr, 2, aq.ptr, as_.ptr, asum.ptr, T,
+                                        None, 0)
+        assert rc == 0, rc
+
+    def exchange():
+        if world > 1:
+            lib.tq_d2d_async(ycat.ptr, y[0].ptr, y[0].nbytes)
+            lib.tq_d2d_async(ycat.ptr + y[0].nbytes, y[1].ptr, y[1].nbytes)
+            assert lib.tq_comm_allgather(ycat.ptr, gathered.ptr, ycat.nbytes) == 0
+
+    def step(i):
+        stage()
+        gemm(i)
+        exchange()
+
+    def barrier():
+        lib.tq_sync()
+        if dist:
+            dist.barrier()
+
+    ev = [lib.tq_event_create() for _ in range(2)]
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    t_load0 = time.time()
+
+    # ---- timed region: whole steps ----------------------------------------------------
+    for i in range(args.warmup):
+        step(i)
+    barrier()
+    lib.tq_event_record(ev[0])
+    for i in range(args.steps):
+        step(i)
+    lib.tq_event_record(ev[1])
+    barrier()
+    ms = lib.tq_event_elapsed_ms(ev[0], ev[1])
+    if dist:
+        import torch
+        tt = torch.tensor([ms], dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms = float(tt.item())
+    full_weight_bytes = 2 * wl.weight_bytes(N_EACH, K, GROUP)
+    value = full_weight_bytes * args.steps / (ms * 1e-3) / 1e9
+
+    # ---- dominant kernel alone (this rank's shard), for the roofline -----------------------
+    stage()
+    for i in range(args.warmup):
+        gemm(i)
+    lib.tq_sync()
+    k_iters = max(args.steps, 200)
+    lib.tq_event_record(ev[0])
+    for i in range(k_iters):
+        gemm(i)
+    lib.tq_event_record(ev[1])
+    lib.tq_sync()
+    k_ms = lib.tq_event_elapsed_ms(ev[0], ev[1]) / k_iters
+    shard_weight = 2 * wl.weight_bytes(n_shard, K, GROUP)
+    algo_bytes = shard_weight + T * K + nblk * 8 + 2 * T * n_shard * 4
+    achieved = algo_bytes / (k_ms * 1e-3) / 1e9
+    peak, peak_kind = measured_peaks()
+
+    # ---- end to end through the C-ABI with host buffers ----------------------------------
+    hx = lib.tq_host_alloc_pinned(x.nbytes)
+    C.memmove(hx, x.ctypes.data, x.nbytes)
+    out_bytes = (gathered.nbytes if world > 1 else 2 * y[0].nbytes)
+    hy = lib.tq_host_alloc_pinned(out_bytes)
+
+    def e2e_step(i):
+        lib.tq_h2d_async(dx.ptr, hx, x.nbytes)
+        step(i)
+        if world > 1:
+            lib.tq_d2h_async(hy, gathered.ptr, gathered.nbytes)
+        else:
+            lib.tq_d2h_async(hy, y[0].ptr, y[0].nbytes)
+            lib.tq_d2h_async(hy + y[0].nbytes, y[1].ptr, y[1].nbytes)
+
+    e_iters = max(min(args.steps, 2000), 50)
+    for i in range(args.warmup):
+        e2e_step(i)
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(e_iters):
+        e2e_step(i)
+    lib.tq_sync()
+    e_s = time.perf_counter() - t0
+    if dist:
+        import torch
+        tt = torch.tensor([e_s], dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        e_s = float(tt.item())
+    e2e_val = full_weight_bytes * e_iters / e_s / 1e9
+    t_load1 = time.time()
+    if sampler and (t_load1 - t_load0) < 0.6:
+        # too short for nvidia-smi's sampling period: keep the same kernels running a little
+        tend = time.time() + 0.6
+        i = 0
+        while time.time() < tend:
+            gemm(i)
+            i += 1
+            if i % 256 == 0:
+                lib.tq_sync()
+        lib.tq_sync()
+        t_load1 = time.time()
+    clocks = sampler.stop(t_load0, t_load1) if sampler else None
+    err = lib.tq_last_error()
+
+    # ---- CPU baseline (rank 0, N = 1 only) ----------------------------------------------------
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        from oracle import oracle as orc
+        oq, os_, osm = orc.quantize_act_chunk(x, per_token=True)
+        cpu_pass(orc, host_w, oq, os_, osm)      # warm
+        passes, t0 = 0, time.perf_counter()
+        while time.perf_counter() - t0 < 12.0:
+            orc.quantize_act_chunk(x, per_token=True)
+            cpu_pass(orc, host_w, oq, os_, osm)
+            passes += 1
+        dt = time.perf_counter() - t0
+        cpu = {"value": full_weight_bytes * passes / dt / 1e9, "unit": UNIT, "cores": orc.num_threads(),
+               "kind": "port", "sample": f"{passes} full passes of cfg2 in {dt:.1f} s (OpenMP, all host threads)"}
+
+    if rank == 0:
+        out = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "s8xs4->s32, fp32 out",
+            "data": "synthetic",
+            "config": {"workload": "cfg2: batched decode fused gate+up, K64 scale tier, T=8, K=5120, "
+                                   "N=2x17408, int8 per-token activations",
+                       "parallelism": f"column shard tp{world}" + (" + NCCL all-gather" if world > 1 else ""),
+                       "l2": f"inputs larger than L2: {args.rotate} rotating weight copies, "
+                             f"{args.rotate * full_weight_bytes // world / 1e6:.0f} MB per GPU",
+                       "step": "token_scale + quant_chunk + fused gate|up GEMM" +
+                               (" + all-gather" if world > 1 else "")},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "peak_source": f"{peak_kind} copy bandwidth",
+                         "kernel": "gemm_w4a8_mma_kernel", "us_per_launch": k_ms * 1e3,
+                         "algorithmic_bytes_per_launch": algo_bytes,
+                         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH},
+            "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": int(x.nbytes),
+                    "d2h_bytes_per_step": int(out_bytes), "steps": e_iters,
+                    "us_per_step": e_s / e_iters * 1e6},
+            "gpu_launches": 3 * args.steps,
+            "clocks": clocks,
+            "cpu_baseline": cpu,
+            "device_error": err,
+        }
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        lib.tq_comm_destroy()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

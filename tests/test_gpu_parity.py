@@ -1,0 +1,376 @@
+"""GPU parity: every CUDA entry point against the CPU oracle on the same seeded inputs,
+called through the C-ABI. Integer layers (codes, sums, tile dots) must be bit-exact. fp32
+outputs are compared bit-for-bit with the oracle's fused-multiply-add variant (the kernels
+use explicit fmaf in the same order) and within 1e-3 of its separate-multiply-add variant
+(the tolerance stated for fp32 outputs)."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+import refgen
+
+pytestmark = pytest.mark.gpu
+
+RTOL = 1e-3   # stated fp32 tolerance against the reference semantics
+
+
+def close_1e3(got, want):
+    scale = np.abs(want).max() + 1e-30
+    return np.abs(got - want).max() <= RTOL * scale
+
+
+def dev(pkg, a):
+    return pkg.DevBuf.from_numpy(np.ascontiguousarray(a))
+
+
+def prepared(lib, pkg, K):
+    q, s, sm = pkg.DevBuf(K), pkg.DevBuf(K // 32 * 4), pkg.DevBuf(K // 16 * 4)
+    assert lib.qwn_dbg_prepared_act(K, q.ptr, s.ptr, sm.ptr) == 0
+    lib.tq_sync()
+    return q.to_numpy(np.int8), s.to_numpy(np.float32), sm.to_numpy(np.int32)
+
+
+# ---------------------------------------------------------------- quantisers
+@pytest.mark.parametrize("K", [32, 5120, 17408])
+def test_quantize_act_s8(lib, pkg, orc, K):
+    x = refgen.lcg_floats(K)[0] if K <= 5120 else np.random.default_rng(K).standard_normal(K).astype(np.float32)
+    x[:32] = 0.0
+    dx = dev(pkg, x)
+    q, s, sm = pkg.DevBuf(K), pkg.DevBuf(K // 32 * 4), pkg.DevBuf(K // 16 * 4)
+    for b in (q, s, sm):
+        b.fill(0xA5)
+    lib.qwn_x_quantize_act_s8(dx.ptr, K, q.ptr, s.ptr, sm.ptr)
+    lib.tq_sync()
+    oq, os_, osm = orc.quantize_act_s8(x)
+    assert np.array_equal(q.to_numpy(np.int8), oq)
+    assert s.to_numpy(np.float32).tobytes() == os_.tobytes()
+    assert np.array_equal(sm.to_numpy(np.int32), osm)
+    lib.qwn_x_prepare_gemv_act_s8(dx.ptr, K)
+    pq, ps, psm = prepared(lib, pkg, K)
+    assert np.array_equal(pq, oq) and ps.tobytes() == os_.tobytes() and np.array_equal(psm, osm)
+
+
+@pytest.mark.parametrize("K,T,exceptional", [(128, 16, True), (128, 16, False), (5120, 8, False),
+                                             (256, 40, True)])
+def test_quantize_act_chunk(lib, pkg, orc, K, T, exceptional):
+    x = refgen.chunk_quant_probe_input(K, T, exceptional)
+    dx = dev(pkg, x)
+    n = K // 32 * T
+    aq, as_, asum = pkg.DevBuf(n * 32), pkg.DevBuf(n * 4), pkg.DevBuf(n * 4)
+    for b in (aq, as_, asum):
+        b.fill(0xA5)                      # poison: a missed store fails the comparison
+    lib.qwn_x_quantize_act_chunk(dx.ptr, K, T, aq.ptr, as_.ptr, asum.ptr)
+    lib.tq_sync()
+    oq, os_, osm = orc.quantize_act_chunk(x)
+    assert np.array_equal(aq.to_numpy(np.int8), oq)
+    assert as_.to_numpy(np.float32).tobytes() == os_.tobytes()
+    assert np.array_equal(asum.to_numpy(np.int32), osm)
+
+
+def test_quantize_act_chunk_pertoken(lib, pkg, orc, wl):
+    K, T = 5120, 16
+    x = wl.activations_normal(T, K, seed=2, outlier_frac=0.01)
+    dx = dev(pkg, x)
+    n = K // 32 * T
+    aq, as_, asum, at = pkg.DevBuf(n * 32), pkg.DevBuf(n * 4), pkg.DevBuf(n * 4), pkg.DevBuf(T * 4)
+    lib.qwn_x_quantize_act_chunk_pertoken(dx.ptr, K, T, aq.ptr, as_.ptr, asum.ptr, at.ptr)
+    lib.tq_sync()
+    oq, os_, osm = orc.quantize_act_chunk(x, per_token=True)
+    assert np.array_equal(aq.to_numpy(np.int8), oq)
+    assert as_.to_numpy(np.float32).tobytes() == os_.tobytes()
+    assert np.array_equal(asum.to_numpy(np.int32), osm)
+    assert at.to_numpy(np.float32).tobytes() == os_.reshape(K // 32, T)[0].tobytes()
+
+
+def test_silu_mul_quant_fused_equals_unfused_and_oracle(lib, pkg, orc):
+    rng = np.random.default_rng(5)
+    K = 17408
+    gate = ((rng.random(K) * 2 - 1) * 8).astype(np.float32)
+    up = ((rng.random(K) * 2 - 1) * 4).astype(np.float32)
+    gate[:32] = 0.0
+    gate[0] = -0.0
+    gate[32], gate[33] = -100.0, 100.0
+    up[64:96] *= np.float32(1e-20)
+    dg, du = dev(pkg, gate), dev(pkg, up)
+    h0, h1 = pkg.DevBuf(K * 4), pkg.DevBuf(K * 4)
+    lib.qwn_x_silu_mul(h0.ptr, dg.ptr, du.ptr, K)
+    lib.qwn_x_prepare_gemv_act_s8(h0.ptr, K)
+    a = prepared(lib, pkg, K)
+    lib.qwn_x_silu_mul_quant(h1.ptr, dg.ptr, du.ptr, K)
+    b = prepared(lib, pkg, K)
+    assert h0.to_numpy(np.float32).tobytes() == h1.to_numpy(np.float32).tobytes()
+    assert all(np.array_equal(u, v) for u, v in zip(a, b))
+    oh, oq, os_, osm = orc.silu_mul_quant(gate, up)
+    assert h1.to_numpy(np.float32).tobytes() == oh.tobytes()
+    assert np.array_equal(b[0], oq) and b[1].tobytes() == os_.tobytes() and np.array_equal(b[2], osm)
+
+
+@pytest.mark.parametrize("H", [5120, 352])
+def test_rmsnorm_quant(lib, pkg, orc, H):
+    rng = np.random.default_rng(6)
+    x = (rng.standard_normal(H) * 3).astype(np.float32)
+    w = ((rng.standard_normal(H) * 0.1).astype(np.float32).view(np.uint32) >> 16).astype(np.uint16)
+    dx, dw, out = dev(pkg, x), dev(pkg, w), pkg.DevBuf(H * 4)
+    lib.qwn_x_rmsnorm_quant(out.ptr, dx.ptr, dw.ptr, H, 1e-6)
+    q, s, sm = prepared(lib, pkg, H)
+    oo, oq, os_, osm = orc.rmsnorm_quant(x, w, 1e-6)
+    assert out.to_numpy(np.float32).tobytes() == oo.tobytes()
+    assert np.array_equal(q, oq) and s.tobytes() == os_.tobytes() and np.array_equal(sm, osm)
+
+
+# ---------------------------------------------------------------- repack / shard
+@pytest.mark.parametrize("mode", [0, 1, 2])
+@pytest.mark.parametrize("k32_scales", [False, True])
+def test_repack_bit_exact(lib, pkg, orc, mode, k32_scales):
+    rng = np.random.default_rng(7 + mode)
+    M, K = 128, 512
+    codes6 = rng.integers(0, 64, size=(M, K), dtype=np.uint8)
+    Kt = K // 32
+    sc = Kt if k32_scales else Kt // 4
+    bs = (rng.random(((M + 127) // 128, sc)) * 0.01 + 0.002).astype(np.float32)
+    payload = orc.e2m3_payload_from_codes_fast(codes6)
+    w = pkg.TqWeight()
+    w.M, w.K, w.Mt, w.Kt = M, K, M // 16, Kt
+    w.block_scaled, w.e2m3, w.scale_rows, w.scale_cols = 1, 1, (M + 127) // 128, sc
+    w.d_A = lib.tq_dev_alloc(payload.nbytes, b"t.payload")
+    w.d_block_scale_inv = lib.tq_dev_alloc(bs.nbytes, b"t.bs")
+    lib.tq_h2d(w.d_A, payload.ctypes.data, payload.nbytes)
+    lib.tq_h2d(w.d_block_scale_inv, bs.ctypes.data, bs.nbytes)
+    assert lib.qwn_x_w4_repack_weight_mode(C.byref(w), mode) == 0
+    assert w.s4_ready == 1 and w.s4_k16 == (mode == 1) and w.s4_k64 == (mode == 2)
+    assert not w.d_A and not w.d_block_scale_inv
+    rc, oc, osc = orc.w4_repack(payload, bs, sc, M, K, mode)
+    assert rc == 0
+    gc = np.empty_like(oc)
+    gs = np.empty_like(osc)
+    lib.tq_d2h(gc.ctypes.data, w.d_s4, gc.nbytes)
+    lib.tq_d2h(gs.ctypes.data, w.d_s4_scale, gs.nbytes)
+    assert np.array_equal(gs, osc)
+    assert np.array_equal(gc, oc)
+    lib.qwn_x_w4_shard_free(C.byref(w))
+
+
+def test_repack_errors(lib, pkg):
+    w = pkg.TqWeight()
+    assert lib.qwn_x_w4_repack_weight_mode(C.byref(w), 0) == -1
+    w.d_A = w.d_block_scale_inv = 1
+    w.block_scaled = w.e2m3 = 1
+    w.M, w.K, w.Mt, w.Kt = 24, 128, 1, 4
+    assert lib.qwn_x_w4_repack_weight(C.byref(w)) == -2
+    w.M, w.K, w.Kt = 32, 96, 3
+    assert lib.qwn_x_w4_repack_weight(C.byref(w)) == -2
+
+
+@pytest.mark.parametrize("tp,groups", [(2, None), (4, None), (8, None), (2, [512, 256, 256])])
+def test_shard_matches_oracle_and_concat_bit_identical(lib, pkg, orc, wl, tp, groups):
+    M, K, ksh = 1024, 1024, 1   # every shard keeps > 4 row-groups, so the split count is unchanged
+    codes, scales = wl.random_packed_weight(M, K, seed=21, ksh=ksh)
+    w = pkg.PackedWeight(codes, scales, M, K, k64=True)
+    x = refgen.shard_check_row(K)
+    dx = dev(pkg, x)
+    lib.qwn_x_prepare_gemv_act_s8(dx.ptr, K)
+    full = pkg.DevBuf(M * 4)
+    assert lib.qwn_x_gemv_w4a8_prepared(w.ref, full.ptr, None) == 0
+    got = pkg.DevBuf(M * 4)
+    garr = (C.c_int * len(groups))(*groups) if groups else None
+    for r in range(tp):
+        s = pkg.TqWeight()
+        assert lib.qwn_x_w4_shard(C.byref(s), w.ref, r, tp, 0, garr, len(groups) if groups else 0) == 0
+        rc, oc, osc = orc.w4_shard_column(codes, scales, M, K, ksh, r, tp, groups)
+        gc, gs = np.empty_like(oc), np.empty_like(osc)
+        lib.tq_d2h(gc.ctypes.data, s.d_s4, gc.nbytes)
+        lib.tq_d2h(gs.ctypes.data, s.d_s4_scale, gs.nbytes)
+        assert np.array_equal(gc, oc) and np.array_equal(gs, osc) and s.M == M // tp
+        assert lib.qwn_x_gemv_w4a8_prepared(C.byref(s), got.ptr + r * (M // tp) * 4, None) == 0
+        lib.tq_sync()
+        lib.qwn_x_w4_shard_free(C.byref(s))
+    part = got.to_numpy(np.float32)
+    gsz = groups or [M]
+    out = np.empty(M, np.float32)
+    base = 0
+    cur = [r * (M // tp) for r in range(tp)]
+    for g in gsz:
+        per = g // tp
+        for r in range(tp):
+            out[base + r * per: base + (r + 1) * per] = part[cur[r]: cur[r] + per]
+            cur[r] += per
+        base += g
+    assert out.tobytes() == full.to_numpy(np.float32).tobytes()
+    if not groups:
+        assert lib.qwn_shard_check(w.ref, tp) == 0
+    s = pkg.TqWeight()
+    assert lib.qwn_x_w4_shard(C.byref(s), w.ref, 0, 3, 0, None, 0) == -6
+    assert lib.qwn_x_w4_shard(C.byref(s), w.ref, 5, 2, 0, None, 0) == -2
+    assert lib.qwn_x_w4_shard(C.byref(s), w.ref, 0, 2, 1, None, 0) == -9
+
+
+# ---------------------------------------------------------------- GEMV
+GEMV_SHAPES = [(64, 256, 0), (48, 384, 1), (16, 128, 0), (16, 128, 1), (272, 5120, 0),
+               (5120, 1024, 1), (65536 + 16, 64, 0)]
+
+
+@pytest.mark.parametrize("M,K,ksh", GEMV_SHAPES)
+def test_gemv_int32_dots_and_fp32(lib, pkg, orc, wl, M, K, ksh):
+    codes, scales = wl.random_packed_weight(M, K, seed=M * 7 + K, ksh=ksh)
+    w = pkg.PackedWeight(codes, scales, M, K, k64=bool(ksh))
+    x = refgen.lcg_floats(K, seed=391 + M)[0]
+    x[:32] = 0.0
+    dx = dev(pkg, x)
+    y = pkg.DevBuf(M * 4)
+    y.fill(0xA5)
+    assert lib.qwn_x_gemv_w4a8(w.ref, dx.ptr, y.ptr) == 0
+    lib.tq_sync()
+    q, s, sm = orc.quantize_act_s8(x)
+    # int32 layer, from the same unpack + dp4a code path
+    dd = pkg.DevBuf((M // 16) * (K // 32) * 16 * 4)
+    dd.fill(0xA5)
+    assert lib.qwn_dbg_tile_dots_gemv(w.ref, dd.ptr) == 0
+    lib.tq_sync()
+    assert np.array_equal(dd.to_numpy(np.int32), orc.tile_dots_gemv(codes, M, K, q))
+    got = y.to_numpy(np.float32)
+    _, want_fma = orc.gemv_w4a8(codes, scales, M, K, ksh, q, s, sm, fma=1)
+    _, want_sep = orc.gemv_w4a8(codes, scales, M, K, ksh, q, s, sm, fma=0)
+    assert got.tobytes() == want_fma.tobytes()
+    assert close_1e3(got, want_sep)
+    # residual forms
+    res = np.linspace(-3, 3, M).astype(np.float32)
+    dr = dev(pkg, res)
+    assert lib.qwn_x_gemv_w4a8_add(w.ref, dx.ptr, dr.ptr, y.ptr) == 0
+    lib.tq_sync()
+    _, want_res = orc.gemv_w4a8(codes, scales, M, K, ksh, q, s, sm, residual=res, fma=1)
+    assert y.to_numpy(np.float32).tobytes() == want_res.tobytes()
+    assert lib.qwn_x_gemv_qmma_prepared(w.ref, dx.ptr, y.ptr, dr.ptr) == 0
+    lib.tq_sync()
+    assert y.to_numpy(np.float32).tobytes() == want_res.tobytes()
+    assert lib.tq_last_error() == 0
+
+
+@pytest.mark.parametrize("Ms,K,ksh", [([64, 64], 256, 0), ([160, 96, 48, 48], 384, 1),
+                                      ([16, 48], 128, 0), ([1088, 1088], 1024, 1)])
+def test_gemv_fanout(lib, pkg, orc, wl, Ms, K, ksh):
+    ws, host = [], []
+    for i, M in enumerate(Ms):
+        c, s = wl.random_packed_weight(M, K, seed=100 + i, ksh=ksh)
+        host.append((c, s, M))
+        ws.append(pkg.PackedWeight(c, s, M, K, k64=bool(ksh)))
+    x = refgen.lcg_floats(K)[0]
+    dx = dev(pkg, x)
+    lib.qwn_x_prepare_gemv_act_s8(dx.ptr, K)
+    ys = [pkg.DevBuf(M * 4) for M in Ms]
+    for b in ys:
+        b.fill(0xA5)
+    assert lib.qwn_x_gemv_w4a8_fanout(pkg.weight_array(ws), pkg.ptr_array(ys), len(ws)) == 0
+    lib.tq_sync()
+    q, s, sm = orc.quantize_act_s8(x)
+    rc, want = orc.gemv_w4a8_fanout(host, K, ksh, q, s, sm, fma=1)
+    rc2, want_sep = orc.gemv_w4a8_fanout(host, K, ksh, q, s, sm, fma=0)
+    for b, w1, w0 in zip(ys, want, want_sep):
+        got = b.to_numpy(np.float32)
+        assert got.tobytes() == w1.tobytes()
+        assert close_1e3(got, w0)
+
+
+def test_gemv_errors(lib, pkg, wl):
+    M, K = 32, 128
+    c, s = wl.random_packed_weight(M, K, seed=1)
+    w = pkg.PackedWeight(c, s, M, K)
+    y = pkg.DevBuf(M * 4)
+    x = pkg.DevBuf(K * 4)
+    assert lib.qwn_x_gemv_w4a8(None, x.ptr, y.ptr) == -1
+    assert lib.qwn_x_gemv_w4a8(w.ref, None, y.ptr) == -1
+    w.rec.s4_ready = 0
+    assert lib.qwn_x_gemv_w4a8_prepared(w.ref, y.ptr, None) == -1
+    w.rec.s4_ready = 1
+    big = pkg.PackedWeight(c, s, 16, 1 << 20)        # K larger than anything prepared
+    assert lib.qwn_x_gemv_w4a8_prepared(big.ref, y.ptr, None) == -2
+    w2 = pkg.PackedWeight(c, s, M, 256)
+    assert lib.qwn_x_gemv_w4a8_fanout(pkg.weight_array([w, w2]), pkg.ptr_array([y, y]), 2) == -2
+    assert lib.qwn_x_gemv_w4a8_fanout(pkg.weight_array([w]), pkg.ptr_array([y]), 5) == -1
+    w.rec.s8_ready = 1
+    assert lib.qwn_x_gemv_qmma(w.ref, x.ptr, y.ptr) == -20
+
+
+# ---------------------------------------------------------------- GEMM
+GEMM_CASES = [
+    (64, 512, 0, 8, None), (64, 512, 1, 16, None), (48, 384, 0, 24, None),
+    (64, 512, 0, 32, [0, 8, 32]), (64, 512, 1, 64, [0, 8, 16, 40, 64]),
+    (320, 1024, 0, 8, None), (2176, 256, 1, 8, None), (16, 128, 0, 8, None),
+    (128, 256, 0, 136, None), (5120, 512, 0, 64, None),
+    (2048, 512, 0, 64, [0, 8, 64]),      # segments with different split counts (16 and 4)
+]
+
+
+@pytest.mark.parametrize("M,K,ksh,T,offsets", GEMM_CASES)
+def test_gemm_int32_dots_and_fp32(lib, pkg, orc, wl, M, K, ksh, T, offsets):
+    codes, scales = wl.random_packed_weight(M, K, seed=M + K + T, ksh=ksh)
+    w = pkg.PackedWeight(codes, scales, M, K, k64=bool(ksh))
+    x = refgen.gemm_check_rows(T, K)
+    dx = dev(pkg, x)
+    n = K // 32 * T
+    aq, as_, asum = pkg.DevBuf(n * 32), pkg.DevBuf(n * 4), pkg.DevBuf(n * 4)
+    lib.qwn_x_quantize_act_chunk(dx.ptr, K, T, aq.ptr, as_.ptr, asum.ptr)
+    y = pkg.DevBuf(T * M * 4)
+    y.fill(0xA5)
+    off = (C.c_int * len(offsets))(*offsets) if offsets else None
+    nseg = len(offsets) - 1 if offsets else 0
+    assert lib.qwn_x_gemm_w4a8(w.ref, aq.ptr, as_.ptr, asum.ptr, y.ptr, T, off, nseg) == 0
+    lib.tq_sync()
+    oq, os_, osm = orc.quantize_act_chunk(x)
+    dd = pkg.DevBuf(n * M * 4)
+    dd.fill(0xA5)
+    assert lib.qwn_dbg_tile_dots_gemm(w.ref, aq.ptr, T, dd.ptr) == 0
+    assert np.array_equal(dd.to_numpy(np.int32), orc.tile_dots_gemm(codes, M, K, oq, T))
+    got = y.to_numpy(np.float32).reshape(T, M)
+    _, want = orc.gemm_w4a8(codes, scales, M, K, ksh, oq, os_, osm, T, offsets=offsets, fma=1)
+    _, want_sep = orc.gemm_w4a8(codes, scales, M, K, ksh, oq, os_, osm, T, offsets=offsets, fma=0)
+    assert got.tobytes() == want.tobytes()
+    assert close_1e3(got, want_sep)
+    assert lib.tq_last_error() == 0
+
+
+def test_gemm_fanout_equals_per_weight(lib, pkg, orc, wl):
+    K, T, ksh = 512, 8, 1
+    Ms = [1088, 1088]
+    ws = [pkg.PackedWeight(*wl.random_packed_weight(M, K, seed=40 + i, ksh=ksh), M, K, k64=True)
+          for i, M in enumerate(Ms)]
+    x = wl.activations_normal(T, K, seed=4, outlier_frac=0.01)
+    dx = dev(pkg, x)
+    n = K // 32 * T
+    aq, as_, asum = pkg.DevBuf(n * 32), pkg.DevBuf(n * 4), pkg.DevBuf(n * 4)
+    lib.qwn_x_quantize_act_chunk(dx.ptr, K, T, aq.ptr, as_.ptr, asum.ptr)
+    ys = [pkg.DevBuf(T * M * 4) for M in Ms]
+    assert lib.qwn_x_gemm_w4a8_fanout(pkg.weight_array(ws), pkg.ptr_array(ys), 2, aq.ptr, as_.ptr,
+                                      asum.ptr, T, None, 0) == 0
+    for w, yb, M in zip(ws, ys, Ms):
+        y1 = pkg.DevBuf(T * M * 4)
+        assert lib.qwn_x_gemm_w4a8(w.ref, aq.ptr, as_.ptr, asum.ptr, y1.ptr, T, None, 0) == 0
+        lib.tq_sync()
+        assert yb.to_numpy(np.float32).tobytes() == y1.to_numpy(np.float32).tobytes()
+
+
+def test_gemm_errors(lib, pkg, wl):
+    M, K = 16, 128
+    w = pkg.PackedWeight(*wl.random_packed_weight(M, K, seed=1), M, K)
+    b = pkg.DevBuf(8 * K * 4)
+    bad = (C.c_int * 3)(0, 4, 8)
+    assert lib.qwn_x_gemm_w4a8(w.ref, b.ptr, b.ptr, b.ptr, b.ptr, 12, None, 0) == -2
+    assert lib.qwn_x_gemm_w4a8(w.ref, b.ptr, b.ptr, b.ptr, b.ptr, 8, bad, 2) == -2
+    assert lib.qwn_x_gemm_w4a8(w.ref, b.ptr, b.ptr, b.ptr, b.ptr, 8, None, 1) == -2
+    assert lib.qwn_x_gemm_w4a8(w.ref, None, b.ptr, b.ptr, b.ptr, 8, None, 0) == -2
+    w.rec.s4_k16 = 1
+    assert lib.qwn_x_gemm_w4a8(w.ref, b.ptr, b.ptr, b.ptr, b.ptr, 8, None, 0) == -1
+
+
+def test_reference_gates_on_synthetic_weight(lib, pkg, wl):
+    """qwn_gemm_check (cos >= 0.9999), qwn_specwave_check (byte-identical prefix rows)."""
+    M, K = 1088, 5120
+    for ksh in (0, 1):
+        c, s = wl.make_weight_w4(M, K, seed=9, group=32 << ksh)
+        w = pkg.PackedWeight(c, s, M, K, k64=bool(ksh))
+        cos, rel = C.c_double(), C.c_double()
+        for T in (8, 32):
+            assert lib.qwn_gemm_check(w.ref, T, C.byref(cos), C.byref(rel)) == 0
+            assert cos.value >= 0.9999
+        assert lib.qwn_specwave_check(w.ref) == 0
+        assert lib.qwn_gemv_bench(w.ref, 5) > 0 and lib.qwn_gemm_bench(w.ref, 8, 5) > 0
