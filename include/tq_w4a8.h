@@ -184,6 +184,18 @@ int qwn_gemm_check(const tq_qmma_weight_t *w, int tokens, double *worst_cos, dou
 int qwn_specwave_check(const tq_qmma_weight_t *w);
 int qwn_shard_check(const tq_qmma_weight_t *w, int tp);
 
+/* No counterpart in the reference. Same result as qwn_x_gemv_w4a8, for callers that must
+ * not trigger a device allocation (pre-allocated serving loops, callers whose memory pool
+ * already owns the GPU): the quantised-activation staging lives in a fixed array inside the
+ * library's device image (about 80 KiB per GPU, held from load to exit) instead of
+ * cudaMalloc'ed scratch, and no allocating call is made. K is limited to
+ * qwn_static_max_k() (32768); larger K returns -30 with a message. All calls share that one
+ * array: calls ordered on the library's stream are fine, calls made to overlap on the GPU
+ * race. The first call on a device resolves the array's address; make it before any stream
+ * capture. Other return codes as qwn_x_gemv_w4a8 (-31: the address lookup failed). */
+int qwn_x_gemv_w4a8_static(const tq_qmma_weight_t *w, const float *d_x, float *d_y);
+int qwn_static_max_k(void);
+
 /* ---- tensor-parallel exchange: one process per GPU, NCCL loaded at run time.
  * Replaces tq_allreduce's role as the only collective (xpu/src/decode.cpp:133-154) with
  * the all-gather a column shard needs. */

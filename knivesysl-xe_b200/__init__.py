@@ -80,6 +80,7 @@ SIGNATURES = {
     "qwn_gemv_bench": (_d, [_WP, _i]), "qwn_gemm_bench": (_d, [_WP, _i, _i]),
     "qwn_gemm_check": (_i, [_WP, _i, C.POINTER(_d), C.POINTER(_d)]),
     "qwn_specwave_check": (_i, [_WP]), "qwn_shard_check": (_i, [_WP, _i]),
+    "qwn_x_gemv_w4a8_static": (_i, [_WP, _vp, _vp]), "qwn_static_max_k": (_i, []),
     "tq_comm_unique_id": (_i, [_vp]), "tq_comm_init": (_i, [_vp, _i, _i]),
     "tq_comm_allgather": (_i, [_vp, _vp, _sz]),
     "tq_comm_rank": (_i, []), "tq_comm_world": (_i, []), "tq_comm_destroy": (None, []),
