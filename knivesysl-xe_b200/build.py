@@ -13,7 +13,7 @@ ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libforward_qwen_xpu.so")
 
-SOURCES = ["runtime.cu", "quant.cu", "repack.cu", "gemv.cu", "gemm_mma.cu", "gemm_tc.cu",
+SOURCES = ["runtime.cu", "quant.cu", "repack.cu", "gemv.cu", "gemm_mma.cu", "gemm_stream.cu", "gemm_tc.cu",
            "dispatch.cu", "checks.cu", "comm.cu", "gemv_static.cu"]
 
 NVCC_FLAGS = [

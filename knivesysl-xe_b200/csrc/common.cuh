@@ -99,6 +99,16 @@ struct GemmArgs {
     int32_t *dump;           // non-null: write int32 tile dots (single weight)
 };
 void launch_gemm_mma(const GemmArgs &a);
+// gemm_stream.cu (decode batches: one segment, T <= 64, uniform split count <= 8)
+bool gemm_stream_covers(const GemmArgs &a);
+void launch_gemm_stream(const GemmArgs &a);
+// Picks the streaming kernel when it covers the call, else the general mma kernel.
+inline void launch_gemm(const GemmArgs &a) {
+    if (gemm_stream_covers(a))
+        launch_gemm_stream(a);
+    else
+        launch_gemm_mma(a);
+}
 
 // gemm_tc.cu (tcgen05 path, unsplit, per-token or per-block scales)
 struct GemmTcArgs {

@@ -296,7 +296,7 @@ int x_gemm_w4a8_fanout(const tq_qmma_weight_t *const *ws, float *const *ys, int 
     a.ksh = ksh;
     a.T = T;
     a.dump = nullptr;
-    launch_gemm_mma(a);
+    launch_gemm(a);
     return 0;
 }
 
@@ -501,7 +501,7 @@ int qwn_dbg_tile_dots_gemm(const tq_qmma_weight_t *w, const int8_t *d_aq, int T,
     tq::launch_code_sums(d_aq, nblk, d_asum);
     a.as = d_as;
     a.asum = d_asum;
-    tq::launch_gemm_mma(a);
+    tq::launch_gemm(a);
     tq_sync();
     tq_dev_free(d_as);
     tq_dev_free(d_asum);

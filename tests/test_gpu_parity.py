@@ -298,6 +298,13 @@ GEMM_CASES = [
     (320, 1024, 0, 8, None), (2176, 256, 1, 8, None), (16, 128, 0, 8, None),
     (128, 256, 0, 136, None), (5120, 512, 0, 64, None),
     (2048, 512, 0, 64, [0, 8, 64]),      # segments with different split counts (16 and 4)
+    # streaming kernel: several row-groups per warp team, a ragged last ring stage
+    (40000, 320, 1, 8, None),
+    # K64 splits that start on an odd k-tile, odd tile counts, two token groups
+    (4800, 2112, 1, 16, None),
+    # five token groups, 8 splits of 4..5 tiles
+    (1600, 1056, 0, 40, None),
+    (1088, 5120, 1, 8, None),
 ]
 
 
