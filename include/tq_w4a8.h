@@ -81,6 +81,14 @@ void *tq_event_create(void);
 void tq_event_destroy(void *ev);
 void tq_event_record(void *ev);
 float tq_event_elapsed_ms(void *start, void *stop);     /* synchronises on stop */
+/* CUDA graph capture of the calls made on tq_stream() between begin and end (the B200
+ * counterpart of replaying a recorded command list on the reference's in-order queue): no
+ * allocating or blocking call in between, so call every entry point once before capturing.
+ * tq_graph_capture_end returns a handle for tq_graph_launch, or NULL on failure. */
+int tq_graph_capture_begin(void);
+void *tq_graph_capture_end(void);
+void tq_graph_launch(void *graph_exec);
+void tq_graph_destroy(void *graph_exec);
 
 /* ---- flat C entry points (for ctypes / cgo / JNI style bindings). Each forwards
  * to the C++ function of the same name without the qwn_ prefix. */

@@ -51,6 +51,8 @@ SIGNATURES = {
     "tq_d2d_async": (None, [_vp, _vp, _sz]),
     "tq_event_create": (_vp, []), "tq_event_destroy": (None, [_vp]),
     "tq_event_record": (None, [_vp]), "tq_event_elapsed_ms": (_f, [_vp, _vp]),
+    "tq_graph_capture_begin": (_i, []), "tq_graph_capture_end": (_vp, []),
+    "tq_graph_launch": (None, [_vp]), "tq_graph_destroy": (None, [_vp]),
     "qwn_x_w4_repack_weight": (_i, [_WP]), "qwn_x_w4_repack_weight_mode": (_i, [_WP, _i]),
     "qwn_x_quantize_act_s8": (None, [_vp, _i, _vp, _vp, _vp]),
     "qwn_x_prepare_gemv_act_s8": (None, [_vp, _i]),

@@ -4,8 +4,8 @@
 // 945-1102). HBM-bound: the packed weight stream (256 B per 16-row x K32 tile plus a
 // 32 B scale line) is read exactly once; activations (32 B per k-tile) stay in L1/L2.
 //
-// Mapping. One warp owns one (row-group, K-split) task, as the reference's sub-group
-// does. A 256-byte tile is 16 rows x 16 B, so a HALF-warp reads one tile with one
+// Mapping. One warp owns one (row-group, K-split) task at a time, as the reference's
+// sub-group does; the kernel is persistent (two CTAs of 16 warps per SM). A 256-byte tile is 16 rows x 16 B, so a HALF-warp reads one tile with one
 // 128-bit load per lane and the two halves of a warp walk the even and the odd tiles
 // of the split. That is exactly the reference's two-accumulator order (acc0 takes the
 // even offsets from kt_begin, acc1 the odd ones, leftover to acc0), so each lane keeps
@@ -18,17 +18,16 @@
 // activation bytes yields d + 8*asum and the exact int32 dot is recovered inside the
 // zero-point term: d - z*asum == d' - (z+8)*asum. The activation scratch is stored
 // already split into even-k / odd-k halves per tile.
-#include "common.cuh"
+#include "stream.cuh"
+
+#include <algorithm>
 
 namespace tq {
 
 namespace {
 
-constexpr int kUnroll = 4;   // 128-bit weight loads in flight per lane
-
-struct TileOperands {
-    uint4 w;
-};
+constexpr int kU = 5;     // 128-bit weight loads in flight per lane (one batch); more spills at 64 registers
+constexpr int kW = 16;    // warps per CTA
 
 __device__ __forceinline__ int tile_dot_plus8(const uint4 &w, const uint4 &e, const uint4 &o) {
     int d = 0;
@@ -37,49 +36,70 @@ __device__ __forceinline__ int tile_dot_plus8(const uint4 &w, const uint4 &e, co
     const uint32_t oo[4] = {o.x, o.y, o.z, o.w};
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-        const uint32_t lo = (ww[j] & 0x0F0F0F0Fu) ^ 0x08080808u;
-        const uint32_t hi = ((ww[j] >> 4) & 0x0F0F0F0Fu) ^ 0x08080808u;
-        d = __dp4a((int)lo, (int)ee[j], d);
-        d = __dp4a((int)hi, (int)oo[j], d);
+        d = __dp4a((int)nib_plus8(ww[j]), (int)ee[j], d);
+        d = __dp4a((int)nib_plus8(ww[j] >> 4), (int)oo[j], d);
     }
     return d;
 }
 
-template <int W, bool SERIAL, bool DUMP>
-__global__ void __launch_bounds__(W * 32) gemv_w4a8_kernel(const GemvArgs a) {
-    __shared__ float part[W * 16];
+__device__ __forceinline__ uint32_t ldg_stream_u16(const uint16_t *p) {
+    uint16_t v;
+    asm volatile("ld.global.nc.L1::no_allocate.u16 %0, [%1];" : "=h"(v) : "l"(p));
+    return v;
+}
+
+// Persistent kernel: a team of S warps owns one 16-row group at a time (warp s = K-split
+// s) and walks the row-groups team, team + teams, ... Each half-warp reads whole tiles
+// (one 128-bit load per lane = one row of a tile), so a warp keeps up to 2 * kU tiles
+// in flight per batch; a batch is loaded completely, scale words included, before
+// it is consumed, and 32 warps per SM overlap each other's batches.
+template <bool SERIAL, bool DUMP>
+__global__ void __launch_bounds__(kW * 32, 2) gemv_w4a8_kernel(const GemvArgs a) {
+    __shared__ float part[kW * 16];
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int h = lane >> 4;
     const int n = lane & 15;
     const int S = a.splits;
+    const int tpc = kW / S;                       // teams per CTA
+    const int team = warp / S;
+    const int split = warp - team * S;
     const int Kt = a.K >> 5;
+    const int Ktg = Kt >> a.ksh;
     const int groups = a.goff[a.count];
-    const int tasks = groups * S;
-    const int task = blockIdx.x * W + warp;
+    const int teams = gridDim.x * tpc;
+    const int kt_begin = Kt * split / S;
+    const int cnt = Kt * (split + 1) / S - kt_begin;
+    // tiles of this half-warp: offsets h, h+2, ... inside the split; balanced batches
+    const int nper = (cnt + 1) >> 1;
+    const int nb = (nper + kU - 1) / kU;
+    const int ub = nb ? (nper + nb - 1) / nb : 0;
 
-    float acc = 0.0f;
-    if (task < tasks) {
-        const int g = task / S;
-        const int split = task - g * S;
+    for (int g = blockIdx.x + gridDim.x * team; g < groups; g += teams) {
         int wi = 0;
         while (wi + 1 < a.count && g >= a.goff[wi + 1]) ++wi;
         const int lg = g - a.goff[wi];
-        const uint8_t *bbase = a.codes[wi] + (size_t)lg * Kt * 256u + (size_t)n * 16u;
-        const uint16_t *sbase = a.scales[wi] + (size_t)lg * (Kt >> a.ksh) * 16u + n;
-        const int kt_begin = Kt * split / S;
-        const int cnt = Kt * (split + 1) / S - kt_begin;
+        const uint8_t *bbase =
+            a.codes[wi] + ((size_t)lg * Kt + kt_begin) * 256u + (size_t)n * 16u;
+        const uint16_t *sbase = a.scales[wi] + (size_t)lg * Ktg * 16u + n;
 
-        for (int i0 = 0; i0 < cnt; i0 += 2 * kUnroll) {
-            uint4 wv[kUnroll];
+        float acc = 0.0f;
+        for (int b = 0; b < nb; ++b) {
+            const int i0 = b * ub;
+            uint4 wv[kU];
+            uint32_t sc[kU];
 #pragma unroll
-            for (int u = 0; u < kUnroll; ++u) {
-                const int idx = i0 + 2 * u + h;
-                if (idx < cnt) wv[u] = ldg_stream_v4(bbase + (size_t)(kt_begin + idx) * 256u);
+            for (int u = 0; u < kU; ++u) {
+                const int idx = 2 * (i0 + u) + h;
+                if (u < ub && idx < cnt) {
+                    wv[u] = ldg_stream_v4(bbase + (size_t)idx * 256u);
+                    sc[u] = ldg_stream_u16(sbase + (size_t)((kt_begin + idx) >> a.ksh) * 16u);
+                }
             }
 #pragma unroll
-            for (int u = 0; u < kUnroll; ++u) {
-                const int idx = i0 + 2 * u + h;
+            for (int u = 0; u < kU; ++u) {
+                if (u >= ub) break;
+                const int idx = 2 * (i0 + u) + h;
                 const bool valid = idx < cnt;
                 float fa = 0.0f, fb = 0.0f;
                 if (valid) {
@@ -88,14 +108,11 @@ __global__ void __launch_bounds__(W * 32) gemv_w4a8_kernel(const GemvArgs a) {
                     const uint4 o =
                         __ldg(reinterpret_cast<const uint4 *>(a.qp + (size_t)kt * 32 + 16));
                     const int dp = tile_dot_plus8(wv[u], e, o);
-                    const uint32_t packed = __ldg(sbase + (size_t)(kt >> a.ksh) * 16u);
                     int zp;
                     float ws;
-                    unpack_scale(packed, zp, ws);
+                    unpack_scale(sc[u], zp, ws);
                     const int asum = __ldg(a.sum32 + kt);
-                    if (DUMP) {
-                        a.dump[((size_t)g * Kt + kt) * 16 + n] = dp - 8 * asum;
-                    }
+                    if (DUMP) a.dump[((size_t)g * Kt + kt) * 16 + n] = dp - 8 * asum;
                     const float f = (float)(dp - (zp + 8) * asum);
                     fa = __fmul_rn(f, ws);
                     fb = __ldg(a.as + kt);
@@ -108,63 +125,55 @@ __global__ void __launch_bounds__(W * 32) gemv_w4a8_kernel(const GemvArgs a) {
                     const float ob = __shfl_down_sync(0xffffffffu, fb, 16);
                     if (h == 0) {
                         if (valid) acc = fmaf(fa, fb, acc);
-                        if (i0 + 2 * u + 1 < cnt) acc = fmaf(oa, ob, acc);
+                        if (idx + 1 < cnt) acc = fmaf(oa, ob, acc);
                     }
                 }
             }
         }
+        if (DUMP) continue;
         if (!SERIAL) acc = __fadd_rn(acc, __shfl_down_sync(0xffffffffu, acc, 16));
-    }
-    if (DUMP) return;
 
-    if (S == 1) {
-        if (task < tasks && h == 0) {
-            int wi = 0;
-            while (wi + 1 < a.count && task >= a.goff[wi + 1]) ++wi;
-            const int row = (task - a.goff[wi]) * 16 + n;
+        const int row = lg * 16 + n;
+        if (S == 1) {
             // unsplit: the accumulator is stored as is; a residual is a separate add
-            a.y[wi][row] = a.residual ? __fadd_rn(acc, a.residual[row]) : acc;
+            if (h == 0) a.y[wi][row] = a.residual ? __fadd_rn(acc, a.residual[row]) : acc;
+            continue;
         }
-        return;
+        if (h == 0) part[warp * 16 + n] = acc;
+        named_bar_sync(1 + team, S * 32);
+        if (split == 0 && h == 0) {
+            float sum = 0.0f;
+            for (int i = 0; i < S; ++i) sum = __fadd_rn(sum, part[(warp + i) * 16 + n]);
+            if (SERIAL)
+                a.y[wi][row] = sum;
+            else
+                a.y[wi][row] = __fadd_rn(sum, a.residual ? a.residual[row] : 0.0f);
+        }
+        named_bar_sync(1 + team, S * 32);     // part is rewritten by the next row-group
     }
-    if (h == 0) part[warp * 16 + n] = acc;
-    __syncthreads();
-    const int gpw = W / S;                 // complete row-groups per block
-    if (warp >= gpw || h != 0) return;
-    const int g = blockIdx.x * gpw + warp;
-    if (g >= groups) return;
-    float sum = 0.0f;
-    for (int i = 0; i < S; ++i) sum = __fadd_rn(sum, part[(warp * S + i) * 16 + n]);
-    int wi = 0;
-    while (wi + 1 < a.count && g >= a.goff[wi + 1]) ++wi;
-    const int row = (g - a.goff[wi]) * 16 + n;
-    if (SERIAL)
-        a.y[wi][row] = sum;
-    else
-        a.y[wi][row] = __fadd_rn(sum, a.residual ? a.residual[row] : 0.0f);
 }
 
-template <int W>
-void launch_w(const GemvArgs &a, int grid) {
-    if (a.dump)
-        gemv_w4a8_kernel<W, false, true><<<grid, W * 32, 0, stream()>>>(a);
-    else if (a.serial)
-        gemv_w4a8_kernel<W, true, false><<<grid, W * 32, 0, stream()>>>(a);
-    else
-        gemv_w4a8_kernel<W, false, false><<<grid, W * 32, 0, stream()>>>(a);
-}
+int g_sms = 0;
 
 }  // namespace
 
 void launch_gemv(const GemvArgs &a) {
     const int groups = a.goff[a.count];
-    const int tasks = groups * a.splits;
-    if (tasks <= 0) return;
-    if (a.splits == 16) {
-        launch_w<16>(a, (tasks + 15) / 16);
-    } else {
-        launch_w<8>(a, (tasks + 7) / 8);
+    if (groups <= 0 || a.splits <= 0) return;
+    if (!g_sms) {
+        int dev = 0;
+        TQ_CHECK(cudaGetDevice(&dev));
+        TQ_CHECK(cudaDeviceGetAttribute(&g_sms, cudaDevAttrMultiProcessorCount, dev));
+        if (g_sms <= 0) g_sms = 148;
     }
+    const int tpc = kW / a.splits;
+    const int grid = std::min(2 * g_sms, (groups + tpc - 1) / tpc);
+    if (a.dump)
+        gemv_w4a8_kernel<false, true><<<grid, kW * 32, 0, stream()>>>(a);
+    else if (a.serial)
+        gemv_w4a8_kernel<true, false><<<grid, kW * 32, 0, stream()>>>(a);
+    else
+        gemv_w4a8_kernel<false, false><<<grid, kW * 32, 0, stream()>>>(a);
     TQ_LAUNCH_CHECK("gemv_w4a8_kernel");
 }
 

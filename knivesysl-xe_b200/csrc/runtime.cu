@@ -187,6 +187,37 @@ void tq_event_destroy(void *ev) {
 
 void tq_event_record(void *ev) { TQ_CHECK(cudaEventRecord((cudaEvent_t)ev, tq::stream())); }
 
+// Stream capture into a CUDA graph: everything issued on tq_stream() between begin and end
+// becomes one replayable graph (no allocation or blocking call may happen in between, so
+// warm every entry point up once before capturing).
+int tq_graph_capture_begin(void) {
+    cudaError_t e = cudaStreamBeginCapture(tq::stream(), cudaStreamCaptureModeThreadLocal);
+    tq::note_error(e, "cudaStreamBeginCapture");
+    return e == cudaSuccess ? 0 : -1;
+}
+
+void *tq_graph_capture_end(void) {
+    cudaGraph_t graph = nullptr;
+    cudaError_t e = cudaStreamEndCapture(tq::stream(), &graph);
+    if (e != cudaSuccess || !graph) {
+        tq::note_error(e, "cudaStreamEndCapture");
+        return nullptr;
+    }
+    cudaGraphExec_t exec = nullptr;
+    e = cudaGraphInstantiate(&exec, graph, 0);
+    tq::note_error(e, "cudaGraphInstantiate");
+    cudaGraphDestroy(graph);
+    return e == cudaSuccess ? (void *)exec : nullptr;
+}
+
+void tq_graph_launch(void *exec) {
+    if (exec) TQ_CHECK(cudaGraphLaunch((cudaGraphExec_t)exec, tq::stream()));
+}
+
+void tq_graph_destroy(void *exec) {
+    if (exec) TQ_CHECK(cudaGraphExecDestroy((cudaGraphExec_t)exec));
+}
+
 float tq_event_elapsed_ms(void *start, void *stop) {
     float ms = -1.0f;
     TQ_CHECK(cudaEventSynchronize((cudaEvent_t)stop));

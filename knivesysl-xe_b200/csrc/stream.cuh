@@ -72,6 +72,17 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t
         : "memory");
 }
 
+// Asks the copy engine to pull [src, src + bytes) into L2 (fire and forget; 16-byte aligned,
+// bytes % 16 == 0). Later plain loads of the range then hit L2 instead of waiting for HBM.
+__device__ __forceinline__ void bulk_prefetch_l2(const void *src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
+
+// Pulls the 128-byte line at p into L2 (no register, no wait).
+__device__ __forceinline__ void prefetch_l2(const void *p) {
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+}
+
 // 16-byte asynchronous copy global -> shared that bypasses L1 (per-lane; completion is
 // tracked with commit/wait groups, so there is nothing to spin on).
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint64_t policy) {
@@ -113,6 +124,14 @@ __device__ __forceinline__ void mma_s8_c(int (&d)[4], uint32_t a0, uint32_t a1, 
 __device__ __forceinline__ void make_const_quad(int (&c)[4], int v) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) asm volatile("mov.b32 %0, %1;" : "=r"(c[i]) : "r"(v));
+}
+
+// Four two's-complement nibbles (the low nibble of each byte of w) -> four bytes q+8:
+// (w & 0x0F0F0F0F) ^ 0x08080808 as ONE three-input logic op.
+__device__ __forceinline__ uint32_t nib_plus8(uint32_t w) {
+    uint32_t d;
+    asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(d) : "r"(w), "r"(0x0F0F0F0Fu), "r"(0x08080808u));
+    return d;
 }
 
 // ---- packed pairs of fp32 (one instruction for two IEEE round-to-nearest results) ----
