@@ -131,6 +131,33 @@ void launch_w4_repack(const uint8_t *d_payload, const float *d_bs, int scale_col
 // ---- device helpers ---------------------------------------------------------------
 #ifdef __CUDACC__
 
+// Programmatic dependent launch. A kernel started with launch_pdl may begin while the
+// kernel before it on the stream is still running; it must call pdl_wait() before it reads
+// anything an earlier kernel wrote and before its first global write (pdl_wait returns
+// once every earlier kernel has completed and its writes are visible). What comes before
+// pdl_wait may only read data no kernel writes, i.e. the packed weights. pdl_trigger() lets
+// the next kernel's CTAs be scheduled as soon as there is room for them.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+template <class... KArgs, class... Args>
+inline void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                       Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream();
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    TQ_CHECK(cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...));
+}
+
 // exp() built only from IEEE add/mul/fma so that host and device agree bit-for-bit
 // (the reference's sycl::exp is implementation-defined within 3 ulp).
 __device__ __forceinline__ float det_expf(float x) {

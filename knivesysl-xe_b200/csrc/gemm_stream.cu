@@ -6,7 +6,7 @@
 // decode uses. The kernel is HBM-bound on the packed weight stream; what limits it in
 // practice is the shared-memory/L1 data path (128 B per clock per SM) and the issue slots
 // spent per 256-byte tile, so the design keeps both small:
-//  * one CTA per SM, 16 warps. All warps of a CTA work on the SAME K-split s (CTA b takes
+//  * one CTA per SM, 16 warps (24 when that saves a pass). All warps of a CTA work on the SAME K-split s (CTA b takes
 //    s = b % S), each warp on its own 16-row groups. Lane (r, c) loads word c of rows r
 //    and r+8 of a tile (two coalesced 128-byte requests per tile, L1 not allocated) -
 //    exactly the A fragment of mma.sync.m16n8k32 - into one of two register buffers of
@@ -44,7 +44,7 @@ namespace tq {
 namespace {
 
 constexpr int kCT = 8;                          // k-tiles per chunk (register queue depth)
-constexpr int kW = 16;                          // warps per CTA
+constexpr int kWmax = 24;                       // most warps per CTA of any variant
 constexpr int kExpBytes = kCT * 16 * 8;         // expanded scales of one chunk, per group
 constexpr int kActTileBytes = 256 + 64;         // staged activations per (k-tile, 8 tokens)
 
@@ -54,7 +54,7 @@ __device__ __forceinline__ uint32_t ldg_stream_u16(const uint16_t *p) {
     return v;
 }
 
-template <int NTG, bool STAGED, bool DUMP>
+template <int NTG, bool STAGED, bool DUMP, int kW>
 __global__ void __launch_bounds__(kW * 32, 1)
 gemm_w4a8_stream_kernel(const GemmArgs a, float *__restrict__ part, int *__restrict__ count) {
     extern __shared__ __align__(128) unsigned char smem[];
@@ -148,11 +148,14 @@ gemm_w4a8_stream_kernel(const GemmArgs a, float *__restrict__ part, int *__restr
     };
 
     // first chunk of this warp: fill the queue
+    pdl_trigger();
     advance();
     load_chunk(w0);
     load_scales();
     int cur_nt = nx_nt, cur_kt0 = nx_kt0;
     advance();
+    // Everything above reads only packed weights; what follows depends on earlier kernels.
+    pdl_wait();
 
     // Stage this split's activations (all warps; the first weight loads are in flight).
     // Layout per (k-tile, token group): 32 lanes x 8 bytes of codes in B-fragment order
@@ -400,11 +403,11 @@ void ensure_scratch(size_t part_floats, int count_n) {
     }
 }
 
-template <int NTG, bool STAGED, bool DUMP>
+template <int NTG, bool STAGED, bool DUMP, int kW>
 void launch_variant(const GemmArgs &a, size_t smem) {
     static bool attr_set = false;
     if (!attr_set) {
-        TQ_CHECK(cudaFuncSetAttribute(gemm_w4a8_stream_kernel<NTG, STAGED, DUMP>,
+        TQ_CHECK(cudaFuncSetAttribute(gemm_w4a8_stream_kernel<NTG, STAGED, DUMP, kW>,
                                       cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       (int)kSmemLimit));
         attr_set = true;
@@ -414,8 +417,8 @@ void launch_variant(const GemmArgs &a, size_t smem) {
     if (S > 1 && !DUMP) ensure_scratch((size_t)groups * S * NTG * 128, groups);
     const int want = ((groups + kW - 1) / kW) * S;
     const int grid = std::max(S, std::min(g_num_sms, want));
-    gemm_w4a8_stream_kernel<NTG, STAGED, DUMP>
-        <<<grid, kW * 32, smem, stream()>>>(a, g_scratch.part, g_scratch.count);
+    launch_pdl(gemm_w4a8_stream_kernel<NTG, STAGED, DUMP, kW>, dim3(grid), dim3(kW * 32), smem, a,
+               g_scratch.part, g_scratch.count);
     TQ_LAUNCH_CHECK("gemm_w4a8_stream_kernel");
 }
 
@@ -428,20 +431,31 @@ void launch_ntg(const GemmArgs &a) {
         if (g_num_sms <= 0) g_num_sms = 148;
     }
     if (a.dump) {
-        launch_variant<NTG, false, true>(a, (size_t)kW * kExpBytes);
+        launch_variant<NTG, false, true, 16>(a, (size_t)16 * kExpBytes);
         return;
     }
-    const size_t base = (size_t)kW * kExpBytes;
     if constexpr (NTG <= 4) {
         // stage this split's activations in shared memory when they fit
         const int Kt = a.K >> 5, S = a.max_splits;
         const size_t act = (size_t)((Kt + S - 1) / S) * NTG * kActTileBytes;
-        if (base + act <= kSmemLimit) {
-            launch_variant<NTG, true, false>(a, base + act);
+        if ((size_t)kWmax * kExpBytes + act <= kSmemLimit) {
+            if constexpr (NTG <= 2) {
+                // 24 warps per CTA (fewer registers each) when that saves a whole pass over
+                // the row-groups: every (row-group, split) is one indivisible warp task
+                const int groups = a.goff[a.count];
+                const int ctas = std::max(1, g_num_sms / S);
+                const int rounds16 = (groups + ctas * 16 - 1) / (ctas * 16);
+                const int rounds24 = (groups + ctas * 24 - 1) / (ctas * 24);
+                if (rounds24 < rounds16 && rounds16 <= 3) {
+                    launch_variant<NTG, true, false, 24>(a, (size_t)24 * kExpBytes + act);
+                    return;
+                }
+            }
+            launch_variant<NTG, true, false, 16>(a, (size_t)16 * kExpBytes + act);
             return;
         }
     }
-    launch_variant<NTG, false, false>(a, base);
+    launch_variant<NTG, false, false, 16>(a, (size_t)16 * kExpBytes);
 }
 
 }  // namespace

@@ -75,6 +75,20 @@ __global__ void __launch_bounds__(kW * 32, 2) gemv_w4a8_kernel(const GemvArgs a)
     const int nb = (nper + kU - 1) / kU;
     const int ub = nb ? (nper + nb - 1) / nb : 0;
 
+    pdl_trigger();
+    {
+        // Before waiting for earlier kernels: pull this warp's first weight span into L2.
+        const int g = blockIdx.x + gridDim.x * team;
+        if (g < groups && cnt > 0) {
+            int wi = 0;
+            while (wi + 1 < a.count && g >= a.goff[wi + 1]) ++wi;
+            const int lg = g - a.goff[wi];
+            const uint8_t *p = a.codes[wi] + ((size_t)lg * Kt + kt_begin) * 256u;
+            for (int line = lane; line < cnt * 2; line += 32) prefetch_l2(p + line * 128);
+        }
+    }
+    pdl_wait();
+
     for (int g = blockIdx.x + gridDim.x * team; g < groups; g += teams) {
         int wi = 0;
         while (wi + 1 < a.count && g >= a.goff[wi + 1]) ++wi;
@@ -169,11 +183,11 @@ void launch_gemv(const GemvArgs &a) {
     const int tpc = kW / a.splits;
     const int grid = std::min(2 * g_sms, (groups + tpc - 1) / tpc);
     if (a.dump)
-        gemv_w4a8_kernel<false, true><<<grid, kW * 32, 0, stream()>>>(a);
+        launch_pdl(gemv_w4a8_kernel<false, true>, dim3(grid), dim3(kW * 32), 0, a);
     else if (a.serial)
-        gemv_w4a8_kernel<true, false><<<grid, kW * 32, 0, stream()>>>(a);
+        launch_pdl(gemv_w4a8_kernel<true, false>, dim3(grid), dim3(kW * 32), 0, a);
     else
-        gemv_w4a8_kernel<false, false><<<grid, kW * 32, 0, stream()>>>(a);
+        launch_pdl(gemv_w4a8_kernel<false, false>, dim3(grid), dim3(kW * 32), 0, a);
     TQ_LAUNCH_CHECK("gemv_w4a8_kernel");
 }
 

@@ -43,6 +43,7 @@ quant_s8_kernel(const float *__restrict__ x, const float *__restrict__ up,
                 float *__restrict__ hidden, int blocks, int8_t *__restrict__ q,
                 int8_t *__restrict__ qp, float *__restrict__ scale, int32_t *__restrict__ sum16,
                 int32_t *__restrict__ sum32) {
+    pdl_trigger();   // the next kernel may start its weight prefetch now
     const int b = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (b >= blocks) return;
@@ -69,6 +70,7 @@ quant_s8_kernel(const float *__restrict__ x, const float *__restrict__ up,
 // warp sums added 0..7 (the order the CPU oracle restates).
 __global__ void __launch_bounds__(256)
 sumsq_partial_kernel(const float *__restrict__ in, int H, float *__restrict__ part) {
+    pdl_trigger();   // the next kernel may start its weight prefetch now
     __shared__ float wsum[8];
     const int i = blockIdx.x * 256 + threadIdx.x;
     const float v = (i < H) ? in[i] : 0.0f;
@@ -92,6 +94,7 @@ rmsnorm_quant_kernel(float *__restrict__ out, const float *__restrict__ in,
                      const float *__restrict__ part, int nblk, int8_t *__restrict__ q,
                      int8_t *__restrict__ qp, float *__restrict__ scale,
                      int32_t *__restrict__ sum16, int32_t *__restrict__ sum32) {
+    pdl_trigger();   // the next kernel may start its weight prefetch now
     __shared__ float s_rms;
     if (threadIdx.x == 0) {
         float sum_sq = 0.0f;
@@ -126,6 +129,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 quant_chunk_kernel(const float *__restrict__ x, int K, int T, size_t blocks,
                    int8_t *__restrict__ aq, float *__restrict__ as, int32_t *__restrict__ asum,
                    const float *__restrict__ as_tok) {
+    pdl_trigger();   // the next kernel may start its weight prefetch now
     const size_t blk = (size_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (blk >= blocks) return;
@@ -151,6 +155,7 @@ quant_chunk_kernel(const float *__restrict__ x, int K, int T, size_t blocks,
 // Per-token absmax -> scale (one block per token row).
 __global__ void __launch_bounds__(256)
 token_scale_kernel(const float *__restrict__ x, int K, float *__restrict__ as_tok) {
+    pdl_trigger();   // the next kernel may start its weight prefetch now
     __shared__ float wmax[8];
     const float *row = x + (size_t)blockIdx.x * K;
     float m = -INFINITY;
