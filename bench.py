@@ -36,7 +36,7 @@ METRIC = "decode_gemv_weight_GBps"
 UNIT = "GB/s"
 # dram__bytes_read.sum + dram__bytes_write.sum of one GEMM launch of this workload, from the
 # ncu capture summarised in profiles/ (None until a capture exists)
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 97_661_952
 
 
 def measured_peaks():
@@ -345,7 +345,7 @@ def main():
                                (" + all-gather" if world > 1 else "")},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "peak_source": f"{peak_kind} copy bandwidth",
-                         "kernel": "gemm_w4a8_mma_kernel", "us_per_launch": k_ms * 1e3,
+                         "kernel": "gemm_w4a8_stream_kernel", "us_per_launch": k_ms * 1e3,
                          "algorithmic_bytes_per_launch": algo_bytes,
                          "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH},
             "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": int(x.nbytes),

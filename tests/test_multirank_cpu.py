@@ -1,0 +1,109 @@
+"""The N > 1 path on CPU: two gloo ranks column-shard a packed weight the way bench.py and
+x_w4_shard (mode 0) do, run the projection on their shard (CPU oracle in the role of the
+device kernel), all-gather the output slices and compare with the unsharded result. Mirrors
+the reference's shard gate (xpu/src/kernels_dpas.cpp:2544-2599): the concatenation of column
+shards must be bit-identical to the full projection."""
+import importlib
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _rank_main(rank, world, port, groups, q):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import torch
+    import torch.distributed as dist
+    from oracle import oracle as orc
+    import refgen
+    wl = importlib.import_module("knivesysl-xe_b200.workloads")
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        M, K, T, ksh = 256, 512, 8, 1
+        codes, scales = wl.random_packed_weight(M, K, seed=5, ksh=ksh)     # same on every rank
+        x = refgen.gemm_check_rows(T, K)
+        aq, as_, asum = orc.quantize_act_chunk(x)
+        rc, sc, ss = orc.w4_shard_column(codes, scales, M, K, ksh, rank, world, groups=groups)
+        assert rc == 0
+        Mn = M // world
+        _, y_local = orc.gemm_w4a8(sc, ss, Mn, K, ksh, aq, as_, asum, T, fma=1)
+        y_local = torch.from_numpy(np.ascontiguousarray(y_local.reshape(T, Mn)))
+        gathered = [torch.empty_like(y_local) for _ in range(world)]
+        dist.all_gather(gathered, y_local)                                  # [rank][T][Mn]
+        if rank == 0:
+            _, y_full = orc.gemm_w4a8(codes, scales, M, K, ksh, aq, as_, asum, T, fma=1)
+            y_full = y_full.reshape(T, M)
+            # rebuild the row order: within every group, rank r owns the r-th run of rows
+            gs = groups or [M]
+            out = np.empty((T, M), dtype=np.float32)
+            src_off = [0] * world
+            dst = 0
+            for gsz in gs:
+                per = gsz // world
+                for r in range(world):
+                    out[:, dst:dst + per] = gathered[r].numpy()[:, src_off[r]:src_off[r] + per]
+                    src_off[r] += per
+                    dst += per
+            q.put(out.tobytes() == y_full.tobytes())
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("groups", [None, [128, 128]])
+def test_two_rank_column_shard_allgather_bit_identical(groups):
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, groups, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+    assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+    assert q.get(timeout=5) is True
+
+
+def test_max_over_ranks_timing_reduction():
+    """bench.py reports the slowest rank: the MAX all-reduce it uses, on two gloo ranks."""
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_max_main, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+    assert all(p.exitcode == 0 for p in procs)
+    assert q.get(timeout=5) == 7.0
+
+
+def _max_main(rank, world, port, q):
+    import torch
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    t = torch.tensor([3.0 if rank == 0 else 7.0], dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        q.put(float(t.item()))
+    dist.barrier()
+    dist.destroy_process_group()
