@@ -1,9 +1,443 @@
-// gemm_tc.cu — tcgen05 prefill GEMM (placeholder until the tensor-memory kernel lands):
-// reports "shape not covered" so callers take the mma.sync kernel.
-#include "common.cuh"
+// gemm_tc.cu — prefill W4A8 GEMM on the sm_100a tensor cores: tcgen05.mma kind::i8 with
+// int32 accumulators in tensor memory (TMEM).
+//
+// Replaces gemm_rc16 / the unsplit path of x_gemm_w4a8 (xpu/src/kernels_dpas.cpp:1255-1332,
+// 1371-1378): Y[tok][n] = sum over k-tiles, ascending, of (float)(d - z*asum) * (ws*as) with
+// d the exact int32 dot of one 16-row x K32 tile, accumulated with fma into one fp32
+// accumulator per output - the arithmetic and the order of the reference.
+//
+// Mapping. Weights are the M side of the MMA (128 output rows = 128 TMEM lanes), tokens the
+// N side (128 per CTA tile), K = 32 per instruction = one k-tile, so one MMA produces exactly
+// the per-k-tile int32 dots the reference promotes. A CTA (13 warps, one per SM, persistent
+// over tiles) runs three roles connected by mbarriers, 4 slots deep:
+//  * producers (4 warps, thread = weight row): load the row's 16 packed bytes of a k-tile,
+//    expand the nibbles to int8 bytes q+8 with two logic ops per word and store them as the
+//    two 16-byte K-chunks of the row in the canonical no-swizzle K-major core-matrix layout
+//    (even-k codes first, then odd-k: any fixed permutation of k inside a tile is exact for
+//    an integer dot, and the activation image uses the same one); one thread starts bulk
+//    (TMA) copies of the activation image of the tile (4 KiB) and of its per-token
+//    {as, as, asum, asum} pairs (1 KiB), prepared by a pre-pass in exactly that layout;
+//  * one MMA thread: tcgen05.mma (M=128, N=128, K=32) into accumulator slot b. The slot was
+//    pre-filled with the bit pattern of 12582912.0f, and the MMA accumulates on top of it,
+//    so the exact int32 dot comes back as an fp32 bit pattern that one add converts;
+//    tcgen05.commit signals the epilogue;
+//  * epilogue (8 warps, thread = weight row x 64 tokens): tcgen05.ld the slot, re-arm it
+//    with the bias pattern (tcgen05.st), then per token pair on packed f32x2 instructions:
+//    f = fma(-(z+8), asum, bits - 12582912) (exact), acc = fma(f, ws*as, acc); 64 fp32
+//    accumulators stay in registers for the whole K loop and are stored at the end
+//    (coalesced over rows).
+// The epilogue is the wall, as on the reference's hardware: 2 issue slots per output per
+// k-tile against 64 tensor-core clocks per 128x128x32 MMA.
+//
+// Every mbarrier wait is bounded; on expiry the kernel records a status word, stops
+// issuing work, still frees its TMEM and returns.
+#include "stream.cuh"
+
+#include <cuda_bf16.h>
+
+#include <algorithm>
 
 namespace tq {
 
-int launch_gemm_tc(const GemmTcArgs &) { return -1; }
+namespace {
+
+constexpr int kTM = 128;                 // weight rows per tile (TMEM lanes)
+constexpr int kTN = 128;                 // tokens per tile (accumulator columns)
+constexpr int kNB = 4;                   // pipeline slots = accumulator buffers
+constexpr int kABytes = kTM * 32;        // expanded int8 weights of one k-tile
+constexpr int kBBytes = kTN * 32;        // int8 activations of one k-tile
+constexpr int kSBytes = kTN / 2 * 16;    // {as0, as1, asum0, asum1} per token pair
+constexpr int kSlotBytes = kABytes + kBBytes + kSBytes;
+constexpr int kEpiWarps = 8, kProdWarps = 4;
+constexpr int kThreads = (kEpiWarps + kProdWarps + 1) * 32;
+constexpr int kSmemBytes = 120 * 1024;   // > half an SM's shared memory: one CTA per SM,
+                                         // which the 512-column TMEM allocation requires
+
+// ---- tcgen05 wrappers ------------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst),
+                 "r"(cols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols)
+                 : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                     bar)
+                 : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem], M = 128, K = 32 bytes, int8 x int8 -> int32
+__device__ __forceinline__ void tc_mma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                          uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+        :
+        : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,"
+        "%15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+          "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
+          "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st16_const(uint32_t taddr, uint32_t c) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,"
+        "%14,%15,%16};" ::"r"(taddr),
+        "r"(c), "r"(c), "r"(c), "r"(c), "r"(c), "r"(c), "r"(c), "r"(c), "r"(c), "r"(c), "r"(c),
+        "r"(c), "r"(c), "r"(c), "r"(c), "r"(c)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() {
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() {
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// plain (no cache hint) bulk copy global -> shared, completion on an mbarrier
+__device__ __forceinline__ void bulk_g2s_plain(uint32_t dst, const void *src, uint32_t bytes,
+                                               uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
+            "r"(dst),
+        "l"(src), "r"(bytes), "r"(bar)
+        : "memory");
+}
+
+// K-major, no swizzle: core matrix = 8 rows x 16 bytes (128 contiguous bytes); the two
+// 16-byte K-chunks of a row group are kLbo apart, row groups of 8 are kSbo apart.
+constexpr uint32_t kLbo = 128, kSbo = 256;
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)(kLbo >> 4) << 16) |
+           ((uint64_t)(kSbo >> 4) << 32) | (1ull << 46);   // version 1, base offset 0, no swizzle
+}
+// instruction descriptor: D = s32 (2), A and B signed 8 bit (1) (the expanded weights are
+// 0..15), both K-major, N >> 3 at bit 17, M >> 4 at bit 24
+constexpr uint32_t kIdesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kTN >> 3) << 17) |
+                            ((uint32_t)(kTM >> 4) << 24);
+
+struct TcParams {
+    const uint8_t *codes;
+    const uint16_t *scales;
+    const uint8_t *bimg;     // activation image [Kt][Tpad/8][2][8][16]
+    const float4 *simg;      // [Kt][Tpad/2] {as0, as1, (float)asum0, (float)asum1}
+    void *y;
+    int *status;
+    int M, Kt, ksh, T, Tpad, out_bf16;
+};
+
+// Pre-pass: the caller's staging (aq[kt][tok][32], as[kt][tok], asum[kt][tok]) -> the images
+// the GEMM tiles copy with one bulk copy each. Tokens >= T are padded with zeros.
+__global__ void __launch_bounds__(256)
+gemm_tc_prepass_kernel(const int8_t *__restrict__ aq, const float *__restrict__ as,
+                       const int32_t *__restrict__ asum, int T, int Tpad, int Kt,
+                       uint8_t *__restrict__ bimg, float4 *__restrict__ simg) {
+    pdl_trigger();
+    const size_t nrow = (size_t)Kt * Tpad;
+    for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < nrow; i += (size_t)gridDim.x * 256) {
+        const int kt = (int)(i / Tpad), tok = (int)(i % Tpad);
+        uint4 lo = make_uint4(0, 0, 0, 0), hi = make_uint4(0, 0, 0, 0);
+        if (tok < T) {
+            const uint4 *src = reinterpret_cast<const uint4 *>(aq + ((size_t)kt * T + tok) * 32);
+            const uint4 a = __ldg(src), b = __ldg(src + 1);    // k = 0..15, 16..31
+            // even-k bytes -> chunk 0, odd-k bytes -> chunk 1 (the weight expansion's order)
+            lo = make_uint4(__byte_perm(a.x, a.y, 0x6420), __byte_perm(a.z, a.w, 0x6420),
+                            __byte_perm(b.x, b.y, 0x6420), __byte_perm(b.z, b.w, 0x6420));
+            hi = make_uint4(__byte_perm(a.x, a.y, 0x7531), __byte_perm(a.z, a.w, 0x7531),
+                            __byte_perm(b.x, b.y, 0x7531), __byte_perm(b.z, b.w, 0x7531));
+        }
+        uint8_t *dst = bimg + ((size_t)kt * (Tpad / 8) + (tok >> 3)) * 256 + (tok & 7) * 16;
+        *reinterpret_cast<uint4 *>(dst) = lo;
+        *reinterpret_cast<uint4 *>(dst + 128) = hi;
+        if ((tok & 1) == 0) {
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (tok < T) {
+                v.x = as[(size_t)kt * T + tok];
+                v.z = (float)asum[(size_t)kt * T + tok];
+            }
+            if (tok + 1 < T) {
+                v.y = as[(size_t)kt * T + tok + 1];
+                v.w = (float)asum[(size_t)kt * T + tok + 1];
+            }
+            simg[((size_t)kt * Tpad + tok) >> 1] = v;
+        }
+    }
+}
+
+constexpr int kWaitMma = 21, kWaitEpi = 22, kWaitProd = 23;   // status codes of failed waits
+
+__global__ void __launch_bounds__(kThreads, 1) gemm_w4a8_tc_kernel(const TcParams p) {
+    extern __shared__ __align__(1024) unsigned char smem[];
+    __shared__ uint64_t bars[3 * kNB];          // full[kNB], accfull[kNB], empty[kNB]
+    __shared__ uint32_t tmem_base_s;
+    __shared__ int dead_s;                      // a wait gave up somewhere in the CTA
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t smem_u = smem_u32(smem);
+    const uint32_t full0 = smem_u32(&bars[0]), acc0 = smem_u32(&bars[kNB]),
+                   empty0 = smem_u32(&bars[2 * kNB]);
+
+    if (threadIdx.x == 0) {
+        for (int b = 0; b < kNB; ++b) {
+            mbar_init(full0 + b * 8, kProdWarps * 32);   // every producer thread arrives once
+            mbar_init(acc0 + b * 8, 1);                  // tcgen05.commit
+            mbar_init(empty0 + b * 8, kEpiWarps);        // one arrive per epilogue warp
+        }
+        dead_s = 0;
+        mbar_init_fence();
+    }
+    if (warp == 0) {                                     // one warp allocates all 512 columns
+        tmem_alloc(smem_u32(&tmem_base_s), 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_s;
+
+    // epilogue warps arm every accumulator slot with the fp32 bias bit pattern
+    if (warp < kEpiWarps) {
+        const uint32_t lane_base = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+        const int chalf = (warp >> 2) * 64;
+#pragma unroll
+        for (int b = 0; b < kNB; ++b)
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+                tmem_st16_const(lane_base + b * kTN + chalf + q * 16, (uint32_t)kMagicBits);
+        tmem_wait_st();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    pdl_trigger();
+    pdl_wait();      // everything below reads the images an earlier kernel wrote
+
+    const int Kt = p.Kt, Ktg = Kt >> p.ksh;
+    const int row_blocks = p.M / kTM, tok_blocks = p.Tpad / kTN;
+    const int ntiles = row_blocks * tok_blocks;
+    int it = 0;      // k-tile counter across the tiles of this CTA: slot = it % kNB
+
+    if (warp < kEpiWarps) {
+        // ================================ epilogue ======================================
+        const int q4 = warp & 3, chalf = (warp >> 2) * 64;
+        const int rloc = q4 * 32 + lane;                  // row inside the tile = TMEM lane
+        const uint32_t lane_base = tmem_base + ((uint32_t)(q4 * 32) << 16);
+        const f32x2 neg_magic2 = pack2(-kMagicF, -kMagicF);
+        for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+            const int rb = tile % row_blocks, tb = tile / row_blocks;
+            const int row = rb * kTM + rloc;
+            const uint16_t *sc = p.scales + ((size_t)(row >> 4) * Ktg) * 16 + (row & 15);
+            f32x2 acc[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) acc[i] = 0ull;
+            uint32_t scw = __ldg(sc);
+            for (int kt = 0; kt < Kt; ++kt, ++it) {
+                const int b = it % kNB;
+                const uint32_t ph = (uint32_t)(it / kNB) & 1u;
+                int zp;
+                float ws;
+                unpack_scale(scw, zp, ws);
+                if (kt + 1 < Kt) scw = __ldg(sc + (size_t)((kt + 1) >> p.ksh) * 16);
+                const f32x2 ws2 = pack2(ws, ws);
+                const float nzf = (float)(-(zp + 8));
+                const f32x2 nz2 = pack2(nzf, nzf);
+                bool ok = !*(volatile int *)&dead_s && mbar_wait_bounded(acc0 + b * 8, ph, p.status, kWaitEpi);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) {
+                    dead_s = 1;
+                    break;
+                }
+                tc_fence_after();
+                const float4 *sv = reinterpret_cast<const float4 *>(
+                                       smem + (size_t)b * kSlotBytes + kABytes + kBBytes) +
+                                   (chalf >> 1);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    uint32_t d[16];
+                    const uint32_t ta = lane_base + b * kTN + chalf + q * 16;
+                    tmem_ld16(ta, d);
+                    tmem_wait_ld();
+                    tmem_st16_const(ta, (uint32_t)kMagicBits);     // re-arm for its next MMA
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const float4 s4 = sv[q * 8 + j];          // {as0, as1, asum0, asum1}
+                        const f32x2 f = fma2(nz2, pack2(s4.z, s4.w),
+                                             add2(pack2i((int)d[2 * j], (int)d[2 * j + 1]), neg_magic2));
+                        acc[q * 8 + j] = fma2(f, mul2(ws2, pack2(s4.x, s4.y)), acc[q * 8 + j]);
+                    }
+                }
+                tmem_wait_st();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(empty0 + b * 8);
+            }
+            if (*(volatile int *)&dead_s) break;
+            // store: thread = row, 64 tokens; rows are contiguous in y, so a warp writes 128 B
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                float v0, v1;
+                unpack2(acc[i], v0, v1);
+                const int tok = tb * kTN + chalf + 2 * i;
+                if (p.out_bf16) {
+                    __nv_bfloat16 *y = static_cast<__nv_bfloat16 *>(p.y);
+                    if (tok < p.T) y[(size_t)tok * p.M + row] = __float2bfloat16_rn(v0);
+                    if (tok + 1 < p.T) y[(size_t)(tok + 1) * p.M + row] = __float2bfloat16_rn(v1);
+                } else {
+                    float *y = static_cast<float *>(p.y);
+                    if (tok < p.T) y[(size_t)tok * p.M + row] = v0;
+                    if (tok + 1 < p.T) y[(size_t)(tok + 1) * p.M + row] = v1;
+                }
+            }
+        }
+    } else if (warp < kEpiWarps + kProdWarps) {
+        // ================================ producers =====================================
+        const int pr = threadIdx.x - kEpiWarps * 32;       // row inside the tile
+        // destination of this row's two K-chunks in the core-matrix layout
+        const uint32_t a_off = (uint32_t)((pr >> 3) * kSbo + (pr & 7) * 16);
+        for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+            const int rb = tile % row_blocks, tb = tile / row_blocks;
+            const int row = rb * kTM + pr;
+            const uint8_t *src = p.codes + ((size_t)(row >> 4) * Kt) * 256 + (row & 15) * 16;
+            uint4 w = ldg_stream_v4(src);
+            for (int kt = 0; kt < Kt; ++kt, ++it) {
+                const int b = it % kNB;
+                const uint32_t ph = ((uint32_t)(it / kNB) & 1u) ^ 1u;   // first pass is free
+                const uint4 cur = w;
+                if (kt + 1 < Kt) w = ldg_stream_v4(src + (size_t)(kt + 1) * 256);
+                bool ok = !*(volatile int *)&dead_s && mbar_wait_bounded(empty0 + b * 8, ph, p.status, kWaitProd);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) {
+                    dead_s = 1;
+                    break;
+                }
+                unsigned char *slot = smem + (size_t)b * kSlotBytes;
+                const uint4 lo = make_uint4(nib_plus8(cur.x), nib_plus8(cur.y), nib_plus8(cur.z),
+                                            nib_plus8(cur.w));
+                const uint4 hi = make_uint4(nib_plus8(cur.x >> 4), nib_plus8(cur.y >> 4),
+                                            nib_plus8(cur.z >> 4), nib_plus8(cur.w >> 4));
+                *reinterpret_cast<uint4 *>(slot + a_off) = lo;             // even-k chunk
+                *reinterpret_cast<uint4 *>(slot + a_off + kLbo) = hi;      // odd-k chunk
+                fence_proxy_async_smem();     // generic-proxy stores -> visible to the MMA
+                const uint32_t fb = full0 + b * 8;
+                if (pr == 0) {
+                    // this thread's arrival also announces the bytes of the two bulk copies
+                    mbar_expect_tx(fb, kBBytes + kSBytes);
+                    const uint32_t dst = smem_u + b * kSlotBytes + kABytes;
+                    bulk_g2s_plain(dst, p.bimg + ((size_t)kt * (p.Tpad / 8) + tb * (kTN / 8)) * 256,
+                                   kBBytes, fb);
+                    bulk_g2s_plain(dst + kBBytes,
+                                   p.simg + (((size_t)kt * p.Tpad + (size_t)tb * kTN) >> 1), kSBytes,
+                                   fb);
+                } else {
+                    mbar_arrive(fb);
+                }
+            }
+            if (*(volatile int *)&dead_s) break;
+        }
+    } else {
+        // ================================ MMA issuer ====================================
+        for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+            for (int kt = 0; kt < Kt; ++kt, ++it) {
+                const int b = it % kNB;
+                const uint32_t ph = (uint32_t)(it / kNB) & 1u;
+                bool ok = !*(volatile int *)&dead_s && mbar_wait_bounded(full0 + b * 8, ph, p.status, kWaitMma);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) {
+                    dead_s = 1;
+                    break;
+                }
+                tc_fence_after();
+                if (lane == 0) {
+                    const uint32_t a_addr = smem_u + b * kSlotBytes;
+                    tc_mma_i8(tmem_base + b * kTN, smem_desc(a_addr), smem_desc(a_addr + kABytes),
+                              kIdesc, 1u);
+                    tc_commit(acc0 + b * 8);
+                }
+                __syncwarp();
+            }
+            if (*(volatile int *)&dead_s) break;
+        }
+    }
+
+    // ---- teardown: every role comes here, also after a failed wait ------------------------
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (warp == 0) tmem_dealloc(tmem_base, 512);
+}
+
+struct TcScratch {
+    uint8_t *bimg = nullptr;
+    float4 *simg = nullptr;
+    size_t bimg_bytes = 0, simg_bytes = 0;
+} g_tc;
+
+int g_tc_sms = 0;
+
+}  // namespace
+
+int launch_gemm_tc(const GemmTcArgs &a) {
+    // covered: per-block activation scales (the reference's x_gemm_w4a8 arithmetic), rows a
+    // multiple of 128, K64 tier only with an even number of k-tiles
+    if (!a.as || a.as_tok) return -1;
+    if (a.M % kTM || a.K % 32 || a.T < 128) return -1;
+    const int Kt = a.K / 32;
+    if (a.ksh && (Kt & 1)) return -1;
+    if (!g_tc_sms) {
+        int dev = 0;
+        TQ_CHECK(cudaGetDevice(&dev));
+        TQ_CHECK(cudaDeviceGetAttribute(&g_tc_sms, cudaDevAttrMultiProcessorCount, dev));
+        if (g_tc_sms <= 0) g_tc_sms = 148;
+        TQ_CHECK(cudaFuncSetAttribute(gemm_w4a8_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      kSmemBytes));
+    }
+    const int Tpad = (a.T + kTN - 1) / kTN * kTN;
+    const size_t bbytes = (size_t)Kt * Tpad * 32, sbytes = (size_t)Kt * Tpad * 8;
+    if (bbytes > g_tc.bimg_bytes) {
+        if (g_tc.bimg) tq_dev_free(g_tc.bimg);
+        g_tc.bimg = static_cast<uint8_t *>(tq_dev_alloc(bbytes, "gemm.tc.activation.image"));
+        g_tc.bimg_bytes = bbytes;
+    }
+    if (sbytes > g_tc.simg_bytes) {
+        if (g_tc.simg) tq_dev_free(g_tc.simg);
+        g_tc.simg = static_cast<float4 *>(tq_dev_alloc(sbytes, "gemm.tc.scale.image"));
+        g_tc.simg_bytes = sbytes;
+    }
+    const size_t nrow = (size_t)Kt * Tpad;
+    const int pgrid = (int)std::min<size_t>((nrow + 255) / 256, (size_t)g_tc_sms * 8);
+    gemm_tc_prepass_kernel<<<pgrid, 256, 0, stream()>>>(a.aq, a.as, a.asum, a.T, Tpad, Kt, g_tc.bimg,
+                                                       g_tc.simg);
+    TQ_LAUNCH_CHECK("gemm_tc_prepass_kernel");
+    TcParams p{};
+    p.codes = a.codes; p.scales = a.scales; p.bimg = g_tc.bimg; p.simg = g_tc.simg; p.y = a.y;
+    p.status = device_status_word();
+    p.M = a.M; p.Kt = Kt; p.ksh = a.ksh; p.T = a.T; p.Tpad = Tpad; p.out_bf16 = a.out_bf16;
+    const int ntiles = (a.M / kTM) * (Tpad / kTN);
+    const int grid = std::min(g_tc_sms, ntiles);
+    launch_pdl(gemm_w4a8_tc_kernel, dim3(grid), dim3(kThreads), (size_t)kSmemBytes, p);
+    TQ_LAUNCH_CHECK("gemm_w4a8_tc_kernel");
+    return 0;
+}
 
 }  // namespace tq

@@ -44,14 +44,23 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
     return ok;
 }
 
-// Bounded wait: every lane polls; gives up after kSpinLimit polls (each poll already
-// blocks for a hardware-defined interval), records `code` in *status and returns false.
+// Bounded wait: polls until the phase completes or two seconds of wall clock have passed
+// (%globaltimer), then records `code` in *status (first failure wins) and returns false.
 // The result is made warp-uniform by the caller.
-constexpr uint32_t kSpinLimit = 1u << 22;
+__device__ __forceinline__ uint64_t global_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+constexpr uint64_t kWaitLimitNs = 2000000000ull;
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, int *status,
                                                   int code) {
-    for (uint32_t i = 0; i < kSpinLimit; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = global_timer_ns();
+    for (;;) {
         if (mbar_try_wait(bar, parity)) return true;
+        if (global_timer_ns() - t0 > kWaitLimitNs) break;
+    }
     atomicCAS(status, 0, code);
     return false;
 }
