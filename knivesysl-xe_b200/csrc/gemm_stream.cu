@@ -300,8 +300,8 @@ gemm_w4a8_stream_kernel(const GemmArgs a, float *__restrict__ part, int *__restr
                                                    add2(pack2i(d[0], d[1]), neg_magic2));
                             const f32x2 f23 = fma2(pack2(nz1, nz1), smf,
                                                    add2(pack2i(d[2], d[3]), neg_magic2));
-                            acc01[g][t] = fma2(f01, mul2(pack2(ws0, ws0), as2), acc01[g][t]);
-                            acc23[g][t] = fma2(f23, mul2(pack2(ws1, ws1), as2), acc23[g][t]);
+                            fma2_acc(acc01[g][t], f01, mul2(pack2(ws0, ws0), as2));
+                            fma2_acc(acc23[g][t], f23, mul2(pack2(ws1, ws1), as2));
                         }
                     }
                 }

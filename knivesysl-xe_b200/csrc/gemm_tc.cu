@@ -9,7 +9,8 @@
 // Mapping. Weights are the M side of the MMA (128 output rows = 128 TMEM lanes), tokens the
 // N side (128 per CTA tile), K = 32 per instruction = one k-tile, so one MMA produces exactly
 // the per-k-tile int32 dots the reference promotes. A CTA (13 warps, one per SM, persistent
-// over tiles) runs three roles connected by mbarriers, 4 slots deep:
+// over tiles) runs three roles connected by mbarriers (10 operand slots in shared memory, 4
+// accumulator buffers in TMEM):
 //  * producers (4 warps, thread = weight row): load the row's 16 packed bytes of a k-tile,
 //    expand the nibbles to int8 bytes q+8 with two logic ops per word and store them as the
 //    two 16-byte K-chunks of the row in the canonical no-swizzle K-major core-matrix layout
@@ -43,7 +44,9 @@ namespace {
 
 constexpr int kTM = 128;                 // weight rows per tile (TMEM lanes)
 constexpr int kTN = 128;                 // tokens per tile (accumulator columns)
-constexpr int kNB = 4;                   // pipeline slots = accumulator buffers
+constexpr int kNB = 4;                   // accumulator buffers in TMEM (4 x 128 columns)
+constexpr int kNS = 10;                  // operand slots in shared memory
+constexpr int kPB = 8;                   // k-tiles a producer thread loads per batch
 constexpr int kABytes = kTM * 32;        // expanded int8 weights of one k-tile
 constexpr int kBBytes = kTN * 32;        // int8 activations of one k-tile
 constexpr int kSBytes = kTN / 2 * 16;    // {as0, as1, asum0, asum1} per token pair
@@ -88,6 +91,8 @@ __device__ __forceinline__ void tc_mma_i8(uint32_t d_tmem, uint64_t a_desc, uint
         : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
         : "memory");
 }
+// Starts the load of 16 columns of this thread's TMEM lane (asynchronous: the registers are
+// valid only after tmem_wait_ld16 on the same array).
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,"
@@ -98,6 +103,16 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
         : "r"(taddr)
         : "memory");
 }
+// Waits for every TMEM load this thread has started. The loaded registers pass through the
+// statement as read-write operands, so no use of them can be scheduled before the wait.
+__device__ __forceinline__ void tmem_wait_ld16(uint32_t (&v)[16]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]),
+                   "+r"(v[6]), "+r"(v[7]), "+r"(v[8]), "+r"(v[9]), "+r"(v[10]), "+r"(v[11]),
+                   "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15])
+                 :
+                 : "memory");
+}
 __device__ __forceinline__ void tmem_st16_const(uint32_t taddr, uint32_t c) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,"
@@ -105,9 +120,6 @@ __device__ __forceinline__ void tmem_st16_const(uint32_t taddr, uint32_t c) {
         "r"(c), "r"(c), "r"(c), "r"(c), "r"(c), "r"(c), "r"(c), "r"(c), "r"(c), "r"(c), "r"(c),
         "r"(c), "r"(c), "r"(c), "r"(c), "r"(c)
         : "memory");
-}
-__device__ __forceinline__ void tmem_wait_ld() {
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 __device__ __forceinline__ void tmem_wait_st() {
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
@@ -140,8 +152,9 @@ constexpr uint32_t kIdesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kTN
 struct TcParams {
     const uint8_t *codes;
     const uint16_t *scales;
-    const uint8_t *bimg;     // activation image [Kt][Tpad/8][2][8][16]
-    const float4 *simg;      // [Kt][Tpad/2] {as0, as1, (float)asum0, (float)asum1}
+    const uint8_t *img;      // per (k-tile, 128-token block): kBBytes of codes as
+                             // [16 token groups][2 K-chunks][8][16], then kSBytes of
+                             // {as0, as1, (float)asum0, (float)asum1} per token pair
     void *y;
     int *status;
     int M, Kt, ksh, T, Tpad, out_bf16;
@@ -152,7 +165,7 @@ struct TcParams {
 __global__ void __launch_bounds__(256)
 gemm_tc_prepass_kernel(const int8_t *__restrict__ aq, const float *__restrict__ as,
                        const int32_t *__restrict__ asum, int T, int Tpad, int Kt,
-                       uint8_t *__restrict__ bimg, float4 *__restrict__ simg) {
+                       uint8_t *__restrict__ img) {
     pdl_trigger();
     const size_t nrow = (size_t)Kt * Tpad;
     for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < nrow; i += (size_t)gridDim.x * 256) {
@@ -167,7 +180,9 @@ gemm_tc_prepass_kernel(const int8_t *__restrict__ aq, const float *__restrict__ 
             hi = make_uint4(__byte_perm(a.x, a.y, 0x7531), __byte_perm(a.z, a.w, 0x7531),
                             __byte_perm(b.x, b.y, 0x7531), __byte_perm(b.z, b.w, 0x7531));
         }
-        uint8_t *dst = bimg + ((size_t)kt * (Tpad / 8) + (tok >> 3)) * 256 + (tok & 7) * 16;
+        uint8_t *blk = img + ((size_t)kt * (Tpad / kTN) + tok / kTN) * (kBBytes + kSBytes);
+        const int tl = tok % kTN;
+        uint8_t *dst = blk + (tl >> 3) * 256 + (tl & 7) * 16;
         *reinterpret_cast<uint4 *>(dst) = lo;
         *reinterpret_cast<uint4 *>(dst + 128) = hi;
         if ((tok & 1) == 0) {
@@ -180,7 +195,7 @@ gemm_tc_prepass_kernel(const int8_t *__restrict__ aq, const float *__restrict__ 
                 v.y = as[(size_t)kt * T + tok + 1];
                 v.w = (float)asum[(size_t)kt * T + tok + 1];
             }
-            simg[((size_t)kt * Tpad + tok) >> 1] = v;
+            reinterpret_cast<float4 *>(blk + kBBytes)[tl >> 1] = v;
         }
     }
 }
@@ -189,20 +204,23 @@ constexpr int kWaitMma = 21, kWaitEpi = 22, kWaitProd = 23;   // status codes of
 
 __global__ void __launch_bounds__(kThreads, 1) gemm_w4a8_tc_kernel(const TcParams p) {
     extern __shared__ __align__(1024) unsigned char smem[];
-    __shared__ uint64_t bars[3 * kNB];          // full[kNB], accfull[kNB], empty[kNB]
+    __shared__ uint64_t bars[2 * kNS + 2 * kNB];   // full[kNS], empty[kNS], accfull[kNB], accempty[kNB]
     __shared__ uint32_t tmem_base_s;
     __shared__ int dead_s;                      // a wait gave up somewhere in the CTA
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const uint32_t smem_u = smem_u32(smem);
-    const uint32_t full0 = smem_u32(&bars[0]), acc0 = smem_u32(&bars[kNB]),
-                   empty0 = smem_u32(&bars[2 * kNB]);
+    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[kNS]),
+                   acc0 = smem_u32(&bars[2 * kNS]), accempty0 = smem_u32(&bars[2 * kNS + kNB]);
 
     if (threadIdx.x == 0) {
+        for (int s = 0; s < kNS; ++s) {
+            mbar_init(full0 + s * 8, kProdWarps * 32);   // every producer thread arrives once
+            mbar_init(empty0 + s * 8, kEpiWarps);        // one arrive per epilogue warp
+        }
         for (int b = 0; b < kNB; ++b) {
-            mbar_init(full0 + b * 8, kProdWarps * 32);   // every producer thread arrives once
             mbar_init(acc0 + b * 8, 1);                  // tcgen05.commit
-            mbar_init(empty0 + b * 8, kEpiWarps);        // one arrive per epilogue warp
+            mbar_init(accempty0 + b * 8, kEpiWarps);     // one arrive per epilogue warp
         }
         dead_s = 0;
         mbar_init_fence();
@@ -236,7 +254,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_w4a8_tc_kernel(const TcParam
     const int Kt = p.Kt, Ktg = Kt >> p.ksh;
     const int row_blocks = p.M / kTM, tok_blocks = p.Tpad / kTN;
     const int ntiles = row_blocks * tok_blocks;
-    int it = 0;      // k-tile counter across the tiles of this CTA: slot = it % kNB
+    int it = 0;      // k-tile counter across the tiles of this CTA: operand slot it % kNS,
+                     // accumulator buffer it % kNB
 
     if (warp < kEpiWarps) {
         // ================================ epilogue ======================================
@@ -253,7 +272,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_w4a8_tc_kernel(const TcParam
             for (int i = 0; i < 32; ++i) acc[i] = 0ull;
             uint32_t scw = __ldg(sc);
             for (int kt = 0; kt < Kt; ++kt, ++it) {
-                const int b = it % kNB;
+                const int b = it % kNB, sl = it % kNS;
                 const uint32_t ph = (uint32_t)(it / kNB) & 1u;
                 int zp;
                 float ws;
@@ -269,28 +288,42 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_w4a8_tc_kernel(const TcParam
                     break;
                 }
                 tc_fence_after();
-                const float4 *sv = reinterpret_cast<const float4 *>(
-                                       smem + (size_t)b * kSlotBytes + kABytes + kBBytes) +
-                                   (chalf >> 1);
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    uint32_t d[16];
-                    const uint32_t ta = lane_base + b * kTN + chalf + q * 16;
-                    tmem_ld16(ta, d);
-                    tmem_wait_ld();
-                    tmem_st16_const(ta, (uint32_t)kMagicBits);     // re-arm for its next MMA
+                const ulonglong2 *sv = reinterpret_cast<const ulonglong2 *>(
+                                           smem + (size_t)sl * kSlotBytes + kABytes + kBBytes) +
+                                       (chalf >> 1);
+                // The four 16-column loads are software-pipelined: the load of chunk q+1 is in
+                // flight while chunk q is re-armed and promoted.
+                uint32_t da[16], db[16];
+                const uint32_t tcol = lane_base + b * kTN + chalf;
+                auto promote = [&](const int q, uint32_t (&d)[16]) {
+                    tmem_st16_const(tcol + q * 16, (uint32_t)kMagicBits);   // re-arm for the next MMA
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
-                        const float4 s4 = sv[q * 8 + j];          // {as0, as1, asum0, asum1}
-                        const f32x2 f = fma2(nz2, pack2(s4.z, s4.w),
+                        const ulonglong2 s4 = sv[q * 8 + j];      // {as0, as1}, {asum0, asum1}
+                        const f32x2 f = fma2(nz2, s4.y,
                                              add2(pack2i((int)d[2 * j], (int)d[2 * j + 1]), neg_magic2));
-                        acc[q * 8 + j] = fma2(f, mul2(ws2, pack2(s4.x, s4.y)), acc[q * 8 + j]);
+                        fma2_acc(acc[q * 8 + j], f, mul2(ws2, s4.x));
                     }
-                }
+                };
+                tmem_ld16(tcol, da);
+                tmem_wait_ld16(da);
+                tmem_ld16(tcol + 16, db);
+                promote(0, da);
+                tmem_wait_ld16(db);
+                tmem_ld16(tcol + 32, da);
+                promote(1, db);
+                tmem_wait_ld16(da);
+                tmem_ld16(tcol + 48, db);
+                promote(2, da);
+                tmem_wait_ld16(db);
+                promote(3, db);
                 tmem_wait_st();
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(empty0 + b * 8);
+                if (lane == 0) {
+                    mbar_arrive(accempty0 + b * 8);      // the MMA may overwrite the buffer
+                    mbar_arrive(empty0 + sl * 8);        // the producers may refill the slot
+                }
             }
             if (*(volatile int *)&dead_s) break;
             // store: thread = row, 64 tokens; rows are contiguous in y, so a warp writes 128 B
@@ -315,43 +348,71 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_w4a8_tc_kernel(const TcParam
         const int pr = threadIdx.x - kEpiWarps * 32;       // row inside the tile
         // destination of this row's two K-chunks in the core-matrix layout
         const uint32_t a_off = (uint32_t)((pr >> 3) * kSbo + (pr & 7) * 16);
+        // Weight words are fetched kPB k-tiles at a time into one of two register batches:
+        // the next batch (of this tile, or the first of the next tile) is in flight while the
+        // current one is expanded.
+        auto tile_src = [&](int tile) {
+            const int row = (tile % row_blocks) * kTM + pr;
+            return p.codes + ((size_t)(row >> 4) * Kt) * 256 + (row & 15) * 16;
+        };
+        auto load_batch = [&](uint4 (&w)[kPB], const uint8_t *src, int kt0) {
+#pragma unroll
+            for (int j = 0; j < kPB; ++j)
+                if (kt0 + j < Kt) w[j] = ldg_stream_v4(src + (size_t)(kt0 + j) * 256);
+        };
+        uint4 w0[kPB], w1[kPB];
+        int par = 0;
+        const int nbatch = (Kt + kPB - 1) / kPB;
+        if (blockIdx.x < ntiles) load_batch(w0, tile_src(blockIdx.x), 0);
         for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
-            const int rb = tile % row_blocks, tb = tile / row_blocks;
-            const int row = rb * kTM + pr;
-            const uint8_t *src = p.codes + ((size_t)(row >> 4) * Kt) * 256 + (row & 15) * 16;
-            uint4 w = ldg_stream_v4(src);
-            for (int kt = 0; kt < Kt; ++kt, ++it) {
-                const int b = it % kNB;
-                const uint32_t ph = ((uint32_t)(it / kNB) & 1u) ^ 1u;   // first pass is free
-                const uint4 cur = w;
-                if (kt + 1 < Kt) w = ldg_stream_v4(src + (size_t)(kt + 1) * 256);
-                bool ok = !*(volatile int *)&dead_s && mbar_wait_bounded(empty0 + b * 8, ph, p.status, kWaitProd);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) {
-                    dead_s = 1;
-                    break;
-                }
-                unsigned char *slot = smem + (size_t)b * kSlotBytes;
-                const uint4 lo = make_uint4(nib_plus8(cur.x), nib_plus8(cur.y), nib_plus8(cur.z),
-                                            nib_plus8(cur.w));
-                const uint4 hi = make_uint4(nib_plus8(cur.x >> 4), nib_plus8(cur.y >> 4),
-                                            nib_plus8(cur.z >> 4), nib_plus8(cur.w >> 4));
-                *reinterpret_cast<uint4 *>(slot + a_off) = lo;             // even-k chunk
-                *reinterpret_cast<uint4 *>(slot + a_off + kLbo) = hi;      // odd-k chunk
-                fence_proxy_async_smem();     // generic-proxy stores -> visible to the MMA
-                const uint32_t fb = full0 + b * 8;
-                if (pr == 0) {
-                    // this thread's arrival also announces the bytes of the two bulk copies
-                    mbar_expect_tx(fb, kBBytes + kSBytes);
-                    const uint32_t dst = smem_u + b * kSlotBytes + kABytes;
-                    bulk_g2s_plain(dst, p.bimg + ((size_t)kt * (p.Tpad / 8) + tb * (kTN / 8)) * 256,
-                                   kBBytes, fb);
-                    bulk_g2s_plain(dst + kBBytes,
-                                   p.simg + (((size_t)kt * p.Tpad + (size_t)tb * kTN) >> 1), kSBytes,
-                                   fb);
-                } else {
-                    mbar_arrive(fb);
-                }
+            const int tb = tile / row_blocks;
+            const uint8_t *src = tile_src(tile);
+            for (int kb = 0; kb < nbatch; ++kb, par ^= 1) {
+                auto batch = [&](uint4 (&cur)[kPB], uint4 (&nxt)[kPB]) {
+                    if (kb + 1 < nbatch) load_batch(nxt, src, (kb + 1) * kPB);
+                    else if (tile + (int)gridDim.x < ntiles)
+                        load_batch(nxt, tile_src(tile + gridDim.x), 0);
+#pragma unroll
+                    for (int j = 0; j < kPB; ++j) {
+                        const int kt = kb * kPB + j;
+                        if (kt >= Kt || *(volatile int *)&dead_s) break;
+                        const int sl = it % kNS;
+                        const uint32_t ph = ((uint32_t)(it / kNS) & 1u) ^ 1u;   // first pass is free
+                        bool ok = mbar_wait_bounded(empty0 + sl * 8, ph, p.status, kWaitProd);
+                        ok = __all_sync(0xffffffffu, ok);
+                        if (!ok) {
+                            dead_s = 1;
+                            break;
+                        }
+                        unsigned char *slot = smem + (size_t)sl * kSlotBytes;
+                        const uint4 c4 = cur[j];
+                        const uint4 lo = make_uint4(nib_plus8(c4.x), nib_plus8(c4.y),
+                                                    nib_plus8(c4.z), nib_plus8(c4.w));
+                        const uint4 hi = make_uint4(nib_plus8(c4.x >> 4), nib_plus8(c4.y >> 4),
+                                                    nib_plus8(c4.z >> 4), nib_plus8(c4.w >> 4));
+                        *reinterpret_cast<uint4 *>(slot + a_off) = lo;             // even-k chunk
+                        *reinterpret_cast<uint4 *>(slot + a_off + kLbo) = hi;      // odd-k chunk
+                        fence_proxy_async_smem();   // generic-proxy stores -> visible to the MMA
+                        const uint32_t fb = full0 + sl * 8;
+                        if (pr == (sl & 3) * 32) {
+                            // One bulk copy brings the activation image of this (k-tile, token
+                            // block); this thread's arrival also announces its bytes. The
+                            // issuing thread rotates over the producer warps: one thread
+                            // sustains only about two bulk copies in flight.
+                            mbar_expect_tx(fb, kBBytes + kSBytes);
+                            bulk_g2s_plain(
+                                smem_u + sl * kSlotBytes + kABytes,
+                                p.img + ((size_t)kt * (p.Tpad / kTN) + tb) * (kBBytes + kSBytes),
+                                kBBytes + kSBytes, fb);
+                        } else {
+                            mbar_arrive(fb);
+                        }
+                        ++it;
+                    }
+                };
+                if (par) batch(w1, w0);
+                else batch(w0, w1);
+                if (*(volatile int *)&dead_s) break;
             }
             if (*(volatile int *)&dead_s) break;
         }
@@ -359,9 +420,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_w4a8_tc_kernel(const TcParam
         // ================================ MMA issuer ====================================
         for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
             for (int kt = 0; kt < Kt; ++kt, ++it) {
-                const int b = it % kNB;
-                const uint32_t ph = (uint32_t)(it / kNB) & 1u;
-                bool ok = !*(volatile int *)&dead_s && mbar_wait_bounded(full0 + b * 8, ph, p.status, kWaitMma);
+                const int b = it % kNB, sl = it % kNS;
+                bool ok = !*(volatile int *)&dead_s &&
+                          mbar_wait_bounded(full0 + sl * 8, (uint32_t)(it / kNS) & 1u, p.status, kWaitMma);
+                // ... and the accumulator buffer has been read out and re-armed
+                ok = ok && mbar_wait_bounded(accempty0 + b * 8, ((uint32_t)(it / kNB) & 1u) ^ 1u,
+                                             p.status, kWaitMma);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) {
                     dead_s = 1;
@@ -369,7 +433,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_w4a8_tc_kernel(const TcParam
                 }
                 tc_fence_after();
                 if (lane == 0) {
-                    const uint32_t a_addr = smem_u + b * kSlotBytes;
+                    const uint32_t a_addr = smem_u + sl * kSlotBytes;
                     tc_mma_i8(tmem_base + b * kTN, smem_desc(a_addr), smem_desc(a_addr + kABytes),
                               kIdesc, 1u);
                     tc_commit(acc0 + b * 8);
@@ -388,9 +452,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_w4a8_tc_kernel(const TcParam
 }
 
 struct TcScratch {
-    uint8_t *bimg = nullptr;
-    float4 *simg = nullptr;
-    size_t bimg_bytes = 0, simg_bytes = 0;
+    uint8_t *img = nullptr;
+    size_t img_bytes = 0;
 } g_tc;
 
 int g_tc_sms = 0;
@@ -413,24 +476,18 @@ int launch_gemm_tc(const GemmTcArgs &a) {
                                       kSmemBytes));
     }
     const int Tpad = (a.T + kTN - 1) / kTN * kTN;
-    const size_t bbytes = (size_t)Kt * Tpad * 32, sbytes = (size_t)Kt * Tpad * 8;
-    if (bbytes > g_tc.bimg_bytes) {
-        if (g_tc.bimg) tq_dev_free(g_tc.bimg);
-        g_tc.bimg = static_cast<uint8_t *>(tq_dev_alloc(bbytes, "gemm.tc.activation.image"));
-        g_tc.bimg_bytes = bbytes;
-    }
-    if (sbytes > g_tc.simg_bytes) {
-        if (g_tc.simg) tq_dev_free(g_tc.simg);
-        g_tc.simg = static_cast<float4 *>(tq_dev_alloc(sbytes, "gemm.tc.scale.image"));
-        g_tc.simg_bytes = sbytes;
+    const size_t ibytes = (size_t)Kt * (Tpad / kTN) * (kBBytes + kSBytes);
+    if (ibytes > g_tc.img_bytes) {
+        if (g_tc.img) tq_dev_free(g_tc.img);
+        g_tc.img = static_cast<uint8_t *>(tq_dev_alloc(ibytes, "gemm.tc.activation.image"));
+        g_tc.img_bytes = ibytes;
     }
     const size_t nrow = (size_t)Kt * Tpad;
     const int pgrid = (int)std::min<size_t>((nrow + 255) / 256, (size_t)g_tc_sms * 8);
-    gemm_tc_prepass_kernel<<<pgrid, 256, 0, stream()>>>(a.aq, a.as, a.asum, a.T, Tpad, Kt, g_tc.bimg,
-                                                       g_tc.simg);
+    gemm_tc_prepass_kernel<<<pgrid, 256, 0, stream()>>>(a.aq, a.as, a.asum, a.T, Tpad, Kt, g_tc.img);
     TQ_LAUNCH_CHECK("gemm_tc_prepass_kernel");
     TcParams p{};
-    p.codes = a.codes; p.scales = a.scales; p.bimg = g_tc.bimg; p.simg = g_tc.simg; p.y = a.y;
+    p.codes = a.codes; p.scales = a.scales; p.img = g_tc.img; p.y = a.y;
     p.status = device_status_word();
     p.M = a.M; p.Kt = Kt; p.ksh = a.ksh; p.T = a.T; p.Tpad = Tpad; p.out_bf16 = a.out_bf16;
     const int ntiles = (a.M / kTM) * (Tpad / kTN);

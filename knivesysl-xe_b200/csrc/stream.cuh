@@ -56,10 +56,17 @@ constexpr uint64_t kWaitLimitNs = 2000000000ull;
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, int *status,
                                                   int code) {
     if (mbar_try_wait(bar, parity)) return true;
-    const uint64_t t0 = global_timer_ns();
-    for (;;) {
+    // Slow path: back off between polls so that waiting warps leave the issue slots to the
+    // warps doing the work, and look at the clock only every 1024 polls.
+    uint64_t t0 = 0;
+    for (uint32_t polls = 1;; ++polls) {
+        __nanosleep(200);
         if (mbar_try_wait(bar, parity)) return true;
-        if (global_timer_ns() - t0 > kWaitLimitNs) break;
+        if ((polls & 1023u) == 0) {
+            const uint64_t now = global_timer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > kWaitLimitNs) break;
+        }
     }
     atomicCAS(status, 0, code);
     return false;
@@ -173,6 +180,11 @@ __device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
     f32x2 d;
     asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
     return d;
+}
+
+// acc = a * b + acc, accumulating in place (no copy of the result into acc)
+__device__ __forceinline__ void fma2_acc(f32x2 &acc, f32x2 a, f32x2 b) {
+    asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc) : "l"(a), "l"(b));
 }
 
 // Integer n with |n| < 2^22 carried as the fp32 bit pattern of 12582912 + n: adding n to
