@@ -154,6 +154,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--rotate", type=int, default=4)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--exchange", default="fused", choices=["fused", "nccl"],
+                    help="N > 1: all-gather by peer stores from the GEMM epilogue (fused) or by NCCL")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank, local_rank, world = dist_env()
@@ -201,11 +203,39 @@ def main():
     nblk = K // 32 * T
     aq, as_, asum, as_tok = (pkg.DevBuf(nblk * 32), pkg.DevBuf(nblk * 4), pkg.DevBuf(nblk * 4),
                              pkg.DevBuf(T * 4))
-    y = [pkg.DevBuf(T * n_shard * 4) for _ in range(2)]
-    yarr = pkg.ptr_array(y)
-    # gathered outputs: [world][gate|up][T][n_shard]
-    ycat = pkg.DevBuf(2 * T * n_shard * 4)
-    gathered = pkg.DevBuf(world * 2 * T * n_shard * 4) if world > 1 else None
+    # this rank's outputs [gate|up][T][n_shard], contiguous so that they are one send buffer
+    block = 2 * T * n_shard                      # floats per rank
+    ycat = pkg.DevBuf(block * 4)
+    y_ptrs = [ycat.ptr, ycat.ptr + T * n_shard * 4]
+    yarr = (C.c_void_p * 2)(*y_ptrs)
+    # gathered outputs: [2 halves][world][gate|up][T][n_shard] (NCCL uses the first half)
+    gathered = pkg.DevBuf(2 * world * block * 4) if world > 1 else None
+    fused = world > 1 and args.exchange == "fused"
+    half_off = C.c_size_t(0)
+    if world > 1:
+        flags = pkg.DevBuf(world * 4)
+        lib.tq_dev_zero(flags.ptr, world * 4)
+        handles = []
+        for buf in (gathered, flags):
+            h = (C.c_char * 64)()
+            assert lib.tq_comm_ipc_export(buf.ptr, h) == 0
+            handles.append(bytes(h.raw))
+        allh = [None] * world
+        dist.all_gather_object(allh, handles)
+        bufs, flgs = (C.c_void_p * world)(), (C.c_void_p * world)()
+        for p in range(world):
+            if p == rank:
+                bufs[p], flgs[p] = gathered.ptr, flags.ptr
+            else:
+                bufs[p] = lib.tq_comm_ipc_open(C.create_string_buffer(allh[p][0], 64))
+                flgs[p] = lib.tq_comm_ipc_open(C.create_string_buffer(allh[p][1], 64))
+                if not bufs[p] or not flgs[p]:
+                    fused = False
+        ok_all = [None] * world
+        dist.all_gather_object(ok_all, bool(fused))
+        fused = all(ok_all)                      # every rank takes the same path
+        if fused:
+            assert lib.tq_comm_gather_setup(bufs, flgs, world, rank) == 0
 
     def stage():
         lib.qwn_x_quantize_act_chunk_pertoken(dx.ptr, K, T, aq.ptr, as_.ptr, asum.ptr, as_tok.ptr)
@@ -215,16 +245,34 @@ def main():
                                         None, 0)
         assert rc == 0, rc
 
-    def exchange():
-        if world > 1:
-            lib.tq_d2d_async(ycat.ptr, y[0].ptr, y[0].nbytes)
-            lib.tq_d2d_async(ycat.ptr + y[0].nbytes, y[1].ptr, y[1].nbytes)
-            assert lib.tq_comm_allgather(ycat.ptr, gathered.ptr, ycat.nbytes) == 0
+    def gemm_gathered(i):
+        rc = lib.qwn_x_gemm_w4a8_fanout_gathered(warr[i % args.rotate], 2, aq.ptr, as_.ptr, asum.ptr,
+                                                 T, C.byref(half_off))
+        assert rc == 0, rc
+        assert lib.tq_comm_gather_wait() == 0
 
     def step(i):
         stage()
-        gemm(i)
-        exchange()
+        if fused:
+            gemm_gathered(i)             # the epilogue stores this rank's slice on every rank
+        else:
+            gemm(i)
+            if world > 1:
+                assert lib.tq_comm_allgather(ycat.ptr, gathered.ptr, ycat.nbytes) == 0
+
+    if fused:
+        # the fused gather must deliver exactly what NCCL delivers
+        stage()
+        gemm(0)
+        assert lib.tq_comm_allgather(ycat.ptr, gathered.ptr, ycat.nbytes) == 0
+        lib.tq_sync()
+        ref = gathered.to_numpy(np.float32)[: world * block].copy()
+        dist.barrier()
+        gemm_gathered(0)
+        lib.tq_sync()
+        dist.barrier()
+        got = gathered.to_numpy(np.float32)[half_off.value: half_off.value + world * block]
+        assert got.tobytes() == ref.tobytes(), "fused all-gather differs from NCCL"
 
     def barrier():
         lib.tq_sync()
@@ -266,24 +314,23 @@ def main():
     lib.tq_sync()
     k_ms = lib.tq_event_elapsed_ms(ev[0], ev[1]) / k_iters
     shard_weight = 2 * wl.weight_bytes(n_shard, K, GROUP)
-    algo_bytes = shard_weight + T * K + nblk * 8 + 2 * T * n_shard * 4
+    algo_bytes = shard_weight + T * K + nblk * 8 + block * 4
     achieved = algo_bytes / (k_ms * 1e-3) / 1e9
     peak, peak_kind = measured_peaks()
 
     # ---- end to end through the C-ABI with host buffers ----------------------------------
     hx = lib.tq_host_alloc_pinned(x.nbytes)
     C.memmove(hx, x.ctypes.data, x.nbytes)
-    out_bytes = (gathered.nbytes if world > 1 else 2 * y[0].nbytes)
+    out_bytes = (world * block * 4 if world > 1 else ycat.nbytes)
     hy = lib.tq_host_alloc_pinned(out_bytes)
 
     def e2e_step(i):
         lib.tq_h2d_async(dx.ptr, hx, x.nbytes)
         step(i)
         if world > 1:
-            lib.tq_d2h_async(hy, gathered.ptr, gathered.nbytes)
+            lib.tq_d2h_async(hy, gathered.ptr + half_off.value * 4, out_bytes)
         else:
-            lib.tq_d2h_async(hy, y[0].ptr, y[0].nbytes)
-            lib.tq_d2h_async(hy + y[0].nbytes, y[1].ptr, y[1].nbytes)
+            lib.tq_d2h_async(hy, ycat.ptr, ycat.nbytes)
 
     e_iters = max(min(args.steps, 2000), 50)
     for i in range(args.warmup):
@@ -338,7 +385,9 @@ def main():
             "data": "synthetic",
             "config": {"workload": "cfg2: batched decode fused gate+up, K64 scale tier, T=8, K=5120, "
                                    "N=2x17408, int8 per-token activations",
-                       "parallelism": f"column shard tp{world}" + (" + NCCL all-gather" if world > 1 else ""),
+                       "parallelism": f"column shard tp{world}" + (
+                           "" if world == 1 else " + all-gather by peer stores from the GEMM epilogue"
+                           if fused else " + NCCL all-gather"),
                        "l2": f"inputs larger than L2: {args.rotate} rotating weight copies, "
                              f"{args.rotate * full_weight_bytes // world / 1e6:.0f} MB per GPU",
                        "step": "token_scale + quant_chunk + fused gate|up GEMM" +

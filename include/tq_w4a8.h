@@ -210,6 +210,25 @@ int qwn_static_max_k(void);
 int tq_comm_unique_id(void *id128);                       /* rank 0 fills 128 bytes */
 int tq_comm_init(const void *id128, int rank, int world);
 int tq_comm_allgather(const void *d_send, void *d_recv, size_t bytes_per_rank);
+/* Fused all-gather over peer memory (no counterpart in the reference). Every rank owns a
+ * gathered buffer [2][world][block] (two halves used by alternate calls, so a rank that
+ * runs one step ahead never overwrites what its peers still read; the half a call used is
+ * returned in *half_offset_floats) and a zeroed flag array int[world] in plain device memory;
+ * tq_comm_ipc_export / _open map them into the other ranks' processes (64-byte CUDA IPC
+ * handles, exchanged by the host program), tq_comm_gather_setup registers the world's
+ * pointers. qwn_x_gemm_w4a8_fanout_gathered then writes this rank's outputs
+ * [count][T][M_i] into block `rank` of EVERY rank's buffer from the GEMM epilogue and
+ * publishes a step flag; tq_comm_gather_wait enqueues a bounded wait for all ranks' blocks
+ * (status 10031 from tq_last_error() if a rank never publishes). All ranks must make the
+ * same sequence of gathered calls. Returns -21 when the shape is not a decode batch. */
+int tq_comm_ipc_export(void *d_ptr, void *handle64);
+void *tq_comm_ipc_open(const void *handle64);
+void tq_comm_ipc_close(void *p);
+int tq_comm_gather_setup(void *const *bufs, void *const *flags, int world, int rank);
+int tq_comm_gather_wait(void);
+int qwn_x_gemm_w4a8_fanout_gathered(const tq_qmma_weight_t *const *ws, int count,
+                                    const int8_t *d_aq, const float *d_as, const int32_t *d_asum,
+                                    int T, size_t *half_offset_floats);
 int tq_comm_rank(void);
 int tq_comm_world(void);
 void tq_comm_destroy(void);
@@ -249,6 +268,9 @@ void x_w4_shard_free(tq_qmma_weight_t *w);
 int x_gemm_w4a8_fanout(const tq_qmma_weight_t *const *ws, float *const *ys, int count,
                        const int8_t *d_aq, const float *d_as, const int32_t *d_asum, int T,
                        const int *offsets = nullptr, int segments = 0);
+int x_gemm_w4a8_fanout_gathered(const tq_qmma_weight_t *const *ws, int count, const int8_t *d_aq,
+                                const float *d_as, const int32_t *d_asum, int T,
+                                size_t *half_offset_floats = nullptr);
 void x_quantize_act_chunk_pertoken(const float *d_x, int K, int T, int8_t *d_aq, float *d_as,
                                    int32_t *d_asum, float *d_as_tok);
 int x_gemm_w4a8_pertoken(const tq_qmma_weight_t *w, const int8_t *d_aq, const float *d_as_tok,

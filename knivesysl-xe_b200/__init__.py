@@ -85,6 +85,12 @@ SIGNATURES = {
     "qwn_x_gemv_w4a8_static": (_i, [_WP, _vp, _vp]), "qwn_static_max_k": (_i, []),
     "tq_comm_unique_id": (_i, [_vp]), "tq_comm_init": (_i, [_vp, _i, _i]),
     "tq_comm_allgather": (_i, [_vp, _vp, _sz]),
+    "tq_comm_ipc_export": (_i, [_vp, _vp]), "tq_comm_ipc_open": (_vp, [_vp]),
+    "tq_comm_ipc_close": (None, [_vp]),
+    "tq_comm_gather_setup": (_i, [C.POINTER(_vp), C.POINTER(_vp), _i, _i]),
+    "tq_comm_gather_wait": (_i, []),
+    "qwn_x_gemm_w4a8_fanout_gathered": (_i, [C.POINTER(_WP), _i, _vp, _vp, _vp, _i,
+                                         C.POINTER(_sz)]),
     "tq_comm_rank": (_i, []), "tq_comm_world": (_i, []), "tq_comm_destroy": (None, []),
 }
 

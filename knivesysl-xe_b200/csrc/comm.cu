@@ -26,6 +26,30 @@ struct NcclApi {
 
 ncclComm_t g_comm = nullptr;
 int g_rank = 0, g_world = 1;
+tq::GatherState g_gather;
+
+// One warp waits until the flag words written by all source ranks have reached `step`
+// (bounded: two seconds of wall clock, then status 31 and a normal return).
+__global__ void gather_wait_kernel(const int *flags, int world, int step, int *status) {
+    tq::pdl_trigger();
+    tq::pdl_wait();
+    const int p = threadIdx.x;
+    if (p >= world) return;
+    unsigned long long t0 = 0;
+    for (unsigned polls = 0;; ++polls) {
+        int v;
+        asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(flags + p) : "memory");
+        if (v - step >= 0) return;
+        __nanosleep(100);
+        if ((polls & 255u) == 255u) {
+            unsigned long long now;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > 2000000000ull) break;
+        }
+    }
+    atomicCAS(status, 0, 31);
+}
 
 bool load_nccl() {
     if (g_api.handle) return true;
@@ -59,6 +83,10 @@ int nccl_fail(ncclResult_t r, const char *where) {
 }
 
 }  // namespace
+
+namespace tq {
+GatherState &gather_state() { return g_gather; }
+}  // namespace tq
 
 extern "C" {
 
@@ -97,6 +125,69 @@ int tq_comm_allgather(const void *d_send, void *d_recv, size_t bytes_per_rank) {
     const ncclResult_t r =
         g_api.AllGather(d_send, d_recv, bytes_per_rank, kNcclInt8, g_comm, tq::stream());
     if (r != 0) return nccl_fail(r, "ncclAllGather");
+    return 0;
+}
+
+// ---- fused all-gather over peer memory ------------------------------------------------
+// Each rank owns a gathered buffer [world][block] and a flag array int[world] (zeroed),
+// both plain cudaMalloc memory; the other ranks map them through CUDA IPC.
+int tq_comm_ipc_export(void *d_ptr, void *handle64) {
+    if (!d_ptr || !handle64) return -1;
+    cudaIpcMemHandle_t h;
+    const cudaError_t e = cudaIpcGetMemHandle(&h, d_ptr);
+    if (e != cudaSuccess) {
+        tq::note_error(e, "cudaIpcGetMemHandle");
+        return -2;
+    }
+    memcpy(handle64, &h, sizeof h);
+    return 0;
+}
+
+void *tq_comm_ipc_open(const void *handle64) {
+    if (!handle64) return nullptr;
+    tq::stream();
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, sizeof h);
+    void *p = nullptr;
+    const cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) {
+        tq::note_error(e, "cudaIpcOpenMemHandle");
+        return nullptr;
+    }
+    return p;
+}
+
+void tq_comm_ipc_close(void *p) {
+    if (p) cudaIpcCloseMemHandle(p);
+}
+
+// bufs[p], flags[p]: rank p's gathered buffer and flag array as addressable from this
+// process (its own allocation for p == rank). world <= 8.
+int tq_comm_gather_setup(void *const *bufs, void *const *flags, int world, int rank) {
+    if (!bufs || !flags || world < 1 || world > 8 || rank < 0 || rank >= world) return -1;
+    tq::GatherState &g = g_gather;
+    for (int p = 0; p < world; ++p) {
+        if (!bufs[p] || !flags[p]) return -1;
+        g.buf[p] = static_cast<float *>(bufs[p]);
+        g.flag[p] = static_cast<int *>(flags[p]);
+    }
+    if (!g.done) {
+        g.done = static_cast<int *>(tq_dev_alloc(sizeof(int), "gather.done"));
+        tq_dev_zero(g.done, sizeof(int));
+    }
+    g.world = world;
+    g.rank = rank;
+    g.step = 0;
+    return 0;
+}
+
+// Enqueues the wait for the slices of every rank of the last gathered call.
+int tq_comm_gather_wait(void) {
+    tq::GatherState &g = g_gather;
+    if (g.world < 1) return -3;
+    tq::launch_pdl(gather_wait_kernel, dim3(1), dim3(32), 0, (const int *)g.flag[g.rank], g.world,
+                   g.step, tq::device_status_word());
+    tq::note_error(cudaGetLastError(), "gather_wait_kernel");
     return 0;
 }
 

@@ -42,6 +42,17 @@ void ensure_act_scratch(int K);
 // Device status word for bounded waits inside kernels (0 = clean).
 int *device_status_word();
 
+// State of the fused all-gather (comm.cu): buffers and flag words of every rank as mapped
+// into this process, set up by tq_comm_gather_setup.
+struct GatherState {
+    int world = 0, rank = 0;
+    float *buf[8] = {};       // rank p's gathered buffer
+    int *flag[8] = {};        // rank p's flag array (one int per source rank)
+    int *done = nullptr;      // local CTA counter
+    int step = 0;             // last published step
+};
+GatherState &gather_state();
+
 // ---- split heuristics (dispatch.cu) --------------------------------------------
 int choose_gemv_splits(int groups);
 int choose_gemm_splits(int rgroups, int tgroups, int ktiles);
@@ -97,6 +108,14 @@ struct GemmArgs {
     GemmSegments seg[4];     // per weight (each keeps the splits it would get alone)
     int max_splits;
     int32_t *dump;           // non-null: write int32 tile dots (single weight)
+    // Fused all-gather of a column shard (streaming kernel only): when npeer > 0 the
+    // output of weight i goes to ypeer[p][i] for every rank p instead of y[i], and the last
+    // CTA to finish stores `step` into peer_flag[p] of every rank (see comm.cu).
+    int npeer;
+    float *ypeer[8][4];
+    int *peer_flag[8];
+    int *done;               // CTA arrival counter of this launch (zero between launches)
+    int step;
 };
 void launch_gemm_mma(const GemmArgs &a);
 // gemm_stream.cu (decode batches: one segment, T <= 64, uniform split count <= 8)

@@ -300,6 +300,58 @@ int x_gemm_w4a8_fanout(const tq_qmma_weight_t *const *ws, float *const *ys, int 
     return 0;
 }
 
+// Fused projection + all-gather of a column shard: this rank's outputs [count][T][M_i] go
+// to block `rank` of the gathered buffer [2 halves][world][count][T][M_i] of EVERY rank (peer stores
+// from the kernel's epilogue), followed by a flag store; tq_comm_gather_wait() orders later
+// work after the arrival of all ranks' blocks. Decode shapes only (the streaming kernel).
+int x_gemm_w4a8_fanout_gathered(const tq_qmma_weight_t *const *ws, int count, const int8_t *d_aq,
+                                const float *d_as, const int32_t *d_asum, int T,
+                                size_t *half_offset_floats) {
+    GatherState &g = gather_state();
+    if (g.world < 1) return -3;
+    if (!ws || count <= 0 || count > 4 || !ws[0]) return -1;
+    GemmArgs a{};
+    const int K = ws[0]->K;
+    const int ksh = ws[0]->s4_k64 ? 1 : 0;
+    if (!d_aq || !d_as || !d_asum || T <= 0 || (T % 8) != 0) return -2;
+    size_t block = 0;
+    for (int i = 0; i < count; ++i) block += (size_t)T * ws[i] ->M;
+    a.goff[0] = 0;
+    a.max_splits = 1;
+    size_t off = 0;
+    for (int i = 0; i < count; ++i) {
+        const tq_qmma_weight_t *w = ws[i];
+        if (!w || !w->s4_ready || w->s4_k16 || !w->d_s4 || !w->d_s4_scale) return -1;
+        if (w->K != K || (w->s4_k64 ? 1 : 0) != ksh || (w->M % 16) || (K % 32)) return -1;
+        a.codes[i] = w->d_s4;
+        a.scales[i] = w->d_s4_scale;
+        a.M[i] = w->M;
+        a.goff[i + 1] = a.goff[i] + w->M / 16;
+        int ms = 1;
+        const int rc = build_segments(w->M / 16, K / 32, T, nullptr, 0, a.seg[i], ms);
+        if (rc) return rc;
+        a.max_splits = std::max(a.max_splits, ms);
+        // two halves, used alternately: a rank that is one step ahead never overwrites a
+        // block its peers may still be reading
+        const size_t half = (size_t)((g.step + 1) & 1) * g.world * block;
+        for (int p = 0; p < g.world; ++p)
+            a.ypeer[p][i] = g.buf[p] + half + (size_t)g.rank * block + off;
+        off += (size_t)T * w->M;
+    }
+    a.count = count;
+    a.aq = d_aq; a.as = d_as; a.asum = d_asum;
+    a.K = K; a.ksh = ksh; a.T = T;
+    a.npeer = g.world;
+    for (int p = 0; p < g.world; ++p) a.peer_flag[p] = g.flag[p] + g.rank;
+    a.done = g.done;
+    a.step = g.step + 1;
+    if (!gemm_stream_covers(a)) return -21;
+    g.step += 1;
+    if (half_offset_floats) *half_offset_floats = (size_t)(g.step & 1) * g.world * block;
+    launch_gemm_stream(a);
+    return 0;
+}
+
 int x_gemm_w4a8(const tq_qmma_weight_t *w, const int8_t *d_aq, const float *d_as,
                 const int32_t *d_asum, float *d_y, int T, const int *offsets, int segments) {
     if (!w || !w->s4_ready || w->s4_k16 || !w->d_s4 || !w->d_s4_scale) return -1;
@@ -466,6 +518,12 @@ void qwn_x_quantize_act_chunk_pertoken(const float *d_x, int K, int T, int8_t *d
 int qwn_x_gemm_w4a8_pertoken(const tq_qmma_weight_t *w, const int8_t *d_aq, const float *d_as_tok,
                              const int32_t *d_asum, void *d_y, int T, int out_bf16) {
     return x_gemm_w4a8_pertoken(w, d_aq, d_as_tok, d_asum, d_y, T, out_bf16);
+}
+
+int qwn_x_gemm_w4a8_fanout_gathered(const tq_qmma_weight_t *const *ws, int count,
+                                    const int8_t *d_aq, const float *d_as, const int32_t *d_asum,
+                                    int T, size_t *half_offset_floats) {
+    return x_gemm_w4a8_fanout_gathered(ws, count, d_aq, d_as, d_asum, T, half_offset_floats);
 }
 
 int qwn_dbg_tile_dots_gemv(const tq_qmma_weight_t *w, int32_t *d_out) {

@@ -359,16 +359,58 @@ gemm_w4a8_stream_kernel(const GemmArgs a, float *__restrict__ part, int *__restr
                         }
                     if (lane == 0) count[gg] = 0;   // ready for the next launch
                 }
-                float *y = a.y[wi];
                 const size_t row = (size_t)(lg + g) * 16 + r;
+                if (!a.npeer) {
+                    float *y = a.y[wi];
 #pragma unroll
-                for (int t = 0; t < NTG; ++t) {
-                    const size_t tok = (size_t)t * 8 + 2 * c;
-                    y[tok * M + row] = out[t][0];
-                    y[(tok + 1) * M + row] = out[t][1];
-                    y[tok * M + row + 8] = out[t][2];
-                    y[(tok + 1) * M + row + 8] = out[t][3];
+                    for (int t = 0; t < NTG; ++t) {
+                        const size_t tok = (size_t)t * 8 + 2 * c;
+                        y[tok * M + row] = out[t][0];
+                        y[(tok + 1) * M + row] = out[t][1];
+                        y[tok * M + row + 8] = out[t][2];
+                        y[(tok + 1) * M + row + 8] = out[t][3];
+                    }
+                } else {
+                    // Fused all-gather: the same slice goes into the gathered buffer of every
+                    // rank. The 16 x 8 tile of a token group is transposed through the warp's
+                    // scale buffer (free at this point) so that a lane holds four consecutive
+                    // rows of one token and every peer gets 16-byte stores (64-byte runs).
+                    float *tile = reinterpret_cast<float *>(expw);
+#pragma unroll
+                    for (int t = 0; t < NTG; ++t) {
+                        __syncwarp();
+                        tile[(2 * c) * 16 + r] = out[t][0];
+                        tile[(2 * c + 1) * 16 + r] = out[t][1];
+                        tile[(2 * c) * 16 + r + 8] = out[t][2];
+                        tile[(2 * c + 1) * 16 + r + 8] = out[t][3];
+                        __syncwarp();
+                        const float4 v = *reinterpret_cast<const float4 *>(tile + lane * 4);
+                        const size_t tok = (size_t)t * 8 + (lane >> 2);
+                        const size_t off = tok * M + (size_t)(lg + g) * 16 + (lane & 3) * 4;
+                        for (int pi = 0; pi < a.npeer; ++pi)
+                            *reinterpret_cast<float4 *>(a.ypeer[pi][wi] + off) = v;
+                    }
+                    __syncwarp();
                 }
+            }
+        }
+    }
+    if (!DUMP && a.npeer) {
+        // Publish. The CTA barrier orders every thread's peer stores before thread 0, whose
+        // device-scope fence + counter increment hands them to the last CTA of the grid;
+        // that CTA alone pays the system-scope fence and stores the step number into this
+        // rank's flag word on every rank (one fence per launch, not one per thread).
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            __threadfence();
+            const int prev = atomicAdd(a.done, 1);
+            if (prev == (int)gridDim.x - 1) {
+                *a.done = 0;                       // ready for the next launch
+                __threadfence_system();
+                for (int pi = 0; pi < a.npeer; ++pi)
+                    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(a.peer_flag[pi]),
+                                 "r"(a.step)
+                                 : "memory");
             }
         }
     }
@@ -461,6 +503,7 @@ void launch_ntg(const GemmArgs &a) {
 }  // namespace
 
 bool gemm_stream_covers(const GemmArgs &a) {
+    if (a.npeer < 0 || a.npeer > 8) return false;
     if (a.count < 1 || a.T < 8 || a.T > 64 || (a.T % 8)) return false;
     if (a.max_splits > 16) return false;
     if (a.ksh && ((a.K >> 5) & 1)) return false;

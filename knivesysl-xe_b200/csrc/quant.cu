@@ -43,7 +43,8 @@ quant_s8_kernel(const float *__restrict__ x, const float *__restrict__ up,
                 float *__restrict__ hidden, int blocks, int8_t *__restrict__ q,
                 int8_t *__restrict__ qp, float *__restrict__ scale, int32_t *__restrict__ sum16,
                 int32_t *__restrict__ sum32) {
-    pdl_trigger();   // the next kernel may start its weight prefetch now
+    pdl_trigger();   // the next kernel may be scheduled (its weight prefetch, its launch latency)
+    pdl_wait();      // ... while this one waits here for everything launched before it
     const int b = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (b >= blocks) return;
@@ -70,7 +71,8 @@ quant_s8_kernel(const float *__restrict__ x, const float *__restrict__ up,
 // warp sums added 0..7 (the order the CPU oracle restates).
 __global__ void __launch_bounds__(256)
 sumsq_partial_kernel(const float *__restrict__ in, int H, float *__restrict__ part) {
-    pdl_trigger();   // the next kernel may start its weight prefetch now
+    pdl_trigger();   // the next kernel may be scheduled (its weight prefetch, its launch latency)
+    pdl_wait();      // ... while this one waits here for everything launched before it
     __shared__ float wsum[8];
     const int i = blockIdx.x * 256 + threadIdx.x;
     const float v = (i < H) ? in[i] : 0.0f;
@@ -94,7 +96,8 @@ rmsnorm_quant_kernel(float *__restrict__ out, const float *__restrict__ in,
                      const float *__restrict__ part, int nblk, int8_t *__restrict__ q,
                      int8_t *__restrict__ qp, float *__restrict__ scale,
                      int32_t *__restrict__ sum16, int32_t *__restrict__ sum32) {
-    pdl_trigger();   // the next kernel may start its weight prefetch now
+    pdl_trigger();   // the next kernel may be scheduled (its weight prefetch, its launch latency)
+    pdl_wait();      // ... while this one waits here for everything launched before it
     __shared__ float s_rms;
     if (threadIdx.x == 0) {
         float sum_sq = 0.0f;
@@ -129,7 +132,8 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 quant_chunk_kernel(const float *__restrict__ x, int K, int T, size_t blocks,
                    int8_t *__restrict__ aq, float *__restrict__ as, int32_t *__restrict__ asum,
                    const float *__restrict__ as_tok) {
-    pdl_trigger();   // the next kernel may start its weight prefetch now
+    pdl_trigger();   // the next kernel may be scheduled (its weight prefetch, its launch latency)
+    pdl_wait();      // ... while this one waits here for everything launched before it
     const size_t blk = (size_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (blk >= blocks) return;
@@ -155,7 +159,8 @@ quant_chunk_kernel(const float *__restrict__ x, int K, int T, size_t blocks,
 // Per-token absmax -> scale (one block per token row).
 __global__ void __launch_bounds__(256)
 token_scale_kernel(const float *__restrict__ x, int K, float *__restrict__ as_tok) {
-    pdl_trigger();   // the next kernel may start its weight prefetch now
+    pdl_trigger();   // the next kernel may be scheduled (its weight prefetch, its launch latency)
+    pdl_wait();      // ... while this one waits here for everything launched before it
     __shared__ float wmax[8];
     const float *row = x + (size_t)blockIdx.x * K;
     float m = -INFINITY;
@@ -201,11 +206,12 @@ void launch_quant_s8(const float *d_x, const float *d_up, float *d_hidden, int K
     if (blocks <= 0) return;
     const int grid = (blocks + kWarpsPerBlock - 1) / kWarpsPerBlock;
     if (silu)
-        quant_s8_kernel<true><<<grid, kWarpsPerBlock * 32, 0, stream()>>>(
-            d_x, d_up, d_hidden, blocks, d_q, d_qp, d_scale, d_sum16, d_sum32);
+        launch_pdl(quant_s8_kernel<true>, dim3(grid), dim3(kWarpsPerBlock * 32), 0, d_x, d_up,
+                   d_hidden, blocks, d_q, d_qp, d_scale, d_sum16, d_sum32);
     else
-        quant_s8_kernel<false><<<grid, kWarpsPerBlock * 32, 0, stream()>>>(
-            d_x, nullptr, nullptr, blocks, d_q, d_qp, d_scale, d_sum16, d_sum32);
+        launch_pdl(quant_s8_kernel<false>, dim3(grid), dim3(kWarpsPerBlock * 32), 0, d_x,
+                   (const float *)nullptr, (float *)nullptr, blocks, d_q, d_qp, d_scale, d_sum16,
+                   d_sum32);
     TQ_LAUNCH_CHECK("quant_s8_kernel");
 }
 
@@ -213,10 +219,10 @@ void launch_rmsnorm_quant(float *d_out, const float *d_in, const uint16_t *d_w, 
                           float *d_partial, int8_t *d_q, int8_t *d_qp, float *d_scale,
                           int32_t *d_sum16, int32_t *d_sum32) {
     const int nblk = (H + 255) / 256;
-    sumsq_partial_kernel<<<nblk, 256, 0, stream()>>>(d_in, H, d_partial);
+    launch_pdl(sumsq_partial_kernel, dim3(nblk), dim3(256), 0, d_in, H, d_partial);
     TQ_LAUNCH_CHECK("sumsq_partial_kernel");
-    rmsnorm_quant_kernel<<<nblk, 256, 0, stream()>>>(d_out, d_in, d_w, H, eps, d_partial, nblk,
-                                                      d_q, d_qp, d_scale, d_sum16, d_sum32);
+    launch_pdl(rmsnorm_quant_kernel, dim3(nblk), dim3(256), 0, d_out, d_in, d_w, H, eps,
+               (const float *)d_partial, nblk, d_q, d_qp, d_scale, d_sum16, d_sum32);
     TQ_LAUNCH_CHECK("rmsnorm_quant_kernel");
 }
 
@@ -225,8 +231,8 @@ void launch_quant_chunk(const float *d_x, int K, int T, int8_t *d_aq, float *d_a
     const size_t blocks = (size_t)(K / 32) * (size_t)T;
     if (!blocks) return;
     const unsigned grid = (unsigned)((blocks + kWarpsPerBlock - 1) / kWarpsPerBlock);
-    quant_chunk_kernel<false><<<grid, kWarpsPerBlock * 32, 0, stream()>>>(d_x, K, T, blocks, d_aq,
-                                                                          d_as, d_asum, nullptr);
+    launch_pdl(quant_chunk_kernel<false>, dim3(grid), dim3(kWarpsPerBlock * 32), 0, d_x, K, T,
+               blocks, d_aq, d_as, d_asum, (const float *)nullptr);
     TQ_LAUNCH_CHECK("quant_chunk_kernel");
 }
 
@@ -234,11 +240,11 @@ void launch_quant_chunk_pertoken(const float *d_x, int K, int T, int8_t *d_aq, f
                                  int32_t *d_asum, float *d_as_tok) {
     const size_t blocks = (size_t)(K / 32) * (size_t)T;
     if (!blocks) return;
-    token_scale_kernel<<<T, 256, 0, stream()>>>(d_x, K, d_as_tok);
+    launch_pdl(token_scale_kernel, dim3(T), dim3(256), 0, d_x, K, d_as_tok);
     TQ_LAUNCH_CHECK("token_scale_kernel");
     const unsigned grid = (unsigned)((blocks + kWarpsPerBlock - 1) / kWarpsPerBlock);
-    quant_chunk_kernel<true><<<grid, kWarpsPerBlock * 32, 0, stream()>>>(d_x, K, T, blocks, d_aq,
-                                                                         d_as, d_asum, d_as_tok);
+    launch_pdl(quant_chunk_kernel<true>, dim3(grid), dim3(kWarpsPerBlock * 32), 0, d_x, K, T,
+               blocks, d_aq, d_as, d_asum, (const float *)d_as_tok);
     TQ_LAUNCH_CHECK("quant_chunk_kernel<pertoken>");
 }
 

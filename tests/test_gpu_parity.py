@@ -384,3 +384,44 @@ def test_reference_gates_on_synthetic_weight(lib, pkg, wl):
             assert cos.value >= 0.9999
         assert lib.qwn_specwave_check(w.ref) == 0
         assert lib.qwn_gemv_bench(w.ref, 5) > 0 and lib.qwn_gemm_bench(w.ref, 8, 5) > 0
+
+
+# ---------------------------------------------------------------- fused all-gather (1 rank)
+@pytest.mark.gpu
+def test_gathered_gemm_single_rank(lib, pkg, orc, wl):
+    """World of one: the peer-store epilogue, the step flag and the bounded wait kernel run
+    against this GPU's own buffers; both halves of the gathered buffer are exercised and
+    the result is bit-identical to the plain fan-out call."""
+    K, T, ksh = 512, 8, 1
+    Ms = [1088, 544]
+    ws = [pkg.PackedWeight(*wl.random_packed_weight(M, K, seed=70 + i, ksh=ksh), M, K, k64=True)
+          for i, M in enumerate(Ms)]
+    x = refgen.gemm_check_rows(T, K)
+    n = K // 32 * T
+    aq, as_, asum = pkg.DevBuf(n * 32), pkg.DevBuf(n * 4), pkg.DevBuf(n * 4)
+    lib.qwn_x_quantize_act_chunk(dev(pkg, x).ptr, K, T, aq.ptr, as_.ptr, asum.ptr)
+    ys = [pkg.DevBuf(T * M * 4) for M in Ms]
+    assert lib.qwn_x_gemm_w4a8_fanout(pkg.weight_array(ws), pkg.ptr_array(ys), 2, aq.ptr, as_.ptr,
+                                      asum.ptr, T, None, 0) == 0
+    want = np.concatenate([y.to_numpy(np.float32) for y in ys])
+    block = T * sum(Ms)
+    gathered = pkg.DevBuf(2 * block * 4)
+    gathered.fill(0xA5)
+    flags = pkg.DevBuf(4)
+    lib.tq_dev_zero(flags.ptr, 4)
+    bufs = (C.c_void_p * 1)(gathered.ptr)
+    flg = (C.c_void_p * 1)(flags.ptr)
+    assert lib.tq_comm_gather_setup(bufs, flg, 1, 0) == 0
+    halves = []
+    for step in range(2):
+        off = C.c_size_t(0)
+        assert lib.qwn_x_gemm_w4a8_fanout_gathered(pkg.weight_array(ws), 2, aq.ptr, as_.ptr,
+                                                   asum.ptr, T, C.byref(off)) == 0
+        assert lib.tq_comm_gather_wait() == 0
+        lib.tq_sync()
+        halves.append(off.value)
+        got = gathered.to_numpy(np.float32)[off.value: off.value + block]
+        assert got.tobytes() == want.tobytes()
+        assert flags.to_numpy(np.int32)[0] == step + 1
+    assert sorted(halves) == [0, block]
+    assert lib.tq_last_error() == 0
