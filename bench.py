@@ -4,7 +4,7 @@
 Workload ("cfg2"): batched decode fused gate+up projection, K64 scale tier, T = 8 tokens,
 K = 5120, N = 2 x 17408; seeded N(0, 0.02) weights symmetric-quantised to int4; N(0, 1)
 activations with 1% of channels scaled x20, quantised to int8 per token. One step = one pass:
-per-token activation staging (2 launches) + ONE fused gate|up GEMM launch over a weight copy
+per-token activation staging (1 launch) + ONE fused gate|up GEMM launch over a weight copy
 that rotates through `rotate` distinct copies (> L2 in total), so weights come from HBM.
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
@@ -390,7 +390,7 @@ def main():
                            if fused else " + NCCL all-gather"),
                        "l2": f"inputs larger than L2: {args.rotate} rotating weight copies, "
                              f"{args.rotate * full_weight_bytes // world / 1e6:.0f} MB per GPU",
-                       "step": "token_scale + quant_chunk + fused gate|up GEMM" +
+                       "step": "per-token staging (1 launch) + fused gate|up GEMM" +
                                (" + all-gather" if world > 1 else "")},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "peak_source": f"{peak_kind} copy bandwidth",
@@ -400,7 +400,7 @@ def main():
             "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": int(x.nbytes),
                     "d2h_bytes_per_step": int(out_bytes), "steps": e_iters,
                     "us_per_step": e_s / e_iters * 1e6},
-            "gpu_launches": 3 * args.steps,
+            "gpu_launches": (2 + (1 if fused else 0) + (1 if world > 1 and not fused else 0)) * args.steps,
             "clocks": clocks,
             "cpu_baseline": cpu,
             "device_error": err,

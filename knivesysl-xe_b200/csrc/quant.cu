@@ -176,6 +176,54 @@ token_scale_kernel(const float *__restrict__ x, int K, float *__restrict__ as_to
     }
 }
 
+// Small token counts (decode batches): absmax and quantisation of a token row in ONE launch,
+// one CTA per token; the row is read twice (the second time from L1/L2). Same arithmetic as
+// token_scale_kernel followed by quant_chunk_kernel<true>.
+__global__ void __launch_bounds__(1024)
+quant_chunk_pertoken_fused_kernel(const float *__restrict__ x, int K, int T,
+                                  int8_t *__restrict__ aq, float *__restrict__ as,
+                                  int32_t *__restrict__ asum, float *__restrict__ as_tok) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ float wmax[32];
+    __shared__ float s_scale;
+    const int tok = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const float *row = x + (size_t)tok * K;
+    float m = -INFINITY;
+    const float4 *row4 = reinterpret_cast<const float4 *>(row);     // K % 32 == 0
+    for (int i = threadIdx.x; i < (K >> 2); i += 1024) {
+        const float4 v = row4[i];
+        m = fmaxf(m, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+    }
+    m = warp_max(m);
+    if (lane == 0) wmax[warp] = m;
+    __syncthreads();
+    if (warp == 0) {
+        const float t = warp_max(wmax[lane]);
+        if (lane == 0) {
+            const float s = (t > 0.0f) ? __fdiv_rn(t, 127.0f) : 1.0f;
+            s_scale = s;
+            as_tok[tok] = s;
+        }
+    }
+    __syncthreads();
+    const float s = s_scale;
+    const int Kt = K >> 5;
+    for (int kt = warp; kt < Kt; kt += 32) {
+        const float v = row[kt * 32 + lane];
+        const int qv = quantise_one(v, s);
+        int sum = half_sum16(qv);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 16);
+        const size_t blk = (size_t)kt * T + tok;
+        aq[blk * 32 + lane] = (int8_t)qv;
+        if (lane == 0) {
+            as[blk] = s;
+            asum[blk] = sum;
+        }
+    }
+}
+
 // K32 code sums of already staged codes (debug helper for the int32 dump).
 __global__ void code_sums_kernel(const int8_t *__restrict__ aq, size_t blocks,
                                  int32_t *__restrict__ asum) {
@@ -240,6 +288,12 @@ void launch_quant_chunk_pertoken(const float *d_x, int K, int T, int8_t *d_aq, f
                                  int32_t *d_asum, float *d_as_tok) {
     const size_t blocks = (size_t)(K / 32) * (size_t)T;
     if (!blocks) return;
+    if (T <= 32) {
+        launch_pdl(quant_chunk_pertoken_fused_kernel, dim3(T), dim3(1024), 0, d_x, K, T, d_aq, d_as,
+                   d_asum, d_as_tok);
+        TQ_LAUNCH_CHECK("quant_chunk_pertoken_fused_kernel");
+        return;
+    }
     launch_pdl(token_scale_kernel, dim3(T), dim3(256), 0, d_x, K, d_as_tok);
     TQ_LAUNCH_CHECK("token_scale_kernel");
     const unsigned grid = (unsigned)((blocks + kWarpsPerBlock - 1) / kWarpsPerBlock);

@@ -68,8 +68,9 @@ def test_quantize_act_chunk(lib, pkg, orc, K, T, exceptional):
     assert np.array_equal(asum.to_numpy(np.int32), osm)
 
 
-def test_quantize_act_chunk_pertoken(lib, pkg, orc, wl):
-    K, T = 5120, 16
+@pytest.mark.parametrize("T", [8, 16, 40])      # one fused launch up to 32 tokens, two above
+def test_quantize_act_chunk_pertoken(lib, pkg, orc, wl, T):
+    K = 5120
     x = wl.activations_normal(T, K, seed=2, outlier_frac=0.01)
     dx = dev(pkg, x)
     n = K // 32 * T
