@@ -58,7 +58,10 @@ template <int NTG, bool STAGED, bool DUMP, int kW>
 __global__ void __launch_bounds__(kW * 32, 1)
 gemm_w4a8_stream_kernel(const GemmArgs a, float *__restrict__ part, int *__restrict__ count) {
     extern __shared__ __align__(128) unsigned char smem[];
-    constexpr int T = NTG * 8;
+    constexpr int T = NTG * 8;              // tokens of this CTA's window
+    const int Ttot = a.T;                   // tokens of the call (row stride of the staging)
+    const int win = blockIdx.y;             // token window: tokens [tok0, tok0 + T)
+    const int tok0 = win * T;
     constexpr int G = 1;   // 16-row groups a warp works on at a time (kept as a loop bound)
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -73,7 +76,8 @@ gemm_w4a8_stream_kernel(const GemmArgs a, float *__restrict__ part, int *__restr
     float2 *expw = reinterpret_cast<float2 *>(smem) + warp * (G * 128);
     unsigned char *act = smem + (size_t)kW * G * kExpBytes;
 
-    const int units = a.goff[a.count] / G;                  // a unit = G adjacent row-groups
+    const int groups_all = a.goff[a.count];
+    const int units = groups_all / G;                       // a unit = G adjacent row-groups
     const int tgid = cta_i + nctas * warp;                  // first unit of this warp
     const int tstride = nctas * kW;
     const int ntasks = (tgid < units) ? (units - tgid + tstride - 1) / tstride : 0;
@@ -167,7 +171,7 @@ gemm_w4a8_stream_kernel(const GemmArgs a, float *__restrict__ part, int *__restr
             const int kl = i / (NTG * 32);
             const int rem = i - kl * (NTG * 32);             // = tg * 32 + lane'
             const uint2 bb = __ldg(reinterpret_cast<const uint2 *>(
-                a.aq + ((size_t)(kt_begin + kl) * T) * 32 + (size_t)rem * 8));
+                a.aq + ((size_t)(kt_begin + kl) * Ttot + tok0) * 32 + (size_t)rem * 8));
             uint2 o;
             o.x = __byte_perm(bb.x, bb.y, 0x6420);
             o.y = __byte_perm(bb.x, bb.y, 0x7531);
@@ -178,7 +182,7 @@ gemm_w4a8_stream_kernel(const GemmArgs a, float *__restrict__ part, int *__restr
         for (int i = threadIdx.x; i < pairs; i += kW * 32) {
             const int kl = i / (NTG * 4);
             const int rem = i - kl * (NTG * 4);              // = tg * 4 + c'
-            const size_t src = (size_t)(kt_begin + kl) * T + (size_t)rem * 2;
+            const size_t src = (size_t)(kt_begin + kl) * Ttot + tok0 + (size_t)rem * 2;
             const float2 as2 = __ldg(reinterpret_cast<const float2 *>(a.as + src));
             const int2 sm2 = __ldg(reinterpret_cast<const int2 *>(a.asum + src));
             *reinterpret_cast<float4 *>(act + (size_t)(kl * NTG + (rem >> 2)) * kActTileBytes +
@@ -228,9 +232,9 @@ gemm_w4a8_stream_kernel(const GemmArgs a, float *__restrict__ part, int *__restr
             const int kl0 = ci * kCT;
             const unsigned char *actp = act + (size_t)kl0 * NTG * kActTileBytes + lane * 8;
             const unsigned char *asq = act + (size_t)kl0 * NTG * kActTileBytes + 256 + c * 16;
-            const int8_t *aqp = a.aq + ((size_t)cur_kt0 * T + r) * 32 + c * 8;
-            const float *asp = a.as + (size_t)cur_kt0 * T + 2 * c;
-            const int32_t *smp = a.asum + (size_t)cur_kt0 * T + 2 * c;
+            const int8_t *aqp = a.aq + ((size_t)cur_kt0 * Ttot + tok0 + r) * 32 + c * 8;
+            const float *asp = a.as + (size_t)cur_kt0 * Ttot + tok0 + 2 * c;
+            const int32_t *smp = a.asum + (size_t)cur_kt0 * Ttot + tok0 + 2 * c;
 
             // Two tiles (2jp, 2jp+1) of every group of the unit. FULL: the chunk has all 8 tiles.
             auto tile_pair = [&](auto full_tag, const int jp) {
@@ -271,12 +275,12 @@ gemm_w4a8_stream_kernel(const GemmArgs a, float *__restrict__ part, int *__restr
                             as2 = av.x; smf = av.y;
                         } else {
                             const uint2 bb =
-                                __ldg(reinterpret_cast<const uint2 *>(aqp + (u * T + t * 8) * 32));
+                                __ldg(reinterpret_cast<const uint2 *>(aqp + ((size_t)u * Ttot + t * 8) * 32));
                             b0 = __byte_perm(bb.x, bb.y, 0x6420);
                             b1 = __byte_perm(bb.x, bb.y, 0x7531);
                             as2 = __ldg(
-                                reinterpret_cast<const unsigned long long *>(asp + u * T + t * 8));
-                            sm2 = __ldg(reinterpret_cast<const int2 *>(smp + u * T + t * 8));
+                                reinterpret_cast<const unsigned long long *>(asp + (size_t)u * Ttot + t * 8));
+                            sm2 = __ldg(reinterpret_cast<const int2 *>(smp + (size_t)u * Ttot + t * 8));
                             smf = pack2((float)sm2.x, (float)sm2.y);
                         }
 #pragma unroll
@@ -287,7 +291,7 @@ gemm_w4a8_stream_kernel(const GemmArgs a, float *__restrict__ part, int *__restr
                                 const size_t Mz = (size_t)a.M[0];
                                 const size_t row0 = (size_t)(lg + g) * 16 + r;
                                 int32_t *o =
-                                    a.dump + ((size_t)(cur_kt0 + u) * T + t * 8 + 2 * c) * Mz;
+                                    a.dump + ((size_t)(cur_kt0 + u) * Ttot + tok0 + t * 8 + 2 * c) * Mz;
                                 o[row0] = d[0] - kMagicBits - 8 * sm2.x;
                                 o[Mz + row0] = d[1] - kMagicBits - 8 * sm2.y;
                                 o[row0 + 8] = d[2] - kMagicBits - 8 * sm2.x;
@@ -334,7 +338,7 @@ gemm_w4a8_stream_kernel(const GemmArgs a, float *__restrict__ part, int *__restr
                 }
                 if (S > 1) {
                     // partial of this split -> scratch; the last split to arrive sums 0..S-1
-                    float *pp = part + ((size_t)gg * S + split) * (NTG * 128) + lane;
+                    float *pp = part + (((size_t)win * groups_all + gg) * S + split) * (NTG * 128) + lane;
 #pragma unroll
                     for (int t = 0; t < NTG; ++t)
 #pragma unroll
@@ -342,11 +346,11 @@ gemm_w4a8_stream_kernel(const GemmArgs a, float *__restrict__ part, int *__restr
                     __threadfence();
                     __syncwarp();
                     int old = 0;
-                    if (lane == 0) old = atomicAdd(count + gg, 1);
+                    if (lane == 0) old = atomicAdd(count + win * groups_all + gg, 1);
                     old = __shfl_sync(0xffffffffu, old, 0);
                     if (old != S - 1) continue;
                     __threadfence();
-                    const float *base = part + (size_t)gg * S * (NTG * 128) + lane;
+                    const float *base = part + ((size_t)win * groups_all + gg) * S * (NTG * 128) + lane;
 #pragma unroll
                     for (int t = 0; t < NTG; ++t)
 #pragma unroll
@@ -357,14 +361,14 @@ gemm_w4a8_stream_kernel(const GemmArgs a, float *__restrict__ part, int *__restr
                                                             (t * 4 + k) * 32));
                             out[t][k] = sum;
                         }
-                    if (lane == 0) count[gg] = 0;   // ready for the next launch
+                    if (lane == 0) count[win * groups_all + gg] = 0;   // ready for the next launch
                 }
                 const size_t row = (size_t)(lg + g) * 16 + r;
                 if (!a.npeer) {
                     float *y = a.y[wi];
 #pragma unroll
                     for (int t = 0; t < NTG; ++t) {
-                        const size_t tok = (size_t)t * 8 + 2 * c;
+                        const size_t tok = (size_t)tok0 + t * 8 + 2 * c;
                         y[tok * M + row] = out[t][0];
                         y[(tok + 1) * M + row] = out[t][1];
                         y[tok * M + row + 8] = out[t][2];
@@ -385,7 +389,7 @@ gemm_w4a8_stream_kernel(const GemmArgs a, float *__restrict__ part, int *__restr
                         tile[(2 * c + 1) * 16 + r + 8] = out[t][3];
                         __syncwarp();
                         const float4 v = *reinterpret_cast<const float4 *>(tile + lane * 4);
-                        const size_t tok = (size_t)t * 8 + (lane >> 2);
+                        const size_t tok = (size_t)tok0 + t * 8 + (lane >> 2);
                         const size_t off = tok * M + (size_t)(lg + g) * 16 + (lane & 3) * 4;
                         for (int pi = 0; pi < a.npeer; ++pi)
                             *reinterpret_cast<float4 *>(a.ypeer[pi][wi] + off) = v;
@@ -456,11 +460,13 @@ void launch_variant(const GemmArgs &a, size_t smem) {
     }
     const int S = a.max_splits;
     const int groups = a.goff[a.count];
-    if (S > 1 && !DUMP) ensure_scratch((size_t)groups * S * NTG * 128, groups);
+    const int nwin = a.T / (NTG * 8);            // token windows (grid.y), one per CTA column
+    if (S > 1 && !DUMP)
+        ensure_scratch((size_t)nwin * groups * S * NTG * 128, nwin * groups);
     const int want = ((groups + kW - 1) / kW) * S;
-    const int grid = std::max(S, std::min(g_num_sms, want));
-    launch_pdl(gemm_w4a8_stream_kernel<NTG, STAGED, DUMP, kW>, dim3(grid), dim3(kW * 32), smem, a,
-               g_scratch.part, g_scratch.count);
+    const int grid = std::max(S, std::min(std::max(1, g_num_sms / nwin), want));
+    launch_pdl(gemm_w4a8_stream_kernel<NTG, STAGED, DUMP, kW>, dim3(grid, nwin), dim3(kW * 32),
+               smem, a, g_scratch.part, g_scratch.count);
     TQ_LAUNCH_CHECK("gemm_w4a8_stream_kernel");
 }
 
@@ -513,8 +519,24 @@ bool gemm_stream_covers(const GemmArgs &a) {
     return true;
 }
 
+// Tokens per CTA window. Up to 16 tokens a warp carries all of them (weights are fetched
+// once). Above that the reference's split rule leaves few (row-group, split) tasks, so the
+// tokens are cut into windows handled by different CTAs (grid.y): 16 tokens per window when
+// the window's activations of one split fit in shared memory, else 8 if those fit, else 16
+// read through L1. A call that feeds the fused all-gather keeps one window.
+int window_groups(const GemmArgs &a) {
+    const int ntg = a.T / 8;
+    if (ntg <= 2 || a.dump || a.npeer) return ntg;
+    const int Kt = a.K >> 5, S = a.max_splits;
+    const size_t per_tg = (size_t)((Kt + S - 1) / S) * kActTileBytes;
+    const size_t room = kSmemLimit - (size_t)kWmax * kExpBytes;
+    if (ntg % 2 == 0 && 2 * per_tg <= room) return 2;
+    if (per_tg <= room) return 1;
+    return (ntg % 2 == 0) ? 2 : 1;
+}
+
 void launch_gemm_stream(const GemmArgs &a) {
-    switch (a.T / 8) {
+    switch (window_groups(a)) {
         case 1: launch_ntg<1>(a); break;
         case 2: launch_ntg<2>(a); break;
         case 3: launch_ntg<3>(a); break;
