@@ -85,6 +85,14 @@ struct GemvArgs {
     int K, ksh, splits;
     int serial;              // 1 = one serial accumulator (fan-out order), 0 = two accumulators
     int32_t *dump;           // non-null: write int32 tile dots instead of y
+    // Fused activation quantisation (x_gemv_w4a8 / _add): when x is set every CTA quantises
+    // the fp32 row itself into shared memory and CTA 0 also refreshes the prepared scratch
+    // (sq, sqp, sscale, ssum16, ssum32), so the "prepared" state after the call is the same
+    // as with a separate x_prepare_gemv_act_s8.
+    const float *x;
+    int8_t *sq, *sqp;
+    float *sscale;
+    int32_t *ssum16, *ssum32;
 };
 void launch_gemv(const GemvArgs &a);
 
@@ -214,6 +222,29 @@ __device__ __forceinline__ float clampf(float x, float lo, float hi) {
 __device__ __forceinline__ void unpack_scale(uint32_t packed, int &zp, float &ws) {
     zp = ((int)(packed << 28)) >> 28;
     ws = __half2float(__ushort_as_half((unsigned short)(packed & 0xFFF0u)));
+}
+
+// ---- pieces of the activation quantisers shared by quant.cu and the fused GEMV prologue ----
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, off));
+    return v;
+}
+
+// Sum inside each 16-lane half (the K16 sums).
+__device__ __forceinline__ int half_sum16(int v) {
+#pragma unroll
+    for (int off = 8; off >= 1; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+    return v;
+}
+
+// Position of code k inside the permuted 32-byte tile (even-k codes, then odd-k).
+__device__ __forceinline__ int permuted_pos(int k) {
+    return ((k & 1) << 4) + ((k >> 3) << 2) + ((k & 7) >> 1);
+}
+
+__device__ __forceinline__ int quantise_one(float v, float s) {
+    return (int)clampf(rintf(__fdiv_rn(v, s)), -127.0f, 127.0f);
 }
 
 __device__ __forceinline__ uint4 ldg_stream_v4(const void *p) {

@@ -47,7 +47,7 @@ bool w4_usable(const tq_qmma_weight_t *w) {
 }
 
 int gemv_prepared_impl(const tq_qmma_weight_t *w, float *d_y, const float *d_residual,
-                       int32_t *dump) {
+                       int32_t *dump, const float *d_x_fused = nullptr) {
     if (!w4_usable(w) || (!d_y && !dump)) return -1;
     ActScratch &s = act_scratch();
     if (s.cap < w->K || !s.q || !s.scale || s.prepared_K < w->K) return -2;
@@ -69,8 +69,34 @@ int gemv_prepared_impl(const tq_qmma_weight_t *w, float *d_y, const float *d_res
     a.splits = choose_gemv_splits(w->M / 16);
     a.serial = 0;
     a.dump = dump;
+    if (d_x_fused) {
+        a.x = d_x_fused;
+        a.sq = s.q; a.sqp = s.qp; a.sscale = s.scale; a.ssum16 = s.sum16; a.ssum32 = s.sum32;
+    }
     launch_gemv(a);
     return 0;
+}
+
+// One launch for x_gemv_w4a8 / _add: the GEMV quantises the row in its prologue (and keeps
+// the prepared scratch current). Rows too long for the kernel's shared memory take the two
+// launches of the reference (x_prepare_gemv_act_s8, then the prepared GEMV).
+int gemv_fused_impl(const tq_qmma_weight_t *w, const float *d_x, const float *d_residual,
+                    float *d_y) {
+    if (!w4_usable(w) || w->K <= 0 || (w->K % 32)) {
+        x_prepare_gemv_act_s8(d_x, w ? w->K : 0);
+        return gemv_prepared_impl(w, d_y, d_residual, nullptr);
+    }
+    ensure_act_scratch(w->K);
+    ActScratch &s = act_scratch();
+    if ((size_t)w->K + (size_t)(w->K / 32) * 8 > 40 * 1024) {
+        x_prepare_gemv_act_s8(d_x, w->K);
+        return gemv_prepared_impl(w, d_y, d_residual, nullptr);
+    }
+    const int before = s.prepared_K;
+    s.prepared_K = w->K;      // the launch below (re)writes the scratch for this K
+    const int rc = gemv_prepared_impl(w, d_y, d_residual, nullptr, d_x);
+    if (rc != 0) s.prepared_K = before;
+    return rc;
 }
 
 // Segment table + per-weight split counts (kernels_dpas.cpp:1343-1367).
@@ -177,15 +203,13 @@ int x_gemv_w4a8_prepared(const tq_qmma_weight_t *w, float *d_y, const float *d_r
 
 int x_gemv_w4a8(const tq_qmma_weight_t *w, const float *d_x, float *d_y) {
     if (!w || !d_x) return -1;
-    x_prepare_gemv_act_s8(d_x, w->K);
-    return gemv_prepared_impl(w, d_y, nullptr, nullptr);
+    return gemv_fused_impl(w, d_x, nullptr, d_y);
 }
 
 int x_gemv_w4a8_add(const tq_qmma_weight_t *w, const float *d_x, const float *d_residual,
                     float *d_y) {
     if (!w || !d_x || !d_residual) return -1;
-    x_prepare_gemv_act_s8(d_x, w->K);
-    return gemv_prepared_impl(w, d_y, d_residual, nullptr);
+    return gemv_fused_impl(w, d_x, d_residual, d_y);
 }
 
 int x_gemv_w4a8_fanout(const tq_qmma_weight_t *const *ws, float *const *ys, int count) {

@@ -53,9 +53,13 @@ __device__ __forceinline__ uint32_t ldg_stream_u16(const uint16_t *p) {
 // (one 128-bit load per lane = one row of a tile), so a warp keeps up to 2 * kU tiles
 // in flight per batch; a batch is loaded completely, scale words included, before
 // it is consumed, and 32 warps per SM overlap each other's batches.
-template <bool SERIAL, bool DUMP>
+// FUSEQ: the fp32 activation row is quantised by every CTA into shared memory (the same
+// per-block rule and code as quant_s8_kernel) after the wait on earlier kernels, instead of
+// being read from the prepared scratch; CTA 0 also writes the scratch.
+template <bool SERIAL, bool DUMP, bool FUSEQ>
 __global__ void __launch_bounds__(kW * 32, 2) gemv_w4a8_kernel(const GemvArgs a) {
     __shared__ float part[kW * 16];
+    extern __shared__ __align__(16) unsigned char dyn[];   // FUSEQ: qp[K], as[K/32], sum32[K/32]
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int h = lane >> 4;
@@ -89,6 +93,42 @@ __global__ void __launch_bounds__(kW * 32, 2) gemv_w4a8_kernel(const GemvArgs a)
     }
     pdl_wait();
 
+    const int8_t *qp = a.qp;
+    const float *asv = a.as;
+    const int32_t *sumv = a.sum32;
+    if (FUSEQ) {
+        int8_t *sqp = reinterpret_cast<int8_t *>(dyn);
+        float *sas = reinterpret_cast<float *>(dyn + a.K);
+        int32_t *ssum = reinterpret_cast<int32_t *>(dyn + a.K + (size_t)Kt * 4);
+        const bool scribe = blockIdx.x == 0;     // keeps the library's prepared scratch current
+        for (int b = warp; b < Kt; b += kW) {
+            const float v = a.x[b * 32 + lane];
+            const float mx = warp_max(fabsf(v));
+            const float sc = (mx > 0.0f) ? __fdiv_rn(mx, 127.0f) : 1.0f;
+            const int qv = quantise_one(v, sc);
+            const int hs = half_sum16(qv);
+            const int other = __shfl_xor_sync(0xffffffffu, hs, 16);
+            sqp[b * 32 + permuted_pos(lane)] = (int8_t)qv;
+            if (lane == 0) {
+                sas[b] = sc;
+                ssum[b] = hs + other;
+            }
+            if (scribe) {
+                a.sq[b * 32 + lane] = (int8_t)qv;
+                a.sqp[b * 32 + permuted_pos(lane)] = (int8_t)qv;
+                if ((lane & 15) == 0) a.ssum16[b * 2 + (lane >> 4)] = hs;
+                if (lane == 0) {
+                    a.sscale[b] = sc;
+                    a.ssum32[b] = hs + other;
+                }
+            }
+        }
+        __syncthreads();
+        qp = sqp;
+        asv = sas;
+        sumv = ssum;
+    }
+
     for (int g = blockIdx.x + gridDim.x * team; g < groups; g += teams) {
         int wi = 0;
         while (wi + 1 < a.count && g >= a.goff[wi + 1]) ++wi;
@@ -118,18 +158,23 @@ __global__ void __launch_bounds__(kW * 32, 2) gemv_w4a8_kernel(const GemvArgs a)
                 float fa = 0.0f, fb = 0.0f;
                 if (valid) {
                     const int kt = kt_begin + idx;
-                    const uint4 e = __ldg(reinterpret_cast<const uint4 *>(a.qp + (size_t)kt * 32));
-                    const uint4 o =
-                        __ldg(reinterpret_cast<const uint4 *>(a.qp + (size_t)kt * 32 + 16));
+                    uint4 e, o;
+                    if (FUSEQ) {
+                        e = *reinterpret_cast<const uint4 *>(qp + (size_t)kt * 32);
+                        o = *reinterpret_cast<const uint4 *>(qp + (size_t)kt * 32 + 16);
+                    } else {
+                        e = __ldg(reinterpret_cast<const uint4 *>(qp + (size_t)kt * 32));
+                        o = __ldg(reinterpret_cast<const uint4 *>(qp + (size_t)kt * 32 + 16));
+                    }
                     const int dp = tile_dot_plus8(wv[u], e, o);
                     int zp;
                     float ws;
                     unpack_scale(sc[u], zp, ws);
-                    const int asum = __ldg(a.sum32 + kt);
+                    const int asum = FUSEQ ? sumv[kt] : __ldg(sumv + kt);
                     if (DUMP) a.dump[((size_t)g * Kt + kt) * 16 + n] = dp - 8 * asum;
                     const float f = (float)(dp - (zp + 8) * asum);
                     fa = __fmul_rn(f, ws);
-                    fb = __ldg(a.as + kt);
+                    fb = FUSEQ ? asv[kt] : __ldg(asv + kt);
                 }
                 if (!SERIAL) {
                     if (valid) acc = fmaf(fa, fb, acc);
@@ -183,11 +228,14 @@ void launch_gemv(const GemvArgs &a) {
     const int tpc = kW / a.splits;
     const int grid = std::min(2 * g_sms, (groups + tpc - 1) / tpc);
     if (a.dump)
-        launch_pdl(gemv_w4a8_kernel<false, true>, dim3(grid), dim3(kW * 32), 0, a);
+        launch_pdl(gemv_w4a8_kernel<false, true, false>, dim3(grid), dim3(kW * 32), 0, a);
     else if (a.serial)
-        launch_pdl(gemv_w4a8_kernel<true, false>, dim3(grid), dim3(kW * 32), 0, a);
+        launch_pdl(gemv_w4a8_kernel<true, false, false>, dim3(grid), dim3(kW * 32), 0, a);
+    else if (a.x && (size_t)a.K + (size_t)(a.K / 32) * 8 <= 40 * 1024)
+        launch_pdl(gemv_w4a8_kernel<false, false, true>, dim3(grid), dim3(kW * 32),
+                   (size_t)a.K + (size_t)(a.K / 32) * 8, a);
     else
-        launch_pdl(gemv_w4a8_kernel<false, false>, dim3(grid), dim3(kW * 32), 0, a);
+        launch_pdl(gemv_w4a8_kernel<false, false, false>, dim3(grid), dim3(kW * 32), 0, a);
     TQ_LAUNCH_CHECK("gemv_w4a8_kernel");
 }
 

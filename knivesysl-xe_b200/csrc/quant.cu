@@ -14,28 +14,6 @@ namespace {
 
 constexpr int kWarpsPerBlock = 8;
 
-__device__ __forceinline__ float warp_max(float v) {
-#pragma unroll
-    for (int off = 16; off >= 1; off >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, off));
-    return v;
-}
-
-// Sum inside each 16-lane half (the K16 sums).
-__device__ __forceinline__ int half_sum16(int v) {
-#pragma unroll
-    for (int off = 8; off >= 1; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
-    return v;
-}
-
-// Position of code k inside the permuted 32-byte tile (even-k codes, then odd-k).
-__device__ __forceinline__ int permuted_pos(int k) {
-    return ((k & 1) << 4) + ((k >> 3) << 2) + ((k & 7) >> 1);
-}
-
-__device__ __forceinline__ int quantise_one(float v, float s) {
-    return (int)clampf(rintf(__fdiv_rn(v, s)), -127.0f, 127.0f);
-}
-
 // Decode staging (x_quantize_act_s8 / x_prepare_gemv_act_s8 / x_silu_mul_quant).
 template <bool SILU>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)

@@ -426,3 +426,32 @@ def test_gathered_gemm_single_rank(lib, pkg, orc, wl):
         assert flags.to_numpy(np.int32)[0] == step + 1
     assert sorted(halves) == [0, block]
     assert lib.tq_last_error() == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,K,ksh", [(1088, 5120, 0), (320, 1024, 1), (64, 256, 0)])
+def test_gemv_fused_quant_prologue(lib, pkg, orc, wl, M, K, ksh):
+    """x_gemv_w4a8 quantises the row inside the GEMV launch: same bits as the oracle, and the
+    prepared scratch it leaves behind serves a following *_prepared call like the reference's
+    x_prepare_gemv_act_s8 would."""
+    codes, scales = wl.random_packed_weight(M, K, seed=3 * M + K, ksh=ksh)
+    w = pkg.PackedWeight(codes, scales, M, K, k64=bool(ksh))
+    x = refgen.shard_check_row(K)
+    y = pkg.DevBuf(M * 4)
+    y.fill(0xA5)
+    assert lib.qwn_x_gemv_w4a8(w.ref, dev(pkg, x).ptr, y.ptr) == 0
+    lib.tq_sync()
+    q, s, sm = orc.quantize_act_s8(x)
+    _, want = orc.gemv_w4a8(codes, scales, M, K, ksh, q, s, sm, fma=1)
+    assert y.to_numpy(np.float32).tobytes() == want.tobytes()
+    dq, ds, dsum = pkg.DevBuf(K), pkg.DevBuf(K // 32 * 4), pkg.DevBuf(K // 16 * 4)
+    assert lib.qwn_dbg_prepared_act(K, dq.ptr, ds.ptr, dsum.ptr) == 0
+    lib.tq_sync()
+    assert np.array_equal(dq.to_numpy(np.int8), q)
+    assert ds.to_numpy(np.float32).tobytes() == s.tobytes()
+    assert np.array_equal(dsum.to_numpy(np.int32), sm)
+    y2 = pkg.DevBuf(M * 4)
+    assert lib.qwn_x_gemv_w4a8_prepared(w.ref, y2.ptr, None) == 0
+    lib.tq_sync()
+    assert y2.to_numpy(np.float32).tobytes() == want.tobytes()
+    assert lib.tq_last_error() == 0
