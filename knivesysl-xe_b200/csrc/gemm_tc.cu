@@ -156,6 +156,7 @@ struct TcParams {
                              // [16 token groups][2 K-chunks][8][16], then kSBytes of
                              // {as0, as1, (float)asum0, (float)asum1} per token pair
     void *y;
+    const float *as_tok;     // per-token scales (PERTOK kernels)
     int *status;
     int M, Kt, ksh, T, Tpad, out_bf16;
 };
@@ -188,11 +189,11 @@ gemm_tc_prepass_kernel(const int8_t *__restrict__ aq, const float *__restrict__ 
         if ((tok & 1) == 0) {
             float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
             if (tok < T) {
-                v.x = as[(size_t)kt * T + tok];
+                v.x = as ? as[(size_t)kt * T + tok] : 0.0f;
                 v.z = (float)asum[(size_t)kt * T + tok];
             }
             if (tok + 1 < T) {
-                v.y = as[(size_t)kt * T + tok + 1];
+                v.y = as ? as[(size_t)kt * T + tok + 1] : 0.0f;
                 v.w = (float)asum[(size_t)kt * T + tok + 1];
             }
             reinterpret_cast<float4 *>(blk + kBBytes)[tl >> 1] = v;
@@ -202,6 +203,10 @@ gemm_tc_prepass_kernel(const int8_t *__restrict__ aq, const float *__restrict__ 
 
 constexpr int kWaitMma = 21, kWaitEpi = 22, kWaitProd = 23;   // status codes of failed waits
 
+// GW = k-tiles accumulated in TMEM before one fp32 promote (1: the reference's arithmetic with
+// a scale per (token, K32); 2: per-token activation scales with K64 weight groups). PERTOK:
+// the activation scale is applied once at the end (y = acc * as_tok).
+template <int GW, bool PERTOK>
 __global__ void __launch_bounds__(kThreads, 1) gemm_w4a8_tc_kernel(const TcParams p) {
     extern __shared__ __align__(1024) unsigned char smem[];
     __shared__ uint64_t bars[2 * kNS + 2 * kNB];   // full[kNS], empty[kNS], accfull[kNB], accempty[kNB]
@@ -271,13 +276,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_w4a8_tc_kernel(const TcParam
 #pragma unroll
             for (int i = 0; i < 32; ++i) acc[i] = 0ull;
             uint32_t scw = __ldg(sc);
-            for (int kt = 0; kt < Kt; ++kt, ++it) {
-                const int b = it % kNB, sl = it % kNS;
-                const uint32_t ph = (uint32_t)(it / kNB) & 1u;
+            for (int kt = 0; kt < Kt; kt += GW, it += GW) {
+                const int ig = it / GW;                       // promote groups done by this CTA
+                const int b = ig % kNB, sl = it % kNS;
+                const uint32_t ph = (uint32_t)(ig / kNB) & 1u;
                 int zp;
                 float ws;
                 unpack_scale(scw, zp, ws);
-                if (kt + 1 < Kt) scw = __ldg(sc + (size_t)((kt + 1) >> p.ksh) * 16);
+                if (kt + GW < Kt) scw = __ldg(sc + (size_t)((kt + GW) >> p.ksh) * 16);
                 const f32x2 ws2 = pack2(ws, ws);
                 const float nzf = (float)(-(zp + 8));
                 const f32x2 nz2 = pack2(nzf, nzf);
@@ -291,6 +297,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_w4a8_tc_kernel(const TcParam
                 const ulonglong2 *sv = reinterpret_cast<const ulonglong2 *>(
                                            smem + (size_t)sl * kSlotBytes + kABytes + kBBytes) +
                                        (chalf >> 1);
+                // second k-tile of the group (GW == 2): only its code sums are needed
+                const int sl1 = (it + GW - 1) % kNS;
+                const ulonglong2 *sv1 = reinterpret_cast<const ulonglong2 *>(
+                                            smem + (size_t)sl1 * kSlotBytes + kABytes + kBBytes) +
+                                        (chalf >> 1);
                 // The four 16-column loads are software-pipelined: the load of chunk q+1 is in
                 // flight while chunk q is re-armed and promoted.
                 uint32_t da[16], db[16];
@@ -300,9 +311,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_w4a8_tc_kernel(const TcParam
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
                         const ulonglong2 s4 = sv[q * 8 + j];      // {as0, as1}, {asum0, asum1}
-                        const f32x2 f = fma2(nz2, s4.y,
+                        f32x2 smf = s4.y;
+                        if (GW == 2) smf = add2(smf, sv1[q * 8 + j].y);   // exact: small integers
+                        const f32x2 f = fma2(nz2, smf,
                                              add2(pack2i((int)d[2 * j], (int)d[2 * j + 1]), neg_magic2));
-                        fma2_acc(acc[q * 8 + j], f, mul2(ws2, s4.x));
+                        if (PERTOK) fma2_acc(acc[q * 8 + j], f, ws2);
+                        else fma2_acc(acc[q * 8 + j], f, mul2(ws2, s4.x));
                     }
                 };
                 tmem_ld16(tcol, da);
@@ -322,7 +336,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_w4a8_tc_kernel(const TcParam
                 __syncwarp();
                 if (lane == 0) {
                     mbar_arrive(accempty0 + b * 8);      // the MMA may overwrite the buffer
-                    mbar_arrive(empty0 + sl * 8);        // the producers may refill the slot
+                    mbar_arrive(empty0 + sl * 8);        // the producers may refill the slot(s)
+                    if (GW == 2) mbar_arrive(empty0 + sl1 * 8);
                 }
             }
             if (*(volatile int *)&dead_s) break;
@@ -332,6 +347,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_w4a8_tc_kernel(const TcParam
                 float v0, v1;
                 unpack2(acc[i], v0, v1);
                 const int tok = tb * kTN + chalf + 2 * i;
+                if (PERTOK) {
+                    if (tok < p.T) v0 = __fmul_rn(v0, __ldg(p.as_tok + tok));
+                    if (tok + 1 < p.T) v1 = __fmul_rn(v1, __ldg(p.as_tok + tok + 1));
+                }
                 if (p.out_bf16) {
                     __nv_bfloat16 *y = static_cast<__nv_bfloat16 *>(p.y);
                     if (tok < p.T) y[(size_t)tok * p.M + row] = __float2bfloat16_rn(v0);
@@ -420,12 +439,15 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_w4a8_tc_kernel(const TcParam
         // ================================ MMA issuer ====================================
         for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
             for (int kt = 0; kt < Kt; ++kt, ++it) {
-                const int b = it % kNB, sl = it % kNS;
+                const int ig = it / GW;
+                const int b = ig % kNB, sl = it % kNS;
                 bool ok = !*(volatile int *)&dead_s &&
                           mbar_wait_bounded(full0 + sl * 8, (uint32_t)(it / kNS) & 1u, p.status, kWaitMma);
-                // ... and the accumulator buffer has been read out and re-armed
-                ok = ok && mbar_wait_bounded(accempty0 + b * 8, ((uint32_t)(it / kNB) & 1u) ^ 1u,
-                                             p.status, kWaitMma);
+                // ... and, for the first k-tile of a group, the accumulator buffer has been
+                // read out and re-armed
+                if (it % GW == 0)
+                    ok = ok && mbar_wait_bounded(accempty0 + b * 8, ((uint32_t)(ig / kNB) & 1u) ^ 1u,
+                                                 p.status, kWaitMma);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) {
                     dead_s = 1;
@@ -436,7 +458,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_w4a8_tc_kernel(const TcParam
                     const uint32_t a_addr = smem_u + sl * kSlotBytes;
                     tc_mma_i8(tmem_base + b * kTN, smem_desc(a_addr), smem_desc(a_addr + kABytes),
                               kIdesc, 1u);
-                    tc_commit(acc0 + b * 8);
+                    if (it % GW == GW - 1) tc_commit(acc0 + b * 8);
                 }
                 __syncwarp();
             }
@@ -461,9 +483,9 @@ int g_tc_sms = 0;
 }  // namespace
 
 int launch_gemm_tc(const GemmTcArgs &a) {
-    // covered: per-block activation scales (the reference's x_gemm_w4a8 arithmetic), rows a
-    // multiple of 128, K64 tier only with an even number of k-tiles
-    if (!a.as || a.as_tok) return -1;
+    // covered: per-block activation scales (the reference's x_gemm_w4a8 arithmetic) or
+    // per-token scales, rows a multiple of 128, K64 tier only with an even number of k-tiles
+    if (!a.as == !a.as_tok) return -1;          // exactly one kind of activation scale
     if (a.M % kTM || a.K % 32 || a.T < 128) return -1;
     const int Kt = a.K / 32;
     if (a.ksh && (Kt & 1)) return -1;
@@ -472,8 +494,12 @@ int launch_gemm_tc(const GemmTcArgs &a) {
         TQ_CHECK(cudaGetDevice(&dev));
         TQ_CHECK(cudaDeviceGetAttribute(&g_tc_sms, cudaDevAttrMultiProcessorCount, dev));
         if (g_tc_sms <= 0) g_tc_sms = 148;
-        TQ_CHECK(cudaFuncSetAttribute(gemm_w4a8_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      kSmemBytes));
+        TQ_CHECK(cudaFuncSetAttribute(gemm_w4a8_tc_kernel<1, false>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+        TQ_CHECK(cudaFuncSetAttribute(gemm_w4a8_tc_kernel<1, true>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+        TQ_CHECK(cudaFuncSetAttribute(gemm_w4a8_tc_kernel<2, true>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
     }
     const int Tpad = (a.T + kTN - 1) / kTN * kTN;
     const size_t ibytes = (size_t)Kt * (Tpad / kTN) * (kBBytes + kSBytes);
@@ -492,7 +518,13 @@ int launch_gemm_tc(const GemmTcArgs &a) {
     p.M = a.M; p.Kt = Kt; p.ksh = a.ksh; p.T = a.T; p.Tpad = Tpad; p.out_bf16 = a.out_bf16;
     const int ntiles = (a.M / kTM) * (Tpad / kTN);
     const int grid = std::min(g_tc_sms, ntiles);
-    launch_pdl(gemm_w4a8_tc_kernel, dim3(grid), dim3(kThreads), (size_t)kSmemBytes, p);
+    p.as_tok = a.as_tok;
+    if (!a.as_tok)
+        launch_pdl(gemm_w4a8_tc_kernel<1, false>, dim3(grid), dim3(kThreads), (size_t)kSmemBytes, p);
+    else if (a.ksh)
+        launch_pdl(gemm_w4a8_tc_kernel<2, true>, dim3(grid), dim3(kThreads), (size_t)kSmemBytes, p);
+    else
+        launch_pdl(gemm_w4a8_tc_kernel<1, true>, dim3(grid), dim3(kThreads), (size_t)kSmemBytes, p);
     TQ_LAUNCH_CHECK("gemm_w4a8_tc_kernel");
     return 0;
 }

@@ -115,7 +115,11 @@ void *tq_dev_alloc(size_t bytes, const char *what) {
 }
 
 void tq_dev_free(void *p) {
-    if (p) TQ_CHECK(cudaFree(p));
+    if (!p) return;
+    // Kernels that were launched with programmatic dependent launch may not have started
+    // yet; wait for the stream explicitly so that nothing in flight can still touch p.
+    if (tq::g_stream) TQ_CHECK(cudaStreamSynchronize(tq::g_stream));
+    TQ_CHECK(cudaFree(p));
 }
 
 void tq_h2d(void *dst, const void *src, size_t bytes) {

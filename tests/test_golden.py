@@ -73,7 +73,8 @@ def test_cuda_matches_golden(g, lib, pkg):
     # decode quantiser
     K = g["q1_x"].size
     dq, ds, dsum = pkg.DevBuf(K), pkg.DevBuf(K // 32 * 4), pkg.DevBuf(K // 16 * 4)
-    lib.qwn_x_quantize_act_s8(dev(g["q1_x"]).ptr, K, dq.ptr, ds.ptr, dsum.ptr)
+    dx = dev(g["q1_x"])       # inputs stay alive until the asynchronous calls have run
+    lib.qwn_x_quantize_act_s8(dx.ptr, K, dq.ptr, ds.ptr, dsum.ptr)
     lib.tq_sync()
     assert same(dq.to_numpy(np.int8), g["q1_q"]) and same(ds.to_numpy(np.float32), g["q1_scale"])
     assert same(dsum.to_numpy(np.int32), g["q1_sum16"])
@@ -81,15 +82,16 @@ def test_cuda_matches_golden(g, lib, pkg):
     for ksh in (0, 1):
         w = pkg.PackedWeight(g[f"gv{ksh}_codes"], g[f"gv{ksh}_scales"], 48, 512, k64=bool(ksh))
         y = pkg.DevBuf(48 * 4)
-        assert lib.qwn_x_gemv_w4a8_add(w.ref, dev(g[f"gv{ksh}_x"]).ptr, dev(g[f"gv{ksh}_res"]).ptr,
-                                       y.ptr) == 0
+        dxv, dres = dev(g[f"gv{ksh}_x"]), dev(g[f"gv{ksh}_res"])
+        assert lib.qwn_x_gemv_w4a8_add(w.ref, dxv.ptr, dres.ptr, y.ptr) == 0
         lib.tq_sync()
         assert same(y.to_numpy(np.float32), g[f"gv{ksh}_y"])
     # segmented GEMM
     T, Kg, M = 32, 512, 64
     n = Kg // 32 * T
     aq, as_, asum = pkg.DevBuf(n * 32), pkg.DevBuf(n * 4), pkg.DevBuf(n * 4)
-    lib.qwn_x_quantize_act_chunk(dev(g["gm_x"]).ptr, Kg, T, aq.ptr, as_.ptr, asum.ptr)
+    dgx = dev(g["gm_x"])
+    lib.qwn_x_quantize_act_chunk(dgx.ptr, Kg, T, aq.ptr, as_.ptr, asum.ptr)
     w = pkg.PackedWeight(g["gm_codes"], g["gm_scales"], M, Kg, k64=True)
     y = pkg.DevBuf(T * M * 4)
     offs = (C.c_int * 3)(*[int(v) for v in g["gm_offsets"]])

@@ -400,7 +400,8 @@ def test_gathered_gemm_single_rank(lib, pkg, orc, wl):
     x = refgen.gemm_check_rows(T, K)
     n = K // 32 * T
     aq, as_, asum = pkg.DevBuf(n * 32), pkg.DevBuf(n * 4), pkg.DevBuf(n * 4)
-    lib.qwn_x_quantize_act_chunk(dev(pkg, x).ptr, K, T, aq.ptr, as_.ptr, asum.ptr)
+    dx = dev(pkg, x)          # stays alive until the asynchronous calls below have run
+    lib.qwn_x_quantize_act_chunk(dx.ptr, K, T, aq.ptr, as_.ptr, asum.ptr)
     ys = [pkg.DevBuf(T * M * 4) for M in Ms]
     assert lib.qwn_x_gemm_w4a8_fanout(pkg.weight_array(ws), pkg.ptr_array(ys), 2, aq.ptr, as_.ptr,
                                       asum.ptr, T, None, 0) == 0
@@ -439,7 +440,8 @@ def test_gemv_fused_quant_prologue(lib, pkg, orc, wl, M, K, ksh):
     x = refgen.shard_check_row(K)
     y = pkg.DevBuf(M * 4)
     y.fill(0xA5)
-    assert lib.qwn_x_gemv_w4a8(w.ref, dev(pkg, x).ptr, y.ptr) == 0
+    dx = dev(pkg, x)
+    assert lib.qwn_x_gemv_w4a8(w.ref, dx.ptr, y.ptr) == 0
     lib.tq_sync()
     q, s, sm = orc.quantize_act_s8(x)
     _, want = orc.gemv_w4a8(codes, scales, M, K, ksh, q, s, sm, fma=1)
@@ -454,4 +456,40 @@ def test_gemv_fused_quant_prologue(lib, pkg, orc, wl, M, K, ksh):
     assert lib.qwn_x_gemv_w4a8_prepared(w.ref, y2.ptr, None) == 0
     lib.tq_sync()
     assert y2.to_numpy(np.float32).tobytes() == want.tobytes()
+    assert lib.tq_last_error() == 0
+
+
+def _bf16_rne(a):
+    """fp32 -> bfloat16 bits, round to nearest even (what __float2bfloat16_rn does)."""
+    u = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    r = ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+    return r
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,K,ksh,T,bf16", [(2048, 512, 1, 128, False), (1024, 1024, 0, 256, False),
+                                            (2048, 256, 1, 136, False), (1024, 512, 1, 128, True)])
+def test_gemm_pertoken_tcgen05(lib, pkg, orc, wl, M, K, ksh, T, bf16):
+    """Per-token activation scales: the int32 dot runs over a whole weight-scale group in
+    TMEM (two k-tiles under K64) before one fp32 promote; y = acc * as_tok. Bit-identical to
+    the oracle's restatement of that formula."""
+    codes, scales = wl.random_packed_weight(M, K, seed=M + K + T, ksh=ksh)
+    w = pkg.PackedWeight(codes, scales, M, K, k64=bool(ksh))
+    x = wl.activations_normal(T, K, seed=9, outlier_frac=0.01)
+    n = K // 32 * T
+    aq, as_, asum, at = pkg.DevBuf(n * 32), pkg.DevBuf(n * 4), pkg.DevBuf(n * 4), pkg.DevBuf(T * 4)
+    dx = dev(pkg, x)
+    lib.qwn_x_quantize_act_chunk_pertoken(dx.ptr, K, T, aq.ptr, as_.ptr, asum.ptr, at.ptr)
+    y = pkg.DevBuf(T * M * (2 if bf16 else 4))
+    y.fill(0xA5)
+    assert lib.qwn_x_gemm_w4a8_pertoken(w.ref, aq.ptr, at.ptr, asum.ptr, y.ptr, T, int(bf16)) == 0
+    lib.tq_sync()
+    oq, os_, osm = orc.quantize_act_chunk(x, per_token=True)
+    as_tok = os_.reshape(K // 32, T)[0].copy()
+    rc, want = orc.gemm_w4a8_pertoken(codes, scales, M, K, ksh, oq, as_tok, osm, T)
+    assert rc == 0
+    if bf16:
+        assert np.array_equal(y.to_numpy(np.uint16), _bf16_rne(want).reshape(-1))
+    else:
+        assert y.to_numpy(np.float32).tobytes() == np.ascontiguousarray(want).tobytes()
     assert lib.tq_last_error() == 0
