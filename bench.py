@@ -116,11 +116,11 @@ def run_reference(args, rank):
     t0 = time.perf_counter()
     cpu_pass(orc, host_w, aq, as_, asum, rows=1088)
     t_probe = (time.perf_counter() - t0) * 16.0
-    budget = 150.0
+    max_seconds = 150.0
     frac_rows = N_EACH
     total = args.steps + args.warmup
-    if t_probe * total > budget:
-        frac_rows = max(16, int(N_EACH * budget / (t_probe * total)) // 16 * 16)
+    if t_probe * total > max_seconds:
+        frac_rows = max(16, int(N_EACH * max_seconds / (t_probe * total)) // 16 * 16)
     for _ in range(args.warmup):
         orc.quantize_act_chunk(x, per_token=True)
         cpu_pass(orc, host_w, aq, as_, asum, rows=frac_rows)
