@@ -5,9 +5,9 @@
 // 32 B scale line) is read exactly once; activations (32 B per k-tile) stay in L1/L2.
 //
 // Mapping. One warp owns one (row-group, K-split) task at a time, as the reference's
-// sub-group does; the kernel is persistent (two CTAs of 16 warps per SM). A 256-byte tile is 16 rows x 16 B, so a HALF-warp reads one tile with one
-// 128-bit load per lane and the two halves of a warp walk the even and the odd tiles
-// of the split. That is exactly the reference's two-accumulator order (acc0 takes the
+// sub-group does; the kernel is persistent (two CTAs of 16 warps per SM). A 256-byte tile
+// is 16 rows x 16 B, so a HALF-warp reads one tile with one 128-bit load per lane and the
+// two halves of a warp walk the even and the odd tiles of the split. That is exactly the reference's two-accumulator order (acc0 takes the
 // even offsets from kt_begin, acc1 the odd ones, leftover to acc0), so each lane keeps
 // ONE accumulator and acc0+acc1 is a single shuffle. The fan-out order (one serial
 // accumulator) passes the odd half's product terms to the even half every pair.
@@ -26,80 +26,146 @@ namespace tq {
 
 namespace {
 
-constexpr int kU = 5;     // 128-bit weight loads in flight per lane (one batch); more spills at 64 registers
 constexpr int kW = 16;    // warps per CTA
+constexpr int kST = 8;    // tiles per ring stage
+constexpr int kStageBytes = kST * 256 + kST * 32;   // codes, then one 32-byte scale line per tile
 
+__device__ __forceinline__ uint4 lds_v4(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds_u16(uint32_t addr) {
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+    return v;
+}
+
+// High nibbles in place: ((w & 0xF0F0F0F0) ^ 0x80808080) = four unsigned bytes 16 * (q + 8).
+__device__ __forceinline__ uint32_t nib_hi_plus8_x16(uint32_t w) {
+    uint32_t d;
+    asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(d) : "r"(w), "r"(0xF0F0F0F0u), "r"(0x80808080u));
+    return d;
+}
+__device__ __forceinline__ int dp4a_u8s8(uint32_t ua, uint32_t sb, int c) {
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(ua), "r"(sb), "r"(c));
+    return d;
+}
+
+// sum over the tile row of (q + 8) * a. The odd-k codes stay in the high nibbles and are
+// multiplied as 16 * (q + 8): that accumulator is an exact multiple of 16.
 __device__ __forceinline__ int tile_dot_plus8(const uint4 &w, const uint4 &e, const uint4 &o) {
-    int d = 0;
+    int dlo = 0, dhi = 0;
     const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
     const uint32_t ee[4] = {e.x, e.y, e.z, e.w};
     const uint32_t oo[4] = {o.x, o.y, o.z, o.w};
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-        d = __dp4a((int)nib_plus8(ww[j]), (int)ee[j], d);
-        d = __dp4a((int)nib_plus8(ww[j] >> 4), (int)oo[j], d);
+        dlo = __dp4a((int)nib_plus8(ww[j]), (int)ee[j], dlo);
+        dhi = dp4a_u8s8(nib_hi_plus8_x16(ww[j]), oo[j], dhi);
     }
-    return d;
-}
-
-__device__ __forceinline__ uint32_t ldg_stream_u16(const uint16_t *p) {
-    uint16_t v;
-    asm volatile("ld.global.nc.L1::no_allocate.u16 %0, [%1];" : "=h"(v) : "l"(p));
-    return v;
+    return dlo + (dhi >> 4);
 }
 
 // Persistent kernel: a team of S warps owns one 16-row group at a time (warp s = K-split
-// s) and walks the row-groups team, team + teams, ... Each half-warp reads whole tiles
-// (one 128-bit load per lane = one row of a tile), so a warp keeps up to 2 * kU tiles
-// in flight per batch; a batch is loaded completely, scale words included, before
-// it is consumed, and 32 warps per SM overlap each other's batches.
+// s), walks the row-groups team, team + teams, ... and adds its partial sums in split order
+// through shared memory behind a named barrier.
+// Every warp streams its tiles through a private ring of NS shared-memory stages (kST tiles
+// and their scale lines each) filled with cp.async, so that NS-1 stages (2 KiB each) per
+// warp are in flight while one is consumed, and the ring keeps running across the warp's
+// units. In a stage the two half-warps take the even and the odd tiles (one 128-bit
+// shared-memory load per lane = one row of a tile).
 // FUSEQ: the fp32 activation row is quantised by every CTA into shared memory (the same
 // per-block rule and code as quant_s8_kernel) after the wait on earlier kernels, instead of
 // being read from the prepared scratch; CTA 0 also writes the scratch.
-template <bool SERIAL, bool DUMP, bool FUSEQ>
+template <bool SERIAL, bool DUMP, bool FUSEQ, int NS>
 __global__ void __launch_bounds__(kW * 32, 2) gemv_w4a8_kernel(const GemvArgs a) {
     __shared__ float part[kW * 16];
-    extern __shared__ __align__(16) unsigned char dyn[];   // FUSEQ: qp[K], as[K/32], sum32[K/32]
+    // ring[kW][NS][kStageBytes], then (FUSEQ) qp[K], as[K/32], sum32[K/32]
+    extern __shared__ __align__(16) unsigned char dyn[];
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int h = lane >> 4;
     const int n = lane & 15;
     const int S = a.splits;
-    const int tpc = kW / S;                       // teams per CTA
+    const int tpc = kW / S;                            // teams per CTA
     const int team = warp / S;
     const int split = warp - team * S;
+    const int g0 = blockIdx.x + gridDim.x * team;
+    const int teams = gridDim.x * tpc;                 // row-group stride of this warp
     const int Kt = a.K >> 5;
     const int Ktg = Kt >> a.ksh;
     const int groups = a.goff[a.count];
-    const int teams = gridDim.x * tpc;
     const int kt_begin = Kt * split / S;
     const int cnt = Kt * (split + 1) / S - kt_begin;
-    // tiles of this half-warp: offsets h, h+2, ... inside the split; balanced batches
-    const int nper = (cnt + 1) >> 1;
-    const int nb = (nper + kU - 1) / kU;
-    const int ub = nb ? (nper + nb - 1) / nb : 0;
+    unsigned char *ring = dyn + (size_t)warp * NS * kStageBytes;
+    const uint32_t ring_s = smem_u32(ring);
+    const uint64_t pol = l2_policy_evict_first();
+
+    // Producer side of the ring: the next (row-group, tile offset) to fetch. The source
+    // pointers of the row-group are kept per lane and only move by a stage per call.
+    int pg = g0, pi0 = 0;
+    uint32_t pdst = ring_s;
+    const uint8_t *psrc = nullptr;        // this lane's first 16-byte piece of the next stage
+    const uint16_t *pscl = nullptr;       // scale line 0 of the row-group, this lane's half
+    auto producer_group = [&]() {
+        if (pg < groups) {
+            int wi = 0;
+            while (wi + 1 < a.count && pg >= a.goff[wi + 1]) ++wi;
+            const int lg = pg - a.goff[wi];
+            psrc = a.codes[wi] + ((size_t)lg * Kt + kt_begin) * 256u + lane * 16;
+            pscl = a.scales[wi] + (size_t)lg * Ktg * 16u + (lane & 1) * 8;
+        }
+    };
+    producer_group();
+    auto issue_next = [&]() {
+        if (pg < groups && cnt > 0) {
+            const int left = cnt - pi0;
+            if (left >= kST) {
+#pragma unroll
+                for (int p = 0; p < kST / 2; ++p)
+                    cp_async16(pdst + lane * 16 + p * 512, psrc + p * 512, pol);
+                if (lane < 2 * kST)
+                    cp_async16(pdst + kST * 256 + lane * 16,
+                               pscl + (size_t)((kt_begin + pi0 + (lane >> 1)) >> a.ksh) * 16u, pol);
+            } else {
+#pragma unroll
+                for (int p = 0; p < kST / 2; ++p)
+                    if (lane + 32 * p < left * 16)
+                        cp_async16(pdst + lane * 16 + p * 512, psrc + p * 512, pol);
+                if (lane < 2 * left)
+                    cp_async16(pdst + kST * 256 + lane * 16,
+                               pscl + (size_t)((kt_begin + pi0 + (lane >> 1)) >> a.ksh) * 16u, pol);
+            }
+            pi0 += kST;
+            psrc += kST * 256;
+            if (pi0 >= cnt) {
+                pi0 = 0;
+                pg += teams;
+                producer_group();
+            }
+            pdst = (pdst + kStageBytes == ring_s + NS * kStageBytes) ? ring_s : pdst + kStageBytes;
+        }
+        cp_async_commit();
+    };
 
     pdl_trigger();
-    {
-        // Before waiting for earlier kernels: pull this warp's first weight span into L2.
-        const int g = blockIdx.x + gridDim.x * team;
-        if (g < groups && cnt > 0) {
-            int wi = 0;
-            while (wi + 1 < a.count && g >= a.goff[wi + 1]) ++wi;
-            const int lg = g - a.goff[wi];
-            const uint8_t *p = a.codes[wi] + ((size_t)lg * Kt + kt_begin) * 256u;
-            for (int line = lane; line < cnt * 2; line += 32) prefetch_l2(p + line * 128);
-        }
-    }
+    // Weights do not depend on earlier kernels: the ring starts filling before the wait.
+#pragma unroll
+    for (int i = 0; i < NS - 1; ++i) issue_next();
     pdl_wait();
 
     const int8_t *qp = a.qp;
     const float *asv = a.as;
     const int32_t *sumv = a.sum32;
     if (FUSEQ) {
-        int8_t *sqp = reinterpret_cast<int8_t *>(dyn);
-        float *sas = reinterpret_cast<float *>(dyn + a.K);
-        int32_t *ssum = reinterpret_cast<int32_t *>(dyn + a.K + (size_t)Kt * 4);
+        unsigned char *qbase = dyn + (size_t)kW * NS * kStageBytes;
+        int8_t *sqp = reinterpret_cast<int8_t *>(qbase);
+        float *sas = reinterpret_cast<float *>(qbase + a.K);
+        int32_t *ssum = reinterpret_cast<int32_t *>(qbase + a.K + (size_t)Kt * 4);
         const bool scribe = blockIdx.x == 0;     // keeps the library's prepared scratch current
         for (int b = warp; b < Kt; b += kW) {
             const float v = a.x[b * 32 + lane];
@@ -129,65 +195,87 @@ __global__ void __launch_bounds__(kW * 32, 2) gemv_w4a8_kernel(const GemvArgs a)
         sumv = ssum;
     }
 
-    for (int g = blockIdx.x + gridDim.x * team; g < groups; g += teams) {
+    // Consumer side. One stage: the half-warp h takes tiles h, h + 2, ... of the stage. A
+    // pair step handles tile 2u + h on both half-warps; its shared-memory addresses are
+    // constant offsets from the per-stage bases.
+    uint32_t cst = ring_s;
+    const uint32_t lane_w = h * 256 + n * 16;              // this lane's row in tile h
+    const uint32_t lane_s = kST * 256 + h * 32 + n * 2;    // and its scale word
+    auto pair_step = [&](uint32_t wl, uint32_t sl, const int8_t *ap, const int32_t *smp,
+                         const float *asp, int32_t *dmp, bool valid, bool odd_valid,
+                         float &acc) {
+        float fa = 0.0f, fb = 0.0f;
+        if (valid) {
+            const uint4 wv = lds_v4(wl);
+            const uint32_t sc = lds_u16(sl);
+            uint4 e, o;
+            int asum;
+            if (FUSEQ) {
+                e = *reinterpret_cast<const uint4 *>(ap);
+                o = *reinterpret_cast<const uint4 *>(ap + 16);
+                asum = *smp;
+                fb = *asp;
+            } else {
+                e = __ldg(reinterpret_cast<const uint4 *>(ap));
+                o = __ldg(reinterpret_cast<const uint4 *>(ap + 16));
+                asum = __ldg(smp);
+                fb = __ldg(asp);
+            }
+            const int dp = tile_dot_plus8(wv, e, o);
+            int zp;
+            float ws;
+            unpack_scale(sc, zp, ws);
+            if (DUMP) *dmp = dp - 8 * asum;
+            const float f = (float)(dp - (zp + 8) * asum);
+            fa = __fmul_rn(f, ws);
+        }
+        if (!SERIAL) {
+            if (valid) acc = fmaf(fa, fb, acc);
+        } else {
+            // pair (even tile on h == 0, odd tile on h == 1), added in tile order
+            const float oa = __shfl_down_sync(0xffffffffu, fa, 16);
+            const float ob = __shfl_down_sync(0xffffffffu, fb, 16);
+            if (h == 0) {
+                if (valid) acc = fmaf(fa, fb, acc);
+                if (odd_valid) acc = fmaf(oa, ob, acc);
+            }
+        }
+    };
+
+    for (int g = g0; g < groups; g += teams) {
         int wi = 0;
         while (wi + 1 < a.count && g >= a.goff[wi + 1]) ++wi;
         const int lg = g - a.goff[wi];
-        const uint8_t *bbase =
-            a.codes[wi] + ((size_t)lg * Kt + kt_begin) * 256u + (size_t)n * 16u;
-        const uint16_t *sbase = a.scales[wi] + (size_t)lg * Ktg * 16u + n;
+        const int8_t *ap = qp + (size_t)(kt_begin + h) * 32;
+        const int32_t *smp = sumv + kt_begin + h;
+        const float *asp = asv + kt_begin + h;
+        int32_t *dmp = DUMP ? a.dump + ((size_t)g * Kt + kt_begin + h) * 16 + n : nullptr;
 
         float acc = 0.0f;
-        for (int b = 0; b < nb; ++b) {
-            const int i0 = b * ub;
-            uint4 wv[kU];
-            uint32_t sc[kU];
+        for (int left = cnt; left > 0; left -= kST) {
+            cp_async_wait<NS - 2>();
+            __syncwarp();                 // the stage is complete; the slot read last is free
+            issue_next();
+            const uint32_t wl = cst + lane_w, sl = cst + lane_s;
+            if (left >= kST) {
 #pragma unroll
-            for (int u = 0; u < kU; ++u) {
-                const int idx = 2 * (i0 + u) + h;
-                if (u < ub && idx < cnt) {
-                    wv[u] = ldg_stream_v4(bbase + (size_t)idx * 256u);
-                    sc[u] = ldg_stream_u16(sbase + (size_t)((kt_begin + idx) >> a.ksh) * 16u);
-                }
+                for (int u = 0; u < kST / 2; ++u)
+                    pair_step(wl + u * 512, sl + u * 64, ap + u * 64, smp + 2 * u, asp + 2 * u,
+                              DUMP ? dmp + u * 32 : nullptr, true, true, acc);
+            } else {
+                // last, short stage of the split: a plain loop, only its last pair can be half
+                const int np = (left + 1) >> 1;
+#pragma unroll 1
+                for (int u = 0; u < np; ++u)
+                    pair_step(wl + u * 512, sl + u * 64, ap + u * 64, smp + 2 * u, asp + 2 * u,
+                              DUMP ? dmp + u * 32 : nullptr, 2 * u + h < left, 2 * u + 1 < left,
+                              acc);
             }
-#pragma unroll
-            for (int u = 0; u < kU; ++u) {
-                if (u >= ub) break;
-                const int idx = 2 * (i0 + u) + h;
-                const bool valid = idx < cnt;
-                float fa = 0.0f, fb = 0.0f;
-                if (valid) {
-                    const int kt = kt_begin + idx;
-                    uint4 e, o;
-                    if (FUSEQ) {
-                        e = *reinterpret_cast<const uint4 *>(qp + (size_t)kt * 32);
-                        o = *reinterpret_cast<const uint4 *>(qp + (size_t)kt * 32 + 16);
-                    } else {
-                        e = __ldg(reinterpret_cast<const uint4 *>(qp + (size_t)kt * 32));
-                        o = __ldg(reinterpret_cast<const uint4 *>(qp + (size_t)kt * 32 + 16));
-                    }
-                    const int dp = tile_dot_plus8(wv[u], e, o);
-                    int zp;
-                    float ws;
-                    unpack_scale(sc[u], zp, ws);
-                    const int asum = FUSEQ ? sumv[kt] : __ldg(sumv + kt);
-                    if (DUMP) a.dump[((size_t)g * Kt + kt) * 16 + n] = dp - 8 * asum;
-                    const float f = (float)(dp - (zp + 8) * asum);
-                    fa = __fmul_rn(f, ws);
-                    fb = FUSEQ ? asv[kt] : __ldg(asv + kt);
-                }
-                if (!SERIAL) {
-                    if (valid) acc = fmaf(fa, fb, acc);
-                } else {
-                    // pair (even tile on h == 0, odd tile on h == 1), added in tile order
-                    const float oa = __shfl_down_sync(0xffffffffu, fa, 16);
-                    const float ob = __shfl_down_sync(0xffffffffu, fb, 16);
-                    if (h == 0) {
-                        if (valid) acc = fmaf(fa, fb, acc);
-                        if (idx + 1 < cnt) acc = fmaf(oa, ob, acc);
-                    }
-                }
-            }
+            cst = (cst + kStageBytes == ring_s + NS * kStageBytes) ? ring_s : cst + kStageBytes;
+            ap += kST * 32;
+            smp += kST;
+            asp += kST;
+            if (DUMP) dmp += kST * 16;
         }
         if (DUMP) continue;
         if (!SERIAL) acc = __fadd_rn(acc, __shfl_down_sync(0xffffffffu, acc, 16));
@@ -225,17 +313,42 @@ void launch_gemv(const GemvArgs &a) {
         TQ_CHECK(cudaDeviceGetAttribute(&g_sms, cudaDevAttrMultiProcessorCount, dev));
         if (g_sms <= 0) g_sms = 148;
     }
+    if (a.splits > kW || (kW % a.splits)) {
+        fprintf(stderr, "launch_gemv: %d splits do not divide the %d warps of a CTA\n", a.splits, kW);
+        note_error(cudaErrorInvalidValue, "launch_gemv");
+        return;
+    }
     const int tpc = kW / a.splits;
     const int grid = std::min(2 * g_sms, (groups + tpc - 1) / tpc);
+    constexpr size_t kRing3 = (size_t)kW * 3 * kStageBytes, kRing2 = (size_t)kW * 2 * kStageBytes;
+    constexpr size_t kPerCta = (227 * 1024) / 2 - 1024 - kW * 16 * 4;   // two CTAs per SM
+    const size_t qbytes = (size_t)a.K + (size_t)(a.K / 32) * 8;
+    static bool attr = false;
+    if (!attr) {
+        TQ_CHECK(cudaFuncSetAttribute(gemv_w4a8_kernel<false, true, false, 3>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRing3));
+        TQ_CHECK(cudaFuncSetAttribute(gemv_w4a8_kernel<true, false, false, 3>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRing3));
+        TQ_CHECK(cudaFuncSetAttribute(gemv_w4a8_kernel<false, false, false, 3>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRing3));
+        TQ_CHECK(cudaFuncSetAttribute(gemv_w4a8_kernel<false, false, true, 3>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPerCta));
+        TQ_CHECK(cudaFuncSetAttribute(gemv_w4a8_kernel<false, false, true, 2>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPerCta));
+        attr = true;
+    }
     if (a.dump)
-        launch_pdl(gemv_w4a8_kernel<false, true, false>, dim3(grid), dim3(kW * 32), 0, a);
+        launch_pdl(gemv_w4a8_kernel<false, true, false, 3>, dim3(grid), dim3(kW * 32), kRing3, a);
     else if (a.serial)
-        launch_pdl(gemv_w4a8_kernel<true, false, false>, dim3(grid), dim3(kW * 32), 0, a);
-    else if (a.x && (size_t)a.K + (size_t)(a.K / 32) * 8 <= 40 * 1024)
-        launch_pdl(gemv_w4a8_kernel<false, false, true>, dim3(grid), dim3(kW * 32),
-                   (size_t)a.K + (size_t)(a.K / 32) * 8, a);
+        launch_pdl(gemv_w4a8_kernel<true, false, false, 3>, dim3(grid), dim3(kW * 32), kRing3, a);
+    else if (a.x && kRing3 + qbytes <= kPerCta)
+        launch_pdl(gemv_w4a8_kernel<false, false, true, 3>, dim3(grid), dim3(kW * 32),
+                   kRing3 + qbytes, a);
+    else if (a.x && kRing2 + qbytes <= kPerCta)
+        launch_pdl(gemv_w4a8_kernel<false, false, true, 2>, dim3(grid), dim3(kW * 32),
+                   kRing2 + qbytes, a);
     else
-        launch_pdl(gemv_w4a8_kernel<false, false, false>, dim3(grid), dim3(kW * 32), 0, a);
+        launch_pdl(gemv_w4a8_kernel<false, false, false, 3>, dim3(grid), dim3(kW * 32), kRing3, a);
     TQ_LAUNCH_CHECK("gemv_w4a8_kernel");
 }
 
