@@ -394,7 +394,7 @@ def main():
                                (" + all-gather" if world > 1 else "")},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "peak_source": f"{peak_kind} copy bandwidth",
-                         "kernel": "gemm_w4a8_stream_kernel", "us_per_launch": k_ms * 1e3,
+                         "kernel": "gemm_w4a8_ring_kernel", "us_per_launch": k_ms * 1e3,
                          "algorithmic_bytes_per_launch": algo_bytes,
                          "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH},
             "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": int(x.nbytes),

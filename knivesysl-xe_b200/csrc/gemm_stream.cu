@@ -1,5 +1,7 @@
 // gemm_stream.cu — batched W4A8 GEMM for decode batches (T = 8..64 tokens, one segment)
-// on sm_100a: a persistent kernel in which every warp streams packed weights from HBM
+// on sm_100a. Two persistent kernels: gemm_w4a8_ring_kernel (T = 8: 32 warps per SM, per-warp
+// cp.async ring in shared memory, further down) and gemm_w4a8_stream_kernel (T = 16..64 and
+// the int32 dump used by the tests), in which every warp streams packed weights from HBM
 // straight into registers, a chunk of eight k-tiles ahead of the math.
 //
 // Replaces x_gemm_w4a8's split path (xpu/src/kernels_dpas.cpp:1379-1489) for the shapes
@@ -30,10 +32,11 @@
 //    the S partials in the order 0..S-1 starting from 0.0f and stores y: the reference's
 //    summation order, independent of arrival order. An unsplit weight stores its
 //    accumulator untouched.
-// (A shared-memory ring fed by cp.async, and before it by 1-D bulk TMA copies, was measured
-// first: parity-identical, but every weight byte then crosses the shared-memory data path
-// twice more, and with the scale and activation reads that path saturates near 45% of HBM
-// bandwidth; one warp also sustains only about two bulk copies in flight.)
+// (With 16 warps per SM a shared-memory ring fed by cp.async, and before it by 1-D bulk TMA
+// copies, measured slower than the register queue: every weight byte crosses the
+// shared-memory data path twice more, and one warp sustains only about two bulk copies in
+// flight. The ring pays off once it frees enough registers for 32 warps per SM: the T = 8
+// kernel below.)
 #include "stream.cuh"
 
 #include <algorithm>
@@ -420,6 +423,285 @@ gemm_w4a8_stream_kernel(const GemmArgs a, float *__restrict__ part, int *__restr
     }
 }
 
+// ---------------------------------------------------------------------------------------
+// Ring kernel for T = 8: 32 warps per SM at 64 registers. The register queue above leaves
+// 16 warps per SM, each of which spends most of its time waiting on its own dependency
+// chains; here every warp streams its tiles through a private two-stage shared-memory ring
+// filled with cp.async (16 bytes per lane, eight tiles and their scale lines per stage) and
+// reads MMA A fragments back with ldmatrix, so the registers hold only one tile pair and
+// twice as many warps share an SM. Scale words are read raw from the stage (one 32-byte line
+// per tile) and unpacked by the lanes that use them. Task mapping, staged activations, split
+// reduction, stores and the fused all-gather are those of the kernel above.
+constexpr int kRW = 32;                              // warps per CTA
+constexpr int kRST = 8;                              // tiles per ring stage (4 and 6 measured slower)
+constexpr int kRStage = kRST * 256 + kRST * 32;      // codes, then one scale line per tile
+constexpr int kRNS = 2;                              // ring stages per warp
+
+__device__ __forceinline__ uint2 lds_v2(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ ulonglong2 lds_v2u64(uint32_t addr) {
+    ulonglong2 v;
+    asm volatile("ld.shared.v2.u64 {%0,%1}, [%2];" : "=l"(v.x), "=l"(v.y) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds_u16(uint32_t addr) {
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+    return v;
+}
+
+// Packed scale word -> fp32 scale and (float)(z + 8): the 4-bit two's-complement zero point
+// with its top bit flipped is z + 8 in [0, 15].
+__device__ __forceinline__ void scale_pair(uint32_t packed, float &ws, float &z8) {
+    ws = __half2float(__ushort_as_half((unsigned short)(packed & 0xFFF0u)));
+    z8 = (float)(int)((packed ^ 8u) & 15u);
+}
+
+template <bool PAIR>   // PAIR: K64 tier and even split starts - tiles 2j, 2j+1 share a scale line
+__global__ void __launch_bounds__(kRW * 32, 1)
+gemm_w4a8_ring_kernel(const GemmArgs a, float *__restrict__ part, int *__restrict__ count) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int r = lane >> 2;
+    const int c = lane & 3;
+    const int S = a.max_splits;
+    const int split = blockIdx.x % S;
+    const int cta_i = blockIdx.x / S;
+    const int nctas = (gridDim.x - split + S - 1) / S;
+
+    const int groups_all = a.goff[a.count];
+    const int tgid = cta_i + nctas * warp;
+    const int tstride = nctas * kRW;
+    const int Kt = a.K >> 5;
+    const int ksh = a.ksh;
+    const int Ktg = Kt >> ksh;
+    const int kt_begin = Kt * split / S;
+    const int cnt = Kt * (split + 1) / S - kt_begin;
+
+    unsigned char *ring = smem + (size_t)warp * kRNS * kRStage;
+    const uint32_t ring_s = smem_u32(ring);
+    unsigned char *act = smem + (size_t)kRW * kRNS * kRStage;
+    const uint32_t act_s = smem_u32(act);
+    float *xpose = reinterpret_cast<float *>(act + (size_t)cnt * kActTileBytes) + warp * 128;
+    const uint64_t pol = l2_policy_evict_first();
+
+    // ---- producer: next (row-group, tile offset) to fetch --------------------------------
+    int pg = tgid, pi0 = 0;
+    uint32_t pdst = ring_s;
+    const uint8_t *psrc = nullptr;
+    const uint16_t *pscl = nullptr;
+    auto producer_group = [&]() {
+        if (pg < groups_all) {
+            int wi = 0;
+            while (wi + 1 < a.count && pg >= a.goff[wi + 1]) ++wi;
+            const int lg = pg - a.goff[wi];
+            psrc = a.codes[wi] + ((size_t)lg * Kt + kt_begin) * 256u + lane * 16;
+            pscl = a.scales[wi] + (size_t)lg * Ktg * 16u + (lane & 1) * 8;
+        }
+    };
+    producer_group();
+    auto issue_next = [&]() {
+        if (pg < groups_all && cnt > 0) {
+            const int left = cnt - pi0;
+            const uint16_t *sl = pscl + (size_t)((kt_begin + pi0 + (lane >> 1)) >> ksh) * 16u;
+            if (left >= kRST) {
+#pragma unroll
+                for (int p = 0; p < kRST / 2; ++p)
+                    cp_async16(pdst + lane * 16 + p * 512, psrc + p * 512, pol);
+                if (lane < 2 * kRST) cp_async16(pdst + kRST * 256 + lane * 16, sl, pol);
+            } else {
+#pragma unroll
+                for (int p = 0; p < kRST / 2; ++p)
+                    if (lane + 32 * p < left * 16)
+                        cp_async16(pdst + lane * 16 + p * 512, psrc + p * 512, pol);
+                if (lane < 2 * left) cp_async16(pdst + kRST * 256 + lane * 16, sl, pol);
+            }
+            pi0 += kRST;
+            psrc += kRST * 256;
+            if (pi0 >= cnt) {
+                pi0 = 0;
+                pg += tstride;
+                producer_group();
+            }
+            pdst = (pdst + kRStage == ring_s + kRNS * kRStage) ? ring_s : pdst + kRStage;
+        }
+        cp_async_commit();
+    };
+
+    pdl_trigger();
+#pragma unroll
+    for (int i = 0; i < kRNS - 1; ++i) issue_next();
+    // Everything above reads only packed weights; what follows depends on earlier kernels.
+    pdl_wait();
+
+    // Stage this split's activations (layout of the register-queue kernel for T = 8, but the
+    // code sums are stored negated: the tile loop multiplies them by z + 8 >= 0).
+    {
+        const int items = cnt * 32;
+        for (int i = threadIdx.x; i < items; i += kRW * 32) {
+            const int kl = i >> 5;
+            const int rem = i & 31;
+            const uint2 bb = __ldg(reinterpret_cast<const uint2 *>(
+                a.aq + (size_t)(kt_begin + kl) * 8 * 32 + (size_t)rem * 8));
+            uint2 o;
+            o.x = __byte_perm(bb.x, bb.y, 0x6420);
+            o.y = __byte_perm(bb.x, bb.y, 0x7531);
+            *reinterpret_cast<uint2 *>(act + (size_t)kl * kActTileBytes + rem * 8) = o;
+        }
+        const int pairs = cnt * 4;
+        for (int i = threadIdx.x; i < pairs; i += kRW * 32) {
+            const int kl = i >> 2;
+            const int rem = i & 3;
+            const size_t src = (size_t)(kt_begin + kl) * 8 + (size_t)rem * 2;
+            const float2 as2 = __ldg(reinterpret_cast<const float2 *>(a.as + src));
+            const int2 sm2 = __ldg(reinterpret_cast<const int2 *>(a.asum + src));
+            *reinterpret_cast<float4 *>(act + (size_t)kl * kActTileBytes + 256 + rem * 16) =
+                make_float4(as2.x, as2.y, -(float)sm2.x, -(float)sm2.y);
+        }
+        __syncthreads();
+    }
+
+    const f32x2 neg_magic2 = pack2(-kMagicF, -kMagicF);
+    int cmagic[4];
+    make_const_quad(cmagic, kMagicBits);
+    uint32_t cst = ring_s;
+    const uint32_t lane_a = (lane >> 4) * 256 + (lane & 15) * 16;   // ldmatrix row address
+    const uint32_t lane_s = kRST * 256 + r * 2;                     // scale word of row r
+    const uint32_t lane_b = act_s + lane * 8;
+    const uint32_t lane_v = act_s + 256 + c * 16;
+
+    f32x2 acc01 = 0ull, acc23 = 0ull;
+    // one tile: A words of rows r, r+8; {ws, z+8} of those rows; activations at bb / vb
+    auto tile = [&](uint32_t w_lo, uint32_t w_hi, float ws0, float nz0, float ws1, float nz1,
+                    uint32_t bb_addr, uint32_t vb_addr) {
+        const uint32_t A0 = nib_plus8(w_lo), A1 = nib_plus8(w_hi);
+        const uint32_t A2 = nib_plus8(w_lo >> 4), A3 = nib_plus8(w_hi >> 4);
+        const uint2 bb = lds_v2(bb_addr);
+        const ulonglong2 av = lds_v2u64(vb_addr);
+        int d[4];
+        mma_s8_c(d, A0, A1, A2, A3, bb.x, bb.y, cmagic);
+        // (float)(d - z*asum) = (z+8) * (-asum) + d', exact: all integers below 2^24
+        const f32x2 f01 = fma2(pack2(nz0, nz0), av.y, add2(pack2i(d[0], d[1]), neg_magic2));
+        const f32x2 f23 = fma2(pack2(nz1, nz1), av.y, add2(pack2i(d[2], d[3]), neg_magic2));
+        fma2_acc(acc01, f01, mul2(pack2(ws0, ws0), av.x));
+        fma2_acc(acc23, f23, mul2(pack2(ws1, ws1), av.x));
+    };
+    // tiles 2j, 2j+1 of the stage at `cst`; activations of the first one at offset kl_off
+    auto tile_pair = [&](uint32_t ab, uint32_t sb, uint32_t bbase, uint32_t vbase, bool second) {
+        uint32_t w0, w1, w2, w3;
+        ldmatrix_x4(ab, w0, w1, w2, w3);
+        float ws0, ws1, nz0, nz1;
+        scale_pair(lds_u16(sb), ws0, nz0);
+        scale_pair(lds_u16(sb + 16), ws1, nz1);
+        tile(w0, w1, ws0, nz0, ws1, nz1, bbase, vbase);
+        if (second) {
+            if (!PAIR) {
+                scale_pair(lds_u16(sb + 32), ws0, nz0);
+                scale_pair(lds_u16(sb + 48), ws1, nz1);
+            }
+            tile(w2, w3, ws0, nz0, ws1, nz1, bbase + kActTileBytes, vbase + kActTileBytes);
+        }
+    };
+
+    for (int g0 = tgid; g0 < groups_all; g0 += tstride) {
+        int wi = 0;
+        while (wi + 1 < a.count && g0 >= a.goff[wi + 1]) ++wi;
+        const int lg = g0 - a.goff[wi];
+        const int M = a.M[wi];
+        acc01 = acc23 = 0ull;
+        uint32_t bbase = lane_b, vbase = lane_v;
+        for (int left = cnt; left > 0; left -= kRST) {
+            cp_async_wait<kRNS - 2>();
+            __syncwarp();                 // the stage is complete; the other slot is free
+            issue_next();
+            const uint32_t ab = cst + lane_a, sb = cst + lane_s;
+            if (left >= kRST) {
+#pragma unroll
+                for (int j = 0; j < kRST / 2; ++j)
+                    tile_pair(ab + j * 512, sb + j * 64, bbase + j * 2 * kActTileBytes,
+                              vbase + j * 2 * kActTileBytes, true);
+            } else {
+                // last, short stage of the split: a plain loop, only its last pair can be half
+                const int np = (left + 1) >> 1;
+#pragma unroll 1
+                for (int j = 0; j < np; ++j)
+                    tile_pair(ab + j * 512, sb + j * 64, bbase + j * 2 * kActTileBytes,
+                              vbase + j * 2 * kActTileBytes, 2 * j + 1 < left);
+            }
+            bbase += kRST * kActTileBytes;
+            vbase += kRST * kActTileBytes;
+            cst = (cst + kRStage == ring_s + kRNS * kRStage) ? ring_s : cst + kRStage;
+        }
+        float out[4];
+        unpack2(acc01, out[0], out[1]);
+        unpack2(acc23, out[2], out[3]);
+        if (S > 1) {
+            // partial of this split -> scratch; the last split to arrive sums 0..S-1
+            float *pp = part + ((size_t)g0 * S + split) * 128 + lane;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) pp[k * 32] = out[k];
+            __threadfence();
+            __syncwarp();
+            int old = 0;
+            if (lane == 0) old = atomicAdd(count + g0, 1);
+            old = __shfl_sync(0xffffffffu, old, 0);
+            if (old != S - 1) continue;
+            __threadfence();
+            const float *base = part + (size_t)g0 * S * 128 + lane;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                float sum = 0.0f;
+                for (int s2 = 0; s2 < S; ++s2)
+                    sum = __fadd_rn(sum, __ldcg(base + (size_t)s2 * 128 + k * 32));
+                out[k] = sum;
+            }
+            if (lane == 0) count[g0] = 0;   // ready for the next launch
+        }
+        const size_t row = (size_t)lg * 16 + r;
+        if (!a.npeer) {
+            float *y = a.y[wi];
+            const size_t tok = (size_t)2 * c;
+            y[tok * M + row] = out[0];
+            y[(tok + 1) * M + row] = out[1];
+            y[tok * M + row + 8] = out[2];
+            y[(tok + 1) * M + row + 8] = out[3];
+        } else {
+            // Fused all-gather: transpose the 16 x 8 tile so that a lane holds four consecutive
+            // rows of one token and every peer gets 16-byte stores (64-byte runs).
+            __syncwarp();
+            xpose[(2 * c) * 16 + r] = out[0];
+            xpose[(2 * c + 1) * 16 + r] = out[1];
+            xpose[(2 * c) * 16 + r + 8] = out[2];
+            xpose[(2 * c + 1) * 16 + r + 8] = out[3];
+            __syncwarp();
+            const float4 v = *reinterpret_cast<const float4 *>(xpose + lane * 4);
+            const size_t off = (size_t)(lane >> 2) * M + (size_t)lg * 16 + (lane & 3) * 4;
+            for (int pi = 0; pi < a.npeer; ++pi)
+                *reinterpret_cast<float4 *>(a.ypeer[pi][wi] + off) = v;
+        }
+    }
+    if (a.npeer) {
+        // Publish (see the kernel above): one device fence per CTA, one system fence per launch.
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            __threadfence();
+            const int prev = atomicAdd(a.done, 1);
+            if (prev == (int)gridDim.x - 1) {
+                *a.done = 0;
+                __threadfence_system();
+                for (int pi = 0; pi < a.npeer; ++pi)
+                    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(a.peer_flag[pi]),
+                                 "r"(a.step)
+                                 : "memory");
+            }
+        }
+    }
+}
+
 int g_num_sms = 0;
 constexpr size_t kSmemLimit = 227 * 1024;
 
@@ -535,7 +817,45 @@ int window_groups(const GemmArgs &a) {
     return (ntg % 2 == 0) ? 2 : 1;
 }
 
+// The ring kernel takes T = 8 calls whose split activations fit beside the rings.
+bool launch_ring(const GemmArgs &a) {
+    if (a.T != 8 || a.dump) return false;
+    if (!g_num_sms) {
+        int dev = 0;
+        TQ_CHECK(cudaGetDevice(&dev));
+        TQ_CHECK(cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev));
+        if (g_num_sms <= 0) g_num_sms = 148;
+    }
+    const int Kt = a.K >> 5, S = a.max_splits;
+    const int groups = a.goff[a.count];
+    const size_t smem = (size_t)kRW * kRNS * kRStage + (size_t)((Kt + S - 1) / S) * kActTileBytes +
+                        (a.npeer ? (size_t)kRW * 512 : 0);
+    if (smem > kSmemLimit || S > g_num_sms) return false;
+    bool pair = a.ksh != 0;
+    for (int s2 = 0; s2 < S; ++s2) pair = pair && ((Kt * s2 / S) % 2 == 0);
+    static bool attr_set = false;
+    if (!attr_set) {
+        TQ_CHECK(cudaFuncSetAttribute(gemm_w4a8_ring_kernel<false>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit));
+        TQ_CHECK(cudaFuncSetAttribute(gemm_w4a8_ring_kernel<true>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit));
+        attr_set = true;
+    }
+    if (S > 1) ensure_scratch((size_t)groups * S * 128, groups);
+    const long most = (long)groups * S;
+    const int grid = (int)std::max<long>(S, std::min<long>(g_num_sms - g_num_sms % S, most));
+    if (pair)
+        launch_pdl(gemm_w4a8_ring_kernel<true>, dim3(grid), dim3(kRW * 32), smem, a, g_scratch.part,
+                   g_scratch.count);
+    else
+        launch_pdl(gemm_w4a8_ring_kernel<false>, dim3(grid), dim3(kRW * 32), smem, a, g_scratch.part,
+                   g_scratch.count);
+    TQ_LAUNCH_CHECK("gemm_w4a8_ring_kernel");
+    return true;
+}
+
 void launch_gemm_stream(const GemmArgs &a) {
+    if (launch_ring(a)) return;
     switch (window_groups(a)) {
         case 1: launch_ntg<1>(a); break;
         case 2: launch_ntg<2>(a); break;
