@@ -135,7 +135,7 @@ def run_reference(args, rank):
     out = {
         "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
-        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "s8xs4->s32",
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "s8xs4->s32",
         "data": "synthetic",
         "config": {"workload": "cfg2: fused gate+up, K64 tier, T=8, K=5120, N=2x17408 (CPU oracle)"},
         "cpu_baseline": {"value": val, "unit": UNIT, "cores": orc.num_threads(), "kind": "port",
@@ -154,6 +154,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--rotate", type=int, default=4)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
+                    help="N > 1: every rank holds a cfg2-sized column shard of an N-times wider "
+                         "projection (weak, default), or cfg2 itself is cut into N shards (strong)")
     ap.add_argument("--exchange", default="fused", choices=["fused", "nccl"],
                     help="N > 1: all-gather by peer stores from the GEMM epilogue (fused) or by NCCL")
     args = ap.parse_args()
@@ -180,8 +183,12 @@ def main():
         assert lib.tq_comm_init(idbuf, rank, world) == 0
 
     # ---- inputs (same seeds on every rank; a rank keeps only its column shard) ----------
-    host_w = [wl.make_weight_w4(N_EACH, K, seed=11 + i, group=GROUP) for i in range(2)]
-    n_shard = N_EACH // world
+    weak = world > 1 and args.scaling == "weak"
+    # weak: this rank's shard is a whole cfg2-sized weight pair of its own (seeded by rank), i.e.
+    # the column shard of a projection world times as wide; strong: cfg2 cut with x_w4_shard
+    host_w = [wl.make_weight_w4(N_EACH, K, seed=11 + i + (100 * rank if weak else 0), group=GROUP)
+              for i in range(2)]
+    n_shard = N_EACH if weak else N_EACH // world
     copies = []                      # rotate x [gate, up] PackedWeight (this rank's shard)
     for c in range(args.rotate):
         pair = []
@@ -189,7 +196,7 @@ def main():
             cc = np.roll(codes.reshape(N_EACH // 16, -1), c, axis=0).reshape(-1)
             ss = np.roll(scales.reshape(N_EACH // 16, -1), c, axis=0).reshape(-1)
             full = pkg.PackedWeight(cc, ss, N_EACH, K, k64=True)
-            if world > 1:
+            if world > 1 and not weak:
                 sh = pkg.TqWeight()
                 assert lib.qwn_x_w4_shard(C.byref(sh), full.ref, rank, world, 0, None, 0) == 0
                 full.codes.free()
@@ -298,7 +305,8 @@ def main():
         tt = torch.tensor([ms], dtype=torch.float64)
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
         ms = float(tt.item())
-    full_weight_bytes = 2 * wl.weight_bytes(N_EACH, K, GROUP)
+    # weight bytes the whole job streams per step (all ranks)
+    full_weight_bytes = 2 * wl.weight_bytes(N_EACH, K, GROUP) * (world if weak else 1)
     value = full_weight_bytes * args.steps / (ms * 1e-3) / 1e9
 
     # ---- dominant kernel alone (this rank's shard), for the roofline -----------------------
@@ -321,16 +329,34 @@ def main():
     # ---- end to end through the C-ABI with host buffers ----------------------------------
     hx = lib.tq_host_alloc_pinned(x.nbytes)
     C.memmove(hx, x.ctypes.data, x.nbytes)
-    out_bytes = (world * block * 4 if world > 1 else ycat.nbytes)
-    hy = lib.tq_host_alloc_pinned(out_bytes)
+    # strong: every rank reads the whole gathered result back; weak: a rank reads back its own
+    # slice of the gathered buffer, so the host receives the (world times larger) result once
+    out_bytes = (block * 4 if weak else world * block * 4 if world > 1 else ycat.nbytes)
+    hy = [lib.tq_host_alloc_pinned(out_bytes) for _ in range(2)]
+    # Two output buffers: the read-back of step i (second stream) overlaps step i+1, and the
+    # library stream waits for it only before step i+2 overwrites the same buffer.
+    ycat2 = pkg.DevBuf(block * 4)
+    yarr2 = (C.c_void_p * 2)(ycat2.ptr, ycat2.ptr + T * n_shard * 4)
+    tickets = [-1, -1]
 
     def e2e_step(i):
+        # N > 1: this rank's next flag tells its peers that they may overwrite the half it is
+        # still reading back, so there the previous read-back must finish before the next step
+        b = i & 1 if world == 1 else 0
+        if tickets[b] >= 0:
+            lib.tq_stream_wait_copy(tickets[b])
         lib.tq_h2d_async(dx.ptr, hx, x.nbytes)
-        step(i)
-        if world > 1:
-            lib.tq_d2h_async(hy, gathered.ptr + half_off.value * 4, out_bytes)
+        if world == 1:
+            stage()
+            rc = lib.qwn_x_gemm_w4a8_fanout(warr[i % args.rotate], yarr2 if b else yarr, 2, aq.ptr,
+                                            as_.ptr, asum.ptr, T, None, 0)
+            assert rc == 0, rc
+            src = (ycat2 if b else ycat).ptr
         else:
-            lib.tq_d2h_async(hy, ycat.ptr, ycat.nbytes)
+            step(i)
+            src = gathered.ptr + ((half_off.value if fused else 0) + (rank * block if weak else 0)) * 4
+        tickets[b] = lib.tq_d2h_overlapped(hy[i & 1], src, out_bytes)
+        assert tickets[b] >= 0
 
     e_iters = max(min(args.steps, 2000), 50)
     for i in range(args.warmup):
@@ -381,22 +407,26 @@ def main():
         out = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "s8xs4->s32, fp32 out",
+            "scaling": "weak" if (weak or world == 1) else "strong", "vs_baseline": None,
+            "dtype": "s8xs4->s32, fp32 out",
             "data": "synthetic",
             "config": {"workload": "cfg2: batched decode fused gate+up, K64 scale tier, T=8, K=5120, "
-                                   "N=2x17408, int8 per-token activations",
+                                   "N=2x17408, int8 per-token activations" +
+                                   (f"; one cfg2-sized column shard per GPU (N={world}x2x17408 in all)"
+                                    if weak else ""),
                        "parallelism": f"column shard tp{world}" + (
                            "" if world == 1 else " + all-gather by peer stores from the GEMM epilogue"
                            if fused else " + NCCL all-gather"),
                        "l2": f"inputs larger than L2: {args.rotate} rotating weight copies, "
-                             f"{args.rotate * full_weight_bytes // world / 1e6:.0f} MB per GPU",
+                             f"{args.rotate * shard_weight / 1e6:.0f} MB per GPU",
                        "step": "per-token staging (1 launch) + fused gate|up GEMM" +
                                (" + all-gather" if world > 1 else "")},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "peak_source": f"{peak_kind} copy bandwidth",
                          "kernel": "gemm_w4a8_ring_kernel", "us_per_launch": k_ms * 1e3,
                          "algorithmic_bytes_per_launch": algo_bytes,
-                         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH},
+                         # the capture is of the whole-cfg2 launch; a shard's traffic scales with it
+                         "traffic": int(NCU_TRAFFIC_BYTES_PER_LAUNCH * algo_bytes / 95_864_832)},
             "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": int(x.nbytes),
                     "d2h_bytes_per_step": int(out_bytes), "steps": e_iters,
                     "us_per_step": e_s / e_iters * 1e6},

@@ -76,6 +76,12 @@ void tq_host_free_pinned(void *p);
 void tq_h2d_async(void *dst, const void *src, size_t bytes);
 void tq_d2h_async(void *dst, const void *src, size_t bytes);
 void tq_d2d_async(void *dst, const void *src, size_t bytes);
+/* Read-back that overlaps the calls that follow: the copy runs on a second stream once
+ * everything queued so far has run, and returns a ticket (0..15, reused in turn; -1 on
+ * failure). The library stream does not wait for it; before a later call may overwrite src,
+ * pass the ticket to tq_stream_wait_copy(). tq_sync() also waits for these copies. */
+int tq_d2h_overlapped(void *dst, const void *src, size_t bytes);
+void tq_stream_wait_copy(int ticket);
 /* CUDA events on tq_stream() for device-side timing. */
 void *tq_event_create(void);
 void tq_event_destroy(void *ev);

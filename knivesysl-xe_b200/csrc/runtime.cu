@@ -141,8 +141,17 @@ void tq_dev_fill(void *dst, int byte, size_t bytes) {
     TQ_CHECK(cudaMemsetAsync(dst, byte, bytes, tq::stream()));
 }
 
+namespace tq {
+constexpr int kCopyTickets = 16;
+cudaStream_t g_copy_stream = nullptr;
+cudaEvent_t g_copy_ready = nullptr;                 // library stream -> copy stream
+cudaEvent_t g_copy_done[kCopyTickets] = {};         // copy stream -> library stream
+unsigned g_copy_next = 0;
+}  // namespace tq
+
 void tq_sync(void) {
     TQ_CHECK(cudaStreamSynchronize(tq::stream()));
+    if (tq::g_copy_stream) TQ_CHECK(cudaStreamSynchronize(tq::g_copy_stream));
     if (tq::g_status_dev && !tq::g_sticky_error) {
         int st = 0;
         if (cudaMemcpy(&st, tq::g_status_dev, sizeof(int), cudaMemcpyDeviceToHost) == cudaSuccess &&
@@ -172,6 +181,32 @@ void tq_h2d_async(void *dst, const void *src, size_t bytes) {
 
 void tq_d2h_async(void *dst, const void *src, size_t bytes) {
     TQ_CHECK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, tq::stream()));
+}
+
+// ---- read-back that overlaps the next call ------------------------------------------
+// A second stream carries device-to-host copies: the copy waits for what the library stream
+// has queued so far, and the library stream only waits for a copy when the caller says so
+// (before it lets a kernel overwrite the copied buffer), through a ticket.
+
+int tq_d2h_overlapped(void *dst, const void *src, size_t bytes) {
+    cudaStream_t main = tq::stream();
+    if (!tq::g_copy_stream) {
+        TQ_CHECK(cudaStreamCreateWithFlags(&tq::g_copy_stream, cudaStreamNonBlocking));
+        TQ_CHECK(cudaEventCreateWithFlags(&tq::g_copy_ready, cudaEventDisableTiming));
+        for (auto &e : tq::g_copy_done) TQ_CHECK(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    }
+    if (!tq::g_copy_stream) return -1;
+    const int ticket = (int)(tq::g_copy_next++ % tq::kCopyTickets);
+    TQ_CHECK(cudaEventRecord(tq::g_copy_ready, main));
+    TQ_CHECK(cudaStreamWaitEvent(tq::g_copy_stream, tq::g_copy_ready, 0));
+    TQ_CHECK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, tq::g_copy_stream));
+    TQ_CHECK(cudaEventRecord(tq::g_copy_done[ticket], tq::g_copy_stream));
+    return ticket;
+}
+
+void tq_stream_wait_copy(int ticket) {
+    if (ticket < 0 || ticket >= tq::kCopyTickets || !tq::g_copy_stream) return;
+    TQ_CHECK(cudaStreamWaitEvent(tq::stream(), tq::g_copy_done[ticket], 0));
 }
 
 void tq_d2d_async(void *dst, const void *src, size_t bytes) {

@@ -306,6 +306,9 @@ GEMM_CASES = [
     # five token groups, 8 splits of 4..5 tiles
     (1600, 1056, 0, 40, None),
     (1088, 5120, 1, 8, None),
+    # T = 8 ring kernel: K64 splits that start on odd k-tiles (a tile pair then has two scale
+    # lines), K32 with full stages plus a one-tile last stage, 17-tile splits
+    (4800, 2112, 1, 8, None), (320, 2112, 0, 8, None), (1088, 1056, 0, 8, None),
     # tcgen05 path: unsplit, T >= 128, rows a multiple of 128; ragged token tail; segments
     (2048, 512, 0, 128, None), (1024, 1024, 1, 256, None), (2048, 256, 0, 136, None),
     (2048, 512, 1, 256, [0, 128, 256]),
