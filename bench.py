@@ -268,18 +268,21 @@ def main():
                 assert lib.tq_comm_allgather(ycat.ptr, gathered.ptr, ycat.nbytes) == 0
 
     if fused:
-        # the fused gather must deliver exactly what NCCL delivers
+        # the fused gather must deliver exactly what NCCL delivers, on every weight copy and
+        # on both halves of the gathered buffer
         stage()
-        gemm(0)
-        assert lib.tq_comm_allgather(ycat.ptr, gathered.ptr, ycat.nbytes) == 0
-        lib.tq_sync()
-        ref = gathered.to_numpy(np.float32)[: world * block].copy()
-        dist.barrier()
-        gemm_gathered(0)
-        lib.tq_sync()
-        dist.barrier()
-        got = gathered.to_numpy(np.float32)[half_off.value: half_off.value + world * block]
-        assert got.tobytes() == ref.tobytes(), "fused all-gather differs from NCCL"
+        for i in range(2 * args.rotate):
+            gemm(i)
+            assert lib.tq_comm_allgather(ycat.ptr, gathered.ptr, ycat.nbytes) == 0
+            lib.tq_sync()
+            ref = gathered.to_numpy(np.float32)[: world * block].copy()
+            dist.barrier()
+            gemm_gathered(i)
+            lib.tq_sync()
+            dist.barrier()
+            got = gathered.to_numpy(np.float32)[half_off.value: half_off.value + world * block]
+            assert got.tobytes() == ref.tobytes(), f"fused all-gather differs from NCCL (step {i})"
+            dist.barrier()
 
     def barrier():
         lib.tq_sync()
@@ -321,6 +324,18 @@ def main():
     lib.tq_event_record(ev[1])
     lib.tq_sync()
     k_ms = lib.tq_event_elapsed_ms(ev[0], ev[1]) / k_iters
+    if fused:
+        # diagnostic (stderr): the gathered GEMM with its wait kernel, back to back
+        barrier()
+        lib.tq_event_record(ev[0])
+        for i in range(k_iters):
+            gemm_gathered(i)
+        lib.tq_event_record(ev[1])
+        barrier()
+        g_ms = lib.tq_event_elapsed_ms(ev[0], ev[1]) / k_iters
+        if rank == 0:
+            print(f"[bench] GEMM alone {k_ms * 1e3:.2f} us; gathered GEMM + wait {g_ms * 1e3:.2f} us; "
+                  f"step {ms / args.steps * 1e3:.2f} us", file=sys.stderr)
     shard_weight = 2 * wl.weight_bytes(n_shard, K, GROUP)
     algo_bytes = shard_weight + T * K + nblk * 8 + block * 4
     achieved = algo_bytes / (k_ms * 1e-3) / 1e9

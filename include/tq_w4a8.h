@@ -223,10 +223,12 @@ int tq_comm_allgather(const void *d_send, void *d_recv, size_t bytes_per_rank);
  * tq_comm_ipc_export / _open map them into the other ranks' processes (64-byte CUDA IPC
  * handles, exchanged by the host program), tq_comm_gather_setup registers the world's
  * pointers. qwn_x_gemm_w4a8_fanout_gathered then writes this rank's outputs
- * [count][T][M_i] into block `rank` of EVERY rank's buffer from the GEMM epilogue and
- * publishes a step flag; tq_comm_gather_wait enqueues a bounded wait for all ranks' blocks
- * (status 10031 from tq_last_error() if a rank never publishes). All ranks must make the
- * same sequence of gathered calls. Returns -21 when the shape is not a decode batch. */
+ * [count][T][M_i] into block `rank` of EVERY rank's buffer from the GEMM epilogue; a one-warp
+ * kernel behind the GEMM publishes a step flag to every rank and waits (bounded; status 10031
+ * from tq_last_error() if a rank never publishes) for all ranks' flags, so work queued after
+ * the call finds the whole gathered block. tq_comm_gather_wait is kept for callers of the
+ * earlier two-call form and enqueues nothing. All ranks must make the same sequence of
+ * gathered calls. Returns -21 when the shape is not a decode batch. */
 int tq_comm_ipc_export(void *d_ptr, void *handle64);
 void *tq_comm_ipc_open(const void *handle64);
 void tq_comm_ipc_close(void *p);

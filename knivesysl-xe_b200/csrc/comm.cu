@@ -28,17 +28,28 @@ ncclComm_t g_comm = nullptr;
 int g_rank = 0, g_world = 1;
 tq::GatherState g_gather;
 
-// One warp waits until the flag words written by all source ranks have reached `step`
-// (bounded: two seconds of wall clock, then status 31 and a normal return).
-__global__ void gather_wait_kernel(const int *flags, int world, int step, int *status) {
+// Publishes a step and waits for everybody's. Runs after the GEMM whose epilogue stored this
+// rank's slice on every rank (griddepcontrol.wait returns once that kernel has completed and
+// its stores, the peer stores included, have been performed): lane p stores the step number
+// into this rank's flag word on rank p behind a system-scope fence, then waits until rank p's
+// flag word here has reached the step (bounded: two seconds of wall clock, then status 31 and
+// a normal return). Whatever follows on the stream therefore finds every rank's slice in
+// the gathered buffer.
+struct PeerFlags {
+    int *p[8];
+};
+__global__ void gather_publish_wait_kernel(PeerFlags f, const int *mine, int world, int step,
+                                           int *status) {
     tq::pdl_trigger();
     tq::pdl_wait();
     const int p = threadIdx.x;
     if (p >= world) return;
+    __threadfence_system();
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(f.p[p]), "r"(step) : "memory");
     unsigned long long t0 = 0;
     for (unsigned polls = 0;; ++polls) {
         int v;
-        asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(flags + p) : "memory");
+        asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(mine + p) : "memory");
         if (v - step >= 0) return;
         __nanosleep(100);
         if ((polls & 255u) == 255u) {
@@ -86,6 +97,15 @@ int nccl_fail(ncclResult_t r, const char *where) {
 
 namespace tq {
 GatherState &gather_state() { return g_gather; }
+
+void launch_gather_publish(int step) {
+    GatherState &g = g_gather;
+    PeerFlags f{};
+    for (int p = 0; p < g.world; ++p) f.p[p] = g.flag[p] + g.rank;
+    launch_pdl(gather_publish_wait_kernel, dim3(1), dim3(32), 0, f, (const int *)g.flag[g.rank],
+               g.world, step, device_status_word());
+    note_error(cudaGetLastError(), "gather_publish_wait_kernel");
+}
 }  // namespace tq
 
 extern "C" {
@@ -171,25 +191,15 @@ int tq_comm_gather_setup(void *const *bufs, void *const *flags, int world, int r
         g.buf[p] = static_cast<float *>(bufs[p]);
         g.flag[p] = static_cast<int *>(flags[p]);
     }
-    if (!g.done) {
-        g.done = static_cast<int *>(tq_dev_alloc(sizeof(int), "gather.done"));
-        tq_dev_zero(g.done, sizeof(int));
-    }
     g.world = world;
     g.rank = rank;
     g.step = 0;
     return 0;
 }
 
-// Enqueues the wait for the slices of every rank of the last gathered call.
-int tq_comm_gather_wait(void) {
-    tq::GatherState &g = g_gather;
-    if (g.world < 1) return -3;
-    tq::launch_pdl(gather_wait_kernel, dim3(1), dim3(32), 0, (const int *)g.flag[g.rank], g.world,
-                   g.step, tq::device_status_word());
-    tq::note_error(cudaGetLastError(), "gather_wait_kernel");
-    return 0;
-}
+// The wait for every rank's slice is part of the gathered GEMM call (its second, one-warp
+// kernel); this entry point remains for callers written against the two-call form.
+int tq_comm_gather_wait(void) { return g_gather.world < 1 ? -3 : 0; }
 
 int tq_comm_rank(void) { return g_rank; }
 int tq_comm_world(void) { return g_world; }

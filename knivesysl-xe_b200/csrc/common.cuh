@@ -48,10 +48,12 @@ struct GatherState {
     int world = 0, rank = 0;
     float *buf[8] = {};       // rank p's gathered buffer
     int *flag[8] = {};        // rank p's flag array (one int per source rank)
-    int *done = nullptr;      // local CTA counter
     int step = 0;             // last published step
 };
 GatherState &gather_state();
+// One-warp kernel behind the GEMM on the library stream: stores `step` into this rank's flag
+// word on every rank once the GEMM has completed, then waits for every rank's flag.
+void launch_gather_publish(int step);
 
 // ---- split heuristics (dispatch.cu) --------------------------------------------
 int choose_gemv_splits(int groups);
@@ -116,14 +118,11 @@ struct GemmArgs {
     GemmSegments seg[4];     // per weight (each keeps the splits it would get alone)
     int max_splits;
     int32_t *dump;           // non-null: write int32 tile dots (single weight)
-    // Fused all-gather of a column shard (streaming kernel only): when npeer > 0 the
-    // output of weight i goes to ypeer[p][i] for every rank p instead of y[i], and the last
-    // CTA to finish stores `step` into peer_flag[p] of every rank (see comm.cu).
+    // Fused all-gather of a column shard (streaming kernels only): when npeer > 0 the
+    // output of weight i goes to ypeer[p][i] for every rank p instead of y[i]; the step flag
+    // is published by launch_gather_publish (comm.cu) after the GEMM.
     int npeer;
     float *ypeer[8][4];
-    int *peer_flag[8];
-    int *done;               // CTA arrival counter of this launch (zero between launches)
-    int step;
 };
 void launch_gemm_mma(const GemmArgs &a);
 // gemm_stream.cu (decode batches: one segment, T <= 64, uniform split count <= 8)

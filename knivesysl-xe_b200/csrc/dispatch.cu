@@ -366,13 +366,11 @@ int x_gemm_w4a8_fanout_gathered(const tq_qmma_weight_t *const *ws, int count, co
     a.aq = d_aq; a.as = d_as; a.asum = d_asum;
     a.K = K; a.ksh = ksh; a.T = T;
     a.npeer = g.world;
-    for (int p = 0; p < g.world; ++p) a.peer_flag[p] = g.flag[p] + g.rank;
-    a.done = g.done;
-    a.step = g.step + 1;
     if (!gemm_stream_covers(a)) return -21;
     g.step += 1;
     if (half_offset_floats) *half_offset_floats = (size_t)(g.step & 1) * g.world * block;
     launch_gemm_stream(a);
+    launch_gather_publish(g.step);
     return 0;
 }
 

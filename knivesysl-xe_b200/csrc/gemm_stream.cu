@@ -31,7 +31,11 @@
 //    small global scratch, and the warp that arrives last (a counter per row-group) adds
 //    the S partials in the order 0..S-1 starting from 0.0f and stores y: the reference's
 //    summation order, independent of arrival order. An unsplit weight stores its
-//    accumulator untouched.
+//    accumulator untouched;
+//  * with the fused all-gather (a.npeer > 0) the epilogue stores the tile into the gathered
+//    buffer of every rank; the step flag that tells the peers is stored by a one-warp kernel
+//    launched right after this one (comm.cu), i.e. at the kernel boundary, so no CTA of
+//    this kernel pays for a fence.
 // (With 16 warps per SM a shared-memory ring fed by cp.async, and before it by 1-D bulk TMA
 // copies, measured slower than the register queue: every weight byte crosses the
 // shared-memory data path twice more, and one warp sustains only about two bulk copies in
@@ -402,25 +406,6 @@ gemm_w4a8_stream_kernel(const GemmArgs a, float *__restrict__ part, int *__restr
             }
         }
     }
-    if (!DUMP && a.npeer) {
-        // Publish. The CTA barrier orders every thread's peer stores before thread 0, whose
-        // device-scope fence + counter increment hands them to the last CTA of the grid;
-        // that CTA alone pays the system-scope fence and stores the step number into this
-        // rank's flag word on every rank (one fence per launch, not one per thread).
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            __threadfence();
-            const int prev = atomicAdd(a.done, 1);
-            if (prev == (int)gridDim.x - 1) {
-                *a.done = 0;                       // ready for the next launch
-                __threadfence_system();
-                for (int pi = 0; pi < a.npeer; ++pi)
-                    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(a.peer_flag[pi]),
-                                 "r"(a.step)
-                                 : "memory");
-            }
-        }
-    }
 }
 
 // ---------------------------------------------------------------------------------------
@@ -682,22 +667,6 @@ gemm_w4a8_ring_kernel(const GemmArgs a, float *__restrict__ part, int *__restric
             const size_t off = (size_t)(lane >> 2) * M + (size_t)lg * 16 + (lane & 3) * 4;
             for (int pi = 0; pi < a.npeer; ++pi)
                 *reinterpret_cast<float4 *>(a.ypeer[pi][wi] + off) = v;
-        }
-    }
-    if (a.npeer) {
-        // Publish (see the kernel above): one device fence per CTA, one system fence per launch.
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            __threadfence();
-            const int prev = atomicAdd(a.done, 1);
-            if (prev == (int)gridDim.x - 1) {
-                *a.done = 0;
-                __threadfence_system();
-                for (int pi = 0; pi < a.npeer; ++pi)
-                    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(a.peer_flag[pi]),
-                                 "r"(a.step)
-                                 : "memory");
-            }
         }
     }
 }
