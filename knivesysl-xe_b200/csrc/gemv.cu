@@ -28,7 +28,17 @@ namespace {
 
 constexpr int kW = 16;    // warps per CTA
 constexpr int kST = 8;    // tiles per ring stage
-constexpr int kStageBytes = kST * 256 + kST * 32;   // codes, then one 32-byte scale line per tile
+constexpr int kWeightBytes = kST * 256 + kST * 32;  // codes, then one 32-byte scale line per tile
+// A stage also carries its tiles' activations unless the kernel quantised the row itself:
+// 32 bytes of codes (even-k half, odd-k half) per tile, then the int32 sums, then the scales.
+constexpr int kActCodes = kWeightBytes, kActSums = kActCodes + kST * 32, kActScales = kActSums + kST * 4;
+constexpr int kActBytes = kST * 32 + kST * 8;
+__host__ __device__ constexpr int stage_bytes(bool fuseq) { return kWeightBytes + (fuseq ? 0 : kActBytes); }
+__device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
 
 __device__ __forceinline__ uint4 lds_v4(uint32_t addr) {
     uint4 v;
@@ -73,10 +83,11 @@ __device__ __forceinline__ int tile_dot_plus8(const uint4 &w, const uint4 &e, co
 // Persistent kernel: a team of S warps owns one 16-row group at a time (warp s = K-split
 // s), walks the row-groups team, team + teams, ... and adds its partial sums in split order
 // through shared memory behind a named barrier.
-// Every warp streams its tiles through a private ring of NS shared-memory stages (kST tiles
-// and their scale lines each) filled with cp.async, so that NS-1 stages (2 KiB each) per
-// warp are in flight while one is consumed, and the ring keeps running across the warp's
-// units. In a stage the two half-warps take the even and the odd tiles (one 128-bit
+// Every warp streams its tiles through a private ring of NS shared-memory stages (kST tiles,
+// their scale lines and - from the prepared scratch, which stays in L2 - the matching
+// activation codes, sums and scales) filled with cp.async, so that NS-1 stages per warp are
+// in flight while one is consumed and no load of the tile loop leaves the SM; the ring keeps
+// running across the warp's units. In a stage the two half-warps take the even and the odd tiles (one 128-bit
 // shared-memory load per lane = one row of a tile).
 // FUSEQ: the fp32 activation row is quantised by every CTA into shared memory (the same
 // per-block rule and code as quant_s8_kernel) after the wait on earlier kernels, instead of
@@ -85,6 +96,7 @@ template <bool SERIAL, bool DUMP, bool FUSEQ, int NS>
 __global__ void __launch_bounds__(kW * 32, 2) gemv_w4a8_kernel(const GemvArgs a) {
     __shared__ float part[kW * 16];
     // ring[kW][NS][kStageBytes], then (FUSEQ) qp[K], as[K/32], sum32[K/32]
+    constexpr int kStageBytes = stage_bytes(FUSEQ);
     extern __shared__ __align__(16) unsigned char dyn[];
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -121,24 +133,42 @@ __global__ void __launch_bounds__(kW * 32, 2) gemv_w4a8_kernel(const GemvArgs a)
         }
     };
     producer_group();
-    auto issue_next = [&]() {
+    // One stage = the weight part (codes and scale lines: may be fetched before the wait on
+    // earlier kernels) and finish_stage (activations from the prepared scratch, which an
+    // earlier kernel wrote; then the stage is committed and the producer moves on).
+    auto issue_weights = [&]() {
         if (pg < groups && cnt > 0) {
             const int left = cnt - pi0;
+            const uint16_t *sl = pscl + (size_t)((kt_begin + pi0 + (lane >> 1)) >> a.ksh) * 16u;
             if (left >= kST) {
 #pragma unroll
                 for (int p = 0; p < kST / 2; ++p)
                     cp_async16(pdst + lane * 16 + p * 512, psrc + p * 512, pol);
-                if (lane < 2 * kST)
-                    cp_async16(pdst + kST * 256 + lane * 16,
-                               pscl + (size_t)((kt_begin + pi0 + (lane >> 1)) >> a.ksh) * 16u, pol);
+                if (lane < 2 * kST) cp_async16(pdst + kST * 256 + lane * 16, sl, pol);
             } else {
 #pragma unroll
                 for (int p = 0; p < kST / 2; ++p)
                     if (lane + 32 * p < left * 16)
                         cp_async16(pdst + lane * 16 + p * 512, psrc + p * 512, pol);
-                if (lane < 2 * left)
-                    cp_async16(pdst + kST * 256 + lane * 16,
-                               pscl + (size_t)((kt_begin + pi0 + (lane >> 1)) >> a.ksh) * 16u, pol);
+                if (lane < 2 * left) cp_async16(pdst + kST * 256 + lane * 16, sl, pol);
+            }
+        }
+    };
+    auto finish_stage = [&]() {
+        if (pg < groups && cnt > 0) {
+            if (!FUSEQ) {
+                const int nt = min(kST, cnt - pi0);
+                const int kt0 = kt_begin + pi0;
+                if (lane < 16) {
+                    // codes of tile lane/2, half lane%2
+                    if (lane < 2 * nt)
+                        cp_async16_plain(pdst + kActCodes + lane * 16, a.qp + (size_t)kt0 * 32 + lane * 16);
+                } else if ((lane & 7) < nt) {
+                    // lanes 16..23: int32 sums, lanes 24..31: scales (adjacent in the stage)
+                    const void *src = lane < 24 ? static_cast<const void *>(a.sum32 + kt0 + (lane - 16))
+                                                : static_cast<const void *>(a.as + kt0 + (lane - 24));
+                    cp_async4(pdst + kActSums + (lane - 16) * 4, src);
+                }
             }
             pi0 += kST;
             psrc += kST * 256;
@@ -154,13 +184,21 @@ __global__ void __launch_bounds__(kW * 32, 2) gemv_w4a8_kernel(const GemvArgs a)
 
     pdl_trigger();
     // Weights do not depend on earlier kernels: the ring starts filling before the wait.
+    if (FUSEQ) {
 #pragma unroll
-    for (int i = 0; i < NS - 1; ++i) issue_next();
-    pdl_wait();
+        for (int i = 0; i < NS - 1; ++i) {
+            issue_weights();
+            finish_stage();
+        }
+        pdl_wait();
+    } else {
+        static_assert(FUSEQ || NS == 2, "the prepared path prefetches one stage across the wait");
+        issue_weights();
+        pdl_wait();
+        finish_stage();
+    }
 
-    const int8_t *qp = a.qp;
-    const float *asv = a.as;
-    const int32_t *sumv = a.sum32;
+    uint32_t fq_codes = 0, fq_scales = 0, fq_sums = 0;   // FUSEQ: the CTA's quantised row
     if (FUSEQ) {
         unsigned char *qbase = dyn + (size_t)kW * NS * kStageBytes;
         int8_t *sqp = reinterpret_cast<int8_t *>(qbase);
@@ -190,9 +228,9 @@ __global__ void __launch_bounds__(kW * 32, 2) gemv_w4a8_kernel(const GemvArgs a)
             }
         }
         __syncthreads();
-        qp = sqp;
-        asv = sas;
-        sumv = ssum;
+        fq_codes = smem_u32(sqp);
+        fq_scales = smem_u32(sas);
+        fq_sums = smem_u32(ssum);
     }
 
     // Consumer side. One stage: the half-warp h takes tiles h, h + 2, ... of the stage. A
@@ -201,26 +239,17 @@ __global__ void __launch_bounds__(kW * 32, 2) gemv_w4a8_kernel(const GemvArgs a)
     uint32_t cst = ring_s;
     const uint32_t lane_w = h * 256 + n * 16;              // this lane's row in tile h
     const uint32_t lane_s = kST * 256 + h * 32 + n * 2;    // and its scale word
-    auto pair_step = [&](uint32_t wl, uint32_t sl, const int8_t *ap, const int32_t *smp,
-                         const float *asp, int32_t *dmp, bool valid, bool odd_valid,
-                         float &acc) {
+    // ea: even-k codes of the tile (odd-k at +16); sa / fa_: its int32 sum and fp32 scale
+    auto pair_step = [&](uint32_t wl, uint32_t sl, uint32_t ea, uint32_t sa, uint32_t fa_,
+                         int32_t *dmp, bool valid, bool odd_valid, float &acc) {
         float fa = 0.0f, fb = 0.0f;
         if (valid) {
             const uint4 wv = lds_v4(wl);
             const uint32_t sc = lds_u16(sl);
-            uint4 e, o;
-            int asum;
-            if (FUSEQ) {
-                e = *reinterpret_cast<const uint4 *>(ap);
-                o = *reinterpret_cast<const uint4 *>(ap + 16);
-                asum = *smp;
-                fb = *asp;
-            } else {
-                e = __ldg(reinterpret_cast<const uint4 *>(ap));
-                o = __ldg(reinterpret_cast<const uint4 *>(ap + 16));
-                asum = __ldg(smp);
-                fb = __ldg(asp);
-            }
+            const uint4 e = lds_v4(ea);
+            const uint4 o = lds_v4(ea + 16);
+            const int asum = (int)lds_u32(sa);
+            fb = __uint_as_float(lds_u32(fa_));
             const int dp = tile_dot_plus8(wv, e, o);
             int zp;
             float ws;
@@ -246,35 +275,40 @@ __global__ void __launch_bounds__(kW * 32, 2) gemv_w4a8_kernel(const GemvArgs a)
         int wi = 0;
         while (wi + 1 < a.count && g >= a.goff[wi + 1]) ++wi;
         const int lg = g - a.goff[wi];
-        const int8_t *ap = qp + (size_t)(kt_begin + h) * 32;
-        const int32_t *smp = sumv + kt_begin + h;
-        const float *asp = asv + kt_begin + h;
+        // FUSEQ: activations of tile kt_begin + h in the CTA's arrays; they move with the stages
+        uint32_t fe = fq_codes + (kt_begin + h) * 32, fs = fq_sums + (kt_begin + h) * 4,
+                 ff = fq_scales + (kt_begin + h) * 4;
         int32_t *dmp = DUMP ? a.dump + ((size_t)g * Kt + kt_begin + h) * 16 + n : nullptr;
 
         float acc = 0.0f;
         for (int left = cnt; left > 0; left -= kST) {
             cp_async_wait<NS - 2>();
             __syncwarp();                 // the stage is complete; the slot read last is free
-            issue_next();
+            issue_weights();
+            finish_stage();
             const uint32_t wl = cst + lane_w, sl = cst + lane_s;
+            // activations of tile h of this stage, and the distance between tile pairs
+            const uint32_t ea = FUSEQ ? fe : cst + kActCodes + h * 32;
+            const uint32_t sa = FUSEQ ? fs : cst + kActSums + h * 4;
+            const uint32_t fa_ = FUSEQ ? ff : cst + kActScales + h * 4;
             if (left >= kST) {
 #pragma unroll
                 for (int u = 0; u < kST / 2; ++u)
-                    pair_step(wl + u * 512, sl + u * 64, ap + u * 64, smp + 2 * u, asp + 2 * u,
+                    pair_step(wl + u * 512, sl + u * 64, ea + u * 64, sa + u * 8, fa_ + u * 8,
                               DUMP ? dmp + u * 32 : nullptr, true, true, acc);
             } else {
                 // last, short stage of the split: a plain loop, only its last pair can be half
                 const int np = (left + 1) >> 1;
 #pragma unroll 1
                 for (int u = 0; u < np; ++u)
-                    pair_step(wl + u * 512, sl + u * 64, ap + u * 64, smp + 2 * u, asp + 2 * u,
+                    pair_step(wl + u * 512, sl + u * 64, ea + u * 64, sa + u * 8, fa_ + u * 8,
                               DUMP ? dmp + u * 32 : nullptr, 2 * u + h < left, 2 * u + 1 < left,
                               acc);
             }
             cst = (cst + kStageBytes == ring_s + NS * kStageBytes) ? ring_s : cst + kStageBytes;
-            ap += kST * 32;
-            smp += kST;
-            asp += kST;
+            fe += kST * 32;
+            fs += kST * 4;
+            ff += kST * 4;
             if (DUMP) dmp += kST * 16;
         }
         if (DUMP) continue;
@@ -320,17 +354,21 @@ void launch_gemv(const GemvArgs &a) {
     }
     const int tpc = kW / a.splits;
     const int grid = std::min(2 * g_sms, (groups + tpc - 1) / tpc);
-    constexpr size_t kRing3 = (size_t)kW * 3 * kStageBytes, kRing2 = (size_t)kW * 2 * kStageBytes;
+    // prepared path: two stages that carry their activations; fused quantiser: the CTA's
+    // quantised row sits beside the rings, three stages when that fits two CTAs per SM
+    constexpr size_t kRingP = (size_t)kW * 2 * stage_bytes(false);
+    constexpr size_t kRingF3 = (size_t)kW * 3 * stage_bytes(true), kRingF2 = (size_t)kW * 2 * stage_bytes(true);
     constexpr size_t kPerCta = (227 * 1024) / 2 - 1024 - kW * 16 * 4;   // two CTAs per SM
+    static_assert(kRingP <= kPerCta, "ring too large for two CTAs per SM");
     const size_t qbytes = (size_t)a.K + (size_t)(a.K / 32) * 8;
     static bool attr = false;
     if (!attr) {
-        TQ_CHECK(cudaFuncSetAttribute(gemv_w4a8_kernel<false, true, false, 3>,
-                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRing3));
-        TQ_CHECK(cudaFuncSetAttribute(gemv_w4a8_kernel<true, false, false, 3>,
-                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRing3));
-        TQ_CHECK(cudaFuncSetAttribute(gemv_w4a8_kernel<false, false, false, 3>,
-                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRing3));
+        TQ_CHECK(cudaFuncSetAttribute(gemv_w4a8_kernel<false, true, false, 2>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingP));
+        TQ_CHECK(cudaFuncSetAttribute(gemv_w4a8_kernel<true, false, false, 2>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingP));
+        TQ_CHECK(cudaFuncSetAttribute(gemv_w4a8_kernel<false, false, false, 2>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingP));
         TQ_CHECK(cudaFuncSetAttribute(gemv_w4a8_kernel<false, false, true, 3>,
                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPerCta));
         TQ_CHECK(cudaFuncSetAttribute(gemv_w4a8_kernel<false, false, true, 2>,
@@ -338,17 +376,17 @@ void launch_gemv(const GemvArgs &a) {
         attr = true;
     }
     if (a.dump)
-        launch_pdl(gemv_w4a8_kernel<false, true, false, 3>, dim3(grid), dim3(kW * 32), kRing3, a);
+        launch_pdl(gemv_w4a8_kernel<false, true, false, 2>, dim3(grid), dim3(kW * 32), kRingP, a);
     else if (a.serial)
-        launch_pdl(gemv_w4a8_kernel<true, false, false, 3>, dim3(grid), dim3(kW * 32), kRing3, a);
-    else if (a.x && kRing3 + qbytes <= kPerCta)
+        launch_pdl(gemv_w4a8_kernel<true, false, false, 2>, dim3(grid), dim3(kW * 32), kRingP, a);
+    else if (a.x && kRingF3 + qbytes <= kPerCta)
         launch_pdl(gemv_w4a8_kernel<false, false, true, 3>, dim3(grid), dim3(kW * 32),
-                   kRing3 + qbytes, a);
-    else if (a.x && kRing2 + qbytes <= kPerCta)
+                   kRingF3 + qbytes, a);
+    else if (a.x && kRingF2 + qbytes <= kPerCta)
         launch_pdl(gemv_w4a8_kernel<false, false, true, 2>, dim3(grid), dim3(kW * 32),
-                   kRing2 + qbytes, a);
+                   kRingF2 + qbytes, a);
     else
-        launch_pdl(gemv_w4a8_kernel<false, false, false, 3>, dim3(grid), dim3(kW * 32), kRing3, a);
+        launch_pdl(gemv_w4a8_kernel<false, false, false, 2>, dim3(grid), dim3(kW * 32), kRingP, a);
     TQ_LAUNCH_CHECK("gemv_w4a8_kernel");
 }
 

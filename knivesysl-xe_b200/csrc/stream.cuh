@@ -106,6 +106,14 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint64
                  "l"(src), "l"(policy)
                  : "memory");
 }
+// The same without a cache hint, and a 4-byte copy (through L1), for small operands that
+// should stay cached.
+__device__ __forceinline__ void cp_async16_plain(uint32_t dst, const void *src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void *src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() {
     asm volatile("cp.async.commit_group;" ::: "memory");
 }
