@@ -26,7 +26,7 @@ namespace tq {
 
 namespace {
 
-constexpr int kW = 16;    // warps per CTA
+constexpr int kW = 16;    // most warps per CTA (a launch may use fewer: blockDim.x / 32)
 constexpr int kST = 8;    // tiles per ring stage
 constexpr int kWeightBytes = kST * 256 + kST * 32;  // codes, then one 32-byte scale line per tile
 // A stage also carries its tiles' activations unless the kernel quantised the row itself:
@@ -95,7 +95,8 @@ __device__ __forceinline__ int tile_dot_plus8(const uint4 &w, const uint4 &e, co
 template <bool SERIAL, bool DUMP, bool FUSEQ, int NS>
 __global__ void __launch_bounds__(kW * 32, 2) gemv_w4a8_kernel(const GemvArgs a) {
     __shared__ float part[kW * 16];
-    // ring[kW][NS][kStageBytes], then (FUSEQ) qp[K], as[K/32], sum32[K/32]
+    // ring[warps][NS][kStageBytes], then (FUSEQ) qp[K], as[K/32], sum32[K/32]
+    const int nw = blockDim.x >> 5;
     constexpr int kStageBytes = stage_bytes(FUSEQ);
     extern __shared__ __align__(16) unsigned char dyn[];
     const int warp = threadIdx.x >> 5;
@@ -103,7 +104,7 @@ __global__ void __launch_bounds__(kW * 32, 2) gemv_w4a8_kernel(const GemvArgs a)
     const int h = lane >> 4;
     const int n = lane & 15;
     const int S = a.splits;
-    const int tpc = kW / S;                            // teams per CTA
+    const int tpc = nw / S;                            // teams per CTA
     const int team = warp / S;
     const int split = warp - team * S;
     const int g0 = blockIdx.x + gridDim.x * team;
@@ -192,20 +193,24 @@ __global__ void __launch_bounds__(kW * 32, 2) gemv_w4a8_kernel(const GemvArgs a)
         }
         pdl_wait();
     } else {
-        static_assert(FUSEQ || NS == 2, "the prepared path prefetches one stage across the wait");
-        issue_weights();
+        issue_weights();          // the first stage's weights cross the wait
         pdl_wait();
         finish_stage();
+#pragma unroll
+        for (int i = 1; i < NS - 1; ++i) {
+            issue_weights();
+            finish_stage();
+        }
     }
 
     uint32_t fq_codes = 0, fq_scales = 0, fq_sums = 0;   // FUSEQ: the CTA's quantised row
     if (FUSEQ) {
-        unsigned char *qbase = dyn + (size_t)kW * NS * kStageBytes;
+        unsigned char *qbase = dyn + (size_t)nw * NS * kStageBytes;
         int8_t *sqp = reinterpret_cast<int8_t *>(qbase);
         float *sas = reinterpret_cast<float *>(qbase + a.K);
         int32_t *ssum = reinterpret_cast<int32_t *>(qbase + a.K + (size_t)Kt * 4);
         const bool scribe = blockIdx.x == 0;     // keeps the library's prepared scratch current
-        for (int b = warp; b < Kt; b += kW) {
+        for (int b = warp; b < Kt; b += nw) {
             const float v = a.x[b * 32 + lane];
             const float mx = warp_max(fabsf(v));
             const float sc = (mx > 0.0f) ? __fdiv_rn(mx, 127.0f) : 1.0f;
@@ -297,13 +302,14 @@ __global__ void __launch_bounds__(kW * 32, 2) gemv_w4a8_kernel(const GemvArgs a)
                     pair_step(wl + u * 512, sl + u * 64, ea + u * 64, sa + u * 8, fa_ + u * 8,
                               DUMP ? dmp + u * 32 : nullptr, true, true, acc);
             } else {
-                // last, short stage of the split: a plain loop, only its last pair can be half
-                const int np = (left + 1) >> 1;
-#pragma unroll 1
-                for (int u = 0; u < np; ++u)
-                    pair_step(wl + u * 512, sl + u * 64, ea + u * 64, sa + u * 8, fa_ + u * 8,
-                              DUMP ? dmp + u * 32 : nullptr, 2 * u + h < left, 2 * u + 1 < left,
-                              acc);
+                // last, short stage of the split: the same steps behind warp-uniform tests,
+                // only the last pair can be half
+#pragma unroll
+                for (int u = 0; u < kST / 2; ++u)
+                    if (2 * u < left)
+                        pair_step(wl + u * 512, sl + u * 64, ea + u * 64, sa + u * 8, fa_ + u * 8,
+                                  DUMP ? dmp + u * 32 : nullptr, 2 * u + h < left, 2 * u + 1 < left,
+                                  acc);
             }
             cst = (cst + kStageBytes == ring_s + NS * kStageBytes) ? ring_s : cst + kStageBytes;
             fe += kST * 32;
@@ -369,6 +375,9 @@ void launch_gemv(const GemvArgs &a) {
                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingP));
         TQ_CHECK(cudaFuncSetAttribute(gemv_w4a8_kernel<false, false, false, 2>,
                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingP));
+        TQ_CHECK(cudaFuncSetAttribute(gemv_w4a8_kernel<false, false, false, 3>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      (int)((size_t)kW * 3 * stage_bytes(false))));
         TQ_CHECK(cudaFuncSetAttribute(gemv_w4a8_kernel<false, false, true, 3>,
                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPerCta));
         TQ_CHECK(cudaFuncSetAttribute(gemv_w4a8_kernel<false, false, true, 2>,
@@ -385,7 +394,14 @@ void launch_gemv(const GemvArgs &a) {
     else if (a.x && kRingF2 + qbytes <= kPerCta)
         launch_pdl(gemv_w4a8_kernel<false, false, true, 2>, dim3(grid), dim3(kW * 32),
                    kRingF2 + qbytes, a);
-    else
+    else if (a.splits >= 4 && groups <= 3 * g_sms) {
+        // Few row-groups (a long-K weight): 16-warp CTAs would leave warp slots empty and each
+        // warp's long chain would have one stage in flight. One team per CTA instead, up to
+        // three CTAs per SM, three ring stages.
+        const int nw = a.splits;
+        launch_pdl(gemv_w4a8_kernel<false, false, false, 3>, dim3(groups), dim3(nw * 32),
+                   (size_t)nw * 3 * stage_bytes(false), a);
+    } else
         launch_pdl(gemv_w4a8_kernel<false, false, false, 2>, dim3(grid), dim3(kW * 32), kRingP, a);
     TQ_LAUNCH_CHECK("gemv_w4a8_kernel");
 }
