@@ -417,10 +417,9 @@ gemm_w4a8_stream_kernel(const GemmArgs a, float *__restrict__ part, int *__restr
 // twice as many warps share an SM. Scale words are read raw from the stage (one 32-byte line
 // per tile) and unpacked by the lanes that use them. Task mapping, staged activations, split
 // reduction, stores and the fused all-gather are those of the kernel above.
-constexpr int kRW = 32;                              // warps per CTA
+constexpr int kRW = 32;                              // most warps per CTA (a launch may use fewer)
 constexpr int kRST = 8;                              // tiles per ring stage (4 and 6 measured slower)
 constexpr int kRStage = kRST * 256 + kRST * 32;      // codes, then one scale line per tile
-constexpr int kRNS = 2;                              // ring stages per warp
 
 __device__ __forceinline__ uint2 lds_v2(uint32_t addr) {
     uint2 v;
@@ -445,8 +444,11 @@ __device__ __forceinline__ void scale_pair(uint32_t packed, float &ws, float &z8
     z8 = (float)(int)((packed ^ 8u) & 15u);
 }
 
-template <bool PAIR>   // PAIR: K64 tier and even split starts - tiles 2j, 2j+1 share a scale line
-__global__ void __launch_bounds__(kRW * 32, 1)
+// PAIR: K64 tier and even split starts - tiles 2j, 2j+1 share a scale line. kRNS: ring stages
+// per warp (2 with all 32 warps; more when the call has fewer tasks than warp slots).
+// MAXW: most warps the instantiation is launched with (fewer warps leave it more registers).
+template <bool PAIR, int kRNS, int MAXW>
+__global__ void __launch_bounds__(MAXW * 32, 1)
 gemm_w4a8_ring_kernel(const GemmArgs a, float *__restrict__ part, int *__restrict__ count) {
     extern __shared__ __align__(128) unsigned char smem[];
     const int warp = threadIdx.x >> 5;
@@ -460,7 +462,8 @@ gemm_w4a8_ring_kernel(const GemmArgs a, float *__restrict__ part, int *__restric
 
     const int groups_all = a.goff[a.count];
     const int tgid = cta_i + nctas * warp;
-    const int tstride = nctas * kRW;
+    const int nw = blockDim.x >> 5;
+    const int tstride = nctas * nw;
     const int Kt = a.K >> 5;
     const int ksh = a.ksh;
     const int Ktg = Kt >> ksh;
@@ -469,7 +472,7 @@ gemm_w4a8_ring_kernel(const GemmArgs a, float *__restrict__ part, int *__restric
 
     unsigned char *ring = smem + (size_t)warp * kRNS * kRStage;
     const uint32_t ring_s = smem_u32(ring);
-    unsigned char *act = smem + (size_t)kRW * kRNS * kRStage;
+    unsigned char *act = smem + (size_t)nw * kRNS * kRStage;
     const uint32_t act_s = smem_u32(act);
     float *xpose = reinterpret_cast<float *>(act + (size_t)cnt * kActTileBytes) + warp * 128;
     const uint64_t pol = l2_policy_evict_first();
@@ -527,7 +530,7 @@ gemm_w4a8_ring_kernel(const GemmArgs a, float *__restrict__ part, int *__restric
     // code sums are stored negated: the tile loop multiplies them by z + 8 >= 0).
     {
         const int items = cnt * 32;
-        for (int i = threadIdx.x; i < items; i += kRW * 32) {
+        for (int i = threadIdx.x; i < items; i += nw * 32) {
             const int kl = i >> 5;
             const int rem = i & 31;
             const uint2 bb = __ldg(reinterpret_cast<const uint2 *>(
@@ -538,7 +541,7 @@ gemm_w4a8_ring_kernel(const GemmArgs a, float *__restrict__ part, int *__restric
             *reinterpret_cast<uint2 *>(act + (size_t)kl * kActTileBytes + rem * 8) = o;
         }
         const int pairs = cnt * 4;
-        for (int i = threadIdx.x; i < pairs; i += kRW * 32) {
+        for (int i = threadIdx.x; i < pairs; i += nw * 32) {
             const int kl = i >> 2;
             const int rem = i & 3;
             const size_t src = (size_t)(kt_begin + kl) * 8 + (size_t)rem * 2;
@@ -797,28 +800,53 @@ bool launch_ring(const GemmArgs &a) {
     }
     const int Kt = a.K >> 5, S = a.max_splits;
     const int groups = a.goff[a.count];
-    const size_t smem = (size_t)kRW * kRNS * kRStage + (size_t)((Kt + S - 1) / S) * kActTileBytes +
-                        (a.npeer ? (size_t)kRW * 512 : 0);
-    if (smem > kSmemLimit || S > g_num_sms) return false;
-    bool pair = a.ksh != 0;
-    for (int s2 = 0; s2 < S; ++s2) pair = pair && ((Kt * s2 / S) % 2 == 0);
-    static bool attr_set = false;
-    if (!attr_set) {
-        TQ_CHECK(cudaFuncSetAttribute(gemm_w4a8_ring_kernel<false>,
-                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit));
-        TQ_CHECK(cudaFuncSetAttribute(gemm_w4a8_ring_kernel<true>,
-                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit));
-        attr_set = true;
-    }
-    if (S > 1) ensure_scratch((size_t)groups * S * 128, groups);
+    if (S > g_num_sms) return false;
     const long most = (long)groups * S;
     const int grid = (int)std::max<long>(S, std::min<long>(g_num_sms - g_num_sms % S, most));
-    if (pair)
-        launch_pdl(gemm_w4a8_ring_kernel<true>, dim3(grid), dim3(kRW * 32), smem, a, g_scratch.part,
-                   g_scratch.count);
-    else
-        launch_pdl(gemm_w4a8_ring_kernel<false>, dim3(grid), dim3(kRW * 32), smem, a, g_scratch.part,
-                   g_scratch.count);
+    // One task per warp when the call has fewer tasks than warp slots: fewer warps, and the
+    // shared memory they leave goes into deeper rings (each warp's chain is then longer
+    // than the memory latency its ring covers with two stages).
+    const int per_cta = (groups + grid / S - 1) / (grid / S);          // tasks of the busiest CTA
+    int nw = kRW;
+    if (per_cta < kRW) nw = std::max(8, (per_cta + 1) / 2 * 2);
+    const size_t fixed = (size_t)((Kt + S - 1) / S) * kActTileBytes + (a.npeer ? (size_t)nw * 512 : 0);
+    int ns = 4;
+    while (ns > 2 && (size_t)nw * ns * kRStage + fixed > kSmemLimit) --ns;
+    const size_t smem = (size_t)nw * ns * kRStage + fixed;
+    if (smem > kSmemLimit) return false;
+    bool pair = a.ksh != 0;
+    for (int s2 = 0; s2 < S; ++s2) pair = pair && ((Kt * s2 / S) % 2 == 0);
+    if (S > 1) ensure_scratch((size_t)groups * S * 128, groups);
+    static bool attr_set = false;
+    if (!attr_set) {
+        auto big = [](auto kernel) {
+            TQ_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          (int)kSmemLimit));
+        };
+        big(gemm_w4a8_ring_kernel<true, 2, kRW>);
+        big(gemm_w4a8_ring_kernel<true, 3, kRW>);
+        big(gemm_w4a8_ring_kernel<true, 4, kRW>);
+        big(gemm_w4a8_ring_kernel<true, 4, 20>);
+        big(gemm_w4a8_ring_kernel<false, 2, kRW>);
+        big(gemm_w4a8_ring_kernel<false, 3, kRW>);
+        big(gemm_w4a8_ring_kernel<false, 4, kRW>);
+        big(gemm_w4a8_ring_kernel<false, 4, 20>);
+        attr_set = true;
+    }
+    auto go = [&](auto kernel) {
+        launch_pdl(kernel, dim3(grid), dim3(nw * 32), smem, a, g_scratch.part, g_scratch.count);
+    };
+    if (pair) {
+        if (ns == 2) go(gemm_w4a8_ring_kernel<true, 2, kRW>);
+        else if (ns == 3) go(gemm_w4a8_ring_kernel<true, 3, kRW>);
+        else if (nw <= 20) go(gemm_w4a8_ring_kernel<true, 4, 20>);
+        else go(gemm_w4a8_ring_kernel<true, 4, kRW>);
+    } else {
+        if (ns == 2) go(gemm_w4a8_ring_kernel<false, 2, kRW>);
+        else if (ns == 3) go(gemm_w4a8_ring_kernel<false, 3, kRW>);
+        else if (nw <= 20) go(gemm_w4a8_ring_kernel<false, 4, 20>);
+        else go(gemm_w4a8_ring_kernel<false, 4, kRW>);
+    }
     TQ_LAUNCH_CHECK("gemm_w4a8_ring_kernel");
     return true;
 }
