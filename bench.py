@@ -36,7 +36,7 @@ METRIC = "decode_gemv_weight_GBps"
 UNIT = "GB/s"
 # dram__bytes_read.sum + dram__bytes_write.sum of one GEMM launch of this workload, from the
 # ncu capture summarised in profiles/ (None until a capture exists)
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 98_918_656
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 100_617_216
 
 
 def measured_peaks():
