@@ -181,6 +181,19 @@ void qwn_x_quantize_act_chunk_pertoken(const float *d_x, int K, int T, int8_t *d
 int qwn_x_gemm_w4a8_pertoken(const tq_qmma_weight_t *w, const int8_t *d_aq, const float *d_as_tok,
                              const int32_t *d_asum, void *d_y, int T, int out_bf16);
 
+/* W4A4, the tier the reference runs K64 weights at in prefill (x_quantize_act_chunk_s4 and
+ * x_gemm_w4a4, xpu/src/kernels_dpas.cpp:1495-1571). Staging: one block per (token, 64
+ * values), codes in [-7, 7] with scale absmax/7, two per byte (byte b of a block's 32 =
+ * k 2b low nibble, k 2b+1 high nibble): aq4[(kt64*T+tok)*32+b], as4[kt64*T+tok],
+ * asum4[kt64*T+tok]. GEMM: K64 weights only (-1 otherwise); y[tok][n] accumulates
+ * (float)(d - z*asum4) * (ws*as4) over the K64 groups in ascending order, d the exact int32
+ * dot of the 64 int4 x int4 products. Built for prefill shapes: T >= 128 and rows a multiple
+ * of 128, else -3. */
+void qwn_x_quantize_act_chunk_s4(const float *d_x, int K, int T, uint8_t *d_aq4, float *d_as4,
+                                 int32_t *d_asum4);
+int qwn_x_gemm_w4a4(const tq_qmma_weight_t *w, const uint8_t *d_aq4, const float *d_as4,
+                    const int32_t *d_asum4, float *d_y, int T);
+
 /* int32 layer exposed for bit-exact checks: the dot of every (row, k-tile) with the
  * staged activation, produced by the same unpack/dot code as the kernels above.
  * gemv: d[(g*Kt+kt)*16+n] from the prepared scratch; gemm: d[(kt*T+tok)*M+row]. */
@@ -283,6 +296,10 @@ void x_quantize_act_chunk_pertoken(const float *d_x, int K, int T, int8_t *d_aq,
                                    int32_t *d_asum, float *d_as_tok);
 int x_gemm_w4a8_pertoken(const tq_qmma_weight_t *w, const int8_t *d_aq, const float *d_as_tok,
                          const int32_t *d_asum, void *d_y, int T, int out_bf16 = 0);
+void x_quantize_act_chunk_s4(const float *d_x, int K, int T, uint8_t *d_aq4, float *d_as4,
+                             int32_t *d_asum4);
+int x_gemm_w4a4(const tq_qmma_weight_t *w, const uint8_t *d_aq4, const float *d_as4,
+                const int32_t *d_asum4, float *d_y, int T);
 #endif /* __cplusplus */
 
 #endif /* TQ_W4A8_H */

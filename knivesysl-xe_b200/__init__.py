@@ -77,6 +77,8 @@ SIGNATURES = {
                                     C.POINTER(_i), _i]),
     "qwn_x_quantize_act_chunk_pertoken": (None, [_vp, _i, _i, _vp, _vp, _vp, _vp]),
     "qwn_x_gemm_w4a8_pertoken": (_i, [_WP, _vp, _vp, _vp, _vp, _i, _i]),
+    "qwn_x_quantize_act_chunk_s4": (None, [_vp, _i, _i, _vp, _vp, _vp]),
+    "qwn_x_gemm_w4a4": (_i, [_WP, _vp, _vp, _vp, _vp, _i]),
     "qwn_dbg_tile_dots_gemv": (_i, [_WP, _vp]),
     "qwn_dbg_tile_dots_gemm": (_i, [_WP, _vp, _i, _vp]),
     "qwn_dbg_prepared_act": (_i, [_i, _vp, _vp, _vp]),

@@ -6,7 +6,8 @@
 
 Cases: cfg1 (GEMV 17408x5120 K32), gemv_down (GEMV 5120x17408), cfg2 (fused gate+up K64,
 T=8), down_t8 / down_t16 / down_t32 / down_t64 (5120x17408 K32), prefill_small (tcgen05 GEMM
-2048x5120, T=1024), cfg4 (tcgen05 GEMM 17408x5120 K64, T=4096 in 4 segments).
+2048x5120, T=1024), cfg4 (tcgen05 GEMM 17408x5120 K64, T=4096 in 4 segments), cfg4_w4a4 (the
+same shape through x_gemm_w4a4: int4 activations, one promote per K64 group).
 Weights are seeded random codes and scales: timing does not depend on their values.
 """
 from __future__ import annotations
@@ -78,6 +79,27 @@ class Gemm:
         assert rc == 0, rc
 
 
+class GemmW4A4:
+    """x_gemm_w4a4 on one K64 weight (int4 activations per (token, K64))."""
+
+    def __init__(self, lib, M, K, T):
+        self.lib, self.T = lib, T
+        self.w = rand_weight(M, K, True, 3)
+        x = np.random.default_rng(1).standard_normal((T, K)).astype(np.float32)
+        self.dx = pkg.DevBuf.from_numpy(x)
+        n = K // 64 * T
+        self.aq4, self.as4, self.asum4 = pkg.DevBuf(n * 32), pkg.DevBuf(n * 4), pkg.DevBuf(n * 4)
+        lib.qwn_x_quantize_act_chunk_s4(self.dx.ptr, K, T, self.aq4.ptr, self.as4.ptr, self.asum4.ptr)
+        self.y = pkg.DevBuf(T * M * 4)
+        self.bytes = self.w.weight_bytes
+        self.ops = 2.0 * T * M * K
+
+    def launch(self, i):
+        rc = self.lib.qwn_x_gemm_w4a4(self.w.ref, self.aq4.ptr, self.as4.ptr, self.asum4.ptr,
+                                      self.y.ptr, self.T)
+        assert rc == 0, rc
+
+
 CASES = {
     "cfg1": lambda lib: Gemv(lib, 17408, 5120, False),
     "gemv_down": lambda lib: Gemv(lib, 5120, 17408, False),
@@ -88,6 +110,7 @@ CASES = {
     "down_t64": lambda lib: Gemm(lib, [5120], 17408, False, 64),
     "prefill_small": lambda lib: Gemm(lib, [2048], 5120, True, 1024, rot=1),
     "cfg4": lambda lib: Gemm(lib, [17408], 5120, True, 4096, segments=4, rot=1),
+    "cfg4_w4a4": lambda lib: GemmW4A4(lib, 17408, 5120, 4096),
 }
 
 

@@ -67,6 +67,8 @@ void launch_rmsnorm_quant(float *d_out, const float *d_in, const uint16_t *d_w, 
                           float *d_partial, int8_t *d_q, int8_t *d_qp, float *d_scale,
                           int32_t *d_sum16, int32_t *d_sum32);
 void launch_quant_chunk(const float *d_x, int K, int T, int8_t *d_aq, float *d_as, int32_t *d_asum);
+void launch_quant_chunk_s4(const float *d_x, int K, int T, uint8_t *d_aq4, float *d_as4,
+                           int32_t *d_asum4);
 void launch_quant_chunk_pertoken(const float *d_x, int K, int T, int8_t *d_aq, float *d_as,
                                  int32_t *d_asum, float *d_as_tok);
 void launch_code_sums(const int8_t *d_aq, size_t blocks, int32_t *d_asum);
@@ -141,6 +143,8 @@ struct GemmTcArgs {
     const uint8_t *codes;
     const uint16_t *scales;
     const int8_t *aq;
+    const uint8_t *aq4;      // W4A4: packed int4 activations per (K64 block, token) instead of aq;
+                             // as and asum are then per (K64 block, token)
     const float *as;         // per (kt, tok) scales, or nullptr in per-token mode
     const float *as_tok;     // per-token scales, or nullptr
     const int32_t *asum;

@@ -409,6 +409,27 @@ int x_gemm_w4a8_pertoken(const tq_qmma_weight_t *w, const int8_t *d_aq, const fl
     return rc == 0 ? 0 : -3;   // -3: shape not covered by the per-token kernel
 }
 
+// ---- W4A4 (xpu/src/kernels_dpas.cpp:1495-1571): the tier K64 weights run at prefill -------
+void x_quantize_act_chunk_s4(const float *d_x, int K, int T, uint8_t *d_aq4, float *d_as4,
+                             int32_t *d_asum4) {
+    if (!d_x || !d_aq4 || !d_as4 || !d_asum4 || K <= 0 || T <= 0 || (K % 64) != 0) return;
+    launch_quant_chunk_s4(d_x, K, T, d_aq4, d_as4, d_asum4);
+}
+
+// One exact int32 dot per (row, token, K64 group) on the tcgen05 kernel: both k-tiles of the
+// group accumulate in TMEM before the single fp32 promote. Covers prefill shapes (T >= 128,
+// rows a multiple of 128); -3 otherwise.
+int x_gemm_w4a4(const tq_qmma_weight_t *w, const uint8_t *d_aq4, const float *d_as4,
+                const int32_t *d_asum4, float *d_y, int T) {
+    if (!w || !w->s4_ready || !w->s4_k64 || !w->d_s4 || !w->d_s4_scale) return -1;
+    if (!d_aq4 || !d_as4 || !d_asum4 || !d_y || T <= 0 || (T % 8) != 0) return -2;
+    GemmTcArgs t{};
+    t.codes = w->d_s4; t.scales = w->d_s4_scale; t.aq4 = d_aq4; t.as = d_as4;
+    t.asum = d_asum4; t.y = d_y; t.M = w->M; t.K = w->K; t.ksh = 1; t.T = T;
+    const int rc = launch_gemm_tc(t);
+    return rc == 0 ? 0 : -3;
+}
+
 // ---- tensor-parallel column shard (xpu/src/kernels_dpas.cpp:450-499, 549-556) ------------
 int x_w4_shard(tq_qmma_weight_t *dst, const tq_qmma_weight_t *src, int rank, int tp, int mode,
                const int *groups, int ngroups) {
@@ -540,6 +561,15 @@ void qwn_x_quantize_act_chunk_pertoken(const float *d_x, int K, int T, int8_t *d
 int qwn_x_gemm_w4a8_pertoken(const tq_qmma_weight_t *w, const int8_t *d_aq, const float *d_as_tok,
                              const int32_t *d_asum, void *d_y, int T, int out_bf16) {
     return x_gemm_w4a8_pertoken(w, d_aq, d_as_tok, d_asum, d_y, T, out_bf16);
+}
+
+void qwn_x_quantize_act_chunk_s4(const float *d_x, int K, int T, uint8_t *d_aq4, float *d_as4,
+                                 int32_t *d_asum4) {
+    x_quantize_act_chunk_s4(d_x, K, T, d_aq4, d_as4, d_asum4);
+}
+int qwn_x_gemm_w4a4(const tq_qmma_weight_t *w, const uint8_t *d_aq4, const float *d_as4,
+                    const int32_t *d_asum4, float *d_y, int T) {
+    return x_gemm_w4a4(w, d_aq4, d_as4, d_asum4, d_y, T);
 }
 
 int qwn_x_gemm_w4a8_fanout_gathered(const tq_qmma_weight_t *const *ws, int count,

@@ -201,10 +201,60 @@ gemm_tc_prepass_kernel(const int8_t *__restrict__ aq, const float *__restrict__ 
     }
 }
 
+// Four 4-bit two's-complement codes (the low nibble of each byte) -> four int8 bytes.
+__device__ __forceinline__ uint32_t sext_nibbles(uint32_t l) {
+    l &= 0x0F0F0F0Fu;
+    return l | ((l & 0x08080808u) * 0x1Eu);      // a set sign bit fills bits 4..7 of its byte
+}
+
+// W4A4 pre-pass: packed int4 activations aq4[kt64][tok][32] (byte b = k 2b, 2b+1 of the 64),
+// as4 / asum4 per (kt64, tok) -> the same images as above, two K32 images per K64 block. The
+// block's scale and code sum go with its first K32 image; the second one carries zeros, so
+// the GEMM that adds the two sums of a promote group gets the block's sum.
+__global__ void __launch_bounds__(256)
+gemm_tc_prepass_s4_kernel(const uint8_t *__restrict__ aq4, const float *__restrict__ as4,
+                          const int32_t *__restrict__ asum4, int T, int Tpad, int Kt,
+                          uint8_t *__restrict__ img) {
+    pdl_trigger();
+    const size_t nrow = (size_t)Kt * Tpad;
+    for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < nrow; i += (size_t)gridDim.x * 256) {
+        const int kt = (int)(i / Tpad), tok = (int)(i % Tpad);
+        const int kg = kt >> 1, half = kt & 1;
+        uint4 lo = make_uint4(0, 0, 0, 0), hi = make_uint4(0, 0, 0, 0);
+        if (tok < T) {
+            const uint4 a = __ldg(reinterpret_cast<const uint4 *>(aq4 + ((size_t)kg * T + tok) * 32) + half);
+            // low nibbles = even k -> chunk 0, high nibbles = odd k -> chunk 1
+            lo = make_uint4(sext_nibbles(a.x), sext_nibbles(a.y), sext_nibbles(a.z), sext_nibbles(a.w));
+            hi = make_uint4(sext_nibbles(a.x >> 4), sext_nibbles(a.y >> 4), sext_nibbles(a.z >> 4),
+                            sext_nibbles(a.w >> 4));
+        }
+        uint8_t *blk = img + ((size_t)kt * (Tpad / kTN) + tok / kTN) * (kBBytes + kSBytes);
+        const int tl = tok % kTN;
+        uint8_t *dst = blk + (tl >> 3) * 256 + (tl & 7) * 16;
+        *reinterpret_cast<uint4 *>(dst) = lo;
+        *reinterpret_cast<uint4 *>(dst + 128) = hi;
+        if ((tok & 1) == 0) {
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (half == 0) {
+                if (tok < T) {
+                    v.x = as4[(size_t)kg * T + tok];
+                    v.z = (float)asum4[(size_t)kg * T + tok];
+                }
+                if (tok + 1 < T) {
+                    v.y = as4[(size_t)kg * T + tok + 1];
+                    v.w = (float)asum4[(size_t)kg * T + tok + 1];
+                }
+            }
+            reinterpret_cast<float4 *>(blk + kBBytes)[tl >> 1] = v;
+        }
+    }
+}
+
 constexpr int kWaitMma = 21, kWaitEpi = 22, kWaitProd = 23;   // status codes of failed waits
 
 // GW = k-tiles accumulated in TMEM before one fp32 promote (1: the reference's arithmetic with
-// a scale per (token, K32); 2: per-token activation scales with K64 weight groups). PERTOK:
+// a scale per (token, K32); 2: K64 weight groups with per-token activation scales, or - not
+// PERTOK - with one activation scale per (token, K64): the W4A4 arithmetic). PERTOK:
 // the activation scale is applied once at the end (y = acc * as_tok).
 template <int GW, bool PERTOK>
 __global__ void __launch_bounds__(kThreads, 1) gemm_w4a8_tc_kernel(const TcParams p) {
@@ -486,6 +536,7 @@ int launch_gemm_tc(const GemmTcArgs &a) {
     // covered: per-block activation scales (the reference's x_gemm_w4a8 arithmetic) or
     // per-token scales, rows a multiple of 128, K64 tier only with an even number of k-tiles
     if (!a.as == !a.as_tok) return -1;          // exactly one kind of activation scale
+    if (a.aq4 && (!a.as || !a.ksh)) return -1;  // W4A4: K64 weights, scale per (token, K64)
     if (a.M % kTM || a.K % 32 || a.T < 128) return -1;
     const int Kt = a.K / 32;
     if (a.ksh && (Kt & 1)) return -1;
@@ -500,6 +551,8 @@ int launch_gemm_tc(const GemmTcArgs &a) {
                                       cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
         TQ_CHECK(cudaFuncSetAttribute(gemm_w4a8_tc_kernel<2, true>,
                                       cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+        TQ_CHECK(cudaFuncSetAttribute(gemm_w4a8_tc_kernel<2, false>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
     }
     const int Tpad = (a.T + kTN - 1) / kTN * kTN;
     const size_t ibytes = (size_t)Kt * (Tpad / kTN) * (kBBytes + kSBytes);
@@ -510,7 +563,11 @@ int launch_gemm_tc(const GemmTcArgs &a) {
     }
     const size_t nrow = (size_t)Kt * Tpad;
     const int pgrid = (int)std::min<size_t>((nrow + 255) / 256, (size_t)g_tc_sms * 8);
-    gemm_tc_prepass_kernel<<<pgrid, 256, 0, stream()>>>(a.aq, a.as, a.asum, a.T, Tpad, Kt, g_tc.img);
+    if (a.aq4)
+        gemm_tc_prepass_s4_kernel<<<pgrid, 256, 0, stream()>>>(a.aq4, a.as, a.asum, a.T, Tpad, Kt,
+                                                              g_tc.img);
+    else
+        gemm_tc_prepass_kernel<<<pgrid, 256, 0, stream()>>>(a.aq, a.as, a.asum, a.T, Tpad, Kt, g_tc.img);
     TQ_LAUNCH_CHECK("gemm_tc_prepass_kernel");
     TcParams p{};
     p.codes = a.codes; p.scales = a.scales; p.img = g_tc.img; p.y = a.y;
@@ -519,7 +576,9 @@ int launch_gemm_tc(const GemmTcArgs &a) {
     const int ntiles = (a.M / kTM) * (Tpad / kTN);
     const int grid = std::min(g_tc_sms, ntiles);
     p.as_tok = a.as_tok;
-    if (!a.as_tok)
+    if (a.aq4)
+        launch_pdl(gemm_w4a8_tc_kernel<2, false>, dim3(grid), dim3(kThreads), (size_t)kSmemBytes, p);
+    else if (!a.as_tok)
         launch_pdl(gemm_w4a8_tc_kernel<1, false>, dim3(grid), dim3(kThreads), (size_t)kSmemBytes, p);
     else if (a.ksh)
         launch_pdl(gemm_w4a8_tc_kernel<2, true>, dim3(grid), dim3(kThreads), (size_t)kSmemBytes, p);

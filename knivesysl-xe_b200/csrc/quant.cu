@@ -134,6 +134,34 @@ quant_chunk_kernel(const float *__restrict__ x, int K, int T, size_t blocks,
     }
 }
 
+// W4A4 staging (x_quantize_act_chunk_s4, xpu/src/kernels_dpas.cpp:1149-1193, 1495-1498): one
+// warp per (token, 64 values) block blk = kt64*T + tok; lane l quantises k = 2l, 2l+1 to
+// [-7, 7] with scale absmax/7 and stores them as one byte (low nibble = even k).
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+quant_chunk_s4_kernel(const float *__restrict__ x, int K, int T, size_t blocks,
+                      uint8_t *__restrict__ aq4, float *__restrict__ as4,
+                      int32_t *__restrict__ asum4) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t blk = (size_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (blk >= blocks) return;
+    const size_t kt = blk / (size_t)T, tok = blk % (size_t)T;
+    const float2 v = *reinterpret_cast<const float2 *>(x + tok * (size_t)K + kt * 64 + 2 * lane);
+    const float mx = warp_max(fmaxf(fmaxf(-INFINITY, fabsf(v.x)), fabsf(v.y)));
+    const float s = (mx > 0.0f) ? __fdiv_rn(mx, 7.0f) : 1.0f;
+    const int q0 = (int)clampf(rintf(__fdiv_rn(v.x, s)), -7.0f, 7.0f);
+    const int q1 = (int)clampf(rintf(__fdiv_rn(v.y, s)), -7.0f, 7.0f);
+    int sum = q0 + q1;
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+    aq4[blk * 32 + lane] = (uint8_t)((q0 & 0xF) | ((q1 & 0xF) << 4));
+    if (lane == 0) {
+        as4[blk] = s;
+        asum4[blk] = sum;
+    }
+}
+
 // Per-token absmax -> scale (one block per token row).
 __global__ void __launch_bounds__(256)
 token_scale_kernel(const float *__restrict__ x, int K, float *__restrict__ as_tok) {
@@ -260,6 +288,16 @@ void launch_quant_chunk(const float *d_x, int K, int T, int8_t *d_aq, float *d_a
     launch_pdl(quant_chunk_kernel<false>, dim3(grid), dim3(kWarpsPerBlock * 32), 0, d_x, K, T,
                blocks, d_aq, d_as, d_asum, (const float *)nullptr);
     TQ_LAUNCH_CHECK("quant_chunk_kernel");
+}
+
+void launch_quant_chunk_s4(const float *d_x, int K, int T, uint8_t *d_aq4, float *d_as4,
+                           int32_t *d_asum4) {
+    const size_t blocks = (size_t)(K / 64) * (size_t)T;
+    if (!blocks) return;
+    const unsigned grid = (unsigned)((blocks + kWarpsPerBlock - 1) / kWarpsPerBlock);
+    launch_pdl(quant_chunk_s4_kernel, dim3(grid), dim3(kWarpsPerBlock * 32), 0, d_x, K, T, blocks,
+               d_aq4, d_as4, d_asum4);
+    TQ_LAUNCH_CHECK("quant_chunk_s4_kernel");
 }
 
 void launch_quant_chunk_pertoken(const float *d_x, int K, int T, int8_t *d_aq, float *d_as,

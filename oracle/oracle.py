@@ -276,6 +276,26 @@ def gemm_w4a8_pertoken(codes, scales, M, K, ksh, aq, as_tok, asum, T):
     return rc, y
 
 
+def quantize_act_chunk_s4(x):
+    x = _c(x, np.float32)
+    T, K = x.shape
+    n = K // 64 * T
+    aq4 = np.empty(n * 32, dtype=np.uint8)
+    as4 = np.empty(n, dtype=np.float32)
+    asum4 = np.empty(n, dtype=np.int32)
+    lib().orc_quantize_act_chunk_s4(_p(x), C.c_int(K), C.c_int(T), _p(aq4), _p(as4), _p(asum4))
+    return aq4, as4, asum4
+
+
+def gemm_w4a4(codes, scales, M, K, aq4, as4, asum4, T, fma=1):
+    codes, scales = _c(codes, np.uint8), _c(scales, np.uint16)
+    aq4, as4, asum4 = _c(aq4, np.uint8), _c(as4, np.float32), _c(asum4, np.int32)
+    y = np.empty((T, M), dtype=np.float32)
+    rc = lib().orc_gemm_w4a4(_p(codes), _p(scales), C.c_int(M), C.c_int(K), _p(aq4), _p(as4),
+                             _p(asum4), _p(y), C.c_int(T), C.c_int(fma))
+    return rc, y
+
+
 def w4_shard_column(codes, scales, M, K, ksh, rank, tp, groups=None, k16=0):
     codes, scales = _c(codes, np.uint8), _c(scales, np.uint16)
     Kt = K // 32

@@ -764,6 +764,73 @@ ORC_API int orc_gemm_w4a8_pertoken(const uint8_t *codes, const uint16_t *scales,
     return 0;
 }
 
+/* W4A4 staging, quantize_act_chunk_subgroup<true>, xpu/src/kernels_dpas.cpp:1149-1193 and
+ * x_quantize_act_chunk_s4 (1495-1498): one block per (token, 64 values): scale = absmax/7
+ * (1 if the block is all zero), codes clamp(rint(v/scale), -7, 7) packed two per byte
+ * (byte b of the block's 32 = k 2b in the low nibble, k 2b+1 in the high nibble),
+ * aq4[(kt*T+tok)*32 + b], as4[kt*T+tok], asum4[kt*T+tok] = sum of the 64 codes. */
+ORC_API void orc_quantize_act_chunk_s4(const float *x, int K, int T, uint8_t *aq4, float *as4,
+                                       int32_t *asum4) {
+    const int Kt64 = K / 64;
+#pragma omp parallel for schedule(static)
+    for (int kt = 0; kt < Kt64; ++kt) {
+        for (int tok = 0; tok < T; ++tok) {
+            const size_t blk = (size_t)kt * T + tok;
+            const float *v = x + (size_t)tok * K + (size_t)kt * 64;
+            float mx = -INFINITY;
+            for (int j = 0; j < 64; ++j) mx = fmaxf(mx, fabsf(v[j]));
+            const float s = (mx > 0.0f) ? (mx / 7.0f) : 1.0f;
+            int32_t sum = 0;
+            for (int b = 0; b < 32; ++b) {
+                const int32_t q0 = (int32_t)clampf(rintf(v[2 * b] / s), -7.0f, 7.0f);
+                const int32_t q1 = (int32_t)clampf(rintf(v[2 * b + 1] / s), -7.0f, 7.0f);
+                sum += q0 + q1;
+                aq4[blk * 32 + b] = (uint8_t)((q0 & 0xF) | ((q1 & 0xF) << 4));
+            }
+            as4[blk] = s;
+            asum4[blk] = sum;
+        }
+    }
+}
+
+/* x_gemm_w4a4, xpu/src/kernels_dpas.cpp:1500-1571 (the RC16 variants compute the same
+ * values): K64 weights only; per (row, token) one accumulator over the K64 groups in
+ * ascending order, d = int32 dot of 64 int4 x int4 products,
+ * acc += (float)(d - z*asum4) * (ws * as4). Unsplit. fma: the multiply-add contracted. */
+ORC_API int orc_gemm_w4a4(const uint8_t *codes, const uint16_t *scales, int M, int K,
+                          const uint8_t *aq4, const float *as4, const int32_t *asum4, float *y,
+                          int T, int fma) {
+    if (!codes || !scales) return -1;
+    if (!aq4 || !as4 || !asum4 || !y || T <= 0 || (T % 8) != 0) return -2;
+    const int Kt = K / 32, Kt64 = K / 64;
+#pragma omp parallel for schedule(static)
+    for (int row = 0; row < M; ++row) {
+        const int rg = row >> 4, n = row & 15;
+        const uint8_t *bbase = codes + (size_t)rg * Kt * 256u;
+        const uint16_t *sbase = scales + (size_t)rg * Kt64 * 16u;
+        for (int tok = 0; tok < T; ++tok) {
+            float acc = 0.0f;
+            for (int kg = 0; kg < Kt64; ++kg) {
+                int zp; float ws;
+                unpack_scale(sbase[(size_t)kg * 16u + n], &zp, &ws);
+                const size_t a = (size_t)kg * T + tok;
+                const uint8_t *ab = aq4 + a * 32;
+                int32_t d = 0;
+                for (int k = 0; k < 64; ++k) {
+                    const int nib = (ab[k >> 1] >> ((k & 1) * 4)) & 0xF;
+                    const int qa = nib >= 8 ? nib - 16 : nib;
+                    d += w4_code(bbase + (size_t)(2 * kg + (k >> 5)) * 256u, n, k & 31) * qa;
+                }
+                const float f = (float)(d - zp * asum4[a]);
+                const float p = ws * as4[a];
+                acc = fma ? fmaf(f, p, acc) : acc + f * p;
+            }
+            y[(size_t)tok * M + row] = acc;
+        }
+    }
+    return 0;
+}
+
 /* ------------------------------------------------------------------ shard */
 
 /* A12. x_w4_shard mode 0, xpu/src/kernels_dpas.cpp:450-499: every packed

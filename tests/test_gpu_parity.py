@@ -496,3 +496,83 @@ def test_gemm_pertoken_tcgen05(lib, pkg, orc, wl, M, K, ksh, T, bf16):
     else:
         assert y.to_numpy(np.float32).tobytes() == np.ascontiguousarray(want).tobytes()
     assert lib.tq_last_error() == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("K,T", [(256, 8), (5120, 40), (128, 136)])
+def test_quantize_act_chunk_s4(lib, pkg, orc, wl, K, T):
+    """W4A4 staging: packed int4 codes, scales and sums bit-identical to the oracle."""
+    x = wl.activations_normal(T, K, seed=K + T, outlier_frac=0.01)
+    x[0, :64] = 0.0
+    n = K // 64 * T
+    aq4, as4, asum4 = pkg.DevBuf(n * 32), pkg.DevBuf(n * 4), pkg.DevBuf(n * 4)
+    for b in (aq4, as4, asum4):
+        b.fill(0xA5)
+    dx = dev(pkg, x)
+    lib.qwn_x_quantize_act_chunk_s4(dx.ptr, K, T, aq4.ptr, as4.ptr, asum4.ptr)
+    lib.tq_sync()
+    oq, os_, osm = orc.quantize_act_chunk_s4(x)
+    assert np.array_equal(aq4.to_numpy(np.uint8), oq)
+    assert as4.to_numpy(np.float32).tobytes() == os_.tobytes()
+    assert np.array_equal(asum4.to_numpy(np.int32), osm)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,K,T", [(2048, 512, 128), (1024, 1024, 256), (2048, 256, 136)])
+def test_gemm_w4a4_tcgen05(lib, pkg, orc, wl, M, K, T):
+    """W4A4 GEMM: both k-tiles of a K64 group accumulate in TMEM, one fp32 promote per group
+    with the (token, K64) activation scale; bit-identical to the oracle (contracted
+    multiply-add), within 1e-3 of the uncontracted form. Error codes as the reference."""
+    codes, scales = wl.random_packed_weight(M, K, seed=M + K + T, ksh=1)
+    w = pkg.PackedWeight(codes, scales, M, K, k64=True)
+    x = wl.activations_normal(T, K, seed=11, outlier_frac=0.01)
+    n = K // 64 * T
+    aq4, as4, asum4 = pkg.DevBuf(n * 32), pkg.DevBuf(n * 4), pkg.DevBuf(n * 4)
+    dx = dev(pkg, x)
+    lib.qwn_x_quantize_act_chunk_s4(dx.ptr, K, T, aq4.ptr, as4.ptr, asum4.ptr)
+    y = pkg.DevBuf(T * M * 4)
+    y.fill(0xA5)
+    assert lib.qwn_x_gemm_w4a4(w.ref, aq4.ptr, as4.ptr, asum4.ptr, y.ptr, T) == 0
+    lib.tq_sync()
+    oq, os_, osm = orc.quantize_act_chunk_s4(x)
+    rc, want = orc.gemm_w4a4(codes, scales, M, K, oq, os_, osm, T, fma=1)
+    rc0, want0 = orc.gemm_w4a4(codes, scales, M, K, oq, os_, osm, T, fma=0)
+    assert rc == 0 and rc0 == 0
+    got = y.to_numpy(np.float32).reshape(T, M)
+    assert got.tobytes() == np.ascontiguousarray(want).tobytes()
+    assert close_1e3(got, want0)
+    assert lib.tq_last_error() == 0
+    # argument errors and the shapes this build does not cover
+    assert lib.qwn_x_gemm_w4a4(w.ref, aq4.ptr, as4.ptr, asum4.ptr, y.ptr, 12) == -2
+    assert lib.qwn_x_gemm_w4a4(w.ref, aq4.ptr, as4.ptr, asum4.ptr, y.ptr, 8) == -3
+    c32, s32 = wl.random_packed_weight(M, K, seed=1, ksh=0)
+    w32 = pkg.PackedWeight(c32, s32, M, K, k64=False)
+    assert lib.qwn_x_gemm_w4a4(w32.ref, aq4.ptr, as4.ptr, asum4.ptr, y.ptr, T) == -1
+
+
+@pytest.mark.gpu
+def test_overlapped_readback(lib, pkg):
+    """tq_d2h_overlapped: the copy runs behind what was queued before it, tickets come in
+    turn, tq_stream_wait_copy orders a later overwrite after the copy, tq_sync covers both
+    streams."""
+    n = 1 << 20
+    a = np.arange(n, dtype=np.int32)
+    d = dev(pkg, a)
+    host = [lib.tq_host_alloc_pinned(n * 4) for _ in range(2)]
+    try:
+        t0 = lib.tq_d2h_overlapped(host[0], d.ptr, n * 4)
+        assert 0 <= t0 < 16
+        lib.tq_stream_wait_copy(t0)          # the fill below must not overtake the copy
+        d.fill(0x11)
+        t1 = lib.tq_d2h_overlapped(host[1], d.ptr, n * 4)
+        assert t1 == (t0 + 1) % 16
+        lib.tq_sync()
+        got0 = np.ctypeslib.as_array(C.cast(host[0], C.POINTER(C.c_int32)), shape=(n,))
+        got1 = np.ctypeslib.as_array(C.cast(host[1], C.POINTER(C.c_int32)), shape=(n,))
+        assert np.array_equal(got0, a)
+        assert np.all(got1 == 0x11111111)
+        lib.tq_stream_wait_copy(-1)          # out of range: ignored
+        assert lib.tq_last_error() == 0
+    finally:
+        for h in host:
+            lib.tq_host_free_pinned(h)

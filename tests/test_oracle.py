@@ -331,3 +331,41 @@ def test_pertoken_mode(orc, wl):
     rc2, y2 = orc.gemm_w4a8(codes, scales, M, K, ksh, aq, as_, asum, T)
     assert rc == 0 and rc2 == 0
     assert np.abs(y - y2).max() <= 1e-3 * np.abs(y2).max()   # 1e-3: the stated fp32 tolerance
+
+
+def test_w4a4_staging_and_gemm(orc, wl):
+    """W4A4 (kernels_dpas.cpp:1149-1193, 1495-1571): the int4 staging rule checked against a
+    numpy restatement, and the GEMM against a float64 dense product of the dequantised
+    operands (the int32 dots are exact, so only the fp32 promote order differs)."""
+    M, K, T = 64, 256, 8
+    rng = np.random.default_rng(4)
+    x = rng.standard_normal((T, K)).astype(np.float32)
+    x[0, :64] = 0.0                                   # an all-zero block: scale 1, codes 0
+    aq4, as4, asum4 = orc.quantize_act_chunk_s4(x)
+    xb = x.reshape(T, K // 64, 64)
+    mx = np.abs(xb).max(axis=2)
+    s = np.where(mx > 0, (mx / np.float32(7.0)).astype(np.float32), np.float32(1.0)).astype(np.float32)
+    q = np.clip(np.rint(xb / s[:, :, None]), -7, 7).astype(np.int32)       # [T][Kt64][64]
+    qk = q.transpose(1, 0, 2)                                                # [Kt64][T][64]
+    packed = ((qk[:, :, 0::2] & 0xF) | ((qk[:, :, 1::2] & 0xF) << 4)).astype(np.uint8)
+    assert np.array_equal(aq4.reshape(K // 64, T, 32), packed)
+    assert as4.reshape(K // 64, T).tobytes() == np.ascontiguousarray(s.T).tobytes()
+    assert np.array_equal(asum4.reshape(K // 64, T), qk.sum(axis=2))
+
+    codes, scales = wl.random_packed_weight(M, K, seed=3, ksh=1)
+    rc, y = orc.gemm_w4a4(codes, scales, M, K, aq4, as4, asum4, T, fma=1)
+    assert rc == 0
+    rc, y0 = orc.gemm_w4a4(codes, scales, M, K, aq4, as4, asum4, T, fma=0)
+    assert rc == 0
+    qw = wl.unpack_codes(codes, M, K).astype(np.float64)
+    sc = scales.reshape(M // 16, K // 64, 16).transpose(0, 2, 1).reshape(M, K // 64)
+    z = (sc & 0xF).astype(np.int16)
+    z = np.where(z >= 8, z - 16, z).astype(np.float64)
+    ws = (sc & 0xFFF0).view(np.float16).astype(np.float64)
+    W = ((qw.reshape(M, K // 64, 64) - z[:, :, None]) * ws[:, :, None]).reshape(M, K)
+    A = (q.astype(np.float64) * s[:, :, None].astype(np.float64)).reshape(T, K)
+    dense = A @ W.T
+    scale = np.abs(dense).max()
+    assert np.abs(y - dense).max() <= 1e-5 * scale
+    assert np.abs(y0 - dense).max() <= 1e-5 * scale
+    assert orc.gemm_w4a4(codes, scales, M, K, aq4, as4, asum4, 12)[0] == -2
