@@ -85,6 +85,8 @@ struct GemvArgs {
     const int8_t *qp;        // permuted codes
     const float *as;
     const int32_t *sum32;
+    const int32_t *sum16;    // K16 tier: the two half sums per tile
+    int k16;                 // 1 = K16 scale tier (two scale lines per tile; single weight)
     const float *residual;   // single-weight only
     int K, ksh, splits;
     int serial;              // 1 = one serial accumulator (fan-out order), 0 = two accumulators

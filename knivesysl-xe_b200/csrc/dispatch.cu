@@ -51,8 +51,8 @@ int gemv_prepared_impl(const tq_qmma_weight_t *w, float *d_y, const float *d_res
     if (!w4_usable(w) || (!d_y && !dump)) return -1;
     ActScratch &s = act_scratch();
     if (s.cap < w->K || !s.q || !s.scale || s.prepared_K < w->K) return -2;
-    if (w->s4_k16) return -20;   // K16 tier is not built
     if (w->M % 16 || w->K % 32) return -1;
+    if (w->s4_k16 && (dump || d_x_fused)) return -1;   // K16: prepared activations, no dump
     GemvArgs a{};
     a.codes[0] = w->d_s4;
     a.scales[0] = w->d_s4_scale;
@@ -63,6 +63,8 @@ int gemv_prepared_impl(const tq_qmma_weight_t *w, float *d_y, const float *d_res
     a.qp = s.qp;
     a.as = s.scale;
     a.sum32 = s.sum32;
+    a.sum16 = s.sum16;
+    a.k16 = w->s4_k16 ? 1 : 0;
     a.residual = d_residual;
     a.K = w->K;
     a.ksh = w->s4_k64 ? 1 : 0;
@@ -82,7 +84,7 @@ int gemv_prepared_impl(const tq_qmma_weight_t *w, float *d_y, const float *d_res
 // launches of the reference (x_prepare_gemv_act_s8, then the prepared GEMV).
 int gemv_fused_impl(const tq_qmma_weight_t *w, const float *d_x, const float *d_residual,
                     float *d_y) {
-    if (!w4_usable(w) || w->K <= 0 || (w->K % 32)) {
+    if (!w4_usable(w) || w->K <= 0 || (w->K % 32) || w->s4_k16) {
         x_prepare_gemv_act_s8(d_x, w ? w->K : 0);
         return gemv_prepared_impl(w, d_y, d_residual, nullptr);
     }

@@ -28,12 +28,24 @@ namespace {
 
 constexpr int kW = 16;    // most warps per CTA (a launch may use fewer: blockDim.x / 32)
 constexpr int kST = 8;    // tiles per ring stage
-constexpr int kWeightBytes = kST * 256 + kST * 32;  // codes, then one 32-byte scale line per tile
-// A stage also carries its tiles' activations unless the kernel quantised the row itself:
-// 32 bytes of codes (even-k half, odd-k half) per tile, then the int32 sums, then the scales.
-constexpr int kActCodes = kWeightBytes, kActSums = kActCodes + kST * 32, kActScales = kActSums + kST * 4;
-constexpr int kActBytes = kST * 32 + kST * 8;
-__host__ __device__ constexpr int stage_bytes(bool fuseq) { return kWeightBytes + (fuseq ? 0 : kActBytes); }
+// Stage layout: codes (256 B per tile), scale lines (32 B per tile; 64 B in the K16 tier: one
+// line per half tile), and - unless the kernel quantised the row itself - the tiles'
+// activations: 32 bytes of codes (even-k half, odd-k half) per tile, the int32 code sums (one
+// per tile; the two K16 half sums in the K16 tier), the fp32 scales.
+struct StageLayout {
+    int scales, act_codes, act_sums, act_scales, bytes;
+};
+__host__ __device__ constexpr StageLayout stage_layout(bool fuseq, bool k16) {
+    const int scales = kST * 256;
+    const int act_codes = scales + kST * (k16 ? 64 : 32);
+    const int act_sums = act_codes + kST * 32;
+    const int act_scales = act_sums + kST * (k16 ? 8 : 4);
+    return StageLayout{scales, act_codes, act_sums, act_scales,
+                       fuseq ? act_codes : act_scales + kST * 4};
+}
+__host__ __device__ constexpr int stage_bytes(bool fuseq, bool k16 = false) {
+    return stage_layout(fuseq, k16).bytes;
+}
 __device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
     uint32_t v;
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
@@ -92,12 +104,18 @@ __device__ __forceinline__ int tile_dot_plus8(const uint4 &w, const uint4 &e, co
 // FUSEQ: the fp32 activation row is quantised by every CTA into shared memory (the same
 // per-block rule and code as quant_s8_kernel) after the wait on earlier kernels, instead of
 // being read from the prepared scratch; CTA 0 also writes the scratch.
-template <bool SERIAL, bool DUMP, bool FUSEQ, int NS>
+// K16: the K16 scale tier (x_gemv_w4a8_core_k16, xpu/src/kernels_dpas.cpp:683-767): two scale
+// lines per tile, each half dot promoted with its own scale and K16 sum, and ONE accumulator
+// per split (the halves of a warp pass their terms along as in the fan-out order).
+template <bool SERIAL, bool DUMP, bool FUSEQ, int NS, bool K16 = false>
 __global__ void __launch_bounds__(kW * 32, 2) gemv_w4a8_kernel(const GemvArgs a) {
     __shared__ float part[kW * 16];
     // ring[warps][NS][kStageBytes], then (FUSEQ) qp[K], as[K/32], sum32[K/32]
     const int nw = blockDim.x >> 5;
-    constexpr int kStageBytes = stage_bytes(FUSEQ);
+    constexpr StageLayout L = stage_layout(FUSEQ, K16);
+    constexpr int kStageBytes = L.bytes;
+    constexpr int kActCodes = L.act_codes, kActSums = L.act_sums, kActScales = L.act_scales;
+    constexpr bool ORDERED = SERIAL || K16;      // one accumulator, terms added in tile order
     extern __shared__ __align__(16) unsigned char dyn[];
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -130,7 +148,9 @@ __global__ void __launch_bounds__(kW * 32, 2) gemv_w4a8_kernel(const GemvArgs a)
             while (wi + 1 < a.count && pg >= a.goff[wi + 1]) ++wi;
             const int lg = pg - a.goff[wi];
             psrc = a.codes[wi] + ((size_t)lg * Kt + kt_begin) * 256u + lane * 16;
-            pscl = a.scales[wi] + (size_t)lg * Ktg * 16u + (lane & 1) * 8;
+            // K16: two 32-byte lines per tile, lane l copies piece l of the stage's 8 x 64 bytes
+            pscl = K16 ? a.scales[wi] + (size_t)lg * (Kt * 2) * 16u + lane * 8
+                       : a.scales[wi] + (size_t)lg * Ktg * 16u + (lane & 1) * 8;
         }
     };
     producer_group();
@@ -140,18 +160,21 @@ __global__ void __launch_bounds__(kW * 32, 2) gemv_w4a8_kernel(const GemvArgs a)
     auto issue_weights = [&]() {
         if (pg < groups && cnt > 0) {
             const int left = cnt - pi0;
-            const uint16_t *sl = pscl + (size_t)((kt_begin + pi0 + (lane >> 1)) >> a.ksh) * 16u;
+            const uint16_t *sl =
+                K16 ? pscl + (size_t)(kt_begin + pi0) * 32u
+                    : pscl + (size_t)((kt_begin + pi0 + (lane >> 1)) >> a.ksh) * 16u;
+            constexpr int kPieces = K16 ? 4 : 2;      // 16-byte scale pieces per tile
             if (left >= kST) {
 #pragma unroll
                 for (int p = 0; p < kST / 2; ++p)
                     cp_async16(pdst + lane * 16 + p * 512, psrc + p * 512, pol);
-                if (lane < 2 * kST) cp_async16(pdst + kST * 256 + lane * 16, sl, pol);
+                if (lane < kPieces * kST) cp_async16(pdst + kST * 256 + lane * 16, sl, pol);
             } else {
 #pragma unroll
                 for (int p = 0; p < kST / 2; ++p)
                     if (lane + 32 * p < left * 16)
                         cp_async16(pdst + lane * 16 + p * 512, psrc + p * 512, pol);
-                if (lane < 2 * left) cp_async16(pdst + kST * 256 + lane * 16, sl, pol);
+                if (lane < kPieces * left) cp_async16(pdst + kST * 256 + lane * 16, sl, pol);
             }
         }
     };
@@ -164,12 +187,17 @@ __global__ void __launch_bounds__(kW * 32, 2) gemv_w4a8_kernel(const GemvArgs a)
                     // codes of tile lane/2, half lane%2
                     if (lane < 2 * nt)
                         cp_async16_plain(pdst + kActCodes + lane * 16, a.qp + (size_t)kt0 * 32 + lane * 16);
+                } else if (K16) {
+                    // lanes 16..31: the two K16 sums of tile (lane - 16) / 2
+                    if (lane - 16 < 2 * nt)
+                        cp_async4(pdst + kActSums + (lane - 16) * 4, a.sum16 + 2 * kt0 + (lane - 16));
                 } else if ((lane & 7) < nt) {
                     // lanes 16..23: int32 sums, lanes 24..31: scales (adjacent in the stage)
                     const void *src = lane < 24 ? static_cast<const void *>(a.sum32 + kt0 + (lane - 16))
                                                 : static_cast<const void *>(a.as + kt0 + (lane - 24));
                     cp_async4(pdst + kActSums + (lane - 16) * 4, src);
                 }
+                if (K16 && lane < nt) cp_async4(pdst + kActScales + lane * 4, a.as + kt0 + lane);
             }
             pi0 += kST;
             psrc += kST * 256;
@@ -243,11 +271,11 @@ __global__ void __launch_bounds__(kW * 32, 2) gemv_w4a8_kernel(const GemvArgs a)
     // constant offsets from the per-stage bases.
     uint32_t cst = ring_s;
     const uint32_t lane_w = h * 256 + n * 16;              // this lane's row in tile h
-    const uint32_t lane_s = kST * 256 + h * 32 + n * 2;    // and its scale word
+    const uint32_t lane_s = kST * 256 + h * (K16 ? 64 : 32) + n * 2;    // and its scale word
     // ea: even-k codes of the tile (odd-k at +16); sa / fa_: its int32 sum and fp32 scale
     auto pair_step = [&](uint32_t wl, uint32_t sl, uint32_t ea, uint32_t sa, uint32_t fa_,
                          int32_t *dmp, bool valid, bool odd_valid, float &acc) {
-        float fa = 0.0f, fb = 0.0f;
+        float fa = 0.0f, fb = 0.0f, fa2 = 0.0f;      // fa2: the high half's term (K16)
         if (valid) {
             const uint4 wv = lds_v4(wl);
             const uint32_t sc = lds_u16(sl);
@@ -255,23 +283,51 @@ __global__ void __launch_bounds__(kW * 32, 2) gemv_w4a8_kernel(const GemvArgs a)
             const uint4 o = lds_v4(ea + 16);
             const int asum = (int)lds_u32(sa);
             fb = __uint_as_float(lds_u32(fa_));
-            const int dp = tile_dot_plus8(wv, e, o);
             int zp;
             float ws;
             unpack_scale(sc, zp, ws);
-            if (DUMP) *dmp = dp - 8 * asum;
-            const float f = (float)(dp - (zp + 8) * asum);
-            fa = __fmul_rn(f, ws);
+            if (K16) {
+                // k 0..15 = words x, y; k 16..31 = words z, w: each half has its own scale
+                // line (the second one 32 bytes on) and its own K16 sum (4 bytes on)
+                int lo = __dp4a((int)nib_plus8(wv.x), (int)e.x, 0);
+                lo = __dp4a((int)nib_plus8(wv.y), (int)e.y, lo);
+                int hi = dp4a_u8s8(nib_hi_plus8_x16(wv.x), o.x, 0);
+                hi = dp4a_u8s8(nib_hi_plus8_x16(wv.y), o.y, hi);
+                const float f = (float)(lo + (hi >> 4) - (zp + 8) * asum);
+                fa = __fmul_rn(f, ws);
+                int lo2 = __dp4a((int)nib_plus8(wv.z), (int)e.z, 0);
+                lo2 = __dp4a((int)nib_plus8(wv.w), (int)e.w, lo2);
+                int hi2 = dp4a_u8s8(nib_hi_plus8_x16(wv.z), o.z, 0);
+                hi2 = dp4a_u8s8(nib_hi_plus8_x16(wv.w), o.w, hi2);
+                int zp2;
+                float ws2;
+                unpack_scale(lds_u16(sl + 32), zp2, ws2);
+                const int asum2 = (int)lds_u32(sa + 4);
+                const float f2 = (float)(lo2 + (hi2 >> 4) - (zp2 + 8) * asum2);
+                fa2 = __fmul_rn(f2, ws2);
+            } else {
+                const int dp = tile_dot_plus8(wv, e, o);
+                if (DUMP) *dmp = dp - 8 * asum;
+                const float f = (float)(dp - (zp + 8) * asum);
+                fa = __fmul_rn(f, ws);
+            }
         }
-        if (!SERIAL) {
+        if (!ORDERED) {
             if (valid) acc = fmaf(fa, fb, acc);
         } else {
             // pair (even tile on h == 0, odd tile on h == 1), added in tile order
             const float oa = __shfl_down_sync(0xffffffffu, fa, 16);
             const float ob = __shfl_down_sync(0xffffffffu, fb, 16);
+            const float oa2 = K16 ? __shfl_down_sync(0xffffffffu, fa2, 16) : 0.0f;
             if (h == 0) {
-                if (valid) acc = fmaf(fa, fb, acc);
-                if (odd_valid) acc = fmaf(oa, ob, acc);
+                if (valid) {
+                    acc = fmaf(fa, fb, acc);
+                    if (K16) acc = fmaf(fa2, fb, acc);
+                }
+                if (odd_valid) {
+                    acc = fmaf(oa, ob, acc);
+                    if (K16) acc = fmaf(oa2, ob, acc);
+                }
             }
         }
     };
@@ -292,14 +348,15 @@ __global__ void __launch_bounds__(kW * 32, 2) gemv_w4a8_kernel(const GemvArgs a)
             issue_weights();
             finish_stage();
             const uint32_t wl = cst + lane_w, sl = cst + lane_s;
+            constexpr int kSclPair = K16 ? 128 : 64, kSumPair = K16 ? 16 : 8;   // per tile pair
             // activations of tile h of this stage, and the distance between tile pairs
             const uint32_t ea = FUSEQ ? fe : cst + kActCodes + h * 32;
-            const uint32_t sa = FUSEQ ? fs : cst + kActSums + h * 4;
+            const uint32_t sa = FUSEQ ? fs : cst + kActSums + h * (K16 ? 8 : 4);
             const uint32_t fa_ = FUSEQ ? ff : cst + kActScales + h * 4;
             if (left >= kST) {
 #pragma unroll
                 for (int u = 0; u < kST / 2; ++u)
-                    pair_step(wl + u * 512, sl + u * 64, ea + u * 64, sa + u * 8, fa_ + u * 8,
+                    pair_step(wl + u * 512, sl + u * kSclPair, ea + u * 64, sa + u * kSumPair, fa_ + u * 8,
                               DUMP ? dmp + u * 32 : nullptr, true, true, acc);
             } else {
                 // last, short stage of the split: the same steps behind warp-uniform tests,
@@ -307,7 +364,7 @@ __global__ void __launch_bounds__(kW * 32, 2) gemv_w4a8_kernel(const GemvArgs a)
 #pragma unroll
                 for (int u = 0; u < kST / 2; ++u)
                     if (2 * u < left)
-                        pair_step(wl + u * 512, sl + u * 64, ea + u * 64, sa + u * 8, fa_ + u * 8,
+                        pair_step(wl + u * 512, sl + u * kSclPair, ea + u * 64, sa + u * kSumPair, fa_ + u * 8,
                                   DUMP ? dmp + u * 32 : nullptr, 2 * u + h < left, 2 * u + 1 < left,
                                   acc);
             }
@@ -318,7 +375,7 @@ __global__ void __launch_bounds__(kW * 32, 2) gemv_w4a8_kernel(const GemvArgs a)
             if (DUMP) dmp += kST * 16;
         }
         if (DUMP) continue;
-        if (!SERIAL) acc = __fadd_rn(acc, __shfl_down_sync(0xffffffffu, acc, 16));
+        if (!ORDERED) acc = __fadd_rn(acc, __shfl_down_sync(0xffffffffu, acc, 16));
 
         const int row = lg * 16 + n;
         if (S == 1) {
@@ -384,7 +441,18 @@ void launch_gemv(const GemvArgs &a) {
                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPerCta));
         attr = true;
     }
-    if (a.dump)
+    if (a.k16 && !a.dump) {
+        // K16 tier: prepared activations only (a fused-quantiser call prepares first)
+        constexpr size_t kRingK16 = (size_t)kW * 2 * stage_bytes(false, true);
+        static_assert(kRingK16 <= kPerCta, "K16 ring too large for two CTAs per SM");
+        static bool attr16 = false;
+        if (!attr16) {
+            TQ_CHECK(cudaFuncSetAttribute(gemv_w4a8_kernel<false, false, false, 2, true>,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingK16));
+            attr16 = true;
+        }
+        launch_pdl(gemv_w4a8_kernel<false, false, false, 2, true>, dim3(grid), dim3(kW * 32), kRingK16, a);
+    } else if (a.dump)
         launch_pdl(gemv_w4a8_kernel<false, true, false, 2>, dim3(grid), dim3(kW * 32), kRingP, a);
     else if (a.serial)
         launch_pdl(gemv_w4a8_kernel<true, false, false, 2>, dim3(grid), dim3(kW * 32), kRingP, a);

@@ -68,12 +68,12 @@ def make_weight_w4(M: int, K: int, seed: int, group: int = 32, chunk_rows: int =
     return np.concatenate(codes), np.concatenate(scales)
 
 
-def random_packed_weight(M: int, K: int, seed: int, ksh: int = 0):
+def random_packed_weight(M: int, K: int, seed: int, ksh: int = 0, k16: bool = False):
     """Arbitrary codes, positive normal FP16 scales with every zero point -8..7 and some
     zero scales: the pattern of the reference's fan-out probe (xpu/probe/fanout_bench.cpp:
     66-77), driven by its LCG."""
     n_codes = M * K // 2
-    n_scales = M * ((K // 32) >> ksh)
+    n_scales = M * (K // 16) if k16 else M * ((K // 32) >> ksh)
     state = np.uint32(391 + seed)
     # vectorised LCG: x_{n} = a^n x0 + c (a^n - 1)/(a - 1) is awkward in uint32, so use numpy's
     # generator for bulk values and keep the scale pattern itself exact

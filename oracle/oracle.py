@@ -236,6 +236,17 @@ def gemv_w4a8(codes, scales, M, K, ksh, q, as_, sum16, residual=None, fma=1):
     return rc, y
 
 
+def gemv_w4a8_k16(codes, scales, M, K, q, as_, sum16, residual=None, fma=1):
+    codes, scales = _c(codes, np.uint8), _c(scales, np.uint16)
+    q, as_, sum16 = _c(q, np.int8), _c(as_, np.float32), _c(sum16, np.int32)
+    res = _c(residual, np.float32) if residual is not None else None
+    y = np.empty(M, dtype=np.float32)
+    rc = lib().orc_gemv_w4a8_k16(_p(codes), _p(scales), C.c_int(M), C.c_int(K), _p(q), _p(as_),
+                                 _p(sum16), _p(res) if res is not None else None, _p(y), C.c_int(fma))
+    assert rc == 0, rc
+    return y
+
+
 def gemv_w4a8_fanout(weights, K, ksh, q, as_, sum16, fma=1):
     """weights: list of (codes, scales, M)."""
     n = len(weights)

@@ -624,6 +624,50 @@ ORC_API int orc_gemv_w4a8(const uint8_t *codes, const uint16_t *scales, int M, i
     return 0;
 }
 
+/* K16 tier GEMV, x_gemv_w4a8_core_k16 (xpu/src/kernels_dpas.cpp:683-767) under
+ * x_gemv_w4a8_prepared_impl (1631-1662): scales[Mt][Kt*2][16], one packed scale per (row,
+ * 16 codes). Per tile the two half dots (k 0..15 and 16..31) are promoted separately with
+ * their own scale, zero point and K16 code sum, into ONE accumulator per split:
+ * acc += ((float)(d_lo - z_lo*sum16[2kt]) * ws_lo) * as[kt]; then the same for the high
+ * half. Splits are summed 0..S-1 from 0.0f, + residual (or + 0.0f); S == 1 stores the
+ * accumulator and adds a residual separately. */
+ORC_API int orc_gemv_w4a8_k16(const uint8_t *codes, const uint16_t *scales, int M, int K,
+                              const int8_t *q, const float *as, const int32_t *sum16,
+                              const float *residual, float *y, int fma) {
+    if (!codes || !scales || !y || M % 16 || K % 32) return -1;
+    const int Kt = K / 32, groups = M / 16;
+    const int splits = orc_choose_gemv_splits(groups);
+#pragma omp parallel for schedule(static)
+    for (int g = 0; g < groups; ++g) {
+        const uint8_t *bbase = codes + (size_t)g * Kt * 256u;
+        const uint16_t *sbase = scales + (size_t)g * (Kt * 2) * 16u;
+        for (int n = 0; n < 16; ++n) {
+            const int row = g * 16 + n;
+            float sum = 0.0f, acc = 0.0f;
+            for (int s = 0; s < splits; ++s) {
+                acc = 0.0f;
+                for (int kt = Kt * s / splits; kt < Kt * (s + 1) / splits; ++kt) {
+                    const uint8_t *tile = bbase + (size_t)kt * 256u;
+                    for (int half = 0; half < 2; ++half) {
+                        int zp; float ws;
+                        unpack_scale(sbase[(size_t)(kt * 2 + half) * 16u + n], &zp, &ws);
+                        int32_t d = 0;
+                        for (int k = 16 * half; k < 16 * half + 16; ++k)
+                            d += w4_code(tile, n, k) * (int32_t)q[(size_t)kt * 32 + k];
+                        const float f = (float)(d - zp * sum16[2 * kt + half]);
+                        if (fma) acc = fmaf(f * ws, as[kt], acc);
+                        else acc += f * ws * as[kt];
+                    }
+                }
+                sum += acc;
+            }
+            if (splits == 1) y[row] = residual ? acc + residual[row] : acc;
+            else y[row] = sum + (residual ? residual[row] : 0.0f);
+        }
+    }
+    return 0;
+}
+
 /* A8. x_gemv_w4a8_fanout, xpu/src/kernels_dpas.cpp:945-1102. Up to four
  * weights share K, ksh and one quantised activation; the split count comes from
  * the total row-group count. Returns -1/-2 like the reference (the scratch

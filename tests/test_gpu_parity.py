@@ -272,6 +272,41 @@ def test_gemv_fanout(lib, pkg, orc, wl, Ms, K, ksh):
         assert close_1e3(got, w0)
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,K,res", [(64, 256, False), (48, 384, True), (16, 128, True), (272, 5120, False),
+                                     (5120, 1056, True), (65536 + 16, 64, True)])
+def test_gemv_k16_tier(lib, pkg, orc, wl, M, K, res):
+    """K16 scale tier (x_gemv_w4a8_core_k16): one scale, zero point and code sum per 16 codes,
+    one accumulator per split; x_gemv_w4a8(_add) and the x_gemv_qmma shim route to it.
+    Bit-identical to the oracle (contracted form), within 1e-3 of the uncontracted one."""
+    codes, scales = wl.random_packed_weight(M, K, seed=M + K, k16=True)
+    w = pkg.PackedWeight(codes, scales, M, K, k16=True)
+    x = refgen.lcg_floats(K, seed=17 + M)[0]
+    x[:16] = 0.0
+    dx = dev(pkg, x)
+    r = refgen.lcg_floats(M, seed=5)[0] if res else None
+    dr = dev(pkg, r) if res else None
+    y = pkg.DevBuf(M * 4)
+    y.fill(0xA5)
+    if res:
+        assert lib.qwn_x_gemv_w4a8_add(w.ref, dx.ptr, dr.ptr, y.ptr) == 0
+    else:
+        assert lib.qwn_x_gemv_qmma(w.ref, dx.ptr, y.ptr) == 0
+    lib.tq_sync()
+    q, s, sm = orc.quantize_act_s8(x)
+    want = orc.gemv_w4a8_k16(codes, scales, M, K, q, s, sm, residual=r, fma=1)
+    want0 = orc.gemv_w4a8_k16(codes, scales, M, K, q, s, sm, residual=r, fma=0)
+    got = y.to_numpy(np.float32)
+    assert got.tobytes() == want.tobytes()
+    assert close_1e3(got, want0)
+    # the prepared form gives the same bits; the GEMM does not take this tier
+    y2 = pkg.DevBuf(M * 4)
+    assert lib.qwn_x_gemv_w4a8_prepared(w.ref, y2.ptr, dr.ptr if res else None) == 0
+    lib.tq_sync()
+    assert y2.to_numpy(np.float32).tobytes() == want.tobytes()
+    assert lib.tq_last_error() == 0
+
+
 def test_gemv_errors(lib, pkg, wl):
     M, K = 32, 128
     c, s = wl.random_packed_weight(M, K, seed=1)

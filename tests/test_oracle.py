@@ -369,3 +369,30 @@ def test_w4a4_staging_and_gemm(orc, wl):
     assert np.abs(y - dense).max() <= 1e-5 * scale
     assert np.abs(y0 - dense).max() <= 1e-5 * scale
     assert orc.gemm_w4a4(codes, scales, M, K, aq4, as4, asum4, 12)[0] == -2
+
+
+def test_k16_tier_gemv(orc, wl):
+    """K16 tier (kernels_dpas.cpp:683-767) against a float64 dense product with one scale and
+    zero point per 16 codes, and against the K32 GEMV when both halves share their scale."""
+    M, K = 48, 512
+    codes, s16 = wl.random_packed_weight(M, K, seed=8, k16=True)
+    x = np.random.default_rng(2).standard_normal(K).astype(np.float32)
+    q, as_, sm = orc.quantize_act_s8(x)
+    y = orc.gemv_w4a8_k16(codes, s16, M, K, q, as_, sm)
+    qw = wl.unpack_codes(codes, M, K).astype(np.float64)
+    sc = s16.reshape(M // 16, K // 16, 16).transpose(0, 2, 1).reshape(M, K // 16)
+    z = (sc & 0xF).astype(np.int16)
+    z = np.where(z >= 8, z - 16, z).astype(np.float64)
+    ws = (sc & 0xFFF0).view(np.float16).astype(np.float64)
+    W = ((qw.reshape(M, K // 16, 16) - z[:, :, None]) * ws[:, :, None]).reshape(M, K)
+    xd = (q.astype(np.float64).reshape(-1, 32) * as_.astype(np.float64)[:, None]).reshape(K)
+    dense = W @ xd
+    assert np.abs(y - dense).max() <= 1e-5 * np.abs(dense).max()
+    # same scale on both halves of every tile: the K32 tier's value up to summation order
+    s32 = sc.reshape(M, K // 32, 2)[:, :, 0]
+    s16b = np.repeat(s32, 2, axis=1)
+    pk16 = np.ascontiguousarray(s16b.reshape(M // 16, 16, K // 16).transpose(0, 2, 1)).reshape(-1)
+    pk32 = np.ascontiguousarray(s32.reshape(M // 16, 16, K // 32).transpose(0, 2, 1)).reshape(-1)
+    ya = orc.gemv_w4a8_k16(codes, pk16, M, K, q, as_, sm)
+    _, yb = orc.gemv_w4a8(codes, pk32, M, K, 0, q, as_, sm)
+    assert np.abs(ya - yb).max() <= 1e-4 * max(np.abs(yb).max(), 1e-6)
