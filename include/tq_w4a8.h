@@ -129,8 +129,23 @@ int qwn_x_gemv_w4a8_prepared(const tq_qmma_weight_t *w, float *d_y, const float 
  * activation in one launch. Returns 0, -1, -2 (tier/K mismatch), -3 (not prepared). */
 int qwn_x_gemv_w4a8_fanout(const tq_qmma_weight_t *const *ws, float *const *ys, int count);
 
-/* xpu/src/kernels_core.cpp:164-252: tier dispatchers used by the layer bodies. Only the
- * W4 K32/K64 tiers exist here; other tiers return -20. */
+/* W8A8 tier (xpu/src/kernels_dpas.cpp:345-395, 558-573, 768-843, 1578-1629, 1682-1726): int8
+ * weights d_s8[Mt][Kt][16 rows][32 B] with one plain FP16 scale per (row, K32)
+ * d_s8_scale[Mt][Kt][16], no zero point; activations are the W4A8 staging. The repack takes
+ * the E2M3 payload like x_w4_repack_weight and sets s8_ready. GEMV: the W4A8 GEMV's two
+ * accumulators and split order with term ((float)d * ws) * as[kt]; GEMM: unsplit, one
+ * accumulator, (float)d * (ws * as[kt][tok]). Error codes as the W4 entry points. */
+int qwn_x_w8_repack_weight(tq_qmma_weight_t *w);
+int qwn_x_gemv_w8a8(const tq_qmma_weight_t *w, const float *d_x, float *d_y);
+int qwn_x_gemv_w8a8_add(const tq_qmma_weight_t *w, const float *d_x, const float *d_residual,
+                        float *d_y);
+int qwn_x_gemv_w8a8_prepared(const tq_qmma_weight_t *w, float *d_y, const float *d_residual);
+int qwn_x_gemm_w8a8(const tq_qmma_weight_t *w, const int8_t *d_aq, const float *d_as, float *d_y,
+                    int T);
+
+/* xpu/src/kernels_core.cpp:164-252: tier dispatchers used by the layer bodies: s8_ready
+ * weights go to the W8A8 GEMV, s4_ready ones (K16, K32 or K64 scales) to the W4A8 GEMV; the
+ * scalar E2M3 tier is not built (-20). */
 int qwn_x_gemv_qmma(const tq_qmma_weight_t *w, const float *d_x, float *d_y);
 int qwn_x_gemv_qmma_add(const tq_qmma_weight_t *w, const float *d_x, const float *d_residual,
                         float *d_y);
@@ -296,6 +311,11 @@ void x_quantize_act_chunk_pertoken(const float *d_x, int K, int T, int8_t *d_aq,
                                    int32_t *d_asum, float *d_as_tok);
 int x_gemm_w4a8_pertoken(const tq_qmma_weight_t *w, const int8_t *d_aq, const float *d_as_tok,
                          const int32_t *d_asum, void *d_y, int T, int out_bf16 = 0);
+int x_w8_repack_weight(tq_qmma_weight_t *w);
+int x_gemv_w8a8(const tq_qmma_weight_t *w, const float *d_x, float *d_y);
+int x_gemv_w8a8_add(const tq_qmma_weight_t *w, const float *d_x, const float *d_residual, float *d_y);
+int x_gemv_w8a8_prepared(const tq_qmma_weight_t *w, float *d_y, const float *d_residual = nullptr);
+int x_gemm_w8a8(const tq_qmma_weight_t *w, const int8_t *d_aq, const float *d_as, float *d_y, int T);
 void x_quantize_act_chunk_s4(const float *d_x, int K, int T, uint8_t *d_aq4, float *d_as4,
                              int32_t *d_asum4);
 int x_gemm_w4a4(const tq_qmma_weight_t *w, const uint8_t *d_aq4, const float *d_as4,

@@ -14,7 +14,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libforward_qwen_xpu.so")
 
 SOURCES = ["runtime.cu", "quant.cu", "repack.cu", "gemv.cu", "gemm_mma.cu", "gemm_stream.cu", "gemm_tc.cu",
-           "dispatch.cu", "checks.cu", "comm.cu", "gemv_static.cu"]
+           "dispatch.cu", "checks.cu", "comm.cu", "gemv_static.cu", "w8a8.cu"]
 
 NVCC_FLAGS = [
     "-O3", "-std=c++17", "-lineinfo",

@@ -7,7 +7,8 @@
 Cases: cfg1 (GEMV 17408x5120 K32), gemv_down (GEMV 5120x17408), cfg2 (fused gate+up K64,
 T=8), down_t8 / down_t16 / down_t32 / down_t64 (5120x17408 K32), prefill_small (tcgen05 GEMM
 2048x5120, T=1024), cfg4 (tcgen05 GEMM 17408x5120 K64, T=4096 in 4 segments), cfg4_w4a4 (the
-same shape through x_gemm_w4a4: int4 activations, one promote per K64 group).
+same shape through x_gemm_w4a4: int4 activations, one promote per K64 group), w8_lm_head (W8A8
+GEMV 151936x5120, 803 MB of weights: no rotation needed).
 Weights are seeded random codes and scales: timing does not depend on their values.
 """
 from __future__ import annotations
@@ -79,6 +80,29 @@ class Gemm:
         assert rc == 0, rc
 
 
+class GemvW8:
+    """x_gemv_w8a8_prepared on one int8 weight (random codes, FP16 scales): the lm_head tier."""
+
+    def __init__(self, lib, M, K):
+        self.lib = lib
+        rng = np.random.default_rng(5)
+        codes = rng.integers(0, 256, size=M * K, dtype=np.uint8)
+        scales = (0x2400 + rng.integers(0, 64, size=M * (K // 32), dtype=np.uint16) * 16).astype(np.uint16)
+        self.codes, self.scales = pkg.DevBuf.from_numpy(codes), pkg.DevBuf.from_numpy(scales)
+        self.rec = pkg.TqWeight()
+        self.rec.M, self.rec.K, self.rec.Mt, self.rec.Kt = M, K, M // 16, K // 32
+        self.rec.d_s8, self.rec.d_s8_scale, self.rec.s8_ready = self.codes.ptr, self.scales.ptr, 1
+        x = np.random.default_rng(1).standard_normal(K).astype(np.float32)
+        self.dx = pkg.DevBuf.from_numpy(x)
+        self.y = pkg.DevBuf(M * 4)
+        lib.qwn_x_prepare_gemv_act_s8(self.dx.ptr, K)
+        self.bytes = codes.nbytes + scales.nbytes
+        self.ops = 2.0 * M * K
+
+    def launch(self, i):
+        assert self.lib.qwn_x_gemv_w8a8_prepared(C.byref(self.rec), self.y.ptr, None) == 0
+
+
 class GemmW4A4:
     """x_gemm_w4a4 on one K64 weight (int4 activations per (token, K64))."""
 
@@ -111,6 +135,7 @@ CASES = {
     "prefill_small": lambda lib: Gemm(lib, [2048], 5120, True, 1024, rot=1),
     "cfg4": lambda lib: Gemm(lib, [17408], 5120, True, 4096, segments=4, rot=1),
     "cfg4_w4a4": lambda lib: GemmW4A4(lib, 17408, 5120, 4096),
+    "w8_lm_head": lambda lib: GemvW8(lib, 151936, 5120),
 }
 
 

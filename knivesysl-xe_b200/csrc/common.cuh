@@ -160,6 +160,14 @@ int launch_gemm_tc(const GemmTcArgs &a);   // returns 0, or <0 when the shape is
 void launch_w4_repack(const uint8_t *d_payload, const float *d_bs, int scale_cols, int M, int K,
                       int mode, uint8_t *d_codes, uint16_t *d_scales);
 
+// w8a8.cu / repack.cu (W8A8 tier)
+void launch_w8_repack(const uint8_t *d_payload, const float *d_bs, int scale_cols, int M, int K,
+                      uint8_t *d_codes, uint16_t *d_scales);
+void launch_gemv_w8a8(const uint8_t *codes, const uint16_t *scales, const int8_t *q,
+                      const float *as, const float *residual, float *y, int M, int K, int splits);
+void launch_gemm_w8a8(const uint8_t *codes, const uint16_t *scales, const int8_t *aq,
+                      const float *as, float *y, int M, int K, int T);
+
 // ---- device helpers ---------------------------------------------------------------
 #ifdef __CUDACC__
 

@@ -247,11 +247,59 @@ int x_gemv_w4a8_fanout(const tq_qmma_weight_t *const *ws, float *const *ys, int 
     return 0;
 }
 
+// ---- W8A8 tier (xpu/src/kernels_dpas.cpp:558-573, 768-843, 1578-1629, 1682-1726) --------
+int x_w8_repack_weight(tq_qmma_weight_t *w) {
+    if (!w || !w->d_A || !w->d_block_scale_inv || !w->block_scaled || !w->e2m3) return -1;
+    if (w->M % 16 || w->K % 128) return -2;
+    w->d_s8 = static_cast<uint8_t *>(tq_dev_alloc((size_t)w->Mt * w->Kt * 512u, "w8.codes"));
+    w->d_s8_scale =
+        static_cast<uint16_t *>(tq_dev_alloc((size_t)w->M * w->Kt * sizeof(uint16_t), "w8.scales"));
+    launch_w8_repack(w->d_A, w->d_block_scale_inv, w->scale_cols, w->M, w->K, w->d_s8, w->d_s8_scale);
+    tq_sync();
+    tq_dev_free(w->d_A);
+    tq_dev_free(w->d_block_scale_inv);
+    w->d_A = nullptr;
+    w->d_block_scale_inv = nullptr;
+    w->s8_ready = 1;
+    return 0;
+}
+
+int x_gemv_w8a8_prepared(const tq_qmma_weight_t *w, float *d_y, const float *d_residual) {
+    if (!w || !w->s8_ready || !w->d_s8 || !w->d_s8_scale || !d_y) return -1;
+    ActScratch &s = act_scratch();
+    if (s.cap < w->K || !s.q || !s.scale || s.prepared_K < w->K) return -2;
+    if (w->M % 16 || w->K % 32) return -1;
+    launch_gemv_w8a8(w->d_s8, w->d_s8_scale, s.q, s.scale, d_residual, d_y, w->M, w->K,
+                     choose_gemv_splits(w->M / 16));
+    return 0;
+}
+
+int x_gemv_w8a8(const tq_qmma_weight_t *w, const float *d_x, float *d_y) {
+    if (!w || !d_x) return -1;
+    x_prepare_gemv_act_s8(d_x, w->K);
+    return x_gemv_w8a8_prepared(w, d_y, nullptr);
+}
+
+int x_gemv_w8a8_add(const tq_qmma_weight_t *w, const float *d_x, const float *d_residual,
+                    float *d_y) {
+    if (!w || !d_x || !d_residual) return -1;
+    x_prepare_gemv_act_s8(d_x, w->K);
+    return x_gemv_w8a8_prepared(w, d_y, d_residual);
+}
+
+int x_gemm_w8a8(const tq_qmma_weight_t *w, const int8_t *d_aq, const float *d_as, float *d_y,
+                int T) {
+    if (!w || !w->s8_ready || !w->d_s8 || !w->d_s8_scale) return -1;
+    if (!d_aq || !d_as || !d_y || T <= 0 || (T % 8) != 0) return -2;
+    launch_gemm_w8a8(w->d_s8, w->d_s8_scale, d_aq, d_as, d_y, w->M, w->K, T);
+    return 0;
+}
+
 // ---- tier dispatchers (xpu/src/kernels_core.cpp:164-252) -------------------------------
 int x_gemv_qmma(const tq_qmma_weight_t *w, const float *d_x, float *d_y) {
     if (!w || !d_x || !d_y) return -1;
     if (w->M <= 0 || w->K <= 0 || w->Mt <= 0 || w->Kt <= 0) return -2;
-    if (w->s8_ready) return -20;              // W8A8 tier is not built
+    if (w->s8_ready) return x_gemv_w8a8(w, d_x, d_y);
     if (w->s4_ready) return x_gemv_w4a8(w, d_x, d_y);
     return -20;                               // scalar E2M3 tier is not built
 }
@@ -259,7 +307,7 @@ int x_gemv_qmma(const tq_qmma_weight_t *w, const float *d_x, float *d_y) {
 int x_gemv_qmma_add(const tq_qmma_weight_t *w, const float *d_x, const float *d_residual,
                     float *d_y) {
     if (!w || !d_x || !d_residual || !d_y) return -1;
-    if (w->s8_ready) return -20;
+    if (w->s8_ready) return x_gemv_w8a8_add(w, d_x, d_residual, d_y);
     if (w->s4_ready) return x_gemv_w4a8_add(w, d_x, d_residual, d_y);
     return -20;
 }
@@ -267,7 +315,7 @@ int x_gemv_qmma_add(const tq_qmma_weight_t *w, const float *d_x, const float *d_
 int x_gemv_qmma_prepared(const tq_qmma_weight_t *w, const float *d_x, float *d_y,
                          const float *d_residual) {
     if (!w || !d_x || !d_y) return -1;
-    if (w->s8_ready) return -20;
+    if (w->s8_ready) return x_gemv_w8a8_prepared(w, d_y, d_residual);
     if (w->s4_ready) return x_gemv_w4a8_prepared(w, d_y, d_residual);
     return -20;
 }
@@ -518,6 +566,21 @@ int qwn_x_gemv_w4a8_prepared(const tq_qmma_weight_t *w, float *d_y, const float 
 }
 int qwn_x_gemv_w4a8_fanout(const tq_qmma_weight_t *const *ws, float *const *ys, int count) {
     return x_gemv_w4a8_fanout(ws, ys, count);
+}
+int qwn_x_w8_repack_weight(tq_qmma_weight_t *w) { return x_w8_repack_weight(w); }
+int qwn_x_gemv_w8a8(const tq_qmma_weight_t *w, const float *d_x, float *d_y) {
+    return x_gemv_w8a8(w, d_x, d_y);
+}
+int qwn_x_gemv_w8a8_add(const tq_qmma_weight_t *w, const float *d_x, const float *d_residual,
+                        float *d_y) {
+    return x_gemv_w8a8_add(w, d_x, d_residual, d_y);
+}
+int qwn_x_gemv_w8a8_prepared(const tq_qmma_weight_t *w, float *d_y, const float *d_residual) {
+    return x_gemv_w8a8_prepared(w, d_y, d_residual);
+}
+int qwn_x_gemm_w8a8(const tq_qmma_weight_t *w, const int8_t *d_aq, const float *d_as, float *d_y,
+                    int T) {
+    return x_gemm_w8a8(w, d_aq, d_as, d_y, T);
 }
 int qwn_x_gemv_qmma(const tq_qmma_weight_t *w, const float *d_x, float *d_y) {
     return x_gemv_qmma(w, d_x, d_y);

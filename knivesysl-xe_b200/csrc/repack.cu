@@ -126,7 +126,54 @@ w4_repack_kernel(const uint8_t *__restrict__ payload, const float *__restrict__ 
     }
 }
 
+// E2M3 -> symmetric int8 with one plain FP16 scale per (row, K32): w8_repack_kernel,
+// xpu/src/kernels_dpas.cpp:348-395. codes[Mt][Kt][16 rows][32 B], scales[Mt][Kt][16].
+__global__ void __launch_bounds__(128)
+w8_repack_kernel(const uint8_t *__restrict__ payload, const float *__restrict__ bs, int scale_cols,
+                 int M, int Kt, uint8_t *__restrict__ d_s8, uint16_t *__restrict__ d_sc) {
+    const size_t gid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (gid >= (size_t)M * Kt) return;
+    const int row = (int)(gid / Kt);
+    const int kt = (int)(gid % Kt);
+    const int mt = row >> 4;
+    const int sc = (scale_cols == Kt) ? kt : (kt >> 2);
+    const float b = bs[(size_t)(mt >> 3) * scale_cols + sc];
+    float wf[32];
+    float hi = 0.0f, neg = 0.0f;
+    for (int j = 0; j < 32; ++j) {
+        wf[j] = __fmul_rn(e2m3f(e2m3_code_at(payload, Kt, row, kt * 32 + j)), b);
+        hi = fmaxf(hi, wf[j]);
+        neg = fmaxf(neg, -wf[j]);
+    }
+    float s = fmaxf(__fdiv_rn(hi, 127.0f), __fdiv_rn(neg, 128.0f));
+    if (!(s > 0.0f)) s = 1.0f;
+    for (int iter = 0; iter < 2; ++iter) {
+        float num = 0.0f, den = 0.0f;
+        for (int j = 0; j < 32; ++j) {
+            const float q = clampf(rintf(__fdiv_rn(wf[j], s)), -128.0f, 127.0f);
+            num = __fadd_rn(num, __fmul_rn(wf[j], q));
+            den = __fadd_rn(den, __fmul_rn(q, q));
+        }
+        if (den > 0.0f) s = __fdiv_rn(num, den);
+    }
+    const uint16_t sh = __half_as_ushort(__float2half_rn(s));
+    d_sc[((size_t)(row >> 4) * Kt + kt) * 16u + (row & 15)] = sh;
+    const float stored = __half2float(__ushort_as_half(sh));
+    uint8_t *dst = d_s8 + ((size_t)(row >> 4) * Kt + kt) * 512u + (size_t)(row & 15) * 32u;
+    for (int j = 0; j < 32; ++j)
+        dst[j] = (uint8_t)(int8_t)(int)clampf(rintf(__fdiv_rn(wf[j], stored)), -128.0f, 127.0f);
+}
+
 }  // namespace
+
+void launch_w8_repack(const uint8_t *d_payload, const float *d_bs, int scale_cols, int M, int K,
+                      uint8_t *d_codes, uint16_t *d_scales) {
+    const int Kt = K / 32;
+    const size_t items = (size_t)M * Kt;
+    const unsigned grid = (unsigned)((items + 127) / 128);
+    w8_repack_kernel<<<grid, 128, 0, stream()>>>(d_payload, d_bs, scale_cols, M, Kt, d_codes, d_scales);
+    TQ_LAUNCH_CHECK("w8_repack_kernel");
+}
 
 void launch_w4_repack(const uint8_t *d_payload, const float *d_bs, int scale_cols, int M, int K,
                       int mode, uint8_t *d_codes, uint16_t *d_scales) {

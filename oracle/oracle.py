@@ -287,6 +287,35 @@ def gemm_w4a8_pertoken(codes, scales, M, K, ksh, aq, as_tok, asum, T):
     return rc, y
 
 
+def w8_repack(payload, bs, scale_cols, M, K):
+    payload, bs = _c(payload, np.uint8), _c(bs, np.float32)
+    codes = np.empty(M * K, dtype=np.uint8)
+    scales = np.empty(M * (K // 32), dtype=np.uint16)
+    rc = lib().orc_w8_repack(_p(payload), _p(bs), C.c_int(scale_cols), C.c_int(M), C.c_int(K),
+                             _p(codes), _p(scales))
+    return rc, codes, scales
+
+
+def gemv_w8a8(codes, scales, M, K, q, as_, residual=None, fma=1):
+    codes, scales = _c(codes, np.uint8), _c(scales, np.uint16)
+    q, as_ = _c(q, np.int8), _c(as_, np.float32)
+    res = _c(residual, np.float32) if residual is not None else None
+    y = np.empty(M, dtype=np.float32)
+    rc = lib().orc_gemv_w8a8(_p(codes), _p(scales), C.c_int(M), C.c_int(K), _p(q), _p(as_),
+                             _p(res) if res is not None else None, _p(y), C.c_int(fma))
+    assert rc == 0, rc
+    return y
+
+
+def gemm_w8a8(codes, scales, M, K, aq, as_, T, fma=1):
+    codes, scales = _c(codes, np.uint8), _c(scales, np.uint16)
+    aq, as_ = _c(aq, np.int8), _c(as_, np.float32)
+    y = np.empty((T, M), dtype=np.float32)
+    rc = lib().orc_gemm_w8a8(_p(codes), _p(scales), C.c_int(M), C.c_int(K), _p(aq), _p(as_), _p(y),
+                             C.c_int(T), C.c_int(fma))
+    return rc, y
+
+
 def quantize_act_chunk_s4(x):
     x = _c(x, np.float32)
     T, K = x.shape

@@ -875,6 +875,119 @@ ORC_API int orc_gemm_w4a4(const uint8_t *codes, const uint16_t *scales, int M, i
     return 0;
 }
 
+/* ------------------------------------------------------------------- W8A8 */
+
+/* x_w8_repack_weight + w8_repack_kernel, xpu/src/kernels_dpas.cpp:345-395, 558-573: per
+ * (row, K32) symmetric int8 with one plain FP16 scale: s = max(hi/127, neg/128) (1 if not
+ * positive), two least-squares refinements s = sum(w q)/sum(q q), FP16 rounding of s, codes
+ * re-quantised against the stored scale. codes[Mt][Kt][16 rows][32 B], scales[Mt][Kt][16]. */
+ORC_API int orc_w8_repack(const uint8_t *payload, const float *bs, int scale_cols, int M, int K,
+                          uint8_t *codes, uint16_t *scales) {
+    if (M % 16 || K % 128) return -2;
+    const int Kt = K / 32;
+#pragma omp parallel for schedule(static)
+    for (int row = 0; row < M; ++row) {
+        for (int kt = 0; kt < Kt; ++kt) {
+            const int mt = row >> 4;
+            const int sc = (scale_cols == Kt) ? kt : (kt >> 2);
+            const float b = bs[(size_t)(mt >> 3) * scale_cols + sc];
+            float wf[32], hi = 0.0f, neg = 0.0f;
+            for (int j = 0; j < 32; ++j) {
+                wf[j] = orc_e2m3f(orc_e2m3_code_at(payload, Kt, row, kt * 32 + j)) * b;
+                hi = fmaxf(hi, wf[j]);
+                neg = fmaxf(neg, -wf[j]);
+            }
+            float s = fmaxf(hi / 127.0f, neg / 128.0f);
+            if (!(s > 0.0f)) s = 1.0f;
+            for (int iter = 0; iter < 2; ++iter) {
+                float num = 0.0f, den = 0.0f;
+                for (int j = 0; j < 32; ++j) {
+                    const float q = clampf(rintf(wf[j] / s), -128.0f, 127.0f);
+                    num += wf[j] * q;
+                    den += q * q;
+                }
+                if (den > 0.0f) s = num / den;
+            }
+            const uint16_t sh = orc_f32_to_f16(s);
+            scales[((size_t)(row >> 4) * Kt + kt) * 16u + (row & 15)] = sh;
+            const float stored = orc_f16_to_f32(sh);
+            const size_t base = ((size_t)(row >> 4) * Kt + kt) * 512u + (size_t)(row & 15) * 32u;
+            for (int j = 0; j < 32; ++j)
+                codes[base + j] = (uint8_t)(int8_t)(int)clampf(rintf(wf[j] / stored), -128.0f, 127.0f);
+        }
+    }
+    return 0;
+}
+
+static inline int32_t w8_tile_dot(const uint8_t *tile, int n, const int8_t *a) {
+    int32_t d = 0;
+    for (int k = 0; k < 32; ++k) d += (int32_t)(int8_t)tile[n * 32 + k] * (int32_t)a[k];
+    return d;
+}
+
+/* x_gemv_w8a8_core under x_gemv_w8a8_prepared_impl, xpu/src/kernels_dpas.cpp:768-843,
+ * 1682-1707: term = ((float)d * ws) * as[kt]; two accumulators per split like the W4A8 GEMV,
+ * splits summed 0..S-1 from 0.0f + residual (or + 0.0f); S == 1 stores the accumulator and
+ * adds a residual separately. */
+ORC_API int orc_gemv_w8a8(const uint8_t *codes, const uint16_t *scales, int M, int K,
+                          const int8_t *q, const float *as, const float *residual, float *y,
+                          int fma) {
+    if (!codes || !scales || !y || M % 16 || K % 32) return -1;
+    const int Kt = K / 32, groups = M / 16;
+    const int splits = orc_choose_gemv_splits(groups);
+#pragma omp parallel for schedule(static)
+    for (int g = 0; g < groups; ++g) {
+        const uint8_t *bbase = codes + (size_t)g * Kt * 512u;
+        const uint16_t *sbase = scales + (size_t)g * Kt * 16u;
+        for (int n = 0; n < 16; ++n) {
+            const int row = g * 16 + n;
+            float sum = 0.0f, acc = 0.0f;
+            for (int s = 0; s < splits; ++s) {
+                float acc0 = 0.0f, acc1 = 0.0f;
+                const int kb = Kt * s / splits, ke = Kt * (s + 1) / splits;
+                for (int kt = kb; kt < ke; ++kt) {
+                    const float f = (float)w8_tile_dot(bbase + (size_t)kt * 512u, n, q + (size_t)kt * 32);
+                    const float ws = orc_f16_to_f32(sbase[(size_t)kt * 16u + n]);
+                    float *a = (((kt - kb) & 1) && (kt - kb) < ((ke - kb) & ~1)) ? &acc1 : &acc0;
+                    if (fma) *a = fmaf(f * ws, as[kt], *a);
+                    else *a += f * ws * as[kt];
+                }
+                acc = acc0 + acc1;
+                sum += acc;
+            }
+            if (splits == 1) y[row] = residual ? acc + residual[row] : acc;
+            else y[row] = sum + (residual ? residual[row] : 0.0f);
+        }
+    }
+    return 0;
+}
+
+/* x_gemm_w8a8, xpu/src/kernels_dpas.cpp:1578-1629: unsplit, one accumulator over the k-tiles,
+ * acc += (float)d * (ws * as[kt][tok]). */
+ORC_API int orc_gemm_w8a8(const uint8_t *codes, const uint16_t *scales, int M, int K,
+                          const int8_t *aq, const float *as, float *y, int T, int fma) {
+    if (!codes || !scales) return -1;
+    if (!aq || !as || !y || T <= 0 || (T % 8) != 0) return -2;
+    const int Kt = K / 32;
+#pragma omp parallel for schedule(static)
+    for (int row = 0; row < M; ++row) {
+        const int rg = row >> 4, n = row & 15;
+        const uint8_t *bbase = codes + (size_t)rg * Kt * 512u;
+        const uint16_t *sbase = scales + (size_t)rg * Kt * 16u;
+        for (int tok = 0; tok < T; ++tok) {
+            float acc = 0.0f;
+            for (int kt = 0; kt < Kt; ++kt) {
+                const size_t a = (size_t)kt * T + tok;
+                const float f = (float)w8_tile_dot(bbase + (size_t)kt * 512u, n, aq + a * 32);
+                const float p = orc_f16_to_f32(sbase[(size_t)kt * 16u + n]) * as[a];
+                acc = fma ? fmaf(f, p, acc) : acc + f * p;
+            }
+            y[(size_t)tok * M + row] = acc;
+        }
+    }
+    return 0;
+}
+
 /* ------------------------------------------------------------------ shard */
 
 /* A12. x_w4_shard mode 0, xpu/src/kernels_dpas.cpp:450-499: every packed

@@ -323,7 +323,9 @@ def test_gemv_errors(lib, pkg, wl):
     w2 = pkg.PackedWeight(c, s, M, 256)
     assert lib.qwn_x_gemv_w4a8_fanout(pkg.weight_array([w, w2]), pkg.ptr_array([y, y]), 2) == -2
     assert lib.qwn_x_gemv_w4a8_fanout(pkg.weight_array([w]), pkg.ptr_array([y]), 5) == -1
-    w.rec.s8_ready = 1
+    w.rec.s8_ready = 1                                   # flagged W8A8 but no W8 buffers
+    assert lib.qwn_x_gemv_qmma(w.ref, x.ptr, y.ptr) == -1
+    w.rec.s8_ready = w.rec.s4_ready = 0                  # scalar E2M3 tier: not built
     assert lib.qwn_x_gemv_qmma(w.ref, x.ptr, y.ptr) == -20
 
 
@@ -611,3 +613,101 @@ def test_overlapped_readback(lib, pkg):
     finally:
         for h in host:
             lib.tq_host_free_pinned(h)
+
+
+# ---------------------------------------------------------------- W8A8 tier
+def _w8_weight(pkg, orc, M, K, seed):
+    """A W8A8 record repacked on the device from a random E2M3 payload, plus the oracle's
+    codes and scales of the same payload."""
+    rng = np.random.default_rng(seed)
+    codes6 = rng.integers(0, 64, size=(M, K), dtype=np.uint8)
+    Kt = K // 32
+    sc = Kt // 4
+    bs = (rng.random(((M + 127) // 128, sc)) * 0.01 + 0.002).astype(np.float32)
+    payload = orc.e2m3_payload_from_codes_fast(codes6)
+    lib = pkg.load()
+    w = pkg.TqWeight()
+    w.M, w.K, w.Mt, w.Kt = M, K, M // 16, Kt
+    w.block_scaled, w.e2m3, w.scale_rows, w.scale_cols = 1, 1, (M + 127) // 128, sc
+    w.d_A = lib.tq_dev_alloc(payload.nbytes, b"t.payload")
+    w.d_block_scale_inv = lib.tq_dev_alloc(bs.nbytes, b"t.bs")
+    lib.tq_h2d(w.d_A, payload.ctypes.data, payload.nbytes)
+    lib.tq_h2d(w.d_block_scale_inv, bs.ctypes.data, bs.nbytes)
+    assert lib.qwn_x_w8_repack_weight(C.byref(w)) == 0
+    assert w.s8_ready == 1 and not w.d_A and not w.d_block_scale_inv
+    rc, oc, osc = orc.w8_repack(payload, bs, sc, M, K)
+    assert rc == 0
+    return w, oc, osc
+
+
+def _w8_free(lib, w):
+    lib.tq_dev_free(w.d_s8)
+    lib.tq_dev_free(w.d_s8_scale)
+
+
+@pytest.mark.gpu
+def test_w8_repack_bit_exact(lib, pkg, orc):
+    M, K = 128, 512
+    w, oc, osc = _w8_weight(pkg, orc, M, K, seed=31)
+    gc, gs = np.empty_like(oc), np.empty_like(osc)
+    lib.tq_d2h(gc.ctypes.data, w.d_s8, gc.nbytes)
+    lib.tq_d2h(gs.ctypes.data, w.d_s8_scale, gs.nbytes)
+    assert np.array_equal(gs, osc)
+    assert np.array_equal(gc, oc)
+    _w8_free(lib, w)
+    bad = pkg.TqWeight()
+    assert lib.qwn_x_w8_repack_weight(C.byref(bad)) == -1
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,K,res", [(64, 256, False), (48, 384, True), (272, 5120, True),
+                                     (65536 + 16, 128, False)])
+def test_gemv_w8a8(lib, pkg, orc, M, K, res):
+    """W8A8 GEMV through the tier dispatcher: bit-identical to the oracle (contracted form),
+    within 1e-3 of the uncontracted one; split counts 16, 8 and 1."""
+    w, oc, osc = _w8_weight(pkg, orc, M, K, seed=M + K)
+    x = refgen.lcg_floats(K, seed=3 + M)[0]
+    dx = dev(pkg, x)
+    r = refgen.lcg_floats(M, seed=9)[0] if res else None
+    dr = dev(pkg, r) if res else None
+    y = pkg.DevBuf(M * 4)
+    y.fill(0xA5)
+    if res:
+        assert lib.qwn_x_gemv_qmma_add(C.byref(w), dx.ptr, dr.ptr, y.ptr) == 0
+    else:
+        assert lib.qwn_x_gemv_qmma(C.byref(w), dx.ptr, y.ptr) == 0
+    lib.tq_sync()
+    q, s, _ = orc.quantize_act_s8(x)
+    want = orc.gemv_w8a8(oc, osc, M, K, q, s, residual=r, fma=1)
+    want0 = orc.gemv_w8a8(oc, osc, M, K, q, s, residual=r, fma=0)
+    got = y.to_numpy(np.float32)
+    assert got.tobytes() == want.tobytes()
+    assert close_1e3(got, want0)
+    assert lib.qwn_x_gemv_w8a8_prepared(C.byref(w), None, None) == -1
+    assert lib.tq_last_error() == 0
+    _w8_free(lib, w)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,K,T", [(64, 256, 8), (272, 512, 24), (1024, 1024, 128)])
+def test_gemm_w8a8(lib, pkg, orc, M, K, T):
+    w, oc, osc = _w8_weight(pkg, orc, M, K, seed=M + K + T)
+    x = refgen.gemm_check_rows(T, K)
+    dx = dev(pkg, x)
+    n = K // 32 * T
+    aq, as_, asum = pkg.DevBuf(n * 32), pkg.DevBuf(n * 4), pkg.DevBuf(n * 4)
+    lib.qwn_x_quantize_act_chunk(dx.ptr, K, T, aq.ptr, as_.ptr, asum.ptr)
+    y = pkg.DevBuf(T * M * 4)
+    y.fill(0xA5)
+    assert lib.qwn_x_gemm_w8a8(C.byref(w), aq.ptr, as_.ptr, y.ptr, T) == 0
+    lib.tq_sync()
+    oq, os_, _ = orc.quantize_act_chunk(x)
+    rc, want = orc.gemm_w8a8(oc, osc, M, K, oq, os_, T, fma=1)
+    rc0, want0 = orc.gemm_w8a8(oc, osc, M, K, oq, os_, T, fma=0)
+    assert rc == 0 and rc0 == 0
+    got = y.to_numpy(np.float32).reshape(T, M)
+    assert got.tobytes() == np.ascontiguousarray(want).tobytes()
+    assert close_1e3(got, want0)
+    assert lib.qwn_x_gemm_w8a8(C.byref(w), aq.ptr, as_.ptr, y.ptr, 12) == -2
+    assert lib.tq_last_error() == 0
+    _w8_free(lib, w)

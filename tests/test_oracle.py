@@ -396,3 +396,33 @@ def test_k16_tier_gemv(orc, wl):
     ya = orc.gemv_w4a8_k16(codes, pk16, M, K, q, as_, sm)
     _, yb = orc.gemv_w4a8(codes, pk32, M, K, 0, q, as_, sm)
     assert np.abs(ya - yb).max() <= 1e-4 * max(np.abs(yb).max(), 1e-6)
+
+
+def test_w8a8_tier(orc):
+    """W8A8 (kernels_dpas.cpp:345-395, 768-843, 1578-1629): the repack reproduces the E2M3
+    weights to int8 accuracy, GEMV and GEMM agree with a float64 dense product and with each
+    other (the GEMM at T tokens = T GEMVs up to fp32 summation order)."""
+    M, K, T = 64, 256, 8
+    rng = np.random.default_rng(12)
+    codes6 = rng.integers(0, 64, size=(M, K), dtype=np.uint8)
+    bs = (rng.random((1, K // 128)) * 0.01 + 0.002).astype(np.float32)
+    payload = orc.e2m3_payload_from_codes_fast(codes6)
+    rc, c8, s8 = orc.w8_repack(payload, bs, K // 128, M, K)
+    assert rc == 0
+    W = orc.e2m3_decode(payload, bs, K // 128, M, K).astype(np.float64)
+    q8 = c8.view(np.int8).reshape(M // 16, K // 32, 16, 32).transpose(0, 2, 1, 3).reshape(M, K // 32, 32)
+    sc = s8.view(np.float16).reshape(M // 16, K // 32, 16).transpose(0, 2, 1).reshape(M, K // 32).astype(np.float64)
+    Wq = (q8.astype(np.float64) * sc[:, :, None]).reshape(M, K)
+    assert np.abs(Wq - W).max() <= np.abs(W).max() / 127.0        # one int8 step of the largest
+    x = rng.standard_normal((T, K)).astype(np.float32)
+    aq, as_, _ = orc.quantize_act_chunk(x)
+    rc, y = orc.gemm_w8a8(c8, s8, M, K, aq, as_, T)
+    assert rc == 0
+    A = (aq.reshape(K // 32, T, 32).astype(np.float64) * as_.reshape(K // 32, T, 1).astype(np.float64))
+    A = A.transpose(1, 0, 2).reshape(T, K)
+    dense = A @ Wq.T
+    assert np.abs(y - dense).max() <= 1e-5 * np.abs(dense).max()
+    q, s, _ = orc.quantize_act_s8(x[0])
+    yv = orc.gemv_w8a8(c8, s8, M, K, q, s)
+    assert np.abs(yv - y[0]).max() <= 1e-4 * np.abs(y[0]).max()
+    assert orc.gemm_w8a8(c8, s8, M, K, aq, as_, 12)[0] == -2
