@@ -152,6 +152,10 @@ int qwn_x_gemv_qmma_add(const tq_qmma_weight_t *w, const float *d_x, const float
 int qwn_x_gemv_qmma_prepared(const tq_qmma_weight_t *w, const float *d_x, float *d_y,
                              const float *d_residual);
 /* xpu/src/kernels_core.cpp:254-281: the fp32 glue either side of a projection. */
+/* xpu/src/kernels_dpas.cpp:1124-1144: out[tok] = x[tok] * rsqrt(mean(x^2) + eps) * (1 + bf16 w)
+ * for T rows of H values (the norm in front of a prefill chunk's projections). */
+void qwn_x_rmsnorm_chunk(float *d_out, const float *d_in, const uint16_t *d_w, int H, int T,
+                         float eps);
 void qwn_x_silu_mul(float *d_out, const float *d_gate, const float *d_up, int N);
 void qwn_x_add_inplace(float *d_x, const float *d_y, int N);
 
@@ -166,7 +170,11 @@ int qwn_x_gemm_w4a8(const tq_qmma_weight_t *w, const int8_t *d_aq, const float *
                     const int32_t *d_asum, float *d_y, int T, const int *offsets, int segments);
 
 /* xpu/src/kernels_dpas.cpp:450-499, 549-556: column (mode 0) shard of a packed weight.
- * Returns 0, -1..-6 as the reference; modes 1 and 2 return -9 (not built). */
+ * Returns 0, -1..-6 as the reference. Mode 1 (kernels_dpas.cpp:501-526) is the row-parallel
+ * shard: rank takes k-tiles [rank*Kt/tp, (rank+1)*Kt/tp) of every row-group (-7 if tp does not
+ * divide Kt, -8 if a K64 shard would split a tile pair); its outputs are partial sums, added
+ * across ranks with tq_comm_allreduce_sum. Mode 2 (527-546) replicates the weight. Other
+ * modes: -9. */
 int qwn_x_w4_shard(tq_qmma_weight_t *dst, const tq_qmma_weight_t *src, int rank, int tp, int mode,
                    const int *groups, int ngroups);
 void qwn_x_w4_shard_free(tq_qmma_weight_t *w);
@@ -244,6 +252,10 @@ int qwn_static_max_k(void);
 int tq_comm_unique_id(void *id128);                       /* rank 0 fills 128 bytes */
 int tq_comm_init(const void *id128, int rank, int world);
 int tq_comm_allgather(const void *d_send, void *d_recv, size_t bytes_per_rank);
+/* Sum of fp32 partial outputs over the ranks: the exchange of a row-parallel (K) shard,
+ * x_w4_shard mode 1. In place when d_send == d_recv. NCCL's summation order: equal to the
+ * unsharded projection to fp32 rounding, not bit for bit. */
+int tq_comm_allreduce_sum(const float *d_send, float *d_recv, size_t count);
 /* Fused all-gather over peer memory (no counterpart in the reference). Every rank owns a
  * gathered buffer [2][world][block] (two halves used by alternate calls, so a rank that
  * runs one step ahead never overwrites what its peers still read; the half a call used is
@@ -285,6 +297,7 @@ int x_gemv_qmma_add(const tq_qmma_weight_t *w, const float *d_x, const float *d_
 void x_prepare_gemv_act_s8(const float *d_x, int K);
 void x_silu_mul_quant(float *d_out, const float *d_gate, const float *d_up, int K);
 void x_silu_mul(float *d_out, const float *d_gate, const float *d_up, int N);
+void x_rmsnorm_chunk(float *d_out, const float *d_in, const uint16_t *d_w, int H, int T, float eps);
 void x_add_inplace(float *d_x, const float *d_y, int N);
 void x_rmsnorm_quant(float *d_out, const float *d_in, const uint16_t *d_w, int H, float eps);
 int x_gemv_w4a8_fanout(const tq_qmma_weight_t *const *ws, float *const *ys, int count);

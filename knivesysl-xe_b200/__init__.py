@@ -82,6 +82,7 @@ SIGNATURES = {
     "qwn_x_quantize_act_chunk_pertoken": (None, [_vp, _i, _i, _vp, _vp, _vp, _vp]),
     "qwn_x_gemm_w4a8_pertoken": (_i, [_WP, _vp, _vp, _vp, _vp, _i, _i]),
     "qwn_x_quantize_act_chunk_s4": (None, [_vp, _i, _i, _vp, _vp, _vp]),
+    "qwn_x_rmsnorm_chunk": (None, [_vp, _vp, _vp, _i, _i, C.c_float]),
     "qwn_x_gemm_w4a4": (_i, [_WP, _vp, _vp, _vp, _vp, _i]),
     "qwn_dbg_tile_dots_gemv": (_i, [_WP, _vp]),
     "qwn_dbg_tile_dots_gemm": (_i, [_WP, _vp, _i, _vp]),
@@ -92,6 +93,7 @@ SIGNATURES = {
     "qwn_x_gemv_w4a8_static": (_i, [_WP, _vp, _vp]), "qwn_static_max_k": (_i, []),
     "tq_comm_unique_id": (_i, [_vp]), "tq_comm_init": (_i, [_vp, _i, _i]),
     "tq_comm_allgather": (_i, [_vp, _vp, _sz]),
+    "tq_comm_allreduce_sum": (_i, [_vp, _vp, _sz]),
     "tq_comm_ipc_export": (_i, [_vp, _vp]), "tq_comm_ipc_open": (_vp, [_vp]),
     "tq_comm_ipc_close": (None, [_vp]),
     "tq_comm_gather_setup": (_i, [C.POINTER(_vp), C.POINTER(_vp), _i, _i]),

@@ -20,6 +20,7 @@ struct NcclApi {
     ncclResult_t (*GetUniqueId)(ncclUniqueId *) = nullptr;
     ncclResult_t (*CommInitRank)(ncclComm_t *, int, ncclUniqueId, int) = nullptr;
     ncclResult_t (*AllGather)(const void *, void *, size_t, int, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*AllReduce)(const void *, void *, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
     ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
     const char *(*GetErrorString)(ncclResult_t) = nullptr;
 } g_api;
@@ -76,6 +77,7 @@ bool load_nccl() {
     g_api.GetUniqueId = (decltype(g_api.GetUniqueId))dlsym(g_api.handle, "ncclGetUniqueId");
     g_api.CommInitRank = (decltype(g_api.CommInitRank))dlsym(g_api.handle, "ncclCommInitRank");
     g_api.AllGather = (decltype(g_api.AllGather))dlsym(g_api.handle, "ncclAllGather");
+    g_api.AllReduce = (decltype(g_api.AllReduce))dlsym(g_api.handle, "ncclAllReduce");
     g_api.CommDestroy = (decltype(g_api.CommDestroy))dlsym(g_api.handle, "ncclCommDestroy");
     g_api.GetErrorString = (decltype(g_api.GetErrorString))dlsym(g_api.handle, "ncclGetErrorString");
     if (!g_api.GetUniqueId || !g_api.CommInitRank || !g_api.AllGather || !g_api.CommDestroy) {
@@ -145,6 +147,22 @@ int tq_comm_allgather(const void *d_send, void *d_recv, size_t bytes_per_rank) {
     const ncclResult_t r =
         g_api.AllGather(d_send, d_recv, bytes_per_rank, kNcclInt8, g_comm, tq::stream());
     if (r != 0) return nccl_fail(r, "ncclAllGather");
+    return 0;
+}
+
+// Sum of fp32 partial outputs over the ranks (the exchange of a row-parallel shard,
+// x_w4_shard mode 1). In place when d_send == d_recv. The sum order is NCCL's, so results
+// match the unsharded projection to fp32 rounding, not bit for bit.
+int tq_comm_allreduce_sum(const float *d_send, float *d_recv, size_t count) {
+    if (!d_send || !d_recv) return -1;
+    if (g_world == 1) {
+        if (d_send != d_recv) tq_d2d_async(d_recv, d_send, count * sizeof(float));
+        return 0;
+    }
+    if (!g_comm || !g_api.AllReduce) return -3;
+    const ncclResult_t r = g_api.AllReduce(d_send, d_recv, count, /*ncclFloat32*/ 7, /*ncclSum*/ 0,
+                                           g_comm, tq::stream());
+    if (r != 0) return nccl_fail(r, "ncclAllReduce");
     return 0;
 }
 

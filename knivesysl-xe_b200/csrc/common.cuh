@@ -67,6 +67,8 @@ void launch_rmsnorm_quant(float *d_out, const float *d_in, const uint16_t *d_w, 
                           float *d_partial, int8_t *d_q, int8_t *d_qp, float *d_scale,
                           int32_t *d_sum16, int32_t *d_sum32);
 void launch_quant_chunk(const float *d_x, int K, int T, int8_t *d_aq, float *d_as, int32_t *d_asum);
+void launch_rmsnorm_chunk(float *d_out, const float *d_in, const uint16_t *d_w, int H, int T,
+                          float eps);
 void launch_quant_chunk_s4(const float *d_x, int K, int T, uint8_t *d_aq4, float *d_as4,
                            int32_t *d_asum4);
 void launch_quant_chunk_pertoken(const float *d_x, int K, int T, int8_t *d_aq, float *d_as,

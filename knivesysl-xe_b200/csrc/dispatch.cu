@@ -459,6 +459,12 @@ int x_gemm_w4a8_pertoken(const tq_qmma_weight_t *w, const int8_t *d_aq, const fl
     return rc == 0 ? 0 : -3;   // -3: shape not covered by the per-token kernel
 }
 
+// xpu/src/kernels_dpas.cpp:1124-1144: (1+w) RMSNorm of a chunk of token rows.
+void x_rmsnorm_chunk(float *d_out, const float *d_in, const uint16_t *d_w, int H, int T, float eps) {
+    if (!d_out || !d_in || !d_w || H <= 0 || T <= 0) return;
+    launch_rmsnorm_chunk(d_out, d_in, d_w, H, T, eps);
+}
+
 // ---- W4A4 (xpu/src/kernels_dpas.cpp:1495-1571): the tier K64 weights run at prefill -------
 void x_quantize_act_chunk_s4(const float *d_x, int K, int T, uint8_t *d_aq4, float *d_as4,
                              int32_t *d_asum4) {
@@ -487,9 +493,49 @@ int x_w4_shard(tq_qmma_weight_t *dst, const tq_qmma_weight_t *src, int rank, int
     if (tp < 1 || rank < 0 || rank >= tp) return -2;
     const int ksh = src->s4_k64 ? 1 : 0;
     if (src->s4_k16) return -3;
-    if (mode != 0) return -9;   // row-parallel and replicate shards are not built
     const int Kt = src->Kt;
     const int sg = Kt >> ksh;
+    if (mode == 1) {
+        // Row-parallel (K) shard, kernels_dpas.cpp:501-526: rank takes k-tiles
+        // [rank*Kt/tp, (rank+1)*Kt/tp) of every row-group; the ranks' outputs are partial sums
+        // (tq_comm_allreduce_sum adds them).
+        if (Kt % tp) return -7;
+        if (ksh && (Kt / tp) % 2) return -8;       // K64 needs paired tiles
+        const int Ktnew = Kt / tp, sgnew = Ktnew >> ksh;
+        *dst = *src;
+        dst->d_A = nullptr;
+        dst->d_block_scale_inv = nullptr;
+        dst->K = src->K / tp;
+        dst->Kt = Ktnew;
+        dst->scale_cols = sgnew;
+        dst->d_s4 = static_cast<uint8_t *>(tq_dev_alloc((size_t)src->Mt * Ktnew * 256u, "shard.codes"));
+        dst->d_s4_scale =
+            static_cast<uint16_t *>(tq_dev_alloc((size_t)src->M * sgnew * 2u, "shard.scales"));
+        const size_t kt0 = (size_t)Ktnew * (size_t)rank;
+        TQ_CHECK(cudaMemcpy2DAsync(dst->d_s4, (size_t)Ktnew * 256u, src->d_s4 + kt0 * 256u,
+                                   (size_t)Kt * 256u, (size_t)Ktnew * 256u, (size_t)src->Mt,
+                                   cudaMemcpyDeviceToDevice, stream()));
+        TQ_CHECK(cudaMemcpy2DAsync(dst->d_s4_scale, (size_t)sgnew * 32u,
+                                   src->d_s4_scale + (kt0 >> ksh) * 16u, (size_t)sg * 32u,
+                                   (size_t)sgnew * 32u, (size_t)src->Mt, cudaMemcpyDeviceToDevice,
+                                   stream()));
+        tq_sync();
+        return 0;
+    }
+    if (mode == 2) {
+        // Replicate, kernels_dpas.cpp:527-546: a full copy for this rank.
+        *dst = *src;
+        dst->d_A = nullptr;
+        dst->d_block_scale_inv = nullptr;
+        const size_t code_bytes = (size_t)src->Mt * Kt * 256u, scale_bytes = (size_t)src->M * sg * 2u;
+        dst->d_s4 = static_cast<uint8_t *>(tq_dev_alloc(code_bytes, "rep.codes"));
+        dst->d_s4_scale = static_cast<uint16_t *>(tq_dev_alloc(scale_bytes, "rep.scales"));
+        tq_d2d_async(dst->d_s4, src->d_s4, code_bytes);
+        tq_d2d_async(dst->d_s4_scale, src->d_s4_scale, scale_bytes);
+        tq_sync();
+        return 0;
+    }
+    if (mode != 0) return -9;
     int gs[8];
     const int ng = (groups && ngroups > 0) ? ngroups : 1;
     if (ng > 8) return -4;
@@ -628,6 +674,10 @@ int qwn_x_gemm_w4a8_pertoken(const tq_qmma_weight_t *w, const int8_t *d_aq, cons
     return x_gemm_w4a8_pertoken(w, d_aq, d_as_tok, d_asum, d_y, T, out_bf16);
 }
 
+void qwn_x_rmsnorm_chunk(float *d_out, const float *d_in, const uint16_t *d_w, int H, int T,
+                         float eps) {
+    x_rmsnorm_chunk(d_out, d_in, d_w, H, T, eps);
+}
 void qwn_x_quantize_act_chunk_s4(const float *d_x, int K, int T, uint8_t *d_aq4, float *d_as4,
                                  int32_t *d_asum4) {
     x_quantize_act_chunk_s4(d_x, K, T, d_aq4, d_as4, d_asum4);

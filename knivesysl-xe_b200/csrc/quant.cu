@@ -134,6 +134,33 @@ quant_chunk_kernel(const float *__restrict__ x, int K, int T, size_t blocks,
     }
 }
 
+// x_rmsnorm_chunk (xpu/src/kernels_dpas.cpp:1124-1144): one 256-thread block per token row.
+// Thread t adds the squares of elements t, t+256, ... in order; the block sum is a fixed
+// binary tree over the 256 partial sums (the reference leaves that order to the SYCL runtime).
+__global__ void __launch_bounds__(256)
+rmsnorm_chunk_kernel(float *__restrict__ out, const float *__restrict__ in,
+                     const uint16_t *__restrict__ w, int H, float eps) {
+    __shared__ float p[256];
+    pdl_trigger();
+    pdl_wait();
+    const int tid = threadIdx.x;
+    const float *row = in + (size_t)blockIdx.x * H;
+    float ss = 0.0f;
+    for (int i = tid; i < H; i += 256) ss = __fadd_rn(ss, __fmul_rn(row[i], row[i]));
+    p[tid] = ss;
+    __syncthreads();
+    for (int stride = 128; stride >= 1; stride >>= 1) {
+        if (tid < stride) p[tid] = __fadd_rn(p[tid], p[tid + stride]);
+        __syncthreads();
+    }
+    const float rms_inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(p[0], (float)H), eps)));
+    float *dst = out + (size_t)blockIdx.x * H;
+    for (int i = tid; i < H; i += 256) {
+        const float wf = __uint_as_float((uint32_t)w[i] << 16);
+        dst[i] = __fmul_rn(__fmul_rn(row[i], rms_inv), __fadd_rn(1.0f, wf));
+    }
+}
+
 // W4A4 staging (x_quantize_act_chunk_s4, xpu/src/kernels_dpas.cpp:1149-1193, 1495-1498): one
 // warp per (token, 64 values) block blk = kt64*T + tok; lane l quantises k = 2l, 2l+1 to
 // [-7, 7] with scale absmax/7 and stores them as one byte (low nibble = even k).
@@ -288,6 +315,12 @@ void launch_quant_chunk(const float *d_x, int K, int T, int8_t *d_aq, float *d_a
     launch_pdl(quant_chunk_kernel<false>, dim3(grid), dim3(kWarpsPerBlock * 32), 0, d_x, K, T,
                blocks, d_aq, d_as, d_asum, (const float *)nullptr);
     TQ_LAUNCH_CHECK("quant_chunk_kernel");
+}
+
+void launch_rmsnorm_chunk(float *d_out, const float *d_in, const uint16_t *d_w, int H, int T,
+                          float eps) {
+    launch_pdl(rmsnorm_chunk_kernel, dim3(T), dim3(256), 0, d_out, d_in, d_w, H, eps);
+    TQ_LAUNCH_CHECK("rmsnorm_chunk_kernel");
 }
 
 void launch_quant_chunk_s4(const float *d_x, int K, int T, uint8_t *d_aq4, float *d_as4,

@@ -198,6 +198,14 @@ def rmsnorm_quant(x, w_bf16, eps):
     return out, q, s, sm
 
 
+def rmsnorm_chunk(x, w_bf16, eps):
+    x, w_bf16 = _c(x, np.float32), _c(w_bf16, np.uint16)
+    T, H = x.shape
+    out = np.empty((T, H), dtype=np.float32)
+    lib().orc_rmsnorm_chunk(_p(out), _p(x), _p(w_bf16), C.c_int(H), C.c_int(T), C.c_float(eps))
+    return out
+
+
 def quantize_act_chunk(x, per_token: bool = False):
     x = _c(x, np.float32)
     T, K = x.shape

@@ -875,6 +875,30 @@ ORC_API int orc_gemm_w4a4(const uint8_t *codes, const uint16_t *scales, int M, i
     return 0;
 }
 
+/* x_rmsnorm_chunk, xpu/src/kernels_dpas.cpp:1124-1144: per token row, 256 work-items each
+ * add the squares of elements i = tid, tid+256, ... in order; the group sum (whose order the
+ * reference leaves to sycl::reduce_over_group) is taken here as a fixed binary tree
+ * p[t] += p[t+stride], stride = 128..1; rms_inv = 1/sqrt(ss/H + eps) with IEEE sqrt and
+ * divide; out = (x * rms_inv) * (1 + bf16(w)). */
+ORC_API void orc_rmsnorm_chunk(float *out, const float *in, const uint16_t *w, int H, int T,
+                               float eps) {
+#pragma omp parallel for schedule(static)
+    for (int tok = 0; tok < T; ++tok) {
+        const float *row = in + (size_t)tok * H;
+        float p[256];
+        for (int t = 0; t < 256; ++t) {
+            float ss = 0.0f;
+            for (int i = t; i < H; i += 256) ss += row[i] * row[i];
+            p[t] = ss;
+        }
+        for (int stride = 128; stride >= 1; stride >>= 1)
+            for (int t = 0; t < stride; ++t) p[t] = p[t] + p[t + stride];
+        const float rms_inv = 1.0f / sqrtf(p[0] / (float)H + eps);
+        for (int i = 0; i < H; ++i)
+            out[(size_t)tok * H + i] = row[i] * rms_inv * (1.0f + bf16f(w[i]));
+    }
+}
+
 /* ------------------------------------------------------------------- W8A8 */
 
 /* x_w8_repack_weight + w8_repack_kernel, xpu/src/kernels_dpas.cpp:345-395, 558-573: per

@@ -203,7 +203,7 @@ def test_shard_matches_oracle_and_concat_bit_identical(lib, pkg, orc, wl, tp, gr
     s = pkg.TqWeight()
     assert lib.qwn_x_w4_shard(C.byref(s), w.ref, 0, 3, 0, None, 0) == -6
     assert lib.qwn_x_w4_shard(C.byref(s), w.ref, 5, 2, 0, None, 0) == -2
-    assert lib.qwn_x_w4_shard(C.byref(s), w.ref, 0, 2, 1, None, 0) == -9
+    assert lib.qwn_x_w4_shard(C.byref(s), w.ref, 0, 2, 3, None, 0) == -9
 
 
 # ---------------------------------------------------------------- GEMV
@@ -711,3 +711,76 @@ def test_gemm_w8a8(lib, pkg, orc, M, K, T):
     assert lib.qwn_x_gemm_w8a8(C.byref(w), aq.ptr, as_.ptr, y.ptr, 12) == -2
     assert lib.tq_last_error() == 0
     _w8_free(lib, w)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("ksh,tp", [(0, 2), (1, 4), (0, 8)])
+def test_row_parallel_and_replicate_shards(lib, pkg, orc, wl, ksh, tp):
+    """x_w4_shard modes 1 and 2 (kernels_dpas.cpp:501-546). Mode 1: a rank's shard is the
+    weight restricted to its K range, so its GEMV equals the oracle's GEMV of that slice bit
+    for bit, and the ranks' partial outputs add up to the full projection within 1e-3
+    (tq_comm_allreduce_sum is that sum; with one rank it is a copy). Mode 2: a full copy."""
+    M, K = 256, 2048
+    codes, scales = wl.random_packed_weight(M, K, seed=5 + ksh, ksh=ksh)
+    w = pkg.PackedWeight(codes, scales, M, K, k64=bool(ksh))
+    x = refgen.shard_check_row(K)
+    q, sc, sm = orc.quantize_act_s8(x)
+    _, full = orc.gemv_w4a8(codes, scales, M, K, ksh, q, sc, sm, fma=1)
+    Kt, Kn = K // 32, K // tp
+    cs = codes.reshape(M // 16, Kt, 256)
+    ss = scales.reshape(M // 16, Kt >> ksh, 16)
+    total = np.zeros(M, np.float64)
+    for r in range(tp):
+        s = pkg.TqWeight()
+        assert lib.qwn_x_w4_shard(C.byref(s), w.ref, r, tp, 1, None, 0) == 0
+        assert s.K == Kn and s.Kt == Kt // tp and s.M == M
+        want_c = np.ascontiguousarray(cs[:, r * (Kt // tp):(r + 1) * (Kt // tp)]).reshape(-1)
+        g = (Kt // tp) >> ksh
+        want_s = np.ascontiguousarray(ss[:, r * g:(r + 1) * g]).reshape(-1)
+        gc, gs = np.empty_like(want_c), np.empty_like(want_s)
+        lib.tq_d2h(gc.ctypes.data, s.d_s4, gc.nbytes)
+        lib.tq_d2h(gs.ctypes.data, s.d_s4_scale, gs.nbytes)
+        assert np.array_equal(gc, want_c) and np.array_equal(gs, want_s)
+        xs = np.ascontiguousarray(x[r * Kn:(r + 1) * Kn])
+        dxs = dev(pkg, xs)
+        y = pkg.DevBuf(M * 4)
+        assert lib.qwn_x_gemv_w4a8(C.byref(s), dxs.ptr, y.ptr) == 0
+        y2 = pkg.DevBuf(M * 4)
+        assert lib.tq_comm_allreduce_sum(y.ptr, y2.ptr, M) == 0      # world of one: a copy
+        lib.tq_sync()
+        qs, scs, sms = orc.quantize_act_s8(xs)
+        _, part = orc.gemv_w4a8(want_c, want_s, M, Kn, ksh, qs, scs, sms, fma=1)
+        assert y.to_numpy(np.float32).tobytes() == part.tobytes()
+        assert y2.to_numpy(np.float32).tobytes() == part.tobytes()
+        total += part
+        lib.qwn_x_w4_shard_free(C.byref(s))
+    assert close_1e3(total.astype(np.float32), full)
+    rep = pkg.TqWeight()
+    assert lib.qwn_x_w4_shard(C.byref(rep), w.ref, 1, tp, 2, None, 0) == 0
+    gc, gs = np.empty_like(codes), np.empty_like(scales)
+    lib.tq_d2h(gc.ctypes.data, rep.d_s4, gc.nbytes)
+    lib.tq_d2h(gs.ctypes.data, rep.d_s4_scale, gs.nbytes)
+    assert np.array_equal(gc, codes) and np.array_equal(gs, scales) and rep.M == M and rep.K == K
+    lib.qwn_x_w4_shard_free(C.byref(rep))
+    bad = pkg.TqWeight()
+    assert lib.qwn_x_w4_shard(C.byref(bad), w.ref, 0, 3, 1, None, 0) == -7
+    if ksh:
+        assert lib.qwn_x_w4_shard(C.byref(bad), w.ref, 0, 64, 1, None, 0) == -8
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("H,T", [(5120, 8), (352, 3), (256, 40)])
+def test_rmsnorm_chunk(lib, pkg, orc, H, T):
+    rng = np.random.default_rng(H + T)
+    x = (rng.standard_normal((T, H)) * 3).astype(np.float32)
+    w = ((rng.standard_normal(H) * 0.1).astype(np.float32).view(np.uint32) >> 16).astype(np.uint16)
+    dx, dw, out = dev(pkg, x), dev(pkg, w), pkg.DevBuf(T * H * 4)
+    out.fill(0xA5)
+    lib.qwn_x_rmsnorm_chunk(out.ptr, dx.ptr, dw.ptr, H, T, 1e-6)
+    lib.tq_sync()
+    want = orc.rmsnorm_chunk(x, w, 1e-6)
+    assert out.to_numpy(np.float32).tobytes() == want.tobytes()
+    wf = (w.astype(np.uint32) << 16).view(np.float32).astype(np.float64)
+    x64 = x.astype(np.float64)
+    ref = x64 / np.sqrt((x64 ** 2).mean(axis=1, keepdims=True) + 1e-6) * (1.0 + wf)
+    assert np.abs(want - ref).max() <= 1e-5 * np.abs(ref).max()
