@@ -451,9 +451,17 @@ void launch_gemv(const GemvArgs &a) {
                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingK16));
             attr16 = true;
         }
-        launch_pdl(gemv_w4a8_kernel<false, false, false, 2, true>, dim3(grid), dim3(kW * 32), kRingK16, a);
+        if (a.splits >= 4)      // one row-group per CTA, as for the other tiers below
+            launch_pdl(gemv_w4a8_kernel<false, false, false, 2, true>, dim3(groups),
+                       dim3(a.splits * 32), (size_t)a.splits * 2 * stage_bytes(false, true), a);
+        else
+            launch_pdl(gemv_w4a8_kernel<false, false, false, 2, true>, dim3(grid), dim3(kW * 32),
+                       kRingK16, a);
     } else if (a.dump)
         launch_pdl(gemv_w4a8_kernel<false, true, false, 2>, dim3(grid), dim3(kW * 32), kRingP, a);
+    else if (a.serial && a.splits >= 4)
+        launch_pdl(gemv_w4a8_kernel<true, false, false, 2>, dim3(groups), dim3(a.splits * 32),
+                   (size_t)a.splits * 2 * stage_bytes(false), a);
     else if (a.serial)
         launch_pdl(gemv_w4a8_kernel<true, false, false, 2>, dim3(grid), dim3(kW * 32), kRingP, a);
     else if (a.x && kRingF3 + qbytes <= kPerCta)
@@ -462,13 +470,20 @@ void launch_gemv(const GemvArgs &a) {
     else if (a.x && kRingF2 + qbytes <= kPerCta)
         launch_pdl(gemv_w4a8_kernel<false, false, true, 2>, dim3(grid), dim3(kW * 32),
                    kRingF2 + qbytes, a);
-    else if (a.splits >= 4 && groups <= 3 * g_sms) {
-        // Few row-groups (a long-K weight): 16-warp CTAs would leave warp slots empty and each
-        // warp's long chain would have one stage in flight. One team per CTA instead, up to
-        // three CTAs per SM, three ring stages.
+    else if (a.splits >= 4) {
+        // Split weights (fewer than 4096 row-groups): one team per CTA, one row-group per CTA,
+        // so the hardware places CTAs as SMs free up instead of a fixed share per SM (5%
+        // faster than the persistent split on 17408x5120), and the next launch's first CTAs
+        // start while the last ones of this launch drain. Few row-groups (a long-K weight,
+        // at most three CTAs per SM in flight) get three ring stages, else two (four CTAs
+        // per SM).
         const int nw = a.splits;
-        launch_pdl(gemv_w4a8_kernel<false, false, false, 3>, dim3(groups), dim3(nw * 32),
-                   (size_t)nw * 3 * stage_bytes(false), a);
+        if (groups <= 3 * g_sms)
+            launch_pdl(gemv_w4a8_kernel<false, false, false, 3>, dim3(groups), dim3(nw * 32),
+                       (size_t)nw * 3 * stage_bytes(false), a);
+        else
+            launch_pdl(gemv_w4a8_kernel<false, false, false, 2>, dim3(groups), dim3(nw * 32),
+                       (size_t)nw * 2 * stage_bytes(false), a);
     } else
         launch_pdl(gemv_w4a8_kernel<false, false, false, 2>, dim3(grid), dim3(kW * 32), kRingP, a);
     TQ_LAUNCH_CHECK("gemv_w4a8_kernel");
