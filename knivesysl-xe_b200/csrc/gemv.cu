@@ -2,15 +2,19 @@
 //
 // Replaces x_gemv_w4a8_core and x_gemv_w4a8_fanout (xpu/src/kernels_dpas.cpp:586-675,
 // 945-1102). HBM-bound: the packed weight stream (256 B per 16-row x K32 tile plus a
-// 32 B scale line) is read exactly once; activations (32 B per k-tile) stay in L1/L2.
+// 32 B scale line) is read exactly once; activations (40 B per k-tile) come from L2.
 //
 // Mapping. One warp owns one (row-group, K-split) task at a time, as the reference's
-// sub-group does; the kernel is persistent (two CTAs of 16 warps per SM). A 256-byte tile
-// is 16 rows x 16 B, so a HALF-warp reads one tile with one 128-bit load per lane and the
-// two halves of a warp walk the even and the odd tiles of the split. That is exactly the reference's two-accumulator order (acc0 takes the
-// even offsets from kt_begin, acc1 the odd ones, leftover to acc0), so each lane keeps
-// ONE accumulator and acc0+acc1 is a single shuffle. The fan-out order (one serial
-// accumulator) passes the odd half's product terms to the even half every pair.
+// sub-group does. Split weights launch one CTA of S warps per row-group (the hardware places
+// them as SMs free up); unsplit ones and the fused-quantiser form run persistent 16-warp
+// CTAs, two per SM. A 256-byte tile is 16 rows x 16 B, so a HALF-warp reads one tile with
+// one 128-bit load per lane and the two halves of a warp walk the even and the odd tiles of
+// the split. That is exactly the reference's two-accumulator order (acc0 takes the even
+// offsets from kt_begin, acc1 the odd ones, leftover to acc0), so each lane keeps ONE
+// accumulator and acc0+acc1 is a single shuffle. The fan-out order and the K16 tier (one
+// serial accumulator) pass the odd half's product terms to the even half every pair.
+// Weights, their scale lines and the matching activations reach the tile loop through
+// per-warp cp.async rings in shared memory (see the kernel).
 //
 // Unpack. A row's 16 bytes hold k = 2b (low nibble) and 2b+1 (high nibble). Masking
 // gives the even-k and the odd-k codes of a word as four bytes each; xor 8 turns a
