@@ -193,6 +193,14 @@ int qwn_choose_gemm_splits(int rgroups, int tgroups, int ktiles);
 int qwn_x_gemm_w4a8_fanout(const tq_qmma_weight_t *const *ws, float *const *ys, int count,
                            const int8_t *d_aq, const float *d_as, const int32_t *d_asum, int T,
                            const int *offsets, int segments);
+/* The fan-out GEMM from fp32 rows x[T][K]: quantised like x_quantize_act_chunk (per_token == 0)
+ * or x_quantize_act_chunk_pertoken (per_token != 0) and multiplied in one call, results
+ * bit-identical to staging first and calling x_gemm_w4a8_fanout. For T = 8 the quantiser
+ * runs in the GEMM kernel's prologue (one launch, nothing staged in global memory); other
+ * shapes stage into a library-owned scratch. No counterpart in the reference (its decode
+ * GEMV fuses the quantiser the same way). */
+int qwn_x_gemm_w4a8_fanout_fused(const tq_qmma_weight_t *const *ws, float *const *ys, int count,
+                                 const float *d_x, int T, int per_token);
 /* Per-token activation scale (absmax/127 over the whole row): same staging layout as
  * x_quantize_act_chunk with the scale replicated into every as[kt][tok], plus the
  * per-token vector d_as_tok[T]. */
@@ -277,6 +285,10 @@ int tq_comm_gather_wait(void);
 int qwn_x_gemm_w4a8_fanout_gathered(const tq_qmma_weight_t *const *ws, int count,
                                     const int8_t *d_aq, const float *d_as, const int32_t *d_asum,
                                     int T, size_t *half_offset_floats);
+/* The gathered call from fp32 rows (see qwn_x_gemm_w4a8_fanout_fused). */
+int qwn_x_gemm_w4a8_fanout_gathered_fused(const tq_qmma_weight_t *const *ws, int count,
+                                          const float *d_x, int T, int per_token,
+                                          size_t *half_offset_floats);
 int tq_comm_rank(void);
 int tq_comm_world(void);
 void tq_comm_destroy(void);
@@ -320,6 +332,10 @@ int x_gemm_w4a8_fanout(const tq_qmma_weight_t *const *ws, float *const *ys, int 
 int x_gemm_w4a8_fanout_gathered(const tq_qmma_weight_t *const *ws, int count, const int8_t *d_aq,
                                 const float *d_as, const int32_t *d_asum, int T,
                                 size_t *half_offset_floats = nullptr);
+int x_gemm_w4a8_fanout_fused(const tq_qmma_weight_t *const *ws, float *const *ys, int count,
+                             const float *d_x, int T, int per_token);
+int x_gemm_w4a8_fanout_gathered_fused(const tq_qmma_weight_t *const *ws, int count, const float *d_x,
+                                      int T, int per_token, size_t *half_offset_floats = nullptr);
 void x_quantize_act_chunk_pertoken(const float *d_x, int K, int T, int8_t *d_aq, float *d_as,
                                    int32_t *d_asum, float *d_as_tok);
 int x_gemm_w4a8_pertoken(const tq_qmma_weight_t *w, const int8_t *d_aq, const float *d_as_tok,

@@ -100,6 +100,8 @@ SIGNATURES = {
     "tq_comm_gather_wait": (_i, []),
     "qwn_x_gemm_w4a8_fanout_gathered": (_i, [C.POINTER(_WP), _i, _vp, _vp, _vp, _i,
                                          C.POINTER(_sz)]),
+    "qwn_x_gemm_w4a8_fanout_fused": (_i, [C.POINTER(_WP), C.POINTER(_vp), _i, _vp, _i, _i]),
+    "qwn_x_gemm_w4a8_fanout_gathered_fused": (_i, [C.POINTER(_WP), _i, _vp, _i, _i, C.POINTER(_sz)]),
     "tq_comm_rank": (_i, []), "tq_comm_world": (_i, []), "tq_comm_destroy": (None, []),
 }
 

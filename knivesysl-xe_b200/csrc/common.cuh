@@ -121,6 +121,12 @@ struct GemmArgs {
     const float *as;
     const int32_t *asum;
     int K, ksh, T;
+    // Fused activation quantisation (ring kernel, T = 8): when x is set the kernel quantises the
+    // fp32 rows x[T][K] itself (aq / as / asum are not read): x_mode 1 = one scale per
+    // (token, K32) block as x_quantize_act_chunk, 2 = one scale per token row as
+    // x_quantize_act_chunk_pertoken.
+    const float *x;
+    int x_mode;
     GemmSegments seg[4];     // per weight (each keeps the splits it would get alone)
     int max_splits;
     int32_t *dump;           // non-null: write int32 tile dots (single weight)
@@ -133,6 +139,7 @@ struct GemmArgs {
 void launch_gemm_mma(const GemmArgs &a);
 // gemm_stream.cu (decode batches: one segment, T <= 64, uniform split count <= 8)
 bool gemm_stream_covers(const GemmArgs &a);
+bool gemm_ring_covers(const GemmArgs &a);     // the T = 8 ring kernel takes the call
 void launch_gemm_stream(const GemmArgs &a);
 // Picks the streaming kernel when it covers the call, else the general mma kernel.
 inline void launch_gemm(const GemmArgs &a) {

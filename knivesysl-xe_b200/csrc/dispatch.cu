@@ -334,11 +334,40 @@ void x_quantize_act_chunk_pertoken(const float *d_x, int K, int T, int8_t *d_aq,
     launch_quant_chunk_pertoken(d_x, K, T, d_aq, d_as, d_asum, d_as_tok);
 }
 
-int x_gemm_w4a8_fanout(const tq_qmma_weight_t *const *ws, float *const *ys, int count,
-                       const int8_t *d_aq, const float *d_as, const int32_t *d_asum, int T,
-                       const int *offsets, int segments) {
-    if (!ws || !ys || count <= 0 || count > 4 || !ws[0]) return -1;
-    GemmArgs a{};
+namespace {
+
+// Library-owned chunk staging for the fused-quantiser entry points when the shape is not
+// the ring kernel's (grown on demand, like the decode scratch).
+struct ChunkScratch {
+    int8_t *aq = nullptr;
+    float *as = nullptr;
+    int32_t *asum = nullptr;
+    float *as_tok = nullptr;
+    size_t blocks = 0;
+    int tokens = 0;
+} g_chunk;
+
+void ensure_chunk_scratch(size_t blocks, int T) {
+    if (blocks > g_chunk.blocks) {
+        if (g_chunk.aq) { tq_dev_free(g_chunk.aq); tq_dev_free(g_chunk.as); tq_dev_free(g_chunk.asum); }
+        g_chunk.aq = static_cast<int8_t *>(tq_dev_alloc(blocks * 32, "chunk.aq"));
+        g_chunk.as = static_cast<float *>(tq_dev_alloc(blocks * 4, "chunk.as"));
+        g_chunk.asum = static_cast<int32_t *>(tq_dev_alloc(blocks * 4, "chunk.asum"));
+        g_chunk.blocks = blocks;
+    }
+    if (T > g_chunk.tokens) {
+        if (g_chunk.as_tok) tq_dev_free(g_chunk.as_tok);
+        g_chunk.as_tok = static_cast<float *>(tq_dev_alloc((size_t)T * 4, "chunk.as_tok"));
+        g_chunk.tokens = T;
+    }
+}
+
+// Common part of the fan-out GEMM entry points. d_x != nullptr: quantise x[T][K] first
+// (x_mode 1 per (token, K32) block, 2 per token) - inside the GEMM kernel when the ring kernel
+// takes the call, else into the library's chunk scratch.
+int fanout_args(GemmArgs &a, const tq_qmma_weight_t *const *ws, int count, int T, const int *offsets,
+                int segments) {
+    if (!ws || count <= 0 || count > 4 || !ws[0]) return -1;
     const int K = ws[0]->K;
     const int ksh = ws[0]->s4_k64 ? 1 : 0;
     for (int i = 0; i < count; ++i) {
@@ -346,15 +375,13 @@ int x_gemm_w4a8_fanout(const tq_qmma_weight_t *const *ws, float *const *ys, int 
         if (!w || !w->s4_ready || w->s4_k16 || !w->d_s4 || !w->d_s4_scale) return -1;
         if (w->K != K || (w->s4_k64 ? 1 : 0) != ksh || (w->M % 16) || (K % 32)) return -1;
     }
-    if (!d_aq || !d_as || !d_asum || T <= 0 || (T % 8) != 0) return -2;
+    if (T <= 0 || (T % 8) != 0) return -2;
     a.goff[0] = 0;
     a.max_splits = 1;
     for (int i = 0; i < count; ++i) {
-        if (!ys[i]) return -2;
         const tq_qmma_weight_t *w = ws[i];
         a.codes[i] = w->d_s4;
         a.scales[i] = w->d_s4_scale;
-        a.y[i] = ys[i];
         a.M[i] = w->M;
         a.goff[i + 1] = a.goff[i] + w->M / 16;
         int ms = 1;
@@ -363,13 +390,68 @@ int x_gemm_w4a8_fanout(const tq_qmma_weight_t *const *ws, float *const *ys, int 
         a.max_splits = std::max(a.max_splits, ms);
     }
     a.count = count;
-    a.aq = d_aq;
-    a.as = d_as;
-    a.asum = d_asum;
     a.K = K;
     a.ksh = ksh;
     a.T = T;
     a.dump = nullptr;
+    return 0;
+}
+
+// Sets the activation source of a prepared GemmArgs: the caller's staging, or x fused / staged.
+void set_fused_input(GemmArgs &a, const float *d_x, int per_token) {
+    a.x = d_x;
+    a.x_mode = per_token ? 2 : 1;
+    if (gemm_ring_covers(a)) return;
+    const size_t blocks = (size_t)(a.K / 32) * a.T;
+    ensure_chunk_scratch(blocks, a.T);
+    if (per_token)
+        launch_quant_chunk_pertoken(d_x, a.K, a.T, g_chunk.aq, g_chunk.as, g_chunk.asum, g_chunk.as_tok);
+    else
+        launch_quant_chunk(d_x, a.K, a.T, g_chunk.aq, g_chunk.as, g_chunk.asum);
+    a.x = nullptr;
+    a.x_mode = 0;
+    a.aq = g_chunk.aq;
+    a.as = g_chunk.as;
+    a.asum = g_chunk.asum;
+}
+
+}  // namespace
+
+int x_gemm_w4a8_fanout(const tq_qmma_weight_t *const *ws, float *const *ys, int count,
+                       const int8_t *d_aq, const float *d_as, const int32_t *d_asum, int T,
+                       const int *offsets, int segments) {
+    if (!ys) return -1;
+    GemmArgs a{};
+    const int rc = fanout_args(a, ws, count, T, offsets, segments);
+    if (rc) return rc;
+    if (!d_aq || !d_as || !d_asum) return -2;
+    for (int i = 0; i < count; ++i) {
+        if (!ys[i]) return -2;
+        a.y[i] = ys[i];
+    }
+    a.aq = d_aq;
+    a.as = d_as;
+    a.asum = d_asum;
+    launch_gemm(a);
+    return 0;
+}
+
+// The same projection from fp32 rows: x[T][K] is quantised like x_quantize_act_chunk
+// (per_token == 0) or x_quantize_act_chunk_pertoken (per_token != 0) and multiplied in one
+// call; for T = 8 the quantiser runs in the GEMM kernel's prologue (one launch). Results are
+// bit-identical to staging first and calling x_gemm_w4a8_fanout.
+int x_gemm_w4a8_fanout_fused(const tq_qmma_weight_t *const *ws, float *const *ys, int count,
+                             const float *d_x, int T, int per_token) {
+    if (!ys) return -1;
+    GemmArgs a{};
+    const int rc = fanout_args(a, ws, count, T, nullptr, 0);
+    if (rc) return rc;
+    if (!d_x) return -2;
+    for (int i = 0; i < count; ++i) {
+        if (!ys[i]) return -2;
+        a.y[i] = ys[i];
+    }
+    set_fused_input(a, d_x, per_token);
     launch_gemm(a);
     return 0;
 }
@@ -378,50 +460,49 @@ int x_gemm_w4a8_fanout(const tq_qmma_weight_t *const *ws, float *const *ys, int 
 // to block `rank` of the gathered buffer [2 halves][world][count][T][M_i] of EVERY rank (peer stores
 // from the kernel's epilogue), followed by a flag store; tq_comm_gather_wait() orders later
 // work after the arrival of all ranks' blocks. Decode shapes only (the streaming kernel).
-int x_gemm_w4a8_fanout_gathered(const tq_qmma_weight_t *const *ws, int count, const int8_t *d_aq,
-                                const float *d_as, const int32_t *d_asum, int T,
-                                size_t *half_offset_floats) {
+namespace {
+// d_x != nullptr: the fused-quantiser form (d_aq / d_as / d_asum unused).
+int gathered_impl(const tq_qmma_weight_t *const *ws, int count, const int8_t *d_aq, const float *d_as,
+                  const int32_t *d_asum, const float *d_x, int per_token, int T,
+                  size_t *half_offset_floats) {
     GatherState &g = gather_state();
     if (g.world < 1) return -3;
-    if (!ws || count <= 0 || count > 4 || !ws[0]) return -1;
     GemmArgs a{};
-    const int K = ws[0]->K;
-    const int ksh = ws[0]->s4_k64 ? 1 : 0;
-    if (!d_aq || !d_as || !d_asum || T <= 0 || (T % 8) != 0) return -2;
+    const int rc = fanout_args(a, ws, count, T, nullptr, 0);
+    if (rc) return rc;
+    if (d_x ? false : (!d_aq || !d_as || !d_asum)) return -2;
     size_t block = 0;
-    for (int i = 0; i < count; ++i) block += (size_t)T * ws[i] ->M;
-    a.goff[0] = 0;
-    a.max_splits = 1;
+    for (int i = 0; i < count; ++i) block += (size_t)T * ws[i]->M;
+    // two halves, used alternately: a rank that is one step ahead never overwrites a block
+    // its peers may still be reading
+    const size_t half = (size_t)((g.step + 1) & 1) * g.world * block;
     size_t off = 0;
     for (int i = 0; i < count; ++i) {
-        const tq_qmma_weight_t *w = ws[i];
-        if (!w || !w->s4_ready || w->s4_k16 || !w->d_s4 || !w->d_s4_scale) return -1;
-        if (w->K != K || (w->s4_k64 ? 1 : 0) != ksh || (w->M % 16) || (K % 32)) return -1;
-        a.codes[i] = w->d_s4;
-        a.scales[i] = w->d_s4_scale;
-        a.M[i] = w->M;
-        a.goff[i + 1] = a.goff[i] + w->M / 16;
-        int ms = 1;
-        const int rc = build_segments(w->M / 16, K / 32, T, nullptr, 0, a.seg[i], ms);
-        if (rc) return rc;
-        a.max_splits = std::max(a.max_splits, ms);
-        // two halves, used alternately: a rank that is one step ahead never overwrites a
-        // block its peers may still be reading
-        const size_t half = (size_t)((g.step + 1) & 1) * g.world * block;
-        for (int p = 0; p < g.world; ++p)
-            a.ypeer[p][i] = g.buf[p] + half + (size_t)g.rank * block + off;
-        off += (size_t)T * w->M;
+        for (int p = 0; p < g.world; ++p) a.ypeer[p][i] = g.buf[p] + half + (size_t)g.rank * block + off;
+        off += (size_t)T * ws[i]->M;
     }
-    a.count = count;
     a.aq = d_aq; a.as = d_as; a.asum = d_asum;
-    a.K = K; a.ksh = ksh; a.T = T;
     a.npeer = g.world;
     if (!gemm_stream_covers(a)) return -21;
+    if (d_x) set_fused_input(a, d_x, per_token);
     g.step += 1;
     if (half_offset_floats) *half_offset_floats = (size_t)(g.step & 1) * g.world * block;
     launch_gemm_stream(a);
     launch_gather_publish(g.step);
     return 0;
+}
+}  // namespace
+
+int x_gemm_w4a8_fanout_gathered(const tq_qmma_weight_t *const *ws, int count, const int8_t *d_aq,
+                                const float *d_as, const int32_t *d_asum, int T,
+                                size_t *half_offset_floats) {
+    return gathered_impl(ws, count, d_aq, d_as, d_asum, nullptr, 0, T, half_offset_floats);
+}
+
+int x_gemm_w4a8_fanout_gathered_fused(const tq_qmma_weight_t *const *ws, int count, const float *d_x,
+                                      int T, int per_token, size_t *half_offset_floats) {
+    if (!d_x) return -2;
+    return gathered_impl(ws, count, nullptr, nullptr, nullptr, d_x, per_token, T, half_offset_floats);
 }
 
 int x_gemm_w4a8(const tq_qmma_weight_t *w, const int8_t *d_aq, const float *d_as,
@@ -687,6 +768,15 @@ int qwn_x_gemm_w4a4(const tq_qmma_weight_t *w, const uint8_t *d_aq4, const float
     return x_gemm_w4a4(w, d_aq4, d_as4, d_asum4, d_y, T);
 }
 
+int qwn_x_gemm_w4a8_fanout_fused(const tq_qmma_weight_t *const *ws, float *const *ys, int count,
+                                 const float *d_x, int T, int per_token) {
+    return x_gemm_w4a8_fanout_fused(ws, ys, count, d_x, T, per_token);
+}
+int qwn_x_gemm_w4a8_fanout_gathered_fused(const tq_qmma_weight_t *const *ws, int count,
+                                          const float *d_x, int T, int per_token,
+                                          size_t *half_offset_floats) {
+    return x_gemm_w4a8_fanout_gathered_fused(ws, count, d_x, T, per_token, half_offset_floats);
+}
 int qwn_x_gemm_w4a8_fanout_gathered(const tq_qmma_weight_t *const *ws, int count,
                                     const int8_t *d_aq, const float *d_as, const int32_t *d_asum,
                                     int T, size_t *half_offset_floats) {

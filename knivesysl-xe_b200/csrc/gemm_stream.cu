@@ -420,6 +420,7 @@ gemm_w4a8_stream_kernel(const GemmArgs a, float *__restrict__ part, int *__restr
 constexpr int kRW = 32;                              // most warps per CTA (a launch may use fewer)
 constexpr int kRST = 8;                              // tiles per ring stage (4 and 6 measured slower)
 constexpr int kRStage = kRST * 256 + kRST * 32;      // codes, then one scale line per tile
+constexpr int kRHead = 64;                           // small per-CTA header in front of the rings
 
 __device__ __forceinline__ uint2 lds_v2(uint32_t addr) {
     uint2 v;
@@ -470,9 +471,11 @@ gemm_w4a8_ring_kernel(const GemmArgs a, float *__restrict__ part, int *__restric
     const int kt_begin = Kt * split / S;
     const int cnt = Kt * (split + 1) / S - kt_begin;
 
-    unsigned char *ring = smem + (size_t)warp * kRNS * kRStage;
+    // 64 bytes in front of the rings: the row maxima of the fused per-token quantiser
+    int *s_rowmax = reinterpret_cast<int *>(smem);
+    unsigned char *ring = smem + kRHead + (size_t)warp * kRNS * kRStage;
     const uint32_t ring_s = smem_u32(ring);
-    unsigned char *act = smem + (size_t)nw * kRNS * kRStage;
+    unsigned char *act = smem + kRHead + (size_t)nw * kRNS * kRStage;
     const uint32_t act_s = smem_u32(act);
     float *xpose = reinterpret_cast<float *>(act + (size_t)cnt * kActTileBytes) + warp * 128;
     const uint64_t pol = l2_policy_evict_first();
@@ -528,7 +531,59 @@ gemm_w4a8_ring_kernel(const GemmArgs a, float *__restrict__ part, int *__restric
 
     // Stage this split's activations (layout of the register-queue kernel for T = 8, but the
     // code sums are stored negated: the tile loop multiplies them by z + 8 >= 0).
-    {
+    if (a.x) {
+        // Fused quantiser: the fp32 rows are quantised here with the rule and the arithmetic
+        // of quant_chunk_kernel (per (token, K32) block, or with the row's absmax / 127 in
+        // per-token mode), straight into the staged layout. A warp takes one (k-tile, token)
+        // block at a time, lane = k.
+        const int K = a.K;
+        if (a.x_mode == 2) {
+            if (threadIdx.x < 8) s_rowmax[threadIdx.x] = __float_as_int(-INFINITY);
+            __syncthreads();
+            float m[8];
+#pragma unroll
+            for (int t = 0; t < 8; ++t) m[t] = -INFINITY;
+            for (int i = threadIdx.x; i < (K >> 2); i += nw * 32) {
+#pragma unroll
+                for (int t = 0; t < 8; ++t) {
+                    const float4 v = __ldg(reinterpret_cast<const float4 *>(a.x + (size_t)t * K) + i);
+                    m[t] = fmaxf(m[t], fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+                }
+            }
+#pragma unroll
+            for (int t = 0; t < 8; ++t) {
+                const float wm = warp_max(m[t]);
+                // non-negative floats (and -inf) order like their bit patterns as signed ints
+                if (lane == 0) atomicMax(&s_rowmax[t], __float_as_int(wm));
+            }
+            __syncthreads();
+        }
+        for (int b = warp; b < cnt * 8; b += nw) {
+            const int kl = b >> 3, t = b & 7;
+            const float v = __ldg(a.x + (size_t)t * K + (size_t)(kt_begin + kl) * 32 + lane);
+            float s;
+            if (a.x_mode == 2) {
+                const float mx = __int_as_float(s_rowmax[t]);
+                s = (mx > 0.0f) ? __fdiv_rn(mx, 127.0f) : 1.0f;
+            } else {
+                const float mx = warp_max(fmaxf(-INFINITY, fabsf(v)));
+                s = (mx > 0.0f) ? __fdiv_rn(mx, 127.0f) : 1.0f;
+            }
+            const int qv = quantise_one(v, s);
+            int sum = half_sum16(qv);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 16);
+            // B-fragment order: token t, chunk c = k / 8: the chunk's even-k bytes, then its odd-k
+            const int c8 = lane >> 3, j = lane & 7;
+            act[(size_t)kl * kActTileBytes + (t * 4 + c8) * 8 + ((j & 1) * 4 + (j >> 1))] =
+                (unsigned char)(int8_t)qv;
+            if (lane == 0) {
+                float *pv = reinterpret_cast<float *>(act + (size_t)kl * kActTileBytes + 256 + (t >> 1) * 16);
+                pv[t & 1] = s;
+                pv[2 + (t & 1)] = -(float)sum;
+            }
+        }
+        __syncthreads();
+    } else {
         const int items = cnt * 32;
         for (int i = threadIdx.x; i < items; i += nw * 32) {
             const int kl = i >> 5;
@@ -790,7 +845,12 @@ int window_groups(const GemmArgs &a) {
 }
 
 // The ring kernel takes T = 8 calls whose split activations fit beside the rings.
-bool launch_ring(const GemmArgs &a) {
+// Launch shape of the ring kernel for a call, or false when the call is not its to take.
+struct RingPlan {
+    int grid, nw, ns;
+    size_t smem;
+};
+bool ring_plan(const GemmArgs &a, RingPlan &p) {
     if (a.T != 8 || a.dump) return false;
     if (!g_num_sms) {
         int dev = 0;
@@ -800,20 +860,30 @@ bool launch_ring(const GemmArgs &a) {
     }
     const int Kt = a.K >> 5, S = a.max_splits;
     const int groups = a.goff[a.count];
-    if (S > g_num_sms) return false;
+    if (S > g_num_sms || groups <= 0) return false;
     const long most = (long)groups * S;
-    const int grid = (int)std::max<long>(S, std::min<long>(g_num_sms - g_num_sms % S, most));
+    p.grid = (int)std::max<long>(S, std::min<long>(g_num_sms - g_num_sms % S, most));
     // One task per warp when the call has fewer tasks than warp slots: fewer warps, and the
     // shared memory they leave goes into deeper rings (each warp's chain is then longer
     // than the memory latency its ring covers with two stages).
-    const int per_cta = (groups + grid / S - 1) / (grid / S);          // tasks of the busiest CTA
-    int nw = kRW;
-    if (per_cta < kRW) nw = std::max(8, (per_cta + 1) / 2 * 2);
-    const size_t fixed = (size_t)((Kt + S - 1) / S) * kActTileBytes + (a.npeer ? (size_t)nw * 512 : 0);
-    int ns = 4;
-    while (ns > 2 && (size_t)nw * ns * kRStage + fixed > kSmemLimit) --ns;
-    const size_t smem = (size_t)nw * ns * kRStage + fixed;
-    if (smem > kSmemLimit) return false;
+    const int per_cta = (groups + p.grid / S - 1) / (p.grid / S);      // tasks of the busiest CTA
+    p.nw = kRW;
+    if (per_cta < kRW) p.nw = std::max(8, (per_cta + 1) / 2 * 2);
+    const size_t fixed =
+        kRHead + (size_t)((Kt + S - 1) / S) * kActTileBytes + (a.npeer ? (size_t)p.nw * 512 : 0);
+    p.ns = 4;
+    while (p.ns > 2 && (size_t)p.nw * p.ns * kRStage + fixed > kSmemLimit) --p.ns;
+    p.smem = (size_t)p.nw * p.ns * kRStage + fixed;
+    return p.smem <= kSmemLimit;
+}
+
+bool launch_ring(const GemmArgs &a) {
+    RingPlan plan;
+    if (!ring_plan(a, plan)) return false;
+    const int Kt = a.K >> 5, S = a.max_splits;
+    const int groups = a.goff[a.count];
+    const int grid = plan.grid, nw = plan.nw, ns = plan.ns;
+    const size_t smem = plan.smem;
     bool pair = a.ksh != 0;
     for (int s2 = 0; s2 < S; ++s2) pair = pair && ((Kt * s2 / S) % 2 == 0);
     if (S > 1) ensure_scratch((size_t)groups * S * 128, groups);
@@ -849,6 +919,11 @@ bool launch_ring(const GemmArgs &a) {
     }
     TQ_LAUNCH_CHECK("gemm_w4a8_ring_kernel");
     return true;
+}
+
+bool gemm_ring_covers(const GemmArgs &a) {
+    RingPlan plan;
+    return gemm_stream_covers(a) && ring_plan(a, plan);
 }
 
 void launch_gemm_stream(const GemmArgs &a) {

@@ -455,17 +455,21 @@ def test_gathered_gemm_single_rank(lib, pkg, orc, wl):
     flg = (C.c_void_p * 1)(flags.ptr)
     assert lib.tq_comm_gather_setup(bufs, flg, 1, 0) == 0
     halves = []
-    for step in range(2):
+    for step in range(3):
         off = C.c_size_t(0)
-        assert lib.qwn_x_gemm_w4a8_fanout_gathered(pkg.weight_array(ws), 2, aq.ptr, as_.ptr,
-                                                   asum.ptr, T, C.byref(off)) == 0
+        if step == 2:      # the fused-quantiser form of the same call (per-block scales)
+            assert lib.qwn_x_gemm_w4a8_fanout_gathered_fused(pkg.weight_array(ws), 2, dx.ptr, T, 0,
+                                                             C.byref(off)) == 0
+        else:
+            assert lib.qwn_x_gemm_w4a8_fanout_gathered(pkg.weight_array(ws), 2, aq.ptr, as_.ptr,
+                                                       asum.ptr, T, C.byref(off)) == 0
         assert lib.tq_comm_gather_wait() == 0
         lib.tq_sync()
         halves.append(off.value)
         got = gathered.to_numpy(np.float32)[off.value: off.value + block]
         assert got.tobytes() == want.tobytes()
         assert flags.to_numpy(np.int32)[0] == step + 1
-    assert sorted(halves) == [0, block]
+    assert sorted(set(halves)) == [0, block]
     assert lib.tq_last_error() == 0
 
 
@@ -784,3 +788,33 @@ def test_rmsnorm_chunk(lib, pkg, orc, H, T):
     x64 = x.astype(np.float64)
     ref = x64 / np.sqrt((x64 ** 2).mean(axis=1, keepdims=True) + 1e-6) * (1.0 + wf)
     assert np.abs(want - ref).max() <= 1e-5 * np.abs(ref).max()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("Ms,K,ksh,T,per_token", [
+    ([1088, 1088], 5120, 1, 8, True), ([1088, 544], 512, 1, 8, False), ([320], 2112, 0, 8, True),
+    ([4800], 2112, 1, 8, False), ([64, 64], 512, 0, 16, True), ([48], 384, 0, 24, False)])
+def test_gemm_fanout_fused_quantiser(lib, pkg, orc, wl, Ms, K, ksh, T, per_token):
+    """x_gemm_w4a8_fanout_fused: the quantiser in the GEMM's prologue (T = 8) or staged by the
+    library (other T) gives the bits of staging first and calling x_gemm_w4a8_fanout, which in
+    turn are the oracle's."""
+    ws, host = [], []
+    for i, M in enumerate(Ms):
+        c, s = wl.random_packed_weight(M, K, seed=300 + i + T, ksh=ksh)
+        host.append((c, s, M))
+        ws.append(pkg.PackedWeight(c, s, M, K, k64=bool(ksh)))
+    x = wl.activations_normal(T, K, seed=K + T, outlier_frac=0.01)
+    x[1, :32] = 0.0
+    dx = dev(pkg, x)
+    ys = [pkg.DevBuf(T * M * 4) for M in Ms]
+    for y in ys:
+        y.fill(0xA5)
+    assert lib.qwn_x_gemm_w4a8_fanout_fused(pkg.weight_array(ws), pkg.ptr_array(ys), len(Ms), dx.ptr, T,
+                                            int(per_token)) == 0
+    lib.tq_sync()
+    oq, os_, osm = orc.quantize_act_chunk(x, per_token=per_token)
+    for (c, s, M), y in zip(host, ys):
+        _, want = orc.gemm_w4a8(c, s, M, K, ksh, oq, os_, osm, T, fma=1)
+        assert y.to_numpy(np.float32).tobytes() == np.ascontiguousarray(want).tobytes()
+    assert lib.qwn_x_gemm_w4a8_fanout_fused(pkg.weight_array(ws), pkg.ptr_array(ys), len(Ms), None, T, 0) == -2
+    assert lib.tq_last_error() == 0
