@@ -157,6 +157,11 @@ def main():
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
                     help="N > 1: every rank holds a cfg2-sized column shard of an N-times wider "
                          "projection (weak, default), or cfg2 itself is cut into N shards (strong)")
+    ap.add_argument("--quantiser", default="staged", choices=["fused", "staged"],
+                    help="activation quantiser as its own launch before the GEMM (the reference's "
+                         "two calls; default, faster here), or in the GEMM's prologue (one launch: "
+                         "every CTA then reads the same fp32 rows from L2 at once, which costs more "
+                         "than the staging launch it saves)")
     ap.add_argument("--exchange", default="fused", choices=["fused", "nccl"],
                     help="N > 1: all-gather by peer stores from the GEMM epilogue (fused) or by NCCL")
     args = ap.parse_args()
@@ -258,12 +263,29 @@ def main():
         assert rc == 0, rc
         assert lib.tq_comm_gather_wait() == 0
 
-    def step(i):
-        stage()
-        if fused:
-            gemm_gathered(i)             # the epilogue stores this rank's slice on every rank
+    # The step a user runs: ONE call that quantises the fp32 activations per token in the GEMM
+    # kernel's prologue, multiplies gate|up and (N > 1) gathers the ranks' slices.
+    qfused = args.quantiser == "fused"
+
+    def gemm_fused(i, out=None):
+        if qfused:
+            rc = lib.qwn_x_gemm_w4a8_fanout_fused(warr[i % args.rotate], out or yarr, 2, dx.ptr, T, 1)
         else:
-            gemm(i)
+            stage()
+            rc = lib.qwn_x_gemm_w4a8_fanout(warr[i % args.rotate], out or yarr, 2, aq.ptr, as_.ptr,
+                                            asum.ptr, T, None, 0)
+        assert rc == 0, rc
+
+    def step(i):
+        if fused and qfused:
+            rc = lib.qwn_x_gemm_w4a8_fanout_gathered_fused(warr[i % args.rotate], 2, dx.ptr, T, 1,
+                                                           C.byref(half_off))
+            assert rc == 0, rc
+        elif fused:
+            stage()
+            gemm_gathered(i)
+        else:
+            gemm_fused(i)
             if world > 1:
                 assert lib.tq_comm_allgather(ycat.ptr, gathered.ptr, ycat.nbytes) == 0
 
@@ -277,7 +299,7 @@ def main():
             lib.tq_sync()
             ref = gathered.to_numpy(np.float32)[: world * block].copy()
             dist.barrier()
-            gemm_gathered(i)
+            step(i)                  # fused quantiser + GEMM + peer-store gather
             lib.tq_sync()
             dist.barrier()
             got = gathered.to_numpy(np.float32)[half_off.value: half_off.value + world * block]
@@ -314,13 +336,14 @@ def main():
 
     # ---- dominant kernel alone (this rank's shard), for the roofline -----------------------
     stage()
+    alone = gemm_fused if qfused else gemm      # staged: the GEMM launch without its staging
     for i in range(args.warmup):
-        gemm(i)
+        alone(i)
     lib.tq_sync()
     k_iters = max(args.steps, 200)
     lib.tq_event_record(ev[0])
     for i in range(k_iters):
-        gemm(i)
+        alone(i)
     lib.tq_event_record(ev[1])
     lib.tq_sync()
     k_ms = lib.tq_event_elapsed_ms(ev[0], ev[1]) / k_iters
@@ -329,7 +352,7 @@ def main():
         barrier()
         lib.tq_event_record(ev[0])
         for i in range(k_iters):
-            gemm_gathered(i)
+            step(i)
         lib.tq_event_record(ev[1])
         barrier()
         g_ms = lib.tq_event_elapsed_ms(ev[0], ev[1]) / k_iters
@@ -337,7 +360,8 @@ def main():
             print(f"[bench] GEMM alone {k_ms * 1e3:.2f} us; gathered GEMM + wait {g_ms * 1e3:.2f} us; "
                   f"step {ms / args.steps * 1e3:.2f} us", file=sys.stderr)
     shard_weight = 2 * wl.weight_bytes(n_shard, K, GROUP)
-    algo_bytes = shard_weight + T * K + nblk * 8 + block * 4
+    # weights + the fp32 activation rows the prologue quantises + the fp32 outputs
+    algo_bytes = shard_weight + (T * K * 4 if qfused else T * K + nblk * 8) + block * 4
     achieved = algo_bytes / (k_ms * 1e-3) / 1e9
     peak, peak_kind = measured_peaks()
 
@@ -362,10 +386,7 @@ def main():
             lib.tq_stream_wait_copy(tickets[b])
         lib.tq_h2d_async(dx.ptr, hx, x.nbytes)
         if world == 1:
-            stage()
-            rc = lib.qwn_x_gemm_w4a8_fanout(warr[i % args.rotate], yarr2 if b else yarr, 2, aq.ptr,
-                                            as_.ptr, asum.ptr, T, None, 0)
-            assert rc == 0, rc
+            gemm_fused(i, yarr2 if b else yarr)
             src = (ycat2 if b else ycat).ptr
         else:
             step(i)
@@ -394,7 +415,7 @@ def main():
         tend = time.time() + 0.6
         i = 0
         while time.time() < tend:
-            gemm(i)
+            gemm_fused(i)
             i += 1
             if i % 256 == 0:
                 lib.tq_sync()
@@ -434,18 +455,20 @@ def main():
                            if fused else " + NCCL all-gather"),
                        "l2": f"inputs larger than L2: {args.rotate} rotating weight copies, "
                              f"{args.rotate * shard_weight / 1e6:.0f} MB per GPU",
-                       "step": "per-token staging (1 launch) + fused gate|up GEMM" +
+                       "step": ("one launch: per-token activation quantiser in the prologue of the "
+                                "fused gate|up GEMM" if qfused else
+                                "per-token staging (1 launch) + fused gate|up GEMM") +
                                (" + all-gather" if world > 1 else "")},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "peak_source": f"{peak_kind} copy bandwidth",
                          "kernel": "gemm_w4a8_ring_kernel", "us_per_launch": k_ms * 1e3,
                          "algorithmic_bytes_per_launch": algo_bytes,
                          # the capture is of the whole-cfg2 launch; a shard's traffic scales with it
-                         "traffic": int(NCU_TRAFFIC_BYTES_PER_LAUNCH * algo_bytes / 95_864_832)},
+                         "traffic": int(NCU_TRAFFIC_BYTES_PER_LAUNCH * algo_bytes / 95_977_472)},
             "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": int(x.nbytes),
                     "d2h_bytes_per_step": int(out_bytes), "steps": e_iters,
                     "us_per_step": e_s / e_iters * 1e6},
-            "gpu_launches": (2 + (1 if fused else 0) + (1 if world > 1 and not fused else 0)) * args.steps,
+            "gpu_launches": ((1 if qfused else 2) + (1 if fused else 0) + (1 if world > 1 and not fused else 0)) * args.steps,
             "clocks": clocks,
             "cpu_baseline": cpu,
             "device_error": err,

@@ -558,28 +558,43 @@ gemm_w4a8_ring_kernel(const GemmArgs a, float *__restrict__ part, int *__restric
             }
             __syncthreads();
         }
-        for (int b = warp; b < cnt * 8; b += nw) {
-            const int kl = b >> 3, t = b & 7;
-            const float v = __ldg(a.x + (size_t)t * K + (size_t)(kt_begin + kl) * 32 + lane);
-            float s;
-            if (a.x_mode == 2) {
-                const float mx = __int_as_float(s_rowmax[t]);
-                s = (mx > 0.0f) ? __fdiv_rn(mx, 127.0f) : 1.0f;
-            } else {
-                const float mx = warp_max(fmaxf(-INFINITY, fabsf(v)));
-                s = (mx > 0.0f) ? __fdiv_rn(mx, 127.0f) : 1.0f;
+        // kQU blocks per pass, their loads issued together (one load per block and lane)
+        constexpr int kQU = 8;
+        for (int b0 = warp; b0 < cnt * 8; b0 += nw * kQU) {
+            float vv[kQU];
+#pragma unroll
+            for (int u = 0; u < kQU; ++u) {
+                const int b = b0 + u * nw;
+                vv[u] = 0.0f;
+                if (b < cnt * 8)
+                    vv[u] = __ldg(a.x + (size_t)(b & 7) * K + (size_t)(kt_begin + (b >> 3)) * 32 + lane);
             }
-            const int qv = quantise_one(v, s);
-            int sum = half_sum16(qv);
-            sum += __shfl_xor_sync(0xffffffffu, sum, 16);
-            // B-fragment order: token t, chunk c = k / 8: the chunk's even-k bytes, then its odd-k
-            const int c8 = lane >> 3, j = lane & 7;
-            act[(size_t)kl * kActTileBytes + (t * 4 + c8) * 8 + ((j & 1) * 4 + (j >> 1))] =
-                (unsigned char)(int8_t)qv;
-            if (lane == 0) {
-                float *pv = reinterpret_cast<float *>(act + (size_t)kl * kActTileBytes + 256 + (t >> 1) * 16);
-                pv[t & 1] = s;
-                pv[2 + (t & 1)] = -(float)sum;
+#pragma unroll
+            for (int u = 0; u < kQU; ++u) {
+                const int b = b0 + u * nw;
+                if (b >= cnt * 8) break;
+                const int kl = b >> 3, t = b & 7;
+                const float v = vv[u];
+                float s;
+                if (a.x_mode == 2) {
+                    const float mx = __int_as_float(s_rowmax[t]);
+                    s = (mx > 0.0f) ? __fdiv_rn(mx, 127.0f) : 1.0f;
+                } else {
+                    const float mx = warp_max(fmaxf(-INFINITY, fabsf(v)));
+                    s = (mx > 0.0f) ? __fdiv_rn(mx, 127.0f) : 1.0f;
+                }
+                const int qv = quantise_one(v, s);
+                int sum = half_sum16(qv);
+                sum += __shfl_xor_sync(0xffffffffu, sum, 16);
+                // B-fragment order: token t, chunk c = k / 8: the chunk's even-k bytes, then its odd-k
+                const int c8 = lane >> 3, j = lane & 7;
+                act[(size_t)kl * kActTileBytes + (t * 4 + c8) * 8 + ((j & 1) * 4 + (j >> 1))] =
+                    (unsigned char)(int8_t)qv;
+                if (lane == 0) {
+                    float *pv = reinterpret_cast<float *>(act + (size_t)kl * kActTileBytes + 256 + (t >> 1) * 16);
+                    pv[t & 1] = s;
+                    pv[2 + (t & 1)] = -(float)sum;
+                }
             }
         }
         __syncthreads();
