@@ -125,6 +125,12 @@ int qwn_x_gemv_w4a8(const tq_qmma_weight_t *w, const float *d_x, float *d_y);
 int qwn_x_gemv_w4a8_add(const tq_qmma_weight_t *w, const float *d_x, const float *d_residual,
                         float *d_y);
 int qwn_x_gemv_w4a8_prepared(const tq_qmma_weight_t *w, float *d_y, const float *d_residual);
+/* x_gemv_w4a8 (d_residual == NULL) or x_gemv_w4a8_add in ONE launch: the GEMV quantises the
+ * row in its prologue and leaves the prepared scratch as x_prepare_gemv_act_s8 would. Same
+ * bits as the two-launch entry points above, which are the faster form on B200 for wide
+ * weights; this one serves callers that count launches. No counterpart in the reference. */
+int qwn_x_gemv_w4a8_fused(const tq_qmma_weight_t *w, const float *d_x, const float *d_residual,
+                          float *d_y);
 /* xpu/src/kernels_dpas.cpp:945-1102: up to 4 weights sharing K, tier and the prepared
  * activation in one launch. Returns 0, -1, -2 (tier/K mismatch), -3 (not prepared). */
 int qwn_x_gemv_w4a8_fanout(const tq_qmma_weight_t *const *ws, float *const *ys, int count);
@@ -321,6 +327,8 @@ void x_quantize_act_chunk(const float *d_x, int K, int T, int8_t *d_aq, float *d
 int x_gemm_w4a8(const tq_qmma_weight_t *w, const int8_t *d_aq, const float *d_as,
                 const int32_t *d_asum, float *d_y, int T, const int *offsets = nullptr,
                 int segments = 0);
+int x_gemv_w4a8_fused(const tq_qmma_weight_t *w, const float *d_x, const float *d_residual,
+                      float *d_y);
 int x_gemv_w4a8_prepared(const tq_qmma_weight_t *w, float *d_y,
                          const float *d_residual = nullptr);
 int x_gemv_qmma_prepared(const tq_qmma_weight_t *w, const float *d_x, float *d_y,

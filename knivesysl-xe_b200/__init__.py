@@ -62,6 +62,7 @@ SIGNATURES = {
     "qwn_x_gemv_w4a8": (_i, [_WP, _vp, _vp]),
     "qwn_x_gemv_w4a8_add": (_i, [_WP, _vp, _vp, _vp]),
     "qwn_x_gemv_w4a8_prepared": (_i, [_WP, _vp, _vp]),
+    "qwn_x_gemv_w4a8_fused": (_i, [_WP, _vp, _vp, _vp]),
     "qwn_x_gemv_w4a8_fanout": (_i, [C.POINTER(_WP), C.POINTER(_vp), _i]),
     "qwn_x_w8_repack_weight": (_i, [_WP]),
     "qwn_x_gemv_w8a8": (_i, [_WP, _vp, _vp]), "qwn_x_gemv_w8a8_add": (_i, [_WP, _vp, _vp, _vp]),

@@ -4,7 +4,9 @@
   python knivesysl-xe_b200/cases.py run <case> [launches]     # e.g. under ncu
   python knivesysl-xe_b200/cases.py time [case ...]           # CUDA-graph replay timing
 
-Cases: cfg1 (GEMV 17408x5120 K32), gemv_down (GEMV 5120x17408), cfg2 (fused gate+up K64,
+Cases: cfg1 (GEMV 17408x5120 K32), gemv_down (GEMV 5120x17408), cfg1_from_x / cfg1_one_launch and
+gemv_down_from_x / gemv_down_one_launch (the same GEMVs from the fp32 row: x_gemv_w4a8 = staging
+launch + GEMV, and x_gemv_w4a8_fused = quantiser in the GEMV's prologue), cfg2 (fused gate+up K64,
 T=8), down_t8 / down_t16 / down_t32 / down_t64 (5120x17408 K32), prefill_small (tcgen05 GEMM
 2048x5120, T=1024), cfg4 (tcgen05 GEMM 17408x5120 K64, T=4096 in 4 segments), cfg4_w4a4 (the
 same shape through x_gemm_w4a4: int4 activations, one promote per K64 group), w8_lm_head (W8A8
@@ -48,6 +50,20 @@ class Gemv:
 
     def launch(self, i):
         assert self.lib.qwn_x_gemv_w4a8_prepared(self.ws[i % ROT].ref, self.y.ptr, None) == 0
+
+
+class GemvFromX(Gemv):
+    """x_gemv_w4a8 from the fp32 row (quantiser + GEMV in one call)."""
+
+    def launch(self, i):
+        assert self.lib.qwn_x_gemv_w4a8(self.ws[i % ROT].ref, self.dx.ptr, self.y.ptr) == 0
+
+
+class GemvOneLaunch(Gemv):
+    """x_gemv_w4a8_fused: the quantiser in the GEMV's prologue (one launch)."""
+
+    def launch(self, i):
+        assert self.lib.qwn_x_gemv_w4a8_fused(self.ws[i % ROT].ref, self.dx.ptr, None, self.y.ptr) == 0
 
 
 class Gemm:
@@ -127,6 +143,10 @@ class GemmW4A4:
 CASES = {
     "cfg1": lambda lib: Gemv(lib, 17408, 5120, False),
     "gemv_down": lambda lib: Gemv(lib, 5120, 17408, False),
+    "cfg1_from_x": lambda lib: GemvFromX(lib, 17408, 5120, False),
+    "cfg1_one_launch": lambda lib: GemvOneLaunch(lib, 17408, 5120, False),
+    "gemv_down_from_x": lambda lib: GemvFromX(lib, 5120, 17408, False),
+    "gemv_down_one_launch": lambda lib: GemvOneLaunch(lib, 5120, 17408, False),
     "cfg2": lambda lib: Gemm(lib, [17408, 17408], 5120, True, 8),
     "down_t8": lambda lib: Gemm(lib, [5120], 17408, False, 8),
     "down_t16": lambda lib: Gemm(lib, [5120], 17408, False, 16),

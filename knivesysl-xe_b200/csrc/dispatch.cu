@@ -79,9 +79,13 @@ int gemv_prepared_impl(const tq_qmma_weight_t *w, float *d_y, const float *d_res
     return 0;
 }
 
-// One launch for x_gemv_w4a8 / _add: the GEMV quantises the row in its prologue (and keeps
-// the prepared scratch current). Rows too long for the kernel's shared memory take the two
-// launches of the reference (x_prepare_gemv_act_s8, then the prepared GEMV).
+// One launch for a GEMV from the fp32 row (x_gemv_w4a8_fused): the GEMV quantises the row in
+// its own prologue and keeps the prepared scratch current. x_gemv_w4a8 / _add themselves take
+// the reference's two launches, which are the faster form on B200 (17408x5120: 11.8 us
+// against 13.7 us; 5120x17408: 12.3 us against 28.7 us): with the quantiser inside, every CTA
+// quantises the whole row from the same L2 lines at the same moment and the kernel cannot
+// use its one-row-group launch shape. Rows too long for the kernel's shared memory, and the
+// K16 tier, take the two launches here too.
 int gemv_fused_impl(const tq_qmma_weight_t *w, const float *d_x, const float *d_residual,
                     float *d_y) {
     if (!w4_usable(w) || w->K <= 0 || (w->K % 32) || w->s4_k16) {
@@ -205,12 +209,20 @@ int x_gemv_w4a8_prepared(const tq_qmma_weight_t *w, float *d_y, const float *d_r
 
 int x_gemv_w4a8(const tq_qmma_weight_t *w, const float *d_x, float *d_y) {
     if (!w || !d_x) return -1;
-    return gemv_fused_impl(w, d_x, nullptr, d_y);
+    x_prepare_gemv_act_s8(d_x, w->K);
+    return gemv_prepared_impl(w, d_y, nullptr, nullptr);
 }
 
 int x_gemv_w4a8_add(const tq_qmma_weight_t *w, const float *d_x, const float *d_residual,
                     float *d_y) {
     if (!w || !d_x || !d_residual) return -1;
+    x_prepare_gemv_act_s8(d_x, w->K);
+    return gemv_prepared_impl(w, d_y, d_residual, nullptr);
+}
+
+int x_gemv_w4a8_fused(const tq_qmma_weight_t *w, const float *d_x, const float *d_residual,
+                      float *d_y) {
+    if (!w || !d_x) return -1;
     return gemv_fused_impl(w, d_x, d_residual, d_y);
 }
 
@@ -708,6 +720,10 @@ int qwn_x_gemv_w8a8_prepared(const tq_qmma_weight_t *w, float *d_y, const float 
 int qwn_x_gemm_w8a8(const tq_qmma_weight_t *w, const int8_t *d_aq, const float *d_as, float *d_y,
                     int T) {
     return x_gemm_w8a8(w, d_aq, d_as, d_y, T);
+}
+int qwn_x_gemv_w4a8_fused(const tq_qmma_weight_t *w, const float *d_x, const float *d_residual,
+                          float *d_y) {
+    return x_gemv_w4a8_fused(w, d_x, d_residual, d_y);
 }
 int qwn_x_gemv_qmma(const tq_qmma_weight_t *w, const float *d_x, float *d_y) {
     return x_gemv_qmma(w, d_x, d_y);

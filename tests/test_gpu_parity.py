@@ -476,20 +476,24 @@ def test_gathered_gemm_single_rank(lib, pkg, orc, wl):
 @pytest.mark.gpu
 @pytest.mark.parametrize("M,K,ksh", [(1088, 5120, 0), (320, 1024, 1), (64, 256, 0)])
 def test_gemv_fused_quant_prologue(lib, pkg, orc, wl, M, K, ksh):
-    """x_gemv_w4a8 quantises the row inside the GEMV launch: same bits as the oracle, and the
-    prepared scratch it leaves behind serves a following *_prepared call like the reference's
-    x_prepare_gemv_act_s8 would."""
+    """x_gemv_w4a8_fused quantises the row inside the GEMV launch: same bits as the oracle and
+    as the two-launch x_gemv_w4a8, and the prepared scratch it leaves behind serves a following
+    *_prepared call like the reference's x_prepare_gemv_act_s8 would."""
     codes, scales = wl.random_packed_weight(M, K, seed=3 * M + K, ksh=ksh)
     w = pkg.PackedWeight(codes, scales, M, K, k64=bool(ksh))
     x = refgen.shard_check_row(K)
     y = pkg.DevBuf(M * 4)
     y.fill(0xA5)
     dx = dev(pkg, x)
-    assert lib.qwn_x_gemv_w4a8(w.ref, dx.ptr, y.ptr) == 0
+    y0 = pkg.DevBuf(M * 4)
+    assert lib.qwn_x_gemv_w4a8(w.ref, dx.ptr, y0.ptr) == 0          # two launches
+    lib.qwn_x_prepare_gemv_act_s8(dev(pkg, np.zeros(K, np.float32)).ptr, K)   # scratch overwritten
+    assert lib.qwn_x_gemv_w4a8_fused(w.ref, dx.ptr, None, y.ptr) == 0
     lib.tq_sync()
     q, s, sm = orc.quantize_act_s8(x)
     _, want = orc.gemv_w4a8(codes, scales, M, K, ksh, q, s, sm, fma=1)
     assert y.to_numpy(np.float32).tobytes() == want.tobytes()
+    assert y0.to_numpy(np.float32).tobytes() == want.tobytes()
     dq, ds, dsum = pkg.DevBuf(K), pkg.DevBuf(K // 32 * 4), pkg.DevBuf(K // 16 * 4)
     assert lib.qwn_dbg_prepared_act(K, dq.ptr, ds.ptr, dsum.ptr) == 0
     lib.tq_sync()
