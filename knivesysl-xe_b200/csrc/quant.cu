@@ -257,6 +257,70 @@ quant_chunk_pertoken_fused_kernel(const float *__restrict__ x, int K, int T,
     }
 }
 
+// The same result in one pass for rows of at most 8192 values: a thread keeps its (up to) two
+// float4 of the row in registers between the maximum and the quantisation, so the kernel is
+// one global round trip, the block reduction and the stores. Eight consecutive lanes hold one
+// K32 block; their code sums are added with three shuffles.
+__global__ void __launch_bounds__(1024)
+quant_chunk_pertoken_regs_kernel(const float *__restrict__ x, int K, int T,
+                                 int8_t *__restrict__ aq, float *__restrict__ as,
+                                 int32_t *__restrict__ asum, float *__restrict__ as_tok) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ float wmax[32];
+    __shared__ float s_scale;
+    const int tok = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const float4 *row4 = reinterpret_cast<const float4 *>(x + (size_t)tok * K);
+    const int n4 = K >> 2;
+    float4 v[2];
+    float m = -INFINITY;
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+        const int i = threadIdx.x + u * 1024;
+        v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (i < n4) {
+            v[u] = row4[i];
+            m = fmaxf(m, fmaxf(fmaxf(fabsf(v[u].x), fabsf(v[u].y)), fmaxf(fabsf(v[u].z), fabsf(v[u].w))));
+        }
+    }
+    m = warp_max(m);
+    if (lane == 0) wmax[warp] = m;
+    __syncthreads();
+    if (warp == 0) {
+        const float t = warp_max(wmax[lane]);
+        if (lane == 0) {
+            const float s = (t > 0.0f) ? __fdiv_rn(t, 127.0f) : 1.0f;
+            s_scale = s;
+            as_tok[tok] = s;
+        }
+    }
+    __syncthreads();
+    const float s = s_scale;
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+        const int i = threadIdx.x + u * 1024;       // float4 index in the row; uniform per warp
+        if (i - lane >= n4) break;
+        const int q0 = quantise_one(v[u].x, s), q1 = quantise_one(v[u].y, s);
+        const int q2 = quantise_one(v[u].z, s), q3 = quantise_one(v[u].w, s);
+        int sum = q0 + q1 + q2 + q3;
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+        if (i < n4) {
+            const int kt = i >> 3;                   // eight float4 per K32 block
+            const size_t blk = (size_t)kt * T + tok;
+            const uint32_t packed = (uint32_t)(q0 & 0xFF) | ((uint32_t)(q1 & 0xFF) << 8) |
+                                    ((uint32_t)(q2 & 0xFF) << 16) | ((uint32_t)(q3 & 0xFF) << 24);
+            reinterpret_cast<uint32_t *>(aq + blk * 32)[i & 7] = packed;
+            if ((i & 7) == 0) {
+                as[blk] = s;
+                asum[blk] = sum;
+            }
+        }
+    }
+}
+
 // K32 code sums of already staged codes (debug helper for the int32 dump).
 __global__ void code_sums_kernel(const int8_t *__restrict__ aq, size_t blocks,
                                  int32_t *__restrict__ asum) {
@@ -337,6 +401,12 @@ void launch_quant_chunk_pertoken(const float *d_x, int K, int T, int8_t *d_aq, f
                                  int32_t *d_asum, float *d_as_tok) {
     const size_t blocks = (size_t)(K / 32) * (size_t)T;
     if (!blocks) return;
+    if (T <= 32 && K <= 8192) {
+        launch_pdl(quant_chunk_pertoken_regs_kernel, dim3(T), dim3(1024), 0, d_x, K, T, d_aq, d_as,
+                   d_asum, d_as_tok);
+        TQ_LAUNCH_CHECK("quant_chunk_pertoken_regs_kernel");
+        return;
+    }
     if (T <= 32) {
         launch_pdl(quant_chunk_pertoken_fused_kernel, dim3(T), dim3(1024), 0, d_x, K, T, d_aq, d_as,
                    d_asum, d_as_tok);

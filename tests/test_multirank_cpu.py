@@ -107,3 +107,54 @@ def _max_main(rank, world, port, q):
         q.put(float(t.item()))
     dist.barrier()
     dist.destroy_process_group()
+
+
+def _row_main(rank, world, port, q):
+    """Row-parallel (K) shard, x_w4_shard mode 1: every rank multiplies its K range and the
+    partial outputs are summed (gloo all-reduce in the role of tq_comm_allreduce_sum)."""
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import torch
+    import torch.distributed as dist
+    from oracle import oracle as orc
+    import refgen
+    wl = importlib.import_module("knivesysl-xe_b200.workloads")
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        M, K, ksh = 128, 1024, 1
+        codes, scales = wl.random_packed_weight(M, K, seed=9, ksh=ksh)
+        x = refgen.shard_check_row(K)
+        Kt, Kn = K // 32, K // world
+        cs = codes.reshape(M // 16, Kt, 256)[:, rank * (Kt // world):(rank + 1) * (Kt // world)]
+        g = (Kt // world) >> ksh
+        ss = scales.reshape(M // 16, Kt >> ksh, 16)[:, rank * g:(rank + 1) * g]
+        xs = np.ascontiguousarray(x[rank * Kn:(rank + 1) * Kn])
+        q8, sc, sm = orc.quantize_act_s8(xs)
+        _, part = orc.gemv_w4a8(np.ascontiguousarray(cs).reshape(-1), np.ascontiguousarray(ss).reshape(-1),
+                                M, Kn, ksh, q8, sc, sm, fma=1)
+        t = torch.from_numpy(part.copy())
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        if rank == 0:
+            qf, scf, smf = orc.quantize_act_s8(x)       # per-K32 scales: the same codes as the shards'
+            _, full = orc.gemv_w4a8(codes, scales, M, K, ksh, qf, scf, smf, fma=1)
+            err = np.abs(t.numpy() - full).max() / max(np.abs(full).max(), 1e-6)
+            q.put(float(err))
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_row_shard_allreduce_within_tolerance():
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_row_main, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+    assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+    assert q.get(timeout=5) <= 1e-3       # the stated fp32 tolerance; not bit-exact by design
