@@ -1,8 +1,9 @@
 // gemm_stream.cu — batched W4A8 GEMM for decode batches (T = 8..64 tokens, one segment)
-// on sm_100a. Two persistent kernels: gemm_w4a8_ring_kernel (T = 8: 32 warps per SM, per-warp
-// cp.async ring in shared memory, further down) and gemm_w4a8_stream_kernel (T = 16..64 and
-// the int32 dump used by the tests), in which every warp streams packed weights from HBM
-// straight into registers, a chunk of eight k-tiles ahead of the math.
+// on sm_100a. Two persistent kernels: gemm_w4a8_ring_kernel (windows of eight tokens: 32 warps
+// per SM, per-warp cp.async ring in shared memory, further down) and gemm_w4a8_stream_kernel
+// (the shapes whose window activations do not fit beside the rings, and the int32 dump used by
+// the tests), in which every warp streams packed weights from HBM straight into registers, a
+// chunk of eight k-tiles ahead of the math.
 //
 // Replaces x_gemm_w4a8's split path (xpu/src/kernels_dpas.cpp:1379-1489) for the shapes
 // decode uses. The kernel is HBM-bound on the packed weight stream; what limits it in
@@ -409,7 +410,9 @@ gemm_w4a8_stream_kernel(const GemmArgs a, float *__restrict__ part, int *__restr
 }
 
 // ---------------------------------------------------------------------------------------
-// Ring kernel for T = 8: 32 warps per SM at 64 registers. The register queue above leaves
+// Ring kernel for T = 8, and for T = 16..64 as token windows of 8 on separate CTA columns
+// (grid.y; the packed weights are then read once per window, from L2 after the first) when a
+// window's activations fit beside the rings: 32 warps per SM at 64 registers. The register queue above leaves
 // 16 warps per SM, each of which spends most of its time waiting on its own dependency
 // chains; here every warp streams its tiles through a private two-stage shared-memory ring
 // filled with cp.async (16 bytes per lane, eight tiles and their scale lines per stage) and
@@ -470,6 +473,8 @@ gemm_w4a8_ring_kernel(const GemmArgs a, float *__restrict__ part, int *__restric
     const int Ktg = Kt >> ksh;
     const int kt_begin = Kt * split / S;
     const int cnt = Kt * (split + 1) / S - kt_begin;
+    // token window of this CTA column: tokens [tok0, tok0 + 8) of the call's Ttot
+    const int win = blockIdx.y, tok0 = win * 8, Ttot = a.T;
 
     // 64 bytes in front of the rings: the row maxima of the fused per-token quantiser
     int *s_rowmax = reinterpret_cast<int *>(smem);
@@ -546,7 +551,7 @@ gemm_w4a8_ring_kernel(const GemmArgs a, float *__restrict__ part, int *__restric
             for (int i = threadIdx.x; i < (K >> 2); i += nw * 32) {
 #pragma unroll
                 for (int t = 0; t < 8; ++t) {
-                    const float4 v = __ldg(reinterpret_cast<const float4 *>(a.x + (size_t)t * K) + i);
+                    const float4 v = __ldg(reinterpret_cast<const float4 *>(a.x + (size_t)(tok0 + t) * K) + i);
                     m[t] = fmaxf(m[t], fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
                 }
             }
@@ -567,7 +572,7 @@ gemm_w4a8_ring_kernel(const GemmArgs a, float *__restrict__ part, int *__restric
                 const int b = b0 + u * nw;
                 vv[u] = 0.0f;
                 if (b < cnt * 8)
-                    vv[u] = __ldg(a.x + (size_t)(b & 7) * K + (size_t)(kt_begin + (b >> 3)) * 32 + lane);
+                    vv[u] = __ldg(a.x + (size_t)(tok0 + (b & 7)) * K + (size_t)(kt_begin + (b >> 3)) * 32 + lane);
             }
 #pragma unroll
             for (int u = 0; u < kQU; ++u) {
@@ -604,7 +609,7 @@ gemm_w4a8_ring_kernel(const GemmArgs a, float *__restrict__ part, int *__restric
             const int kl = i >> 5;
             const int rem = i & 31;
             const uint2 bb = __ldg(reinterpret_cast<const uint2 *>(
-                a.aq + (size_t)(kt_begin + kl) * 8 * 32 + (size_t)rem * 8));
+                a.aq + ((size_t)(kt_begin + kl) * Ttot + tok0) * 32 + (size_t)rem * 8));
             uint2 o;
             o.x = __byte_perm(bb.x, bb.y, 0x6420);
             o.y = __byte_perm(bb.x, bb.y, 0x7531);
@@ -614,7 +619,7 @@ gemm_w4a8_ring_kernel(const GemmArgs a, float *__restrict__ part, int *__restric
         for (int i = threadIdx.x; i < pairs; i += nw * 32) {
             const int kl = i >> 2;
             const int rem = i & 3;
-            const size_t src = (size_t)(kt_begin + kl) * 8 + (size_t)rem * 2;
+            const size_t src = (size_t)(kt_begin + kl) * Ttot + tok0 + (size_t)rem * 2;
             const float2 as2 = __ldg(reinterpret_cast<const float2 *>(a.as + src));
             const int2 sm2 = __ldg(reinterpret_cast<const int2 *>(a.asum + src));
             *reinterpret_cast<float4 *>(act + (size_t)kl * kActTileBytes + 256 + rem * 16) =
@@ -699,17 +704,18 @@ gemm_w4a8_ring_kernel(const GemmArgs a, float *__restrict__ part, int *__restric
         unpack2(acc23, out[2], out[3]);
         if (S > 1) {
             // partial of this split -> scratch; the last split to arrive sums 0..S-1
-            float *pp = part + ((size_t)g0 * S + split) * 128 + lane;
+            const size_t slot = (size_t)win * groups_all + g0;      // (window, row-group)
+            float *pp = part + (slot * S + split) * 128 + lane;
 #pragma unroll
             for (int k = 0; k < 4; ++k) pp[k * 32] = out[k];
             __threadfence();
             __syncwarp();
             int old = 0;
-            if (lane == 0) old = atomicAdd(count + g0, 1);
+            if (lane == 0) old = atomicAdd(count + slot, 1);
             old = __shfl_sync(0xffffffffu, old, 0);
             if (old != S - 1) continue;
             __threadfence();
-            const float *base = part + (size_t)g0 * S * 128 + lane;
+            const float *base = part + slot * S * 128 + lane;
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
                 float sum = 0.0f;
@@ -717,12 +723,12 @@ gemm_w4a8_ring_kernel(const GemmArgs a, float *__restrict__ part, int *__restric
                     sum = __fadd_rn(sum, __ldcg(base + (size_t)s2 * 128 + k * 32));
                 out[k] = sum;
             }
-            if (lane == 0) count[g0] = 0;   // ready for the next launch
+            if (lane == 0) count[slot] = 0;   // ready for the next launch
         }
         const size_t row = (size_t)lg * 16 + r;
         if (!a.npeer) {
             float *y = a.y[wi];
-            const size_t tok = (size_t)2 * c;
+            const size_t tok = (size_t)tok0 + 2 * c;
             y[tok * M + row] = out[0];
             y[(tok + 1) * M + row] = out[1];
             y[tok * M + row + 8] = out[2];
@@ -737,7 +743,7 @@ gemm_w4a8_ring_kernel(const GemmArgs a, float *__restrict__ part, int *__restric
             xpose[(2 * c + 1) * 16 + r + 8] = out[3];
             __syncwarp();
             const float4 v = *reinterpret_cast<const float4 *>(xpose + lane * 4);
-            const size_t off = (size_t)(lane >> 2) * M + (size_t)lg * 16 + (lane & 3) * 4;
+            const size_t off = (size_t)(tok0 + (lane >> 2)) * M + (size_t)lg * 16 + (lane & 3) * 4;
             for (int pi = 0; pi < a.npeer; ++pi)
                 *reinterpret_cast<float4 *>(a.ypeer[pi][wi] + off) = v;
         }
@@ -862,11 +868,13 @@ int window_groups(const GemmArgs &a) {
 // The ring kernel takes T = 8 calls whose split activations fit beside the rings.
 // Launch shape of the ring kernel for a call, or false when the call is not its to take.
 struct RingPlan {
-    int grid, nw, ns;
+    int grid, nw, ns, nwin;
     size_t smem;
 };
 bool ring_plan(const GemmArgs &a, RingPlan &p) {
-    if (a.T != 8 || a.dump) return false;
+    if (a.T < 8 || a.T > 64 || (a.T % 8) || a.dump) return false;
+    if (a.x && a.T != 8) return false;        // the fused quantiser serves one window
+    p.nwin = a.T / 8;                         // token windows: CTA columns (grid.y)
     if (!g_num_sms) {
         int dev = 0;
         TQ_CHECK(cudaGetDevice(&dev));
@@ -875,9 +883,10 @@ bool ring_plan(const GemmArgs &a, RingPlan &p) {
     }
     const int Kt = a.K >> 5, S = a.max_splits;
     const int groups = a.goff[a.count];
-    if (S > g_num_sms || groups <= 0) return false;
+    const int ctas = g_num_sms / p.nwin;      // CTAs of one window
+    if (S > ctas || groups <= 0) return false;
     const long most = (long)groups * S;
-    p.grid = (int)std::max<long>(S, std::min<long>(g_num_sms - g_num_sms % S, most));
+    p.grid = (int)std::max<long>(S, std::min<long>(ctas - ctas % S, most));
     // One task per warp when the call has fewer tasks than warp slots: fewer warps, and the
     // shared memory they leave goes into deeper rings (each warp's chain is then longer
     // than the memory latency its ring covers with two stages).
@@ -901,7 +910,7 @@ bool launch_ring(const GemmArgs &a) {
     const size_t smem = plan.smem;
     bool pair = a.ksh != 0;
     for (int s2 = 0; s2 < S; ++s2) pair = pair && ((Kt * s2 / S) % 2 == 0);
-    if (S > 1) ensure_scratch((size_t)groups * S * 128, groups);
+    if (S > 1) ensure_scratch((size_t)plan.nwin * groups * S * 128, plan.nwin * groups);
     static bool attr_set = false;
     if (!attr_set) {
         auto big = [](auto kernel) {
@@ -919,7 +928,7 @@ bool launch_ring(const GemmArgs &a) {
         attr_set = true;
     }
     auto go = [&](auto kernel) {
-        launch_pdl(kernel, dim3(grid), dim3(nw * 32), smem, a, g_scratch.part, g_scratch.count);
+        launch_pdl(kernel, dim3(grid, plan.nwin), dim3(nw * 32), smem, a, g_scratch.part, g_scratch.count);
     };
     if (pair) {
         if (ns == 2) go(gemm_w4a8_ring_kernel<true, 2, kRW>);
