@@ -109,6 +109,9 @@ def run_reference(args, rank):
     if rank != 0:
         return
     from oracle import oracle as orc
+    # all host threads, also under torchrun (which exports OMP_NUM_THREADS=1 to its workers)
+    orc.set_num_threads(len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity")
+                        else (os.cpu_count() or 1))
     wl = importlib.import_module("knivesysl-xe_b200.workloads")
     host_w = [wl.make_weight_w4(N_EACH, K, seed=11 + i, group=GROUP) for i in range(2)]
     x = wl.activations_normal(T, K, seed=5, outlier_frac=0.01)
@@ -428,6 +431,8 @@ def main():
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         from oracle import oracle as orc
+        orc.set_num_threads(len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity")
+                            else (os.cpu_count() or 1))
         oq, os_, osm = orc.quantize_act_chunk(x, per_token=True)
         cpu_pass(orc, host_w, oq, os_, osm)      # warm
         passes, t0 = 0, time.perf_counter()
