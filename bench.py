@@ -252,8 +252,10 @@ def main():
         if fused:
             assert lib.tq_comm_gather_setup(bufs, flgs, world, rank) == 0
 
+    xin = [dx.ptr]       # the fp32 activations the step reads (the end-to-end loop alternates two)
+
     def stage():
-        lib.qwn_x_quantize_act_chunk_pertoken(dx.ptr, K, T, aq.ptr, as_.ptr, asum.ptr, as_tok.ptr)
+        lib.qwn_x_quantize_act_chunk_pertoken(xin[0], K, T, aq.ptr, as_.ptr, asum.ptr, as_tok.ptr)
 
     def gemm(i):
         rc = lib.qwn_x_gemm_w4a8_fanout(warr[i % args.rotate], yarr, 2, aq.ptr, as_.ptr, asum.ptr, T,
@@ -272,7 +274,7 @@ def main():
 
     def gemm_fused(i, out=None):
         if qfused:
-            rc = lib.qwn_x_gemm_w4a8_fanout_fused(warr[i % args.rotate], out or yarr, 2, dx.ptr, T, 1)
+            rc = lib.qwn_x_gemm_w4a8_fanout_fused(warr[i % args.rotate], out or yarr, 2, xin[0], T, 1)
         else:
             stage()
             rc = lib.qwn_x_gemm_w4a8_fanout(warr[i % args.rotate], out or yarr, 2, aq.ptr, as_.ptr,
@@ -281,7 +283,7 @@ def main():
 
     def step(i):
         if fused and qfused:
-            rc = lib.qwn_x_gemm_w4a8_fanout_gathered_fused(warr[i % args.rotate], 2, dx.ptr, T, 1,
+            rc = lib.qwn_x_gemm_w4a8_fanout_gathered_fused(warr[i % args.rotate], 2, xin[0], T, 1,
                                                            C.byref(half_off))
             assert rc == 0, rc
         elif fused:
@@ -380,14 +382,27 @@ def main():
     ycat2 = pkg.DevBuf(block * 4)
     yarr2 = (C.c_void_p * 2)(ycat2.ptr, ycat2.ptr + T * n_shard * 4)
     tickets = [-1, -1]
+    # Two input buffers as well: step n+1's activations come up from pinned host memory on a
+    # third stream while step n computes (one upload per step; the first is queued before the
+    # timed loop and the last step's upload is the one nothing reads).
+    dx2 = pkg.DevBuf(x.nbytes)
+    xbuf = [dx.ptr, dx2.ptr]
+    up = [lib.tq_h2d_overlapped(xbuf[0], hx, x.nbytes), -1]
+    count = [0]
+    e2e_src = [None]
 
     def e2e_step(i):
+        n = count[0]
+        count[0] = n + 1
         # N > 1: this rank's next flag tells its peers that they may overwrite the half it is
         # still reading back, so there the previous read-back must finish before the next step
         b = i & 1 if world == 1 else 0
         if tickets[b] >= 0:
             lib.tq_stream_wait_copy(tickets[b])
-        lib.tq_h2d_async(dx.ptr, hx, x.nbytes)
+        # the other input buffer was last read by step n-1, which is queued already
+        up[(n + 1) & 1] = lib.tq_h2d_overlapped(xbuf[(n + 1) & 1], hx, x.nbytes)
+        lib.tq_stream_wait_copy(up[n & 1])
+        xin[0] = xbuf[n & 1]
         if world == 1:
             gemm_fused(i, yarr2 if b else yarr)
             src = (ycat2 if b else ycat).ptr
@@ -395,7 +410,8 @@ def main():
             step(i)
             src = gathered.ptr + ((half_off.value if fused else 0) + (rank * block if weak else 0)) * 4
         tickets[b] = lib.tq_d2h_overlapped(hy[i & 1], src, out_bytes)
-        assert tickets[b] >= 0
+        e2e_src[0] = src
+        assert tickets[b] >= 0 and up[(n + 1) & 1] >= 0
 
     e_iters = max(min(args.steps, 2000), 50)
     for i in range(args.warmup):
@@ -406,6 +422,19 @@ def main():
         e2e_step(i)
     lib.tq_sync()
     e_s = time.perf_counter() - t0
+    xin[0] = dx.ptr
+    # what the host received in the last step is what the device holds; at N = 1 the step is
+    # also run again from the input buffer that was uploaded synchronously at the start
+    last = e_iters - 1
+    got = np.ctypeslib.as_array(C.cast(hy[last & 1], C.POINTER(C.c_float)), shape=(out_bytes // 4,)).copy()
+    if world == 1:
+        gemm_fused(last, yarr2 if last & 1 else yarr)
+        want = (ycat2 if last & 1 else ycat).to_numpy(np.float32, out_bytes // 4)
+    else:
+        want = np.empty(out_bytes // 4, dtype=np.float32)
+        lib.tq_d2h(want.ctypes.data, e2e_src[0], out_bytes)
+    if not np.array_equal(got.view(np.uint32), want.view(np.uint32)):
+        raise SystemExit("[bench] the end-to-end loop's last result differs from the device's")
     if dist:
         import torch
         tt = torch.tensor([e_s], dtype=torch.float64)

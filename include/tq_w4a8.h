@@ -81,6 +81,11 @@ void tq_d2d_async(void *dst, const void *src, size_t bytes);
  * failure). The library stream does not wait for it; before a later call may overwrite src,
  * pass the ticket to tq_stream_wait_copy(). tq_sync() also waits for these copies. */
 int tq_d2h_overlapped(void *dst, const void *src, size_t bytes);
+/* The same for an upload (on a third stream, so that both directions can run at once): the
+ * copy starts once everything queued so far has run, hence may overwrite a buffer that
+ * earlier calls read; pass the ticket to tq_stream_wait_copy() before the call that reads
+ * dst. Issued before step i's calls, it brings step i+1's input in while step i runs. */
+int tq_h2d_overlapped(void *dst, const void *src, size_t bytes);
 void tq_stream_wait_copy(int ticket);
 /* CUDA events on tq_stream() for device-side timing. */
 void *tq_event_create(void);

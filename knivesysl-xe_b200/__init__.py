@@ -48,7 +48,8 @@ SIGNATURES = {
     "tq_sync": (None, []), "tq_last_error": (_i, []),
     "tq_host_alloc_pinned": (_vp, [_sz]), "tq_host_free_pinned": (None, [_vp]),
     "tq_h2d_async": (None, [_vp, _vp, _sz]), "tq_d2h_async": (None, [_vp, _vp, _sz]),
-    "tq_d2h_overlapped": (C.c_int, [_vp, _vp, _sz]), "tq_stream_wait_copy": (None, [C.c_int]),
+    "tq_d2h_overlapped": (C.c_int, [_vp, _vp, _sz]),
+    "tq_h2d_overlapped": (C.c_int, [_vp, _vp, _sz]), "tq_stream_wait_copy": (None, [C.c_int]),
     "tq_d2d_async": (None, [_vp, _vp, _sz]),
     "tq_event_create": (_vp, []), "tq_event_destroy": (None, [_vp]),
     "tq_event_record": (None, [_vp]), "tq_event_elapsed_ms": (_f, [_vp, _vp]),

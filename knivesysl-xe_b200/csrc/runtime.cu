@@ -143,7 +143,8 @@ void tq_dev_fill(void *dst, int byte, size_t bytes) {
 
 namespace tq {
 constexpr int kCopyTickets = 16;
-cudaStream_t g_copy_stream = nullptr;
+cudaStream_t g_copy_stream = nullptr;                // device to host
+cudaStream_t g_up_stream = nullptr;                  // host to device
 cudaEvent_t g_copy_ready = nullptr;                 // library stream -> copy stream
 cudaEvent_t g_copy_done[kCopyTickets] = {};         // copy stream -> library stream
 unsigned g_copy_next = 0;
@@ -152,6 +153,7 @@ unsigned g_copy_next = 0;
 void tq_sync(void) {
     TQ_CHECK(cudaStreamSynchronize(tq::stream()));
     if (tq::g_copy_stream) TQ_CHECK(cudaStreamSynchronize(tq::g_copy_stream));
+    if (tq::g_up_stream) TQ_CHECK(cudaStreamSynchronize(tq::g_up_stream));
     if (tq::g_status_dev && !tq::g_sticky_error) {
         int st = 0;
         if (cudaMemcpy(&st, tq::g_status_dev, sizeof(int), cudaMemcpyDeviceToHost) == cudaSuccess &&
@@ -183,25 +185,38 @@ void tq_d2h_async(void *dst, const void *src, size_t bytes) {
     TQ_CHECK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, tq::stream()));
 }
 
-// ---- read-back that overlaps the next call ------------------------------------------
-// A second stream carries device-to-host copies: the copy waits for what the library stream
-// has queued so far, and the library stream only waits for a copy when the caller says so
-// (before it lets a kernel overwrite the copied buffer), through a ticket.
+// ---- copies that overlap the calls around them ---------------------------------------
+// Two more streams carry copies, one per direction so that both copy engines can run at
+// once: a copy waits for what the library stream has queued so far, and the library stream
+// only waits for a copy when the caller says so, through a ticket (before it lets a kernel
+// overwrite a buffer that is being read back, or read a buffer that is being uploaded).
+
+namespace tq {
+int overlapped_copy(void *dst, const void *src, size_t bytes, bool up) {
+    cudaStream_t main = stream();
+    if (!g_copy_stream) {
+        TQ_CHECK(cudaStreamCreateWithFlags(&g_copy_stream, cudaStreamNonBlocking));
+        TQ_CHECK(cudaStreamCreateWithFlags(&g_up_stream, cudaStreamNonBlocking));
+        TQ_CHECK(cudaEventCreateWithFlags(&g_copy_ready, cudaEventDisableTiming));
+        for (auto &e : g_copy_done) TQ_CHECK(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    }
+    if (!g_copy_stream || !g_up_stream) return -1;
+    cudaStream_t cs = up ? g_up_stream : g_copy_stream;
+    const int ticket = (int)(g_copy_next++ % kCopyTickets);
+    TQ_CHECK(cudaEventRecord(g_copy_ready, main));
+    TQ_CHECK(cudaStreamWaitEvent(cs, g_copy_ready, 0));
+    TQ_CHECK(cudaMemcpyAsync(dst, src, bytes, up ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToHost, cs));
+    TQ_CHECK(cudaEventRecord(g_copy_done[ticket], cs));
+    return ticket;
+}
+}  // namespace tq
 
 int tq_d2h_overlapped(void *dst, const void *src, size_t bytes) {
-    cudaStream_t main = tq::stream();
-    if (!tq::g_copy_stream) {
-        TQ_CHECK(cudaStreamCreateWithFlags(&tq::g_copy_stream, cudaStreamNonBlocking));
-        TQ_CHECK(cudaEventCreateWithFlags(&tq::g_copy_ready, cudaEventDisableTiming));
-        for (auto &e : tq::g_copy_done) TQ_CHECK(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
-    }
-    if (!tq::g_copy_stream) return -1;
-    const int ticket = (int)(tq::g_copy_next++ % tq::kCopyTickets);
-    TQ_CHECK(cudaEventRecord(tq::g_copy_ready, main));
-    TQ_CHECK(cudaStreamWaitEvent(tq::g_copy_stream, tq::g_copy_ready, 0));
-    TQ_CHECK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, tq::g_copy_stream));
-    TQ_CHECK(cudaEventRecord(tq::g_copy_done[ticket], tq::g_copy_stream));
-    return ticket;
+    return tq::overlapped_copy(dst, src, bytes, false);
+}
+
+int tq_h2d_overlapped(void *dst, const void *src, size_t bytes) {
+    return tq::overlapped_copy(dst, src, bytes, true);
 }
 
 void tq_stream_wait_copy(int ticket) {

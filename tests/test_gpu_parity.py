@@ -623,6 +623,36 @@ def test_overlapped_readback(lib, pkg):
             lib.tq_host_free_pinned(h)
 
 
+@pytest.mark.gpu
+def test_overlapped_upload(lib, pkg):
+    """tq_h2d_overlapped: the upload starts behind what was queued before it (so it may
+    replace a buffer that an earlier call reads), a later call that reads the buffer is
+    ordered behind it by tq_stream_wait_copy, and it shares the tickets of the read-back."""
+    n = 1 << 20
+    a = np.arange(n, dtype=np.int32)
+    b = a[::-1].copy()
+    d = dev(pkg, a)
+    e = pkg.DevBuf(n * 4)
+    hb = lib.tq_host_alloc_pinned(n * 4)
+    ho = lib.tq_host_alloc_pinned(n * 4)
+    try:
+        C.memmove(hb, b.ctypes.data, n * 4)
+        lib.tq_d2d_async(e.ptr, d.ptr, n * 4)          # reads d before the upload replaces it
+        t0 = lib.tq_h2d_overlapped(d.ptr, hb, n * 4)
+        assert 0 <= t0 < 16
+        lib.tq_stream_wait_copy(t0)
+        t1 = lib.tq_d2h_overlapped(ho, d.ptr, n * 4)   # queued behind the wait: sees b
+        assert t1 == (t0 + 1) % 16
+        lib.tq_sync()
+        got = np.ctypeslib.as_array(C.cast(ho, C.POINTER(C.c_int32)), shape=(n,))
+        assert np.array_equal(got, b)
+        assert np.array_equal(e.to_numpy(np.int32), a)
+        assert lib.tq_last_error() == 0
+    finally:
+        lib.tq_host_free_pinned(hb)
+        lib.tq_host_free_pinned(ho)
+
+
 # ---------------------------------------------------------------- W8A8 tier
 def _w8_weight(pkg, orc, M, K, seed):
     """A W8A8 record repacked on the device from a random E2M3 payload, plus the oracle's
