@@ -394,9 +394,12 @@ def main():
     def e2e_step(i):
         n = count[0]
         count[0] = n + 1
-        # N > 1: this rank's next flag tells its peers that they may overwrite the half it is
-        # still reading back, so there the previous read-back must finish before the next step
-        b = i & 1 if world == 1 else 0
+        # N > 1, strong: this rank's next flag tells its peers that they may overwrite the half
+        # it is still reading back, so there the previous read-back must finish before the next
+        # step. Weak with the fused gather: a rank reads back its own slice only, which no peer
+        # writes, so as at N = 1 the read-back of step n must only be over before step n+2
+        # writes the same half (NCCL's gather has one buffer, rewritten whole every step).
+        b = n & 1 if (world == 1 or (weak and fused)) else 0
         if tickets[b] >= 0:
             lib.tq_stream_wait_copy(tickets[b])
         # the other input buffer was last read by step n-1, which is queued already
@@ -409,8 +412,8 @@ def main():
         else:
             step(i)
             src = gathered.ptr + ((half_off.value if fused else 0) + (rank * block if weak else 0)) * 4
-        tickets[b] = lib.tq_d2h_overlapped(hy[i & 1], src, out_bytes)
-        e2e_src[0] = src
+        tickets[b] = lib.tq_d2h_overlapped(hy[n & 1], src, out_bytes)
+        e2e_src[0] = (src, i, n & 1)
         assert tickets[b] >= 0 and up[(n + 1) & 1] >= 0
 
     e_iters = max(min(args.steps, 2000), 50)
@@ -425,14 +428,14 @@ def main():
     xin[0] = dx.ptr
     # what the host received in the last step is what the device holds; at N = 1 the step is
     # also run again from the input buffer that was uploaded synchronously at the start
-    last = e_iters - 1
-    got = np.ctypeslib.as_array(C.cast(hy[last & 1], C.POINTER(C.c_float)), shape=(out_bytes // 4,)).copy()
+    src, last, lb = e2e_src[0]
+    got = np.ctypeslib.as_array(C.cast(hy[lb], C.POINTER(C.c_float)), shape=(out_bytes // 4,)).copy()
     if world == 1:
-        gemm_fused(last, yarr2 if last & 1 else yarr)
-        want = (ycat2 if last & 1 else ycat).to_numpy(np.float32, out_bytes // 4)
+        gemm_fused(last, yarr2 if lb else yarr)
+        want = (ycat2 if lb else ycat).to_numpy(np.float32, out_bytes // 4)
     else:
         want = np.empty(out_bytes // 4, dtype=np.float32)
-        lib.tq_d2h(want.ctypes.data, e2e_src[0], out_bytes)
+        lib.tq_d2h(want.ctypes.data, src, out_bytes)
     e2e_diff = int(np.count_nonzero(got.view(np.uint32) != want.view(np.uint32)))
     if e2e_diff:
         print(f"[bench] rank {rank}: the end-to-end loop's last result differs from the device's in "
