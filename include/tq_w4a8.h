@@ -58,7 +58,10 @@ typedef struct {
 
 /* ---- device runtime: replaces tq_q()/tq_dev_* of xpu/src/decode.cpp:86-130 and
  * xpu/src/tq_common.hpp:200-216. Allocation failure aborts with a message, like
- * the reference. tq_stream() returns the cudaStream_t every call is ordered on. */
+ * the reference. tq_stream() returns the cudaStream_t every call is ordered on.
+ * tq_dev_alloc, tq_dev_free, tq_h2d, tq_d2h and tq_dev_zero have C++ linkage in the
+ * reference (tq_common.hpp:212-216); the library exports them under those mangled names
+ * too (csrc/cxx_linkage.cpp), so objects compiled against the reference header link. */
 int tq_set_device(int device);            /* one process per GPU: pick it once */
 int tq_device(void);
 void *tq_stream(void);
@@ -71,6 +74,20 @@ void tq_dev_fill(void *dst, int byte, size_t bytes);
 void tq_sync(void);                        /* wait for the stream; returns after errors are read */
 int tq_last_error(void);                   /* sticky: cudaError of the last failed call, or a
                                               device-side wait status (>= 10000); 0 = clean */
+/* Every wait inside a kernel (the mbarrier waits of the tcgen05 GEMM, the flag wait of the
+ * fused all-gather) gives up after a wall-clock limit, records a status word and lets the
+ * kernel return normally; tq_sync() then turns the status into tq_last_error() = 10000 +
+ * code (10021-10023: tcgen05 pipeline, 10031: a rank's gather flag never arrived). Data
+ * produced by a call whose wait gave up is incomplete: check tq_last_error() after
+ * tq_sync() before trusting gathered outputs. The limit is two seconds unless changed here
+ * (a rank can legitimately be further behind during a long prefill). tq_clear_error waits
+ * for the stream, then clears the sticky error and the device status word. No counterpart
+ * in the reference, whose waits are host-side joins (xpu/src/decode.cpp:133-154). */
+void tq_set_wait_limit_ms(int ms);
+void tq_clear_error(void);
+/* Number of tq_dev_alloc calls made so far in this process, by callers and by the library
+ * itself (scratch growth): lets a caller verify that a steady-state loop allocates nothing. */
+unsigned long long tq_dev_alloc_count(void);
 void *tq_host_alloc_pinned(size_t bytes);
 void tq_host_free_pinned(void *p);
 void tq_h2d_async(void *dst, const void *src, size_t bytes);
@@ -220,6 +237,13 @@ int qwn_x_gemm_w4a8_fanout_fused(const tq_qmma_weight_t *const *ws, float *const
  * per-token vector d_as_tok[T]. */
 void qwn_x_quantize_act_chunk_pertoken(const float *d_x, int K, int T, int8_t *d_aq, float *d_as,
                                        int32_t *d_asum, float *d_as_tok);
+/* The decode stagings with a per-token scale: x_prepare_gemv_act_s8 and x_silu_mul_quant with
+ * scale = absmax(row) / 127 for every K32 block (the "int8 per token" activation of the
+ * benchmark configurations; the reference quantises per (token, K32) block,
+ * xpu/src/kernels_dpas.cpp:185-206). The prepared scratch then serves x_gemv_w4a8_prepared,
+ * x_gemv_w4a8_fanout and x_gemv_qmma_prepared unchanged. */
+void qwn_x_prepare_gemv_act_s8_pertoken(const float *d_x, int K);
+void qwn_x_silu_mul_quant_pertoken(float *d_out, const float *d_gate, const float *d_up, int K);
 /* GEMM for per-token scales: the int32 dot runs over a whole weight-scale group before
  * the fp32 promote; y = (sum_g (d_g - z*asum_g) * ws_g) * as_tok. out_bf16 != 0 stores
  * bfloat16 instead of fp32. Returns like x_gemm_w4a8. */
@@ -356,6 +380,8 @@ void x_quantize_act_chunk_pertoken(const float *d_x, int K, int T, int8_t *d_aq,
                                    int32_t *d_asum, float *d_as_tok);
 int x_gemm_w4a8_pertoken(const tq_qmma_weight_t *w, const int8_t *d_aq, const float *d_as_tok,
                          const int32_t *d_asum, void *d_y, int T, int out_bf16 = 0);
+void x_prepare_gemv_act_s8_pertoken(const float *d_x, int K);
+void x_silu_mul_quant_pertoken(float *d_out, const float *d_gate, const float *d_up, int K);
 int x_w8_repack_weight(tq_qmma_weight_t *w);
 int x_gemv_w8a8(const tq_qmma_weight_t *w, const float *d_x, float *d_y);
 int x_gemv_w8a8_add(const tq_qmma_weight_t *w, const float *d_x, const float *d_residual, float *d_y);

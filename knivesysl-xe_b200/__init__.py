@@ -46,6 +46,8 @@ SIGNATURES = {
     "tq_h2d": (None, [_vp, _vp, _sz]), "tq_d2h": (None, [_vp, _vp, _sz]),
     "tq_dev_zero": (None, [_vp, _sz]), "tq_dev_fill": (None, [_vp, _i, _sz]),
     "tq_sync": (None, []), "tq_last_error": (_i, []),
+    "tq_set_wait_limit_ms": (None, [_i]), "tq_clear_error": (None, []),
+    "tq_dev_alloc_count": (C.c_ulonglong, []),
     "tq_host_alloc_pinned": (_vp, [_sz]), "tq_host_free_pinned": (None, [_vp]),
     "tq_h2d_async": (None, [_vp, _vp, _sz]), "tq_d2h_async": (None, [_vp, _vp, _sz]),
     "tq_d2h_overlapped": (C.c_int, [_vp, _vp, _sz]),
@@ -60,6 +62,8 @@ SIGNATURES = {
     "qwn_x_prepare_gemv_act_s8": (None, [_vp, _i]),
     "qwn_x_silu_mul_quant": (None, [_vp, _vp, _vp, _i]),
     "qwn_x_rmsnorm_quant": (None, [_vp, _vp, _vp, _i, _f]),
+    "qwn_x_prepare_gemv_act_s8_pertoken": (None, [_vp, _i]),
+    "qwn_x_silu_mul_quant_pertoken": (None, [_vp, _vp, _vp, _i]),
     "qwn_x_gemv_w4a8": (_i, [_WP, _vp, _vp]),
     "qwn_x_gemv_w4a8_add": (_i, [_WP, _vp, _vp, _vp]),
     "qwn_x_gemv_w4a8_prepared": (_i, [_WP, _vp, _vp]),

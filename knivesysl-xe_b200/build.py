@@ -14,7 +14,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libforward_qwen_xpu.so")
 
 SOURCES = ["runtime.cu", "quant.cu", "repack.cu", "gemv.cu", "gemm_mma.cu", "gemm_stream.cu", "gemm_tc.cu",
-           "dispatch.cu", "checks.cu", "comm.cu", "gemv_static.cu", "w8a8.cu"]
+           "dispatch.cu", "checks.cu", "comm.cu", "gemv_static.cu", "w8a8.cu", "cxx_linkage.cpp"]
 
 NVCC_FLAGS = [
     "-O3", "-std=c++17", "-lineinfo",
@@ -45,7 +45,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     procs = []
     objs = []
     for src in SOURCES:
-        obj = os.path.join(objdir, src.replace(".cu", ".o"))
+        obj = os.path.join(objdir, os.path.splitext(src)[0] + ".o")
         objs.append(obj)
         cmd = [nvcc, *NVCC_FLAGS, "-c", os.path.join(CSRC, src), "-o", obj]
         if verbose:

@@ -2,7 +2,8 @@
 // ranks' output slices over NVLink. One process per GPU; NCCL is loaded at run time
 // (dlopen) so a single-GPU user needs no NCCL at all. The reference's only collective
 // is a 2-rank peer-copy all-reduce (xpu/src/decode.cpp:133-154); a column shard needs
-// an all-gather instead, and no K-split all-reduce is built.
+// an all-gather instead; the row-parallel (K) shard's partial sums are added with
+// tq_comm_allreduce_sum.
 #include "common.cuh"
 
 #include <dlfcn.h>
@@ -33,14 +34,14 @@ tq::GatherState g_gather;
 // rank's slice on every rank (griddepcontrol.wait returns once that kernel has completed and
 // its stores, the peer stores included, have been performed): lane p stores the step number
 // into this rank's flag word on rank p behind a system-scope fence, then waits until rank p's
-// flag word here has reached the step (bounded: two seconds of wall clock, then status 31 and
-// a normal return). Whatever follows on the stream therefore finds every rank's slice in
+// flag word here has reached the step (bounded: limit_ns of wall clock, two seconds unless
+// tq_set_wait_limit_ms changed it, then status 31 and a normal return). Whatever follows on the stream therefore finds every rank's slice in
 // the gathered buffer.
 struct PeerFlags {
     int *p[8];
 };
 __global__ void gather_publish_wait_kernel(PeerFlags f, const int *mine, int world, int step,
-                                           int *status) {
+                                           int *status, unsigned long long limit_ns) {
     tq::pdl_trigger();
     tq::pdl_wait();
     const int p = threadIdx.x;
@@ -57,7 +58,7 @@ __global__ void gather_publish_wait_kernel(PeerFlags f, const int *mine, int wor
             unsigned long long now;
             asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
             if (t0 == 0) t0 = now;
-            else if (now - t0 > 2000000000ull) break;
+            else if (now - t0 > limit_ns) break;
         }
     }
     atomicCAS(status, 0, 31);
@@ -105,7 +106,7 @@ void launch_gather_publish(int step) {
     PeerFlags f{};
     for (int p = 0; p < g.world; ++p) f.p[p] = g.flag[p] + g.rank;
     launch_pdl(gather_publish_wait_kernel, dim3(1), dim3(32), 0, f, (const int *)g.flag[g.rank],
-               g.world, step, device_status_word());
+               g.world, step, device_status_word(), wait_limit_ns());
     note_error(cudaGetLastError(), "gather_publish_wait_kernel");
 }
 }  // namespace tq
@@ -200,7 +201,12 @@ void tq_comm_ipc_close(void *p) {
 }
 
 // bufs[p], flags[p]: rank p's gathered buffer and flag array as addressable from this
-// process (its own allocation for p == rank). world <= 8.
+// process (its own allocation for p == rank). world <= 8. Steps count from zero again after
+// every setup, so this rank's own flag words are cleared here (blocking); the caller must
+// put a host barrier between the setup calls of all ranks and the first gathered call, so
+// that no rank publishes step 1 into an array its owner has not cleared yet. The size of
+// the buffers (2 * world * block floats for the largest gathered call) cannot be checked
+// here and is the caller's to guarantee.
 int tq_comm_gather_setup(void *const *bufs, void *const *flags, int world, int rank) {
     if (!bufs || !flags || world < 1 || world > 8 || rank < 0 || rank >= world) return -1;
     tq::GatherState &g = g_gather;
@@ -212,6 +218,7 @@ int tq_comm_gather_setup(void *const *bufs, void *const *flags, int world, int r
     g.world = world;
     g.rank = rank;
     g.step = 0;
+    tq_dev_zero(g.flag[rank], (size_t)world * sizeof(int));
     return 0;
 }
 

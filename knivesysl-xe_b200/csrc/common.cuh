@@ -39,8 +39,10 @@ struct ActScratch {
 ActScratch &act_scratch();
 void ensure_act_scratch(int K);
 
-// Device status word for bounded waits inside kernels (0 = clean).
+// Device status word for bounded waits inside kernels (0 = clean), and the wall-clock limit
+// of those waits in nanoseconds (tq_set_wait_limit_ms).
 int *device_status_word();
+unsigned long long wait_limit_ns();
 
 // State of the fused all-gather (comm.cu): buffers and flag words of every rank as mapped
 // into this process, set up by tq_comm_gather_setup.
@@ -63,6 +65,9 @@ int choose_gemm_splits(int rgroups, int tgroups, int ktiles);
 // quant.cu
 void launch_quant_s8(const float *d_x, const float *d_up, float *d_hidden, int K, int8_t *d_q,
                      int8_t *d_qp, float *d_scale, int32_t *d_sum16, int32_t *d_sum32, bool silu);
+void launch_quant_s8_pertoken(const float *d_x, const float *d_up, float *d_hidden, int K,
+                              int8_t *d_q, int8_t *d_qp, float *d_scale, int32_t *d_sum16,
+                              int32_t *d_sum32, bool silu);
 void launch_rmsnorm_quant(float *d_out, const float *d_in, const uint16_t *d_w, int H, float eps,
                           float *d_partial, int8_t *d_q, int8_t *d_qp, float *d_scale,
                           int32_t *d_sum16, int32_t *d_sum32);

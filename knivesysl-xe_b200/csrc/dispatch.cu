@@ -14,29 +14,31 @@ int choose_gemv_splits(int groups) {
     return groups >= 4096 ? 1 : 8;
 }
 
-// xpu/src/kernels_dpas.cpp:1226-1250, TQ_XPU_GEMM_SPLITS read once like the reference.
-int choose_gemm_splits(int rgroups, int tgroups, int ktiles) {
-    static const int forced = [] {
+// Split count of a batched GEMM (the rule of xpu/src/kernels_dpas.cpp:1226-1250, which fixes
+// the order an output's partial sums are added in): the smallest power of two that brings
+// row-groups x token-groups x splits to 2048 tasks, never more than 16 nor than the number
+// of k-tiles. TQ_XPU_GEMM_SPLITS = 1, 2, 4, 8 or 16 overrides the count (same cap).
+namespace {
+int forced_gemm_splits() {
+    static int cached = -1;
+    if (cached < 0) {
         const char *e = getenv("TQ_XPU_GEMM_SPLITS");
-        if (!e || !*e) return 0;
-        const int v = atoi(e);
-        return (v == 1 || v == 2 || v == 4 || v == 8 || v == 16) ? v : 0;
-    }();
+        const int v = (e && *e) ? atoi(e) : 0;
+        cached = (v > 0 && v <= 16 && (v & (v - 1)) == 0) ? v : 0;
+    }
+    return cached;
+}
+}  // namespace
+
+int choose_gemm_splits(int rgroups, int tgroups, int ktiles) {
     const long tasks = (long)rgroups * tgroups;
     if (tasks <= 0) return 1;
-    if (forced) {
-        int s = forced;
-        while (s > 1 && s > ktiles) s >>= 1;
-        return s;
-    }
-    const long want = 128L * 16;
-    if (tasks >= want) return 1;
-    for (int s = 2; s <= 16; s <<= 1) {
-        if (s > ktiles) break;
-        if (tasks * s >= want) return s;
-    }
-    int s = 16;
-    while (s > 1 && s > ktiles) s >>= 1;
+    int cap = 1;                                   // largest power of two <= min(16, ktiles)
+    while (cap < 16 && cap * 2 <= ktiles) cap *= 2;
+    if (const int f = forced_gemm_splits()) return std::min(f, cap);
+    const long kEnough = 2048;                     // 128 work-groups of 16 sub-groups
+    int s = 1;
+    while (s < cap && tasks * s < kEnough) s *= 2;
     return s;
 }
 
@@ -180,6 +182,23 @@ void x_silu_mul_quant(float *d_out, const float *d_gate, const float *d_up, int 
     ensure_act_scratch(K);
     ActScratch &s = act_scratch();
     launch_quant_s8(d_gate, d_up, d_out, K, s.q, s.qp, s.scale, s.sum16, s.sum32, true);
+    s.prepared_K = K;
+}
+
+// Per-token forms of the two decode stagings: one scale (absmax / 127) for the whole row.
+void x_prepare_gemv_act_s8_pertoken(const float *d_x, int K) {
+    if (!d_x || K <= 0 || (K % 32) != 0) return;
+    ensure_act_scratch(K);
+    ActScratch &s = act_scratch();
+    launch_quant_s8_pertoken(d_x, nullptr, nullptr, K, s.q, s.qp, s.scale, s.sum16, s.sum32, false);
+    s.prepared_K = K;
+}
+
+void x_silu_mul_quant_pertoken(float *d_out, const float *d_gate, const float *d_up, int K) {
+    if (!d_out || !d_gate || !d_up || K <= 0 || (K % 32) != 0) return;
+    ensure_act_scratch(K);
+    ActScratch &s = act_scratch();
+    launch_quant_s8_pertoken(d_gate, d_up, d_out, K, s.q, s.qp, s.scale, s.sum16, s.sum32, true);
     s.prepared_K = K;
 }
 
@@ -629,40 +648,47 @@ int x_w4_shard(tq_qmma_weight_t *dst, const tq_qmma_weight_t *src, int rank, int
         return 0;
     }
     if (mode != 0) return -9;
-    int gs[8];
-    const int ng = (groups && ngroups > 0) ? ngroups : 1;
-    if (ng > 8) return -4;
-    if (groups && ngroups > 0) {
-        int total = 0;
-        for (int i = 0; i < ng; ++i) { gs[i] = groups[i]; total += gs[i]; }
-        if (total != src->M) return -5;
-    } else {
-        gs[0] = src->M;
+    // Column shard (the slicing rule of kernels_dpas.cpp:463-499): the rows are `ngroups`
+    // consecutive blocks (one when no list is given, e.g. [gate | up]); each block is cut
+    // into tp equal runs of whole 16-row groups and rank r keeps its run of every block, in
+    // block order. A row-group's codes and scale lines are contiguous, so a run is one copy
+    // of each array.
+    const int nblocks = (groups && ngroups > 0) ? ngroups : 1;
+    if (nblocks > 8) return -4;
+    struct Run { size_t first_group, n_groups; } runs[8];
+    {
+        long covered = 0;
+        for (int b = 0; b < nblocks; ++b) covered += groups && ngroups > 0 ? groups[b] : src->M;
+        if (covered != src->M) return -5;
+        size_t first = 0;
+        for (int b = 0; b < nblocks; ++b) {
+            const int rows = groups && ngroups > 0 ? groups[b] : src->M;
+            if (rows % (16 * tp)) return -6;
+            const size_t per_rank = (size_t)(rows / 16) / (size_t)tp;
+            runs[b] = Run{first + per_rank * (size_t)rank, per_rank};
+            first += (size_t)(rows / 16);
+        }
     }
-    for (int i = 0; i < ng; ++i)
-        if (gs[i] % (16 * tp)) return -6;
     *dst = *src;
     dst->d_A = nullptr;
     dst->d_block_scale_inv = nullptr;
-    const int Mnew = src->M / tp;
-    dst->M = Mnew;
-    dst->Mt = Mnew / 16;
-    dst->d_s4 = static_cast<uint8_t *>(tq_dev_alloc((size_t)dst->Mt * Kt * 256u, "shard.codes"));
-    dst->d_s4_scale =
-        static_cast<uint16_t *>(tq_dev_alloc((size_t)Mnew * sg * 2u, "shard.scales"));
-    size_t src_g = 0, dst_g = 0;
-    for (int i = 0; i < ng; ++i) {
-        const size_t gtot = (size_t)gs[i] / 16;
-        const size_t gper = gtot / (size_t)tp;
-        const size_t from = src_g + gper * (size_t)rank;
-        tq_d2d_async(dst->d_s4 + dst_g * Kt * 256u, src->d_s4 + from * Kt * 256u,
-                     gper * Kt * 256u);
-        tq_d2d_async(dst->d_s4_scale + dst_g * (size_t)sg * 16u,
-                     src->d_s4_scale + from * (size_t)sg * 16u,
-                     gper * (size_t)sg * 16u * sizeof(uint16_t));
-        src_g += gtot;
-        dst_g += gper;
+    dst->M = src->M / tp;
+    dst->Mt = dst->M / 16;
+    const size_t code_row = (size_t)Kt * 256u;                    // bytes of codes per row-group
+    const size_t scale_row = (size_t)sg * 16u * sizeof(uint16_t); // bytes of scale lines
+    uint8_t *codes = static_cast<uint8_t *>(tq_dev_alloc((size_t)dst->Mt * code_row, "shard.codes"));
+    uint8_t *scl = static_cast<uint8_t *>(tq_dev_alloc((size_t)dst->Mt * scale_row, "shard.scales"));
+    size_t at = 0;                                                // row-groups placed so far
+    for (int b = 0; b < nblocks; ++b) {
+        const Run &r = runs[b];
+        tq_d2d_async(codes + at * code_row, src->d_s4 + r.first_group * code_row, r.n_groups * code_row);
+        tq_d2d_async(scl + at * scale_row,
+                     reinterpret_cast<const uint8_t *>(src->d_s4_scale) + r.first_group * scale_row,
+                     r.n_groups * scale_row);
+        at += r.n_groups;
     }
+    dst->d_s4 = codes;
+    dst->d_s4_scale = reinterpret_cast<uint16_t *>(scl);
     tq_sync();
     return 0;
 }
@@ -689,6 +715,12 @@ void qwn_x_quantize_act_s8(const float *d_x, int K, int8_t *d_q, float *d_scale,
 void qwn_x_prepare_gemv_act_s8(const float *d_x, int K) { x_prepare_gemv_act_s8(d_x, K); }
 void qwn_x_silu_mul_quant(float *d_out, const float *d_gate, const float *d_up, int K) {
     x_silu_mul_quant(d_out, d_gate, d_up, K);
+}
+void qwn_x_prepare_gemv_act_s8_pertoken(const float *d_x, int K) {
+    x_prepare_gemv_act_s8_pertoken(d_x, K);
+}
+void qwn_x_silu_mul_quant_pertoken(float *d_out, const float *d_gate, const float *d_up, int K) {
+    x_silu_mul_quant_pertoken(d_out, d_gate, d_up, K);
 }
 void qwn_x_rmsnorm_quant(float *d_out, const float *d_in, const uint16_t *d_w, int H, float eps) {
     x_rmsnorm_quant(d_out, d_in, d_w, H, eps);

@@ -158,6 +158,7 @@ struct TcParams {
     void *y;
     const float *as_tok;     // per-token scales (PERTOK kernels)
     int *status;
+    unsigned long long wait_ns;   // limit of every mbarrier wait
     int M, Kt, ksh, T, Tpad, out_bf16;
 };
 
@@ -337,7 +338,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_w4a8_tc_kernel(const TcParam
                 const f32x2 ws2 = pack2(ws, ws);
                 const float nzf = (float)(-(zp + 8));
                 const f32x2 nz2 = pack2(nzf, nzf);
-                bool ok = !*(volatile int *)&dead_s && mbar_wait_bounded(acc0 + b * 8, ph, p.status, kWaitEpi);
+                bool ok = !*(volatile int *)&dead_s && mbar_wait_bounded(acc0 + b * 8, ph, p.status, kWaitEpi, p.wait_ns);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) {
                     dead_s = 1;
@@ -447,7 +448,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_w4a8_tc_kernel(const TcParam
                         if (kt >= Kt || *(volatile int *)&dead_s) break;
                         const int sl = it % kNS;
                         const uint32_t ph = ((uint32_t)(it / kNS) & 1u) ^ 1u;   // first pass is free
-                        bool ok = mbar_wait_bounded(empty0 + sl * 8, ph, p.status, kWaitProd);
+                        bool ok = mbar_wait_bounded(empty0 + sl * 8, ph, p.status, kWaitProd, p.wait_ns);
                         ok = __all_sync(0xffffffffu, ok);
                         if (!ok) {
                             dead_s = 1;
@@ -492,12 +493,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_w4a8_tc_kernel(const TcParam
                 const int ig = it / GW;
                 const int b = ig % kNB, sl = it % kNS;
                 bool ok = !*(volatile int *)&dead_s &&
-                          mbar_wait_bounded(full0 + sl * 8, (uint32_t)(it / kNS) & 1u, p.status, kWaitMma);
+                          mbar_wait_bounded(full0 + sl * 8, (uint32_t)(it / kNS) & 1u, p.status, kWaitMma, p.wait_ns);
                 // ... and, for the first k-tile of a group, the accumulator buffer has been
                 // read out and re-armed
                 if (it % GW == 0)
                     ok = ok && mbar_wait_bounded(accempty0 + b * 8, ((uint32_t)(ig / kNB) & 1u) ^ 1u,
-                                                 p.status, kWaitMma);
+                                                 p.status, kWaitMma, p.wait_ns);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) {
                     dead_s = 1;
@@ -572,6 +573,7 @@ int launch_gemm_tc(const GemmTcArgs &a) {
     TcParams p{};
     p.codes = a.codes; p.scales = a.scales; p.img = g_tc.img; p.y = a.y;
     p.status = device_status_word();
+    p.wait_ns = wait_limit_ns();
     p.M = a.M; p.Kt = Kt; p.ksh = a.ksh; p.T = a.T; p.Tpad = Tpad; p.out_bf16 = a.out_bf16;
     const int ntiles = (a.M / kTM) * (Tpad / kTN);
     const int grid = std::min(g_tc_sms, ntiles);

@@ -13,6 +13,8 @@ int g_device = -1;
 int g_sticky_error = 0;
 ActScratch g_act;
 int *g_status_dev = nullptr;
+unsigned long long g_alloc_calls = 0;
+unsigned long long g_wait_limit_ns = 2000000000ull;   // bounded device-side waits: 2 s
 
 void init_device_once() {
     if (g_stream) return;
@@ -53,10 +55,13 @@ void note_error(cudaError_t e, const char *where) {
 
 ActScratch &act_scratch() { return g_act; }
 
+unsigned long long wait_limit_ns() { return g_wait_limit_ns; }
+
 void ensure_act_scratch(int K) {
     ActScratch &s = g_act;
     if (s.cap >= K) return;
-    // Stream order makes freeing safe: cudaFree waits for outstanding work.
+    // tq_dev_free waits for the library stream before it frees, so nothing queued can
+    // still read the old scratch.
     if (s.q) tq_dev_free(s.q);
     if (s.qp) tq_dev_free(s.qp);
     if (s.scale) tq_dev_free(s.scale);
@@ -104,6 +109,7 @@ void *tq_stream(void) { return (void *)tq::stream(); }
 
 void *tq_dev_alloc(size_t bytes, const char *what) {
     tq::init_device_once();
+    ++tq::g_alloc_calls;
     void *p = nullptr;
     cudaError_t e = cudaMalloc(&p, bytes ? bytes : 1);
     if (e != cudaSuccess || !p) {
@@ -165,6 +171,20 @@ void tq_sync(void) {
 }
 
 int tq_last_error(void) { return tq::g_sticky_error; }
+
+void tq_clear_error(void) {
+    if (tq::g_status_dev) {
+        TQ_CHECK(cudaStreamSynchronize(tq::stream()));
+        TQ_CHECK(cudaMemset(tq::g_status_dev, 0, sizeof(int)));
+    }
+    tq::g_sticky_error = 0;
+}
+
+void tq_set_wait_limit_ms(int ms) {
+    tq::g_wait_limit_ns = (unsigned long long)(ms < 1 ? 1 : ms) * 1000000ull;
+}
+
+unsigned long long tq_dev_alloc_count(void) { return tq::g_alloc_calls; }
 
 void *tq_host_alloc_pinned(size_t bytes) {
     tq::init_device_once();

@@ -1,5 +1,5 @@
 // stream.cuh — device helpers shared by the streaming GEMV/GEMM kernels: mbarrier,
-// 1-D bulk (TMA) copies into shared memory, ldmatrix, the s8 tensor-core MMA and packed
+// cp.async copies into shared memory, ldmatrix, the s8 tensor-core MMA and packed
 // two-lane fp32 arithmetic (sm_100a).
 #pragma once
 
@@ -44,17 +44,17 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
     return ok;
 }
 
-// Bounded wait: polls until the phase completes or two seconds of wall clock have passed
-// (%globaltimer), then records `code` in *status (first failure wins) and returns false.
-// The result is made warp-uniform by the caller.
+// Bounded wait: polls until the phase completes or limit_ns of wall clock have passed
+// (%globaltimer; the host passes tq::wait_limit_ns(), two seconds unless
+// tq_set_wait_limit_ms changed it), then records `code` in *status (first failure wins) and
+// returns false. The result is made warp-uniform by the caller.
 __device__ __forceinline__ uint64_t global_timer_ns() {
     uint64_t t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
-constexpr uint64_t kWaitLimitNs = 2000000000ull;
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, int *status,
-                                                  int code) {
+                                                  int code, uint64_t limit_ns) {
     if (mbar_try_wait(bar, parity)) return true;
     // Slow path: back off between polls so that waiting warps leave the issue slots to the
     // warps doing the work, and look at the clock only every 1024 polls.
@@ -65,7 +65,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
         if ((polls & 1023u) == 0) {
             const uint64_t now = global_timer_ns();
             if (t0 == 0) t0 = now;
-            else if (now - t0 > kWaitLimitNs) break;
+            else if (now - t0 > limit_ns) break;
         }
     }
     atomicCAS(status, 0, code);
@@ -76,22 +76,6 @@ __device__ __forceinline__ uint64_t l2_policy_evict_first() {
     uint64_t pol;
     asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
     return pol;
-}
-
-// global -> shared bulk copy (1-D TMA); dst, src 16-byte aligned, bytes % 16 == 0.
-__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes,
-                                         uint32_t bar, uint64_t policy) {
-    asm volatile(
-        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint "
-        "[%0], [%1], %2, [%3], %4;" ::"r"(dst),
-        "l"(src), "r"(bytes), "r"(bar), "l"(policy)
-        : "memory");
-}
-
-// Asks the copy engine to pull [src, src + bytes) into L2 (fire and forget; 16-byte aligned,
-// bytes % 16 == 0). Later plain loads of the range then hit L2 instead of waiting for HBM.
-__device__ __forceinline__ void bulk_prefetch_l2(const void *src, uint32_t bytes) {
-    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
 }
 
 // Pulls the 128-byte line at p into L2 (no register, no wait).

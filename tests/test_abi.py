@@ -44,6 +44,27 @@ def test_cpp_projection_symbols_keep_reference_mangling():
     assert "_Z11x_gemv_w4a8PK16tq_qmma_weight_tPKfPf" in out
     assert "_Z11x_gemm_w4a8PK16tq_qmma_weight_tPKaPKfPKiPfiS7_i" in out
     assert "_Z20x_quantize_act_chunkPKfiiPaPfPi" in out
+    # the runtime helpers have C++ linkage in the reference (xpu/src/tq_common.hpp:212-216):
+    # exported under those mangled names as well as the C ones
+    for sym in ("_Z12tq_dev_allocmPKc", "_Z11tq_dev_freePv", "_Z6tq_h2dPvPKvm", "_Z6tq_d2hPvPKvm",
+                "_Z11tq_dev_zeroPvm"):
+        assert re.search(rf" T {sym}$", out, flags=re.M), sym
+
+
+def test_split_rules_match_the_oracle_on_the_host():
+    """The library's split heuristics are host functions: same counts as the oracle's
+    restatement of xpu/src/kernels_dpas.cpp:170-173 and 1226-1250 over a grid that covers
+    every branch (no GPU needed)."""
+    from oracle import oracle as orc
+    pkg = importlib.import_module("knivesysl-xe_b200")
+    lib = pkg.load()
+    for g in (1, 4, 5, 320, 1088, 2176, 4095, 4096, 9999):
+        assert lib.qwn_choose_gemv_splits(g) == orc.choose_gemv_splits(g)
+    for rg in (0, 1, 3, 20, 64, 320, 640, 1088, 2176, 5000):
+        for tg in (0, 1, 2, 4, 8, 17, 128, 512):
+            for kt in (0, 1, 2, 3, 5, 8, 15, 16, 33, 160, 544):
+                assert lib.qwn_choose_gemm_splits(rg, tg, kt) == orc.choose_gemm_splits(rg, tg, kt), \
+                    (rg, tg, kt)
 
 
 def test_weight_record_layout_matches_header():
