@@ -1,17 +1,24 @@
 #!/usr/bin/env python
 """Benchmark of the W4A8 projection path.
 
-Workload ("cfg2"): batched decode fused gate+up projection, K64 scale tier, T = 8 tokens,
-K = 5120, N = 2 x 17408; seeded N(0, 0.02) weights symmetric-quantised to int4; N(0, 1)
-activations with 1% of channels scaled x20, quantised to int8 per token. One step = one pass:
-per-token activation staging (1 launch) + ONE fused gate|up GEMM launch over a weight copy
-that rotates through `rotate` distinct copies (> L2 in total), so weights come from HBM.
-
   python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+  python bench.py --case NAME --launches L       # one kernel, L launches (profiler target)
 
-N > 1 (torchrun, one rank per GPU): gate and up are column-sharded (x_w4_shard), each rank
-computes its slice of every step and the slices are all-gathered over NCCL ("strong").
 Prints ONE JSON line on rank 0.
+
+N = 1. Headline ("cfg2"): batched decode fused gate+up projection, K64 scale tier, T = 8
+tokens, K = 5120, N = 2 x 17408; seeded N(0, 0.02) weights symmetric-quantised to int4;
+N(0, 1) activations with 1% of the channels scaled x20, quantised to int8 per token. One step
+= per-token activation staging (1 launch) + ONE fused gate|up GEMM launch over a weight copy
+that rotates through `rotate` distinct copies (> L2 in total), so weights come from HBM.
+`per_config` holds one record for every other benchmark configuration (single GEMV, the
+down-projection sweep, the packed prefill GEMM in each activation mode, the 64-layer stack),
+each with its own device time, roofline, end-to-end time through the C ABI with host buffers
+and a bounded CPU sample; `prefill_int8_TOPS` is the packed prefill GEMM's throughput and
+`int8_peak` the tcgen05 kind::i8 issue peak measured in the same run.
+
+N > 1 (torchrun, one rank per GPU): the 64-layer stack, every projection column-sharded N ways
+with x_w4_shard, strong scaling (the same 13.4 GB of weights per step at every N).
 """
 from __future__ import annotations
 
@@ -31,20 +38,27 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-T, K, N_EACH, GROUP = 8, 5120, 17408, 64
 METRIC = "decode_gemv_weight_GBps"
 UNIT = "GB/s"
-# dram__bytes_read.sum + dram__bytes_write.sum of one GEMM launch of this workload, from the
-# ncu capture summarised in profiles/ (None until a capture exists)
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 100_617_216
+WORKLOAD_CFG2 = ("cfg2: batched decode fused gate+up, K64 scale tier, T=8, K=5120, N=2x17408, "
+                 "int8 per-token activations")
+WORKLOAD_CFG5 = ("cfg5: 64-layer projection stack at decode T=8 (5120->10240, 10240->5120, "
+                 "5120->2x17408, 17408->5120 per layer, group-32 int4 weights, int8 per-token "
+                 "activations), column-sharded over the GPUs, strong scaling")
+H, I_FF, QKV = 5120, 17408, 10240          # hidden, MLP width, first projection's width
+# DRAM traffic of one launch of the headline kernel, from the profiler capture named here;
+# None when the kernel has changed since the capture.
+NCU_TRAFFIC = {"bytes_per_launch": None, "capture": None}
+NOMINAL_INT8_TOPS = 4500.0
 
 
 def measured_peaks():
     try:
         with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
-            return float(json.load(f)["hbm_gbs"]), "measured"
+            d = json.load(f)
+        return float(d["hbm_gbs"]), float(d.get("bf16_tflops", 0.0)), "measured"
     except Exception:
-        return 6650.0, "fallback"
+        return 6650.0, 1590.0, "fallback"
 
 
 class ClockSampler:
@@ -68,14 +82,15 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.rows.append((time.time(), line.strip()))
 
-    def stop(self, t0: float, t1: float):
+    def stop(self, spans):
+        """spans: list of (t0, t1) wall-clock intervals in which the GPU was under load."""
         if not self.proc:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
         sm, mx, reasons = [], None, set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for ts, line in self.rows:
-            if ts < t0 or ts > t1 + 0.06:
+            if not any(t0 <= ts <= t1 + 0.06 for t0, t1 in spans):
                 continue
             f = [c.strip() for c in line.split(",")]
             try:
@@ -95,57 +110,833 @@ def dist_env():
             int(os.environ.get("WORLD_SIZE", 1)))
 
 
-def cpu_pass(orc, host_w, aq, as_, asum, rows=None):
-    """One pass of the workload on the CPU oracle (all OpenMP threads); rows limits each
-    matrix to its first `rows` output rows."""
-    for codes, scales in host_w:
-        M = N_EACH if rows is None else rows
-        orc.gemm_w4a8(codes[: M * K // 2], scales[: M * (K // GROUP)], M, K, 1, aq, as_, asum, T)
+def host_threads():
+    return len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
 
 
-def run_reference(args, rank):
+# ------------------------------------------------------------------------------------------
+# shared state of one benchmark process
+# ------------------------------------------------------------------------------------------
+class Ctx:
+    def __init__(self, rotate: int):
+        self.pkg = importlib.import_module("knivesysl-xe_b200")
+        self.wl = importlib.import_module("knivesysl-xe_b200.workloads")
+        self.lib = self.pkg.load()          # raises if the CUDA library is missing
+        self.rotate = rotate
+        self.ev = None
+        self._host_w = {}
+        self.load_spans = []
+        self.peak_hbm, self.peak_bf16, self.peak_kind = measured_peaks()
+
+    def events(self):
+        if self.ev is None:
+            self.ev = [self.lib.tq_event_create() for _ in range(2)]
+        return self.ev
+
+    def host_weight(self, M, K, seed, group):
+        key = (M, K, seed, group)
+        if key not in self._host_w:
+            self._host_w[key] = self.wl.make_weight_w4(M, K, seed=seed, group=group)
+        return self._host_w[key]
+
+    def rotated(self, M, K, seed, group, n=None):
+        """n device copies of one seeded weight, each rolled by a different number of
+        row-groups (distinct bytes at every address, same statistics)."""
+        codes, scales = self.host_weight(M, K, seed, group)
+        out = []
+        for c in range(n or self.rotate):
+            cc = np.roll(codes.reshape(M // 16, -1), c, axis=0).reshape(-1)
+            ss = np.roll(scales.reshape(M // 16, -1), c, axis=0).reshape(-1)
+            out.append(self.pkg.PackedWeight(cc, ss, M, K, k64=(group == 64)))
+        return out
+
+    def time_loop(self, fn, iters, warmup=3):
+        """Mean device time of fn(i) in milliseconds (CUDA events on the library stream)."""
+        lib, ev = self.lib, self.events()
+        for i in range(warmup):
+            fn(i)
+        lib.tq_sync()
+        t0 = time.time()
+        lib.tq_event_record(ev[0])
+        for i in range(iters):
+            fn(i)
+        lib.tq_event_record(ev[1])
+        lib.tq_sync()
+        self.load_spans.append((t0, time.time()))
+        return lib.tq_event_elapsed_ms(ev[0], ev[1]) / iters
+
+
+def pinned_copy(lib, a):
+    a = np.ascontiguousarray(a)
+    p = lib.tq_host_alloc_pinned(a.nbytes)
+    C.memmove(p, a.ctypes.data, a.nbytes)
+    return p
+
+
+def e2e_loop(ctx, case, iters, warmup=3):
+    """The step through the C ABI with HOST buffers: every step uploads its fp32 activations
+    from pinned host memory and reads its result back. Uploads and read-backs run on streams
+    of their own (one per direction): step n+1's upload and step n's read-back overlap step
+    n+1's kernels; tickets order the library stream behind a copy only where a buffer is about
+    to be reused (two input and two output buffer sets). Returns seconds per step and the
+    number of 32-bit words of the last host result that differ from a synchronous rerun."""
+    lib = ctx.lib
+    hx = pinned_copy(lib, case.x_host)
+    nbx = case.x_host.nbytes
+    hy = [lib.tq_host_alloc_pinned(case.out_bytes) for _ in range(2)]
+    tickets, up = [-1, -1], [-1, -1]
+    up[0] = lib.tq_h2d_overlapped(case.x_dev[0].ptr, hx, nbx)
+    n = 0
+    last = None
+
+    def one(i):
+        nonlocal n, last
+        b = n & 1
+        if tickets[b] >= 0:
+            lib.tq_stream_wait_copy(tickets[b])
+        up[(n + 1) & 1] = lib.tq_h2d_overlapped(case.x_dev[(n + 1) & 1].ptr, hx, nbx)
+        lib.tq_stream_wait_copy(up[n & 1])
+        case.run(i, n & 1, b)
+        tickets[b] = lib.tq_d2h_overlapped(hy[b], case.out_ptr(b), case.out_bytes)
+        last = (i, n & 1, b)
+        n += 1
+
+    for i in range(warmup):
+        one(i)
+    lib.tq_sync()
+    t0w = time.time()
+    t0 = time.perf_counter()
+    for i in range(iters):
+        one(i)
+    lib.tq_sync()
+    dt = time.perf_counter() - t0
+    ctx.load_spans.append((t0w, time.time()))
+    i, xb, b = last
+    got = np.ctypeslib.as_array(C.cast(hy[b], C.POINTER(C.c_uint32)), shape=(case.out_bytes // 4,)).copy()
+    lib.tq_h2d(case.x_dev[xb].ptr, hx, nbx)
+    case.run(i, xb, b)
+    want = np.empty(case.out_bytes // 4, dtype=np.uint32)
+    lib.tq_d2h(want.ctypes.data, case.out_ptr(b), case.out_bytes)
+    diff = int(np.count_nonzero(got != want))
+    lib.tq_host_free_pinned(hx)
+    for p in hy:
+        lib.tq_host_free_pinned(p)
+    return dt / iters, diff
+
+
+def cpu_sample(fn, units_per_pass, budget_s, unit, what):
+    """Time-bounded CPU sample: fn() is one pass of the oracle over `units_per_pass` units."""
+    from oracle import oracle as orc
+    fn()
+    passes, t0 = 0, time.perf_counter()
+    while True:
+        fn()
+        passes += 1
+        if time.perf_counter() - t0 >= budget_s:
+            break
+    dt = time.perf_counter() - t0
+    return {"value": units_per_pass * passes / dt, "unit": unit, "cores": orc.num_threads(),
+            "kind": "port", "sample": f"{passes} x ({what}) in {dt:.1f} s, OpenMP over all host threads"}
+
+
+# ------------------------------------------------------------------------------------------
+# cases
+# ------------------------------------------------------------------------------------------
+class DecodeGemm:
+    """Chunk staging + batched GEMM over one or two weights that share the staged
+    activations (xpu/src/decode.cpp:1856-1871): cfg2 (gate|up, K64) and the T >= 8 points of
+    the down-projection sweep (cfg3)."""
+
+    def __init__(self, ctx, name, M, count, K, group, T, mode, seed0, xgen, rows_note=""):
+        self.ctx, self.name, self.M, self.count, self.K, self.group, self.T = ctx, name, M, count, K, group, T
+        self.mode = mode                       # "pertoken" | "exact" (scale per (token, K32))
+        lib, pkg = ctx.lib, ctx.pkg
+        self.sets = list(zip(*[ctx.rotated(M, K, seed0 + j, group) for j in range(count)]))
+        self.warr = [pkg.weight_array(list(s)) for s in self.sets]
+        self.x_host = xgen()
+        self.x_dev = [pkg.DevBuf.from_numpy(self.x_host), pkg.DevBuf.from_numpy(self.x_host)]
+        nblk = K // 32 * T
+        self.nblk = nblk
+        self.aq, self.as_, self.asum, self.as_tok = (pkg.DevBuf(nblk * 32), pkg.DevBuf(nblk * 4),
+                                                     pkg.DevBuf(nblk * 4), pkg.DevBuf(T * 4))
+        self.out_bytes = count * T * M * 4
+        self.y = [pkg.DevBuf(self.out_bytes) for _ in range(2)]
+        self.yarr = [(C.c_void_p * count)(*[b.ptr + j * T * M * 4 for j in range(count)]) for b in self.y]
+        self.weight_bytes = count * ctx.wl.weight_bytes(M, K, group)
+        self.algo_bytes = self.weight_bytes + T * K + nblk * 8 + self.out_bytes
+        self.ops = 2.0 * T * count * M * K
+        self.rows_note = rows_note
+        self.launches_per_step = 2
+
+    def stage(self, xb):
+        lib = self.ctx.lib
+        if self.mode == "pertoken":
+            lib.qwn_x_quantize_act_chunk_pertoken(self.x_dev[xb].ptr, self.K, self.T, self.aq.ptr,
+                                                  self.as_.ptr, self.asum.ptr, self.as_tok.ptr)
+        else:
+            lib.qwn_x_quantize_act_chunk(self.x_dev[xb].ptr, self.K, self.T, self.aq.ptr, self.as_.ptr,
+                                         self.asum.ptr)
+
+    def kernel(self, i, b=0):
+        lib = self.ctx.lib
+        if self.mode == "pertoken":
+            rc = lib.qwn_x_gemm_w4a8_fanout_pertoken(self.warr[i % len(self.warr)], self.yarr[b], self.count,
+                                                     self.aq.ptr, self.as_tok.ptr, self.asum.ptr, self.T)
+        else:
+            rc = lib.qwn_x_gemm_w4a8_fanout(self.warr[i % len(self.warr)], self.yarr[b], self.count,
+                                            self.aq.ptr, self.as_.ptr, self.asum.ptr, self.T, None, 0)
+        assert rc == 0, rc
+
+    def _oracle_gemm(self, codes, scales, rows, oq, os_, osm):
+        from oracle import oracle as orc
+        ksh = int(self.group == 64)
+        if self.mode == "pertoken":
+            S = self.ctx.lib.qwn_choose_gemm_splits(self.M // 16, self.T // 8, self.K // 32)
+            at = os_.reshape(self.K // 32, self.T)[0].copy()
+            return orc.gemm_w4a8_pertoken(codes, scales, rows, self.K, ksh, oq, at, osm, self.T, splits=S)[1]
+        if rows != self.M:
+            S = self.ctx.lib.qwn_choose_gemm_splits(self.M // 16, self.T // 8, self.K // 32)
+            return orc.gemm_w4a8(codes, scales, rows, self.K, ksh, oq, os_, osm, self.T, forced_splits=S)[1]
+        return orc.gemm_w4a8(codes, scales, rows, self.K, ksh, oq, os_, osm, self.T, fma=1)[1]
+
+    def run(self, i, xb, b):
+        self.stage(xb)
+        self.kernel(i, b)
+
+    def out_ptr(self, b):
+        return self.y[b].ptr
+
+    def oracle_diff(self):
+        """Words of weight copy 0's output that differ from the CPU oracle (fused variant)."""
+        from oracle import oracle as orc
+        lib = self.ctx.lib
+        lib.tq_h2d(self.x_dev[0].ptr, self.x_host.ctypes.data, self.x_host.nbytes)
+        self.run(0, 0, 0)
+        lib.tq_sync()
+        got = self.y[0].to_numpy(np.uint32).reshape(self.count, self.T, self.M)
+        oq, os_, osm = orc.quantize_act_chunk(self.x_host, per_token=(self.mode == "pertoken"))
+        diff = 0
+        for j in range(self.count):
+            codes, scales = self.ctx.host_weight(self.M, self.K, self.seed_of(j), self.group)
+            want = self._oracle_gemm(codes, scales, self.M, oq, os_, osm)
+            diff += int(np.count_nonzero(got[j] != want.view(np.uint32)))
+        return diff
+
+    def seed_of(self, j):
+        return self._seed0 + j
+
+    def cpu_pass_fn(self, rows):
+        from oracle import oracle as orc
+        oq, os_, osm = orc.quantize_act_chunk(self.x_host, per_token=(self.mode == "pertoken"))
+        ws = [self.ctx.host_weight(self.M, self.K, self.seed_of(j), self.group) for j in range(self.count)]
+        Kt = self.K // 32
+        sg = Kt >> int(self.group == 64)
+
+        def fn():
+            orc.quantize_act_chunk(self.x_host, per_token=(self.mode == "pertoken"))
+            for codes, scales in ws:
+                self._oracle_gemm(codes[: rows * self.K // 2], scales[: rows * sg], rows, oq, os_, osm)
+        return fn
+
+
+class DecodeGemv:
+    """Single-token staging + prepared GEMV: cfg1 and the T = 1 point of cfg3 (there the
+    staging is the fused silu(gate) * up quantiser, xpu/src/decode.cpp:250-258)."""
+
+    def __init__(self, ctx, name, M, K, group, mode, seed0, silu):
+        self.ctx, self.name, self.M, self.K, self.group, self.mode, self.silu = ctx, name, M, K, group, mode, silu
+        self.T = 1
+        pkg = ctx.pkg
+        self._seed0 = seed0
+        self.ws = ctx.rotated(M, K, seed0, group)
+        rng = np.random.Generator(np.random.Philox(key=seed0 + 1000))
+        rows = 2 if silu else 1
+        self.x_host = rng.standard_normal((rows, K), dtype=np.float32)
+        self.x_dev = [pkg.DevBuf.from_numpy(self.x_host), pkg.DevBuf.from_numpy(self.x_host)]
+        self.hidden = pkg.DevBuf(K * 4)
+        self.out_bytes = M * 4
+        self.y = [pkg.DevBuf(M * 4) for _ in range(2)]
+        self.weight_bytes = ctx.wl.weight_bytes(M, K, group)
+        self.algo_bytes = self.weight_bytes + K + (K // 32) * 8 + M * 4
+        self.ops = 2.0 * M * K
+        self.launches_per_step = 2
+
+    def stage(self, xb):
+        lib, x = self.ctx.lib, self.x_dev[xb].ptr
+        if self.silu:
+            f = lib.qwn_x_silu_mul_quant_pertoken if self.mode == "pertoken" else lib.qwn_x_silu_mul_quant
+            f(self.hidden.ptr, x, x + self.K * 4, self.K)
+        elif self.mode == "pertoken":
+            lib.qwn_x_prepare_gemv_act_s8_pertoken(x, self.K)
+        else:
+            lib.qwn_x_prepare_gemv_act_s8(x, self.K)
+
+    def kernel(self, i, b=0):
+        rc = self.ctx.lib.qwn_x_gemv_w4a8_prepared(self.ws[i % len(self.ws)].ref, self.y[b].ptr, None)
+        assert rc == 0, rc
+
+    def run(self, i, xb, b):
+        self.stage(xb)
+        self.kernel(i, b)
+
+    def out_ptr(self, b):
+        return self.y[b].ptr
+
+    def _oracle_act(self):
+        from oracle import oracle as orc
+        if self.silu:
+            v = orc.silu_mul(self.x_host[0], self.x_host[1])
+        else:
+            v = self.x_host[0]
+        if self.mode == "pertoken":
+            q, s, _ = orc.quantize_act_chunk(v[None, :], per_token=True)
+            sm = q.astype(np.int32).reshape(-1, 16).sum(axis=1).astype(np.int32)
+        else:
+            q, s, sm = orc.quantize_act_s8(v)
+        return q, s, sm
+
+    def oracle_diff(self):
+        from oracle import oracle as orc
+        lib = self.ctx.lib
+        lib.tq_h2d(self.x_dev[0].ptr, self.x_host.ctypes.data, self.x_host.nbytes)
+        self.run(0, 0, 0)
+        lib.tq_sync()
+        got = self.y[0].to_numpy(np.uint32)
+        q, s, sm = self._oracle_act()
+        codes, scales = self.ctx.host_weight(self.M, self.K, self._seed0, self.group)
+        _, want = orc.gemv_w4a8(codes, scales, self.M, self.K, int(self.group == 64), q, s, sm, fma=1)
+        return int(np.count_nonzero(got != want.view(np.uint32)))
+
+    def cpu_pass_fn(self, rows):
+        from oracle import oracle as orc
+        q, s, sm = self._oracle_act()
+        codes, scales = self.ctx.host_weight(self.M, self.K, self._seed0, self.group)
+
+        def fn():
+            self._oracle_act()
+            orc.gemv_w4a8(codes, scales, self.M, self.K, int(self.group == 64), q, s, sm)
+        return fn
+
+
+class Prefill:
+    """cfg4: packed prefill GEMM, 4096 tokens in four segments of 1024, 17408 x 5120, K64."""
+
+    MODES = {"exact_fp32": "scale per (token, K32): the reference's arithmetic, fp32 out",
+             "pertoken_fp32": "scale per token, fp32 out", "pertoken_bf16": "scale per token, bf16 out",
+             "w4a4_fp32": "int4 activations per (token, K64) (x_gemm_w4a4), fp32 out"}
+
+    def __init__(self, ctx, name, mode, shared=None):
+        self.ctx, self.name, self.mode = ctx, name, mode
+        self.M, self.K, self.T, self.group = I_FF, H, 4096, 64
+        pkg, lib = ctx.pkg, ctx.lib
+        if shared is None:
+            shared = {}
+            shared["w"] = ctx.rotated(self.M, self.K, 11, 64, n=1)[0]
+            shared["x_host"] = ctx.wl.activations_normal(self.T, self.K, seed=7)
+            shared["x_dev"] = [pkg.DevBuf.from_numpy(shared["x_host"]) for _ in range(2)]
+            n = self.K // 32 * self.T
+            shared["stg"] = (pkg.DevBuf(n * 32), pkg.DevBuf(n * 4), pkg.DevBuf(n * 4), pkg.DevBuf(self.T * 4))
+            shared["y"] = [pkg.DevBuf(self.T * self.M * 4) for _ in range(2)]
+        self.shared = shared
+        self.w, self.x_host, self.x_dev = shared["w"], shared["x_host"], shared["x_dev"]
+        self.aq, self.as_, self.asum, self.as_tok = shared["stg"]
+        self.y = shared["y"]
+        self.out_bytes = self.T * self.M * (2 if mode.endswith("bf16") else 4)
+        self.off = (C.c_int * 5)(0, 1024, 2048, 3072, 4096)
+        self.weight_bytes = ctx.wl.weight_bytes(self.M, self.K, 64)
+        self.ops = 2.0 * self.T * self.M * self.K
+        self.launches_per_step = 3      # staging, activation image pre-pass, GEMM
+
+    def stage(self, xb):
+        lib, x = self.ctx.lib, self.x_dev[xb].ptr
+        if self.mode == "exact_fp32":
+            lib.qwn_x_quantize_act_chunk(x, self.K, self.T, self.aq.ptr, self.as_.ptr, self.asum.ptr)
+        elif self.mode == "w4a4_fp32":
+            lib.qwn_x_quantize_act_chunk_s4(x, self.K, self.T, self.aq.ptr, self.as_.ptr, self.asum.ptr)
+        else:
+            lib.qwn_x_quantize_act_chunk_pertoken(x, self.K, self.T, self.aq.ptr, self.as_.ptr,
+                                                  self.asum.ptr, self.as_tok.ptr)
+
+    def kernel(self, i, b=0):
+        lib = self.ctx.lib
+        if self.mode == "exact_fp32":
+            rc = lib.qwn_x_gemm_w4a8(self.w.ref, self.aq.ptr, self.as_.ptr, self.asum.ptr, self.y[b].ptr,
+                                     self.T, self.off, 4)
+        elif self.mode == "w4a4_fp32":
+            rc = lib.qwn_x_gemm_w4a4(self.w.ref, self.aq.ptr, self.as_.ptr, self.asum.ptr, self.y[b].ptr,
+                                     self.T)
+        else:
+            rc = lib.qwn_x_gemm_w4a8_pertoken(self.w.ref, self.aq.ptr, self.as_tok.ptr, self.asum.ptr,
+                                              self.y[b].ptr, self.T, int(self.mode.endswith("bf16")))
+        assert rc == 0, rc
+
+    def run(self, i, xb, b):
+        self.stage(xb)
+        self.kernel(i, b)
+
+    def out_ptr(self, b):
+        return self.y[b].ptr
+
+    def cpu_pass_fn(self, rows, tokens=256):
+        """A bounded sample: `rows` weight rows x the first `tokens` tokens."""
+        from oracle import oracle as orc
+        x = self.x_host[:tokens]
+        codes, scales = self.ctx.host_weight(self.M, self.K, 11, 64)
+        c, s = codes[: rows * self.K // 2], scales[: rows * (self.K // 64)]
+        if self.mode == "w4a4_fp32":
+            q = orc.quantize_act_chunk_s4(x)
+            return lambda: (orc.quantize_act_chunk_s4(x), orc.gemm_w4a4(c, s, rows, self.K, *q, tokens))
+        if self.mode == "exact_fp32":
+            q = orc.quantize_act_chunk(x)
+            return lambda: (orc.quantize_act_chunk(x), orc.gemm_w4a8(c, s, rows, self.K, 1, *q, tokens))
+        oq, os_, osm = orc.quantize_act_chunk(x, per_token=True)
+        at = os_.reshape(self.K // 32, tokens)[0].copy()
+        return lambda: (orc.quantize_act_chunk(x, per_token=True),
+                        orc.gemm_w4a8_pertoken(c, s, rows, self.K, 1, oq, at, osm, tokens))
+
+
+class Stack:
+    """cfg5: 64 layers x four projections at T = 8, group-32 weights, per-token int8
+    activations. Per layer: RMSNorm of the incoming rows (keeps values O(1) through 64
+    layers), 5120->10240, 10240->5120, fused 5120->gate|up, silu(gate)*up, 17408->5120; every
+    projection is staging + GEMM through the C ABI (the batched path of
+    xpu/src/decode.cpp:1856-1871). Layers use distinct weights: four seeded base matrices,
+    rolled by a different number of row-groups per layer. With tp > 1 every projection is a
+    column shard (x_w4_shard mode 0; gate|up as two groups so silu*mul stays local) and the
+    output slices are exchanged after every projection."""
+
+    LAYERS = 64
+
+    def __init__(self, ctx, layers=None, tp=1, rank=0):
+        self.ctx, self.tp, self.rank = ctx, tp, rank
+        self.L = layers or self.LAYERS
+        self.T = 8
+        pkg, lib, wl = ctx.pkg, ctx.lib, ctx.wl
+        shapes = [(QKV, H, 41), (H, QKV, 42), (I_FF, H, 43), (I_FF, H, 44), (H, I_FF, 45)]
+        base = [ctx.rotated(M, K, seed, 32, n=1)[0] for M, K, seed in shapes]
+        self.shapes = shapes
+        self.layers = []
+        for l in range(self.L):
+            ws = []
+            for (M, K, _), b in zip(shapes, base):
+                ws.append(self._rolled_shard(b, M, K, (l * 37) % (M // 16)))
+            self.layers.append(ws)
+        for b in base:
+            b.codes.free()
+            b.scales.free()
+        T = self.T
+        self.x_host = wl.activations_normal(T, H, seed=5)
+        self.x_dev = [pkg.DevBuf.from_numpy(self.x_host), pkg.DevBuf.from_numpy(self.x_host)]
+        self.norm_w = pkg.DevBuf.from_numpy(np.zeros(H, dtype=np.uint16))     # (1 + 0) weights
+        kmax = I_FF
+        nb = kmax // 32 * T
+        self.aq, self.as_, self.asum, self.as_tok = (pkg.DevBuf(nb * 32), pkg.DevBuf(nb * 4),
+                                                     pkg.DevBuf(nb * 4), pkg.DevBuf(T * 4))
+        self.xn = pkg.DevBuf(T * H * 4)
+        self.y1 = pkg.DevBuf(T * QKV * 4)
+        self.y2 = pkg.DevBuf(T * H * 4)
+        self.gu = pkg.DevBuf(2 * T * I_FF * 4)
+        self.h = pkg.DevBuf(T * I_FF * 4)
+        self.out_bytes = T * H * 4
+        self.y = [pkg.DevBuf(self.out_bytes) for _ in range(2)]
+        self.cur = pkg.DevBuf(T * H * 4)
+        self.weight_bytes = self.L * sum(wl.weight_bytes(M, K, 32) for M, K, _ in shapes)
+        self.launches_per_step = self.L * 10
+        self.graph = None
+
+    def _rolled_shard(self, base, M, K, shift):
+        """Device copy of `base` rolled by `shift` row-groups (two runs per array)."""
+        pkg, lib = self.ctx.pkg, self.ctx.lib
+        cb, sb = (K // 32) * 256, (K // 32) * 32
+        codes, scales = pkg.DevBuf(M // 16 * cb), pkg.DevBuf(M // 16 * sb)
+        g = M // 16
+        for dst, src, rb in ((codes, base.codes, cb), (scales, base.scales, sb)):
+            lib.tq_d2d_async(dst.ptr + shift * rb, src.ptr, (g - shift) * rb)
+            if shift:
+                lib.tq_d2d_async(dst.ptr, src.ptr + (g - shift) * rb, shift * rb)
+        w = pkg.PackedWeight.__new__(pkg.PackedWeight)
+        w.codes, w.scales = codes, scales
+        w.rec = pkg.TqWeight()
+        w.rec.M, w.rec.K, w.rec.Mt, w.rec.Kt = M, K, M // 16, K // 32
+        w.rec.d_s4, w.rec.d_s4_scale, w.rec.s4_ready = codes.ptr, scales.ptr, 1
+        lib.tq_sync()
+        return w
+
+    def _proj(self, w, x_ptr, K, y_ptr):
+        lib, T = self.ctx.lib, self.T
+        lib.qwn_x_quantize_act_chunk_pertoken(x_ptr, K, T, self.aq.ptr, self.as_.ptr, self.asum.ptr,
+                                              self.as_tok.ptr)
+        rc = lib.qwn_x_gemm_w4a8(w.ref, self.aq.ptr, self.as_.ptr, self.asum.ptr, y_ptr, T, None, 0)
+        assert rc == 0, rc
+
+    def _issue(self, x_ptr, out_ptr):
+        lib, pkg, T = self.ctx.lib, self.ctx.pkg, self.T
+        src = x_ptr
+        for l, (w1, w2, wg, wu, wd) in enumerate(self.layers):
+            lib.qwn_x_rmsnorm_chunk(self.xn.ptr, src, self.norm_w.ptr, H, T, 1e-6)
+            self._proj(w1, self.xn.ptr, H, self.y1.ptr)
+            self._proj(w2, self.y1.ptr, QKV, self.y2.ptr)
+            lib.qwn_x_quantize_act_chunk_pertoken(self.y2.ptr, H, T, self.aq.ptr, self.as_.ptr,
+                                                  self.asum.ptr, self.as_tok.ptr)
+            warr = pkg.weight_array([wg, wu])
+            yarr = (C.c_void_p * 2)(self.gu.ptr, self.gu.ptr + T * I_FF * 4)
+            rc = lib.qwn_x_gemm_w4a8_fanout(warr, yarr, 2, self.aq.ptr, self.as_.ptr, self.asum.ptr, T,
+                                            None, 0)
+            assert rc == 0, rc
+            lib.qwn_x_silu_mul(self.h.ptr, self.gu.ptr, self.gu.ptr + T * I_FF * 4, T * I_FF)
+            dst = out_ptr if l == self.L - 1 else self.cur.ptr
+            self._proj(wd, self.h.ptr, I_FF, dst)
+            src = dst
+
+    def capture(self):
+        """One CUDA graph per (input buffer, output buffer) pair: 640 launches per replay."""
+        lib = self.ctx.lib
+        self._issue(self.x_dev[0].ptr, self.y[0].ptr)        # warm: all scratch allocated
+        lib.tq_sync()
+        self.graph = {}
+        for xb in range(2):
+            for b in range(2):
+                assert lib.tq_graph_capture_begin() == 0
+                self._issue(self.x_dev[xb].ptr, self.y[b].ptr)
+                g = lib.tq_graph_capture_end()
+                assert g, "graph capture failed"
+                self.graph[(xb, b)] = g
+
+    def run(self, i, xb, b):
+        if self.graph:
+            self.ctx.lib.tq_graph_launch(self.graph[(xb, b)])
+        else:
+            self._issue(self.x_dev[xb].ptr, self.y[b].ptr)
+
+    def kernel(self, i, b=0):
+        self.run(i, 0, b)
+
+    def out_ptr(self, b):
+        return self.y[b].ptr
+
+    def cpu_pass_fn(self):
+        """One projection of each kind of layer 0 on the oracle (1/64 of a step)."""
+        from oracle import oracle as orc
+        T = self.T
+        ws = [self.ctx.host_weight(M, K, seed, 32) for M, K, seed in self.shapes]
+        xs = {K: self.ctx.wl.activations_normal(T, K, seed=K) for K in (H, QKV, I_FF)}
+        qs = {K: orc.quantize_act_chunk(x, per_token=True) for K, x in xs.items()}
+
+        def fn():
+            for (M, K, _), (codes, scales) in zip(self.shapes, ws):
+                orc.quantize_act_chunk(xs[K], per_token=True)
+                orc.gemm_w4a8(codes, scales, M, K, 0, *qs[K], T)
+        return fn
+
+
+# ------------------------------------------------------------------------------------------
+# records
+# ------------------------------------------------------------------------------------------
+def hbm_record(ctx, case, kernel_name, kernel_ms):
+    ach = case.algo_bytes / (kernel_ms * 1e-3) / 1e9
+    return {"bound": "hbm", "achieved": ach, "peak": ctx.peak_hbm, "unit": "GB/s", "frac": ach / ctx.peak_hbm,
+            "peak_source": f"{ctx.peak_kind} copy bandwidth", "kernel": kernel_name,
+            "us_per_launch": kernel_ms * 1e3, "algorithmic_bytes_per_launch": int(case.algo_bytes),
+            "weight_GBps": case.weight_bytes / (kernel_ms * 1e-3) / 1e9, "traffic": None}
+
+
+def tensor_record(ctx, case, kernel_name, kernel_ms, int8_peak):
+    tops = case.ops / (kernel_ms * 1e-3) / 1e12
+    peak = int8_peak or NOMINAL_INT8_TOPS
+    return {"bound": "tensor", "achieved": tops, "peak": peak, "unit": "TOP/s (int8)", "frac": tops / peak,
+            "peak_source": ("tcgen05 kind::i8 issue peak measured in this run" if int8_peak
+                            else "nominal dense int8"),
+            "frac_of_nominal_4500": tops / NOMINAL_INT8_TOPS,
+            "frac_of_2x_measured_bf16": tops / (2.0 * ctx.peak_bf16) if ctx.peak_bf16 else None,
+            "kernel": kernel_name, "us_per_launch": kernel_ms * 1e3, "algorithmic_ops_per_launch": case.ops,
+            "traffic": None}
+
+
+def run_case(ctx, case, kernel_name, iters, e2e_iters, cpu_budget, cpu_rows, bound="hbm", int8_peak=None,
+             check=True, cpu_units=None, cpu_what=None, cpu_fn=None):
+    lib = ctx.lib
+    rec = {"name": case.name, "T": case.T, "mode": getattr(case, "mode", None)}
+    if check and hasattr(case, "oracle_diff"):
+        rec["oracle_words_differing"] = case.oracle_diff()
+    step_ms = ctx.time_loop(lambda i: case.run(i, 0, 0), iters)
+    case.stage(0)
+    k_ms = ctx.time_loop(lambda i: case.kernel(i), iters)
+    rec["us"] = step_ms * 1e3
+    rec["launches_per_step"] = case.launches_per_step
+    rec["roofline"] = (hbm_record(ctx, case, kernel_name, k_ms) if bound == "hbm"
+                       else tensor_record(ctx, case, kernel_name, k_ms, int8_peak))
+    s, diff = e2e_loop(ctx, case, e2e_iters)
+    if bound == "hbm":
+        val, unit = case.weight_bytes / s / 1e9, UNIT
+        rec["value"], rec["unit"] = case.weight_bytes / (step_ms * 1e-3) / 1e9, UNIT
+    else:
+        val, unit = case.ops / s / 1e12, "TOP/s (int8)"
+        rec["value"], rec["unit"] = case.ops / (step_ms * 1e-3) / 1e12, unit
+    rec["e2e"] = {"value": val, "unit": unit, "us_per_step": s * 1e6, "h2d_bytes_per_step": int(case.x_host.nbytes),
+                  "d2h_bytes_per_step": int(case.out_bytes), "steps": e2e_iters,
+                  "last_result_words_differing": diff}
+    if cpu_budget > 0:
+        fn = cpu_fn or case.cpu_pass_fn(cpu_rows)
+        rec["cpu_baseline"] = cpu_sample(fn, cpu_units, cpu_budget, unit, cpu_what)
+    return rec
+
+
+def int8_peak_tops(ctx):
+    """tcgen05 kind::i8 issue peak (TMEM accumulate only, no epilogue), if the library has it."""
+    lib = ctx.lib
+    if not hasattr(lib, "qwn_tc_int8_peak"):
+        return None
+    lib.qwn_tc_int8_peak.restype = C.c_double
+    lib.qwn_tc_int8_peak.argtypes = [C.c_int]
+    t0 = time.time()
+    v = float(lib.qwn_tc_int8_peak(4000))
+    ctx.load_spans.append((t0, time.time()))
+    return v if v > 0 else None
+
+
+def build_cases(ctx, which):
+    """name -> (case, kernel name, bound). Built lazily: only what `which` selects."""
+    wl = ctx.wl
+    out = {}
+
+    def want(n):
+        return which is None or n in which
+
+    if want("cfg2"):
+        c = DecodeGemm(ctx, "cfg2", I_FF, 2, H, 64, 8, "pertoken", 11,
+                       lambda: wl.activations_normal(8, H, seed=5, outlier_frac=0.01))
+        c._seed0 = 11
+        out["cfg2"] = (c, "gemm_w4a8_dtc_kernel", "hbm")
+    if want("cfg2_exact"):
+        c = DecodeGemm(ctx, "cfg2_exact", I_FF, 2, H, 64, 8, "exact", 11,
+                       lambda: wl.activations_normal(8, H, seed=5, outlier_frac=0.01))
+        c._seed0 = 11
+        out["cfg2_exact"] = (c, "gemm_w4a8_dtc_kernel", "hbm")
+    if want("cfg1"):
+        out["cfg1"] = (DecodeGemv(ctx, "cfg1", I_FF, H, 32, "pertoken", 21, silu=False), "gemv_w4a8_kernel", "hbm")
+    if want("cfg3_T1"):
+        out["cfg3_T1"] = (DecodeGemv(ctx, "cfg3_T1", H, I_FF, 32, "pertoken", 23, silu=True),
+                          "gemv_w4a8_kernel", "hbm")
+    for T in (8, 16, 32, 64):
+        n = f"cfg3_T{T}"
+        if want(n):
+            def xg(T=T):
+                rng = np.random.Generator(np.random.Philox(key=31 + T))
+                g = rng.standard_normal((T, I_FF))
+                u = rng.standard_normal((T, I_FF))
+                return (g / (1.0 + np.exp(-g)) * u).astype(np.float32)
+            c = DecodeGemm(ctx, n, H, 1, I_FF, 32, T, "pertoken", 23, xg)
+            c._seed0 = 23
+            out[n] = (c, "gemm_w4a8_dtc_kernel", "hbm")
+    shared = None
+    for mode in Prefill.MODES:
+        n = f"cfg4_{mode}"
+        if want(n):
+            c = Prefill(ctx, n, mode, shared)
+            shared = c.shared
+            out[n] = (c, "gemm_w4a8_tc_kernel", "tensor")
+    return out
+
+
+# ------------------------------------------------------------------------------------------
+# reference arm: the CPU oracle on the host cores
+# ------------------------------------------------------------------------------------------
+def run_reference(args, rank, world):
     """The reference's scalar projection semantics (the CPU oracle; the reference's SYCL
-    sources cannot be built without Intel's toolchain) on the host cores."""
+    sources cannot be built without Intel's toolchain) on the host cores, on the workload
+    the GPU arm runs at this N."""
     if rank != 0:
         return
     from oracle import oracle as orc
-    # all host threads, also under torchrun (which exports OMP_NUM_THREADS=1 to its workers)
-    orc.set_num_threads(len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity")
-                        else (os.cpu_count() or 1))
+    orc.set_num_threads(host_threads())
     wl = importlib.import_module("knivesysl-xe_b200.workloads")
-    host_w = [wl.make_weight_w4(N_EACH, K, seed=11 + i, group=GROUP) for i in range(2)]
-    x = wl.activations_normal(T, K, seed=5, outlier_frac=0.01)
-    aq, as_, asum = orc.quantize_act_chunk(x, per_token=True)
+    T = 8
+    if world == 1:
+        K, M, group = H, I_FF, 64
+        host_w = [wl.make_weight_w4(M, K, seed=11 + i, group=group) for i in range(2)]
+        x = wl.activations_normal(T, K, seed=5, outlier_frac=0.01)
+        aq, as_, asum = orc.quantize_act_chunk(x, per_token=True)
+
+        def cpu_pass(rows):
+            orc.quantize_act_chunk(x, per_token=True)
+            for codes, scales in host_w:
+                orc.gemm_w4a8(codes[: rows * K // 2], scales[: rows * (K // group)], rows, K, 1, aq, as_, asum, T)
+        full_rows, per_row_bytes, workload = M, 2 * (K // 2 + (K // group) * 2), WORKLOAD_CFG2
+        what = "rows of gate and up per step"
+    else:
+        shapes = [(QKV, H, 41), (H, QKV, 42), (I_FF, H, 43), (I_FF, H, 44), (H, I_FF, 45)]
+        ws = [wl.make_weight_w4(M, K, seed=s, group=32) for M, K, s in shapes]
+        xs = {K: wl.activations_normal(T, K, seed=K) for K in (H, QKV, I_FF)}
+        qs = {K: orc.quantize_act_chunk(v, per_token=True) for K, v in xs.items()}
+
+        def cpu_pass(frac_rows):
+            # frac_rows of 17408 scales every projection of one layer by the same fraction
+            for (M, K, _), (codes, scales) in zip(shapes, ws):
+                rows = max(16, M * frac_rows // I_FF // 16 * 16)
+                orc.quantize_act_chunk(xs[K], per_token=True)
+                orc.gemm_w4a8(codes[: rows * K // 2], scales[: rows * (K // 32)], rows, K, 0, *qs[K], T)
+        full_rows = I_FF
+        per_row_bytes = sum(wl.weight_bytes(M, K, 32) for M, K, _ in shapes) / I_FF
+        workload = WORKLOAD_CFG5
+        what = "of one layer's five matrices per step (1 of 64 layers)"
     t0 = time.perf_counter()
-    cpu_pass(orc, host_w, aq, as_, asum, rows=1088)
-    t_probe = (time.perf_counter() - t0) * 16.0
+    cpu_pass(1088)
+    t_probe = (time.perf_counter() - t0) * (full_rows / 1088)
     max_seconds = 150.0
-    frac_rows = N_EACH
     total = args.steps + args.warmup
+    rows = full_rows
     if t_probe * total > max_seconds:
-        frac_rows = max(16, int(N_EACH * max_seconds / (t_probe * total)) // 16 * 16)
+        rows = max(16, int(full_rows * max_seconds / (t_probe * total)) // 16 * 16)
     for _ in range(args.warmup):
-        orc.quantize_act_chunk(x, per_token=True)
-        cpu_pass(orc, host_w, aq, as_, asum, rows=frac_rows)
+        cpu_pass(rows)
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        orc.quantize_act_chunk(x, per_token=True)
-        cpu_pass(orc, host_w, aq, as_, asum, rows=frac_rows)
+        cpu_pass(rows)
     dt = time.perf_counter() - t0
-    wl_bytes = 2 * wl.weight_bytes(frac_rows, K, GROUP)
-    val = wl_bytes * args.steps / dt / 1e9
-    sample = f"{frac_rows} of {N_EACH} rows of gate and up per step, T={T}, K={K}"
+    val = per_row_bytes * rows * args.steps / dt / 1e9
+    sample = f"{rows} of {full_rows} {what}, T={T}"
     out = {
         "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "s8xs4->s32",
-        "data": "synthetic",
-        "config": {"workload": "cfg2: fused gate+up, K64 tier, T=8, K=5120, N=2x17408 (CPU oracle)"},
+        "higher_is_better": True, "scaling": "weak" if world == 1 else "strong", "vs_baseline": None,
+        "dtype": "s8xs4->s32, fp32 out", "data": "synthetic",
+        "config": {"workload": workload},
         "cpu_baseline": {"value": val, "unit": UNIT, "cores": orc.num_threads(), "kind": "port",
                          "sample": sample},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
+    print(json.dumps(out), flush=True)
+
+
+# ------------------------------------------------------------------------------------------
+# N = 1
+# ------------------------------------------------------------------------------------------
+PER_CONFIG = ["cfg1", "cfg2_exact", "cfg3_T1", "cfg3_T8", "cfg3_T16", "cfg3_T32", "cfg3_T64",
+              "cfg4_exact_fp32", "cfg4_pertoken_fp32", "cfg4_pertoken_bf16", "cfg4_w4a4_fp32"]
+
+
+def run_single(args):
+    ctx = Ctx(args.rotate)
+    lib = ctx.lib
+    assert lib.tq_set_device(0) == 0
+    sampler = ClockSampler(0)
+    cpu_on = not args.no_cpu_baseline
+    if cpu_on:
+        from oracle import oracle as orc
+        orc.set_num_threads(host_threads())
+
+    if args.case:
+        # profiler target: L launches of one case's dominant kernel, nothing else timed
+        if args.case == "cfg5":
+            case = Stack(ctx, layers=args.layers)
+            case.run(0, 0, 0)
+            lib.tq_sync()
+            for i in range(args.launches):
+                case.run(i, 0, 0)
+        else:
+            case, kname, _ = build_cases(ctx, {args.case})[args.case]
+            case.stage(0)
+            lib.tq_sync()
+            for i in range(args.launches):
+                case.kernel(i)
+        lib.tq_sync()
+        print(json.dumps({"case": args.case, "launches": args.launches, "device_error": lib.tq_last_error()}))
+        return
+
+    # ---- headline: cfg2 -------------------------------------------------------------------
+    head, head_kernel, _ = build_cases(ctx, {"cfg2"})["cfg2"]
+    oracle_diff = head.oracle_diff()
+    for i in range(args.warmup):
+        head.run(i, 0, 0)
+    ms = ctx.time_loop(lambda i: head.run(i, 0, 0), args.steps, warmup=0)
+    value = head.weight_bytes / (ms * 1e-3) / 1e9
+    head.stage(0)
+    k_ms = ctx.time_loop(lambda i: head.kernel(i), max(args.steps, 200), warmup=args.warmup)
+    roof = hbm_record(ctx, head, head_kernel, k_ms)
+    if NCU_TRAFFIC["bytes_per_launch"]:
+        roof["traffic"] = NCU_TRAFFIC["bytes_per_launch"]
+        roof["traffic_source"] = NCU_TRAFFIC["capture"]
+    e_iters = max(min(args.steps, 2000), 50)
+    e_s, e_diff = e2e_loop(ctx, head, e_iters, warmup=args.warmup)
+    cpu = None
+    if cpu_on:
+        cpu = cpu_sample(head.cpu_pass_fn(I_FF), head.weight_bytes / 1e9, 10.0, UNIT, "full pass of cfg2")
+    head_keep = head          # keep the buffers alive until the line is printed
+
+    # ---- every other configuration ------------------------------------------------------
+    per = []
+    peak_i8 = int8_peak_tops(ctx)
+    if not args.headline_only:
+        for name in PER_CONFIG:
+            cases = build_cases(ctx, {name})
+            case, kname, bound = cases[name]
+            it = 300 if bound == "hbm" else 6
+            eit = 300 if bound == "hbm" else 4
+            if bound == "hbm":
+                rows = case.M if case.T <= 8 else max(16, case.M * 8 // case.T // 16 * 16)
+                units = case.weight_bytes * rows / case.M / 1e9
+                what = f"{rows} of {case.M} rows, T={case.T}"
+                rec = run_case(ctx, case, kname, it, eit, 2.0 if cpu_on else 0, rows, cpu_units=units,
+                               cpu_what=what)
+            else:
+                rows, toks = 256, 256
+                units = 2.0 * toks * rows * case.K / 1e12
+                rec = run_case(ctx, case, kname, it, eit, 2.0 if cpu_on else 0, rows, bound="tensor",
+                               int8_peak=peak_i8, check=False, cpu_units=units,
+                               cpu_what=f"{rows} rows x {toks} tokens")
+            per.append(rec)
+            del case, cases
+        # cfg5 on one GPU
+        st = Stack(ctx, layers=args.layers)
+        st.capture()
+        st_ms = ctx.time_loop(lambda i: st.run(i, 0, 0), 20)
+        st.mode = "pertoken"
+        st.algo_bytes = st.weight_bytes
+        s5, d5 = e2e_loop(ctx, st, 20)
+        rec5 = {"name": "cfg5_tp1", "T": 8, "mode": "pertoken", "layers": st.L, "us": st_ms * 1e3,
+                "launches_per_step": st.launches_per_step, "value": st.weight_bytes / (st_ms * 1e-3) / 1e9,
+                "unit": UNIT,
+                "roofline": {"bound": "hbm", "achieved": st.weight_bytes / (st_ms * 1e-3) / 1e9,
+                             "peak": ctx.peak_hbm, "unit": "GB/s",
+                             "frac": st.weight_bytes / (st_ms * 1e-3) / 1e9 / ctx.peak_hbm,
+                             "peak_source": f"{ctx.peak_kind} copy bandwidth",
+                             "kernel": "whole step (CUDA graph of 10 launches per layer)",
+                             "algorithmic_bytes_per_launch": int(st.weight_bytes), "traffic": None},
+                "e2e": {"value": st.weight_bytes / s5 / 1e9, "unit": UNIT, "us_per_step": s5 * 1e6,
+                        "h2d_bytes_per_step": int(st.x_host.nbytes), "d2h_bytes_per_step": int(st.out_bytes),
+                        "steps": 20, "last_result_words_differing": d5}}
+        if cpu_on:
+            rec5["cpu_baseline"] = cpu_sample(st.cpu_pass_fn(), st.weight_bytes / st.L / 1e9, 3.0, UNIT,
+                                              "the five matrices of one layer")
+        per.append(rec5)
+        del st
+
+    clocks = sampler.stop(ctx.load_spans)
+    prefill = {r["name"]: r["roofline"]["achieved"] for r in per if r["name"].startswith("cfg4")}
+    out = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "s8xs4->s32, fp32 out", "data": "synthetic",
+        "config": {"workload": WORKLOAD_CFG2, "parallelism": "column shard tp1",
+                   "l2": f"inputs larger than L2: {args.rotate} rotating weight copies, "
+                         f"{args.rotate * head.weight_bytes / 1e6:.0f} MB",
+                   "step": "per-token staging (1 launch) + fused gate|up GEMM"},
+        "oracle_words_differing": oracle_diff,
+        "roofline": roof,
+        "e2e": {"value": head.weight_bytes / e_s / 1e9, "unit": UNIT, "h2d_bytes_per_step": int(head.x_host.nbytes),
+                "d2h_bytes_per_step": int(head.out_bytes), "steps": e_iters, "us_per_step": e_s * 1e6,
+                "last_result_words_differing": e_diff},
+        "gpu_launches": head.launches_per_step * args.steps,
+        "clocks": clocks,
+        "cpu_baseline": cpu,
+        "prefill_int8_TOPS": prefill.get("cfg4_pertoken_fp32"),
+        "prefill_int8_TOPS_by_mode": prefill,
+        "int8_peak": {"measured_tcgen05_kind_i8_TOPS": peak_i8, "nominal_TOPS": NOMINAL_INT8_TOPS},
+        "per_config": per,
+        "device_error": lib.tq_last_error(),
+    }
+    del head_keep
     print(json.dumps(out), flush=True)
 
 
@@ -157,366 +948,25 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--rotate", type=int, default=4)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
-                    help="N > 1: every rank holds a cfg2-sized column shard of an N-times wider "
-                         "projection (weak, default), or cfg2 itself is cut into N shards (strong)")
-    ap.add_argument("--quantiser", default="staged", choices=["fused", "staged"],
-                    help="activation quantiser as its own launch before the GEMM (the reference's "
-                         "two calls; default, faster here), or in the GEMM's prologue (one launch: "
-                         "every CTA then reads the same fp32 rows from L2 at once, which costs more "
-                         "than the staging launch it saves)")
-    ap.add_argument("--exchange", default="fused", choices=["fused", "nccl"],
-                    help="N > 1: all-gather by peer stores from the GEMM epilogue (fused) or by NCCL")
+    ap.add_argument("--headline-only", action="store_true", help="skip the per_config records")
+    ap.add_argument("--case", default=None, help="run only this case's dominant kernel (profiler target)")
+    ap.add_argument("--launches", type=int, default=3)
+    ap.add_argument("--layers", type=int, default=None, help="layers of the cfg5 stack (default 64)")
+    ap.add_argument("--scaling", default="strong", choices=["weak", "strong"])
+    ap.add_argument("--exchange", default="fused", choices=["fused", "nccl"])
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank, local_rank, world = dist_env()
     if args.impl == "reference":
-        run_reference(args, rank)
+        run_reference(args, rank, world)
         return
-
-    pkg = importlib.import_module("knivesysl-xe_b200")
-    wl = importlib.import_module("knivesysl-xe_b200.workloads")
-    lib = pkg.load()                      # raises if the CUDA library is missing
-    assert lib.tq_set_device(local_rank) == 0
-    dist = None
-    if world > 1:
-        import torch.distributed as dist   # control plane only: barrier and max-over-ranks
-        dist.init_process_group("gloo", rank=rank, world_size=world)
-        idbuf = (C.c_char * 128)()
-        if rank == 0:
-            assert lib.tq_comm_unique_id(idbuf) == 0
-        obj = [bytes(idbuf.raw)]
-        dist.broadcast_object_list(obj, src=0)
-        idbuf = C.create_string_buffer(obj[0], 128)
-        assert lib.tq_comm_init(idbuf, rank, world) == 0
-
-    # ---- inputs (same seeds on every rank; a rank keeps only its column shard) ----------
-    weak = world > 1 and args.scaling == "weak"
-    # weak: this rank's shard is a whole cfg2-sized weight pair of its own (seeded by rank), i.e.
-    # the column shard of a projection world times as wide; strong: cfg2 cut with x_w4_shard
-    host_w = [wl.make_weight_w4(N_EACH, K, seed=11 + i + (100 * rank if weak else 0), group=GROUP)
-              for i in range(2)]
-    n_shard = N_EACH if weak else N_EACH // world
-    copies = []                      # rotate x [gate, up] PackedWeight (this rank's shard)
-    for c in range(args.rotate):
-        pair = []
-        for codes, scales in host_w:
-            cc = np.roll(codes.reshape(N_EACH // 16, -1), c, axis=0).reshape(-1)
-            ss = np.roll(scales.reshape(N_EACH // 16, -1), c, axis=0).reshape(-1)
-            full = pkg.PackedWeight(cc, ss, N_EACH, K, k64=True)
-            if world > 1 and not weak:
-                sh = pkg.TqWeight()
-                assert lib.qwn_x_w4_shard(C.byref(sh), full.ref, rank, world, 0, None, 0) == 0
-                full.codes.free()
-                full.scales.free()
-                full.rec = sh
-            pair.append(full)
-        copies.append(pair)
-    warr = [pkg.weight_array(p) for p in copies]
-    x = wl.activations_normal(T, K, seed=5, outlier_frac=0.01)
-    dx = pkg.DevBuf.from_numpy(x)
-    nblk = K // 32 * T
-    aq, as_, asum, as_tok = (pkg.DevBuf(nblk * 32), pkg.DevBuf(nblk * 4), pkg.DevBuf(nblk * 4),
-                             pkg.DevBuf(T * 4))
-    # this rank's outputs [gate|up][T][n_shard], contiguous so that they are one send buffer
-    block = 2 * T * n_shard                      # floats per rank
-    ycat = pkg.DevBuf(block * 4)
-    y_ptrs = [ycat.ptr, ycat.ptr + T * n_shard * 4]
-    yarr = (C.c_void_p * 2)(*y_ptrs)
-    # gathered outputs: [2 halves][world][gate|up][T][n_shard] (NCCL uses the first half)
-    gathered = pkg.DevBuf(2 * world * block * 4) if world > 1 else None
-    fused = world > 1 and args.exchange == "fused"
-    half_off = C.c_size_t(0)
-    if world > 1:
-        flags = pkg.DevBuf(world * 4)
-        lib.tq_dev_zero(flags.ptr, world * 4)
-        handles = []
-        for buf in (gathered, flags):
-            h = (C.c_char * 64)()
-            assert lib.tq_comm_ipc_export(buf.ptr, h) == 0
-            handles.append(bytes(h.raw))
-        allh = [None] * world
-        dist.all_gather_object(allh, handles)
-        bufs, flgs = (C.c_void_p * world)(), (C.c_void_p * world)()
-        for p in range(world):
-            if p == rank:
-                bufs[p], flgs[p] = gathered.ptr, flags.ptr
-            else:
-                bufs[p] = lib.tq_comm_ipc_open(C.create_string_buffer(allh[p][0], 64))
-                flgs[p] = lib.tq_comm_ipc_open(C.create_string_buffer(allh[p][1], 64))
-                if not bufs[p] or not flgs[p]:
-                    fused = False
-        ok_all = [None] * world
-        dist.all_gather_object(ok_all, bool(fused))
-        fused = all(ok_all)                      # every rank takes the same path
-        if fused:
-            assert lib.tq_comm_gather_setup(bufs, flgs, world, rank) == 0
-
-    xin = [dx.ptr]       # the fp32 activations the step reads (the end-to-end loop alternates two)
-
-    def stage():
-        lib.qwn_x_quantize_act_chunk_pertoken(xin[0], K, T, aq.ptr, as_.ptr, asum.ptr, as_tok.ptr)
-
-    def gemm(i):
-        rc = lib.qwn_x_gemm_w4a8_fanout(warr[i % args.rotate], yarr, 2, aq.ptr, as_.ptr, asum.ptr, T,
-                                        None, 0)
-        assert rc == 0, rc
-
-    def gemm_gathered(i):
-        rc = lib.qwn_x_gemm_w4a8_fanout_gathered(warr[i % args.rotate], 2, aq.ptr, as_.ptr, asum.ptr,
-                                                 T, C.byref(half_off))
-        assert rc == 0, rc
-        assert lib.tq_comm_gather_wait() == 0
-
-    # The step a user runs: ONE call that quantises the fp32 activations per token in the GEMM
-    # kernel's prologue, multiplies gate|up and (N > 1) gathers the ranks' slices.
-    qfused = args.quantiser == "fused"
-
-    def gemm_fused(i, out=None):
-        if qfused:
-            rc = lib.qwn_x_gemm_w4a8_fanout_fused(warr[i % args.rotate], out or yarr, 2, xin[0], T, 1)
-        else:
-            stage()
-            rc = lib.qwn_x_gemm_w4a8_fanout(warr[i % args.rotate], out or yarr, 2, aq.ptr, as_.ptr,
-                                            asum.ptr, T, None, 0)
-        assert rc == 0, rc
-
-    def step(i):
-        if fused and qfused:
-            rc = lib.qwn_x_gemm_w4a8_fanout_gathered_fused(warr[i % args.rotate], 2, xin[0], T, 1,
-                                                           C.byref(half_off))
-            assert rc == 0, rc
-        elif fused:
-            stage()
-            gemm_gathered(i)
-        else:
-            gemm_fused(i)
-            if world > 1:
-                assert lib.tq_comm_allgather(ycat.ptr, gathered.ptr, ycat.nbytes) == 0
-
-    if fused:
-        # the fused gather must deliver exactly what NCCL delivers, on every weight copy and
-        # on both halves of the gathered buffer
-        stage()
-        for i in range(2 * args.rotate):
-            gemm(i)
-            assert lib.tq_comm_allgather(ycat.ptr, gathered.ptr, ycat.nbytes) == 0
-            lib.tq_sync()
-            ref = gathered.to_numpy(np.float32)[: world * block].copy()
-            dist.barrier()
-            step(i)                  # fused quantiser + GEMM + peer-store gather
-            lib.tq_sync()
-            dist.barrier()
-            got = gathered.to_numpy(np.float32)[half_off.value: half_off.value + world * block]
-            assert got.tobytes() == ref.tobytes(), f"fused all-gather differs from NCCL (step {i})"
-            dist.barrier()
-
-    def barrier():
-        lib.tq_sync()
-        if dist:
-            dist.barrier()
-
-    ev = [lib.tq_event_create() for _ in range(2)]
-    sampler = ClockSampler(local_rank) if rank == 0 else None
-    t_load0 = time.time()
-
-    # ---- timed region: whole steps ----------------------------------------------------
-    for i in range(args.warmup):
-        step(i)
-    barrier()
-    lib.tq_event_record(ev[0])
-    for i in range(args.steps):
-        step(i)
-    lib.tq_event_record(ev[1])
-    barrier()
-    ms = lib.tq_event_elapsed_ms(ev[0], ev[1])
-    if dist:
-        import torch
-        tt = torch.tensor([ms], dtype=torch.float64)
-        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        ms = float(tt.item())
-    # weight bytes the whole job streams per step (all ranks)
-    full_weight_bytes = 2 * wl.weight_bytes(N_EACH, K, GROUP) * (world if weak else 1)
-    value = full_weight_bytes * args.steps / (ms * 1e-3) / 1e9
-
-    # ---- dominant kernel alone (this rank's shard), for the roofline -----------------------
-    stage()
-    alone = gemm_fused if qfused else gemm      # staged: the GEMM launch without its staging
-    for i in range(args.warmup):
-        alone(i)
-    lib.tq_sync()
-    k_iters = max(args.steps, 200)
-    lib.tq_event_record(ev[0])
-    for i in range(k_iters):
-        alone(i)
-    lib.tq_event_record(ev[1])
-    lib.tq_sync()
-    k_ms = lib.tq_event_elapsed_ms(ev[0], ev[1]) / k_iters
-    if fused:
-        # diagnostic (stderr): the gathered GEMM with its wait kernel, back to back
-        barrier()
-        lib.tq_event_record(ev[0])
-        for i in range(k_iters):
-            step(i)
-        lib.tq_event_record(ev[1])
-        barrier()
-        g_ms = lib.tq_event_elapsed_ms(ev[0], ev[1]) / k_iters
-        if rank == 0:
-            print(f"[bench] GEMM alone {k_ms * 1e3:.2f} us; gathered GEMM + wait {g_ms * 1e3:.2f} us; "
-                  f"step {ms / args.steps * 1e3:.2f} us", file=sys.stderr)
-    shard_weight = 2 * wl.weight_bytes(n_shard, K, GROUP)
-    # weights + the fp32 activation rows the prologue quantises + the fp32 outputs
-    algo_bytes = shard_weight + (T * K * 4 if qfused else T * K + nblk * 8) + block * 4
-    achieved = algo_bytes / (k_ms * 1e-3) / 1e9
-    peak, peak_kind = measured_peaks()
-
-    # ---- end to end through the C-ABI with host buffers ----------------------------------
-    hx = lib.tq_host_alloc_pinned(x.nbytes)
-    C.memmove(hx, x.ctypes.data, x.nbytes)
-    # strong: every rank reads the whole gathered result back; weak: a rank reads back its own
-    # slice of the gathered buffer, so the host receives the (world times larger) result once
-    out_bytes = (block * 4 if weak else world * block * 4 if world > 1 else ycat.nbytes)
-    hy = [lib.tq_host_alloc_pinned(out_bytes) for _ in range(2)]
-    # Two output buffers: the read-back of step i (second stream) overlaps step i+1, and the
-    # library stream waits for it only before step i+2 overwrites the same buffer.
-    ycat2 = pkg.DevBuf(block * 4)
-    yarr2 = (C.c_void_p * 2)(ycat2.ptr, ycat2.ptr + T * n_shard * 4)
-    tickets = [-1, -1]
-    # Two input buffers as well: step n+1's activations come up from pinned host memory on a
-    # third stream while step n computes (one upload per step; the first is queued before the
-    # timed loop and the last step's upload is the one nothing reads).
-    dx2 = pkg.DevBuf(x.nbytes)
-    xbuf = [dx.ptr, dx2.ptr]
-    up = [lib.tq_h2d_overlapped(xbuf[0], hx, x.nbytes), -1]
-    count = [0]
-    e2e_src = [None]
-
-    def e2e_step(i):
-        n = count[0]
-        count[0] = n + 1
-        # N > 1, strong: this rank's next flag tells its peers that they may overwrite the half
-        # it is still reading back, so there the previous read-back must finish before the next
-        # step. Weak with the fused gather: a rank reads back its own slice only, which no peer
-        # writes, so as at N = 1 the read-back of step n must only be over before step n+2
-        # writes the same half (NCCL's gather has one buffer, rewritten whole every step).
-        b = n & 1 if (world == 1 or (weak and fused)) else 0
-        if tickets[b] >= 0:
-            lib.tq_stream_wait_copy(tickets[b])
-        # the other input buffer was last read by step n-1, which is queued already
-        up[(n + 1) & 1] = lib.tq_h2d_overlapped(xbuf[(n + 1) & 1], hx, x.nbytes)
-        lib.tq_stream_wait_copy(up[n & 1])
-        xin[0] = xbuf[n & 1]
-        if world == 1:
-            gemm_fused(i, yarr2 if b else yarr)
-            src = (ycat2 if b else ycat).ptr
-        else:
-            step(i)
-            src = gathered.ptr + ((half_off.value if fused else 0) + (rank * block if weak else 0)) * 4
-        tickets[b] = lib.tq_d2h_overlapped(hy[n & 1], src, out_bytes)
-        e2e_src[0] = (src, i, n & 1)
-        assert tickets[b] >= 0 and up[(n + 1) & 1] >= 0
-
-    e_iters = max(min(args.steps, 2000), 50)
-    for i in range(args.warmup):
-        e2e_step(i)
-    barrier()
-    t0 = time.perf_counter()
-    for i in range(e_iters):
-        e2e_step(i)
-    lib.tq_sync()
-    e_s = time.perf_counter() - t0
-    xin[0] = dx.ptr
-    # what the host received in the last step is what the device holds; at N = 1 the step is
-    # also run again from the input buffer that was uploaded synchronously at the start
-    src, last, lb = e2e_src[0]
-    got = np.ctypeslib.as_array(C.cast(hy[lb], C.POINTER(C.c_float)), shape=(out_bytes // 4,)).copy()
     if world == 1:
-        gemm_fused(last, yarr2 if lb else yarr)
-        want = (ycat2 if lb else ycat).to_numpy(np.float32, out_bytes // 4)
-    else:
-        want = np.empty(out_bytes // 4, dtype=np.float32)
-        lib.tq_d2h(want.ctypes.data, src, out_bytes)
-    e2e_diff = int(np.count_nonzero(got.view(np.uint32) != want.view(np.uint32)))
-    if e2e_diff:
-        print(f"[bench] rank {rank}: the end-to-end loop's last result differs from the device's in "
-              f"{e2e_diff} of {got.size} words", file=sys.stderr)
-    if dist:
-        import torch
-        tt = torch.tensor([e_s], dtype=torch.float64)
-        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        e_s = float(tt.item())
-    e2e_val = full_weight_bytes * e_iters / e_s / 1e9
-    t_load1 = time.time()
-    if sampler and (t_load1 - t_load0) < 0.6:
-        # too short for nvidia-smi's sampling period: keep the same kernels running a little
-        tend = time.time() + 0.6
-        i = 0
-        while time.time() < tend:
-            gemm_fused(i)
-            i += 1
-            if i % 256 == 0:
-                lib.tq_sync()
-        lib.tq_sync()
-        t_load1 = time.time()
-    clocks = sampler.stop(t_load0, t_load1) if sampler else None
-    err = lib.tq_last_error()
-
-    # ---- CPU baseline (rank 0, N = 1 only) ----------------------------------------------------
-    cpu = None
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        from oracle import oracle as orc
-        orc.set_num_threads(len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity")
-                            else (os.cpu_count() or 1))
-        oq, os_, osm = orc.quantize_act_chunk(x, per_token=True)
-        cpu_pass(orc, host_w, oq, os_, osm)      # warm
-        passes, t0 = 0, time.perf_counter()
-        while time.perf_counter() - t0 < 12.0:
-            orc.quantize_act_chunk(x, per_token=True)
-            cpu_pass(orc, host_w, oq, os_, osm)
-            passes += 1
-        dt = time.perf_counter() - t0
-        cpu = {"value": full_weight_bytes * passes / dt / 1e9, "unit": UNIT, "cores": orc.num_threads(),
-               "kind": "port", "sample": f"{passes} full passes of cfg2 in {dt:.1f} s (OpenMP, all host threads)"}
-
-    if rank == 0:
-        out = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
-            "scaling": "weak" if (weak or world == 1) else "strong", "vs_baseline": None,
-            "dtype": "s8xs4->s32, fp32 out",
-            "data": "synthetic",
-            "config": {"workload": "cfg2: batched decode fused gate+up, K64 scale tier, T=8, K=5120, "
-                                   "N=2x17408, int8 per-token activations" +
-                                   (f"; one cfg2-sized column shard per GPU (N={world}x2x17408 in all)"
-                                    if weak else ""),
-                       "parallelism": f"column shard tp{world}" + (
-                           "" if world == 1 else " + all-gather by peer stores from the GEMM epilogue"
-                           if fused else " + NCCL all-gather"),
-                       "l2": f"inputs larger than L2: {args.rotate} rotating weight copies, "
-                             f"{args.rotate * shard_weight / 1e6:.0f} MB per GPU",
-                       "step": ("one launch: per-token activation quantiser in the prologue of the "
-                                "fused gate|up GEMM" if qfused else
-                                "per-token staging (1 launch) + fused gate|up GEMM") +
-                               (" + all-gather" if world > 1 else "")},
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "peak_source": f"{peak_kind} copy bandwidth",
-                         "kernel": "gemm_w4a8_ring_kernel", "us_per_launch": k_ms * 1e3,
-                         "algorithmic_bytes_per_launch": algo_bytes,
-                         # the capture is of the whole-cfg2 launch; a shard's traffic scales with it
-                         "traffic": int(NCU_TRAFFIC_BYTES_PER_LAUNCH * algo_bytes / 95_977_472)},
-            "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": int(x.nbytes),
-                    "d2h_bytes_per_step": int(out_bytes), "steps": e_iters,
-                    "us_per_step": e_s / e_iters * 1e6,
-                    "last_result_words_differing": e2e_diff},
-            "gpu_launches": ((1 if qfused else 2) + (1 if fused else 0) + (1 if world > 1 and not fused else 0)) * args.steps,
-            "clocks": clocks,
-            "cpu_baseline": cpu,
-            "device_error": err,
-        }
-        print(json.dumps(out), flush=True)
-    if world > 1:
-        lib.tq_comm_destroy()
-        dist.destroy_process_group()
+        run_single(args)
+        return
+    multi = importlib.import_module("bench_multi") if os.path.exists(os.path.join(ROOT, "bench_multi.py")) else None
+    if multi is None:
+        raise SystemExit("multi-GPU bench module missing")
+    multi.run(args, rank, local_rank, world)
 
 
 if __name__ == "__main__":

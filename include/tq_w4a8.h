@@ -249,6 +249,16 @@ void qwn_x_silu_mul_quant_pertoken(float *d_out, const float *d_gate, const floa
  * bfloat16 instead of fp32. Returns like x_gemm_w4a8. */
 int qwn_x_gemm_w4a8_pertoken(const tq_qmma_weight_t *w, const int8_t *d_aq, const float *d_as_tok,
                              const int32_t *d_asum, void *d_y, int T, int out_bf16);
+/* The same arithmetic for decode batches (T < 128, fp32 out), up to 4 weights that share the
+ * staged codes in one launch (gate|up). Each weight is cut into the split count x_gemm_w4a8
+ * gives it (choose_gemm_splits), a split covering whole weight-scale groups
+ * [G*s/S, G*(s+1)/S) of the G = K/32 (K32) or K/64 (K64) groups; y = ((0 + p_0) + ... + p_S-1)
+ * * as_tok with p_s the split's fma chain (an unsplit weight: y = acc * as_tok).
+ * x_gemm_w4a8_pertoken routes here below 128 tokens. Returns -3 for shapes outside 8..64
+ * tokens. */
+int qwn_x_gemm_w4a8_fanout_pertoken(const tq_qmma_weight_t *const *ws, float *const *ys, int count,
+                                    const int8_t *d_aq, const float *d_as_tok, const int32_t *d_asum,
+                                    int T);
 
 /* W4A4, the tier the reference runs K64 weights at in prefill (x_quantize_act_chunk_s4 and
  * x_gemm_w4a4, xpu/src/kernels_dpas.cpp:1495-1571). Staging: one block per (token, 64
@@ -279,6 +289,15 @@ double qwn_gemm_bench(const tq_qmma_weight_t *w, int tokens, int iters);  /* us 
 int qwn_gemm_check(const tq_qmma_weight_t *w, int tokens, double *worst_cos, double *worst_rel);
 int qwn_specwave_check(const tq_qmma_weight_t *w);
 int qwn_shard_check(const tq_qmma_weight_t *w, int tp);
+
+/* Issue-rate measurement of tcgen05.mma kind::i8 (M128 x N x K32, int32 accumulators in TMEM,
+ * no epilogue) on every SM: the measured dense int8 peak in TOP/s that the prefill GEMM's
+ * fractions are quoted against. qwn_tc_int8_probe takes the MMA width n (16..256, multiple of
+ * 16), the queue length and the number of accumulators used in turn, and can return SM 0's
+ * {issue clocks, clocks to completion}. The reference measures its own roofs with standalone
+ * probes (xpu/probe/dpas_probe.cpp); this is the B200 counterpart. */
+double qwn_tc_int8_peak(int iters);
+double qwn_tc_int8_probe(int n, int iters, int accs, long long *clocks_out);
 
 /* No counterpart in the reference. Same result as qwn_x_gemv_w4a8, for callers that must
  * not trigger a device allocation (pre-allocated serving loops, callers whose memory pool
@@ -380,6 +399,9 @@ void x_quantize_act_chunk_pertoken(const float *d_x, int K, int T, int8_t *d_aq,
                                    int32_t *d_asum, float *d_as_tok);
 int x_gemm_w4a8_pertoken(const tq_qmma_weight_t *w, const int8_t *d_aq, const float *d_as_tok,
                          const int32_t *d_asum, void *d_y, int T, int out_bf16 = 0);
+int x_gemm_w4a8_fanout_pertoken(const tq_qmma_weight_t *const *ws, float *const *ys, int count,
+                                const int8_t *d_aq, const float *d_as_tok, const int32_t *d_asum,
+                                int T);
 void x_prepare_gemv_act_s8_pertoken(const float *d_x, int K);
 void x_silu_mul_quant_pertoken(float *d_out, const float *d_gate, const float *d_up, int K);
 int x_w8_repack_weight(tq_qmma_weight_t *w);

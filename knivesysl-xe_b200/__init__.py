@@ -87,6 +87,7 @@ SIGNATURES = {
                                     C.POINTER(_i), _i]),
     "qwn_x_quantize_act_chunk_pertoken": (None, [_vp, _i, _i, _vp, _vp, _vp, _vp]),
     "qwn_x_gemm_w4a8_pertoken": (_i, [_WP, _vp, _vp, _vp, _vp, _i, _i]),
+    "qwn_x_gemm_w4a8_fanout_pertoken": (_i, [C.POINTER(_WP), C.POINTER(_vp), _i, _vp, _vp, _vp, _i]),
     "qwn_x_quantize_act_chunk_s4": (None, [_vp, _i, _i, _vp, _vp, _vp]),
     "qwn_x_rmsnorm_chunk": (None, [_vp, _vp, _vp, _i, _i, C.c_float]),
     "qwn_x_gemm_w4a4": (_i, [_WP, _vp, _vp, _vp, _vp, _i]),
@@ -97,6 +98,7 @@ SIGNATURES = {
     "qwn_gemm_check": (_i, [_WP, _i, C.POINTER(_d), C.POINTER(_d)]),
     "qwn_specwave_check": (_i, [_WP]), "qwn_shard_check": (_i, [_WP, _i]),
     "qwn_x_gemv_w4a8_static": (_i, [_WP, _vp, _vp]), "qwn_static_max_k": (_i, []),
+    "qwn_tc_int8_peak": (_d, [_i]), "qwn_tc_int8_probe": (_d, [_i, _i, _i, _vp]),
     "tq_comm_unique_id": (_i, [_vp]), "tq_comm_init": (_i, [_vp, _i, _i]),
     "tq_comm_allgather": (_i, [_vp, _vp, _sz]),
     "tq_comm_allreduce_sum": (_i, [_vp, _vp, _sz]),

@@ -140,18 +140,43 @@ struct GemmArgs {
     // is published by launch_gather_publish (comm.cu) after the GEMM.
     int npeer;
     float *ypeer[8][4];
+    // Per-token activation scales (tcgen05 decode kernel only): mode 1 reads as_tok[T] and
+    // asum, promotes once per weight-scale group and multiplies by as_tok at the end.
+    int mode;
+    const float *as_tok;
+    // Row stride of y / ypeer in floats (0 = M): a column shard that writes its slice of a
+    // wider [T][ld] matrix.
+    int ld[4];
 };
 void launch_gemm_mma(const GemmArgs &a);
 // gemm_stream.cu (decode batches: one segment, T <= 64, uniform split count <= 8)
 bool gemm_stream_covers(const GemmArgs &a);
 bool gemm_ring_covers(const GemmArgs &a);     // the T = 8 ring kernel takes the call
 void launch_gemm_stream(const GemmArgs &a);
-// Picks the streaming kernel when it covers the call, else the general mma kernel.
-inline void launch_gemm(const GemmArgs &a) {
-    if (gemm_stream_covers(a))
+// gemm_dtc.cu (decode batches on tcgen05: one segment per weight, 8 <= T <= 64)
+bool gemm_dtc_covers(const GemmArgs &a);
+void launch_gemm_dtc(const GemmArgs &a);
+bool decode_prefers_mma();   // TQ_XPU_DECODE_MMA=1: keep decode batches on the mma.sync kernels
+int decode_dtc_min_tokens(); // fewest tokens the tcgen05 decode kernel takes (16; TQ_XPU_DTC_MIN_TOKENS)
+// Decode batches: 8 tokens stay on the mma.sync ring kernel (a tcgen05.mma of kind::i8 takes
+// the same 152 clocks whatever its N, which caps a 128-row x K32 MMA per 2 KB of packed
+// weights at 0.58 of the HBM roofline; the ring kernel is above that), 16..64 tokens go to
+// the tcgen05 decode kernel, everything else to the general mma kernel. Per-token calls
+// (mode 1) exist on the ring and the tcgen05 kernels only; returns false when neither takes
+// the call.
+inline bool launch_gemm(const GemmArgs &a) {
+    const bool dtc = gemm_dtc_covers(a) && !decode_prefers_mma();
+    if (dtc && a.T >= decode_dtc_min_tokens()) {
+        launch_gemm_dtc(a);
+    } else if (a.mode ? gemm_ring_covers(a) : gemm_stream_covers(a)) {
         launch_gemm_stream(a);
-    else
+    } else if (a.mode) {
+        if (!gemm_dtc_covers(a)) return false;
+        launch_gemm_dtc(a);
+    } else {
         launch_gemm_mma(a);
+    }
+    return true;
 }
 
 // gemm_tc.cu (tcgen05 path, unsplit, per-token or per-block scales)

@@ -42,6 +42,23 @@ int choose_gemm_splits(int rgroups, int tgroups, int ktiles) {
     return s;
 }
 
+bool decode_prefers_mma() {
+    static const int v = [] {
+        const char *e = getenv("TQ_XPU_DECODE_MMA");
+        return (e && *e && *e != '0') ? 1 : 0;
+    }();
+    return v != 0;
+}
+
+int decode_dtc_min_tokens() {
+    static const int v = [] {
+        const char *e = getenv("TQ_XPU_DTC_MIN_TOKENS");
+        const int n = (e && *e) ? atoi(e) : 16;
+        return n < 8 ? 8 : n;
+    }();
+    return v;
+}
+
 namespace {
 
 bool w4_usable(const tq_qmma_weight_t *w) {
@@ -536,6 +553,29 @@ int x_gemm_w4a8_fanout_gathered_fused(const tq_qmma_weight_t *const *ws, int cou
     return gathered_impl(ws, count, nullptr, nullptr, nullptr, d_x, per_token, T, half_offset_floats);
 }
 
+// Per-token activation scales for decode batches (T < 128): several weights that share the
+// staged codes, one launch on the tcgen05 decode kernel. Each weight is split like
+// x_gemm_w4a8 splits it (choose_gemm_splits), the splits cutting whole weight-scale groups.
+int x_gemm_w4a8_fanout_pertoken(const tq_qmma_weight_t *const *ws, float *const *ys, int count,
+                                const int8_t *d_aq, const float *d_as_tok, const int32_t *d_asum,
+                                int T) {
+    if (!ys) return -1;
+    GemmArgs a{};
+    const int rc = fanout_args(a, ws, count, T, nullptr, 0);
+    if (rc) return rc;
+    if (!d_aq || !d_as_tok || !d_asum) return -2;
+    for (int i = 0; i < count; ++i) {
+        if (!ys[i]) return -2;
+        a.y[i] = ys[i];
+    }
+    a.aq = d_aq;
+    a.asum = d_asum;
+    a.as_tok = d_as_tok;
+    a.mode = 1;
+    if (a.T > 64) return -3;
+    return launch_gemm(a) ? 0 : -3;
+}
+
 int x_gemm_w4a8(const tq_qmma_weight_t *w, const int8_t *d_aq, const float *d_as,
                 const int32_t *d_asum, float *d_y, int T, const int *offsets, int segments) {
     if (!w || !w->s4_ready || w->s4_k16 || !w->d_s4 || !w->d_s4_scale) return -1;
@@ -567,8 +607,11 @@ int x_gemm_w4a8_pertoken(const tq_qmma_weight_t *w, const int8_t *d_aq, const fl
     t.codes = w->d_s4; t.scales = w->d_s4_scale; t.aq = d_aq; t.as = nullptr;
     t.as_tok = d_as_tok; t.asum = d_asum; t.y = d_y; t.M = w->M; t.K = w->K;
     t.ksh = w->s4_k64 ? 1 : 0; t.T = T; t.out_bf16 = out_bf16;
-    const int rc = launch_gemm_tc(t);
-    return rc == 0 ? 0 : -3;   // -3: shape not covered by the per-token kernel
+    if (launch_gemm_tc(t) == 0) return 0;
+    if (out_bf16) return -3;   // decode batches store fp32
+    const tq_qmma_weight_t *ws[1] = {w};
+    float *ys[1] = {static_cast<float *>(d_y)};
+    return x_gemm_w4a8_fanout_pertoken(ws, ys, 1, d_aq, d_as_tok, d_asum, T);
 }
 
 // xpu/src/kernels_dpas.cpp:1124-1144: (1+w) RMSNorm of a chunk of token rows.
@@ -801,6 +844,11 @@ void qwn_x_quantize_act_chunk_pertoken(const float *d_x, int K, int T, int8_t *d
 int qwn_x_gemm_w4a8_pertoken(const tq_qmma_weight_t *w, const int8_t *d_aq, const float *d_as_tok,
                              const int32_t *d_asum, void *d_y, int T, int out_bf16) {
     return x_gemm_w4a8_pertoken(w, d_aq, d_as_tok, d_asum, d_y, T, out_bf16);
+}
+int qwn_x_gemm_w4a8_fanout_pertoken(const tq_qmma_weight_t *const *ws, float *const *ys, int count,
+                                    const int8_t *d_aq, const float *d_as_tok, const int32_t *d_asum,
+                                    int T) {
+    return x_gemm_w4a8_fanout_pertoken(ws, ys, count, d_aq, d_as_tok, d_asum, T);
 }
 
 void qwn_x_rmsnorm_chunk(float *d_out, const float *d_in, const uint16_t *d_w, int H, int T,

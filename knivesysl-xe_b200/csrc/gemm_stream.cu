@@ -451,7 +451,11 @@ __device__ __forceinline__ void scale_pair(uint32_t packed, float &ws, float &z8
 // PAIR: K64 tier and even split starts - tiles 2j, 2j+1 share a scale line. kRNS: ring stages
 // per warp (2 with all 32 warps; more when the call has fewer tasks than warp slots).
 // MAXW: most warps the instantiation is launched with (fewer warps leave it more registers).
-template <bool PAIR, int kRNS, int MAXW>
+// PT: per-token activation scales (a.as_tok): one promote per weight-scale group -
+// acc = fma((float)(d - z*asum), ws, acc) with d the int32 dot of the whole group (both k-tiles
+// of a K64 group chained through the MMA's accumulator input) - splits cut whole groups, and
+// the per-token scale multiplies the sum of the splits at the end.
+template <bool PAIR, int kRNS, int MAXW, bool PT>
 __global__ void __launch_bounds__(MAXW * 32, 1)
 gemm_w4a8_ring_kernel(const GemmArgs a, float *__restrict__ part, int *__restrict__ count) {
     extern __shared__ __align__(128) unsigned char smem[];
@@ -471,8 +475,8 @@ gemm_w4a8_ring_kernel(const GemmArgs a, float *__restrict__ part, int *__restric
     const int Kt = a.K >> 5;
     const int ksh = a.ksh;
     const int Ktg = Kt >> ksh;
-    const int kt_begin = Kt * split / S;
-    const int cnt = Kt * (split + 1) / S - kt_begin;
+    const int kt_begin = PT ? ((Ktg * split / S) << ksh) : Kt * split / S;
+    const int cnt = (PT ? ((Ktg * (split + 1) / S) << ksh) : Kt * (split + 1) / S) - kt_begin;
     // token window of this CTA column: tokens [tok0, tok0 + 8) of the call's Ttot
     const int win = blockIdx.y, tok0 = win * 8, Ttot = a.T;
 
@@ -620,8 +624,14 @@ gemm_w4a8_ring_kernel(const GemmArgs a, float *__restrict__ part, int *__restric
             const int kl = i >> 2;
             const int rem = i & 3;
             const size_t src = (size_t)(kt_begin + kl) * Ttot + tok0 + (size_t)rem * 2;
-            const float2 as2 = __ldg(reinterpret_cast<const float2 *>(a.as + src));
-            const int2 sm2 = __ldg(reinterpret_cast<const int2 *>(a.asum + src));
+            float2 as2 = make_float2(0.f, 0.f);
+            if (!PT) as2 = __ldg(reinterpret_cast<const float2 *>(a.as + src));
+            int2 sm2 = __ldg(reinterpret_cast<const int2 *>(a.asum + src));
+            if (PT && PAIR && !(kl & 1) && kl + 1 < cnt) {      // the K64 group's sum, with its first tile
+                const int2 nx = __ldg(reinterpret_cast<const int2 *>(a.asum + src + Ttot));
+                sm2.x += nx.x;
+                sm2.y += nx.y;
+            }
             *reinterpret_cast<float4 *>(act + (size_t)kl * kActTileBytes + 256 + rem * 16) =
                 make_float4(as2.x, as2.y, -(float)sm2.x, -(float)sm2.y);
         }
@@ -650,8 +660,29 @@ gemm_w4a8_ring_kernel(const GemmArgs a, float *__restrict__ part, int *__restric
         // (float)(d - z*asum) = (z+8) * (-asum) + d', exact: all integers below 2^24
         const f32x2 f01 = fma2(pack2(nz0, nz0), av.y, add2(pack2i(d[0], d[1]), neg_magic2));
         const f32x2 f23 = fma2(pack2(nz1, nz1), av.y, add2(pack2i(d[2], d[3]), neg_magic2));
-        fma2_acc(acc01, f01, mul2(pack2(ws0, ws0), av.x));
-        fma2_acc(acc23, f23, mul2(pack2(ws1, ws1), av.x));
+        if (PT) {
+            fma2_acc(acc01, f01, pack2(ws0, ws0));
+            fma2_acc(acc23, f23, pack2(ws1, ws1));
+        } else {
+            fma2_acc(acc01, f01, mul2(pack2(ws0, ws0), av.x));
+            fma2_acc(acc23, f23, mul2(pack2(ws1, ws1), av.x));
+        }
+    };
+    // both tiles of a K64 group against per-token scales: one int32 dot, one promote
+    auto tile_group = [&](uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3, float ws0, float nz0, float ws1,
+                          float nz1, uint32_t bb_addr, uint32_t vb_addr, bool second) {
+        const uint2 bb = lds_v2(bb_addr);
+        const ulonglong2 av = lds_v2u64(vb_addr);
+        int d[4];
+        mma_s8_c(d, nib_plus8(w0), nib_plus8(w1), nib_plus8(w0 >> 4), nib_plus8(w1 >> 4), bb.x, bb.y, cmagic);
+        if (second) {
+            const uint2 bb2 = lds_v2(bb_addr + kActTileBytes);
+            mma_s8_acc(d, nib_plus8(w2), nib_plus8(w3), nib_plus8(w2 >> 4), nib_plus8(w3 >> 4), bb2.x, bb2.y);
+        }
+        const f32x2 f01 = fma2(pack2(nz0, nz0), av.y, add2(pack2i(d[0], d[1]), neg_magic2));
+        const f32x2 f23 = fma2(pack2(nz1, nz1), av.y, add2(pack2i(d[2], d[3]), neg_magic2));
+        fma2_acc(acc01, f01, pack2(ws0, ws0));
+        fma2_acc(acc23, f23, pack2(ws1, ws1));
     };
     // tiles 2j, 2j+1 of the stage at `cst`; activations of the first one at offset kl_off
     auto tile_pair = [&](uint32_t ab, uint32_t sb, uint32_t bbase, uint32_t vbase, bool second) {
@@ -660,6 +691,10 @@ gemm_w4a8_ring_kernel(const GemmArgs a, float *__restrict__ part, int *__restric
         float ws0, ws1, nz0, nz1;
         scale_pair(lds_u16(sb), ws0, nz0);
         scale_pair(lds_u16(sb + 16), ws1, nz1);
+        if (PT && PAIR) {
+            tile_group(w0, w1, w2, w3, ws0, nz0, ws1, nz1, bbase, vbase, second);
+            return;
+        }
         tile(w0, w1, ws0, nz0, ws1, nz1, bbase, vbase);
         if (second) {
             if (!PAIR) {
@@ -724,6 +759,13 @@ gemm_w4a8_ring_kernel(const GemmArgs a, float *__restrict__ part, int *__restric
                 out[k] = sum;
             }
             if (lane == 0) count[slot] = 0;   // ready for the next launch
+        }
+        if (PT) {
+            const float2 at = __ldg(reinterpret_cast<const float2 *>(a.as_tok + tok0 + 2 * c));
+            out[0] = __fmul_rn(out[0], at.x);
+            out[1] = __fmul_rn(out[1], at.y);
+            out[2] = __fmul_rn(out[2], at.x);
+            out[3] = __fmul_rn(out[3], at.y);
         }
         const size_t row = (size_t)lg * 16 + r;
         if (!a.npeer) {
@@ -873,7 +915,7 @@ struct RingPlan {
 };
 bool ring_plan(const GemmArgs &a, RingPlan &p) {
     if (a.T < 8 || a.T > 64 || (a.T % 8) || a.dump) return false;
-    if (a.x && a.T != 8) return false;        // the fused quantiser serves one window
+    if (a.x && (a.T != 8 || a.mode)) return false;   // the fused quantiser serves one window
     p.nwin = a.T / 8;                         // token windows: CTA columns (grid.y)
     if (!g_num_sms) {
         int dev = 0;
@@ -893,8 +935,10 @@ bool ring_plan(const GemmArgs &a, RingPlan &p) {
     const int per_cta = (groups + p.grid / S - 1) / (p.grid / S);      // tasks of the busiest CTA
     p.nw = kRW;
     if (per_cta < kRW) p.nw = std::max(8, (per_cta + 1) / 2 * 2);
-    const size_t fixed =
-        kRHead + (size_t)((Kt + S - 1) / S) * kActTileBytes + (a.npeer ? (size_t)p.nw * 512 : 0);
+    // k-tiles of the longest split (per-token splits cut whole weight-scale groups)
+    const int Ktg = Kt >> a.ksh;
+    const int span = a.mode ? (((Ktg + S - 1) / S) << a.ksh) : (Kt + S - 1) / S;
+    const size_t fixed = kRHead + (size_t)span * kActTileBytes + (a.npeer ? (size_t)p.nw * 512 : 0);
     p.ns = 4;
     while (p.ns > 2 && (size_t)p.nw * p.ns * kRStage + fixed > kSmemLimit) --p.ns;
     p.smem = (size_t)p.nw * p.ns * kRStage + fixed;
@@ -909,37 +953,35 @@ bool launch_ring(const GemmArgs &a) {
     const int grid = plan.grid, nw = plan.nw, ns = plan.ns;
     const size_t smem = plan.smem;
     bool pair = a.ksh != 0;
-    for (int s2 = 0; s2 < S; ++s2) pair = pair && ((Kt * s2 / S) % 2 == 0);
+    if (!a.mode)      // per-token splits cut whole K64 groups, so they always start on a pair
+        for (int s2 = 0; s2 < S; ++s2) pair = pair && ((Kt * s2 / S) % 2 == 0);
     if (S > 1) ensure_scratch((size_t)plan.nwin * groups * S * 128, plan.nwin * groups);
-    static bool attr_set = false;
-    if (!attr_set) {
-        auto big = [](auto kernel) {
+    auto go = [&](auto kernel) {
+        // every instantiation has the same function type, so remember them by address
+        static const void *done[32];
+        static int ndone = 0;
+        bool seen = false;
+        for (int i = 0; i < ndone; ++i) seen = seen || done[i] == (const void *)kernel;
+        if (!seen) {
             TQ_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           (int)kSmemLimit));
-        };
-        big(gemm_w4a8_ring_kernel<true, 2, kRW>);
-        big(gemm_w4a8_ring_kernel<true, 3, kRW>);
-        big(gemm_w4a8_ring_kernel<true, 4, kRW>);
-        big(gemm_w4a8_ring_kernel<true, 4, 20>);
-        big(gemm_w4a8_ring_kernel<false, 2, kRW>);
-        big(gemm_w4a8_ring_kernel<false, 3, kRW>);
-        big(gemm_w4a8_ring_kernel<false, 4, kRW>);
-        big(gemm_w4a8_ring_kernel<false, 4, 20>);
-        attr_set = true;
-    }
-    auto go = [&](auto kernel) {
+            if (ndone < 32) done[ndone++] = (const void *)kernel;
+        }
         launch_pdl(kernel, dim3(grid, plan.nwin), dim3(nw * 32), smem, a, g_scratch.part, g_scratch.count);
     };
-    if (pair) {
-        if (ns == 2) go(gemm_w4a8_ring_kernel<true, 2, kRW>);
-        else if (ns == 3) go(gemm_w4a8_ring_kernel<true, 3, kRW>);
-        else if (nw <= 20) go(gemm_w4a8_ring_kernel<true, 4, 20>);
-        else go(gemm_w4a8_ring_kernel<true, 4, kRW>);
+    auto pick = [&](auto pair_tag, auto pt_tag) {
+        constexpr bool P = decltype(pair_tag)::value, Q = decltype(pt_tag)::value;
+        if (ns == 2) go(gemm_w4a8_ring_kernel<P, 2, kRW, Q>);
+        else if (ns == 3) go(gemm_w4a8_ring_kernel<P, 3, kRW, Q>);
+        else if (nw <= 20) go(gemm_w4a8_ring_kernel<P, 4, 20, Q>);
+        else go(gemm_w4a8_ring_kernel<P, 4, kRW, Q>);
+    };
+    if (a.mode) {
+        if (pair) pick(std::true_type{}, std::true_type{});
+        else pick(std::false_type{}, std::true_type{});
     } else {
-        if (ns == 2) go(gemm_w4a8_ring_kernel<false, 2, kRW>);
-        else if (ns == 3) go(gemm_w4a8_ring_kernel<false, 3, kRW>);
-        else if (nw <= 20) go(gemm_w4a8_ring_kernel<false, 4, 20>);
-        else go(gemm_w4a8_ring_kernel<false, 4, kRW>);
+        if (pair) pick(std::true_type{}, std::false_type{});
+        else pick(std::false_type{}, std::false_type{});
     }
     TQ_LAUNCH_CHECK("gemm_w4a8_ring_kernel");
     return true;

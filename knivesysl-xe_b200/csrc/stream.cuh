@@ -55,14 +55,17 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 }
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, int *status,
                                                   int code, uint64_t limit_ns) {
-    if (mbar_try_wait(bar, parity)) return true;
-    // Slow path: back off between polls so that waiting warps leave the issue slots to the
-    // warps doing the work, and look at the clock only every 1024 polls.
+    // mbarrier.try_wait suspends the thread in hardware for a bounded time while the phase is
+    // incomplete, so polling it back to back costs few issue slots and adds no latency when
+    // the phase completes (a sleep between polls would add its length to every hand-off of a
+    // pipeline whose steps are shorter than the sleep). The clock is read every 2048 polls.
     uint64_t t0 = 0;
     for (uint32_t polls = 1;; ++polls) {
-        __nanosleep(200);
         if (mbar_try_wait(bar, parity)) return true;
-        if ((polls & 1023u) == 0) {
+#ifdef TQ_WAIT_SLEEP_NS
+        __nanosleep(TQ_WAIT_SLEEP_NS);
+#endif
+        if ((polls & 2047u) == 0) {
             const uint64_t now = global_timer_ns();
             if (t0 == 0) t0 = now;
             else if (now - t0 > limit_ns) break;
@@ -125,6 +128,16 @@ __device__ __forceinline__ void mma_s8_c(int (&d)[4], uint32_t a0, uint32_t a1, 
         : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c[0]), "r"(c[1]), "r"(c[2]),
           "r"(c[3]));
+}
+
+// The same with the accumulator input taken from a previous result (a chain of MMAs that adds
+// several k-tiles into one int32 dot).
+__device__ __forceinline__ void mma_s8_acc(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                           uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};"
+        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
 // Four registers holding v that the compiler cannot prove equal (so it keeps them as one

@@ -286,12 +286,13 @@ def gemm_w4a8(codes, scales, M, K, ksh, aq, as_, asum, T, offsets=None, forced_s
     return rc, y
 
 
-def gemm_w4a8_pertoken(codes, scales, M, K, ksh, aq, as_tok, asum, T):
+def gemm_w4a8_pertoken(codes, scales, M, K, ksh, aq, as_tok, asum, T, splits=1):
     codes, scales = _c(codes, np.uint8), _c(scales, np.uint16)
     aq, as_tok, asum = _c(aq, np.int8), _c(as_tok, np.float32), _c(asum, np.int32)
     y = np.empty((T, M), dtype=np.float32)
     rc = lib().orc_gemm_w4a8_pertoken(_p(codes), _p(scales), C.c_int(M), C.c_int(K), C.c_int(ksh),
-                                      _p(aq), _p(as_tok), _p(asum), _p(y), C.c_int(T))
+                                      _p(aq), _p(as_tok), _p(asum), _p(y), C.c_int(T),
+                                      C.c_int(splits))
     return rc, y
 
 

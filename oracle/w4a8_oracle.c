@@ -772,37 +772,44 @@ ORC_API int orc_gemm_w4a8(const uint8_t *codes, const uint16_t *scales, int M, i
     return 0;
 }
 
-/* Per-token-scale GEMM (no counterpart in the reference; pairs with
- * orc_quantize_act_chunk_pertoken). The integer dot runs across one whole
- * weight-scale group (32 codes, or 64 under ksh) before the fp32 promote:
- * acc = fma((float)(d_g - z*asum_g), ws_g, acc) over groups ascending, then
- * y = acc * as_tok. Unsplit only. */
+/* Per-token activation scales (not in the reference, which scales per (token, K32) block,
+ * xpu/src/kernels_dpas.cpp:1434-1451): the int32 dot runs over a whole weight-scale group
+ * (one k-tile, or both k-tiles of a K64 group) before the promote
+ * acc = fma((float)(d - z*asum), ws, acc), groups ascending. `splits` > 1 cuts the G groups
+ * into [G*s/S, G*(s+1)/S) like the reference cuts k-tiles (kernels_dpas.cpp:1413-1420); the
+ * partial sums are added 0..S-1 from 0.0f (1481-1484) and the per-token scale multiplies
+ * the total: y = sum * as_tok. splits <= 1: y = acc * as_tok. */
 ORC_API int orc_gemm_w4a8_pertoken(const uint8_t *codes, const uint16_t *scales, int M,
                                    int K, int ksh, const int8_t *aq, const float *as_tok,
-                                   const int32_t *asum, float *y, int T) {
+                                   const int32_t *asum, float *y, int T, int splits) {
     if (!codes || !scales) return -1;
     if (!aq || !as_tok || !asum || !y || T <= 0 || (T % 8) != 0) return -2;
-    const int Kt = K / 32, gw = 1 << ksh;
+    const int Kt = K / 32, gw = 1 << ksh, G = Kt >> ksh;
+    const int S = splits > 1 ? splits : 1;
 #pragma omp parallel for schedule(static)
     for (int row = 0; row < M; ++row) {
         const int rg = row >> 4, n = row & 15;
         const uint8_t *bbase = codes + (size_t)rg * Kt * 256u;
-        const uint16_t *sbase = scales + (size_t)rg * (Kt >> ksh) * 16u;
+        const uint16_t *sbase = scales + (size_t)rg * G * 16u;
         for (int tok = 0; tok < T; ++tok) {
-            float acc = 0.0f;
-            for (int kg = 0; kg < (Kt >> ksh); ++kg) {
-                int zp; float ws;
-                unpack_scale(sbase[(size_t)kg * 16u + n], &zp, &ws);
-                int32_t d = 0, sa = 0;
-                for (int u = 0; u < gw; ++u) {
-                    const int kt = kg * gw + u;
-                    const size_t a = (size_t)kt * T + tok;
-                    d += tile_dot(bbase + (size_t)kt * 256u, n, aq + a * 32);
-                    sa += asum[a];
+            float total = 0.0f;
+            for (int s = 0; s < S; ++s) {
+                float acc = 0.0f;
+                for (int kg = (int)((long)G * s / S); kg < (int)((long)G * (s + 1) / S); ++kg) {
+                    int zp; float ws;
+                    unpack_scale(sbase[(size_t)kg * 16u + n], &zp, &ws);
+                    int32_t d = 0, sa = 0;
+                    for (int u = 0; u < gw; ++u) {
+                        const int kt = kg * gw + u;
+                        const size_t a = (size_t)kt * T + tok;
+                        d += tile_dot(bbase + (size_t)kt * 256u, n, aq + a * 32);
+                        sa += asum[a];
+                    }
+                    acc = fmaf((float)(d - zp * sa), ws, acc);
                 }
-                acc = fmaf((float)(d - zp * sa), ws, acc);
+                total = (S == 1) ? acc : total + acc;
             }
-            y[(size_t)tok * M + row] = acc * as_tok[tok];
+            y[(size_t)tok * M + row] = total * as_tok[tok];
         }
     }
     return 0;

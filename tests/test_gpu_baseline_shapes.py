@@ -160,6 +160,17 @@ def test_cfg3_down_gemm(lib, pkg, orc, w_down_k32, T, splits):
     _, want_sep = orc.gemm_w4a8(codes, scales, M, K, 0, oq, os_, osm, T, fma=0)
     assert got.tobytes() == want.tobytes()
     assert close_1e3(got, want_sep)
+    # per-token activation scales (what the configuration names): own staging, own kernel mode
+    at = pkg.DevBuf(T * 4)
+    lib.qwn_x_quantize_act_chunk_pertoken(dx.ptr, K, T, aq.ptr, as_.ptr, asum.ptr, at.ptr)
+    y.fill(0xA5)
+    assert lib.qwn_x_gemm_w4a8_pertoken(w.ref, aq.ptr, at.ptr, asum.ptr, y.ptr, T, 0) == 0
+    lib.tq_sync()
+    oq, os_, osm = orc.quantize_act_chunk(x, per_token=True)
+    assert np.array_equal(aq.to_numpy(np.int8), oq)
+    as_tok = os_.reshape(K // 32, T)[0].copy()
+    _, want = orc.gemm_w4a8_pertoken(codes, scales, M, K, 0, oq, as_tok, osm, T, splits=splits)
+    assert y.to_numpy(np.float32).tobytes() == want.tobytes()
     assert lib.tq_last_error() == 0
 
 
@@ -196,6 +207,17 @@ def test_cfg2_fused_gate_up_k64_t8(lib, pkg, orc, wl, w_gate_up_k64, per_token):
         _, want_sep = orc.gemm_w4a8(codes, scales, M, K, 1, oq, os_, osm, T, fma=0)
         assert got.tobytes() == want.tobytes()
         assert close_1e3(got, want_sep)
+    if per_token:
+        # the per-token kernel proper: one promote per K64 group, as_tok applied at the end
+        for b in ys:
+            b.fill(0xA5)
+        assert lib.qwn_x_gemm_w4a8_fanout_pertoken(pkg.weight_array(ws), pkg.ptr_array(ys), 2, aq.ptr,
+                                                   at.ptr, asum.ptr, T) == 0
+        lib.tq_sync()
+        as_tok = os_.reshape(K // 32, T)[0].copy()
+        for (codes, scales), yb in zip(w_gate_up_k64, ys):
+            _, want = orc.gemm_w4a8_pertoken(codes, scales, M, K, 1, oq, as_tok, osm, T, splits=2)
+            assert yb.to_numpy(np.float32).tobytes() == want.tobytes()
     # int32 layer of the gate matrix
     dd = pkg.DevBuf(n * M * 4)
     assert lib.qwn_dbg_tile_dots_gemm(ws[0].ref, aq.ptr, T, dd.ptr) == 0

@@ -852,3 +852,47 @@ def test_gemm_fanout_fused_quantiser(lib, pkg, orc, wl, Ms, K, ksh, T, per_token
         assert y.to_numpy(np.float32).tobytes() == np.ascontiguousarray(want).tobytes()
     assert lib.qwn_x_gemm_w4a8_fanout_fused(pkg.weight_array(ws), pkg.ptr_array(ys), len(Ms), None, T, 0) == -2
     assert lib.tq_last_error() == 0
+
+
+# ---------------------------------------------------------------- per-token decode batches
+PERTOKEN_DECODE = [
+    # Ms, K, ksh, T
+    ([1088, 1088], 5120, 1, 8), ([320], 1024, 0, 8), ([48], 384, 0, 8), ([16, 272], 128, 1, 8),
+    ([5120], 2112, 0, 16), ([4800], 2112, 1, 16), ([1600], 1056, 0, 40), ([2048], 512, 0, 64),
+    ([640, 128], 2048, 1, 32), ([144], 4096, 1, 24), ([34816], 256, 0, 8), ([4096], 64, 1, 64),
+]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("Ms,K,ksh,T", PERTOKEN_DECODE)
+def test_gemm_pertoken_decode(lib, pkg, orc, wl, Ms, K, ksh, T):
+    """x_gemm_w4a8_fanout_pertoken (tcgen05 decode kernel, per-token activation scales): one
+    promote per weight-scale group, splits over groups summed in order, bit-identical to the
+    oracle; arbitrary zero points, zero scales, partial 128-row blocks, odd group counts."""
+    host = [wl.random_packed_weight(M, K, seed=900 + i + M + T, ksh=ksh) for i, M in enumerate(Ms)]
+    ws = [pkg.PackedWeight(c, s, M, K, k64=bool(ksh)) for (c, s), M in zip(host, Ms)]
+    x = wl.activations_normal(T, K, seed=T + K, outlier_frac=0.01)
+    dx = dev(pkg, x)
+    n = K // 32 * T
+    aq, as_, asum, at = pkg.DevBuf(n * 32), pkg.DevBuf(n * 4), pkg.DevBuf(n * 4), pkg.DevBuf(T * 4)
+    lib.qwn_x_quantize_act_chunk_pertoken(dx.ptr, K, T, aq.ptr, as_.ptr, asum.ptr, at.ptr)
+    ys = [pkg.DevBuf(T * M * 4) for M in Ms]
+    for b in ys:
+        b.fill(0xA5)
+    assert lib.qwn_x_gemm_w4a8_fanout_pertoken(pkg.weight_array(ws), pkg.ptr_array(ys), len(Ms), aq.ptr,
+                                               at.ptr, asum.ptr, T) == 0
+    lib.tq_sync()
+    oq, os_, osm = orc.quantize_act_chunk(x, per_token=True)
+    as_tok = os_.reshape(K // 32, T)[0].copy()
+    for (c, s), M, yb in zip(host, Ms, ys):
+        S = lib.qwn_choose_gemm_splits(M // 16, T // 8, K // 32)
+        _, want = orc.gemm_w4a8_pertoken(c, s, M, K, ksh, oq, as_tok, osm, T, splits=S)
+        got = yb.to_numpy(np.float32).reshape(T, M)
+        assert got.tobytes() == want.tobytes(), (M, S)
+    # the single-weight entry point routes decode batches to the same kernel
+    y1 = pkg.DevBuf(T * Ms[0] * 4)
+    assert lib.qwn_x_gemm_w4a8_pertoken(ws[0].ref, aq.ptr, at.ptr, asum.ptr, y1.ptr, T, 0) == 0
+    lib.tq_sync()
+    assert y1.to_numpy(np.float32).tobytes() == ys[0].to_numpy(np.float32).tobytes()
+    assert lib.qwn_x_gemm_w4a8_pertoken(ws[0].ref, aq.ptr, at.ptr, asum.ptr, y1.ptr, T, 1) == -3
+    assert lib.tq_last_error() == 0
