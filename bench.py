@@ -189,9 +189,12 @@ def e2e_loop(ctx, case, iters, warmup=3):
     n = 0
     last = None
 
+    single = getattr(case, "single_out", False)     # one output buffer: a read-back ends before
+                                                    # the next step may rewrite it
+
     def one(i):
         nonlocal n, last
-        b = n & 1
+        b = 0 if single else n & 1
         if tickets[b] >= 0:
             lib.tq_stream_wait_copy(tickets[b])
         up[(n + 1) & 1] = lib.tq_h2d_overlapped(case.x_dev[(n + 1) & 1].ptr, hx, nbx)
@@ -500,17 +503,20 @@ class Stack:
     activations. Per layer: RMSNorm of the incoming rows (keeps values O(1) through 64
     layers), 5120->10240, 10240->5120, fused 5120->gate|up, silu(gate)*up, 17408->5120; every
     projection is staging + GEMM through the C ABI (the batched path of
-    xpu/src/decode.cpp:1856-1871). Layers use distinct weights: four seeded base matrices,
+    xpu/src/decode.cpp:1856-1871). Layers use distinct weights: five seeded base matrices,
     rolled by a different number of row-groups per layer. With tp > 1 every projection is a
-    column shard (x_w4_shard mode 0; gate|up as two groups so silu*mul stays local) and the
-    output slices are exchanged after every projection."""
+    column shard (x_w4_shard mode 0; gate and up sharded alike, so silu*mul stays local), each
+    shard keeps the split count of the whole weight (bit-identical to tp = 1), the projections
+    write their output columns into every rank's copy of the next activation matrix, and the
+    staging / norm kernel that reads the matrix carries the exchange point."""
 
     LAYERS = 64
 
-    def __init__(self, ctx, layers=None, tp=1, rank=0):
-        self.ctx, self.tp, self.rank = ctx, tp, rank
+    def __init__(self, ctx, layers=None, tp=1, rank=0, comm=None):
+        self.ctx, self.tp, self.rank, self.comm = ctx, tp, rank, comm
         self.L = layers or self.LAYERS
         self.T = 8
+        self.name, self.mode = "cfg5", "pertoken"
         pkg, lib, wl = ctx.pkg, ctx.lib, ctx.wl
         shapes = [(QKV, H, 41), (H, QKV, 42), (I_FF, H, 43), (I_FF, H, 44), (H, I_FF, 45)]
         base = [ctx.rotated(M, K, seed, 32, n=1)[0] for M, K, seed in shapes]
@@ -528,24 +534,34 @@ class Stack:
         self.x_host = wl.activations_normal(T, H, seed=5)
         self.x_dev = [pkg.DevBuf.from_numpy(self.x_host), pkg.DevBuf.from_numpy(self.x_host)]
         self.norm_w = pkg.DevBuf.from_numpy(np.zeros(H, dtype=np.uint16))     # (1 + 0) weights
-        kmax = I_FF
-        nb = kmax // 32 * T
+        nb = I_FF // 32 * T
         self.aq, self.as_, self.asum, self.as_tok = (pkg.DevBuf(nb * 32), pkg.DevBuf(nb * 4),
                                                      pkg.DevBuf(nb * 4), pkg.DevBuf(T * 4))
         self.xn = pkg.DevBuf(T * H * 4)
-        self.y1 = pkg.DevBuf(T * QKV * 4)
-        self.y2 = pkg.DevBuf(T * H * 4)
-        self.gu = pkg.DevBuf(2 * T * I_FF * 4)
-        self.h = pkg.DevBuf(T * I_FF * 4)
+        self.gu = pkg.DevBuf(2 * T * (I_FF // tp) * 4)          # this rank's gate and up columns
         self.out_bytes = T * H * 4
-        self.y = [pkg.DevBuf(self.out_bytes) for _ in range(2)]
-        self.cur = pkg.DevBuf(T * H * 4)
+        # activation matrices between the projections (symmetric buffers when tp > 1)
+        self.y1, self.y2, self.h, self.y4 = (pkg.DevBuf(T * QKV * 4), pkg.DevBuf(T * H * 4),
+                                             pkg.DevBuf(T * I_FF * 4), pkg.DevBuf(T * H * 4))
+        self.sym = [self.y1, self.y2, self.h, self.y4]
+        if tp > 1:
+            comm.register(self.sym)
+        else:
+            # a world of one: the same calls, the exchange points wait for this rank's own flag
+            self.flags = pkg.DevBuf(4)
+            one = (C.c_void_p * 1)
+            assert lib.tq_comm_gather_setup(one(self.y1.ptr), one(self.flags.ptr), 1, 0) == 0
+            for i, b in enumerate(self.sym):
+                assert lib.tq_comm_sym_register(i, one(b.ptr)) == 0
         self.weight_bytes = self.L * sum(wl.weight_bytes(M, K, 32) for M, K, _ in shapes)
-        self.launches_per_step = self.L * 10
+        self.algo_bytes = self.weight_bytes
+        self.launches_per_step = self.L * 10 + (2 if tp > 1 else 0)
+        self.single_out = True
         self.graph = None
 
     def _rolled_shard(self, base, M, K, shift):
-        """Device copy of `base` rolled by `shift` row-groups (two runs per array)."""
+        """Device copy of `base` rolled by `shift` row-groups (two runs per array); with
+        tp > 1 only this rank's column shard of it is kept."""
         pkg, lib = self.ctx.pkg, self.ctx.lib
         cb, sb = (K // 32) * 256, (K // 32) * 32
         codes, scales = pkg.DevBuf(M // 16 * cb), pkg.DevBuf(M // 16 * sb)
@@ -560,59 +576,84 @@ class Stack:
         w.rec.M, w.rec.K, w.rec.Mt, w.rec.Kt = M, K, M // 16, K // 32
         w.rec.d_s4, w.rec.d_s4_scale, w.rec.s4_ready = codes.ptr, scales.ptr, 1
         lib.tq_sync()
+        if self.tp > 1:
+            sh = pkg.TqWeight()
+            assert lib.qwn_x_w4_shard(C.byref(sh), w.ref, self.rank, self.tp, 0, None, 0) == 0
+            codes.free()
+            scales.free()
+            w.codes = w.scales = None
+            w.rec = sh
         return w
 
-    def _proj(self, w, x_ptr, K, y_ptr):
-        lib, T = self.ctx.lib, self.T
-        lib.qwn_x_quantize_act_chunk_pertoken(x_ptr, K, T, self.aq.ptr, self.as_.ptr, self.asum.ptr,
-                                              self.as_tok.ptr)
-        rc = lib.qwn_x_gemm_w4a8(w.ref, self.aq.ptr, self.as_.ptr, self.asum.ptr, y_ptr, T, None, 0)
+    def _gemm(self, ws, full_rows, slot, col_off, ld, ys=None):
+        lib, pkg, T = self.ctx.lib, self.ctx.pkg, self.T
+        n = len(ws)
+        warr = (C.POINTER(pkg.TqWeight) * n)(*[C.pointer(w.rec) for w in ws])
+        fr = (C.c_int * n)(*full_rows)
+        co = (C.c_size_t * n)(*col_off) if col_off is not None else None
+        ya = (C.c_void_p * n)(*ys) if ys is not None else None
+        rc = lib.qwn_x_gemm_w4a8_fanout_tp(warr, n, self.aq.ptr, None, self.as_tok.ptr, self.asum.ptr, T, fr,
+                                           ya, slot, co, ld)
         assert rc == 0, rc
 
-    def _issue(self, x_ptr, out_ptr):
-        lib, pkg, T = self.ctx.lib, self.ctx.pkg, self.T
-        src = x_ptr
+    def _stage(self, x_ptr, K, sync):
+        lib, T = self.ctx.lib, self.T
+        sync = sync and self.tp > 1              # one GPU: nothing to wait for
+        f = lib.qwn_x_quantize_act_chunk_pertoken_sync if sync else lib.qwn_x_quantize_act_chunk_pertoken
+        f(x_ptr, K, T, self.aq.ptr, self.as_.ptr, self.asum.ptr, self.as_tok.ptr)
+
+    def _issue(self, x_ptr):
+        """One pass: 64 layers, then the exchange point that makes the last output complete on
+        every rank, then the step base moves on (so the pass can be replayed)."""
+        lib, T, tp, r = self.ctx.lib, self.T, self.tp, self.rank
+        n_i = I_FF // tp
         for l, (w1, w2, wg, wu, wd) in enumerate(self.layers):
-            lib.qwn_x_rmsnorm_chunk(self.xn.ptr, src, self.norm_w.ptr, H, T, 1e-6)
-            self._proj(w1, self.xn.ptr, H, self.y1.ptr)
-            self._proj(w2, self.y1.ptr, QKV, self.y2.ptr)
-            lib.qwn_x_quantize_act_chunk_pertoken(self.y2.ptr, H, T, self.aq.ptr, self.as_.ptr,
-                                                  self.asum.ptr, self.as_tok.ptr)
-            warr = pkg.weight_array([wg, wu])
-            yarr = (C.c_void_p * 2)(self.gu.ptr, self.gu.ptr + T * I_FF * 4)
-            rc = lib.qwn_x_gemm_w4a8_fanout(warr, yarr, 2, self.aq.ptr, self.as_.ptr, self.asum.ptr, T,
-                                            None, 0)
-            assert rc == 0, rc
-            lib.qwn_x_silu_mul(self.h.ptr, self.gu.ptr, self.gu.ptr + T * I_FF * 4, T * I_FF)
-            dst = out_ptr if l == self.L - 1 else self.cur.ptr
-            self._proj(wd, self.h.ptr, I_FF, dst)
-            src = dst
+            if l == 0 or tp == 1:
+                lib.qwn_x_rmsnorm_chunk(self.xn.ptr, x_ptr if l == 0 else self.y4.ptr, self.norm_w.ptr, H, T,
+                                        1e-6)
+            else:
+                lib.qwn_x_rmsnorm_chunk_sync(self.xn.ptr, self.y4.ptr, self.norm_w.ptr, H, T, 1e-6)
+            self._stage(self.xn.ptr, H, False)
+            self._gemm([w1], [QKV], 0, [r * (QKV // tp)], QKV)
+            self._stage(self.y1.ptr, QKV, True)
+            self._gemm([w2], [H], 1, [r * (H // tp)], H)
+            self._stage(self.y2.ptr, H, True)
+            self._gemm([wg, wu], [I_FF, I_FF], -1, None, 0, ys=[self.gu.ptr, self.gu.ptr + T * n_i * 4])
+            assert lib.qwn_x_silu_mul_scatter(self.gu.ptr, self.gu.ptr + T * n_i * 4, T, n_i, 2, r * n_i,
+                                              I_FF) == 0
+            self._stage(self.h.ptr, I_FF, True)
+            self._gemm([wd], [H], 3, [r * (H // tp)], H)
+        if tp > 1:
+            assert lib.tq_comm_exchange_sync() == 0
+            assert lib.tq_comm_exchange_advance() == 0
 
     def capture(self):
-        """One CUDA graph per (input buffer, output buffer) pair: 640 launches per replay."""
+        """One CUDA graph per input buffer: 642 launches per replay."""
         lib = self.ctx.lib
-        self._issue(self.x_dev[0].ptr, self.y[0].ptr)        # warm: all scratch allocated
+        self._issue(self.x_dev[0].ptr)        # warm: all scratch allocated
         lib.tq_sync()
         self.graph = {}
         for xb in range(2):
-            for b in range(2):
-                assert lib.tq_graph_capture_begin() == 0
-                self._issue(self.x_dev[xb].ptr, self.y[b].ptr)
-                g = lib.tq_graph_capture_end()
-                assert g, "graph capture failed"
-                self.graph[(xb, b)] = g
+            assert lib.tq_graph_capture_begin() == 0
+            self._issue(self.x_dev[xb].ptr)
+            g = lib.tq_graph_capture_end()
+            assert g, "graph capture failed"
+            self.graph[xb] = g
+
+    def stage(self, xb):
+        pass
 
     def run(self, i, xb, b):
         if self.graph:
-            self.ctx.lib.tq_graph_launch(self.graph[(xb, b)])
+            self.ctx.lib.tq_graph_launch(self.graph[xb])
         else:
-            self._issue(self.x_dev[xb].ptr, self.y[b].ptr)
+            self._issue(self.x_dev[xb].ptr)
 
     def kernel(self, i, b=0):
         self.run(i, 0, b)
 
     def out_ptr(self, b):
-        return self.y[b].ptr
+        return self.y4.ptr
 
     def cpu_pass_fn(self):
         """One projection of each kind of layer 0 on the oracle (1/64 of a step)."""
@@ -625,7 +666,10 @@ class Stack:
         def fn():
             for (M, K, _), (codes, scales) in zip(self.shapes, ws):
                 orc.quantize_act_chunk(xs[K], per_token=True)
-                orc.gemm_w4a8(codes, scales, M, K, 0, *qs[K], T)
+                oq, os_, osm = qs[K]
+                S = orc.choose_gemm_splits(M // 16, T // 8, K // 32)
+                orc.gemm_w4a8_pertoken(codes, scales, M, K, 0, oq, os_.reshape(K // 32, T)[0].copy(), osm, T,
+                                       splits=S)
         return fn
 
 
@@ -706,12 +750,12 @@ def build_cases(ctx, which):
         c = DecodeGemm(ctx, "cfg2", I_FF, 2, H, 64, 8, "pertoken", 11,
                        lambda: wl.activations_normal(8, H, seed=5, outlier_frac=0.01))
         c._seed0 = 11
-        out["cfg2"] = (c, "gemm_w4a8_dtc_kernel", "hbm")
+        out["cfg2"] = (c, "gemm_w4a8_ring_kernel", "hbm")
     if want("cfg2_exact"):
         c = DecodeGemm(ctx, "cfg2_exact", I_FF, 2, H, 64, 8, "exact", 11,
                        lambda: wl.activations_normal(8, H, seed=5, outlier_frac=0.01))
         c._seed0 = 11
-        out["cfg2_exact"] = (c, "gemm_w4a8_dtc_kernel", "hbm")
+        out["cfg2_exact"] = (c, "gemm_w4a8_ring_kernel", "hbm")
     if want("cfg1"):
         out["cfg1"] = (DecodeGemv(ctx, "cfg1", I_FF, H, 32, "pertoken", 21, silu=False), "gemv_w4a8_kernel", "hbm")
     if want("cfg3_T1"):
@@ -725,9 +769,12 @@ def build_cases(ctx, which):
                 g = rng.standard_normal((T, I_FF))
                 u = rng.standard_normal((T, I_FF))
                 return (g / (1.0 + np.exp(-g)) * u).astype(np.float32)
-            c = DecodeGemm(ctx, n, H, 1, I_FF, 32, T, "pertoken", 23, xg)
+            # 8 tokens: per-token scales on the ring kernel; 16..64 tokens: the reference's
+            # arithmetic (scale per (token, K32)) on the mma.sync kernels, the faster path there
+            mode = "pertoken" if T == 8 else "exact"
+            c = DecodeGemm(ctx, n, H, 1, I_FF, 32, T, mode, 23, xg)
             c._seed0 = 23
-            out[n] = (c, "gemm_w4a8_dtc_kernel", "hbm")
+            out[n] = (c, "gemm_w4a8_ring_kernel" if T <= 32 else "gemm_w4a8_stream_kernel", "hbm")
     shared = None
     for mode in Prefill.MODES:
         n = f"cfg4_{mode}"
@@ -891,8 +938,6 @@ def run_single(args):
         st = Stack(ctx, layers=args.layers)
         st.capture()
         st_ms = ctx.time_loop(lambda i: st.run(i, 0, 0), 20)
-        st.mode = "pertoken"
-        st.algo_bytes = st.weight_bytes
         s5, d5 = e2e_loop(ctx, st, 20)
         rec5 = {"name": "cfg5_tp1", "T": 8, "mode": "pertoken", "layers": st.L, "us": st_ms * 1e3,
                 "launches_per_step": st.launches_per_step, "value": st.weight_bytes / (st_ms * 1e-3) / 1e9,
@@ -901,7 +946,7 @@ def run_single(args):
                              "peak": ctx.peak_hbm, "unit": "GB/s",
                              "frac": st.weight_bytes / (st_ms * 1e-3) / 1e9 / ctx.peak_hbm,
                              "peak_source": f"{ctx.peak_kind} copy bandwidth",
-                             "kernel": "whole step (CUDA graph of 10 launches per layer)",
+                             "kernel": "whole step (CUDA graph: norm, 4 stagings, 4 GEMMs, silu*mul per layer)",
                              "algorithmic_bytes_per_launch": int(st.weight_bytes), "traffic": None},
                 "e2e": {"value": st.weight_bytes / s5 / 1e9, "unit": UNIT, "us_per_step": s5 * 1e6,
                         "h2d_bytes_per_step": int(st.x_host.nbytes), "d2h_bytes_per_step": int(st.out_bytes),

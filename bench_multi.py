@@ -1,0 +1,178 @@
+"""Multi-GPU leg of bench.py (one rank per GPU, launched by torchrun): the 64-layer projection
+stack with every projection column-sharded over the ranks, strong scaling (the same 13.4 GB of
+weights per step at every N). torch.distributed (gloo) is the control plane only: barriers,
+the exchange of IPC handles, max-over-ranks of the device times.
+
+Rank 0 also runs the unsharded stack on its own GPU in the same process: the sharded result
+must be byte-identical to it (`tp1_words_differing`), and its time is the strong-scaling
+baseline measured in the same run (`tp1_ms_per_step`).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import json
+import time
+
+import numpy as np
+
+import bench as B
+
+
+class Comm:
+    """World set-up for the fused exchange: flag arrays and symmetric buffers mapped into
+    every rank through CUDA IPC."""
+
+    def __init__(self, ctx, dist, rank, world):
+        self.ctx, self.dist, self.rank, self.world = ctx, dist, rank, world
+        lib, pkg = ctx.lib, ctx.pkg
+        self.flags = pkg.DevBuf(world * 4)
+        lib.tq_dev_zero(self.flags.ptr, world * 4)
+        self.flag_ptrs = self._map(self.flags)
+        self.slots = 0
+
+    def _map(self, buf):
+        lib = self.ctx.lib
+        h = (C.c_char * 64)()
+        assert lib.tq_comm_ipc_export(buf.ptr, h) == 0
+        allh = [None] * self.world
+        self.dist.all_gather_object(allh, bytes(h.raw))
+        ptrs = (C.c_void_p * self.world)()
+        for p in range(self.world):
+            ptrs[p] = buf.ptr if p == self.rank else lib.tq_comm_ipc_open(C.create_string_buffer(allh[p], 64))
+            assert ptrs[p], f"rank {self.rank}: cannot map rank {p}'s buffer"
+        return ptrs
+
+    def register(self, bufs):
+        lib = self.ctx.lib
+        maps = [self._map(b) for b in bufs]
+        assert lib.tq_comm_gather_setup(maps[0], self.flag_ptrs, self.world, self.rank) == 0
+        for i, m in enumerate(maps):
+            assert lib.tq_comm_sym_register(i, m) == 0
+        self.maps = maps
+        self.dist.barrier()          # every rank has cleared its flags before anyone publishes
+
+
+def run(args, rank, local_rank, world):
+    import torch
+    import torch.distributed as dist
+    ctx = B.Ctx(args.rotate)
+    lib, pkg = ctx.lib, ctx.pkg
+    assert lib.tq_set_device(local_rank) == 0
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    sampler = B.ClockSampler(local_rank) if rank == 0 else None
+
+    def barrier():
+        lib.tq_sync()
+        dist.barrier()
+
+    def max_over_ranks(v):
+        t = torch.tensor([v], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- the unsharded stack on rank 0: result to match, time to scale from ------------------
+    tp1 = {"ms": None, "out": None}
+    if rank == 0:
+        st1 = B.Stack(ctx, layers=args.layers)
+        st1.capture()
+        tp1["ms"] = ctx.time_loop(lambda i: st1.run(i, 0, 0), 10)
+        lib.tq_sync()
+        tp1["out"] = st1.y4.to_numpy(np.uint32).copy()
+        del st1
+    dist.barrier()
+
+    # ---- the sharded stack -------------------------------------------------------------------
+    comm = Comm(ctx, dist, rank, world)
+    st = B.Stack(ctx, layers=args.layers, tp=world, rank=rank, comm=comm)
+    barrier()
+    st.run(0, 0, 0)                      # eager pass: warm-up, all scratch allocated
+    barrier()
+    out = st.y4.to_numpy(np.uint32).copy()
+    diff = int(np.count_nonzero(out != tp1["out"])) if rank == 0 else 0
+    # every rank must hold the same gathered result
+    outs = [None] * world
+    dist.all_gather_object(outs, out.tobytes())
+    ranks_differ = sum(1 for o in outs if o != outs[0])
+    barrier()
+    st.capture()
+    barrier()
+    for i in range(args.warmup):
+        st.run(i, 0, 0)
+    barrier()
+    ev = ctx.events()
+    t0 = time.time()
+    lib.tq_event_record(ev[0])
+    for i in range(args.steps):
+        st.run(i, 0, 0)
+    lib.tq_event_record(ev[1])
+    barrier()
+    ctx.load_spans.append((t0, time.time()))
+    ms = max_over_ranks(lib.tq_event_elapsed_ms(ev[0], ev[1])) / args.steps
+    out2 = st.y4.to_numpy(np.uint32)
+    replay_diff = int(np.count_nonzero(out2 != out))       # graph replays give the eager result
+
+    # ---- this rank's GEMMs alone (no staging, no exchange): where the step's time is not ------
+    lib.qwn_x_quantize_act_chunk_pertoken(st.xn.ptr, B.H, 8, st.aq.ptr, st.as_.ptr, st.asum.ptr, st.as_tok.ptr)
+
+    # (the four GEMM kinds read different K; time each kind with its own staging below)
+    kinds = []
+    for name, K, pick, full in (("5120->10240", B.H, lambda l: [l[0]], [B.QKV]),
+                                ("10240->5120", B.QKV, lambda l: [l[1]], [B.H]),
+                                ("5120->gate|up", B.H, lambda l: [l[2], l[3]], [B.I_FF, B.I_FF]),
+                                ("17408->5120", B.I_FF, lambda l: [l[4]], [B.H])):
+        src = {B.H: st.xn, B.QKV: st.y1, B.I_FF: st.h}[K]
+        lib.qwn_x_quantize_act_chunk_pertoken(src.ptr, K, 8, st.aq.ptr, st.as_.ptr, st.asum.ptr, st.as_tok.ptr)
+        scratch = [st.gu.ptr, st.gu.ptr + 8 * (B.I_FF // world) * 4]
+
+        def one(i, pick=pick, full=full):
+            ws = pick(st.layers[i % st.L])
+            st._gemm(ws, full, -1, None, 0, ys=scratch[: len(ws)])
+        kinds.append((name, ctx.time_loop(one, 4 * st.L, warmup=8) * 1e3))
+    gemm_us = sum(us for _, us in kinds) * st.L
+    gemm_us = max_over_ranks(gemm_us)
+
+    # ---- end to end with host buffers ------------------------------------------------------
+    barrier()
+    e_iters = max(min(args.steps, 200), 10)
+    e_s, e_diff = B.e2e_loop(ctx, st, e_iters, warmup=3)
+    e_s = max_over_ranks(e_s)
+    barrier()
+    clocks = sampler.stop(ctx.load_spans) if sampler else None
+    err = lib.tq_last_error()
+    errs = [None] * world
+    dist.all_gather_object(errs, err)
+
+    if rank == 0:
+        wb = st.weight_bytes
+        line = {
+            "metric": B.METRIC, "value": wb / (ms * 1e-3) / 1e9, "unit": B.UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "s8xs4->s32, fp32 out", "data": "synthetic",
+            "config": {"workload": B.WORKLOAD_CFG5,
+                       "parallelism": f"column shard tp{world}; projections store their output columns into "
+                                      "every rank's activation matrix (peer stores from the GEMM epilogue), "
+                                      "the next staging kernel carries the exchange point",
+                       "l2": f"inputs larger than L2: {wb / world / 1e9:.2f} GB of distinct weights per GPU "
+                             "per step",
+                       "step": f"{st.L} layers x (norm, 4 stagings, 4 GEMMs, silu*mul) replayed as one CUDA "
+                               f"graph; {4 * st.L} exchange points per step"},
+            "tp1_ms_per_step": tp1["ms"],
+            "tp1_words_differing": diff,
+            "ranks_with_a_different_result": ranks_differ,
+            "graph_replay_words_differing": replay_diff,
+            "step_split_us": {"step": ms * 1e3, "gemm_kernels_alone": gemm_us,
+                              "staging_exchange_and_gaps": ms * 1e3 - gemm_us,
+                              "gemm_kinds_us_per_launch": dict(kinds)},
+            "roofline": {"bound": "hbm", "achieved": wb / world / (ms * 1e-3) / 1e9, "peak": ctx.peak_hbm,
+                         "unit": "GB/s", "frac": wb / world / (ms * 1e-3) / 1e9 / ctx.peak_hbm,
+                         "peak_source": f"{ctx.peak_kind} copy bandwidth", "kernel": "whole step, per GPU",
+                         "algorithmic_bytes_per_launch": int(wb / world), "traffic": None},
+            "e2e": {"value": wb / e_s / 1e9, "unit": B.UNIT, "h2d_bytes_per_step": int(st.x_host.nbytes),
+                    "d2h_bytes_per_step": int(st.out_bytes), "steps": e_iters, "us_per_step": e_s * 1e6,
+                    "last_result_words_differing": e_diff},
+            "gpu_launches": st.launches_per_step * args.steps,
+            "clocks": clocks, "cpu_baseline": None, "device_error": max(errs),
+        }
+        print(json.dumps(line), flush=True)
+    lib.tq_comm_destroy()
+    dist.destroy_process_group()

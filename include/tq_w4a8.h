@@ -346,6 +346,38 @@ int qwn_x_gemm_w4a8_fanout_gathered(const tq_qmma_weight_t *const *ws, int count
 int qwn_x_gemm_w4a8_fanout_gathered_fused(const tq_qmma_weight_t *const *ws, int count,
                                           const float *d_x, int T, int per_token,
                                           size_t *half_offset_floats);
+/* Tensor-parallel decode chain without a kernel of its own for the exchange (no counterpart in
+ * the reference, whose TP forward is not built, xpu/docs/level-up-xpu.md:757-801). Every rank
+ * keeps the activations between projections as full [T][ld] fp32 matrices ("symmetric
+ * buffers": same size on every rank, mapped into the other ranks with tq_comm_ipc_*, named by
+ * a slot with tq_comm_sym_register after tq_comm_gather_setup has set world, rank and flag
+ * arrays; bufs[] of that call may repeat any registered buffer). A projection on a column shard
+ * writes its output columns into the matrix of EVERY rank from its epilogue
+ * (qwn_x_gemm_w4a8_fanout_tp with slot >= 0, qwn_x_silu_mul_scatter); the kernel that reads the
+ * matrix next carries the exchange point in its prologue: its first CTA publishes this rank's
+ * step flag to all ranks behind a system-scope fence, every CTA waits (bounded; status 10032)
+ * for all ranks' flags, then the kernel does the work of its plain namesake. The step number
+ * is read from device memory, base + index within the pass; tq_comm_exchange_advance closes a
+ * pass, so a pass can be recorded in a CUDA graph and replayed (tq_comm_exchange_rewind
+ * restarts the host-side index after recording). All ranks make the same sequence of calls.
+ * full_rows[i] = rows of the unsharded projection: the shard is split like the whole weight, so
+ * its outputs are bit-identical to those rows of the unsharded call. d_as_tok != NULL selects
+ * per-token activation scales (d_as then unused). Returns -21 for shapes outside 8..64 tokens. */
+int tq_comm_sym_register(int slot, void *const *ptrs);
+int tq_comm_exchange_advance(void);
+int tq_comm_exchange_rewind(void);
+int tq_comm_exchange_sync(void);
+int qwn_x_gemm_w4a8_fanout_tp(const tq_qmma_weight_t *const *ws, int count, const int8_t *d_aq,
+                              const float *d_as, const float *d_as_tok, const int32_t *d_asum, int T,
+                              const int *full_rows, float *const *ys, int slot, const size_t *col_off,
+                              size_t ld);
+void qwn_x_quantize_act_chunk_sync(const float *d_x, int K, int T, int8_t *d_aq, float *d_as,
+                                   int32_t *d_asum);
+void qwn_x_quantize_act_chunk_pertoken_sync(const float *d_x, int K, int T, int8_t *d_aq, float *d_as,
+                                            int32_t *d_asum, float *d_as_tok);
+void qwn_x_rmsnorm_chunk_sync(float *d_out, const float *d_in, const uint16_t *d_w, int H, int T, float eps);
+int qwn_x_silu_mul_scatter(const float *d_gate, const float *d_up, int T, int n, int slot, size_t col_off,
+                           size_t ld);
 int tq_comm_rank(void);
 int tq_comm_world(void);
 void tq_comm_destroy(void);
@@ -402,6 +434,16 @@ int x_gemm_w4a8_pertoken(const tq_qmma_weight_t *w, const int8_t *d_aq, const fl
 int x_gemm_w4a8_fanout_pertoken(const tq_qmma_weight_t *const *ws, float *const *ys, int count,
                                 const int8_t *d_aq, const float *d_as_tok, const int32_t *d_asum,
                                 int T);
+int x_gemm_w4a8_fanout_tp(const tq_qmma_weight_t *const *ws, int count, const int8_t *d_aq,
+                          const float *d_as, const float *d_as_tok, const int32_t *d_asum, int T,
+                          const int *full_rows, float *const *ys, int slot, const size_t *col_off,
+                          size_t ld);
+void x_quantize_act_chunk_sync(const float *d_x, int K, int T, int8_t *d_aq, float *d_as, int32_t *d_asum);
+void x_quantize_act_chunk_pertoken_sync(const float *d_x, int K, int T, int8_t *d_aq, float *d_as,
+                                        int32_t *d_asum, float *d_as_tok);
+void x_rmsnorm_chunk_sync(float *d_out, const float *d_in, const uint16_t *d_w, int H, int T, float eps);
+int x_silu_mul_scatter(const float *d_gate, const float *d_up, int T, int n, int slot, size_t col_off,
+                       size_t ld);
 void x_prepare_gemv_act_s8_pertoken(const float *d_x, int K);
 void x_silu_mul_quant_pertoken(float *d_out, const float *d_gate, const float *d_up, int K);
 int x_w8_repack_weight(tq_qmma_weight_t *w);

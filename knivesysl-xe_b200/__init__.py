@@ -110,6 +110,14 @@ SIGNATURES = {
                                          C.POINTER(_sz)]),
     "qwn_x_gemm_w4a8_fanout_fused": (_i, [C.POINTER(_WP), C.POINTER(_vp), _i, _vp, _i, _i]),
     "qwn_x_gemm_w4a8_fanout_gathered_fused": (_i, [C.POINTER(_WP), _i, _vp, _i, _i, C.POINTER(_sz)]),
+    "tq_comm_sym_register": (_i, [_i, C.POINTER(_vp)]), "tq_comm_exchange_advance": (_i, []),
+    "tq_comm_exchange_rewind": (_i, []), "tq_comm_exchange_sync": (_i, []),
+    "qwn_x_gemm_w4a8_fanout_tp": (_i, [C.POINTER(_WP), _i, _vp, _vp, _vp, _vp, _i, C.POINTER(_i),
+                                   C.POINTER(_vp), _i, C.POINTER(_sz), _sz]),
+    "qwn_x_quantize_act_chunk_sync": (None, [_vp, _i, _i, _vp, _vp, _vp]),
+    "qwn_x_quantize_act_chunk_pertoken_sync": (None, [_vp, _i, _i, _vp, _vp, _vp, _vp]),
+    "qwn_x_rmsnorm_chunk_sync": (None, [_vp, _vp, _vp, _i, _i, C.c_float]),
+    "qwn_x_silu_mul_scatter": (_i, [_vp, _vp, _i, _i, _i, _sz, _sz]),
     "tq_comm_rank": (_i, []), "tq_comm_world": (_i, []), "tq_comm_destroy": (None, []),
 }
 

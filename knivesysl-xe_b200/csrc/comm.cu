@@ -64,6 +64,21 @@ __global__ void gather_publish_wait_kernel(PeerFlags f, const int *mine, int wor
     atomicCAS(status, 0, 31);
 }
 
+// One thread: the step base of the next pass (see SyncArgs).
+__global__ void exchange_advance_kernel(int *base, int n) {
+    tq::pdl_trigger();
+    tq::pdl_wait();
+    if (threadIdx.x == 0) *base += n;
+}
+
+// An exchange point on its own (nothing to stage behind it): e.g. before the host reads the
+// last gathered result of a pass.
+__global__ void exchange_sync_kernel(tq::SyncArgs sa) {
+    tq::pdl_trigger();
+    tq::pdl_wait();
+    tq::exchange_sync(sa);
+}
+
 bool load_nccl() {
     if (g_api.handle) return true;
     const char *names[] = {"libnccl.so.2", "libnccl.so"};
@@ -100,6 +115,20 @@ int nccl_fail(ncclResult_t r, const char *where) {
 
 namespace tq {
 GatherState &gather_state() { return g_gather; }
+
+SyncArgs exchange_point() {
+    GatherState &g = g_gather;
+    SyncArgs sa{};
+    if (g.world < 1 || !g.step_base) return sa;
+    for (int p = 0; p < g.world; ++p) sa.peer_flag[p] = g.flag[p] + g.rank;
+    sa.mine = g.flag[g.rank];
+    sa.base = g.step_base;
+    sa.k = ++g.pass_syncs;
+    sa.world = g.world;
+    sa.status = device_status_word();
+    sa.limit_ns = wait_limit_ns();
+    return sa;
+}
 
 void launch_gather_publish(int step) {
     GatherState &g = g_gather;
@@ -218,7 +247,49 @@ int tq_comm_gather_setup(void *const *bufs, void *const *flags, int world, int r
     g.world = world;
     g.rank = rank;
     g.step = 0;
+    g.pass_syncs = 0;
     tq_dev_zero(g.flag[rank], (size_t)world * sizeof(int));
+    if (!g.step_base) g.step_base = static_cast<int *>(tq_dev_alloc(sizeof(int), "exchange.step.base"));
+    tq_dev_zero(g.step_base, sizeof(int));
+    return 0;
+}
+
+// ptrs[p]: rank p's copy of a symmetric buffer (a [T][ld] fp32 matrix every rank holds in
+// full) as addressable from this process; slot 0..15 names it in the scatter calls.
+int tq_comm_sym_register(int slot, void *const *ptrs) {
+    tq::GatherState &g = g_gather;
+    if (slot < 0 || slot >= 16 || !ptrs || g.world < 1) return -1;
+    for (int p = 0; p < g.world; ++p) {
+        if (!ptrs[p]) return -1;
+        g.sym[slot][p] = static_cast<float *>(ptrs[p]);
+    }
+    return 0;
+}
+
+// Closes a pass: the step base moves past the exchange points queued since the last call, so
+// the same sequence of calls - or a CUDA graph of it - can run again. Every rank must queue
+// the same number of exchange points per pass.
+int tq_comm_exchange_advance(void) {
+    tq::GatherState &g = g_gather;
+    if (g.world < 1 || !g.step_base) return -3;
+    tq::launch_pdl(exchange_advance_kernel, dim3(1), dim3(32), 0, g.step_base, g.pass_syncs);
+    tq::note_error(cudaGetLastError(), "exchange_advance_kernel");
+    g.pass_syncs = 0;
+    return 0;
+}
+
+// Restarts the count of exchange points of a pass without touching the device (used between
+// recording a pass into a CUDA graph and issuing the same pass again).
+int tq_comm_exchange_rewind(void) {
+    g_gather.pass_syncs = 0;
+    return 0;
+}
+
+int tq_comm_exchange_sync(void) {
+    tq::GatherState &g = g_gather;
+    if (g.world < 1 || !g.step_base) return -3;
+    tq::launch_pdl(exchange_sync_kernel, dim3(1), dim3(32), 0, tq::exchange_point());
+    tq::note_error(cudaGetLastError(), "exchange_sync_kernel");
     return 0;
 }
 

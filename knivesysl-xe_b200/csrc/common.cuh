@@ -51,7 +51,27 @@ struct GatherState {
     float *buf[8] = {};       // rank p's gathered buffer
     int *flag[8] = {};        // rank p's flag array (one int per source rank)
     int step = 0;             // last published step
+    float *sym[16][8] = {};   // registered symmetric buffers: [slot][rank]
+    int *step_base = nullptr; // device word: steps completed before the current pass
+    int pass_syncs = 0;       // exchange points queued since the last tq_comm_exchange_advance
 };
+
+// Exchange point carried by the kernel that consumes gathered data (the staging or norm
+// kernel behind a scattering projection): its first CTA publishes this rank's step flag to
+// every rank behind a system-scope fence - it runs after the projection kernel, peer stores
+// included, has completed - and every CTA waits, bounded, for all ranks' flags before it
+// reads. The step number is *base + k: base lives in device memory and advances once per
+// pass (tq_comm_exchange_advance), so a pass recorded in a CUDA graph can be replayed.
+// world == 0: no exchange.
+struct SyncArgs {
+    int *peer_flag[8];        // this rank's word in every rank's flag array
+    const int *mine;          // this rank's flag array
+    const int *base;
+    int k, world;
+    int *status;
+    unsigned long long limit_ns;
+};
+SyncArgs exchange_point();    // the next exchange point of the current pass (comm.cu)
 GatherState &gather_state();
 // One-warp kernel behind the GEMM on the library stream: stores `step` into this rank's flag
 // word on every rank once the GEMM has completed, then waits for every rank's flag.
@@ -71,13 +91,17 @@ void launch_quant_s8_pertoken(const float *d_x, const float *d_up, float *d_hidd
 void launch_rmsnorm_quant(float *d_out, const float *d_in, const uint16_t *d_w, int H, float eps,
                           float *d_partial, int8_t *d_q, int8_t *d_qp, float *d_scale,
                           int32_t *d_sum16, int32_t *d_sum32);
-void launch_quant_chunk(const float *d_x, int K, int T, int8_t *d_aq, float *d_as, int32_t *d_asum);
+void launch_quant_chunk(const float *d_x, int K, int T, int8_t *d_aq, float *d_as, int32_t *d_asum,
+                        const SyncArgs *sync = nullptr);
 void launch_rmsnorm_chunk(float *d_out, const float *d_in, const uint16_t *d_w, int H, int T,
-                          float eps);
+                          float eps, const SyncArgs *sync = nullptr);
 void launch_quant_chunk_s4(const float *d_x, int K, int T, uint8_t *d_aq4, float *d_as4,
                            int32_t *d_asum4);
 void launch_quant_chunk_pertoken(const float *d_x, int K, int T, int8_t *d_aq, float *d_as,
-                                 int32_t *d_asum, float *d_as_tok);
+                                 int32_t *d_asum, float *d_as_tok, const SyncArgs *sync = nullptr);
+// out[p][tok * ld + j] = silu(gate[tok][j]) * up[tok][j] for j < n, into ndst destinations
+void launch_silu_mul_scatter(float *const *dst, int ndst, const float *d_gate, const float *d_up, int T,
+                             int n, size_t ld);
 void launch_code_sums(const int8_t *d_aq, size_t blocks, int32_t *d_asum);
 void launch_silu_mul(float *d_out, const float *d_gate, const float *d_up, int N);
 void launch_add_inplace(float *d_x, const float *d_y, int N);
@@ -157,13 +181,15 @@ void launch_gemm_stream(const GemmArgs &a);
 bool gemm_dtc_covers(const GemmArgs &a);
 void launch_gemm_dtc(const GemmArgs &a);
 bool decode_prefers_mma();   // TQ_XPU_DECODE_MMA=1: keep decode batches on the mma.sync kernels
-int decode_dtc_min_tokens(); // fewest tokens the tcgen05 decode kernel takes (16; TQ_XPU_DTC_MIN_TOKENS)
-// Decode batches: 8 tokens stay on the mma.sync ring kernel (a tcgen05.mma of kind::i8 takes
-// the same 152 clocks whatever its N, which caps a 128-row x K32 MMA per 2 KB of packed
-// weights at 0.58 of the HBM roofline; the ring kernel is above that), 16..64 tokens go to
-// the tcgen05 decode kernel, everything else to the general mma kernel. Per-token calls
-// (mode 1) exist on the ring and the tcgen05 kernels only; returns false when neither takes
-// the call.
+int decode_dtc_min_tokens(); // fewest tokens the tcgen05 decode kernel takes by itself (TQ_XPU_DTC_MIN_TOKENS)
+// Decode batches in the reference's arithmetic stay on the mma.sync kernels (ring kernel for
+// windows of 8 tokens, streaming kernel otherwise): measured on B200 they are 3x faster than
+// the tcgen05 decode kernel, whose steps are bound by the issue latency of its barrier and
+// tcgen05 instructions, not by the tensor pipe (one tcgen05.mma of kind::i8 costs its issuing
+// thread about 150 clocks whatever its N). The tcgen05 kernel takes the per-token calls the
+// ring kernel does not (more than 8 tokens) and, with TQ_XPU_DTC_MIN_TOKENS=n, every decode
+// batch of at least n tokens. Everything else goes to the general mma kernel. Returns false
+// when no kernel takes a per-token call.
 inline bool launch_gemm(const GemmArgs &a) {
     const bool dtc = gemm_dtc_covers(a) && !decode_prefers_mma();
     if (dtc && a.T >= decode_dtc_min_tokens()) {
@@ -235,6 +261,35 @@ inline void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t s
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     TQ_CHECK(cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...));
+}
+
+// The exchange point of a consuming kernel (see SyncArgs); call after pdl_wait().
+__device__ __forceinline__ void exchange_sync(const SyncArgs &sa) {
+    if (sa.world == 0) return;
+    if ((int)threadIdx.x < sa.world) {
+        const int step = *sa.base + sa.k;
+        if (blockIdx.x == 0 && blockIdx.y == 0) {
+            __threadfence_system();
+            asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(sa.peer_flag[threadIdx.x]), "r"(step)
+                         : "memory");
+        }
+        unsigned long long t0 = 0;
+        for (unsigned polls = 0;; ++polls) {
+            int v;
+            asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(sa.mine + threadIdx.x) : "memory");
+            if (v - step >= 0) break;
+            if ((polls & 255u) == 255u) {
+                unsigned long long now;
+                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+                if (t0 == 0) t0 = now;
+                else if (now - t0 > sa.limit_ns) {
+                    atomicCAS(sa.status, 0, 32);
+                    break;
+                }
+            }
+        }
+    }
+    __syncthreads();
 }
 
 // exp() built only from IEEE add/mul/fma so that host and device agree bit-for-bit

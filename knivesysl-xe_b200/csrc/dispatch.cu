@@ -53,7 +53,7 @@ bool decode_prefers_mma() {
 int decode_dtc_min_tokens() {
     static const int v = [] {
         const char *e = getenv("TQ_XPU_DTC_MIN_TOKENS");
-        const int n = (e && *e) ? atoi(e) : 16;
+        const int n = (e && *e) ? atoi(e) : 1 << 20;     // default: never by itself
         return n < 8 ? 8 : n;
     }();
     return v;
@@ -414,7 +414,7 @@ void ensure_chunk_scratch(size_t blocks, int T) {
 // (x_mode 1 per (token, K32) block, 2 per token) - inside the GEMM kernel when the ring kernel
 // takes the call, else into the library's chunk scratch.
 int fanout_args(GemmArgs &a, const tq_qmma_weight_t *const *ws, int count, int T, const int *offsets,
-                int segments) {
+                int segments, const int *full_rows = nullptr) {
     if (!ws || count <= 0 || count > 4 || !ws[0]) return -1;
     const int K = ws[0]->K;
     const int ksh = ws[0]->s4_k64 ? 1 : 0;
@@ -433,7 +433,9 @@ int fanout_args(GemmArgs &a, const tq_qmma_weight_t *const *ws, int count, int T
         a.M[i] = w->M;
         a.goff[i + 1] = a.goff[i] + w->M / 16;
         int ms = 1;
-        const int rc = build_segments(w->M / 16, K / 32, T, offsets, segments, a.seg[i], ms);
+        // a column shard keeps the split count (hence the summation order) of the whole weight
+        const int rows = (full_rows && full_rows[i] > 0) ? full_rows[i] : w->M;
+        const int rc = build_segments(rows / 16, K / 32, T, offsets, segments, a.seg[i], ms);
         if (rc) return rc;
         a.max_splits = std::max(a.max_splits, ms);
     }
@@ -574,6 +576,90 @@ int x_gemm_w4a8_fanout_pertoken(const tq_qmma_weight_t *const *ws, float *const 
     a.mode = 1;
     if (a.T > 64) return -3;
     return launch_gemm(a) ? 0 : -3;
+}
+
+// Tensor-parallel form of the fan-out GEMM for decode batches. The weights are column shards
+// (x_w4_shard mode 0) of projections with full_rows[i] rows, and each is split like the whole
+// projection would be, so a shard's outputs are bit-identical to the same rows of the
+// unsharded call. slot < 0: outputs go to ys[i] ([T][M_i], local). slot >= 0: outputs go into
+// columns [col_off[i], col_off[i] + M_i) of the registered symmetric [T][ld] matrix `slot` of
+// EVERY rank (peer stores from the GEMM's epilogue); the kernel that consumes the matrix
+// carries the exchange point (x_quantize_act_chunk*_sync, x_rmsnorm_chunk_sync,
+// tq_comm_exchange_sync). d_as_tok != NULL selects per-token activation scales.
+int x_gemm_w4a8_fanout_tp(const tq_qmma_weight_t *const *ws, int count, const int8_t *d_aq,
+                          const float *d_as, const float *d_as_tok, const int32_t *d_asum, int T,
+                          const int *full_rows, float *const *ys, int slot, const size_t *col_off,
+                          size_t ld) {
+    GemmArgs a{};
+    const int rc = fanout_args(a, ws, count, T, nullptr, 0, full_rows);
+    if (rc) return rc;
+    if (!d_aq || !d_asum || (!d_as && !d_as_tok)) return -2;
+    a.aq = d_aq;
+    a.asum = d_asum;
+    a.as = d_as;
+    if (d_as_tok) {
+        a.as_tok = d_as_tok;
+        a.mode = 1;
+    }
+    if (slot < 0) {
+        if (!ys) return -2;
+        for (int i = 0; i < count; ++i) {
+            if (!ys[i]) return -2;
+            a.y[i] = ys[i];
+        }
+    } else {
+        GatherState &g = gather_state();
+        if (g.world < 1 || slot >= 16 || !col_off || !g.sym[slot][g.rank]) return -3;
+        a.npeer = g.world;
+        for (int i = 0; i < count; ++i) {
+            if (col_off[i] + (size_t)ws[i]->M > ld) return -2;
+            a.ld[i] = (int)ld;
+            for (int p = 0; p < g.world; ++p) a.ypeer[p][i] = g.sym[slot][p] + col_off[i];
+        }
+    }
+    if (a.T == 8 && gemm_ring_covers(a)) {
+        launch_gemm_stream(a);
+    } else if (gemm_dtc_covers(a)) {
+        launch_gemm_dtc(a);
+    } else {
+        return -21;
+    }
+    return 0;
+}
+
+// The staging and norm kernels behind a scattering projection: the same results as the calls
+// without _sync, after this rank's step flag has been published to all ranks and all ranks'
+// flags have arrived (bounded wait, status 10032). One exchange point per call.
+void x_quantize_act_chunk_sync(const float *d_x, int K, int T, int8_t *d_aq, float *d_as, int32_t *d_asum) {
+    if (!d_x || !d_aq || !d_as || !d_asum || K <= 0 || T <= 0 || (K % 32) != 0) return;
+    const SyncArgs sa = exchange_point();
+    launch_quant_chunk(d_x, K, T, d_aq, d_as, d_asum, &sa);
+}
+
+void x_quantize_act_chunk_pertoken_sync(const float *d_x, int K, int T, int8_t *d_aq, float *d_as,
+                                        int32_t *d_asum, float *d_as_tok) {
+    if (!d_x || !d_aq || !d_as || !d_asum || !d_as_tok || K <= 0 || T <= 0 || (K % 32) != 0) return;
+    const SyncArgs sa = exchange_point();
+    launch_quant_chunk_pertoken(d_x, K, T, d_aq, d_as, d_asum, d_as_tok, &sa);
+}
+
+void x_rmsnorm_chunk_sync(float *d_out, const float *d_in, const uint16_t *d_w, int H, int T, float eps) {
+    if (!d_out || !d_in || !d_w || H <= 0 || T <= 0) return;
+    const SyncArgs sa = exchange_point();
+    launch_rmsnorm_chunk(d_out, d_in, d_w, H, T, eps, &sa);
+}
+
+// silu(gate) * up of this rank's column slice [T][n] into columns [col_off, col_off + n) of the
+// symmetric [T][ld] matrix `slot` of every rank.
+int x_silu_mul_scatter(const float *d_gate, const float *d_up, int T, int n, int slot, size_t col_off,
+                       size_t ld) {
+    GatherState &g = gather_state();
+    if (!d_gate || !d_up || T <= 0 || n <= 0) return -1;
+    if (g.world < 1 || slot < 0 || slot >= 16 || !g.sym[slot][g.rank] || col_off + (size_t)n > ld) return -3;
+    float *dst[8];
+    for (int p = 0; p < g.world; ++p) dst[p] = g.sym[slot][p] + col_off;
+    launch_silu_mul_scatter(dst, g.world, d_gate, d_up, T, n, ld);
+    return 0;
 }
 
 int x_gemm_w4a8(const tq_qmma_weight_t *w, const int8_t *d_aq, const float *d_as,
@@ -877,6 +963,28 @@ int qwn_x_gemm_w4a8_fanout_gathered(const tq_qmma_weight_t *const *ws, int count
                                     const int8_t *d_aq, const float *d_as, const int32_t *d_asum,
                                     int T, size_t *half_offset_floats) {
     return x_gemm_w4a8_fanout_gathered(ws, count, d_aq, d_as, d_asum, T, half_offset_floats);
+}
+
+int qwn_x_gemm_w4a8_fanout_tp(const tq_qmma_weight_t *const *ws, int count, const int8_t *d_aq,
+                              const float *d_as, const float *d_as_tok, const int32_t *d_asum, int T,
+                              const int *full_rows, float *const *ys, int slot, const size_t *col_off,
+                              size_t ld) {
+    return x_gemm_w4a8_fanout_tp(ws, count, d_aq, d_as, d_as_tok, d_asum, T, full_rows, ys, slot, col_off, ld);
+}
+void qwn_x_quantize_act_chunk_sync(const float *d_x, int K, int T, int8_t *d_aq, float *d_as,
+                                   int32_t *d_asum) {
+    x_quantize_act_chunk_sync(d_x, K, T, d_aq, d_as, d_asum);
+}
+void qwn_x_quantize_act_chunk_pertoken_sync(const float *d_x, int K, int T, int8_t *d_aq, float *d_as,
+                                            int32_t *d_asum, float *d_as_tok) {
+    x_quantize_act_chunk_pertoken_sync(d_x, K, T, d_aq, d_as, d_asum, d_as_tok);
+}
+void qwn_x_rmsnorm_chunk_sync(float *d_out, const float *d_in, const uint16_t *d_w, int H, int T, float eps) {
+    x_rmsnorm_chunk_sync(d_out, d_in, d_w, H, T, eps);
+}
+int qwn_x_silu_mul_scatter(const float *d_gate, const float *d_up, int T, int n, int slot, size_t col_off,
+                           size_t ld) {
+    return x_silu_mul_scatter(d_gate, d_up, T, n, slot, col_off, ld);
 }
 
 int qwn_dbg_tile_dots_gemv(const tq_qmma_weight_t *w, int32_t *d_out) {

@@ -62,7 +62,7 @@ struct Cfg {
     // the producers fill one stage's slots while the other's are multiplied and promoted
     static constexpr int kSlots = 2 * RS;
     static constexpr int kRaw = TN == 32 ? 4 : 5;        // raw ring stages (all but one in flight)
-    static constexpr int MW = 2;                         // MMA-issuing warps (steps in turn)
+    static constexpr int MW = 4;                         // MMA-issuing warps (steps in turn)
     static constexpr int kThreads = (EW + 4 + MW) * 32;
     // step slot: A[2] expanded weights, B[2] activations, S[2] {as0, as1, asum0, asum1} per
     // token pair, W[2] scale words of the 128 rows
@@ -112,8 +112,12 @@ struct Task {
     int wi, rb, tw, s, kt0, cnt;
 };
 
+// Out of line (and the loops around the roles' inner bodies are not unrolled): the three roles
+// run different code on the same SM at once, so the kernel's code has to stay small enough
+// for the instruction cache - an early version of 100-190 KB per instantiation spent most of
+// its time fetching instructions.
 template <int MODE>
-__device__ __forceinline__ Task decode_task(const DtcParams &p, int t) {
+__device__ __noinline__ Task decode_task(const DtcParams &p, int t) {
     Task k;
     int wi = 0;
     while (wi + 1 < p.count && t >= p.toff[wi + 1]) ++wi;
@@ -181,7 +185,7 @@ __global__ void __launch_bounds__(Cfg<TN>::kThreads, 1) gemm_w4a8_dtc_kernel(con
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kSlots; ++s) {
-            mbar_init(full0 + s * 8, 128);       // every producer thread arrives once
+            mbar_init(full0 + s * 8, 4);         // one arrive per producer warp
             mbar_init(accfull0 + s * 8, 1);      // tcgen05.commit
             mbar_init(empty0 + s * 8, EW);       // one arrive per epilogue warp
         }
@@ -281,41 +285,21 @@ __global__ void __launch_bounds__(Cfg<TN>::kThreads, 1) gemm_w4a8_dtc_kernel(con
                         else fma2_acc(acc[qq * (NC / 2) + j], f, mul2(ws2, s4.x));
                     }
                 };
-                if (DTC_DBG(1)) {
-                } else if constexpr (CT == NC) {
-                    // both accumulators of the step are fetched together, re-armed, then promoted
-                    uint32_t d0[NC], d1[NC];
-                    if constexpr (NC == 8) {
-                        tmem_ld8(tcol, d0);
-                        if (nu == 2) tmem_ld8(tcol + TNP, d1);
-                        tmem_wait_ld8(d0);
-                        tmem_st8(tcol, cmagic);
-                        if (nu == 2) {
-                            tmem_wait_ld8(d1);
-                            tmem_st8(tcol + TNP, cmagic);
-                        }
-                    } else {
-                        tmem_ld16(tcol, d0);
-                        if (nu == 2) tmem_ld16(tcol + TNP, d1);
-                        tmem_wait_ld16(d0);
-                        tmem_st16(tcol, cmagic);
-                        if (nu == 2) {
-                            tmem_wait_ld16(d1);
-                            tmem_st16(tcol + TNP, cmagic);
-                        }
-                    }
-                    promote(0, 0, d0);
-                    if (nu == 2) promote(1, 0, d1);
-                } else {
-#pragma unroll
-                    for (int u = 0; u < 2; ++u) {
-                        if (u >= nu) break;
+                if (!DTC_DBG(1)) {
+#pragma unroll 1
+                    for (int u = 0; u < nu; ++u) {
 #pragma unroll
                         for (int qq = 0; qq < CT / NC; ++qq) {
                             uint32_t d[NC];
-                            tmem_ld16(tcol + u * TNP + qq * NC, d);
-                            tmem_wait_ld16(d);
-                            tmem_st16(tcol + u * TNP + qq * NC, cmagic);
+                            if constexpr (NC == 8) {
+                                tmem_ld8(tcol + u * TNP + qq * NC, d);
+                                tmem_wait_ld8(d);
+                                tmem_st8(tcol + u * TNP + qq * NC, cmagic);
+                            } else {
+                                tmem_ld16(tcol + u * TNP + qq * NC, d);
+                                tmem_wait_ld16(d);
+                                tmem_st16(tcol + u * TNP + qq * NC, cmagic);
+                            }
                             promote(u, qq, d);
                         }
                     }
@@ -348,6 +332,7 @@ __global__ void __launch_bounds__(Cfg<TN>::kThreads, 1) gemm_w4a8_dtc_kernel(con
 #pragma unroll
                 for (int j = 0; j < CT; ++j) {
                     float sum = 0.0f;
+#pragma unroll 1
                     for (int s2 = 0; s2 < S; ++s2)
                         sum = __fadd_rn(sum, __ldcg(base + (size_t)s2 * (128 * TN) + j * 128));
                     out[j] = sum;
@@ -362,6 +347,7 @@ __global__ void __launch_bounds__(Cfg<TN>::kThreads, 1) gemm_w4a8_dtc_kernel(con
                     const int tok = k.tw * TN + col0 + j;
                     float v = out[j];
                     if (MODE == 1) v = __fmul_rn(v, __ldg(p.as_tok + tok));
+#pragma unroll 1
                     for (int dd = 0; dd < p.ndst; ++dd) p.y[dd][k.wi][(size_t)tok * ld + row] = v;
                 }
             }
@@ -421,14 +407,14 @@ __global__ void __launch_bounds__(Cfg<TN>::kThreads, 1) gemm_w4a8_dtc_kernel(con
         c = f;
         {   // weights of the first stages go out before the wait on the previous kernel
             Iter f0 = f;
-#pragma unroll
+#pragma unroll 1
             for (int r = 0; r < kRaw - 1; ++r) {
                 fill_w(f0, r);
                 if (f0.valid) f0.next(p);
             }
         }
         pdl_wait();
-#pragma unroll
+#pragma unroll 1
         for (int r = 0; r < kRaw - 1; ++r) {
             fill_a(f, r);
             cp_async_commit();
@@ -479,7 +465,7 @@ __global__ void __launch_bounds__(Cfg<TN>::kThreads, 1) gemm_w4a8_dtc_kernel(con
             if (has_l) ll = *reinterpret_cast<const uint4 *>(rl + pr * 16);
             // (2) the stage's step slots must have been read out
             bool ok = !*(volatile int *)&dead_s;
-#pragma unroll
+#pragma unroll 1
             for (int st = 0; st < RS; ++st)
                 if (st < nst && ok)
                     ok = mbar_wait_bounded(empty0 + ((it + st) % kSlots) * 8,
@@ -537,9 +523,11 @@ __global__ void __launch_bounds__(Cfg<TN>::kThreads, 1) gemm_w4a8_dtc_kernel(con
             }
             DTC_STAMP(1, 3)
             fence_proxy_async_smem();      // generic-proxy stores -> visible to the MMA
-#pragma unroll
-            for (int st = 0; st < RS; ++st)
-                if (st < nst) mbar_arrive(full0 + ((it + st) % kSlots) * 8);
+            __syncwarp();                  // ... of every lane, before the warp's one arrival
+            if (lane == 0) {
+#pragma unroll 1
+                for (int st = 0; st < nst; ++st) mbar_arrive(full0 + ((it + st) % kSlots) * 8);
+            }
             DTC_STAMP(1, 1)
             it += nst;
             c.next(p);

@@ -768,13 +768,14 @@ gemm_w4a8_ring_kernel(const GemmArgs a, float *__restrict__ part, int *__restric
             out[3] = __fmul_rn(out[3], at.y);
         }
         const size_t row = (size_t)lg * 16 + r;
+        const size_t ldy = a.ld[wi] ? (size_t)a.ld[wi] : (size_t)M;      // row stride of y
         if (!a.npeer) {
             float *y = a.y[wi];
             const size_t tok = (size_t)tok0 + 2 * c;
-            y[tok * M + row] = out[0];
-            y[(tok + 1) * M + row] = out[1];
-            y[tok * M + row + 8] = out[2];
-            y[(tok + 1) * M + row + 8] = out[3];
+            y[tok * ldy + row] = out[0];
+            y[(tok + 1) * ldy + row] = out[1];
+            y[tok * ldy + row + 8] = out[2];
+            y[(tok + 1) * ldy + row + 8] = out[3];
         } else {
             // Fused all-gather: transpose the 16 x 8 tile so that a lane holds four consecutive
             // rows of one token and every peer gets 16-byte stores (64-byte runs).
@@ -785,7 +786,7 @@ gemm_w4a8_ring_kernel(const GemmArgs a, float *__restrict__ part, int *__restric
             xpose[(2 * c + 1) * 16 + r + 8] = out[3];
             __syncwarp();
             const float4 v = *reinterpret_cast<const float4 *>(xpose + lane * 4);
-            const size_t off = (size_t)(tok0 + (lane >> 2)) * M + (size_t)lg * 16 + (lane & 3) * 4;
+            const size_t off = (size_t)(tok0 + (lane >> 2)) * ldy + (size_t)lg * 16 + (lane & 3) * 4;
             for (int pi = 0; pi < a.npeer; ++pi)
                 *reinterpret_cast<float4 *>(a.ypeer[pi][wi] + off) = v;
         }
@@ -882,6 +883,8 @@ void launch_ntg(const GemmArgs &a) {
 
 bool gemm_stream_covers(const GemmArgs &a) {
     if (a.npeer < 0 || a.npeer > 8) return false;
+    for (int i = 0; i < a.count; ++i)
+        if (a.ld[i] && a.ld[i] != a.M[i] && a.T != 8) return false;   // only the ring kernel strides y
     if (a.count < 1 || a.T < 8 || a.T > 64 || (a.T % 8)) return false;
     if (a.max_splits > 16) return false;
     if (a.ksh && ((a.K >> 5) & 1)) return false;
@@ -994,6 +997,11 @@ bool gemm_ring_covers(const GemmArgs &a) {
 
 void launch_gemm_stream(const GemmArgs &a) {
     if (launch_ring(a)) return;
+    for (int i = 0; i < a.count; ++i)
+        if (a.ld[i] && a.ld[i] != a.M[i]) {      // only the ring kernel strides its output rows
+            note_error(cudaErrorInvalidValue, "launch_gemm_stream: strided output outside the ring kernel");
+            return;
+        }
     switch (window_groups(a)) {
         case 1: launch_ntg<1>(a); break;
         case 2: launch_ntg<2>(a); break;

@@ -155,9 +155,10 @@ template <bool PER_TOKEN>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 quant_chunk_kernel(const float *__restrict__ x, int K, int T, size_t blocks,
                    int8_t *__restrict__ aq, float *__restrict__ as, int32_t *__restrict__ asum,
-                   const float *__restrict__ as_tok) {
+                   const float *__restrict__ as_tok, const SyncArgs sync) {
     pdl_trigger();   // the next kernel may be scheduled (its weight prefetch, its launch latency)
     pdl_wait();      // ... while this one waits here for everything launched before it
+    exchange_sync(sync);
     const size_t blk = (size_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (blk >= blocks) return;
@@ -185,10 +186,11 @@ quant_chunk_kernel(const float *__restrict__ x, int K, int T, size_t blocks,
 // binary tree over the 256 partial sums (the reference leaves that order to the SYCL runtime).
 __global__ void __launch_bounds__(256)
 rmsnorm_chunk_kernel(float *__restrict__ out, const float *__restrict__ in,
-                     const uint16_t *__restrict__ w, int H, float eps) {
+                     const uint16_t *__restrict__ w, int H, float eps, const SyncArgs sync) {
     __shared__ float p[256];
     pdl_trigger();
     pdl_wait();
+    exchange_sync(sync);
     const int tid = threadIdx.x;
     const float *row = in + (size_t)blockIdx.x * H;
     float ss = 0.0f;
@@ -237,9 +239,10 @@ quant_chunk_s4_kernel(const float *__restrict__ x, int K, int T, size_t blocks,
 
 // Per-token absmax -> scale (one block per token row).
 __global__ void __launch_bounds__(256)
-token_scale_kernel(const float *__restrict__ x, int K, float *__restrict__ as_tok) {
+token_scale_kernel(const float *__restrict__ x, int K, float *__restrict__ as_tok, const SyncArgs sync) {
     pdl_trigger();   // the next kernel may be scheduled (its weight prefetch, its launch latency)
     pdl_wait();      // ... while this one waits here for everything launched before it
+    exchange_sync(sync);
     __shared__ float wmax[8];
     const float *row = x + (size_t)blockIdx.x * K;
     float m = -INFINITY;
@@ -261,9 +264,11 @@ token_scale_kernel(const float *__restrict__ x, int K, float *__restrict__ as_to
 __global__ void __launch_bounds__(1024)
 quant_chunk_pertoken_fused_kernel(const float *__restrict__ x, int K, int T,
                                   int8_t *__restrict__ aq, float *__restrict__ as,
-                                  int32_t *__restrict__ asum, float *__restrict__ as_tok) {
+                                  int32_t *__restrict__ asum, float *__restrict__ as_tok,
+                                  const SyncArgs sync) {
     pdl_trigger();
     pdl_wait();
+    exchange_sync(sync);
     __shared__ float wmax[32];
     __shared__ float s_scale;
     const int tok = blockIdx.x;
@@ -310,9 +315,11 @@ quant_chunk_pertoken_fused_kernel(const float *__restrict__ x, int K, int T,
 __global__ void __launch_bounds__(1024)
 quant_chunk_pertoken_regs_kernel(const float *__restrict__ x, int K, int T,
                                  int8_t *__restrict__ aq, float *__restrict__ as,
-                                 int32_t *__restrict__ asum, float *__restrict__ as_tok) {
+                                 int32_t *__restrict__ asum, float *__restrict__ as_tok,
+                                 const SyncArgs sync) {
     pdl_trigger();
     pdl_wait();
+    exchange_sync(sync);
     __shared__ float wmax[32];
     __shared__ float s_scale;
     const int tok = blockIdx.x;
@@ -384,6 +391,22 @@ __global__ void silu_mul_kernel(float *__restrict__ out, const float *__restrict
     if (i < N) out[i] = silu_mul_f(gate[i], up[i]);
 }
 
+struct ScatterDst {
+    float *p[8];
+};
+// silu(gate) * up of a rank's column slice, stored into the same columns of every rank's
+// [T][ld] matrix (plain peer stores; the consumer's exchange point orders them).
+__global__ void silu_mul_scatter_kernel(ScatterDst dst, int ndst, const float *__restrict__ gate,
+                                        const float *__restrict__ up, int T, int n, size_t ld) {
+    pdl_trigger();
+    pdl_wait();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= T * n) return;
+    const int tok = i / n, j = i - tok * n;
+    const float v = silu_mul_f(gate[i], up[i]);
+    for (int d = 0; d < ndst; ++d) dst.p[d][(size_t)tok * ld + j] = v;
+}
+
 __global__ void add_inplace_kernel(float *__restrict__ x, const float *__restrict__ y, int N) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < N) x[i] = __fadd_rn(x[i], y[i]);
@@ -430,19 +453,24 @@ void launch_rmsnorm_quant(float *d_out, const float *d_in, const uint16_t *d_w, 
     TQ_LAUNCH_CHECK("rmsnorm_quant_kernel");
 }
 
+namespace {
+const SyncArgs kNoSync = {};
+}
+
 void launch_quant_chunk(const float *d_x, int K, int T, int8_t *d_aq, float *d_as,
-                        int32_t *d_asum) {
+                        int32_t *d_asum, const SyncArgs *sync) {
     const size_t blocks = (size_t)(K / 32) * (size_t)T;
     if (!blocks) return;
     const unsigned grid = (unsigned)((blocks + kWarpsPerBlock - 1) / kWarpsPerBlock);
     launch_pdl(quant_chunk_kernel<false>, dim3(grid), dim3(kWarpsPerBlock * 32), 0, d_x, K, T,
-               blocks, d_aq, d_as, d_asum, (const float *)nullptr);
+               blocks, d_aq, d_as, d_asum, (const float *)nullptr, sync ? *sync : kNoSync);
     TQ_LAUNCH_CHECK("quant_chunk_kernel");
 }
 
 void launch_rmsnorm_chunk(float *d_out, const float *d_in, const uint16_t *d_w, int H, int T,
-                          float eps) {
-    launch_pdl(rmsnorm_chunk_kernel, dim3(T), dim3(256), 0, d_out, d_in, d_w, H, eps);
+                          float eps, const SyncArgs *sync) {
+    launch_pdl(rmsnorm_chunk_kernel, dim3(T), dim3(256), 0, d_out, d_in, d_w, H, eps,
+               sync ? *sync : kNoSync);
     TQ_LAUNCH_CHECK("rmsnorm_chunk_kernel");
 }
 
@@ -457,26 +485,27 @@ void launch_quant_chunk_s4(const float *d_x, int K, int T, uint8_t *d_aq4, float
 }
 
 void launch_quant_chunk_pertoken(const float *d_x, int K, int T, int8_t *d_aq, float *d_as,
-                                 int32_t *d_asum, float *d_as_tok) {
+                                 int32_t *d_asum, float *d_as_tok, const SyncArgs *sync) {
+    const SyncArgs sa = sync ? *sync : kNoSync;
     const size_t blocks = (size_t)(K / 32) * (size_t)T;
     if (!blocks) return;
     if (T <= 32 && K <= 8192) {
         launch_pdl(quant_chunk_pertoken_regs_kernel, dim3(T), dim3(1024), 0, d_x, K, T, d_aq, d_as,
-                   d_asum, d_as_tok);
+                   d_asum, d_as_tok, sa);
         TQ_LAUNCH_CHECK("quant_chunk_pertoken_regs_kernel");
         return;
     }
     if (T <= 32) {
         launch_pdl(quant_chunk_pertoken_fused_kernel, dim3(T), dim3(1024), 0, d_x, K, T, d_aq, d_as,
-                   d_asum, d_as_tok);
+                   d_asum, d_as_tok, sa);
         TQ_LAUNCH_CHECK("quant_chunk_pertoken_fused_kernel");
         return;
     }
-    launch_pdl(token_scale_kernel, dim3(T), dim3(256), 0, d_x, K, d_as_tok);
+    launch_pdl(token_scale_kernel, dim3(T), dim3(256), 0, d_x, K, d_as_tok, sa);
     TQ_LAUNCH_CHECK("token_scale_kernel");
     const unsigned grid = (unsigned)((blocks + kWarpsPerBlock - 1) / kWarpsPerBlock);
     launch_pdl(quant_chunk_kernel<true>, dim3(grid), dim3(kWarpsPerBlock * 32), 0, d_x, K, T,
-               blocks, d_aq, d_as, d_asum, (const float *)d_as_tok);
+               blocks, d_aq, d_as, d_asum, (const float *)d_as_tok, kNoSync);
     TQ_LAUNCH_CHECK("quant_chunk_kernel<pertoken>");
 }
 
@@ -490,6 +519,15 @@ void launch_code_sums(const int8_t *d_aq, size_t blocks, int32_t *d_asum) {
 void launch_silu_mul(float *d_out, const float *d_gate, const float *d_up, int N) {
     silu_mul_kernel<<<(N + 255) / 256, 256, 0, stream()>>>(d_out, d_gate, d_up, N);
     TQ_LAUNCH_CHECK("silu_mul_kernel");
+}
+
+void launch_silu_mul_scatter(float *const *dst, int ndst, const float *d_gate, const float *d_up, int T,
+                             int n, size_t ld) {
+    ScatterDst d{};
+    for (int i = 0; i < ndst && i < 8; ++i) d.p[i] = dst[i];
+    launch_pdl(silu_mul_scatter_kernel, dim3((T * n + 255) / 256), dim3(256), 0, d, ndst, d_gate, d_up, T, n,
+               ld);
+    TQ_LAUNCH_CHECK("silu_mul_scatter_kernel");
 }
 
 void launch_add_inplace(float *d_x, const float *d_y, int N) {

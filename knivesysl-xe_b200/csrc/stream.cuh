@@ -44,6 +44,19 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
     return ok;
 }
 
+// Non-blocking test of a phase (mbarrier.test_wait never suspends the thread).
+__device__ __forceinline__ uint32_t mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok;
+}
+
 // Bounded wait: polls until the phase completes or limit_ns of wall clock have passed
 // (%globaltimer; the host passes tq::wait_limit_ns(), two seconds unless
 // tq_set_wait_limit_ms changed it), then records `code` in *status (first failure wins) and
@@ -53,18 +66,17 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, int *status,
-                                                  int code, uint64_t limit_ns) {
+// The polling loop is kept out of line: a pipelined kernel has many waits, and a copy of the
+// loop with its clock arithmetic at each of them multiplies the kernel's code size until its
+// roles evict one another from the instruction cache.
+static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, int *status, int code,
+                                                   uint64_t limit_ns) {
     // mbarrier.try_wait suspends the thread in hardware for a bounded time while the phase is
     // incomplete, so polling it back to back costs few issue slots and adds no latency when
-    // the phase completes (a sleep between polls would add its length to every hand-off of a
-    // pipeline whose steps are shorter than the sleep). The clock is read every 2048 polls.
+    // the phase completes. The clock is read every 2048 polls.
     uint64_t t0 = 0;
     for (uint32_t polls = 1;; ++polls) {
         if (mbar_try_wait(bar, parity)) return true;
-#ifdef TQ_WAIT_SLEEP_NS
-        __nanosleep(TQ_WAIT_SLEEP_NS);
-#endif
         if ((polls & 2047u) == 0) {
             const uint64_t now = global_timer_ns();
             if (t0 == 0) t0 = now;
@@ -73,6 +85,11 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
     }
     atomicCAS(status, 0, code);
     return false;
+}
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, int *status,
+                                                  int code, uint64_t limit_ns) {
+    if (mbar_test_wait(bar, parity)) return true;      // the common case in a pipeline that runs ahead
+    return mbar_wait_slow(bar, parity, status, code, limit_ns);
 }
 
 __device__ __forceinline__ uint64_t l2_policy_evict_first() {
