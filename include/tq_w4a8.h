@@ -172,8 +172,9 @@ int qwn_x_gemm_w8a8(const tq_qmma_weight_t *w, const int8_t *d_aq, const float *
                     int T);
 
 /* xpu/src/kernels_core.cpp:164-252: tier dispatchers used by the layer bodies: s8_ready
- * weights go to the W8A8 GEMV, s4_ready ones (K16, K32 or K64 scales) to the W4A8 GEMV; the
- * scalar E2M3 tier is not built (-20). */
+ * weights go to the W8A8 GEMV, s4_ready ones (K16, K32 or K64 scales) to the W4A8 GEMV, and a
+ * weight that still holds its E2M3 payload to the scalar GEMV (return codes -3..-6 as the
+ * reference's validation). */
 int qwn_x_gemv_qmma(const tq_qmma_weight_t *w, const float *d_x, float *d_y);
 int qwn_x_gemv_qmma_add(const tq_qmma_weight_t *w, const float *d_x, const float *d_residual,
                         float *d_y);
@@ -288,7 +289,37 @@ double qwn_gemv_bench(const tq_qmma_weight_t *w, int iters);              /* us 
 double qwn_gemm_bench(const tq_qmma_weight_t *w, int tokens, int iters);  /* us per call */
 int qwn_gemm_check(const tq_qmma_weight_t *w, int tokens, double *worst_cos, double *worst_rel);
 int qwn_specwave_check(const tq_qmma_weight_t *w);
+/* xpu/src/kernels_dpas.cpp:2613-2693: column shards concatenated must be bit-identical to the
+ * full GEMV (which needs every shard to keep the full weight's split count, as in the
+ * reference), row (K) shards' partial outputs added must agree at cos >= 0.9999 (leg skipped
+ * where x_w4_shard refuses the split). 0 pass, -4 a leg failed. */
 int qwn_shard_check(const tq_qmma_weight_t *w, int tp);
+/* xpu/src/kernels_dpas.cpp:2462-2611: a family of projections, each sharded two ways in its
+ * intended mode (0 column, 1 row, 2 replicate) with its row blocks (groups + 3*i, ngroups[i]
+ * entries; 0 = one block). Returns the number of failures. */
+int qwn_shard_check_all(const tq_qmma_weight_t *const *ws, const int *modes, const int *groups,
+                        const int *ngroups, int count);
+/* xpu/src/kernels_dpas.cpp:2696-2737: scalar E2M3 GEMV (the weight must still hold its payload)
+ * against the W4A8 GEMV after repacking in `mode` (0 / 1 / 2; -1 = 2 when TQ_XPU_K64=1 else 0);
+ * passes at cos >= 0.99. The weight stays repacked. 0 pass, -2 already repacked, -6 below
+ * the gate. */
+int qwn_w4_check(tq_qmma_weight_t *w, int mode, double *cos_out, double *max_rel_out);
+
+/* Load-time pieces that need no model file. qwn_tqf_read_qmma: one quantised-matrix record of a
+ * TQF1 container (read_qmma, xpu/src/tqf_loader.cpp:186-255: uint32 scale_rows, uint32
+ * scale_cols, fp32 block scales, then M/16 * K/32 fragment tiles of 384 bytes) from host memory
+ * into a weight record on the device; `flags` are the container's header flags
+ * (xpu/src/tq_common.hpp:35-44). 0, or -1 with a message. tq_selector_has / tq_repack_tier_for /
+ * qwn_repack_by_policy: the selector grammar and tier policy of xpu/src/tqf_loader.cpp:40-57,
+ * 997-1058 (TQ_XPU_W4A8, TQ_XPU_W8, TQ_XPU_W4_K16, TQ_XPU_K64): tier -1 keep E2M3, 8 int8, 1 / 2 /
+ * 0 int4 with K16 / K64 / K32 scales; qwn_repack_by_policy returns the applied tier or
+ * -100 + rc of the failed repack call. */
+int qwn_tqf_read_qmma(const void *bytes, size_t nbytes, int M, int K, uint32_t flags, tq_qmma_weight_t *w,
+                      size_t *consumed);
+void qwn_tqf_free_qmma(tq_qmma_weight_t *w);
+int tq_selector_has(const char *selector, const char *key);
+int tq_repack_tier_for(const char *kind);
+int qwn_repack_by_policy(tq_qmma_weight_t *w, const char *kind);
 
 /* Issue-rate measurement of tcgen05.mma kind::i8 (M128 x N x K32, int32 accumulators in TMEM,
  * no epilogue) on every SM: the measured dense int8 peak in TOP/s that the prefill GEMM's

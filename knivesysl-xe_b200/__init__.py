@@ -97,6 +97,12 @@ SIGNATURES = {
     "qwn_gemv_bench": (_d, [_WP, _i]), "qwn_gemm_bench": (_d, [_WP, _i, _i]),
     "qwn_gemm_check": (_i, [_WP, _i, C.POINTER(_d), C.POINTER(_d)]),
     "qwn_specwave_check": (_i, [_WP]), "qwn_shard_check": (_i, [_WP, _i]),
+    "qwn_shard_check_all": (_i, [C.POINTER(_WP), C.POINTER(_i), C.POINTER(_i), C.POINTER(_i), _i]),
+    "qwn_w4_check": (_i, [_WP, _i, C.POINTER(_d), C.POINTER(_d)]),
+    "qwn_tqf_read_qmma": (_i, [_vp, _sz, _i, _i, C.c_uint32, _WP, C.POINTER(_sz)]),
+    "qwn_tqf_free_qmma": (None, [_WP]),
+    "tq_selector_has": (_i, [C.c_char_p, C.c_char_p]), "tq_repack_tier_for": (_i, [C.c_char_p]),
+    "qwn_repack_by_policy": (_i, [_WP, C.c_char_p]),
     "qwn_x_gemv_w4a8_static": (_i, [_WP, _vp, _vp]), "qwn_static_max_k": (_i, []),
     "qwn_tc_int8_peak": (_d, [_i]), "qwn_tc_int8_probe": (_d, [_i, _i, _i, _vp]),
     "tq_comm_unique_id": (_i, [_vp]), "tq_comm_init": (_i, [_vp, _i, _i]),

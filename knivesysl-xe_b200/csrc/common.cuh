@@ -87,7 +87,7 @@ void launch_quant_s8(const float *d_x, const float *d_up, float *d_hidden, int K
                      int8_t *d_qp, float *d_scale, int32_t *d_sum16, int32_t *d_sum32, bool silu);
 void launch_quant_s8_pertoken(const float *d_x, const float *d_up, float *d_hidden, int K,
                               int8_t *d_q, int8_t *d_qp, float *d_scale, int32_t *d_sum16,
-                              int32_t *d_sum32, bool silu);
+                              int32_t *d_sum32, float *d_partial, bool silu);
 void launch_rmsnorm_quant(float *d_out, const float *d_in, const uint16_t *d_w, int H, float eps,
                           float *d_partial, int8_t *d_q, int8_t *d_qp, float *d_scale,
                           int32_t *d_sum16, int32_t *d_sum32);
@@ -220,6 +220,9 @@ struct GemmTcArgs {
     int out_bf16;
 };
 int launch_gemm_tc(const GemmTcArgs &a);   // returns 0, or <0 when the shape is not covered
+
+// gemv_e2m3.cu: the scalar tier of a weight that still holds its E2M3 payload
+int launch_gemv_e2m3(const tq_qmma_weight_t *w, const float *d_x, const float *d_residual, float *d_y);
 
 // repack.cu
 void launch_w4_repack(const uint8_t *d_payload, const float *d_bs, int scale_cols, int M, int K,

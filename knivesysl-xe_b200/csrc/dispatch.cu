@@ -207,7 +207,8 @@ void x_prepare_gemv_act_s8_pertoken(const float *d_x, int K) {
     if (!d_x || K <= 0 || (K % 32) != 0) return;
     ensure_act_scratch(K);
     ActScratch &s = act_scratch();
-    launch_quant_s8_pertoken(d_x, nullptr, nullptr, K, s.q, s.qp, s.scale, s.sum16, s.sum32, false);
+    launch_quant_s8_pertoken(d_x, nullptr, nullptr, K, s.q, s.qp, s.scale, s.sum16, s.sum32, s.norm_partial,
+                             false);
     s.prepared_K = K;
 }
 
@@ -215,7 +216,8 @@ void x_silu_mul_quant_pertoken(float *d_out, const float *d_gate, const float *d
     if (!d_out || !d_gate || !d_up || K <= 0 || (K % 32) != 0) return;
     ensure_act_scratch(K);
     ActScratch &s = act_scratch();
-    launch_quant_s8_pertoken(d_gate, d_up, d_out, K, s.q, s.qp, s.scale, s.sum16, s.sum32, true);
+    launch_quant_s8_pertoken(d_gate, d_up, d_out, K, s.q, s.qp, s.scale, s.sum16, s.sum32, s.norm_partial,
+                             true);
     s.prepared_K = K;
 }
 
@@ -349,7 +351,7 @@ int x_gemv_qmma(const tq_qmma_weight_t *w, const float *d_x, float *d_y) {
     if (w->M <= 0 || w->K <= 0 || w->Mt <= 0 || w->Kt <= 0) return -2;
     if (w->s8_ready) return x_gemv_w8a8(w, d_x, d_y);
     if (w->s4_ready) return x_gemv_w4a8(w, d_x, d_y);
-    return -20;                               // scalar E2M3 tier is not built
+    return launch_gemv_e2m3(w, d_x, nullptr, d_y);   // not repacked yet: the scalar E2M3 tier
 }
 
 int x_gemv_qmma_add(const tq_qmma_weight_t *w, const float *d_x, const float *d_residual,
@@ -357,7 +359,9 @@ int x_gemv_qmma_add(const tq_qmma_weight_t *w, const float *d_x, const float *d_
     if (!w || !d_x || !d_residual || !d_y) return -1;
     if (w->s8_ready) return x_gemv_w8a8_add(w, d_x, d_residual, d_y);
     if (w->s4_ready) return x_gemv_w4a8_add(w, d_x, d_residual, d_y);
-    return -20;
+    // the reference adds the residual with a separate x_add_inplace: the same single fp32 add
+    if (w->M <= 0 || w->K <= 0 || w->Mt <= 0 || w->Kt <= 0) return -2;
+    return launch_gemv_e2m3(w, d_x, d_residual, d_y);
 }
 
 int x_gemv_qmma_prepared(const tq_qmma_weight_t *w, const float *d_x, float *d_y,
@@ -365,7 +369,7 @@ int x_gemv_qmma_prepared(const tq_qmma_weight_t *w, const float *d_x, float *d_y
     if (!w || !d_x || !d_y) return -1;
     if (w->s8_ready) return x_gemv_w8a8_prepared(w, d_y, d_residual);
     if (w->s4_ready) return x_gemv_w4a8_prepared(w, d_y, d_residual);
-    return -20;
+    return d_residual ? x_gemv_qmma_add(w, d_x, d_residual, d_y) : x_gemv_qmma(w, d_x, d_y);
 }
 
 // ---- chunk staging + GEMM ------------------------------------------------------------------

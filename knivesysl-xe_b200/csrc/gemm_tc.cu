@@ -8,25 +8,27 @@
 //
 // Mapping. Weights are the M side of the MMA (128 output rows = 128 TMEM lanes), tokens the
 // N side (128 per CTA tile), K = 32 per instruction = one k-tile, so one MMA produces exactly
-// the per-k-tile int32 dots the reference promotes. A CTA (13 warps, one per SM, persistent
+// the per-k-tile int32 dots the reference promotes. A CTA (12 warps, one per SM, persistent
 // over tiles) runs three roles connected by mbarriers (10 operand slots in shared memory, 4
 // accumulator buffers in TMEM):
-//  * producers (4 warps, thread = weight row): load the row's 16 packed bytes of a k-tile,
-//    expand the nibbles to int8 bytes q+8 with two logic ops per word and store them as the
+//  * producers (2 warps, thread = two weight rows): load a row's 16 packed bytes of a k-tile,
+//    expand the nibbles to signed int8 bytes (three ops per word) and store them as the
 //    two 16-byte K-chunks of the row in the canonical no-swizzle K-major core-matrix layout
 //    (even-k codes first, then odd-k: any fixed permutation of k inside a tile is exact for
 //    an integer dot, and the activation image uses the same one); one thread starts bulk
 //    (TMA) copies of the activation image of the tile (4 KiB) and of its per-token
 //    {as, as, asum, asum} pairs (1 KiB), prepared by a pre-pass in exactly that layout;
-//  * one MMA thread: tcgen05.mma (M=128, N=128, K=32) into accumulator slot b. The slot was
-//    pre-filled with the bit pattern of 12582912.0f, and the MMA accumulates on top of it,
-//    so the exact int32 dot comes back as an fp32 bit pattern that one add converts;
-//    tcgen05.commit signals the epilogue;
-//  * epilogue (8 warps, thread = weight row x 64 tokens): tcgen05.ld the slot, re-arm it
-//    with the bias pattern (tcgen05.st), then per token pair on packed f32x2 instructions:
-//    f = fma(-(z+8), asum, bits - 12582912) (exact), acc = fma(f, ws*as, acc); 64 fp32
-//    accumulators stay in registers for the whole K loop and are stored at the end
-//    (coalesced over rows).
+//  * two MMA threads (in two warps, promote groups in turn): tcgen05.mma (M=128, N=128, K=32) into accumulator slot b (the first MMA of a
+//    promote group overwrites the slot, a second one accumulates); tcgen05.commit signals
+//    the epilogue;
+//  * epilogue (8 warps, thread = weight row x 64 tokens): two 32-column tcgen05.ld per
+//    promote (every tcgen05 instruction costs its issuing thread on the order of a hundred
+//    clocks, so the epilogue issues as few as it can and stores nothing back), then per
+//    token pair: the int32 dot becomes fp32 exactly by adding the bit pattern of 12582912.0f
+//    as an integer and subtracting 12582912.0f as a float; f = fma(-z, asum, d) (exact;
+//    skipped while every zero point of the warp's rows is 0, i.e. for symmetric weights),
+//    acc = fma(f, ws*as, acc); 64 fp32 accumulators stay in registers for the whole K loop
+//    and are stored at the end (coalesced over rows).
 // The epilogue is the wall, as on the reference's hardware: 2 issue slots per output per
 // k-tile against 64 tensor-core clocks per 128x128x32 MMA.
 //
@@ -37,6 +39,7 @@
 #include <cuda_bf16.h>
 
 #include <algorithm>
+#include <type_traits>
 
 namespace tq {
 
@@ -46,18 +49,28 @@ constexpr int kTM = 128;                 // weight rows per tile (TMEM lanes)
 constexpr int kTN = 128;                 // tokens per tile (accumulator columns)
 constexpr int kNB = 4;                   // accumulator buffers in TMEM (4 x 128 columns)
 constexpr int kNS = 10;                  // operand slots in shared memory
-constexpr int kPB = 8;                   // k-tiles a producer thread loads per batch
+constexpr int kPB = 4;                   // k-tiles a producer thread loads per batch (two rows each)
 constexpr int kABytes = kTM * 32;        // expanded int8 weights of one k-tile
 constexpr int kBBytes = kTN * 32;        // int8 activations of one k-tile
 constexpr int kSBytes = kTN / 2 * 16;    // {as0, as1, asum0, asum1} per token pair
 constexpr int kSlotBytes = kABytes + kBBytes + kSBytes;
-constexpr int kEpiWarps = 8, kProdWarps = 4;
-constexpr int kThreads = (kEpiWarps + kProdWarps + 1) * 32;
-constexpr int kSmemBytes = 120 * 1024;   // > half an SM's shared memory: one CTA per SM,
-                                         // which the 512-column TMEM allocation requires
+// Twelve warps: three share a scheduler, so a thread may hold up to 168 registers
+// (the epilogue's 64 accumulators and two 32-column TMEM loads do not fit the 128 that a
+// fourth warp per scheduler would leave).
+constexpr int kEpiWarps = 8, kProdWarps = 2;
+// Two MMA-issuing warps take the promote groups in turn: the wait, tcgen05.mma and
+// tcgen05.commit of one k-tile cost the issuing thread several hundred clocks (each tcgen05
+// instruction about 150, whatever the MMA's N), more than the epilogue needs per k-tile in
+// the per-token modes, so one issuing thread was the wall there.
+constexpr int kMmaWarps = 2;
+constexpr int kThreads = (kEpiWarps + kProdWarps + kMmaWarps) * 32;
+constexpr int kRawStages = 4;             // raw ring of the producers: batches of kPB k-tiles
+constexpr int kRawBytes = kPB * 2048;     // 128 rows x 16 packed bytes per k-tile
+constexpr int kSmemBytes = kNS * kSlotBytes + kRawStages * kRawBytes;   // > half an SM's shared
+                                         // memory: one CTA per SM, which the 512-column TMEM
+                                         // allocation requires
 
-// instruction descriptor: D = s32 (2), A and B signed 8 bit (1) (the expanded weights are
-// 0..15), both K-major, N >> 3 at bit 17, M >> 4 at bit 24
+// instruction descriptor: D = s32 (2), A and B signed 8 bit (1), both K-major, N >> 3 at bit 17, M >> 4 at bit 24
 constexpr uint32_t kIdesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kTN >> 3) << 17) |
                             ((uint32_t)(kTM >> 4) << 24);
 
@@ -71,6 +84,9 @@ struct TcParams {
     const float *as_tok;     // per-token scales (PERTOK kernels)
     int *status;
     unsigned long long wait_ns;   // limit of every mbarrier wait
+#ifdef TQ_TC_TRACE
+    long long *trace;
+#endif
     int M, Kt, ksh, T, Tpad, out_bf16;
 };
 
@@ -164,13 +180,22 @@ gemm_tc_prepass_s4_kernel(const uint8_t *__restrict__ aq4, const float *__restri
 }
 
 constexpr int kWaitMma = 21, kWaitEpi = 22, kWaitProd = 23;   // status codes of failed waits
+#ifdef TQ_TC_TRACE
+#define TC_STAMP(idx, which)                                                                  \
+    if (blockIdx.x == 0 && p.trace && (idx) < 256 && threadIdx.x == 0) p.trace[(idx) * 8 + (which)] = clock64();
+#else
+#define TC_STAMP(idx, which)
+#endif
+
+// Four two's-complement nibbles (the low nibble of each byte of w) -> four signed bytes.
+__device__ __forceinline__ uint32_t nib_s8(uint32_t w) { return __vsub4(nib_plus8(w), 0x08080808u); }
 
 // GW = k-tiles accumulated in TMEM before one fp32 promote (1: the reference's arithmetic with
 // a scale per (token, K32); 2: K64 weight groups with per-token activation scales, or - not
 // PERTOK - with one activation scale per (token, K64): the W4A4 arithmetic). PERTOK:
 // the activation scale is applied once at the end (y = acc * as_tok).
 template <int GW, bool PERTOK>
-__global__ void __launch_bounds__(kThreads, 1) gemm_w4a8_tc_kernel(const TcParams p) {
+__global__ void __maxnreg__(168) gemm_w4a8_tc_kernel(const TcParams p) {
     extern __shared__ __align__(1024) unsigned char smem[];
     __shared__ uint64_t bars[2 * kNS + 2 * kNB];   // full[kNS], empty[kNS], accfull[kNB], accempty[kNB]
     __shared__ uint32_t tmem_base_s;
@@ -202,20 +227,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_w4a8_tc_kernel(const TcParam
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_s;
 
-    // epilogue warps arm every accumulator slot with the fp32 bias bit pattern
-    if (warp < kEpiWarps) {
-        const uint32_t lane_base = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
-        const int chalf = (warp >> 2) * 64;
-#pragma unroll
-        for (int b = 0; b < kNB; ++b)
-#pragma unroll
-            for (int q = 0; q < 4; ++q)
-                tmem_st16_const(lane_base + b * kTN + chalf + q * 16, (uint32_t)kMagicBits);
-        tmem_wait_st();
-    }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
     pdl_trigger();
     pdl_wait();      // everything below reads the images an earlier kernel wrote
 
@@ -248,8 +259,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_w4a8_tc_kernel(const TcParam
                 unpack_scale(scw, zp, ws);
                 if (kt + GW < Kt) scw = __ldg(sc + (size_t)((kt + GW) >> p.ksh) * 16);
                 const f32x2 ws2 = pack2(ws, ws);
-                const float nzf = (float)(-(zp + 8));
+                const float nzf = (float)(-zp);
                 const f32x2 nz2 = pack2(nzf, nzf);
+                // symmetric weights (every zero point of the warp's rows is 0) need no
+                // zero-point term at all: the weights enter the MMA as true signed bytes
+                const bool anyz = __any_sync(0xffffffffu, zp != 0);
+                TC_STAMP(ig, 0)
                 bool ok = !*(volatile int *)&dead_s && mbar_wait_bounded(acc0 + b * 8, ph, p.status, kWaitEpi, p.wait_ns);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) {
@@ -257,6 +272,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_w4a8_tc_kernel(const TcParam
                     break;
                 }
                 tc_fence_after();
+                TC_STAMP(ig, 1)
                 const ulonglong2 *sv = reinterpret_cast<const ulonglong2 *>(
                                            smem + (size_t)sl * kSlotBytes + kABytes + kBBytes) +
                                        (chalf >> 1);
@@ -265,36 +281,54 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_w4a8_tc_kernel(const TcParam
                 const ulonglong2 *sv1 = reinterpret_cast<const ulonglong2 *>(
                                             smem + (size_t)sl1 * kSlotBytes + kABytes + kBBytes) +
                                         (chalf >> 1);
-                // The four 16-column loads are software-pipelined: the load of chunk q+1 is in
-                // flight while chunk q is re-armed and promoted.
-                uint32_t da[16], db[16];
+                // Two 32-column loads, the second in flight while the first is promoted. The
+                // accumulator holds the plain int32 dot (the group's first MMA overwrites it), so
+                // nothing has to be stored back; adding the bit pattern of 12582912.0f to the
+                // integer and subtracting 12582912.0f from the result as a float converts it
+                // exactly (|d| < 2^22) on the integer and packed-fp32 pipes.
+                uint32_t da[32], db[32];
                 const uint32_t tcol = lane_base + b * kTN + chalf;
-                auto promote = [&](const int q, uint32_t (&d)[16]) {
-                    tmem_st16_const(tcol + q * 16, (uint32_t)kMagicBits);   // re-arm for the next MMA
+                // Straight-line code per variant (ANYZ is a compile-time tag): a test of `anyz`
+                // inside the unrolled pair loop splits it into one basic block per pair, and the
+                // pairs' short dependency chains then run one after the other.
+                auto promote = [&](auto anyz_tag, const int q, uint32_t (&d)[32]) {
+                    constexpr bool ANYZ = decltype(anyz_tag)::value;
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const ulonglong2 s4 = sv[q * 8 + j];      // {as0, as1}, {asum0, asum1}
-                        f32x2 smf = s4.y;
-                        if (GW == 2) smf = add2(smf, sv1[q * 8 + j].y);   // exact: small integers
-                        const f32x2 f = fma2(nz2, smf,
-                                             add2(pack2i((int)d[2 * j], (int)d[2 * j + 1]), neg_magic2));
-                        if (PERTOK) fma2_acc(acc[q * 8 + j], f, ws2);
-                        else fma2_acc(acc[q * 8 + j], f, mul2(ws2, s4.x));
+                    for (int j = 0; j < 16; ++j) {
+                        f32x2 f = add2(pack2i((int)d[2 * j] + kMagicBits, (int)d[2 * j + 1] + kMagicBits),
+                                       neg_magic2);
+                        if (PERTOK) {
+                            if (ANYZ) {
+                                f32x2 smf = sv[q * 16 + j].y;                  // {asum0, asum1}
+                                if (GW == 2) smf = add2(smf, sv1[q * 16 + j].y);   // exact: small integers
+                                f = fma2(nz2, smf, f);
+                            }
+                            fma2_acc(acc[q * 16 + j], f, ws2);
+                        } else {
+                            const ulonglong2 s4 = sv[q * 16 + j];      // {as0, as1}, {asum0, asum1}
+                            if (ANYZ) {
+                                f32x2 smf = s4.y;
+                                if (GW == 2) smf = add2(smf, sv1[q * 16 + j].y);
+                                f = fma2(nz2, smf, f);
+                            }
+                            fma2_acc(acc[q * 16 + j], f, mul2(ws2, s4.x));
+                        }
                     }
                 };
-                tmem_ld16(tcol, da);
-                tmem_wait_ld16(da);
-                tmem_ld16(tcol + 16, db);
-                promote(0, da);
-                tmem_wait_ld16(db);
-                tmem_ld16(tcol + 32, da);
-                promote(1, db);
-                tmem_wait_ld16(da);
-                tmem_ld16(tcol + 48, db);
-                promote(2, da);
-                tmem_wait_ld16(db);
-                promote(3, db);
-                tmem_wait_st();
+                auto promote_any = [&](const int q, uint32_t (&d)[32]) {
+                    if (anyz) promote(std::true_type{}, q, d);
+                    else promote(std::false_type{}, q, d);
+                };
+                tmem_ld32(tcol, da);
+                tmem_wait_ld32(da);
+                TC_STAMP(ig, 2)
+                tmem_ld32(tcol + 32, db);
+                promote_any(0, da);
+                TC_STAMP(ig, 3)
+                tmem_wait_ld32(db);
+                promote_any(1, db);
+                TC_STAMP(ig, 4)
+                TC_STAMP(ig, 5)
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) {
@@ -302,6 +336,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_w4a8_tc_kernel(const TcParam
                     mbar_arrive(empty0 + sl * 8);        // the producers may refill the slot(s)
                     if (GW == 2) mbar_arrive(empty0 + sl1 * 8);
                 }
+                TC_STAMP(ig, 6)
             }
             if (*(volatile int *)&dead_s) break;
             // store: thread = row, 64 tokens; rows are contiguous in y, so a warp writes 128 B
@@ -327,87 +362,105 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_w4a8_tc_kernel(const TcParam
         }
     } else if (warp < kEpiWarps + kProdWarps) {
         // ================================ producers =====================================
-        const int pr = threadIdx.x - kEpiWarps * 32;       // row inside the tile
-        // destination of this row's two K-chunks in the core-matrix layout
+        const int pr = threadIdx.x - kEpiWarps * 32;       // rows pr and pr + 64 of the tile
+        // destination of a row's two K-chunks in the core-matrix layout (row pr + 64: 8 row
+        // groups further)
         const uint32_t a_off = (uint32_t)((pr >> 3) * kSbo + (pr & 7) * 16);
-        // Weight words are fetched kPB k-tiles at a time into one of two register batches:
-        // the next batch (of this tile, or the first of the next tile) is in flight while the
-        // current one is expanded.
-        auto tile_src = [&](int tile) {
-            const int row = (tile % row_blocks) * kTM + pr;
-            return p.codes + ((size_t)(row >> 4) * Kt) * 256 + (row & 15) * 16;
-        };
-        auto load_batch = [&](uint4 (&w)[kPB], const uint8_t *src, int kt0) {
-#pragma unroll
-            for (int j = 0; j < kPB; ++j)
-                if (kt0 + j < Kt) w[j] = ldg_stream_v4(src + (size_t)(kt0 + j) * 256);
-        };
-        uint4 w0[kPB], w1[kPB];
-        int par = 0;
+        // Packed weights travel through a private raw ring in shared memory (cp.async, kRawStages
+        // batches of kPB k-tiles, all but one in flight): a thread reads back only what it
+        // copied itself, so the ring needs no barrier, and the loop below is the producers'
+        // whole steady-state code (register double-buffering needed two copies of it, and the
+        // kernel's roles were evicting one another from the instruction cache).
+        unsigned char *raw = smem + kNS * kSlotBytes;
+        const uint32_t raw_u = smem_u + kNS * kSlotBytes;
+        const uint64_t pol = l2_policy_evict_first();
         const int nbatch = (Kt + kPB - 1) / kPB;
-        if (blockIdx.x < ntiles) load_batch(w0, tile_src(blockIdx.x), 0);
-        for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
-            const int tb = tile / row_blocks;
-            const uint8_t *src = tile_src(tile);
-            for (int kb = 0; kb < nbatch; ++kb, par ^= 1) {
-                auto batch = [&](uint4 (&cur)[kPB], uint4 (&nxt)[kPB]) {
-                    if (kb + 1 < nbatch) load_batch(nxt, src, (kb + 1) * kPB);
-                    else if (tile + (int)gridDim.x < ntiles)
-                        load_batch(nxt, tile_src(tile + gridDim.x), 0);
+        const int my_tiles = (ntiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+        const int total = my_tiles * nbatch;               // batches this CTA produces
+        const size_t half_rows = (size_t)4 * Kt * 256;     // 64 rows = 4 row-groups further
+        auto fill = [&](int g) {
+            if (g < total) {
+                const int tile = blockIdx.x + (g / nbatch) * gridDim.x, kt0 = (g % nbatch) * kPB;
+                const int row = (tile % row_blocks) * kTM + pr;
+                const uint8_t *src = p.codes + ((size_t)(row >> 4) * Kt + kt0) * 256 + (row & 15) * 16;
+                const uint32_t dst = raw_u + (uint32_t)(g % kRawStages) * kRawBytes + pr * 16;
 #pragma unroll
-                    for (int j = 0; j < kPB; ++j) {
-                        const int kt = kb * kPB + j;
-                        if (kt >= Kt || *(volatile int *)&dead_s) break;
-                        const int sl = it % kNS;
-                        const uint32_t ph = ((uint32_t)(it / kNS) & 1u) ^ 1u;   // first pass is free
-                        bool ok = mbar_wait_bounded(empty0 + sl * 8, ph, p.status, kWaitProd, p.wait_ns);
-                        ok = __all_sync(0xffffffffu, ok);
-                        if (!ok) {
-                            dead_s = 1;
-                            break;
-                        }
-                        unsigned char *slot = smem + (size_t)sl * kSlotBytes;
-                        const uint4 c4 = cur[j];
-                        const uint4 lo = make_uint4(nib_plus8(c4.x), nib_plus8(c4.y),
-                                                    nib_plus8(c4.z), nib_plus8(c4.w));
-                        const uint4 hi = make_uint4(nib_plus8(c4.x >> 4), nib_plus8(c4.y >> 4),
-                                                    nib_plus8(c4.z >> 4), nib_plus8(c4.w >> 4));
-                        *reinterpret_cast<uint4 *>(slot + a_off) = lo;             // even-k chunk
-                        *reinterpret_cast<uint4 *>(slot + a_off + kLbo) = hi;      // odd-k chunk
-                        fence_proxy_async_smem();   // generic-proxy stores -> visible to the MMA
-                        const uint32_t fb = full0 + sl * 8;
-                        if (pr == (sl & 3) * 32) {
-                            // One bulk copy brings the activation image of this (k-tile, token
-                            // block); this thread's arrival also announces its bytes. The
-                            // issuing thread rotates over the producer warps: one thread
-                            // sustains only about two bulk copies in flight.
-                            mbar_expect_tx(fb, kBBytes + kSBytes);
-                            bulk_g2s_plain(
-                                smem_u + sl * kSlotBytes + kABytes,
-                                p.img + ((size_t)kt * (p.Tpad / kTN) + tb) * (kBBytes + kSBytes),
-                                kBBytes + kSBytes, fb);
-                        } else {
-                            mbar_arrive(fb);
-                        }
-                        ++it;
+                for (int j = 0; j < kPB; ++j)
+                    if (kt0 + j < Kt) {
+                        cp_async16(dst + j * 2048, src + (size_t)j * 256, pol);
+                        cp_async16(dst + j * 2048 + 1024, src + half_rows + (size_t)j * 256, pol);
                     }
-                };
-                if (par) batch(w1, w0);
-                else batch(w0, w1);
-                if (*(volatile int *)&dead_s) break;
             }
-            if (*(volatile int *)&dead_s) break;
+            cp_async_commit();
+        };
+#pragma unroll 1
+        for (int g = 0; g < kRawStages - 1; ++g) fill(g);
+#pragma unroll 1
+        for (int g = 0; g < total; ++g) {
+            cp_async_wait<kRawStages - 2>();
+            fill(g + kRawStages - 1);                      // into the stage consumed last
+            const int tb = (blockIdx.x + (g / nbatch) * gridDim.x) / row_blocks, kb = g % nbatch;
+            // The whole batch behind ONE round of waits, one proxy fence and one round of
+            // arrivals.
+            const int nk = min(kPB, Kt - kb * kPB);
+            bool ok = !*(volatile int *)&dead_s;
+#pragma unroll 1
+            for (int j = 0; j < nk && ok; ++j)
+                ok = mbar_wait_bounded(empty0 + ((it + j) % kNS) * 8, ((uint32_t)((it + j) / kNS) & 1u) ^ 1u,
+                                       p.status, kWaitProd, p.wait_ns);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) {
+                dead_s = 1;
+                break;
+            }
+            const unsigned char *rs = raw + (size_t)(g % kRawStages) * kRawBytes + pr * 16;
+#pragma unroll
+            for (int j = 0; j < kPB; ++j) {
+                if (j >= nk) break;
+                unsigned char *slot = smem + (size_t)((it + j) % kNS) * kSlotBytes;
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const uint4 c4 = *reinterpret_cast<const uint4 *>(rs + j * 2048 + h * 1024);
+                    // nibble -> q + 8 (one logic op per four codes) -> q (one SIMD byte subtract)
+                    const uint4 lo = make_uint4(nib_s8(c4.x), nib_s8(c4.y), nib_s8(c4.z), nib_s8(c4.w));
+                    const uint4 hi = make_uint4(nib_s8(c4.x >> 4), nib_s8(c4.y >> 4), nib_s8(c4.z >> 4),
+                                                nib_s8(c4.w >> 4));
+                    *reinterpret_cast<uint4 *>(slot + a_off + h * 8 * kSbo) = lo;          // even-k chunk
+                    *reinterpret_cast<uint4 *>(slot + a_off + h * 8 * kSbo + kLbo) = hi;   // odd-k chunk
+                }
+            }
+            fence_proxy_async_smem();   // generic-proxy stores -> visible to the MMA
+#pragma unroll 1
+            for (int j = 0; j < nk; ++j) {
+                const int sl = (it + j) % kNS;
+                const uint32_t fb = full0 + sl * 8;
+                if (pr == j * 16) {
+                    // One bulk copy brings the activation image of this (k-tile, token block);
+                    // this thread's arrival also announces its bytes. Each k-tile of the batch
+                    // has its own issuing thread: one thread sustains only about two bulk
+                    // copies in flight.
+                    mbar_expect_tx(fb, kBBytes + kSBytes);
+                    bulk_g2s_plain(smem_u + sl * kSlotBytes + kABytes,
+                                   p.img + ((size_t)(kb * kPB + j) * (p.Tpad / kTN) + tb) * (kBBytes + kSBytes),
+                                   kBBytes + kSBytes, fb);
+                } else {
+                    mbar_arrive(fb);
+                }
+            }
+            it += nk;
         }
+        cp_async_wait<0>();
     } else {
         // ================================ MMA issuer ====================================
         for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
             for (int kt = 0; kt < Kt; ++kt, ++it) {
                 const int ig = it / GW;
+                if (ig % kMmaWarps != warp - (kEpiWarps + kProdWarps)) continue;   // the other warp's group
                 const int b = ig % kNB, sl = it % kNS;
                 bool ok = !*(volatile int *)&dead_s &&
                           mbar_wait_bounded(full0 + sl * 8, (uint32_t)(it / kNS) & 1u, p.status, kWaitMma, p.wait_ns);
                 // ... and, for the first k-tile of a group, the accumulator buffer has been
-                // read out and re-armed
+                // read out
                 if (it % GW == 0)
                     ok = ok && mbar_wait_bounded(accempty0 + b * 8, ((uint32_t)(ig / kNB) & 1u) ^ 1u,
                                                  p.status, kWaitMma, p.wait_ns);
@@ -419,8 +472,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_w4a8_tc_kernel(const TcParam
                 tc_fence_after();
                 if (lane == 0) {
                     const uint32_t a_addr = smem_u + sl * kSlotBytes;
+                    // the first MMA of a promote group overwrites the accumulator
                     tc_mma_i8(tmem_base + b * kTN, smem_desc(a_addr), smem_desc(a_addr + kABytes),
-                              kIdesc, 1u);
+                              kIdesc, (it % GW) ? 1u : 0u);
                     if (it % GW == GW - 1) tc_commit(acc0 + b * 8);
                 }
                 __syncwarp();
@@ -442,6 +496,9 @@ struct TcScratch {
 } g_tc;
 
 int g_tc_sms = 0;
+#ifdef TQ_TC_TRACE
+long long *g_tc_trace = nullptr;
+#endif
 
 }  // namespace
 
@@ -486,6 +543,15 @@ int launch_gemm_tc(const GemmTcArgs &a) {
     p.codes = a.codes; p.scales = a.scales; p.img = g_tc.img; p.y = a.y;
     p.status = device_status_word();
     p.wait_ns = wait_limit_ns();
+#ifdef TQ_TC_TRACE
+    {
+        static long long *tr = nullptr;
+        if (!tr) tr = static_cast<long long *>(tq_dev_alloc(256 * 8 * 8, "tc.trace"));
+        TQ_CHECK(cudaMemsetAsync(tr, 0, 256 * 8 * 8, stream()));
+        p.trace = tr;
+        g_tc_trace = tr;
+    }
+#endif
     p.M = a.M; p.Kt = Kt; p.ksh = a.ksh; p.T = a.T; p.Tpad = Tpad; p.out_bf16 = a.out_bf16;
     const int ntiles = (a.M / kTM) * (Tpad / kTN);
     const int grid = std::min(g_tc_sms, ntiles);
@@ -503,3 +569,11 @@ int launch_gemm_tc(const GemmTcArgs &a) {
 }
 
 }  // namespace tq
+
+#ifdef TQ_TC_TRACE
+extern "C" int qwn_dbg_tc_trace(long long *host_out) {
+    if (!tq::g_tc_trace) return -1;
+    tq_d2h(host_out, tq::g_tc_trace, 256 * 8 * 8);
+    return 0;
+}
+#endif

@@ -46,49 +46,65 @@ quant_s8_kernel(const float *__restrict__ x, const float *__restrict__ up,
 }
 
 // Decode staging with ONE scale for the whole row (absmax / 127), replicated into every K32
-// slot of the prepared scratch so that the GEMV kernels read it like per-block scales. One
-// CTA: pass 1 finds the row maximum (and, SILU, stores hidden = silu(gate) * up), pass 2
-// quantises; a thread reads back only elements it wrote itself.
+// slot of the prepared scratch so that the GEMV kernels read it like per-block scales. Two
+// small launches spread over the machine (one CTA for the whole row took 14 us at K = 17408):
+// the first stores hidden = silu(gate) * up (SILU) and the maximum of each 256 values, the
+// second takes the maximum of those maxima (a maximum does not depend on the order) and
+// quantises.
 template <bool SILU>
-__global__ void __launch_bounds__(1024)
-quant_s8_pertoken_kernel(const float *__restrict__ x, const float *__restrict__ up,
-                         float *__restrict__ hidden, int K, int8_t *__restrict__ q,
-                         int8_t *__restrict__ qp, float *__restrict__ scale,
-                         int32_t *__restrict__ sum16, int32_t *__restrict__ sum32) {
+__global__ void __launch_bounds__(256)
+rowmax_partial_kernel(const float *__restrict__ x, const float *__restrict__ up, float *__restrict__ hidden,
+                      int K, float *__restrict__ part) {
     pdl_trigger();
     pdl_wait();
-    __shared__ float wmax[32];
-    __shared__ float s_scale;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __shared__ float wmax[8];
+    const int i = blockIdx.x * 256 + threadIdx.x;
     float m = -INFINITY;
-    for (int i = threadIdx.x; i < K; i += 1024) {
+    if (i < K) {
         float v = x[i];
         if (SILU) {
             v = silu_mul_f(v, up[i]);
             hidden[i] = v;
         }
-        m = fmaxf(m, fabsf(v));
+        m = fabsf(v);
     }
     m = warp_max(m);
-    if (lane == 0) wmax[warp] = m;
+    if ((threadIdx.x & 31) == 0) wmax[threadIdx.x >> 5] = m;
     __syncthreads();
-    if (warp == 0) {
-        const float t = warp_max(wmax[lane]);
-        if (lane == 0) s_scale = (t > 0.0f) ? __fdiv_rn(t, 127.0f) : 1.0f;
+    if (threadIdx.x == 0) {
+        float t = wmax[0];
+#pragma unroll
+        for (int w = 1; w < 8; ++w) t = fmaxf(t, wmax[w]);
+        part[blockIdx.x] = t;
+    }
+}
+
+__global__ void __launch_bounds__(256)
+quant_s8_rowscale_kernel(const float *__restrict__ v_in, int K, const float *__restrict__ part, int nblk,
+                         int8_t *__restrict__ q, int8_t *__restrict__ qp, float *__restrict__ scale,
+                         int32_t *__restrict__ sum16, int32_t *__restrict__ sum32) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ float s_scale;
+    if (threadIdx.x < 32) {
+        float t = -INFINITY;
+        for (int b = threadIdx.x; b < nblk; b += 32) t = fmaxf(t, part[b]);
+        t = warp_max(t);
+        if (threadIdx.x == 0) s_scale = (t > 0.0f) ? __fdiv_rn(t, 127.0f) : 1.0f;
     }
     __syncthreads();
     const float s = s_scale;
-    for (int b = warp; b < (K >> 5); b += 32) {
-        const float v = SILU ? hidden[b * 32 + lane] : x[b * 32 + lane];
-        const int qv = quantise_one(v, s);
-        const int hs = half_sum16(qv);
-        if (lane == 0) scale[b] = s;
-        if ((lane & 15) == 0) sum16[b * 2 + (lane >> 4)] = hs;
-        const int other = __shfl_xor_sync(0xffffffffu, hs, 16);
-        if (lane == 0) sum32[b] = hs + other;
-        q[b * 32 + lane] = (int8_t)qv;
-        qp[b * 32 + permuted_pos(lane)] = (int8_t)qv;
-    }
+    const int i = blockIdx.x * 256 + threadIdx.x;
+    if (i >= K) return;                      // K % 32 == 0: whole warps leave together
+    const int lane = threadIdx.x & 31, b = i >> 5;
+    const int qv = quantise_one(v_in[i], s);
+    const int hs = half_sum16(qv);
+    if (lane == 0) scale[b] = s;
+    if ((lane & 15) == 0) sum16[b * 2 + (lane >> 4)] = hs;
+    const int other = __shfl_xor_sync(0xffffffffu, hs, 16);
+    if (lane == 0) sum32[b] = hs + other;
+    q[i] = (int8_t)qv;
+    qp[b * 32 + permuted_pos(lane)] = (int8_t)qv;
 }
 
 // Sum of squares per 256 elements: xor-butterfly in each warp, then the eight
@@ -431,15 +447,18 @@ void launch_quant_s8(const float *d_x, const float *d_up, float *d_hidden, int K
 
 void launch_quant_s8_pertoken(const float *d_x, const float *d_up, float *d_hidden, int K,
                               int8_t *d_q, int8_t *d_qp, float *d_scale, int32_t *d_sum16,
-                              int32_t *d_sum32, bool silu) {
+                              int32_t *d_sum32, float *d_partial, bool silu) {
     if (K < 32) return;
+    const int nblk = (K + 255) / 256;
     if (silu)
-        launch_pdl(quant_s8_pertoken_kernel<true>, dim3(1), dim3(1024), 0, d_x, d_up, d_hidden, K,
-                   d_q, d_qp, d_scale, d_sum16, d_sum32);
+        launch_pdl(rowmax_partial_kernel<true>, dim3(nblk), dim3(256), 0, d_x, d_up, d_hidden, K, d_partial);
     else
-        launch_pdl(quant_s8_pertoken_kernel<false>, dim3(1), dim3(1024), 0, d_x,
-                   (const float *)nullptr, (float *)nullptr, K, d_q, d_qp, d_scale, d_sum16, d_sum32);
-    TQ_LAUNCH_CHECK("quant_s8_pertoken_kernel");
+        launch_pdl(rowmax_partial_kernel<false>, dim3(nblk), dim3(256), 0, d_x, (const float *)nullptr,
+                   (float *)nullptr, K, d_partial);
+    TQ_LAUNCH_CHECK("rowmax_partial_kernel");
+    launch_pdl(quant_s8_rowscale_kernel, dim3(nblk), dim3(256), 0, silu ? (const float *)d_hidden : d_x, K,
+               (const float *)d_partial, nblk, d_q, d_qp, d_scale, d_sum16, d_sum32);
+    TQ_LAUNCH_CHECK("quant_s8_rowscale_kernel");
 }
 
 void launch_rmsnorm_quant(float *d_out, const float *d_in, const uint16_t *d_w, int H, float eps,

@@ -77,6 +77,9 @@ static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity
     uint64_t t0 = 0;
     for (uint32_t polls = 1;; ++polls) {
         if (mbar_try_wait(bar, parity)) return true;
+#ifdef TQ_WAIT_SLEEP_NS
+        __nanosleep(TQ_WAIT_SLEEP_NS);
+#endif
         if ((polls & 2047u) == 0) {
             const uint64_t now = global_timer_ns();
             if (t0 == 0) t0 = now;

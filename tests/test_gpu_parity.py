@@ -325,8 +325,8 @@ def test_gemv_errors(lib, pkg, wl):
     assert lib.qwn_x_gemv_w4a8_fanout(pkg.weight_array([w]), pkg.ptr_array([y]), 5) == -1
     w.rec.s8_ready = 1                                   # flagged W8A8 but no W8 buffers
     assert lib.qwn_x_gemv_qmma(w.ref, x.ptr, y.ptr) == -1
-    w.rec.s8_ready = w.rec.s4_ready = 0                  # scalar E2M3 tier: not built
-    assert lib.qwn_x_gemv_qmma(w.ref, x.ptr, y.ptr) == -20
+    w.rec.s8_ready = w.rec.s4_ready = 0                  # scalar E2M3 tier, but no payload
+    assert lib.qwn_x_gemv_qmma(w.ref, x.ptr, y.ptr) == -3
 
 
 # ---------------------------------------------------------------- GEMM
@@ -896,3 +896,18 @@ def test_gemm_pertoken_decode(lib, pkg, orc, wl, Ms, K, ksh, T):
     assert y1.to_numpy(np.float32).tobytes() == ys[0].to_numpy(np.float32).tobytes()
     assert lib.qwn_x_gemm_w4a8_pertoken(ws[0].ref, aq.ptr, at.ptr, asum.ptr, y1.ptr, T, 1) == -3
     assert lib.tq_last_error() == 0
+
+
+@pytest.mark.gpu
+def test_gemm_cases_on_the_tcgen05_decode_kernel():
+    """The decode-batch cases of test_gemm_int32_dots_and_fp32 once more with the tcgen05 decode
+    kernel forced for every batch of 8..64 tokens (TQ_XPU_DTC_MIN_TOKENS=8, read once per
+    process, hence the child process): byte-identical to the oracle there too."""
+    import os
+    import subprocess
+    import sys
+    env = dict(os.environ, TQ_XPU_DTC_MIN_TOKENS="8")
+    out = subprocess.run([sys.executable, "-m", "pytest", os.path.abspath(__file__), "-q", "-m", "gpu", "-x",
+                          "-k", "test_gemm_int32_dots_and_fp32 or test_gemm_fanout_equals_per_weight"],
+                         env=env, capture_output=True, text=True, timeout=1200)
+    assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-2000:]
