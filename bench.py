@@ -428,9 +428,9 @@ class Prefill:
              "pertoken_fp32": "scale per token, fp32 out", "pertoken_bf16": "scale per token, bf16 out",
              "w4a4_fp32": "int4 activations per (token, K64) (x_gemm_w4a4), fp32 out"}
 
-    def __init__(self, ctx, name, mode, shared=None):
+    def __init__(self, ctx, name, mode, shared=None, M=I_FF, T=4096):
         self.ctx, self.name, self.mode = ctx, name, mode
-        self.M, self.K, self.T, self.group = I_FF, H, 4096, 64
+        self.M, self.K, self.T, self.group = M, H, T, 64
         pkg, lib = ctx.pkg, ctx.lib
         if shared is None:
             shared = {}
@@ -445,7 +445,7 @@ class Prefill:
         self.aq, self.as_, self.asum, self.as_tok = shared["stg"]
         self.y = shared["y"]
         self.out_bytes = self.T * self.M * (2 if mode.endswith("bf16") else 4)
-        self.off = (C.c_int * 5)(0, 1024, 2048, 3072, 4096)
+        self.off = (C.c_int * 5)(0, self.T // 4, self.T // 2, 3 * self.T // 4, self.T)
         self.weight_bytes = ctx.wl.weight_bytes(self.M, self.K, 64)
         self.ops = 2.0 * self.T * self.M * self.K
         self.launches_per_step = 3      # staging, activation image pre-pass, GEMM
@@ -782,6 +782,11 @@ def build_cases(ctx, which):
             c = Prefill(ctx, n, mode, shared)
             shared = c.shared
             out[n] = (c, "gemm_w4a8_tc_kernel", "tensor")
+    # profiler targets only: the same kernel on 4736 x 5120, 1024 tokens (296 tiles, two per SM)
+    for mode in Prefill.MODES:
+        n = f"prefill_small_{mode}"
+        if which is not None and n in which:
+            out[n] = (Prefill(ctx, n, mode, None, M=4736, T=1024), "gemm_w4a8_tc_kernel", "tensor")
     return out
 
 

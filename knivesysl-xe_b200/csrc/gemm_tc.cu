@@ -1,36 +1,41 @@
-// gemm_tc.cu — prefill W4A8 GEMM on the sm_100a tensor cores: tcgen05.mma kind::i8 with
-// int32 accumulators in tensor memory (TMEM).
+// gemm_tc.cu — prefill W4A8 GEMM on the sm_100a tensor cores: tcgen05.mma kind::f16 on
+// integer-valued fp16 operands, fp32 accumulators in tensor memory (TMEM).
 //
 // Replaces gemm_rc16 / the unsplit path of x_gemm_w4a8 (xpu/src/kernels_dpas.cpp:1255-1332,
 // 1371-1378): Y[tok][n] = sum over k-tiles, ascending, of (float)(d - z*asum) * (ws*as) with
 // d the exact int32 dot of one 16-row x K32 tile, accumulated with fma into one fp32
 // accumulator per output - the arithmetic and the order of the reference.
 //
+// Why the f16 pipe for an integer dot. The 4-bit codes (-8..7) and the int8 activations are
+// exact in fp16, their products (< 2^11) and a k-tile's sum of them (< 2^16; a K64 group:
+// < 2^17) are exact in the tensor core's fp32 accumulation, so the accumulator IS (float)d,
+// bit for bit, and the epilogue promotes it with one fma per output. With kind::i8 the
+// accumulator is int32 and every output costs an integer add and a float add more per k-tile
+// on the CUDA cores (the exact conversion), which is what bounded that version of the
+// kernel: the tensor pipe, at half the int8 rate, is still far from being the wall.
+//
 // Mapping. Weights are the M side of the MMA (128 output rows = 128 TMEM lanes), tokens the
-// N side (128 per CTA tile), K = 32 per instruction = one k-tile, so one MMA produces exactly
-// the per-k-tile int32 dots the reference promotes. A CTA (12 warps, one per SM, persistent
-// over tiles) runs three roles connected by mbarriers (10 operand slots in shared memory, 4
-// accumulator buffers in TMEM):
-//  * producers (2 warps, thread = two weight rows): load a row's 16 packed bytes of a k-tile,
-//    expand the nibbles to signed int8 bytes (three ops per word) and store them as the
-//    two 16-byte K-chunks of the row in the canonical no-swizzle K-major core-matrix layout
-//    (even-k codes first, then odd-k: any fixed permutation of k inside a tile is exact for
-//    an integer dot, and the activation image uses the same one); one thread starts bulk
-//    (TMA) copies of the activation image of the tile (4 KiB) and of its per-token
-//    {as, as, asum, asum} pairs (1 KiB), prepared by a pre-pass in exactly that layout;
-//  * two MMA threads (in two warps, promote groups in turn): tcgen05.mma (M=128, N=128, K=32) into accumulator slot b (the first MMA of a
-//    promote group overwrites the slot, a second one accumulates); tcgen05.commit signals
-//    the epilogue;
+// N side (128 per CTA tile), a k-tile (K = 32) is two K = 16 instructions, so one accumulator
+// read-out yields exactly the per-k-tile dots the reference promotes. A CTA (12 warps, one
+// per SM, persistent over tiles) runs three roles connected by mbarriers (10 operand slots
+// in shared memory, 4 accumulator buffers in TMEM):
+//  * producers (2 warps, thread = two weight rows): cp.async the rows' packed bytes of a
+//    batch of k-tiles into a private ring, expand each 32-bit word (8 codes) to 8 fp16 values
+//    (shift, one logic op that isolates two nibbles and ors in the exponent of 1024 with the
+//    sign bit flipped, one packed subtract of 1032) and store them as the four 16-byte
+//    K-chunks of the row in the canonical no-swizzle K-major core-matrix layout (inside a
+//    chunk the codes sit in the order 0,4,1,5,2,6,3,7: any fixed permutation of k inside an
+//    instruction is exact for a dot, and the activation image uses the same one); one thread
+//    starts the bulk (TMA) copy of the activation image of the tile (8 KiB of fp16) and of its
+//    per-token {as, as, asum, asum} pairs (1 KiB), prepared by a pre-pass in that layout;
+//  * two MMA threads (in two warps, promote groups in turn): two tcgen05.mma (M=128, N=128,
+//    K=16) per k-tile into accumulator slot b (the first MMA of a promote group overwrites
+//    the slot); tcgen05.commit signals the epilogue;
 //  * epilogue (8 warps, thread = weight row x 64 tokens): two 32-column tcgen05.ld per
-//    promote (every tcgen05 instruction costs its issuing thread on the order of a hundred
-//    clocks, so the epilogue issues as few as it can and stores nothing back), then per
-//    token pair: the int32 dot becomes fp32 exactly by adding the bit pattern of 12582912.0f
-//    as an integer and subtracting 12582912.0f as a float; f = fma(-z, asum, d) (exact;
-//    skipped while every zero point of the warp's rows is 0, i.e. for symmetric weights),
-//    acc = fma(f, ws*as, acc); 64 fp32 accumulators stay in registers for the whole K loop
-//    and are stored at the end (coalesced over rows).
-// The epilogue is the wall, as on the reference's hardware: 2 issue slots per output per
-// k-tile against 64 tensor-core clocks per 128x128x32 MMA.
+//    promote, then per token pair f = fma(-z, asum, d) (exact; skipped while every zero
+//    point of the warp's rows is 0, i.e. for symmetric weights), acc = fma(f, ws*as, acc);
+//    64 fp32 accumulators stay in registers for the whole K loop and are stored at the end
+//    (coalesced over rows).
 //
 // Every mbarrier wait is bounded; on expiry the kernel records a status word, stops
 // issuing work, still frees its TMEM and returns.
@@ -48,38 +53,45 @@ namespace {
 constexpr int kTM = 128;                 // weight rows per tile (TMEM lanes)
 constexpr int kTN = 128;                 // tokens per tile (accumulator columns)
 constexpr int kNB = 4;                   // accumulator buffers in TMEM (4 x 128 columns)
-constexpr int kNS = 10;                  // operand slots in shared memory
-constexpr int kPB = 4;                   // k-tiles a producer thread loads per batch (two rows each)
-constexpr int kABytes = kTM * 32;        // expanded int8 weights of one k-tile
-constexpr int kBBytes = kTN * 32;        // int8 activations of one k-tile
-constexpr int kSBytes = kTN / 2 * 16;    // {as0, as1, asum0, asum1} per token pair
+constexpr int kSS = 4;                   // step slots in shared memory (two k-tile slots each)
+constexpr int kABytes = kTM * 64;        // expanded fp16 weights of one k-tile
+constexpr int kBBytes = kTN * 64;        // fp16 activations of one k-tile
+constexpr int kSBytes = kTN * 8;         // as[128] then (float)asum[128] of the tile's tokens
 constexpr int kSlotBytes = kABytes + kBBytes + kSBytes;
-// Twelve warps: three share a scheduler, so a thread may hold up to 168 registers
-// (the epilogue's 64 accumulators and two 32-column TMEM loads do not fit the 128 that a
-// fourth warp per scheduler would leave).
-constexpr int kEpiWarps = 8, kProdWarps = 2;
-// Two MMA-issuing warps take the promote groups in turn: the wait, tcgen05.mma and
-// tcgen05.commit of one k-tile cost the issuing thread several hundred clocks (each tcgen05
-// instruction about 150, whatever the MMA's N), more than the epilogue needs per k-tile in
-// the per-token modes, so one issuing thread was the wall there.
+constexpr int kStepBytes = 2 * kSlotBytes;
+// Eleven warps: at most three share a scheduler, so a thread may hold up to 168 registers
+// (a worker's 64 accumulators and two 32-column TMEM loads do not fit the 128 that a fourth
+// warp per scheduler would leave).
+constexpr int kWorkWarps = 8;
+// Two MMA-issuing threads take the promote groups in turn: waits, four tcgen05.mma and the
+// tcgen05.commit of a K64 group cost the issuing thread about 700 clocks (every tcgen05
+// instruction 80 to 110, whatever the MMA's width), more than a group may take.
 constexpr int kMmaWarps = 2;
-constexpr int kThreads = (kEpiWarps + kProdWarps + kMmaWarps) * 32;
-constexpr int kRawStages = 4;             // raw ring of the producers: batches of kPB k-tiles
-constexpr int kRawBytes = kPB * 2048;     // 128 rows x 16 packed bytes per k-tile
-constexpr int kSmemBytes = kNS * kSlotBytes + kRawStages * kRawBytes;   // > half an SM's shared
+constexpr int kThreads = (kWorkWarps + 1 + kMmaWarps) * 32;    // + the warp that starts the image copies
+constexpr int kAhead = 3;                 // steps (of two k-tiles) the expansion runs ahead of the
+                                          // promote: a slot is rewritten only after the step that
+                                          // used it was promoted by the same warp, kAhead <= kSS - 1
+constexpr uint32_t kNapNs = 64;           // nap between polls of the single-thread roles
+constexpr int kLoadAhead = 2;             // steps the packed bytes are loaded (into registers) ahead
+                                          // of their expansion
+constexpr int kL2Ahead = 8;               // steps their lines are prefetched into L2 ahead of that
+static_assert(kAhead <= kSS - 1, "a slot must have been promoted before it is rewritten");
+static_assert((kSS & (kSS - 1)) == 0 && (kNB & (kNB - 1)) == 0, "ring positions are masks of the step counter");
+constexpr int kSmemBytes = kSS * kStepBytes;   // > half an SM's shared
                                          // memory: one CTA per SM, which the 512-column TMEM
                                          // allocation requires
 
-// instruction descriptor: D = s32 (2), A and B signed 8 bit (1), both K-major, N >> 3 at bit 17, M >> 4 at bit 24
-constexpr uint32_t kIdesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kTN >> 3) << 17) |
-                            ((uint32_t)(kTM >> 4) << 24);
+// fp16 operands: four 16-byte K-chunks per row of a k-tile, 128 bytes apart; row groups of 8
+// are 512 bytes apart; the second K = 16 instruction of a k-tile starts two chunks further
+constexpr uint32_t kLboH = 128, kSboH = 512;
+constexpr uint32_t kIdesc = idesc_f16(kTM, kTN);
 
 struct TcParams {
     const uint8_t *codes;
     const uint16_t *scales;
-    const uint8_t *img;      // per (k-tile, 128-token block): kBBytes of codes as
-                             // [16 token groups][2 K-chunks][8][16], then kSBytes of
-                             // {as0, as1, (float)asum0, (float)asum1} per token pair
+    const uint8_t *img;      // per (k-tile, 128-token block): kBBytes of fp16 codes as
+                             // [16 token groups][4 K-chunks][8 tokens][16 B], then kSBytes:
+                             // as[128], (float)asum[128]
     void *y;
     const float *as_tok;     // per-token scales (PERTOK kernels)
     int *status;
@@ -89,6 +101,22 @@ struct TcParams {
 #endif
     int M, Kt, ksh, T, Tpad, out_bf16;
 };
+
+// Two small integers -> a packed pair of fp16 values (exact for |v| <= 2048).
+__device__ __forceinline__ uint32_t h2_of(int lo, int hi) {
+    return (uint32_t)__half_as_ushort(__int2half_rn(lo)) | ((uint32_t)__half_as_ushort(__int2half_rn(hi)) << 16);
+}
+
+// One token's 32 codes of a k-tile -> its four 16-byte fp16 K-chunks in the image: chunk j
+// holds k = 8j + {0,4,1,5,2,6,3,7} (the order the weight expansion produces).
+__device__ __forceinline__ void store_token_chunks(uint8_t *blk, int tl, const int (&v)[32]) {
+    uint8_t *dst = blk + (tl >> 3) * kSboH + (tl & 7) * 16;
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+        *reinterpret_cast<uint4 *>(dst + j * kLboH) =
+            make_uint4(h2_of(v[8 * j], v[8 * j + 4]), h2_of(v[8 * j + 1], v[8 * j + 5]),
+                       h2_of(v[8 * j + 2], v[8 * j + 6]), h2_of(v[8 * j + 3], v[8 * j + 7]));
+}
 
 // Pre-pass: the caller's staging (aq[kt][tok][32], as[kt][tok], asum[kt][tok]) -> the images
 // the GEMM tiles copy with one bulk copy each. Tokens >= T are padded with zeros.
@@ -100,40 +128,23 @@ gemm_tc_prepass_kernel(const int8_t *__restrict__ aq, const float *__restrict__ 
     const size_t nrow = (size_t)Kt * Tpad;
     for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < nrow; i += (size_t)gridDim.x * 256) {
         const int kt = (int)(i / Tpad), tok = (int)(i % Tpad);
-        uint4 lo = make_uint4(0, 0, 0, 0), hi = make_uint4(0, 0, 0, 0);
+        int v[32];
+#pragma unroll
+        for (int k = 0; k < 32; ++k) v[k] = 0;
         if (tok < T) {
             const uint4 *src = reinterpret_cast<const uint4 *>(aq + ((size_t)kt * T + tok) * 32);
             const uint4 a = __ldg(src), b = __ldg(src + 1);    // k = 0..15, 16..31
-            // even-k bytes -> chunk 0, odd-k bytes -> chunk 1 (the weight expansion's order)
-            lo = make_uint4(__byte_perm(a.x, a.y, 0x6420), __byte_perm(a.z, a.w, 0x6420),
-                            __byte_perm(b.x, b.y, 0x6420), __byte_perm(b.z, b.w, 0x6420));
-            hi = make_uint4(__byte_perm(a.x, a.y, 0x7531), __byte_perm(a.z, a.w, 0x7531),
-                            __byte_perm(b.x, b.y, 0x7531), __byte_perm(b.z, b.w, 0x7531));
+            const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+            for (int k = 0; k < 32; ++k) v[k] = (int)(int8_t)(w[k >> 2] >> ((k & 3) * 8));
         }
         uint8_t *blk = img + ((size_t)kt * (Tpad / kTN) + tok / kTN) * (kBBytes + kSBytes);
         const int tl = tok % kTN;
-        uint8_t *dst = blk + (tl >> 3) * 256 + (tl & 7) * 16;
-        *reinterpret_cast<uint4 *>(dst) = lo;
-        *reinterpret_cast<uint4 *>(dst + 128) = hi;
-        if ((tok & 1) == 0) {
-            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (tok < T) {
-                v.x = as ? as[(size_t)kt * T + tok] : 0.0f;
-                v.z = (float)asum[(size_t)kt * T + tok];
-            }
-            if (tok + 1 < T) {
-                v.y = as ? as[(size_t)kt * T + tok + 1] : 0.0f;
-                v.w = (float)asum[(size_t)kt * T + tok + 1];
-            }
-            reinterpret_cast<float4 *>(blk + kBBytes)[tl >> 1] = v;
-        }
+        store_token_chunks(blk, tl, v);
+        float *sa = reinterpret_cast<float *>(blk + kBBytes);
+        sa[tl] = (tok < T && as) ? as[(size_t)kt * T + tok] : 0.0f;
+        sa[kTN + tl] = tok < T ? (float)asum[(size_t)kt * T + tok] : 0.0f;
     }
-}
-
-// Four 4-bit two's-complement codes (the low nibble of each byte) -> four int8 bytes.
-__device__ __forceinline__ uint32_t sext_nibbles(uint32_t l) {
-    l &= 0x0F0F0F0Fu;
-    return l | ((l & 0x08080808u) * 0x1Eu);      // a set sign bit fills bits 4..7 of its byte
 }
 
 // W4A4 pre-pass: packed int4 activations aq4[kt64][tok][32] (byte b = k 2b, 2b+1 of the 64),
@@ -149,33 +160,23 @@ gemm_tc_prepass_s4_kernel(const uint8_t *__restrict__ aq4, const float *__restri
     for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < nrow; i += (size_t)gridDim.x * 256) {
         const int kt = (int)(i / Tpad), tok = (int)(i % Tpad);
         const int kg = kt >> 1, half = kt & 1;
-        uint4 lo = make_uint4(0, 0, 0, 0), hi = make_uint4(0, 0, 0, 0);
+        int v[32];
+#pragma unroll
+        for (int k = 0; k < 32; ++k) v[k] = 0;
         if (tok < T) {
             const uint4 a = __ldg(reinterpret_cast<const uint4 *>(aq4 + ((size_t)kg * T + tok) * 32) + half);
-            // low nibbles = even k -> chunk 0, high nibbles = odd k -> chunk 1
-            lo = make_uint4(sext_nibbles(a.x), sext_nibbles(a.y), sext_nibbles(a.z), sext_nibbles(a.w));
-            hi = make_uint4(sext_nibbles(a.x >> 4), sext_nibbles(a.y >> 4), sext_nibbles(a.z >> 4),
-                            sext_nibbles(a.w >> 4));
+            const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+            // byte b of the half = k 2b (low nibble), 2b + 1 (high nibble); two's complement
+#pragma unroll
+            for (int k = 0; k < 32; ++k) v[k] = ((int)(w[k >> 3] << (28 - (k & 7) * 4))) >> 28;
         }
         uint8_t *blk = img + ((size_t)kt * (Tpad / kTN) + tok / kTN) * (kBBytes + kSBytes);
         const int tl = tok % kTN;
-        uint8_t *dst = blk + (tl >> 3) * 256 + (tl & 7) * 16;
-        *reinterpret_cast<uint4 *>(dst) = lo;
-        *reinterpret_cast<uint4 *>(dst + 128) = hi;
-        if ((tok & 1) == 0) {
-            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (half == 0) {
-                if (tok < T) {
-                    v.x = as4[(size_t)kg * T + tok];
-                    v.z = (float)asum4[(size_t)kg * T + tok];
-                }
-                if (tok + 1 < T) {
-                    v.y = as4[(size_t)kg * T + tok + 1];
-                    v.w = (float)asum4[(size_t)kg * T + tok + 1];
-                }
-            }
-            reinterpret_cast<float4 *>(blk + kBBytes)[tl >> 1] = v;
-        }
+        store_token_chunks(blk, tl, v);
+        float *sa = reinterpret_cast<float *>(blk + kBBytes);
+        const bool has = half == 0 && tok < T;
+        sa[tl] = has ? as4[(size_t)kg * T + tok] : 0.0f;
+        sa[kTN + tl] = has ? (float)asum4[(size_t)kg * T + tok] : 0.0f;
     }
 }
 
@@ -183,37 +184,61 @@ constexpr int kWaitMma = 21, kWaitEpi = 22, kWaitProd = 23;   // status codes of
 #ifdef TQ_TC_TRACE
 #define TC_STAMP(idx, which)                                                                  \
     if (blockIdx.x == 0 && p.trace && (idx) < 256 && threadIdx.x == 0) p.trace[(idx) * 8 + (which)] = clock64();
+// regions 1 (MMA thread of the first MMA warp) and 2 (producer thread 0): the caller names the thread
+#define TC_STAMP_R(region, cond, idx, which)                                                  \
+    if (blockIdx.x == 0 && p.trace && (idx) < 256 && (cond)) p.trace[(region) * 2048 + (idx) * 8 + (which)] = clock64();
 #else
 #define TC_STAMP(idx, which)
+#define TC_STAMP_R(region, cond, idx, which)
 #endif
 
-// Four two's-complement nibbles (the low nibble of each byte of w) -> four signed bytes.
-__device__ __forceinline__ uint32_t nib_s8(uint32_t w) { return __vsub4(nib_plus8(w), 0x08080808u); }
+// Eight two's-complement nibbles of w (nibble i = code k = i) -> eight fp16 values, as four
+// words holding the codes (0,4), (1,5), (2,6), (3,7). Per word: the two nibbles land in the
+// low bits of the two halves; xor with 0x6408 sets fp16's exponent of 1024 and flips the
+// code's sign bit, so the half reads 1024 + (q + 8); subtracting 1032 leaves q. mask and
+// bias (0x000F000F, 0x64086408) are passed in registers the caller keeps alive: as literals
+// each use costs a move that materialises the constant.
+__device__ __forceinline__ uint4 nib8_to_h8(uint32_t w, uint32_t mask, uint32_t bias) {
+    uint32_t r[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const uint32_t t = ((w >> (4 * i)) & mask) ^ bias;
+        asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(r[i]) : "r"(t), "r"(bias));
+    }
+    return make_uint4(r[0], r[1], r[2], r[3]);
+}
 
 // GW = k-tiles accumulated in TMEM before one fp32 promote (1: the reference's arithmetic with
 // a scale per (token, K32); 2: K64 weight groups with per-token activation scales, or - not
 // PERTOK - with one activation scale per (token, K64): the W4A4 arithmetic). PERTOK:
 // the activation scale is applied once at the end (y = acc * as_tok).
+//
+// The K loop advances in steps of two k-tiles (K is a multiple of 64); step n of the CTA
+// (counted across its tiles) uses step slot n % kSS. A worker warp owns 16 weight rows (one
+// packed row group, so its bytes of consecutive k-tiles are contiguous in memory) and 32
+// TMEM lanes; lane l expands row (l & 15) of k-tile (l >> 4) of a step, kAhead steps ahead
+// of the step it promotes. The loop is kept lean on purpose: with two or three warps per
+// scheduler its time is its instruction count times a dependent-issue latency.
 template <int GW, bool PERTOK>
 __global__ void __maxnreg__(168) gemm_w4a8_tc_kernel(const TcParams p) {
     extern __shared__ __align__(1024) unsigned char smem[];
-    __shared__ uint64_t bars[2 * kNS + 2 * kNB];   // full[kNS], empty[kNS], accfull[kNB], accempty[kNB]
+    __shared__ uint64_t bars[2 * kSS + 2 * kNB];   // full[kSS], empty[kSS], accfull[kNB], accempty[kNB]
     __shared__ uint32_t tmem_base_s;
     __shared__ int dead_s;                      // a wait gave up somewhere in the CTA
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const uint32_t smem_u = smem_u32(smem);
-    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[kNS]),
-                   acc0 = smem_u32(&bars[2 * kNS]), accempty0 = smem_u32(&bars[2 * kNS + kNB]);
+    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[kSS]),
+                   acc0 = smem_u32(&bars[2 * kSS]), accempty0 = smem_u32(&bars[2 * kSS + kNB]);
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kNS; ++s) {
-            mbar_init(full0 + s * 8, kProdWarps * 32);   // every producer thread arrives once
-            mbar_init(empty0 + s * 8, kEpiWarps);        // one arrive per epilogue warp
+        for (int s = 0; s < kSS; ++s) {
+            mbar_init(full0 + s * 8, kWorkWarps + 1);    // every worker warp's rows + the image copies
+            mbar_init(empty0 + s * 8, kWorkWarps);       // one arrive per worker warp
         }
         for (int b = 0; b < kNB; ++b) {
             mbar_init(acc0 + b * 8, 1);                  // tcgen05.commit
-            mbar_init(accempty0 + b * 8, kEpiWarps);     // one arrive per epilogue warp
+            mbar_init(accempty0 + b * 8, kWorkWarps);    // one arrive per worker warp
         }
         dead_s = 0;
         mbar_init_fence();
@@ -231,119 +256,211 @@ __global__ void __maxnreg__(168) gemm_w4a8_tc_kernel(const TcParams p) {
     pdl_wait();      // everything below reads the images an earlier kernel wrote
 
     const int Kt = p.Kt, Ktg = Kt >> p.ksh;
+    const int spt = Kt >> 1;                             // steps per tile
     const int row_blocks = p.M / kTM, tok_blocks = p.Tpad / kTN;
     const int ntiles = row_blocks * tok_blocks;
-    int it = 0;      // k-tile counter across the tiles of this CTA: operand slot it % kNS,
-                     // accumulator buffer it % kNB
+    const int my_tiles = (ntiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+    const int n_total = my_tiles * spt;                  // steps of this CTA
 
-    if (warp < kEpiWarps) {
-        // ================================ epilogue ======================================
+    // A wait that gives up when another role already has: the flag is read on the slow path only.
+    auto wait_on = [&](uint32_t bar, uint32_t parity, int code, uint32_t sleep_ns = 0) -> bool {
+        if (mbar_test_wait(bar, parity)) return true;
+        if (*(volatile int *)&dead_s) return false;
+        if (mbar_wait_slow(bar, parity, p.status, code, p.wait_ns, sleep_ns)) return true;
+        dead_s = 1;
+        return false;
+    };
+
+    if (warp < kWorkWarps) {
+        // ====================== workers: expand weights, promote accumulators =============
+        const int erow = lane & 15, ehalf = lane >> 4;
+        const int r16 = 16 * warp + erow;                 // the row this lane expands
+        // this lane's four chunks inside a step slot: k-tile ehalf, row r16
+        const uint32_t a_off = (uint32_t)(ehalf * kSlotBytes + (r16 >> 3) * kSboH + (r16 & 7) * 16);
+#ifdef TQ_TC_TRACE
+        long long tsum[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0}, tprev = clock64();
+#define TC_LAP(i) { const long long tnow = clock64(); tsum[i] += tnow - tprev; tprev = tnow; }
+#else
+#define TC_LAP(i)
+#endif
+        uint32_t c_mask, c_bias;                           // see nib8_to_h8
+        asm volatile("mov.b32 %0, 0x000F000F;" : "=r"(c_mask));
+        asm volatile("mov.b32 %0, 0x64086408;" : "=r"(c_bias));
+
+        // ---- load stream (step f_n): this lane's 16 packed bytes of a step, kLoadAhead steps
+        // ahead of their expansion, in registers; the 128-byte lines are pulled into L2
+        // kL2Ahead steps earlier still. A lane's bytes of consecutive steps are 512 bytes apart.
+        auto tile_src = [&](int ti) {
+            const int rb = ((int)blockIdx.x + ti * (int)gridDim.x) % row_blocks;
+            return p.codes + ((size_t)(rb * (kTM / 16) + warp) * Kt + ehalf) * 256 + erow * 16;
+        };
+        int f_n = 0, f_ti = 0, f_left = spt;
+        const uint8_t *f_src = tile_src(0);
+        uint4 pre[kLoadAhead];
+        auto load_next = [&](uint4 &dst) {
+            if (f_n < n_total) {
+                dst = ldg_stream_v4(f_src);
+                // only inside the tile's own run of bytes
+                if (f_left > kL2Ahead && (lane & 7) == 0) prefetch_l2(f_src + kL2Ahead * 512);
+                f_src += 512;
+                if (--f_left == 0) {
+                    f_left = spt;
+                    if (++f_ti < my_tiles) f_src = tile_src(f_ti);
+                }
+            }
+            ++f_n;
+        };
+        // ---- expansion stream (step e_n): registers -> fp16 A operands of the step's slot
+        int e_n = 0;
+        auto expand = [&]() {
+            TC_LAP(2)
+            const uint4 c4 = pre[0];
+#pragma unroll
+            for (int i = 0; i + 1 < kLoadAhead; ++i) pre[i] = pre[i + 1];
+            load_next(pre[kLoadAhead - 1]);
+            TC_LAP(7)
+            if (e_n < n_total) {
+                unsigned char *dst = smem + (size_t)(e_n & (kSS - 1)) * kStepBytes + a_off;
+                *reinterpret_cast<uint4 *>(dst) = nib8_to_h8(c4.x, c_mask, c_bias);                 // k 0..7
+                *reinterpret_cast<uint4 *>(dst + kLboH) = nib8_to_h8(c4.y, c_mask, c_bias);         // k 8..15
+                *reinterpret_cast<uint4 *>(dst + 2 * kLboH) = nib8_to_h8(c4.z, c_mask, c_bias);     // k 16..23
+                *reinterpret_cast<uint4 *>(dst + 3 * kLboH) = nib8_to_h8(c4.w, c_mask, c_bias);     // k 24..31
+                TC_LAP(8)
+                fence_proxy_async_smem();   // generic-proxy stores -> visible to the MMA
+                TC_LAP(9)
+                __syncwarp();
+                mbar_arrive_if(full0 + (e_n & (kSS - 1)) * 8, lane == 0);
+                TC_LAP(10)
+            }
+            ++e_n;
+        };
+#pragma unroll
+        for (int i = 0; i < kLoadAhead; ++i) load_next(pre[i]);
+#pragma unroll 1
+        for (int i = 0; i < kAhead; ++i) expand();
+
+        // ---- promote stream
         const int q4 = warp & 3, chalf = (warp >> 2) * 64;
         const int rloc = q4 * 32 + lane;                  // row inside the tile = TMEM lane
-        const uint32_t lane_base = tmem_base + ((uint32_t)(q4 * 32) << 16);
-        const f32x2 neg_magic2 = pack2(-kMagicF, -kMagicF);
-        for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+        const uint32_t lane_base = tmem_base + ((uint32_t)(q4 * 32) << 16) + chalf;
+        // activation scales of this thread's 64 tokens inside a k-tile slot (as four-token
+        // vectors: [0, 16) scales, [32, 48) code sums)
+        const unsigned char *sv_base = smem + kABytes + kBBytes + chalf * 4;
+        int n = 0;                                        // step counter across the CTA's tiles
+        bool alive = true;
+        uint32_t acc_ready = 0;
+
+        for (int ti = 0; ti < my_tiles && alive; ++ti) {
+            const int tile = (int)blockIdx.x + ti * (int)gridDim.x;
             const int rb = tile % row_blocks, tb = tile / row_blocks;
             const int row = rb * kTM + rloc;
             const uint16_t *sc = p.scales + ((size_t)(row >> 4) * Ktg) * 16 + (row & 15);
-            f32x2 acc[32];
+            float acc[64];
 #pragma unroll
-            for (int i = 0; i < 32; ++i) acc[i] = 0ull;
+            for (int i = 0; i < 64; ++i) acc[i] = 0.0f;
             uint32_t scw = __ldg(sc);
-            for (int kt = 0; kt < Kt; kt += GW, it += GW) {
-                const int ig = it / GW;                       // promote groups done by this CTA
-                const int b = ig % kNB, sl = it % kNS;
-                const uint32_t ph = (uint32_t)(ig / kNB) & 1u;
-                int zp;
-                float ws;
-                unpack_scale(scw, zp, ws);
-                if (kt + GW < Kt) scw = __ldg(sc + (size_t)((kt + GW) >> p.ksh) * 16);
-                const f32x2 ws2 = pack2(ws, ws);
-                const float nzf = (float)(-zp);
-                const f32x2 nz2 = pack2(nzf, nzf);
-                // symmetric weights (every zero point of the warp's rows is 0) need no
-                // zero-point term at all: the weights enter the MMA as true signed bytes
-                const bool anyz = __any_sync(0xffffffffu, zp != 0);
-                TC_STAMP(ig, 0)
-                bool ok = !*(volatile int *)&dead_s && mbar_wait_bounded(acc0 + b * 8, ph, p.status, kWaitEpi, p.wait_ns);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) {
-                    dead_s = 1;
-                    break;
-                }
-                tc_fence_after();
-                TC_STAMP(ig, 1)
-                const ulonglong2 *sv = reinterpret_cast<const ulonglong2 *>(
-                                           smem + (size_t)sl * kSlotBytes + kABytes + kBBytes) +
-                                       (chalf >> 1);
-                // second k-tile of the group (GW == 2): only its code sums are needed
-                const int sl1 = (it + GW - 1) % kNS;
-                const ulonglong2 *sv1 = reinterpret_cast<const ulonglong2 *>(
-                                            smem + (size_t)sl1 * kSlotBytes + kABytes + kBBytes) +
-                                        (chalf >> 1);
-                // Two 32-column loads, the second in flight while the first is promoted. The
-                // accumulator holds the plain int32 dot (the group's first MMA overwrites it), so
-                // nothing has to be stored back; adding the bit pattern of 12582912.0f to the
-                // integer and subtracting 12582912.0f from the result as a float converts it
-                // exactly (|d| < 2^22) on the integer and packed-fp32 pipes.
-                uint32_t da[32], db[32];
-                const uint32_t tcol = lane_base + b * kTN + chalf;
-                // Straight-line code per variant (ANYZ is a compile-time tag): a test of `anyz`
-                // inside the unrolled pair loop splits it into one basic block per pair, and the
-                // pairs' short dependency chains then run one after the other.
-                auto promote = [&](auto anyz_tag, const int q, uint32_t (&d)[32]) {
-                    constexpr bool ANYZ = decltype(anyz_tag)::value;
+#pragma unroll 1
+            for (int s = 0; s < spt; ++s, ++n) {
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        f32x2 f = add2(pack2i((int)d[2 * j] + kMagicBits, (int)d[2 * j + 1] + kMagicBits),
-                                       neg_magic2);
-                        if (PERTOK) {
-                            if (ANYZ) {
-                                f32x2 smf = sv[q * 16 + j].y;                  // {asum0, asum1}
-                                if (GW == 2) smf = add2(smf, sv1[q * 16 + j].y);   // exact: small integers
-                                f = fma2(nz2, smf, f);
-                            }
-                            fma2_acc(acc[q * 16 + j], f, ws2);
-                        } else {
-                            const ulonglong2 s4 = sv[q * 16 + j];      // {as0, as1}, {asum0, asum1}
-                            if (ANYZ) {
-                                f32x2 smf = s4.y;
-                                if (GW == 2) smf = add2(smf, sv1[q * 16 + j].y);
-                                f = fma2(nz2, smf, f);
-                            }
-                            fma2_acc(acc[q * 16 + j], f, mul2(ws2, s4.x));
-                        }
+                for (int g = 0; g < (GW == 2 ? 1 : 2); ++g) {
+                    TC_LAP(5)
+                    const int kt = 2 * s + g;              // first k-tile of the group
+                    const int ig = (GW == 2) ? n : 2 * n + g;      // group counter of the CTA
+                    const int b = ig & (kNB - 1);
+                    int zp;
+                    float ws;
+                    unpack_scale(scw, zp, ws);
+                    if (kt + GW < Kt) scw = __ldg(sc + (size_t)((kt + GW) >> p.ksh) * 16);
+                    const f32x2 ws2 = pack2(ws, ws);
+                    const float nzf = (float)(-zp);
+                    // symmetric weights (every zero point of the warp's rows is 0) need no
+                    // zero-point term at all: the weights enter the MMA as true signed values
+                    const bool anyz = __any_sync(0xffffffffu, zp != 0);
+                    // acc_ready: the barrier was already tested, with the previous group's
+                    // load in flight (the test's answer takes about a hundred clocks)
+                    if (!__all_sync(0xffffffffu,
+                                    acc_ready || wait_on(acc0 + b * 8, (uint32_t)(ig / kNB) & 1u, kWaitEpi))) {
+                        alive = false;
+                        break;
                     }
-                };
-                auto promote_any = [&](const int q, uint32_t (&d)[32]) {
-                    if (anyz) promote(std::true_type{}, q, d);
-                    else promote(std::false_type{}, q, d);
-                };
-                tmem_ld32(tcol, da);
-                tmem_wait_ld32(da);
-                TC_STAMP(ig, 2)
-                tmem_ld32(tcol + 32, db);
-                promote_any(0, da);
-                TC_STAMP(ig, 3)
-                tmem_wait_ld32(db);
-                promote_any(1, db);
-                TC_STAMP(ig, 4)
-                TC_STAMP(ig, 5)
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) {
-                    mbar_arrive(accempty0 + b * 8);      // the MMA may overwrite the buffer
-                    mbar_arrive(empty0 + sl * 8);        // the producers may refill the slot(s)
-                    if (GW == 2) mbar_arrive(empty0 + sl1 * 8);
+                    tc_fence_after();
+                    TC_LAP(0)
+                    // One 64-column load of the thread's share of the accumulator: it holds
+                    // (float)d of the group (the group's first MMA overwrites it), so nothing has
+                    // to be converted or stored back. The load is in flight while the warp
+                    // expands the weights of a later step.
+                    uint32_t d[64];
+                    tmem_ld64(lane_base + b * kTN, d);
+                    {
+                        const int ign = ig + 1;            // the CTA's next group, also across tiles
+                        acc_ready = mbar_test_wait(acc0 + (ign & (kNB - 1)) * 8, (uint32_t)(ign / kNB) & 1u);
+                    }
+                    TC_LAP(1)
+                    if (g == 0) expand();                  // kAhead steps ahead
+                    TC_LAP(2)
+                    const ulonglong2 *sv = reinterpret_cast<const ulonglong2 *>(
+                        sv_base + (size_t)((n & (kSS - 1)) * 2 + g) * kSlotBytes);
+                    // second k-tile of a K64 group: only its code sums are needed
+                    const ulonglong2 *sv1 = reinterpret_cast<const ulonglong2 *>(
+                        sv_base + (size_t)((n & (kSS - 1)) * 2 + 1) * kSlotBytes);
+                    // Straight-line code per variant (ANYZ is a compile-time tag): a test of `anyz`
+                    // inside the unrolled pair loop splits it into one basic block per pair, and the
+                    // pairs' short dependency chains then run one after the other.
+                    auto promote = [&](auto anyz_tag) {
+                        constexpr bool ANYZ = decltype(anyz_tag)::value;
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {     // four tokens at a time
+                            // scalar fmas on the loaded registers as they are: pairing them for
+                            // the packed form costs two moves per pair and the registers to hold
+                            // them, more than it saves
+                            float f[4];
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) f[i] = __uint_as_float(d[4 * j + i]);
+                            if (ANYZ) {
+                                ulonglong2 sm = sv[32 + j];                        // four code sums
+                                if (GW == 2) {                                     // exact: small integers
+                                    const ulonglong2 sm1 = sv1[32 + j];
+                                    sm.x = add2(sm.x, sm1.x);
+                                    sm.y = add2(sm.y, sm1.y);
+                                }
+                                float m[4];
+                                unpack2(sm.x, m[0], m[1]);
+                                unpack2(sm.y, m[2], m[3]);
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) f[i] = fmaf(nzf, m[i], f[i]);
+                            }
+                            float w[4] = {ws, ws, ws, ws};
+                            if (!PERTOK) {
+                                const ulonglong2 a4 = sv[j];                       // four activation scales
+                                unpack2(mul2(ws2, a4.x), w[0], w[1]);              // ws * as, rounded once
+                                unpack2(mul2(ws2, a4.y), w[2], w[3]);
+                            }
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) acc[4 * j + i] = fmaf(f[i], w[i], acc[4 * j + i]);
+                        }
+                    };
+                    tmem_wait_ld_all();
+                    TC_LAP(3)
+                    if (anyz) promote(std::true_type{});
+                    else promote(std::false_type{});
+                    TC_LAP(4)
+                    tc_fence_before();
+                    __syncwarp();
+                    // one instruction, two barriers: lane 0 tells the MMA that it may overwrite
+                    // the buffer, lane 1 (after the step's last group) the copy thread that the
+                    // slot's images may be replaced
+                    if (g == (GW == 2 ? 0 : 1))
+                        mbar_arrive_if(lane == 0 ? accempty0 + b * 8 : empty0 + (n & (kSS - 1)) * 8, lane < 2);
+                    else
+                        mbar_arrive_if(accempty0 + b * 8, lane == 0);
                 }
-                TC_STAMP(ig, 6)
+                if (!alive) break;
             }
-            if (*(volatile int *)&dead_s) break;
+            if (!alive) break;
             // store: thread = row, 64 tokens; rows are contiguous in y, so a warp writes 128 B
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
-                float v0, v1;
-                unpack2(acc[i], v0, v1);
+                float v0 = acc[2 * i], v1 = acc[2 * i + 1];
                 const int tok = tb * kTN + chalf + 2 * i;
                 if (PERTOK) {
                     if (tok < p.T) v0 = __fmul_rn(v0, __ldg(p.as_tok + tok));
@@ -360,126 +477,64 @@ __global__ void __maxnreg__(168) gemm_w4a8_tc_kernel(const TcParams p) {
                 }
             }
         }
-    } else if (warp < kEpiWarps + kProdWarps) {
-        // ================================ producers =====================================
-        const int pr = threadIdx.x - kEpiWarps * 32;       // rows pr and pr + 64 of the tile
-        // destination of a row's two K-chunks in the core-matrix layout (row pr + 64: 8 row
-        // groups further)
-        const uint32_t a_off = (uint32_t)((pr >> 3) * kSbo + (pr & 7) * 16);
-        // Packed weights travel through a private raw ring in shared memory (cp.async, kRawStages
-        // batches of kPB k-tiles, all but one in flight): a thread reads back only what it
-        // copied itself, so the ring needs no barrier, and the loop below is the producers'
-        // whole steady-state code (register double-buffering needed two copies of it, and the
-        // kernel's roles were evicting one another from the instruction cache).
-        unsigned char *raw = smem + kNS * kSlotBytes;
-        const uint32_t raw_u = smem_u + kNS * kSlotBytes;
-        const uint64_t pol = l2_policy_evict_first();
-        const int nbatch = (Kt + kPB - 1) / kPB;
-        const int my_tiles = (ntiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
-        const int total = my_tiles * nbatch;               // batches this CTA produces
-        const size_t half_rows = (size_t)4 * Kt * 256;     // 64 rows = 4 row-groups further
-        auto fill = [&](int g) {
-            if (g < total) {
-                const int tile = blockIdx.x + (g / nbatch) * gridDim.x, kt0 = (g % nbatch) * kPB;
-                const int row = (tile % row_blocks) * kTM + pr;
-                const uint8_t *src = p.codes + ((size_t)(row >> 4) * Kt + kt0) * 256 + (row & 15) * 16;
-                const uint32_t dst = raw_u + (uint32_t)(g % kRawStages) * kRawBytes + pr * 16;
-#pragma unroll
-                for (int j = 0; j < kPB; ++j)
-                    if (kt0 + j < Kt) {
-                        cp_async16(dst + j * 2048, src + (size_t)j * 256, pol);
-                        cp_async16(dst + j * 2048 + 1024, src + half_rows + (size_t)j * 256, pol);
-                    }
-            }
-            cp_async_commit();
-        };
-#pragma unroll 1
-        for (int g = 0; g < kRawStages - 1; ++g) fill(g);
-#pragma unroll 1
-        for (int g = 0; g < total; ++g) {
-            cp_async_wait<kRawStages - 2>();
-            fill(g + kRawStages - 1);                      // into the stage consumed last
-            const int tb = (blockIdx.x + (g / nbatch) * gridDim.x) / row_blocks, kb = g % nbatch;
-            // The whole batch behind ONE round of waits, one proxy fence and one round of
-            // arrivals.
-            const int nk = min(kPB, Kt - kb * kPB);
-            bool ok = !*(volatile int *)&dead_s;
-#pragma unroll 1
-            for (int j = 0; j < nk && ok; ++j)
-                ok = mbar_wait_bounded(empty0 + ((it + j) % kNS) * 8, ((uint32_t)((it + j) / kNS) & 1u) ^ 1u,
-                                       p.status, kWaitProd, p.wait_ns);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) {
-                dead_s = 1;
-                break;
-            }
-            const unsigned char *rs = raw + (size_t)(g % kRawStages) * kRawBytes + pr * 16;
-#pragma unroll
-            for (int j = 0; j < kPB; ++j) {
-                if (j >= nk) break;
-                unsigned char *slot = smem + (size_t)((it + j) % kNS) * kSlotBytes;
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const uint4 c4 = *reinterpret_cast<const uint4 *>(rs + j * 2048 + h * 1024);
-                    // nibble -> q + 8 (one logic op per four codes) -> q (one SIMD byte subtract)
-                    const uint4 lo = make_uint4(nib_s8(c4.x), nib_s8(c4.y), nib_s8(c4.z), nib_s8(c4.w));
-                    const uint4 hi = make_uint4(nib_s8(c4.x >> 4), nib_s8(c4.y >> 4), nib_s8(c4.z >> 4),
-                                                nib_s8(c4.w >> 4));
-                    *reinterpret_cast<uint4 *>(slot + a_off + h * 8 * kSbo) = lo;          // even-k chunk
-                    *reinterpret_cast<uint4 *>(slot + a_off + h * 8 * kSbo + kLbo) = hi;   // odd-k chunk
-                }
-            }
-            fence_proxy_async_smem();   // generic-proxy stores -> visible to the MMA
-#pragma unroll 1
-            for (int j = 0; j < nk; ++j) {
-                const int sl = (it + j) % kNS;
-                const uint32_t fb = full0 + sl * 8;
-                if (pr == j * 16) {
-                    // One bulk copy brings the activation image of this (k-tile, token block);
-                    // this thread's arrival also announces its bytes. Each k-tile of the batch
-                    // has its own issuing thread: one thread sustains only about two bulk
-                    // copies in flight.
-                    mbar_expect_tx(fb, kBBytes + kSBytes);
-                    bulk_g2s_plain(smem_u + sl * kSlotBytes + kABytes,
-                                   p.img + ((size_t)(kb * kPB + j) * (p.Tpad / kTN) + tb) * (kBBytes + kSBytes),
-                                   kBBytes + kSBytes, fb);
-                } else {
-                    mbar_arrive(fb);
-                }
-            }
-            it += nk;
+#ifdef TQ_TC_TRACE
+        if (blockIdx.x == 0 && p.trace && lane == 0) {
+            for (int i = 0; i < 12; ++i) p.trace[warp * 16 + i] = tsum[i];
+            p.trace[warp * 16 + 12] = n;
         }
-        cp_async_wait<0>();
-    } else {
-        // ================================ MMA issuer ====================================
-        for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
-            for (int kt = 0; kt < Kt; ++kt, ++it) {
-                const int ig = it / GW;
-                if (ig % kMmaWarps != warp - (kEpiWarps + kProdWarps)) continue;   // the other warp's group
-                const int b = ig % kNB, sl = it % kNS;
-                bool ok = !*(volatile int *)&dead_s &&
-                          mbar_wait_bounded(full0 + sl * 8, (uint32_t)(it / kNS) & 1u, p.status, kWaitMma, p.wait_ns);
-                // ... and, for the first k-tile of a group, the accumulator buffer has been
-                // read out
-                if (it % GW == 0)
-                    ok = ok && mbar_wait_bounded(accempty0 + b * 8, ((uint32_t)(ig / kNB) & 1u) ^ 1u,
-                                                 p.status, kWaitMma, p.wait_ns);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) {
-                    dead_s = 1;
-                    break;
+#endif
+    } else if (warp == kWorkWarps) {
+        // ====================== image copies (one thread) =================================
+        // Two bulk copies per step bring the activation images of its k-tiles for the tile's
+        // token block; the slot's previous images must have been read by every worker warp.
+        if (lane == 0) {
+            const size_t blk = (size_t)(kBBytes + kSBytes), kstride = (size_t)tok_blocks * blk;
+            int n = 0;
+            for (int ti = 0; ti < my_tiles; ++ti) {
+                const int tb = ((int)blockIdx.x + ti * (int)gridDim.x) / row_blocks;
+                const uint8_t *src = p.img + (size_t)tb * blk;
+                bool ok = true;
+                for (int s = 0; s < spt; ++s, ++n, src += 2 * kstride) {
+                    const int ss = n & (kSS - 1);
+                    ok = wait_on(empty0 + ss * 8, ((uint32_t)(n / kSS) & 1u) ^ 1u, kWaitProd, kNapNs);
+                    if (!ok) break;
+                    const uint32_t fb = full0 + ss * 8;
+                    const uint32_t dst = smem_u + ss * kStepBytes + kABytes;
+                    mbar_expect_tx(fb, 2 * (kBBytes + kSBytes));
+                    bulk_g2s_plain(dst, src, kBBytes + kSBytes, fb);
+                    bulk_g2s_plain(dst + kSlotBytes, src + kstride, kBBytes + kSBytes, fb);
                 }
-                tc_fence_after();
-                if (lane == 0) {
-                    const uint32_t a_addr = smem_u + sl * kSlotBytes;
-                    // the first MMA of a promote group overwrites the accumulator
-                    tc_mma_i8(tmem_base + b * kTN, smem_desc(a_addr), smem_desc(a_addr + kABytes),
-                              kIdesc, (it % GW) ? 1u : 0u);
-                    if (it % GW == GW - 1) tc_commit(acc0 + b * 8);
-                }
-                __syncwarp();
+                if (!ok) break;
             }
-            if (*(volatile int *)&dead_s) break;
+        }
+    } else {
+        // ====================== MMA issuers (one thread per warp, steps in turn) ===========
+        if (lane == 0) {
+            const int mw = warp - (kWorkWarps + 1);
+            const uint64_t desc0 = smem_desc_at(smem_u, kLboH, kSboH);
+            for (int n = mw; n < n_total; n += kMmaWarps) {
+                const int ss = n & (kSS - 1);
+                if (!wait_on(full0 + ss * 8, (uint32_t)(n / kSS) & 1u, kWaitMma, kNapNs)) break;
+                bool ok = true;
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {              // the step's two k-tiles
+                    const int ig = (GW == 2) ? n : 2 * n + h;
+                    const int b = ig & (kNB - 1);
+                    // the group's accumulator buffer has been read out
+                    if (GW == 1 || h == 0) {
+                        ok = wait_on(accempty0 + b * 8, ((uint32_t)(ig / kNB) & 1u) ^ 1u, kWaitMma, kNapNs);
+                        if (!ok) break;
+                        tc_fence_after();
+                    }
+                    const uint64_t da = desc0 + (uint64_t)(((ss * 2 + h) * kSlotBytes) >> 4);
+                    const uint64_t db = da + (kABytes >> 4);
+                    // the first MMA of a promote group overwrites the accumulator
+                    tc_mma_f16(tmem_base + b * kTN, da, db, kIdesc, (GW == 2 && h == 1) ? 1u : 0u);
+                    tc_mma_f16(tmem_base + b * kTN, da + (2 * kLboH >> 4), db + (2 * kLboH >> 4), kIdesc, 1u);
+                    if (GW == 1 || h == 1) tc_commit(acc0 + b * 8);
+                }
+                if (!ok) break;
+            }
         }
     }
 
@@ -504,12 +559,11 @@ long long *g_tc_trace = nullptr;
 
 int launch_gemm_tc(const GemmTcArgs &a) {
     // covered: per-block activation scales (the reference's x_gemm_w4a8 arithmetic) or
-    // per-token scales, rows a multiple of 128, K64 tier only with an even number of k-tiles
+    // per-token scales, rows a multiple of 128, K a multiple of 64
     if (!a.as == !a.as_tok) return -1;          // exactly one kind of activation scale
     if (a.aq4 && (!a.as || !a.ksh)) return -1;  // W4A4: K64 weights, scale per (token, K64)
-    if (a.M % kTM || a.K % 32 || a.T < 128) return -1;
+    if (a.M % kTM || a.K % 64 || a.T < 128) return -1;     // steps of two k-tiles
     const int Kt = a.K / 32;
-    if (a.ksh && (Kt & 1)) return -1;
     if (!g_tc_sms) {
         int dev = 0;
         TQ_CHECK(cudaGetDevice(&dev));
@@ -546,8 +600,8 @@ int launch_gemm_tc(const GemmTcArgs &a) {
 #ifdef TQ_TC_TRACE
     {
         static long long *tr = nullptr;
-        if (!tr) tr = static_cast<long long *>(tq_dev_alloc(256 * 8 * 8, "tc.trace"));
-        TQ_CHECK(cudaMemsetAsync(tr, 0, 256 * 8 * 8, stream()));
+        if (!tr) tr = static_cast<long long *>(tq_dev_alloc(3 * 256 * 8 * 8, "tc.trace"));
+        TQ_CHECK(cudaMemsetAsync(tr, 0, 3 * 256 * 8 * 8, stream()));
         p.trace = tr;
         g_tc_trace = tr;
     }
@@ -573,7 +627,7 @@ int launch_gemm_tc(const GemmTcArgs &a) {
 #ifdef TQ_TC_TRACE
 extern "C" int qwn_dbg_tc_trace(long long *host_out) {
     if (!tq::g_tc_trace) return -1;
-    tq_d2h(host_out, tq::g_tc_trace, 256 * 8 * 8);
+    tq_d2h(host_out, tq::g_tc_trace, 3 * 256 * 8 * 8);
     return 0;
 }
 #endif

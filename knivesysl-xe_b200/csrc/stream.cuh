@@ -70,16 +70,16 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 // loop with its clock arithmetic at each of them multiplies the kernel's code size until its
 // roles evict one another from the instruction cache.
 static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, int *status, int code,
-                                                   uint64_t limit_ns) {
-    // mbarrier.try_wait suspends the thread in hardware for a bounded time while the phase is
-    // incomplete, so polling it back to back costs few issue slots and adds no latency when
-    // the phase completes. The clock is read every 2048 polls.
+                                                   uint64_t limit_ns, uint32_t sleep_ns = 0) {
+    // mbarrier.try_wait comes back after some tens of clocks while the phase is incomplete, so
+    // a warp that polls back to back takes a fifth or more of its scheduler's issue slots
+    // from the warps beside it. A role whose reaction time has slack (a single issuing
+    // thread that runs ahead of its consumers) passes sleep_ns > 0 and naps between polls.
+    // The clock is read every 2048 polls.
     uint64_t t0 = 0;
     for (uint32_t polls = 1;; ++polls) {
         if (mbar_try_wait(bar, parity)) return true;
-#ifdef TQ_WAIT_SLEEP_NS
-        __nanosleep(TQ_WAIT_SLEEP_NS);
-#endif
+        if (sleep_ns) __nanosleep(sleep_ns);
         if ((polls & 2047u) == 0) {
             const uint64_t now = global_timer_ns();
             if (t0 == 0) t0 = now;
