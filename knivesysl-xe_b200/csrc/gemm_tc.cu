@@ -16,26 +16,35 @@
 //
 // Mapping. Weights are the M side of the MMA (128 output rows = 128 TMEM lanes), tokens the
 // N side (128 per CTA tile), a k-tile (K = 32) is two K = 16 instructions, so one accumulator
-// read-out yields exactly the per-k-tile dots the reference promotes. A CTA (12 warps, one
-// per SM, persistent over tiles) runs three roles connected by mbarriers (10 operand slots
-// in shared memory, 4 accumulator buffers in TMEM):
-//  * producers (2 warps, thread = two weight rows): cp.async the rows' packed bytes of a
-//    batch of k-tiles into a private ring, expand each 32-bit word (8 codes) to 8 fp16 values
-//    (shift, one logic op that isolates two nibbles and ors in the exponent of 1024 with the
-//    sign bit flipped, one packed subtract of 1032) and store them as the four 16-byte
-//    K-chunks of the row in the canonical no-swizzle K-major core-matrix layout (inside a
-//    chunk the codes sit in the order 0,4,1,5,2,6,3,7: any fixed permutation of k inside an
-//    instruction is exact for a dot, and the activation image uses the same one); one thread
-//    starts the bulk (TMA) copy of the activation image of the tile (8 KiB of fp16) and of its
-//    per-token {as, as, asum, asum} pairs (1 KiB), prepared by a pre-pass in that layout;
-//  * two MMA threads (in two warps, promote groups in turn): two tcgen05.mma (M=128, N=128,
-//    K=16) per k-tile into accumulator slot b (the first MMA of a promote group overwrites
-//    the slot); tcgen05.commit signals the epilogue;
-//  * epilogue (8 warps, thread = weight row x 64 tokens): two 32-column tcgen05.ld per
-//    promote, then per token pair f = fma(-z, asum, d) (exact; skipped while every zero
-//    point of the warp's rows is 0, i.e. for symmetric weights), acc = fma(f, ws*as, acc);
-//    64 fp32 accumulators stay in registers for the whole K loop and are stored at the end
-//    (coalesced over rows).
+// read-out yields exactly the per-k-tile dots the reference promotes. The K loop advances in
+// steps of two k-tiles. A CTA (11 warps, one per SM, persistent over tiles) runs three roles
+// connected by mbarriers (4 step slots in shared memory, 4 accumulator buffers in TMEM):
+//  * workers (8 warps). Each expands weights and promotes accumulators, in one loop:
+//    - expansion, 3 steps ahead of the promote: a warp owns one packed row group (16 rows),
+//      lane = (row, k-tile of the step); the lane's 16 packed bytes were loaded into
+//      registers two steps earlier (and prefetched into L2 eight steps before that); each
+//      32-bit word (8 codes) becomes 8 fp16 values (shift, logic ops that isolate two nibbles
+//      and set the exponent of 1024 with the sign bit flipped, one packed subtract of 1032),
+//      stored as the four 16-byte K-chunks of the row in the canonical no-swizzle K-major
+//      core-matrix layout (inside a chunk the codes sit in the order 0,4,1,5,2,6,3,7: any
+//      fixed permutation of k inside an instruction is exact for a dot, and the activation
+//      image uses the same one);
+//    - promote: thread = weight row x 64 tokens; tcgen05.ld of the thread's 64 columns is
+//      started before the expansion and waited for after it, then per token
+//      f = fma(-z, asum, d) (exact; only in the kernel variant for weights with zero points),
+//      acc = fma(f, ws*as, acc); 64 fp32 accumulators stay in registers for the whole K loop
+//      and are stored at the end (coalesced over rows).
+//    With two or three warps per scheduler the loop's time is close to its instruction count
+//    times a dependent-issue latency, so it is kept short: ring positions are masks of one
+//    step counter, arrivals are predicated instructions, the accumulator barrier of the next
+//    group is tested while this group's load is in flight.
+//  * one thread starts the bulk (TMA) copies of the step's activation images (per k-tile 8 KiB
+//    of fp16 codes and 1 KiB of {as, (float)asum} per token, prepared by a pre-pass in the
+//    operand layout);
+//  * two MMA threads (in two warps, steps in turn): two tcgen05.mma (M=128, N=128, K=16) per
+//    k-tile into accumulator buffer b (the first MMA of a promote group overwrites it);
+//    tcgen05.commit signals the workers. The single-thread roles nap between polls of a
+//    barrier: back-to-back polling took a fifth of the schedulers' issue slots.
 //
 // Every mbarrier wait is bounded; on expiry the kernel records a status word, stops
 // issuing work, still frees its TMEM and returns.
@@ -94,11 +103,9 @@ struct TcParams {
                              // as[128], (float)asum[128]
     void *y;
     const float *as_tok;     // per-token scales (PERTOK kernels)
+    const int *zp_flag;      // written by the pre-pass: some zero point of the weight is not 0
     int *status;
     unsigned long long wait_ns;   // limit of every mbarrier wait
-#ifdef TQ_TC_TRACE
-    long long *trace;
-#endif
     int M, Kt, ksh, T, Tpad, out_bf16;
 };
 
@@ -118,13 +125,29 @@ __device__ __forceinline__ void store_token_chunks(uint8_t *blk, int tl, const i
                        h2_of(v[8 * j + 2], v[8 * j + 6]), h2_of(v[8 * j + 3], v[8 * j + 7]));
 }
 
+// Part of both pre-passes: sets *flag if any scale word of the weight carries a zero point
+// other than 0 (its low nibble). The GEMM is compiled with and without the zero-point term;
+// the flag says which of the two kernels does the work.
+__device__ __forceinline__ void scan_zero_points(const uint16_t *__restrict__ scales, size_t n,
+                                                 int *__restrict__ flag) {
+    const uint4 *v = reinterpret_cast<const uint4 *>(scales);      // 8 words at a time (n % 16 == 0)
+    uint32_t any = 0;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n / 8; i += (size_t)gridDim.x * blockDim.x) {
+        const uint4 w = __ldg(v + i);
+        any |= (w.x | w.y | w.z | w.w) & 0x000F000Fu;
+    }
+    if (__any_sync(0xffffffffu, any != 0) && (threadIdx.x & 31) == 0) atomicOr(flag, 1);
+}
+
 // Pre-pass: the caller's staging (aq[kt][tok][32], as[kt][tok], asum[kt][tok]) -> the images
 // the GEMM tiles copy with one bulk copy each. Tokens >= T are padded with zeros.
 __global__ void __launch_bounds__(256)
 gemm_tc_prepass_kernel(const int8_t *__restrict__ aq, const float *__restrict__ as,
                        const int32_t *__restrict__ asum, int T, int Tpad, int Kt,
-                       uint8_t *__restrict__ img) {
+                       uint8_t *__restrict__ img, const uint16_t *__restrict__ scales, size_t nscales,
+                       int *__restrict__ zp_flag) {
     pdl_trigger();
+    scan_zero_points(scales, nscales, zp_flag);
     const size_t nrow = (size_t)Kt * Tpad;
     for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < nrow; i += (size_t)gridDim.x * 256) {
         const int kt = (int)(i / Tpad), tok = (int)(i % Tpad);
@@ -154,8 +177,10 @@ gemm_tc_prepass_kernel(const int8_t *__restrict__ aq, const float *__restrict__ 
 __global__ void __launch_bounds__(256)
 gemm_tc_prepass_s4_kernel(const uint8_t *__restrict__ aq4, const float *__restrict__ as4,
                           const int32_t *__restrict__ asum4, int T, int Tpad, int Kt,
-                          uint8_t *__restrict__ img) {
+                          uint8_t *__restrict__ img, const uint16_t *__restrict__ scales, size_t nscales,
+                          int *__restrict__ zp_flag) {
     pdl_trigger();
+    scan_zero_points(scales, nscales, zp_flag);
     const size_t nrow = (size_t)Kt * Tpad;
     for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < nrow; i += (size_t)gridDim.x * 256) {
         const int kt = (int)(i / Tpad), tok = (int)(i % Tpad);
@@ -181,16 +206,6 @@ gemm_tc_prepass_s4_kernel(const uint8_t *__restrict__ aq4, const float *__restri
 }
 
 constexpr int kWaitMma = 21, kWaitEpi = 22, kWaitProd = 23;   // status codes of failed waits
-#ifdef TQ_TC_TRACE
-#define TC_STAMP(idx, which)                                                                  \
-    if (blockIdx.x == 0 && p.trace && (idx) < 256 && threadIdx.x == 0) p.trace[(idx) * 8 + (which)] = clock64();
-// regions 1 (MMA thread of the first MMA warp) and 2 (producer thread 0): the caller names the thread
-#define TC_STAMP_R(region, cond, idx, which)                                                  \
-    if (blockIdx.x == 0 && p.trace && (idx) < 256 && (cond)) p.trace[(region) * 2048 + (idx) * 8 + (which)] = clock64();
-#else
-#define TC_STAMP(idx, which)
-#define TC_STAMP_R(region, cond, idx, which)
-#endif
 
 // Eight two's-complement nibbles of w (nibble i = code k = i) -> eight fp16 values, as four
 // words holding the codes (0,4), (1,5), (2,6), (3,7). Per word: the two nibbles land in the
@@ -219,8 +234,14 @@ __device__ __forceinline__ uint4 nib8_to_h8(uint32_t w, uint32_t mask, uint32_t 
 // TMEM lanes; lane l expands row (l & 15) of k-tile (l >> 4) of a step, kAhead steps ahead
 // of the step it promotes. The loop is kept lean on purpose: with two or three warps per
 // scheduler its time is its instruction count times a dependent-issue latency.
-template <int GW, bool PERTOK>
+//
+// ZP: the kernel applies the zero-point term f = d - z * asum. Both variants are launched;
+// the one that does not match the pre-pass's flag returns at once.
+template <int GW, bool PERTOK, bool ZP>
 __global__ void __maxnreg__(168) gemm_w4a8_tc_kernel(const TcParams p) {
+    pdl_trigger();
+    pdl_wait();      // everything below reads what earlier kernels wrote (flag, images)
+    if ((*p.zp_flag != 0) != ZP) return;
     extern __shared__ __align__(1024) unsigned char smem[];
     __shared__ uint64_t bars[2 * kSS + 2 * kNB];   // full[kSS], empty[kSS], accfull[kNB], accempty[kNB]
     __shared__ uint32_t tmem_base_s;
@@ -252,9 +273,6 @@ __global__ void __maxnreg__(168) gemm_w4a8_tc_kernel(const TcParams p) {
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_s;
 
-    pdl_trigger();
-    pdl_wait();      // everything below reads the images an earlier kernel wrote
-
     const int Kt = p.Kt, Ktg = Kt >> p.ksh;
     const int spt = Kt >> 1;                             // steps per tile
     const int row_blocks = p.M / kTM, tok_blocks = p.Tpad / kTN;
@@ -277,12 +295,6 @@ __global__ void __maxnreg__(168) gemm_w4a8_tc_kernel(const TcParams p) {
         const int r16 = 16 * warp + erow;                 // the row this lane expands
         // this lane's four chunks inside a step slot: k-tile ehalf, row r16
         const uint32_t a_off = (uint32_t)(ehalf * kSlotBytes + (r16 >> 3) * kSboH + (r16 & 7) * 16);
-#ifdef TQ_TC_TRACE
-        long long tsum[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0}, tprev = clock64();
-#define TC_LAP(i) { const long long tnow = clock64(); tsum[i] += tnow - tprev; tprev = tnow; }
-#else
-#define TC_LAP(i)
-#endif
         uint32_t c_mask, c_bias;                           // see nib8_to_h8
         asm volatile("mov.b32 %0, 0x000F000F;" : "=r"(c_mask));
         asm volatile("mov.b32 %0, 0x64086408;" : "=r"(c_bias));
@@ -296,7 +308,7 @@ __global__ void __maxnreg__(168) gemm_w4a8_tc_kernel(const TcParams p) {
         };
         int f_n = 0, f_ti = 0, f_left = spt;
         const uint8_t *f_src = tile_src(0);
-        uint4 pre[kLoadAhead];
+        uint4 pre[kLoadAhead] = {};
         auto load_next = [&](uint4 &dst) {
             if (f_n < n_total) {
                 dst = ldg_stream_v4(f_src);
@@ -313,24 +325,19 @@ __global__ void __maxnreg__(168) gemm_w4a8_tc_kernel(const TcParams p) {
         // ---- expansion stream (step e_n): registers -> fp16 A operands of the step's slot
         int e_n = 0;
         auto expand = [&]() {
-            TC_LAP(2)
             const uint4 c4 = pre[0];
 #pragma unroll
             for (int i = 0; i + 1 < kLoadAhead; ++i) pre[i] = pre[i + 1];
             load_next(pre[kLoadAhead - 1]);
-            TC_LAP(7)
             if (e_n < n_total) {
                 unsigned char *dst = smem + (size_t)(e_n & (kSS - 1)) * kStepBytes + a_off;
                 *reinterpret_cast<uint4 *>(dst) = nib8_to_h8(c4.x, c_mask, c_bias);                 // k 0..7
                 *reinterpret_cast<uint4 *>(dst + kLboH) = nib8_to_h8(c4.y, c_mask, c_bias);         // k 8..15
                 *reinterpret_cast<uint4 *>(dst + 2 * kLboH) = nib8_to_h8(c4.z, c_mask, c_bias);     // k 16..23
                 *reinterpret_cast<uint4 *>(dst + 3 * kLboH) = nib8_to_h8(c4.w, c_mask, c_bias);     // k 24..31
-                TC_LAP(8)
                 fence_proxy_async_smem();   // generic-proxy stores -> visible to the MMA
-                TC_LAP(9)
                 __syncwarp();
                 mbar_arrive_if(full0 + (e_n & (kSS - 1)) * 8, lane == 0);
-                TC_LAP(10)
             }
             ++e_n;
         };
@@ -363,7 +370,6 @@ __global__ void __maxnreg__(168) gemm_w4a8_tc_kernel(const TcParams p) {
             for (int s = 0; s < spt; ++s, ++n) {
 #pragma unroll
                 for (int g = 0; g < (GW == 2 ? 1 : 2); ++g) {
-                    TC_LAP(5)
                     const int kt = 2 * s + g;              // first k-tile of the group
                     const int ig = (GW == 2) ? n : 2 * n + g;      // group counter of the CTA
                     const int b = ig & (kNB - 1);
@@ -373,9 +379,6 @@ __global__ void __maxnreg__(168) gemm_w4a8_tc_kernel(const TcParams p) {
                     if (kt + GW < Kt) scw = __ldg(sc + (size_t)((kt + GW) >> p.ksh) * 16);
                     const f32x2 ws2 = pack2(ws, ws);
                     const float nzf = (float)(-zp);
-                    // symmetric weights (every zero point of the warp's rows is 0) need no
-                    // zero-point term at all: the weights enter the MMA as true signed values
-                    const bool anyz = __any_sync(0xffffffffu, zp != 0);
                     // acc_ready: the barrier was already tested, with the previous group's
                     // load in flight (the test's answer takes about a hundred clocks)
                     if (!__all_sync(0xffffffffu,
@@ -384,30 +387,31 @@ __global__ void __maxnreg__(168) gemm_w4a8_tc_kernel(const TcParams p) {
                         break;
                     }
                     tc_fence_after();
-                    TC_LAP(0)
                     // One 64-column load of the thread's share of the accumulator: it holds
                     // (float)d of the group (the group's first MMA overwrites it), so nothing has
                     // to be converted or stored back. The load is in flight while the warp
                     // expands the weights of a later step.
                     uint32_t d[64];
-                    tmem_ld64(lane_base + b * kTN, d);
+                    {
+                        uint32_t (&dlo)[32] = *reinterpret_cast<uint32_t (*)[32]>(&d[0]);
+                        uint32_t (&dhi)[32] = *reinterpret_cast<uint32_t (*)[32]>(&d[32]);
+                        tmem_ld32(lane_base + b * kTN, dlo);
+                        tmem_ld32(lane_base + b * kTN + 32, dhi);
+                    }
                     {
                         const int ign = ig + 1;            // the CTA's next group, also across tiles
                         acc_ready = mbar_test_wait(acc0 + (ign & (kNB - 1)) * 8, (uint32_t)(ign / kNB) & 1u);
                     }
-                    TC_LAP(1)
                     if (g == 0) expand();                  // kAhead steps ahead
-                    TC_LAP(2)
                     const ulonglong2 *sv = reinterpret_cast<const ulonglong2 *>(
                         sv_base + (size_t)((n & (kSS - 1)) * 2 + g) * kSlotBytes);
                     // second k-tile of a K64 group: only its code sums are needed
                     const ulonglong2 *sv1 = reinterpret_cast<const ulonglong2 *>(
                         sv_base + (size_t)((n & (kSS - 1)) * 2 + 1) * kSlotBytes);
-                    // Straight-line code per variant (ANYZ is a compile-time tag): a test of `anyz`
-                    // inside the unrolled pair loop splits it into one basic block per pair, and the
-                    // pairs' short dependency chains then run one after the other.
-                    auto promote = [&](auto anyz_tag) {
-                        constexpr bool ANYZ = decltype(anyz_tag)::value;
+                    // symmetric weights need no zero-point term at all (the weights enter the
+                    // MMA as true signed values): ZP is a compile-time choice, a test inside the
+                    // unrolled loop would split it into one basic block per token group
+                    auto promote = [&]() {
 #pragma unroll
                         for (int j = 0; j < 16; ++j) {     // four tokens at a time
                             // scalar fmas on the loaded registers as they are: pairing them for
@@ -416,7 +420,7 @@ __global__ void __maxnreg__(168) gemm_w4a8_tc_kernel(const TcParams p) {
                             float f[4];
 #pragma unroll
                             for (int i = 0; i < 4; ++i) f[i] = __uint_as_float(d[4 * j + i]);
-                            if (ANYZ) {
+                            if (ZP) {
                                 ulonglong2 sm = sv[32 + j];                        // four code sums
                                 if (GW == 2) {                                     // exact: small integers
                                     const ulonglong2 sm1 = sv1[32 + j];
@@ -440,10 +444,7 @@ __global__ void __maxnreg__(168) gemm_w4a8_tc_kernel(const TcParams p) {
                         }
                     };
                     tmem_wait_ld_all();
-                    TC_LAP(3)
-                    if (anyz) promote(std::true_type{});
-                    else promote(std::false_type{});
-                    TC_LAP(4)
+                    promote();
                     tc_fence_before();
                     __syncwarp();
                     // one instruction, two barriers: lane 0 tells the MMA that it may overwrite
@@ -477,12 +478,6 @@ __global__ void __maxnreg__(168) gemm_w4a8_tc_kernel(const TcParams p) {
                 }
             }
         }
-#ifdef TQ_TC_TRACE
-        if (blockIdx.x == 0 && p.trace && lane == 0) {
-            for (int i = 0; i < 12; ++i) p.trace[warp * 16 + i] = tsum[i];
-            p.trace[warp * 16 + 12] = n;
-        }
-#endif
     } else if (warp == kWorkWarps) {
         // ====================== image copies (one thread) =================================
         // Two bulk copies per step bring the activation images of its k-tiles for the tile's
@@ -548,12 +543,10 @@ __global__ void __maxnreg__(168) gemm_w4a8_tc_kernel(const TcParams p) {
 struct TcScratch {
     uint8_t *img = nullptr;
     size_t img_bytes = 0;
+    int *zp_flag = nullptr;
 } g_tc;
 
 int g_tc_sms = 0;
-#ifdef TQ_TC_TRACE
-long long *g_tc_trace = nullptr;
-#endif
 
 }  // namespace
 
@@ -569,14 +562,18 @@ int launch_gemm_tc(const GemmTcArgs &a) {
         TQ_CHECK(cudaGetDevice(&dev));
         TQ_CHECK(cudaDeviceGetAttribute(&g_tc_sms, cudaDevAttrMultiProcessorCount, dev));
         if (g_tc_sms <= 0) g_tc_sms = 148;
-        TQ_CHECK(cudaFuncSetAttribute(gemm_w4a8_tc_kernel<1, false>,
-                                      cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-        TQ_CHECK(cudaFuncSetAttribute(gemm_w4a8_tc_kernel<1, true>,
-                                      cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-        TQ_CHECK(cudaFuncSetAttribute(gemm_w4a8_tc_kernel<2, true>,
-                                      cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-        TQ_CHECK(cudaFuncSetAttribute(gemm_w4a8_tc_kernel<2, false>,
-                                      cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+        auto big_smem = [](auto kernel) {
+            return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        };
+        TQ_CHECK(big_smem(gemm_w4a8_tc_kernel<1, false, false>));
+        TQ_CHECK(big_smem(gemm_w4a8_tc_kernel<1, false, true>));
+        TQ_CHECK(big_smem(gemm_w4a8_tc_kernel<1, true, false>));
+        TQ_CHECK(big_smem(gemm_w4a8_tc_kernel<1, true, true>));
+        TQ_CHECK(big_smem(gemm_w4a8_tc_kernel<2, true, false>));
+        TQ_CHECK(big_smem(gemm_w4a8_tc_kernel<2, true, true>));
+        TQ_CHECK(big_smem(gemm_w4a8_tc_kernel<2, false, false>));
+        TQ_CHECK(big_smem(gemm_w4a8_tc_kernel<2, false, true>));
+        g_tc.zp_flag = static_cast<int *>(tq_dev_alloc(sizeof(int), "gemm.tc.zero-point.flag"));
     }
     const int Tpad = (a.T + kTN - 1) / kTN * kTN;
     const size_t ibytes = (size_t)Kt * (Tpad / kTN) * (kBBytes + kSBytes);
@@ -587,47 +584,40 @@ int launch_gemm_tc(const GemmTcArgs &a) {
     }
     const size_t nrow = (size_t)Kt * Tpad;
     const int pgrid = (int)std::min<size_t>((nrow + 255) / 256, (size_t)g_tc_sms * 8);
+    const size_t nscales = (size_t)a.M * (Kt >> a.ksh);
+    TQ_CHECK(cudaMemsetAsync(g_tc.zp_flag, 0, sizeof(int), stream()));
     if (a.aq4)
         gemm_tc_prepass_s4_kernel<<<pgrid, 256, 0, stream()>>>(a.aq4, a.as, a.asum, a.T, Tpad, Kt,
-                                                              g_tc.img);
+                                                              g_tc.img, a.scales, nscales, g_tc.zp_flag);
     else
-        gemm_tc_prepass_kernel<<<pgrid, 256, 0, stream()>>>(a.aq, a.as, a.asum, a.T, Tpad, Kt, g_tc.img);
+        gemm_tc_prepass_kernel<<<pgrid, 256, 0, stream()>>>(a.aq, a.as, a.asum, a.T, Tpad, Kt, g_tc.img,
+                                                           a.scales, nscales, g_tc.zp_flag);
     TQ_LAUNCH_CHECK("gemm_tc_prepass_kernel");
     TcParams p{};
     p.codes = a.codes; p.scales = a.scales; p.img = g_tc.img; p.y = a.y;
     p.status = device_status_word();
     p.wait_ns = wait_limit_ns();
-#ifdef TQ_TC_TRACE
-    {
-        static long long *tr = nullptr;
-        if (!tr) tr = static_cast<long long *>(tq_dev_alloc(3 * 256 * 8 * 8, "tc.trace"));
-        TQ_CHECK(cudaMemsetAsync(tr, 0, 3 * 256 * 8 * 8, stream()));
-        p.trace = tr;
-        g_tc_trace = tr;
-    }
-#endif
     p.M = a.M; p.Kt = Kt; p.ksh = a.ksh; p.T = a.T; p.Tpad = Tpad; p.out_bf16 = a.out_bf16;
     const int ntiles = (a.M / kTM) * (Tpad / kTN);
     const int grid = std::min(g_tc_sms, ntiles);
     p.as_tok = a.as_tok;
+    p.zp_flag = g_tc.zp_flag;
+    // both variants of the kernel: the one the flag does not select returns at once
+    auto both = [&](auto without_zp, auto with_zp) {
+        launch_pdl(without_zp, dim3(grid), dim3(kThreads), (size_t)kSmemBytes, p);
+        launch_pdl(with_zp, dim3(grid), dim3(kThreads), (size_t)kSmemBytes, p);
+    };
     if (a.aq4)
-        launch_pdl(gemm_w4a8_tc_kernel<2, false>, dim3(grid), dim3(kThreads), (size_t)kSmemBytes, p);
+        both(gemm_w4a8_tc_kernel<2, false, false>, gemm_w4a8_tc_kernel<2, false, true>);
     else if (!a.as_tok)
-        launch_pdl(gemm_w4a8_tc_kernel<1, false>, dim3(grid), dim3(kThreads), (size_t)kSmemBytes, p);
+        both(gemm_w4a8_tc_kernel<1, false, false>, gemm_w4a8_tc_kernel<1, false, true>);
     else if (a.ksh)
-        launch_pdl(gemm_w4a8_tc_kernel<2, true>, dim3(grid), dim3(kThreads), (size_t)kSmemBytes, p);
+        both(gemm_w4a8_tc_kernel<2, true, false>, gemm_w4a8_tc_kernel<2, true, true>);
     else
-        launch_pdl(gemm_w4a8_tc_kernel<1, true>, dim3(grid), dim3(kThreads), (size_t)kSmemBytes, p);
+        both(gemm_w4a8_tc_kernel<1, true, false>, gemm_w4a8_tc_kernel<1, true, true>);
     TQ_LAUNCH_CHECK("gemm_w4a8_tc_kernel");
     return 0;
 }
 
 }  // namespace tq
 
-#ifdef TQ_TC_TRACE
-extern "C" int qwn_dbg_tc_trace(long long *host_out) {
-    if (!tq::g_tc_trace) return -1;
-    tq_d2h(host_out, tq::g_tc_trace, 3 * 256 * 8 * 8);
-    return 0;
-}
-#endif
