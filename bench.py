@@ -556,7 +556,9 @@ class Stack:
                 assert lib.tq_comm_sym_register(i, one(b.ptr)) == 0
         self.weight_bytes = self.L * sum(wl.weight_bytes(M, K, 32) for M, K, _ in shapes)
         self.algo_bytes = self.weight_bytes
-        self.launches_per_step = self.L * 10 + (2 if tp > 1 else 0)
+        # per layer: norm+staging, 4 GEMMs, 2 stagings, silu*mul+staging (tp 1: one launch; tp > 1: the
+        # scatter and the staging behind the exchange point)
+        self.launches_per_step = self.L * (8 if tp == 1 else 9) + (2 if tp > 1 else 0)
         self.single_out = True
         self.graph = None
 
@@ -609,27 +611,30 @@ class Stack:
         lib, T, tp, r = self.ctx.lib, self.T, self.tp, self.rank
         n_i = I_FF // tp
         for l, (w1, w2, wg, wu, wd) in enumerate(self.layers):
-            if l == 0 or tp == 1:
-                lib.qwn_x_rmsnorm_chunk(self.xn.ptr, x_ptr if l == 0 else self.y4.ptr, self.norm_w.ptr, H, T,
-                                        1e-6)
-            else:
-                lib.qwn_x_rmsnorm_chunk_sync(self.xn.ptr, self.y4.ptr, self.norm_w.ptr, H, T, 1e-6)
-            self._stage(self.xn.ptr, H, False)
+            # norm and per-token staging in one launch (at tp > 1 it carries the exchange point
+            # behind the previous layer's last projection)
+            lib.qwn_x_rmsnorm_quant_chunk_pertoken(self.xn.ptr, x_ptr if l == 0 else self.y4.ptr, self.norm_w.ptr,
+                                                   H, T, 1e-6, self.aq.ptr, self.as_.ptr, self.asum.ptr,
+                                                   self.as_tok.ptr, int(l > 0 and tp > 1))
             self._gemm([w1], [QKV], 0, [r * (QKV // tp)], QKV)
             self._stage(self.y1.ptr, QKV, True)
             self._gemm([w2], [H], 1, [r * (H // tp)], H)
             self._stage(self.y2.ptr, H, True)
             self._gemm([wg, wu], [I_FF, I_FF], -1, None, 0, ys=[self.gu.ptr, self.gu.ptr + T * n_i * 4])
-            assert lib.qwn_x_silu_mul_scatter(self.gu.ptr, self.gu.ptr + T * n_i * 4, T, n_i, 2, r * n_i,
-                                              I_FF) == 0
-            self._stage(self.h.ptr, I_FF, True)
+            if tp == 1:
+                lib.qwn_x_silu_mul_quant_chunk_pertoken(self.h.ptr, self.gu.ptr, self.gu.ptr + T * n_i * 4, I_FF, T,
+                                                        self.aq.ptr, self.as_.ptr, self.asum.ptr, self.as_tok.ptr)
+            else:
+                assert lib.qwn_x_silu_mul_scatter(self.gu.ptr, self.gu.ptr + T * n_i * 4, T, n_i, 2, r * n_i,
+                                                  I_FF) == 0
+                self._stage(self.h.ptr, I_FF, True)
             self._gemm([wd], [H], 3, [r * (H // tp)], H)
         if tp > 1:
             assert lib.tq_comm_exchange_sync() == 0
             assert lib.tq_comm_exchange_advance() == 0
 
     def capture(self):
-        """One CUDA graph per input buffer: 642 launches per replay."""
+        """One CUDA graph per input buffer (`launches_per_step` kernels per replay)."""
         lib = self.ctx.lib
         self._issue(self.x_dev[0].ptr)        # warm: all scratch allocated
         lib.tq_sync()
@@ -952,7 +957,7 @@ def run_single(args):
                              "peak": ctx.peak_hbm, "unit": "GB/s",
                              "frac": st.weight_bytes / (st_ms * 1e-3) / 1e9 / ctx.peak_hbm,
                              "peak_source": f"{ctx.peak_kind} copy bandwidth",
-                             "kernel": "whole step (CUDA graph: norm, 4 stagings, 4 GEMMs, silu*mul per layer)",
+                             "kernel": "whole step (CUDA graph: norm+staging, 4 GEMMs, 2 stagings, silu*mul+staging per layer)",
                              "algorithmic_bytes_per_launch": int(st.weight_bytes), "traffic": None},
                 "e2e": {"value": st.weight_bytes / s5 / 1e9, "unit": UNIT, "us_per_step": s5 * 1e6,
                         "h2d_bytes_per_step": int(st.x_host.nbytes), "d2h_bytes_per_step": int(st.out_bytes),

@@ -154,7 +154,7 @@ def run(args, rank, local_rank, world):
                                       "the next staging kernel carries the exchange point",
                        "l2": f"inputs larger than L2: {wb / world / 1e9:.2f} GB of distinct weights per GPU "
                              "per step",
-                       "step": f"{st.L} layers x (norm, 4 stagings, 4 GEMMs, silu*mul) replayed as one CUDA "
+                       "step": f"{st.L} layers x (norm+staging, 4 GEMMs, 3 stagings, silu*mul scatter) replayed as one CUDA "
                                f"graph; {4 * st.L} exchange points per step"},
             "tp1_ms_per_step": tp1["ms"],
             "tp1_words_differing": diff,

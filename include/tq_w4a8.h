@@ -407,6 +407,18 @@ void qwn_x_quantize_act_chunk_sync(const float *d_x, int K, int T, int8_t *d_aq,
 void qwn_x_quantize_act_chunk_pertoken_sync(const float *d_x, int K, int T, int8_t *d_aq, float *d_as,
                                             int32_t *d_asum, float *d_as_tok);
 void qwn_x_rmsnorm_chunk_sync(float *d_out, const float *d_in, const uint16_t *d_w, int H, int T, float eps);
+/* Two decode-batch fusions, each the same bits as the two calls it replaces (own additions;
+ * the reference runs the separate kernels, xpu/src/kernels_dpas.cpp:1124-1144, 185-206):
+ * x_rmsnorm_chunk then x_quantize_act_chunk_pertoken of its output (sync != 0: the kernel
+ * carries the next exchange point, like x_rmsnorm_chunk_sync), and x_silu_mul then the same
+ * quantiser. d_out receives the intermediate rows [T][H] / [T][K]. For T <= 32 and rows
+ * that divide into K32-aligned slices it is one launch of thread-block clusters (8, 4 or 2
+ * CTAs per token, row maxima joined through distributed shared memory). */
+void qwn_x_rmsnorm_quant_chunk_pertoken(float *d_out, const float *d_in, const uint16_t *d_w, int H, int T,
+                                        float eps, int8_t *d_aq, float *d_as, int32_t *d_asum,
+                                        float *d_as_tok, int sync);
+void qwn_x_silu_mul_quant_chunk_pertoken(float *d_out, const float *d_gate, const float *d_up, int K, int T,
+                                         int8_t *d_aq, float *d_as, int32_t *d_asum, float *d_as_tok);
 int qwn_x_silu_mul_scatter(const float *d_gate, const float *d_up, int T, int n, int slot, size_t col_off,
                            size_t ld);
 int tq_comm_rank(void);
@@ -473,6 +485,11 @@ void x_quantize_act_chunk_sync(const float *d_x, int K, int T, int8_t *d_aq, flo
 void x_quantize_act_chunk_pertoken_sync(const float *d_x, int K, int T, int8_t *d_aq, float *d_as,
                                         int32_t *d_asum, float *d_as_tok);
 void x_rmsnorm_chunk_sync(float *d_out, const float *d_in, const uint16_t *d_w, int H, int T, float eps);
+void x_rmsnorm_quant_chunk_pertoken(float *d_out, const float *d_in, const uint16_t *d_w, int H, int T,
+                                    float eps, int8_t *d_aq, float *d_as, int32_t *d_asum, float *d_as_tok,
+                                    int sync);
+void x_silu_mul_quant_chunk_pertoken(float *d_out, const float *d_gate, const float *d_up, int K, int T,
+                                     int8_t *d_aq, float *d_as, int32_t *d_asum, float *d_as_tok);
 int x_silu_mul_scatter(const float *d_gate, const float *d_up, int T, int n, int slot, size_t col_off,
                        size_t ld);
 void x_prepare_gemv_act_s8_pertoken(const float *d_x, int K);

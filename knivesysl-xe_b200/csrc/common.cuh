@@ -99,6 +99,13 @@ void launch_quant_chunk_s4(const float *d_x, int K, int T, uint8_t *d_aq4, float
                            int32_t *d_asum4);
 void launch_quant_chunk_pertoken(const float *d_x, int K, int T, int8_t *d_aq, float *d_as,
                                  int32_t *d_asum, float *d_as_tok, const SyncArgs *sync = nullptr);
+// rmsnorm_chunk / silu_mul followed by quant_chunk_pertoken of the result, in one launch for
+// decode batches (the intermediate rows are written to d_out as well)
+void launch_rmsnorm_quant_chunk_pertoken(float *d_out, const float *d_in, const uint16_t *d_w, int H, int T,
+                                         float eps, int8_t *d_aq, float *d_as, int32_t *d_asum,
+                                         float *d_as_tok, const SyncArgs *sync = nullptr);
+void launch_silu_mul_quant_chunk_pertoken(float *d_out, const float *d_gate, const float *d_up, int K, int T,
+                                          int8_t *d_aq, float *d_as, int32_t *d_asum, float *d_as_tok);
 // out[p][tok * ld + j] = silu(gate[tok][j]) * up[tok][j] for j < n, into ndst destinations
 void launch_silu_mul_scatter(float *const *dst, int ndst, const float *d_gate, const float *d_up, int T,
                              int n, size_t ld);
@@ -264,6 +271,39 @@ inline void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t s
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     TQ_CHECK(cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...));
+}
+
+// The same for a kernel whose CTAs form thread-block clusters of `cluster` CTAs along x.
+template <class... KArgs, class... Args>
+inline void launch_pdl_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, unsigned cluster,
+                               Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = stream();
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = cluster;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    TQ_CHECK(cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...));
+}
+
+// ---- thread-block cluster helpers (distributed shared memory) -----------------------
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Stores v at the address that `local` (a shared-memory address of this CTA) has in CTA
+// `rank` of the cluster.
+__device__ __forceinline__ void st_cluster_f32(uint32_t local, uint32_t rank, float v) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
 }
 
 // The exchange point of a consuming kernel (see SyncArgs); call after pdl_wait().

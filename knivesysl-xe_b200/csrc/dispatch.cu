@@ -653,6 +653,30 @@ void x_rmsnorm_chunk_sync(float *d_out, const float *d_in, const uint16_t *d_w, 
     launch_rmsnorm_chunk(d_out, d_in, d_w, H, T, eps, &sa);
 }
 
+// x_rmsnorm_chunk followed by x_quantize_act_chunk_pertoken of its output, and x_silu_mul
+// followed by the same quantiser: one launch for decode batches, the same bits as the two
+// calls (own additions: the reference runs the two kernels, xpu/src/kernels_dpas.cpp:
+// 1124-1144 and 185-206). sync != 0: the kernel carries the next exchange point.
+void x_rmsnorm_quant_chunk_pertoken(float *d_out, const float *d_in, const uint16_t *d_w, int H, int T,
+                                    float eps, int8_t *d_aq, float *d_as, int32_t *d_asum, float *d_as_tok,
+                                    int sync) {
+    if (!d_out || !d_in || !d_w || !d_aq || !d_as || !d_asum || !d_as_tok || H <= 0 || T <= 0 || (H % 32) != 0)
+        return;
+    if (sync) {
+        const SyncArgs sa = exchange_point();
+        launch_rmsnorm_quant_chunk_pertoken(d_out, d_in, d_w, H, T, eps, d_aq, d_as, d_asum, d_as_tok, &sa);
+    } else {
+        launch_rmsnorm_quant_chunk_pertoken(d_out, d_in, d_w, H, T, eps, d_aq, d_as, d_asum, d_as_tok, nullptr);
+    }
+}
+
+void x_silu_mul_quant_chunk_pertoken(float *d_out, const float *d_gate, const float *d_up, int K, int T,
+                                     int8_t *d_aq, float *d_as, int32_t *d_asum, float *d_as_tok) {
+    if (!d_out || !d_gate || !d_up || !d_aq || !d_as || !d_asum || !d_as_tok || K <= 0 || T <= 0 || (K % 32) != 0)
+        return;
+    launch_silu_mul_quant_chunk_pertoken(d_out, d_gate, d_up, K, T, d_aq, d_as, d_asum, d_as_tok);
+}
+
 // silu(gate) * up of this rank's column slice [T][n] into columns [col_off, col_off + n) of the
 // symmetric [T][ld] matrix `slot` of every rank.
 int x_silu_mul_scatter(const float *d_gate, const float *d_up, int T, int n, int slot, size_t col_off,
@@ -985,6 +1009,15 @@ void qwn_x_quantize_act_chunk_pertoken_sync(const float *d_x, int K, int T, int8
 }
 void qwn_x_rmsnorm_chunk_sync(float *d_out, const float *d_in, const uint16_t *d_w, int H, int T, float eps) {
     x_rmsnorm_chunk_sync(d_out, d_in, d_w, H, T, eps);
+}
+void qwn_x_rmsnorm_quant_chunk_pertoken(float *d_out, const float *d_in, const uint16_t *d_w, int H, int T,
+                                        float eps, int8_t *d_aq, float *d_as, int32_t *d_asum,
+                                        float *d_as_tok, int sync) {
+    x_rmsnorm_quant_chunk_pertoken(d_out, d_in, d_w, H, T, eps, d_aq, d_as, d_asum, d_as_tok, sync);
+}
+void qwn_x_silu_mul_quant_chunk_pertoken(float *d_out, const float *d_gate, const float *d_up, int K, int T,
+                                         int8_t *d_aq, float *d_as, int32_t *d_asum, float *d_as_tok) {
+    x_silu_mul_quant_chunk_pertoken(d_out, d_gate, d_up, K, T, d_aq, d_as, d_asum, d_as_tok);
 }
 int qwn_x_silu_mul_scatter(const float *d_gate, const float *d_up, int T, int n, int slot, size_t col_off,
                            size_t ld) {

@@ -455,6 +455,14 @@ __device__ __forceinline__ void scale_pair(uint32_t packed, float &ws, float &z8
 // acc = fma((float)(d - z*asum), ws, acc) with d the int32 dot of the whole group (both k-tiles
 // of a K64 group chained through the MMA's accumulator input) - splits cut whole groups, and
 // the per-token scale multiplies the sum of the splits at the end.
+#ifdef TQ_RING_TRACE
+__device__ unsigned long long g_ring_trace[1024 * 8];
+#define RING_STAMP(i) if (threadIdx.x == 0 && blockIdx.x < 1024) g_ring_trace[blockIdx.x * 8 + (i)] = global_timer_ns();
+#define RING_STAMP_END() if (lane == 0 && blockIdx.x < 1024) atomicMax(&g_ring_trace[blockIdx.x * 8 + 5], global_timer_ns());
+#else
+#define RING_STAMP(i)
+#define RING_STAMP_END()
+#endif
 template <bool PAIR, int kRNS, int MAXW, bool PT>
 __global__ void __launch_bounds__(MAXW * 32, 1)
 gemm_w4a8_ring_kernel(const GemmArgs a, float *__restrict__ part, int *__restrict__ count) {
@@ -532,11 +540,14 @@ gemm_w4a8_ring_kernel(const GemmArgs a, float *__restrict__ part, int *__restric
         cp_async_commit();
     };
 
+    RING_STAMP(0)
     pdl_trigger();
 #pragma unroll
     for (int i = 0; i < kRNS - 1; ++i) issue_next();
+    RING_STAMP(1)
     // Everything above reads only packed weights; what follows depends on earlier kernels.
     pdl_wait();
+    RING_STAMP(2)
 
     // Stage this split's activations (layout of the register-queue kernel for T = 8, but the
     // code sums are stored negated: the tile loop multiplies them by z + 8 >= 0).
@@ -608,19 +619,32 @@ gemm_w4a8_ring_kernel(const GemmArgs a, float *__restrict__ part, int *__restric
         }
         __syncthreads();
     } else {
-        const int items = cnt * 32;
-        for (int i = threadIdx.x; i < items; i += nw * 32) {
-            const int kl = i >> 5;
-            const int rem = i & 31;
-            const uint2 bb = __ldg(reinterpret_cast<const uint2 *>(
-                a.aq + ((size_t)(kt_begin + kl) * Ttot + tok0) * 32 + (size_t)rem * 8));
-            uint2 o;
-            o.x = __byte_perm(bb.x, bb.y, 0x6420);
-            o.y = __byte_perm(bb.x, bb.y, 0x7531);
-            *reinterpret_cast<uint2 *>(act + (size_t)kl * kActTileBytes + rem * 8) = o;
+        // All of a thread's loads of a pass are issued before its first store: the staging is a
+        // chain of L2 latencies, and a loop of load-then-store pays one per iteration.
+        const int items = cnt * 32, nthr = nw * 32;
+        constexpr int kSU = 4;
+        for (int i0 = threadIdx.x; i0 < items; i0 += nthr * kSU) {
+            uint2 bb[kSU];
+#pragma unroll
+            for (int u = 0; u < kSU; ++u) {
+                const int i = i0 + u * nthr;
+                if (i < items)
+                    bb[u] = __ldg(reinterpret_cast<const uint2 *>(
+                        a.aq + ((size_t)(kt_begin + (i >> 5)) * Ttot + tok0) * 32 + (size_t)(i & 31) * 8));
+            }
+#pragma unroll
+            for (int u = 0; u < kSU; ++u) {
+                const int i = i0 + u * nthr;
+                if (i < items) {
+                    uint2 o;
+                    o.x = __byte_perm(bb[u].x, bb[u].y, 0x6420);
+                    o.y = __byte_perm(bb[u].x, bb[u].y, 0x7531);
+                    *reinterpret_cast<uint2 *>(act + (size_t)(i >> 5) * kActTileBytes + (i & 31) * 8) = o;
+                }
+            }
         }
         const int pairs = cnt * 4;
-        for (int i = threadIdx.x; i < pairs; i += nw * 32) {
+        for (int i = threadIdx.x; i < pairs; i += nthr) {
             const int kl = i >> 2;
             const int rem = i & 3;
             const size_t src = (size_t)(kt_begin + kl) * Ttot + tok0 + (size_t)rem * 2;
@@ -638,6 +662,7 @@ gemm_w4a8_ring_kernel(const GemmArgs a, float *__restrict__ part, int *__restric
         __syncthreads();
     }
 
+    RING_STAMP(3)
     const f32x2 neg_magic2 = pack2(-kMagicF, -kMagicF);
     int cmagic[4];
     make_const_quad(cmagic, kMagicBits);
@@ -791,6 +816,8 @@ gemm_w4a8_ring_kernel(const GemmArgs a, float *__restrict__ part, int *__restric
                 *reinterpret_cast<float4 *>(a.ypeer[pi][wi] + off) = v;
         }
     }
+    RING_STAMP(4)
+    RING_STAMP_END()
 }
 
 int g_num_sms = 0;
@@ -1015,3 +1042,13 @@ void launch_gemm_stream(const GemmArgs &a) {
 }
 
 }  // namespace tq
+
+#ifdef TQ_RING_TRACE
+extern "C" int qwn_dbg_ring_trace(unsigned long long *out, int clear) {
+    if (clear) {
+        static unsigned long long z[1024 * 8];
+        return (int)cudaMemcpyToSymbol(tq::g_ring_trace, z, sizeof(z));
+    }
+    return (int)cudaMemcpyFromSymbol(out, tq::g_ring_trace, 1024 * 8 * 8);
+}
+#endif

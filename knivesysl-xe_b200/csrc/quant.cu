@@ -390,6 +390,116 @@ quant_chunk_pertoken_regs_kernel(const float *__restrict__ x, int K, int T,
     }
 }
 
+// The same result with a token's row spread over a cluster of C CTAs (grid (C, T), cluster
+// (C, 1, 1)): each CTA keeps its K / C values in registers, the CTAs' maxima meet through
+// distributed shared memory (every CTA stores its own into all C copies of cmax[], one
+// cluster barrier), and each CTA quantises its slice. A maximum does not depend on the order
+// it is taken in, so the codes, sums and scales are those of the kernels above, bit for bit;
+// a decode batch of 8 tokens now runs on 8 C SMs instead of 8, and a row is read once
+// whatever its length.
+//
+// SRC selects where the row comes from: 0 = x; 1 = the (1+w) RMSNorm of `x` (weights w2),
+// every CTA computing the row's sum of squares itself with rmsnorm_chunk_kernel's order of
+// additions; 2 = silu(x) * x2. For 1 and 2 the row is also written to `out`, and the result is
+// that of the separate kernel followed by the quantiser, bit for bit, in one launch.
+struct ClusterSrc {
+    const float *x;          // SRC 0: the rows; 1: the rows before the norm; 2: gate
+    const float *x2;         // SRC 2: up
+    const uint16_t *w;       // SRC 1: bf16 norm weights
+    float *out;              // SRC 1, 2: the rows that are quantised
+    float eps;
+};
+template <int SRC>
+__global__ void __launch_bounds__(256)
+quant_chunk_pertoken_cluster_kernel(const ClusterSrc src, int K, int T,
+                                    int8_t *__restrict__ aq, float *__restrict__ as,
+                                    int32_t *__restrict__ asum, float *__restrict__ as_tok,
+                                    const SyncArgs sync) {
+    pdl_trigger();
+    pdl_wait();
+    exchange_sync(sync);
+    __shared__ float wmax[8];
+    __shared__ float cmax[8];
+    __shared__ float p[256];
+    const int C = gridDim.x, c = blockIdx.x, tok = blockIdx.y;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n4s = (K / C) >> 2;                           // float4 per slice, a multiple of 8
+    const size_t row0 = (size_t)tok * K;
+    float rms_inv = 0.0f;
+    if (SRC == 1) {
+        const float *row = src.x + row0;
+        float ss = 0.0f;
+        for (int i = tid; i < K; i += 256) ss = __fadd_rn(ss, __fmul_rn(row[i], row[i]));
+        p[tid] = ss;
+        __syncthreads();
+        for (int stride = 128; stride >= 1; stride >>= 1) {
+            if (tid < stride) p[tid] = __fadd_rn(p[tid], p[tid + stride]);
+            __syncthreads();
+        }
+        rms_inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(p[0], (float)K), src.eps)));
+    }
+    const float4 *row4 = reinterpret_cast<const float4 *>(src.x + row0) + (size_t)c * n4s;
+    float4 v[4];
+    float m = -INFINITY;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        const int i = tid + u * 256;
+        v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (i < n4s) {
+            v[u] = row4[i];
+            if (SRC == 1) {
+                const uint2 w4 = reinterpret_cast<const uint2 *>(src.w)[(size_t)c * n4s + i];   // four bf16
+                v[u].x = __fmul_rn(__fmul_rn(v[u].x, rms_inv), __fadd_rn(1.0f, __uint_as_float(w4.x << 16)));
+                v[u].y = __fmul_rn(__fmul_rn(v[u].y, rms_inv), __fadd_rn(1.0f, __uint_as_float(w4.x & 0xFFFF0000u)));
+                v[u].z = __fmul_rn(__fmul_rn(v[u].z, rms_inv), __fadd_rn(1.0f, __uint_as_float(w4.y << 16)));
+                v[u].w = __fmul_rn(__fmul_rn(v[u].w, rms_inv), __fadd_rn(1.0f, __uint_as_float(w4.y & 0xFFFF0000u)));
+            }
+            if (SRC == 2) {
+                const float4 up = (reinterpret_cast<const float4 *>(src.x2 + row0) + (size_t)c * n4s)[i];
+                v[u] = make_float4(silu_mul_f(v[u].x, up.x), silu_mul_f(v[u].y, up.y), silu_mul_f(v[u].z, up.z),
+                                   silu_mul_f(v[u].w, up.w));
+            }
+            if (SRC != 0) (reinterpret_cast<float4 *>(src.out + row0) + (size_t)c * n4s)[i] = v[u];
+            m = fmaxf(m, fmaxf(fmaxf(fabsf(v[u].x), fabsf(v[u].y)), fmaxf(fabsf(v[u].z), fabsf(v[u].w))));
+        }
+    }
+    m = warp_max(m);
+    if (lane == 0) wmax[warp] = m;
+    __syncthreads();
+    if (warp == 0) {
+        const float t = warp_max(lane < 8 ? wmax[lane] : -INFINITY);
+        if (lane < C) st_cluster_f32((uint32_t)__cvta_generic_to_shared(&cmax[c]), (uint32_t)lane, t);
+    }
+    cluster_sync_all();
+    float t = cmax[0];
+    for (int j = 1; j < C; ++j) t = fmaxf(t, cmax[j]);
+    const float s = (t > 0.0f) ? __fdiv_rn(t, 127.0f) : 1.0f;
+    if (c == 0 && tid == 0) as_tok[tok] = s;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        const int i = tid + u * 256;                 // float4 index in the slice; uniform per warp
+        if (i - lane >= n4s) break;
+        const int q0 = quantise_one(v[u].x, s), q1 = quantise_one(v[u].y, s);
+        const int q2 = quantise_one(v[u].z, s), q3 = quantise_one(v[u].w, s);
+        int sum = q0 + q1 + q2 + q3;
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+        if (i < n4s) {
+            const int gi = c * n4s + i;              // float4 index in the row
+            const int kt = gi >> 3;                  // eight float4 per K32 block
+            const size_t blk = (size_t)kt * T + tok;
+            const uint32_t packed = (uint32_t)(q0 & 0xFF) | ((uint32_t)(q1 & 0xFF) << 8) |
+                                    ((uint32_t)(q2 & 0xFF) << 16) | ((uint32_t)(q3 & 0xFF) << 24);
+            reinterpret_cast<uint32_t *>(aq + blk * 32)[gi & 7] = packed;
+            if ((gi & 7) == 0) {
+                as[blk] = s;
+                asum[blk] = sum;
+            }
+        }
+    }
+}
+
 // K32 code sums of already staged codes (debug helper for the int32 dump).
 __global__ void code_sums_kernel(const int8_t *__restrict__ aq, size_t blocks,
                                  int32_t *__restrict__ asum) {
@@ -503,11 +613,49 @@ void launch_quant_chunk_s4(const float *d_x, int K, int T, uint8_t *d_aq4, float
     TQ_LAUNCH_CHECK("quant_chunk_s4_kernel");
 }
 
+// Decode batches: a cluster of 8, 4 or 2 CTAs per token when the row divides into K32-aligned
+// slices of at most 4096 values. False: the shape is not covered, nothing was launched.
+template <int SRC>
+bool launch_quant_cluster(const ClusterSrc &src, int K, int T, int8_t *d_aq, float *d_as, int32_t *d_asum,
+                          float *d_as_tok, const SyncArgs &sa) {
+    if (T > 32) return false;
+    for (unsigned c = 8; c >= 2; c >>= 1) {
+        if (K % (32 * (int)c) || K / (int)c > 4096) continue;
+        launch_pdl_cluster(quant_chunk_pertoken_cluster_kernel<SRC>, dim3(c, T), dim3(256), c, src, K, T, d_aq,
+                           d_as, d_asum, d_as_tok, sa);
+        TQ_LAUNCH_CHECK("quant_chunk_pertoken_cluster_kernel");
+        return true;
+    }
+    return false;
+}
+
+void launch_rmsnorm_quant_chunk_pertoken(float *d_out, const float *d_in, const uint16_t *d_w, int H, int T,
+                                         float eps, int8_t *d_aq, float *d_as, int32_t *d_asum,
+                                         float *d_as_tok, const SyncArgs *sync) {
+    const SyncArgs sa = sync ? *sync : kNoSync;
+    if (launch_quant_cluster<1>(ClusterSrc{d_in, nullptr, d_w, d_out, eps}, H, T, d_aq, d_as, d_asum, d_as_tok, sa))
+        return;
+    launch_rmsnorm_chunk(d_out, d_in, d_w, H, T, eps, sync);
+    launch_quant_chunk_pertoken(d_out, H, T, d_aq, d_as, d_asum, d_as_tok, nullptr);
+}
+
+void launch_silu_mul_quant_chunk_pertoken(float *d_out, const float *d_gate, const float *d_up, int K, int T,
+                                          int8_t *d_aq, float *d_as, int32_t *d_asum, float *d_as_tok) {
+    if (launch_quant_cluster<2>(ClusterSrc{d_gate, d_up, nullptr, d_out, 0.0f}, K, T, d_aq, d_as, d_asum,
+                                d_as_tok, kNoSync))
+        return;
+    launch_silu_mul(d_out, d_gate, d_up, K * T);
+    launch_quant_chunk_pertoken(d_out, K, T, d_aq, d_as, d_asum, d_as_tok, nullptr);
+}
+
 void launch_quant_chunk_pertoken(const float *d_x, int K, int T, int8_t *d_aq, float *d_as,
                                  int32_t *d_asum, float *d_as_tok, const SyncArgs *sync) {
     const SyncArgs sa = sync ? *sync : kNoSync;
     const size_t blocks = (size_t)(K / 32) * (size_t)T;
     if (!blocks) return;
+    if (launch_quant_cluster<0>(ClusterSrc{d_x, nullptr, nullptr, nullptr, 0.0f}, K, T, d_aq, d_as, d_asum,
+                                d_as_tok, sa))
+        return;
     if (T <= 32 && K <= 8192) {
         launch_pdl(quant_chunk_pertoken_regs_kernel, dim3(T), dim3(1024), 0, d_x, K, T, d_aq, d_as,
                    d_asum, d_as_tok, sa);

@@ -911,3 +911,54 @@ def test_gemm_cases_on_the_tcgen05_decode_kernel():
                           "-k", "test_gemm_int32_dots_and_fp32 or test_gemm_fanout_equals_per_weight"],
                          env=env, capture_output=True, text=True, timeout=1200)
     assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-2000:]
+
+
+# ---- decode-batch fusions: the two calls' bits in one launch ---------------------------------
+# (5120, 8): clusters of 8 CTAs per token; (1280, 16): clusters of 8 over short slices;
+# (96, 8): no K32-aligned split into 2, 4 or 8 - the two separate launches
+@pytest.mark.gpu
+@pytest.mark.parametrize("H,T", [(5120, 8), (1280, 16), (17408, 8), (96, 8), (5120, 40)])
+def test_rmsnorm_quant_chunk_pertoken(lib, pkg, orc, H, T):
+    rng = np.random.default_rng(H + T)
+    x = (rng.standard_normal((T, H)) * 3).astype(np.float32)
+    x[0, :] = 0.0                                           # a zero row: scale 1, codes 0
+    w = ((rng.standard_normal(H) * 0.1).astype(np.float32).view(np.uint32) >> 16).astype(np.uint16)
+    dx, dw, out = dev(pkg, x), dev(pkg, w), pkg.DevBuf(T * H * 4)
+    n = H // 32 * T
+    aq, as_, asum, at = pkg.DevBuf(n * 32), pkg.DevBuf(n * 4), pkg.DevBuf(n * 4), pkg.DevBuf(T * 4)
+    for b in (out, aq, as_, asum, at):
+        b.fill(0xA5)
+    lib.qwn_x_rmsnorm_quant_chunk_pertoken(out.ptr, dx.ptr, dw.ptr, H, T, 1e-6, aq.ptr, as_.ptr, asum.ptr,
+                                           at.ptr, 0)
+    lib.tq_sync()
+    xn = orc.rmsnorm_chunk(x, w, 1e-6)
+    oq, os_, osm = orc.quantize_act_chunk(xn, per_token=True)
+    assert out.to_numpy(np.float32).tobytes() == xn.tobytes()
+    assert np.array_equal(aq.to_numpy(np.int8), oq)
+    assert as_.to_numpy(np.float32).tobytes() == os_.tobytes()
+    assert np.array_equal(asum.to_numpy(np.int32), osm)
+    assert at.to_numpy(np.float32).tobytes() == os_.reshape(H // 32, T)[0].tobytes()
+    assert lib.tq_last_error() == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("K,T", [(17408, 8), (8704, 8), (160, 8), (5120, 40)])
+def test_silu_mul_quant_chunk_pertoken(lib, pkg, orc, K, T):
+    rng = np.random.default_rng(K + T)
+    g = (rng.standard_normal((T, K)) * 2).astype(np.float32)
+    u = rng.standard_normal((T, K)).astype(np.float32)
+    dg, du, out = dev(pkg, g), dev(pkg, u), pkg.DevBuf(T * K * 4)
+    n = K // 32 * T
+    aq, as_, asum, at = pkg.DevBuf(n * 32), pkg.DevBuf(n * 4), pkg.DevBuf(n * 4), pkg.DevBuf(T * 4)
+    for b in (out, aq, as_, asum, at):
+        b.fill(0xA5)
+    lib.qwn_x_silu_mul_quant_chunk_pertoken(out.ptr, dg.ptr, du.ptr, K, T, aq.ptr, as_.ptr, asum.ptr, at.ptr)
+    lib.tq_sync()
+    h = orc.silu_mul(g, u).reshape(T, K)
+    oq, os_, osm = orc.quantize_act_chunk(h, per_token=True)
+    assert out.to_numpy(np.float32).tobytes() == h.tobytes()
+    assert np.array_equal(aq.to_numpy(np.int8), oq)
+    assert as_.to_numpy(np.float32).tobytes() == os_.tobytes()
+    assert np.array_equal(asum.to_numpy(np.int32), osm)
+    assert at.to_numpy(np.float32).tobytes() == os_.reshape(K // 32, T)[0].tobytes()
+    assert lib.tq_last_error() == 0
