@@ -48,7 +48,11 @@ WORKLOAD_CFG5 = ("cfg5: 64-layer projection stack at decode T=8 (5120->10240, 10
 H, I_FF, QKV = 5120, 17408, 10240          # hidden, MLP width, first projection's width
 # DRAM traffic of one launch of the headline kernel, from the profiler capture named here;
 # None when the kernel has changed since the capture.
-NCU_TRAFFIC = {"bytes_per_launch": None, "capture": None}
+NCU_TRAFFIC = {"bytes_per_launch": 98344448,
+               "capture": "profiles/gemm_w4a8_ring_kernel__cfg2.md: ncu --set full --clock-control none "
+                          "-k regex:gemm_w4a8_ring -s 3 -c 2 python bench.py --case cfg2 --launches 6 "
+                          "(dram__bytes_read.sum 94,822,144 + dram__bytes_write.sum 3,522,304, one launch of "
+                          "the full-size cfg2 workload)"}
 NOMINAL_INT8_TOPS = 4500.0
 
 

@@ -52,6 +52,120 @@ class Comm:
         self.dist.barrier()          # every rank has cleared its flags before anyone publishes
 
 
+class WeakCfg2:
+    """Weak scaling of the headline projection: every rank multiplies its own cfg2 weights
+    (2 x 17408 x 5120, K64 - columns [rank * 34816, (rank + 1) * 34816) of a global
+    [8][world * 34816] output); the GEMM epilogue stores its columns into every rank's copy of
+    that matrix, and an exchange point closes the step. Per-GPU work is fixed, so the ideal
+    time per step is the single-GPU time."""
+
+    def __init__(self, ctx, comm, rank, world):
+        self.ctx, self.rank, self.world = ctx, rank, world
+        pkg, lib = ctx.pkg, ctx.lib
+        self.T, self.N2 = 8, 2 * B.I_FF
+        self.gate = ctx.rotated(B.I_FF, B.H, 11 + 2 * rank, 64)
+        self.up = ctx.rotated(B.I_FF, B.H, 12 + 2 * rank, 64)
+        self.x = pkg.DevBuf.from_numpy(ctx.wl.activations_normal(self.T, B.H, seed=5, outlier_frac=0.01))
+        nb = B.H // 32 * self.T
+        self.aq, self.as_, self.asum, self.as_tok = (pkg.DevBuf(nb * 32), pkg.DevBuf(nb * 4), pkg.DevBuf(nb * 4),
+                                                     pkg.DevBuf(self.T * 4))
+        self.out = pkg.DevBuf(self.T * world * self.N2 * 4)
+        comm.register([self.out])
+        self.weight_bytes = 2 * ctx.wl.weight_bytes(B.I_FF, B.H, 64)
+        self.steps_per_pass = len(self.gate)
+        # staging (with the exchange point) and GEMM per step; exchange point + advance per pass
+        self.launches_per_pass = 2 * self.steps_per_pass + 2
+        self.graph = None
+
+    def _step(self, c, first):
+        """Staging + GEMM on weight copy c. The staging kernel carries the exchange point that
+        orders the previous step's peer stores (as the consumer of a gathered matrix does in a
+        model), so no launch is spent on the exchange itself."""
+        lib, pkg, T = self.ctx.lib, self.ctx.pkg, self.T
+        f = lib.qwn_x_quantize_act_chunk_pertoken if first else lib.qwn_x_quantize_act_chunk_pertoken_sync
+        f(self.x.ptr, B.H, T, self.aq.ptr, self.as_.ptr, self.asum.ptr, self.as_tok.ptr)
+        warr = (C.POINTER(pkg.TqWeight) * 2)(C.pointer(self.gate[c].rec), C.pointer(self.up[c].rec))
+        fr = (C.c_int * 2)(B.I_FF, B.I_FF)
+        co = (C.c_size_t * 2)(self.rank * self.N2, self.rank * self.N2 + B.I_FF)
+        rc = lib.qwn_x_gemm_w4a8_fanout_tp(warr, 2, self.aq.ptr, None, self.as_tok.ptr, self.asum.ptr, T, fr,
+                                           None, 0, co, self.world * self.N2)
+        assert rc == 0, rc
+
+    def _issue_pass(self):
+        """One pass = one step per weight copy, then the exchange point of the last step and the
+        step-base advance that makes the pass replayable."""
+        lib = self.ctx.lib
+        for c in range(len(self.gate)):
+            self._step(c, c == 0)
+        assert lib.tq_comm_exchange_sync() == 0
+        assert lib.tq_comm_exchange_advance() == 0
+
+    def capture(self):
+        lib = self.ctx.lib
+        self._issue_pass()
+        lib.tq_sync()
+        assert lib.tq_graph_capture_begin() == 0
+        self._issue_pass()
+        self.graph = lib.tq_graph_capture_end()
+        assert self.graph, "graph capture failed"
+
+    def run_pass(self):
+        if self.graph:
+            self.ctx.lib.tq_graph_launch(self.graph)
+        else:
+            self._issue_pass()
+
+
+def run_weak(args, ctx, dist, rank, world, barrier, max_over_ranks):
+    """The weak cfg2 record of the multi-GPU line."""
+    lib = ctx.lib
+    single_us = None
+    if rank == 0:
+        head, _, _ = B.build_cases(ctx, {"cfg2"})["cfg2"]
+        single_us = ctx.time_loop(lambda i: head.run(i, 0, 0), 200, warmup=20) * 1e3
+        del head
+    dist.barrier()
+    comm = Comm(ctx, dist, rank, world)
+    wk = WeakCfg2(ctx, comm, rank, world)
+    barrier()
+    wk.run_pass()
+    barrier()
+    full = wk.out.to_numpy(np.uint32)
+    sums = [None] * world
+    dist.all_gather_object(sums, (int(full.astype(np.uint64).sum()), int(np.bitwise_xor.reduce(full))))
+    differ = sum(1 for v in sums if v != sums[0])
+    wk.capture()
+    barrier()
+    for i in range(5):
+        wk.run_pass()
+    barrier()
+    ev, passes = ctx.events(), 50
+    t0 = time.time()
+    lib.tq_event_record(ev[0])
+    for i in range(passes):
+        wk.run_pass()
+    lib.tq_event_record(ev[1])
+    barrier()
+    ctx.load_spans.append((t0, time.time()))
+    steps = passes * wk.steps_per_pass
+    us = max_over_ranks(lib.tq_event_elapsed_ms(ev[0], ev[1])) / steps * 1e3
+    err = lib.tq_last_error()
+    rec = {"workload": B.WORKLOAD_CFG2, "scaling": "weak",
+           "us_per_step": us, "single_gpu_us_per_step": single_us,
+           "value": world * wk.weight_bytes / (us * 1e-6) / 1e9, "unit": B.UNIT,
+           "per_gpu_weight_bytes": int(wk.weight_bytes), "launches_per_pass": wk.launches_per_pass,
+           "steps_per_pass": wk.steps_per_pass,
+           "ranks_with_a_different_result": differ, "steps": steps, "device_error": err,
+           "step": "per-token staging (its prologue is the exchange point behind the previous step's peer "
+                   "stores), fused gate|up GEMM storing its columns into every rank's [8][N x 34816] matrix; "
+                   "a pass of one step per weight copy is one CUDA graph"}
+    barrier()
+    del wk
+    lib.tq_comm_destroy()
+    dist.barrier()
+    return rec
+
+
 def run(args, rank, local_rank, world):
     import torch
     import torch.distributed as dist
@@ -69,6 +183,9 @@ def run(args, rank, local_rank, world):
         t = torch.tensor([v], dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
+
+    # ---- weak scaling of the headline projection (a record inside the line) --------------------
+    weak = run_weak(args, ctx, dist, rank, world, barrier, max_over_ranks)
 
     # ---- the unsharded stack on rank 0: result to match, time to scale from ------------------
     tp1 = {"ms": None, "out": None}
@@ -170,6 +287,7 @@ def run(args, rank, local_rank, world):
             "e2e": {"value": wb / e_s / 1e9, "unit": B.UNIT, "h2d_bytes_per_step": int(st.x_host.nbytes),
                     "d2h_bytes_per_step": int(st.out_bytes), "steps": e_iters, "us_per_step": e_s * 1e6,
                     "last_result_words_differing": e_diff},
+            "weak_cfg2": weak,
             "gpu_launches": st.launches_per_step * args.steps,
             "clocks": clocks, "cpu_baseline": None, "device_error": max(errs),
         }
