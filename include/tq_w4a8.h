@@ -314,6 +314,15 @@ int qwn_w4_check(tq_qmma_weight_t *w, int mode, double *cos_out, double *max_rel
  * 997-1058 (TQ_XPU_W4A8, TQ_XPU_W8, TQ_XPU_W4_K16, TQ_XPU_K64): tier -1 keep E2M3, 8 int8, 1 / 2 /
  * 0 int4 with K16 / K64 / K32 scales; qwn_repack_by_policy returns the applied tier or
  * -100 + rc of the failed repack call. */
+/* Weight-format probe (xpu/src/kernels_dpas.cpp:1726-2146, there bound to a model layer): how
+ * well eleven candidate low-bit formats reconstruct the E2M3 source of `w` (a record that has
+ * not been repacked; nothing is modified). Prints the reference's table; cos_out / rel_out /
+ * bits_out, when not NULL, receive eleven values each (cosine, relative L2 error, bits per
+ * weight incl. metadata; scheme 9's bits are measured). Returns 0 when the shipped tier
+ * (scheme 1: int4 asymmetric, fp16 scale per K32) has the best cosine among the schemes at or
+ * below its 4.5 bits, 1 when another one beats it, -1 / -2 / -3 for a bad, an already
+ * repacked or a non-E2M3 record. An offline qualification tool. */
+int qwn_w4_grid_probe(const tq_qmma_weight_t *w, double *cos_out, double *rel_out, double *bits_out);
 int qwn_tqf_read_qmma(const void *bytes, size_t nbytes, int M, int K, uint32_t flags, tq_qmma_weight_t *w,
                       size_t *consumed);
 void qwn_tqf_free_qmma(tq_qmma_weight_t *w);

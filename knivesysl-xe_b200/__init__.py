@@ -123,6 +123,7 @@ SIGNATURES = {
     "qwn_x_quantize_act_chunk_sync": (None, [_vp, _i, _i, _vp, _vp, _vp]),
     "qwn_x_quantize_act_chunk_pertoken_sync": (None, [_vp, _i, _i, _vp, _vp, _vp, _vp]),
     "qwn_x_rmsnorm_chunk_sync": (None, [_vp, _vp, _vp, _i, _i, C.c_float]),
+    "qwn_w4_grid_probe": (_i, [_vp, _vp, _vp, _vp]),
     "qwn_x_rmsnorm_quant_chunk_pertoken": (None, [_vp, _vp, _vp, _i, _i, C.c_float, _vp, _vp, _vp, _vp, _i]),
     "qwn_x_silu_mul_quant_chunk_pertoken": (None, [_vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _vp]),
     "qwn_x_silu_mul_scatter": (_i, [_vp, _vp, _i, _i, _i, _sz, _sz]),

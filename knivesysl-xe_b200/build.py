@@ -13,7 +13,7 @@ ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libforward_qwen_xpu.so")
 
-SOURCES = ["runtime.cu", "quant.cu", "repack.cu", "gemv.cu", "gemv_e2m3.cu", "tqf.cu", "gemm_mma.cu", "gemm_stream.cu", "gemm_tc.cu", "gemm_dtc.cu", "tc_peak.cu",
+SOURCES = ["runtime.cu", "quant.cu", "repack.cu", "gemv.cu", "gemv_e2m3.cu", "tqf.cu", "grid_probe.cu", "gemm_mma.cu", "gemm_stream.cu", "gemm_tc.cu", "gemm_dtc.cu", "tc_peak.cu",
            "dispatch.cu", "checks.cu", "comm.cu", "gemv_static.cu", "w8a8.cu", "cxx_linkage.cpp"]
 
 NVCC_FLAGS = [

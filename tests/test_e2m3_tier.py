@@ -147,3 +147,63 @@ def test_repack_by_policy_and_shard_check_all(lib, pkg, orc):
     for w in ws:
         lib.qwn_tqf_free_qmma(C.byref(w))
     assert lib.tq_last_error() == 0
+
+
+def _gaussian_record(orc, M, K, seed):
+    """A record whose decoded weights look like a trained matrix: N(0, 1) values snapped to the
+    nearest E2M3 code under one block scale per (128 rows, 128 columns)."""
+    rng = np.random.default_rng(seed)
+    rows, cols = (M + 127) // 128, (K + 127) // 128
+    bs = (rng.random((rows, cols)) * 0.004 + 0.004).astype(np.float32)
+    grid = np.array([orc.e2m3f(c) for c in range(64)], dtype=np.float32)
+    target = rng.standard_normal((M, K)).astype(np.float32) * 2.0          # in units of the block scale
+    codes6 = np.abs(target[..., None] - grid[None, None, :]).argmin(axis=-1).astype(np.uint8)
+    payload = orc.e2m3_payload_from_codes_fast(codes6)
+    blob = struct.pack("<II", rows, cols) + bs.tobytes() + payload.tobytes()
+    return blob, payload, bs, cols
+
+
+def test_grid_probe_oracle_orders_the_formats(orc):
+    """CPU only: on a Gaussian-like matrix more bits reconstruct better, the K16 fit beats the
+    K32 fit beats the K64 fit, and asymmetric int4 beats symmetric int4 at the same budget."""
+    M, K = 128, 512
+    blob, payload, bs, cols = _gaussian_record(orc, M, K, seed=3)
+    W = orc.e2m3_decode(payload, bs, cols, M, K)
+    cos, rel, bits, verdict = orc.w4_grid_probe(W)
+    assert cos[4] > cos[2] > cos[1] > cos[10] and cos[1] > cos[0] and cos[1] > cos[8] and cos[0] > cos[7]
+    assert 3.5 <= bits[9] <= 4.5 and cos[8] <= cos[9] <= cos[1] + 1e-12
+    assert np.all(rel > 0) and np.all(cos > 0.9) and verdict in (0, 1)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,K,gauss", [(256, 512, True), (144, 1024, False)])
+def test_grid_probe_matches_oracle(lib, pkg, orc, M, K, gauss):
+    """Floating-point report: cosine and relative error per format agree with the CPU
+    restatement to 2e-5 and 5e-4 (the device sums each row in fp32, the oracle in double); bits per
+    weight of the mixed format to 0.01; the verdict whenever the oracle's margin exceeds
+    that tolerance."""
+    blob, payload, bs, cols = (_gaussian_record if gauss else make_record)(orc, M, K, 5)
+    w = pkg.TqWeight()
+    buf = np.frombuffer(blob, dtype=np.uint8)
+    assert lib.qwn_tqf_read_qmma(buf.ctypes.data, buf.size, M, K, FLAGS, C.byref(w), None) == 0
+    cos, rel, bits = (C.c_double * 11)(), (C.c_double * 11)(), (C.c_double * 11)()
+    rc = lib.qwn_w4_grid_probe(C.byref(w), cos, rel, bits)
+    assert rc in (0, 1) and lib.tq_last_error() == 0
+    W = orc.e2m3_decode(payload, bs, cols, M, K)
+    ocos, orel, obits, overdict = orc.w4_grid_probe(W)
+    assert np.abs(np.array(cos[:]) - ocos).max() <= 2e-5, (list(cos), ocos)
+    # |w - w_hat|^2 comes out of fp32 row sums as na - 2 dot + nb: for the int8 format it is 3e-5 of
+    # na, so the row sums' rounding shows in the fourth digit of its relative error
+    assert np.abs(np.array(rel[:]) - orel).max() <= 5e-4, (list(rel), orel)
+    assert np.abs(np.array(bits[:]) - obits).max() <= 0.01
+    rivals = [k for k in range(11) if k != 1 and obits[k] <= obits[1] + 1e-9]
+    if min(abs(ocos[1] - ocos[k]) for k in rivals) > 1e-4:
+        assert rc == overdict
+    assert w.d_A and not w.s4_ready                                   # a pure read
+    # validation
+    w.row_major = 1
+    assert lib.qwn_w4_grid_probe(C.byref(w), None, None, None) == -3
+    w.row_major = 0
+    assert lib.qwn_x_w4_repack_weight_mode(C.byref(w), 0) == 0
+    assert lib.qwn_w4_grid_probe(C.byref(w), None, None, None) == -2   # the source is gone
+    lib.qwn_tqf_free_qmma(C.byref(w))
