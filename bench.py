@@ -18,7 +18,9 @@ and a bounded CPU sample; `prefill_int8_TOPS` is the packed prefill GEMM's throu
 `int8_peak` the tcgen05 kind::i8 issue peak measured in the same run.
 
 N > 1 (torchrun, one rank per GPU): the 64-layer stack, every projection column-sharded N ways
-with x_w4_shard, strong scaling (the same 13.4 GB of weights per step at every N).
+with x_w4_shard, strong scaling (the same 13.4 GB of weights per step at every N); the line
+also carries `weak_cfg2`, the headline projection with per-GPU work fixed. `--scaling weak`
+prints that record as the line instead (whole-job weight bytes per second over N GPUs).
 """
 from __future__ import annotations
 
@@ -1013,7 +1015,6 @@ def main():
     ap.add_argument("--launches", type=int, default=3)
     ap.add_argument("--layers", type=int, default=None, help="layers of the cfg5 stack (default 64)")
     ap.add_argument("--scaling", default="strong", choices=["weak", "strong"])
-    ap.add_argument("--exchange", default="fused", choices=["fused", "nccl"])
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank, local_rank, world = dist_env()

@@ -186,6 +186,27 @@ def run(args, rank, local_rank, world):
 
     # ---- weak scaling of the headline projection (a record inside the line) --------------------
     weak = run_weak(args, ctx, dist, rank, world, barrier, max_over_ranks)
+    if args.scaling == "weak":
+        # the weak record as the line: cfg2 on every rank, whole-job weight bytes per second
+        clocks = sampler.stop(ctx.load_spans) if sampler else None
+        if rank == 0:
+            print(json.dumps({
+                "metric": B.METRIC, "value": weak["value"], "unit": B.UNIT, "n_gpus": world,
+                "steps": weak["steps"], "warmup": 5 * weak["steps_per_pass"], "ms_per_step": weak["us_per_step"] / 1e3,
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                "dtype": "s8xs4->s32, fp32 out", "data": "synthetic",
+                "config": {"workload": B.WORKLOAD_CFG2, "parallelism": f"one cfg2-sized column shard per GPU ({world} "
+                           "GPUs), outputs stored into every rank's matrix by the GEMM epilogue",
+                           "l2": "inputs larger than L2: rotating weight copies", "step": weak["step"]},
+                "single_gpu_us_per_step": weak["single_gpu_us_per_step"],
+                "ranks_with_a_different_result": weak["ranks_with_a_different_result"],
+                "roofline": {"bound": "hbm", "achieved": weak["value"] / world, "peak": ctx.peak_hbm, "unit": "GB/s",
+                             "frac": weak["value"] / world / ctx.peak_hbm, "peak_source": f"{ctx.peak_kind} copy bandwidth",
+                             "kernel": "whole step, per GPU", "traffic": None},
+                "e2e": None, "gpu_launches": weak["launches_per_pass"] * weak["steps"] // weak["steps_per_pass"],
+                "clocks": clocks, "cpu_baseline": None, "device_error": weak["device_error"]}), flush=True)
+        dist.destroy_process_group()
+        return
 
     # ---- the unsharded stack on rank 0: result to match, time to scale from ------------------
     tp1 = {"ms": None, "out": None}
