@@ -300,7 +300,7 @@ class DecodeGemm:
         from oracle import oracle as orc
         ksh = int(self.group == 64)
         if self.mode == "pertoken":
-            S = self.ctx.lib.qwn_choose_gemm_splits(self.M // 16, self.T // 8, self.K // 32)
+            S = self.ctx.lib.qwn_choose_pertoken_splits(self.M // 16, self.T // 8, self.K // 32, ksh)
             at = os_.reshape(self.K // 32, self.T)[0].copy()
             return orc.gemm_w4a8_pertoken(codes, scales, rows, self.K, ksh, oq, at, osm, self.T, splits=S)[1]
         if rows != self.M:
@@ -679,7 +679,7 @@ class Stack:
             for (M, K, _), (codes, scales) in zip(self.shapes, ws):
                 orc.quantize_act_chunk(xs[K], per_token=True)
                 oq, os_, osm = qs[K]
-                S = orc.choose_gemm_splits(M // 16, T // 8, K // 32)
+                S = orc.choose_pertoken_splits(M // 16, T // 8, K // 32, 0)
                 orc.gemm_w4a8_pertoken(codes, scales, M, K, 0, oq, os_.reshape(K // 32, T)[0].copy(), osm, T,
                                        splits=S)
         return fn
@@ -781,12 +781,10 @@ def build_cases(ctx, which):
                 g = rng.standard_normal((T, I_FF))
                 u = rng.standard_normal((T, I_FF))
                 return (g / (1.0 + np.exp(-g)) * u).astype(np.float32)
-            # 8 tokens: per-token scales on the ring kernel; 16..64 tokens: the reference's
-            # arithmetic (scale per (token, K32)) on the mma.sync kernels, the faster path there
-            mode = "pertoken" if T == 8 else "exact"
-            c = DecodeGemm(ctx, n, H, 1, I_FF, 32, T, mode, 23, xg)
+            # per-token scales on the ring kernel, a warp carrying all of the call's tokens
+            c = DecodeGemm(ctx, n, H, 1, I_FF, 32, T, "pertoken", 23, xg)
             c._seed0 = 23
-            out[n] = (c, "gemm_w4a8_ring_kernel" if T <= 32 else "gemm_w4a8_stream_kernel", "hbm")
+            out[n] = (c, "gemm_w4a8_ring_kernel", "hbm")
     shared = None
     for mode in Prefill.MODES:
         n = f"cfg4_{mode}"

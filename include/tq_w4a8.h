@@ -212,6 +212,11 @@ void qwn_x_w4_shard_free(tq_qmma_weight_t *w);
  * callers and tests can see the order a result was summed in. */
 int qwn_choose_gemv_splits(int groups);
 int qwn_choose_gemm_splits(int rgroups, int tgroups, int ktiles);
+/* Split count of the per-token decode GEMMs (x_gemm_w4a8_fanout_pertoken, x_gemm_w4a8_fanout_tp with
+ * d_as_tok; own rule): as many splits as an 8-token call of the same weight, doubled while one
+ * split's staged activations (320 bytes per k-tile and 8 tokens) exceed 88 KB; splits cut whole
+ * weight-scale groups (ksh = 1: K64). */
+int qwn_choose_pertoken_splits(int rgroups, int tgroups, int ktiles, int ksh);
 
 /* ---- additions without a counterpart in the reference ----------------------- */
 

@@ -80,6 +80,7 @@ void launch_gather_publish(int step);
 // ---- split heuristics (dispatch.cu) --------------------------------------------
 int choose_gemv_splits(int groups);
 int choose_gemm_splits(int rgroups, int tgroups, int ktiles);
+int choose_pertoken_splits(int rgroups, int tgroups, int ktiles, int ksh);
 
 // ---- kernel launchers -----------------------------------------------------------
 // quant.cu

@@ -42,6 +42,22 @@ int choose_gemm_splits(int rgroups, int tgroups, int ktiles) {
     return s;
 }
 
+// Split count of the per-token decode GEMMs (own rule; the reference has no per-token mode).
+// A warp of the decode kernel carries all tokens of a call, so the task count does not grow
+// with the tokens: as many splits as an 8-token call of the same weight, doubled while the
+// staged activations of one split (320 bytes per k-tile and 8 tokens) exceed 88 KB, so that
+// they fit beside the weight rings in shared memory. Splits cut whole weight-scale groups.
+int choose_pertoken_splits(int rgroups, int tgroups, int ktiles, int ksh) {
+    const int kgroups = ktiles >> ksh;
+    int s = choose_gemm_splits(rgroups, 1, kgroups);
+    if (forced_gemm_splits()) return s;
+    int cap = 1;
+    while (cap < 16 && cap * 2 <= kgroups) cap *= 2;
+    const long budget = 88 * 1024;
+    while (s < cap && (long)(((kgroups + s - 1) / s) << ksh) * tgroups * 320 > budget) s *= 2;
+    return s;
+}
+
 bool decode_prefers_mma() {
     static const int v = [] {
         const char *e = getenv("TQ_XPU_DECODE_MMA");
@@ -451,6 +467,18 @@ int fanout_args(GemmArgs &a, const tq_qmma_weight_t *const *ws, int count, int T
     return 0;
 }
 
+// Per-token calls use their own split rule (one segment, the same count for every weight).
+// full_rows: row counts of the whole projections when the weights are column shards.
+void apply_pertoken_splits(GemmArgs &a, const int *full_rows = nullptr) {
+    int s = 1;
+    for (int i = 0; i < a.count; ++i) {
+        const int rows = (full_rows && full_rows[i] > 0) ? full_rows[i] : a.M[i];
+        s = std::max(s, choose_pertoken_splits(rows / 16, a.T / 8, a.K / 32, a.ksh));
+    }
+    a.max_splits = s;
+    for (int i = 0; i < a.count; ++i) a.seg[i].split[0] = s;
+}
+
 // Sets the activation source of a prepared GemmArgs: the caller's staging, or x fused / staged.
 void set_fused_input(GemmArgs &a, const float *d_x, int per_token) {
     a.x = d_x;
@@ -579,6 +607,7 @@ int x_gemm_w4a8_fanout_pertoken(const tq_qmma_weight_t *const *ws, float *const 
     a.as_tok = d_as_tok;
     a.mode = 1;
     if (a.T > 64) return -3;
+    apply_pertoken_splits(a);
     return launch_gemm(a) ? 0 : -3;
 }
 
@@ -604,6 +633,7 @@ int x_gemm_w4a8_fanout_tp(const tq_qmma_weight_t *const *ws, int count, const in
     if (d_as_tok) {
         a.as_tok = d_as_tok;
         a.mode = 1;
+        apply_pertoken_splits(a, full_rows);
     }
     if (slot < 0) {
         if (!ys) return -2;
@@ -943,6 +973,9 @@ int qwn_x_w4_shard(tq_qmma_weight_t *dst, const tq_qmma_weight_t *src, int rank,
 }
 void qwn_x_w4_shard_free(tq_qmma_weight_t *w) { x_w4_shard_free(w); }
 int qwn_choose_gemv_splits(int groups) { return tq::choose_gemv_splits(groups); }
+int qwn_choose_pertoken_splits(int rgroups, int tgroups, int ktiles, int ksh) {
+    return tq::choose_pertoken_splits(rgroups, tgroups, ktiles, ksh);
+}
 int qwn_choose_gemm_splits(int rgroups, int tgroups, int ktiles) {
     return tq::choose_gemm_splits(rgroups, tgroups, ktiles);
 }

@@ -463,7 +463,10 @@ __device__ unsigned long long g_ring_trace[1024 * 8];
 #define RING_STAMP(i)
 #define RING_STAMP_END()
 #endif
-template <bool PAIR, int kRNS, int MAXW, bool PT>
+// NTG: 8-token groups a warp carries per tile (1, 2, 4 or 8): the tile's A fragments, scale
+// words and ring traffic are paid once for all of them; the staged activations of group g
+// follow those of group g - 1 (`gstride` bytes apart).
+template <bool PAIR, int kRNS, int MAXW, bool PT, int NTG = 1>
 __global__ void __launch_bounds__(MAXW * 32, 1)
 gemm_w4a8_ring_kernel(const GemmArgs a, float *__restrict__ part, int *__restrict__ count) {
     extern __shared__ __align__(128) unsigned char smem[];
@@ -485,8 +488,8 @@ gemm_w4a8_ring_kernel(const GemmArgs a, float *__restrict__ part, int *__restric
     const int Ktg = Kt >> ksh;
     const int kt_begin = PT ? ((Ktg * split / S) << ksh) : Kt * split / S;
     const int cnt = (PT ? ((Ktg * (split + 1) / S) << ksh) : Kt * (split + 1) / S) - kt_begin;
-    // token window of this CTA column: tokens [tok0, tok0 + 8) of the call's Ttot
-    const int win = blockIdx.y, tok0 = win * 8, Ttot = a.T;
+    // token window of this CTA column: tokens [tok0, tok0 + 8 NTG) of the call's Ttot
+    const int win = blockIdx.y, tok0 = win * 8 * NTG, Ttot = a.T;
 
     // 64 bytes in front of the rings: the row maxima of the fused per-token quantiser
     int *s_rowmax = reinterpret_cast<int *>(smem);
@@ -494,7 +497,8 @@ gemm_w4a8_ring_kernel(const GemmArgs a, float *__restrict__ part, int *__restric
     const uint32_t ring_s = smem_u32(ring);
     unsigned char *act = smem + kRHead + (size_t)nw * kRNS * kRStage;
     const uint32_t act_s = smem_u32(act);
-    float *xpose = reinterpret_cast<float *>(act + (size_t)cnt * kActTileBytes) + warp * 128;
+    const uint32_t gstride = (uint32_t)cnt * kActTileBytes;          // one token group's staged bytes
+    float *xpose = reinterpret_cast<float *>(act + (size_t)NTG * gstride) + warp * 128;
     const uint64_t pol = l2_policy_evict_first();
 
     // ---- producer: next (row-group, tile offset) to fetch --------------------------------
@@ -623,41 +627,46 @@ gemm_w4a8_ring_kernel(const GemmArgs a, float *__restrict__ part, int *__restric
         // chain of L2 latencies, and a loop of load-then-store pays one per iteration.
         const int items = cnt * 32, nthr = nw * 32;
         constexpr int kSU = 4;
-        for (int i0 = threadIdx.x; i0 < items; i0 += nthr * kSU) {
-            uint2 bb[kSU];
+#pragma unroll 1
+        for (int g = 0; g < NTG; ++g) {
+            unsigned char *actg = act + (size_t)g * gstride;
+            const int tokg = tok0 + 8 * g;
+            for (int i0 = threadIdx.x; i0 < items; i0 += nthr * kSU) {
+                uint2 bb[kSU];
 #pragma unroll
-            for (int u = 0; u < kSU; ++u) {
-                const int i = i0 + u * nthr;
-                if (i < items)
-                    bb[u] = __ldg(reinterpret_cast<const uint2 *>(
-                        a.aq + ((size_t)(kt_begin + (i >> 5)) * Ttot + tok0) * 32 + (size_t)(i & 31) * 8));
-            }
+                for (int u = 0; u < kSU; ++u) {
+                    const int i = i0 + u * nthr;
+                    if (i < items)
+                        bb[u] = __ldg(reinterpret_cast<const uint2 *>(
+                            a.aq + ((size_t)(kt_begin + (i >> 5)) * Ttot + tokg) * 32 + (size_t)(i & 31) * 8));
+                }
 #pragma unroll
-            for (int u = 0; u < kSU; ++u) {
-                const int i = i0 + u * nthr;
-                if (i < items) {
-                    uint2 o;
-                    o.x = __byte_perm(bb[u].x, bb[u].y, 0x6420);
-                    o.y = __byte_perm(bb[u].x, bb[u].y, 0x7531);
-                    *reinterpret_cast<uint2 *>(act + (size_t)(i >> 5) * kActTileBytes + (i & 31) * 8) = o;
+                for (int u = 0; u < kSU; ++u) {
+                    const int i = i0 + u * nthr;
+                    if (i < items) {
+                        uint2 o;
+                        o.x = __byte_perm(bb[u].x, bb[u].y, 0x6420);
+                        o.y = __byte_perm(bb[u].x, bb[u].y, 0x7531);
+                        *reinterpret_cast<uint2 *>(actg + (size_t)(i >> 5) * kActTileBytes + (i & 31) * 8) = o;
+                    }
                 }
             }
-        }
-        const int pairs = cnt * 4;
-        for (int i = threadIdx.x; i < pairs; i += nthr) {
-            const int kl = i >> 2;
-            const int rem = i & 3;
-            const size_t src = (size_t)(kt_begin + kl) * Ttot + tok0 + (size_t)rem * 2;
-            float2 as2 = make_float2(0.f, 0.f);
-            if (!PT) as2 = __ldg(reinterpret_cast<const float2 *>(a.as + src));
-            int2 sm2 = __ldg(reinterpret_cast<const int2 *>(a.asum + src));
-            if (PT && PAIR && !(kl & 1) && kl + 1 < cnt) {      // the K64 group's sum, with its first tile
-                const int2 nx = __ldg(reinterpret_cast<const int2 *>(a.asum + src + Ttot));
-                sm2.x += nx.x;
-                sm2.y += nx.y;
+            const int pairs = cnt * 4;
+            for (int i = threadIdx.x; i < pairs; i += nthr) {
+                const int kl = i >> 2;
+                const int rem = i & 3;
+                const size_t src = (size_t)(kt_begin + kl) * Ttot + tokg + (size_t)rem * 2;
+                float2 as2 = make_float2(0.f, 0.f);
+                if (!PT) as2 = __ldg(reinterpret_cast<const float2 *>(a.as + src));
+                int2 sm2 = __ldg(reinterpret_cast<const int2 *>(a.asum + src));
+                if (PT && PAIR && !(kl & 1) && kl + 1 < cnt) {      // the K64 group's sum, with its first tile
+                    const int2 nx = __ldg(reinterpret_cast<const int2 *>(a.asum + src + Ttot));
+                    sm2.x += nx.x;
+                    sm2.y += nx.y;
+                }
+                *reinterpret_cast<float4 *>(actg + (size_t)kl * kActTileBytes + 256 + rem * 16) =
+                    make_float4(as2.x, as2.y, -(float)sm2.x, -(float)sm2.y);
             }
-            *reinterpret_cast<float4 *>(act + (size_t)kl * kActTileBytes + 256 + rem * 16) =
-                make_float4(as2.x, as2.y, -(float)sm2.x, -(float)sm2.y);
         }
         __syncthreads();
     }
@@ -672,42 +681,52 @@ gemm_w4a8_ring_kernel(const GemmArgs a, float *__restrict__ part, int *__restric
     const uint32_t lane_b = act_s + lane * 8;
     const uint32_t lane_v = act_s + 256 + c * 16;
 
-    f32x2 acc01 = 0ull, acc23 = 0ull;
-    // one tile: A words of rows r, r+8; {ws, z+8} of those rows; activations at bb / vb
+    f32x2 acc01[NTG], acc23[NTG];
+    // one tile: A words of rows r, r+8; {ws, z+8} of those rows; activations at bb / vb (+ g * gstride)
     auto tile = [&](uint32_t w_lo, uint32_t w_hi, float ws0, float nz0, float ws1, float nz1,
                     uint32_t bb_addr, uint32_t vb_addr) {
         const uint32_t A0 = nib_plus8(w_lo), A1 = nib_plus8(w_hi);
         const uint32_t A2 = nib_plus8(w_lo >> 4), A3 = nib_plus8(w_hi >> 4);
-        const uint2 bb = lds_v2(bb_addr);
-        const ulonglong2 av = lds_v2u64(vb_addr);
-        int d[4];
-        mma_s8_c(d, A0, A1, A2, A3, bb.x, bb.y, cmagic);
-        // (float)(d - z*asum) = (z+8) * (-asum) + d', exact: all integers below 2^24
-        const f32x2 f01 = fma2(pack2(nz0, nz0), av.y, add2(pack2i(d[0], d[1]), neg_magic2));
-        const f32x2 f23 = fma2(pack2(nz1, nz1), av.y, add2(pack2i(d[2], d[3]), neg_magic2));
-        if (PT) {
-            fma2_acc(acc01, f01, pack2(ws0, ws0));
-            fma2_acc(acc23, f23, pack2(ws1, ws1));
-        } else {
-            fma2_acc(acc01, f01, mul2(pack2(ws0, ws0), av.x));
-            fma2_acc(acc23, f23, mul2(pack2(ws1, ws1), av.x));
+        const f32x2 nz0p = pack2(nz0, nz0), nz1p = pack2(nz1, nz1), ws0p = pack2(ws0, ws0), ws1p = pack2(ws1, ws1);
+#pragma unroll
+        for (int g = 0; g < NTG; ++g) {
+            const uint2 bb = lds_v2(bb_addr + g * gstride);
+            const ulonglong2 av = lds_v2u64(vb_addr + g * gstride);
+            int d[4];
+            mma_s8_c(d, A0, A1, A2, A3, bb.x, bb.y, cmagic);
+            // (float)(d - z*asum) = (z+8) * (-asum) + d', exact: all integers below 2^24
+            const f32x2 f01 = fma2(nz0p, av.y, add2(pack2i(d[0], d[1]), neg_magic2));
+            const f32x2 f23 = fma2(nz1p, av.y, add2(pack2i(d[2], d[3]), neg_magic2));
+            if (PT) {
+                fma2_acc(acc01[g], f01, ws0p);
+                fma2_acc(acc23[g], f23, ws1p);
+            } else {
+                fma2_acc(acc01[g], f01, mul2(ws0p, av.x));
+                fma2_acc(acc23[g], f23, mul2(ws1p, av.x));
+            }
         }
     };
     // both tiles of a K64 group against per-token scales: one int32 dot, one promote
     auto tile_group = [&](uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3, float ws0, float nz0, float ws1,
                           float nz1, uint32_t bb_addr, uint32_t vb_addr, bool second) {
-        const uint2 bb = lds_v2(bb_addr);
-        const ulonglong2 av = lds_v2u64(vb_addr);
-        int d[4];
-        mma_s8_c(d, nib_plus8(w0), nib_plus8(w1), nib_plus8(w0 >> 4), nib_plus8(w1 >> 4), bb.x, bb.y, cmagic);
-        if (second) {
-            const uint2 bb2 = lds_v2(bb_addr + kActTileBytes);
-            mma_s8_acc(d, nib_plus8(w2), nib_plus8(w3), nib_plus8(w2 >> 4), nib_plus8(w3 >> 4), bb2.x, bb2.y);
+        const uint32_t A0 = nib_plus8(w0), A1 = nib_plus8(w1), A2 = nib_plus8(w0 >> 4), A3 = nib_plus8(w1 >> 4);
+        const uint32_t B0 = nib_plus8(w2), B1 = nib_plus8(w3), B2 = nib_plus8(w2 >> 4), B3 = nib_plus8(w3 >> 4);
+        const f32x2 nz0p = pack2(nz0, nz0), nz1p = pack2(nz1, nz1), ws0p = pack2(ws0, ws0), ws1p = pack2(ws1, ws1);
+#pragma unroll
+        for (int g = 0; g < NTG; ++g) {
+            const uint2 bb = lds_v2(bb_addr + g * gstride);
+            const ulonglong2 av = lds_v2u64(vb_addr + g * gstride);
+            int d[4];
+            mma_s8_c(d, A0, A1, A2, A3, bb.x, bb.y, cmagic);
+            if (second) {
+                const uint2 bb2 = lds_v2(bb_addr + g * gstride + kActTileBytes);
+                mma_s8_acc(d, B0, B1, B2, B3, bb2.x, bb2.y);
+            }
+            const f32x2 f01 = fma2(nz0p, av.y, add2(pack2i(d[0], d[1]), neg_magic2));
+            const f32x2 f23 = fma2(nz1p, av.y, add2(pack2i(d[2], d[3]), neg_magic2));
+            fma2_acc(acc01[g], f01, ws0p);
+            fma2_acc(acc23[g], f23, ws1p);
         }
-        const f32x2 f01 = fma2(pack2(nz0, nz0), av.y, add2(pack2i(d[0], d[1]), neg_magic2));
-        const f32x2 f23 = fma2(pack2(nz1, nz1), av.y, add2(pack2i(d[2], d[3]), neg_magic2));
-        fma2_acc(acc01, f01, pack2(ws0, ws0));
-        fma2_acc(acc23, f23, pack2(ws1, ws1));
     };
     // tiles 2j, 2j+1 of the stage at `cst`; activations of the first one at offset kl_off
     auto tile_pair = [&](uint32_t ab, uint32_t sb, uint32_t bbase, uint32_t vbase, bool second) {
@@ -735,7 +754,8 @@ gemm_w4a8_ring_kernel(const GemmArgs a, float *__restrict__ part, int *__restric
         while (wi + 1 < a.count && g0 >= a.goff[wi + 1]) ++wi;
         const int lg = g0 - a.goff[wi];
         const int M = a.M[wi];
-        acc01 = acc23 = 0ull;
+#pragma unroll
+        for (int g = 0; g < NTG; ++g) acc01[g] = acc23[g] = 0ull;
         uint32_t bbase = lane_b, vbase = lane_v;
         for (int left = cnt; left > 0; left -= kRST) {
             cp_async_wait<kRNS - 2>();
@@ -759,62 +779,85 @@ gemm_w4a8_ring_kernel(const GemmArgs a, float *__restrict__ part, int *__restric
             vbase += kRST * kActTileBytes;
             cst = (cst + kRStage == ring_s + kRNS * kRStage) ? ring_s : cst + kRStage;
         }
-        float out[4];
-        unpack2(acc01, out[0], out[1]);
-        unpack2(acc23, out[2], out[3]);
+        const size_t row = (size_t)lg * 16 + r;
+        const size_t ldy = a.ld[wi] ? (size_t)a.ld[wi] : (size_t)M;      // row stride of y
+        bool last_split = true;
+        const size_t slot = (size_t)win * groups_all + g0;              // (window, row-group)
         if (S > 1) {
-            // partial of this split -> scratch; the last split to arrive sums 0..S-1
-            const size_t slot = (size_t)win * groups_all + g0;      // (window, row-group)
-            float *pp = part + (slot * S + split) * 128 + lane;
+            // partials of this split -> scratch; the last split to arrive sums 0..S-1
+            float *pp = part + (slot * S + split) * (128 * NTG) + lane;
 #pragma unroll
-            for (int k = 0; k < 4; ++k) pp[k * 32] = out[k];
+            for (int g = 0; g < NTG; ++g) {
+                float o[4];
+                unpack2(acc01[g], o[0], o[1]);
+                unpack2(acc23[g], o[2], o[3]);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) pp[g * 128 + k * 32] = o[k];
+            }
             __threadfence();
             __syncwarp();
             int old = 0;
             if (lane == 0) old = atomicAdd(count + slot, 1);
             old = __shfl_sync(0xffffffffu, old, 0);
-            if (old != S - 1) continue;
+            last_split = old == S - 1;
+            if (!last_split) continue;
             __threadfence();
-            const float *base = part + slot * S * 128 + lane;
+        }
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                float sum = 0.0f;
-                for (int s2 = 0; s2 < S; ++s2)
-                    sum = __fadd_rn(sum, __ldcg(base + (size_t)s2 * 128 + k * 32));
-                out[k] = sum;
+        for (int g = 0; g < NTG; ++g) {
+            float out[4];
+            unpack2(acc01[g], out[0], out[1]);
+            unpack2(acc23[g], out[2], out[3]);
+            if (S > 1) {
+                // all of a group's partials are requested before the first add (the adds keep
+                // the order 0..S-1): a loop of load-then-add pays an L2 latency per split
+                const float *base = part + slot * S * (128 * NTG) + g * 128 + lane;
+                float v[4][16];
+#pragma unroll
+                for (int s2 = 0; s2 < 16; ++s2)
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        v[k][s2] = s2 < S ? __ldcg(base + (size_t)s2 * (128 * NTG) + k * 32) : 0.0f;
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    float sum = 0.0f;
+#pragma unroll
+                    for (int s2 = 0; s2 < 16; ++s2)
+                        if (s2 < S) sum = __fadd_rn(sum, v[k][s2]);
+                    out[k] = sum;
+                }
             }
-            if (lane == 0) count[slot] = 0;   // ready for the next launch
+            const int tokg = tok0 + 8 * g;
+            if (PT) {
+                const float2 at = __ldg(reinterpret_cast<const float2 *>(a.as_tok + tokg + 2 * c));
+                out[0] = __fmul_rn(out[0], at.x);
+                out[1] = __fmul_rn(out[1], at.y);
+                out[2] = __fmul_rn(out[2], at.x);
+                out[3] = __fmul_rn(out[3], at.y);
+            }
+            if (!a.npeer) {
+                float *y = a.y[wi];
+                const size_t tok = (size_t)tokg + 2 * c;
+                y[tok * ldy + row] = out[0];
+                y[(tok + 1) * ldy + row] = out[1];
+                y[tok * ldy + row + 8] = out[2];
+                y[(tok + 1) * ldy + row + 8] = out[3];
+            } else {
+                // Fused all-gather: transpose the 16 x 8 tile so that a lane holds four consecutive
+                // rows of one token and every peer gets 16-byte stores (64-byte runs).
+                __syncwarp();
+                xpose[(2 * c) * 16 + r] = out[0];
+                xpose[(2 * c + 1) * 16 + r] = out[1];
+                xpose[(2 * c) * 16 + r + 8] = out[2];
+                xpose[(2 * c + 1) * 16 + r + 8] = out[3];
+                __syncwarp();
+                const float4 v = *reinterpret_cast<const float4 *>(xpose + lane * 4);
+                const size_t off = (size_t)(tokg + (lane >> 2)) * ldy + (size_t)lg * 16 + (lane & 3) * 4;
+                for (int pi = 0; pi < a.npeer; ++pi)
+                    *reinterpret_cast<float4 *>(a.ypeer[pi][wi] + off) = v;
+            }
         }
-        if (PT) {
-            const float2 at = __ldg(reinterpret_cast<const float2 *>(a.as_tok + tok0 + 2 * c));
-            out[0] = __fmul_rn(out[0], at.x);
-            out[1] = __fmul_rn(out[1], at.y);
-            out[2] = __fmul_rn(out[2], at.x);
-            out[3] = __fmul_rn(out[3], at.y);
-        }
-        const size_t row = (size_t)lg * 16 + r;
-        const size_t ldy = a.ld[wi] ? (size_t)a.ld[wi] : (size_t)M;      // row stride of y
-        if (!a.npeer) {
-            float *y = a.y[wi];
-            const size_t tok = (size_t)tok0 + 2 * c;
-            y[tok * ldy + row] = out[0];
-            y[(tok + 1) * ldy + row] = out[1];
-            y[tok * ldy + row + 8] = out[2];
-            y[(tok + 1) * ldy + row + 8] = out[3];
-        } else {
-            // Fused all-gather: transpose the 16 x 8 tile so that a lane holds four consecutive
-            // rows of one token and every peer gets 16-byte stores (64-byte runs).
-            __syncwarp();
-            xpose[(2 * c) * 16 + r] = out[0];
-            xpose[(2 * c + 1) * 16 + r] = out[1];
-            xpose[(2 * c) * 16 + r + 8] = out[2];
-            xpose[(2 * c + 1) * 16 + r + 8] = out[3];
-            __syncwarp();
-            const float4 v = *reinterpret_cast<const float4 *>(xpose + lane * 4);
-            const size_t off = (size_t)(tok0 + (lane >> 2)) * ldy + (size_t)lg * 16 + (lane & 3) * 4;
-            for (int pi = 0; pi < a.npeer; ++pi)
-                *reinterpret_cast<float4 *>(a.ypeer[pi][wi] + off) = v;
-        }
+        if (S > 1 && lane == 0) count[slot] = 0;   // ready for the next launch
     }
     RING_STAMP(4)
     RING_STAMP_END()
@@ -940,19 +983,13 @@ int window_groups(const GemmArgs &a) {
 // The ring kernel takes T = 8 calls whose split activations fit beside the rings.
 // Launch shape of the ring kernel for a call, or false when the call is not its to take.
 struct RingPlan {
-    int grid, nw, ns, nwin;
+    int grid, nw, ns, nwin, ntg;
     size_t smem;
 };
-bool ring_plan(const GemmArgs &a, RingPlan &p) {
-    if (a.T < 8 || a.T > 64 || (a.T % 8) || a.dump) return false;
-    if (a.x && (a.T != 8 || a.mode)) return false;   // the fused quantiser serves one window
-    p.nwin = a.T / 8;                         // token windows: CTA columns (grid.y)
-    if (!g_num_sms) {
-        int dev = 0;
-        TQ_CHECK(cudaGetDevice(&dev));
-        TQ_CHECK(cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev));
-        if (g_num_sms <= 0) g_num_sms = 148;
-    }
+// Plan with `ntg` token groups per warp (token windows of 8 ntg tokens on CTA columns).
+bool ring_plan_ntg(const GemmArgs &a, int ntg, RingPlan &p) {
+    p.ntg = ntg;
+    p.nwin = a.T / (8 * ntg);                 // token windows: CTA columns (grid.y)
     const int Kt = a.K >> 5, S = a.max_splits;
     const int groups = a.goff[a.count];
     const int ctas = g_num_sms / p.nwin;      // CTAs of one window
@@ -968,11 +1005,34 @@ bool ring_plan(const GemmArgs &a, RingPlan &p) {
     // k-tiles of the longest split (per-token splits cut whole weight-scale groups)
     const int Ktg = Kt >> a.ksh;
     const int span = a.mode ? (((Ktg + S - 1) / S) << a.ksh) : (Kt + S - 1) / S;
-    const size_t fixed = kRHead + (size_t)span * kActTileBytes + (a.npeer ? (size_t)p.nw * 512 : 0);
-    p.ns = 4;
-    while (p.ns > 2 && (size_t)p.nw * p.ns * kRStage + fixed > kSmemLimit) --p.ns;
+    const size_t fixed = kRHead + (size_t)span * ntg * kActTileBytes + (a.npeer ? (size_t)p.nw * 512 : 0);
+    if (ntg > 1) {
+        // several token groups per warp: one instantiation, at most 20 warps (more registers
+        // for the accumulators), three ring stages
+        p.nw = std::min(p.nw, 20);
+        p.ns = 3;
+    } else {
+        p.ns = 4;
+        while (p.ns > 2 && (size_t)p.nw * p.ns * kRStage + fixed > kSmemLimit) --p.ns;
+    }
     p.smem = (size_t)p.nw * p.ns * kRStage + fixed;
     return p.smem <= kSmemLimit;
+}
+// The widest plan that fits: all of a call's tokens on one warp (weights and their unpacking
+// paid once), else windows of 32, 16 or 8 tokens on CTA columns.
+bool ring_plan(const GemmArgs &a, RingPlan &p) {
+    if (a.T < 8 || a.T > 64 || (a.T % 8) || a.dump) return false;
+    if (a.x && (a.T != 8 || a.mode)) return false;   // the fused quantiser serves one window
+    if (!g_num_sms) {
+        int dev = 0;
+        TQ_CHECK(cudaGetDevice(&dev));
+        TQ_CHECK(cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev));
+        if (g_num_sms <= 0) g_num_sms = 148;
+    }
+    const int tg = a.T / 8;
+    for (int ntg = 8; ntg >= 1; ntg >>= 1)
+        if (tg % ntg == 0 && (ntg == 1 || !a.npeer) && ring_plan_ntg(a, ntg, p)) return true;
+    return false;
 }
 
 bool launch_ring(const GemmArgs &a) {
@@ -985,23 +1045,26 @@ bool launch_ring(const GemmArgs &a) {
     bool pair = a.ksh != 0;
     if (!a.mode)      // per-token splits cut whole K64 groups, so they always start on a pair
         for (int s2 = 0; s2 < S; ++s2) pair = pair && ((Kt * s2 / S) % 2 == 0);
-    if (S > 1) ensure_scratch((size_t)plan.nwin * groups * S * 128, plan.nwin * groups);
+    if (S > 1) ensure_scratch((size_t)plan.nwin * groups * S * 128 * plan.ntg, plan.nwin * groups);
     auto go = [&](auto kernel) {
         // every instantiation has the same function type, so remember them by address
-        static const void *done[32];
+        static const void *done[64];
         static int ndone = 0;
         bool seen = false;
         for (int i = 0; i < ndone; ++i) seen = seen || done[i] == (const void *)kernel;
         if (!seen) {
             TQ_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           (int)kSmemLimit));
-            if (ndone < 32) done[ndone++] = (const void *)kernel;
+            if (ndone < 64) done[ndone++] = (const void *)kernel;
         }
         launch_pdl(kernel, dim3(grid, plan.nwin), dim3(nw * 32), smem, a, g_scratch.part, g_scratch.count);
     };
     auto pick = [&](auto pair_tag, auto pt_tag) {
         constexpr bool P = decltype(pair_tag)::value, Q = decltype(pt_tag)::value;
-        if (ns == 2) go(gemm_w4a8_ring_kernel<P, 2, kRW, Q>);
+        if (plan.ntg == 8) go(gemm_w4a8_ring_kernel<P, 3, 20, Q, 8>);
+        else if (plan.ntg == 4) go(gemm_w4a8_ring_kernel<P, 3, 20, Q, 4>);
+        else if (plan.ntg == 2) go(gemm_w4a8_ring_kernel<P, 3, 20, Q, 2>);
+        else if (ns == 2) go(gemm_w4a8_ring_kernel<P, 2, kRW, Q>);
         else if (ns == 3) go(gemm_w4a8_ring_kernel<P, 3, kRW, Q>);
         else if (nw <= 20) go(gemm_w4a8_ring_kernel<P, 4, 20, Q>);
         else go(gemm_w4a8_ring_kernel<P, 4, kRW, Q>);

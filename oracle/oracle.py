@@ -76,6 +76,22 @@ def choose_gemm_splits(rgroups: int, tgroups: int, ktiles: int, forced: int = 0)
                                             C.c_int(ktiles), C.c_int(forced)))
 
 
+def choose_pertoken_splits(rgroups: int, tgroups: int, ktiles: int, ksh: int, forced: int = 0) -> int:
+    """Split rule of the per-token decode GEMMs (own rule, not in the reference): the split
+    count of an 8-token call, doubled while one split's staged activations (320 bytes per
+    k-tile and 8 tokens) exceed 88 KB; splits cut whole weight-scale groups."""
+    kgroups = ktiles >> ksh
+    s = choose_gemm_splits(rgroups, 1, kgroups, forced=forced)
+    if forced in (1, 2, 4, 8, 16):
+        return s
+    cap = 1
+    while cap < 16 and cap * 2 <= kgroups:
+        cap *= 2
+    while s < cap and (((kgroups + s - 1) // s) << ksh) * tgroups * 320 > 88 * 1024:
+        s *= 2
+    return s
+
+
 def fit_int4_asym(wf, reserve_nibble: bool = True):
     wf = _c(wf, np.float32)
     z = C.c_int(0)

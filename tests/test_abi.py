@@ -65,6 +65,9 @@ def test_split_rules_match_the_oracle_on_the_host():
             for kt in (0, 1, 2, 3, 5, 8, 15, 16, 33, 160, 544):
                 assert lib.qwn_choose_gemm_splits(rg, tg, kt) == orc.choose_gemm_splits(rg, tg, kt), \
                     (rg, tg, kt)
+                for ksh in (0, 1):
+                    assert lib.qwn_choose_pertoken_splits(rg, tg, kt, ksh) == \
+                        orc.choose_pertoken_splits(rg, tg, kt, ksh), (rg, tg, kt, ksh)
 
 
 def test_weight_record_layout_matches_header():

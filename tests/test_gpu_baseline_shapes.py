@@ -169,7 +169,9 @@ def test_cfg3_down_gemm(lib, pkg, orc, w_down_k32, T, splits):
     oq, os_, osm = orc.quantize_act_chunk(x, per_token=True)
     assert np.array_equal(aq.to_numpy(np.int8), oq)
     as_tok = os_.reshape(K // 32, T)[0].copy()
-    _, want = orc.gemm_w4a8_pertoken(codes, scales, M, K, 0, oq, as_tok, osm, T, splits=splits)
+    pt_splits = lib.qwn_choose_pertoken_splits(M // 16, T // 8, K // 32, 0)
+    assert pt_splits == {8: 8, 16: 8, 32: 8, 64: 16}[T]      # own rule: see qwn_choose_pertoken_splits
+    _, want = orc.gemm_w4a8_pertoken(codes, scales, M, K, 0, oq, as_tok, osm, T, splits=pt_splits)
     assert y.to_numpy(np.float32).tobytes() == want.tobytes()
     assert lib.tq_last_error() == 0
 

@@ -885,7 +885,8 @@ def test_gemm_pertoken_decode(lib, pkg, orc, wl, Ms, K, ksh, T):
     oq, os_, osm = orc.quantize_act_chunk(x, per_token=True)
     as_tok = os_.reshape(K // 32, T)[0].copy()
     for (c, s), M, yb in zip(host, Ms, ys):
-        S = lib.qwn_choose_gemm_splits(M // 16, T // 8, K // 32)
+        S = lib.qwn_choose_pertoken_splits(M // 16, T // 8, K // 32, ksh)
+        assert S == orc.choose_pertoken_splits(M // 16, T // 8, K // 32, ksh)
         _, want = orc.gemm_w4a8_pertoken(c, s, M, K, ksh, oq, as_tok, osm, T, splits=S)
         got = yb.to_numpy(np.float32).reshape(T, M)
         assert got.tobytes() == want.tobytes(), (M, S)
