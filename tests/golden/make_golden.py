@@ -82,6 +82,14 @@ def cases():
     g.update(gm_codes=wc, gm_scales=ws, gm_x=xg, gm_offsets=np.array(offs, dtype=np.int32), gm_y=y,
              gm_dots=orc.tile_dots_gemm(wc, Mg, Kg, aq, Tg))
 
+    # per-token activation scales (own extension of the path: one scale per token, one promote
+    # per weight-scale group, splits over whole groups): staging and a 16-token GEMM, K64
+    aqp, asp, asump = orc.quantize_act_chunk(xg[:16], per_token=True)
+    as_tok = asp.reshape(Kg // 32, 16)[0].copy()
+    S = orc.choose_pertoken_splits(Mg // 16, 2, Kg // 32, 1)
+    _, ypt = orc.gemm_w4a8_pertoken(wc, ws, Mg, Kg, 1, aqp, as_tok, asump, 16, splits=S)
+    g.update(pt_aq=aqp, pt_as_tok=as_tok, pt_asum=asump, pt_splits=np.array([S], dtype=np.int32), pt_y=ypt)
+
     # column shard (kernels_dpas.cpp:463-499): rank 1 of 2 over groups [32, 32]
     rc, sc_c, sc_s = orc.w4_shard_column(wc, ws, Mg, Kg, 1, 1, 2, groups=[32, 32])
     assert rc == 0

@@ -62,6 +62,13 @@ def test_oracle_repack_gemv_gemm_match_golden(g, orc):
     _, y = orc.gemm_w4a8(g["gm_codes"], g["gm_scales"], 64, 512, 1, aq, as_, asum, 32,
                          offsets=[int(v) for v in g["gm_offsets"]], fma=1)
     assert same(y, g["gm_y"])
+    # per-token mode
+    aq, as_, asum = orc.quantize_act_chunk(g["gm_x"][:16], per_token=True)
+    assert same(aq, g["pt_aq"]) and same(asum, g["pt_asum"]) and same(as_.reshape(16, 16)[0].copy(), g["pt_as_tok"])
+    S = orc.choose_pertoken_splits(64 // 16, 2, 512 // 32, 1)
+    assert S == int(g["pt_splits"][0])
+    _, y = orc.gemm_w4a8_pertoken(g["gm_codes"], g["gm_scales"], 64, 512, 1, aq, g["pt_as_tok"], asum, 16, splits=S)
+    assert same(y, g["pt_y"])
 
 
 # ------------------------------------------------------------------ CUDA library vs golden
@@ -98,6 +105,19 @@ def test_cuda_matches_golden(g, lib, pkg):
     assert lib.qwn_x_gemm_w4a8(w.ref, aq.ptr, as_.ptr, asum.ptr, y.ptr, T, offs, 2) == 0
     lib.tq_sync()
     assert same(y.to_numpy(np.float32).reshape(T, M), g["gm_y"].reshape(T, M))
+    # per-token staging and GEMM (16 tokens: two token groups on one warp of the ring kernel)
+    Tp = 16
+    npt = Kg // 32 * Tp
+    paq, pas, pasum, pat = pkg.DevBuf(npt * 32), pkg.DevBuf(npt * 4), pkg.DevBuf(npt * 4), pkg.DevBuf(Tp * 4)
+    dpx = dev(g["gm_x"][:Tp])
+    lib.qwn_x_quantize_act_chunk_pertoken(dpx.ptr, Kg, Tp, paq.ptr, pas.ptr, pasum.ptr, pat.ptr)
+    ypt = pkg.DevBuf(Tp * M * 4)
+    assert lib.qwn_x_gemm_w4a8_pertoken(w.ref, paq.ptr, pat.ptr, pasum.ptr, ypt.ptr, Tp, 0) == 0
+    lib.tq_sync()
+    assert same(paq.to_numpy(np.int8).reshape(g["pt_aq"].shape), g["pt_aq"])
+    assert same(pat.to_numpy(np.float32), g["pt_as_tok"])
+    assert lib.qwn_choose_pertoken_splits(M // 16, Tp // 8, Kg // 32, 1) == int(g["pt_splits"][0])
+    assert same(ypt.to_numpy(np.float32).reshape(g["pt_y"].shape), g["pt_y"])
     # column shard
     sh = pkg.TqWeight()
     grp = (C.c_int * 2)(32, 32)
