@@ -210,6 +210,18 @@ void qwn_x_w4_shard_free(tq_qmma_weight_t *w);
 
 /* xpu/src/kernels_dpas.cpp:170-173 and 1226-1250: the split heuristics, exported so
  * callers and tests can see the order a result was summed in. */
+/* Per-projection timers (the reference's profile_projection, xpu/src/decode.cpp:156-219, which
+ * waits for the queue and reads the host clock around each call): with profiling on
+ * (TQ_XPU_PROFILE_PROJ=1 in the environment, or tq_profile_enable(1); returns the previous
+ * setting) every GEMV / GEMM entry point brackets its launches with a pair of CUDA events, and
+ * nothing waits until tq_profile_report, which synchronises, prints one line per
+ * (rows, K, tokens, tier) projection and clears the record. rows, when not NULL, receives up to
+ * max_rows entries of six doubles {rows, K, tokens, tier, calls, total microseconds}; the
+ * return value is the number of distinct projections. tier: 4 / 64 / 16 = W4A8 with K32 /
+ * K64 / K16 scales, 8 = W8A8, 6 = scalar E2M3, 44 = W4A4. Calls made while the stream is
+ * being captured into a CUDA graph are not timed. */
+int tq_profile_enable(int on);
+int tq_profile_report(double *rows, int max_rows);
 int qwn_choose_gemv_splits(int groups);
 int qwn_choose_gemm_splits(int rgroups, int tgroups, int ktiles);
 /* Split count of the per-token decode GEMMs (x_gemm_w4a8_fanout_pertoken, x_gemm_w4a8_fanout_tp with

@@ -82,6 +82,7 @@ SIGNATURES = {
     "qwn_x_gemm_w4a8": (_i, [_WP, _vp, _vp, _vp, _vp, _i, C.POINTER(_i), _i]),
     "qwn_x_w4_shard": (_i, [_WP, _WP, _i, _i, _i, C.POINTER(_i), _i]),
     "qwn_x_w4_shard_free": (None, [_WP]),
+    "tq_profile_enable": (_i, [_i]), "tq_profile_report": (_i, [_vp, _i]),
     "qwn_choose_gemv_splits": (_i, [_i]), "qwn_choose_gemm_splits": (_i, [_i, _i, _i]),
     "qwn_choose_pertoken_splits": (_i, [_i, _i, _i, _i]),
     "qwn_x_gemm_w4a8_fanout": (_i, [C.POINTER(_WP), C.POINTER(_vp), _i, _vp, _vp, _vp, _i,

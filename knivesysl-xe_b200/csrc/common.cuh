@@ -77,6 +77,26 @@ GatherState &gather_state();
 // word on every rank once the GEMM has completed, then waits for every rank's flag.
 void launch_gather_publish(int step);
 
+// ---- per-projection timers (runtime.cu) -------------------------------------------
+// Times the calls queued on the stream during its lifetime when profiling is on.
+bool profile_on();
+class ProfScope {
+public:
+    ProfScope(int M, int K, int T, int tier);
+    ~ProfScope();
+    ProfScope(const ProfScope &) = delete;
+    ProfScope &operator=(const ProfScope &) = delete;
+
+private:
+    int index_ = -1;
+};
+inline int weight_tier(const tq_qmma_weight_t *w) {
+    if (!w) return 0;
+    if (w->s8_ready) return 8;
+    if (!w->s4_ready) return 6;
+    return w->s4_k16 ? 16 : (w->s4_k64 ? 64 : 4);
+}
+
 // ---- split heuristics (dispatch.cu) --------------------------------------------
 int choose_gemv_splits(int groups);
 int choose_gemm_splits(int rgroups, int tgroups, int ktiles);

@@ -88,6 +88,7 @@ int gemv_prepared_impl(const tq_qmma_weight_t *w, float *d_y, const float *d_res
     if (s.cap < w->K || !s.q || !s.scale || s.prepared_K < w->K) return -2;
     if (w->M % 16 || w->K % 32) return -1;
     if (w->s4_k16 && (dump || d_x_fused)) return -1;   // K16: prepared activations, no dump
+    ProfScope prof(w->M, w->K, 1, weight_tier(w));
     GemvArgs a{};
     a.codes[0] = w->d_s4;
     a.scales[0] = w->d_s4_scale;
@@ -283,6 +284,9 @@ int x_gemv_w4a8_fused(const tq_qmma_weight_t *w, const float *d_x, const float *
 int x_gemv_w4a8_fanout(const tq_qmma_weight_t *const *ws, float *const *ys, int count) {
     if (!ws || !ys || count <= 0 || count > 4) return -1;
     if (!ws[0]) return -2;
+    int prof_rows = 0;
+    for (int i = 0; i < count; ++i) prof_rows += ws[i] ? ws[i]->M : 0;
+    ProfScope prof(prof_rows, ws[0]->K, 1, weight_tier(ws[0]));
     GemvArgs a{};
     const int K = ws[0]->K;
     const int ksh = ws[0]->s4_k64 ? 1 : 0;
@@ -332,6 +336,7 @@ int x_w8_repack_weight(tq_qmma_weight_t *w) {
 
 int x_gemv_w8a8_prepared(const tq_qmma_weight_t *w, float *d_y, const float *d_residual) {
     if (!w || !w->s8_ready || !w->d_s8 || !w->d_s8_scale || !d_y) return -1;
+    ProfScope prof(w->M, w->K, 1, 8);
     ActScratch &s = act_scratch();
     if (s.cap < w->K || !s.q || !s.scale || s.prepared_K < w->K) return -2;
     if (w->M % 16 || w->K % 32) return -1;
@@ -357,6 +362,7 @@ int x_gemm_w8a8(const tq_qmma_weight_t *w, const int8_t *d_aq, const float *d_as
                 int T) {
     if (!w || !w->s8_ready || !w->d_s8 || !w->d_s8_scale) return -1;
     if (!d_aq || !d_as || !d_y || T <= 0 || (T % 8) != 0) return -2;
+    ProfScope prof(w->M, w->K, T, 8);
     launch_gemm_w8a8(w->d_s8, w->d_s8_scale, d_aq, d_as, d_y, w->M, w->K, T);
     return 0;
 }
@@ -506,6 +512,7 @@ int x_gemm_w4a8_fanout(const tq_qmma_weight_t *const *ws, float *const *ys, int 
     GemmArgs a{};
     const int rc = fanout_args(a, ws, count, T, offsets, segments);
     if (rc) return rc;
+    ProfScope prof(a.goff[a.count] * 16, a.K, T, a.ksh ? 64 : 4);
     if (!d_aq || !d_as || !d_asum) return -2;
     for (int i = 0; i < count; ++i) {
         if (!ys[i]) return -2;
@@ -529,6 +536,7 @@ int x_gemm_w4a8_fanout_fused(const tq_qmma_weight_t *const *ws, float *const *ys
     const int rc = fanout_args(a, ws, count, T, nullptr, 0);
     if (rc) return rc;
     if (!d_x) return -2;
+    ProfScope prof(a.goff[a.count] * 16, a.K, T, a.ksh ? 64 : 4);
     for (int i = 0; i < count; ++i) {
         if (!ys[i]) return -2;
         a.y[i] = ys[i];
@@ -553,6 +561,7 @@ int gathered_impl(const tq_qmma_weight_t *const *ws, int count, const int8_t *d_
     const int rc = fanout_args(a, ws, count, T, nullptr, 0);
     if (rc) return rc;
     if (d_x ? false : (!d_aq || !d_as || !d_asum)) return -2;
+    ProfScope prof(a.goff[a.count] * 16, a.K, T, a.ksh ? 64 : 4);
     size_t block = 0;
     for (int i = 0; i < count; ++i) block += (size_t)T * ws[i]->M;
     // two halves, used alternately: a rank that is one step ahead never overwrites a block
@@ -598,6 +607,7 @@ int x_gemm_w4a8_fanout_pertoken(const tq_qmma_weight_t *const *ws, float *const 
     const int rc = fanout_args(a, ws, count, T, nullptr, 0);
     if (rc) return rc;
     if (!d_aq || !d_as_tok || !d_asum) return -2;
+    ProfScope prof(a.goff[a.count] * 16, a.K, T, a.ksh ? 64 : 4);
     for (int i = 0; i < count; ++i) {
         if (!ys[i]) return -2;
         a.y[i] = ys[i];
@@ -627,6 +637,7 @@ int x_gemm_w4a8_fanout_tp(const tq_qmma_weight_t *const *ws, int count, const in
     const int rc = fanout_args(a, ws, count, T, nullptr, 0, full_rows);
     if (rc) return rc;
     if (!d_aq || !d_asum || (!d_as && !d_as_tok)) return -2;
+    ProfScope prof(a.goff[a.count] * 16, a.K, T, a.ksh ? 64 : 4);
     a.aq = d_aq;
     a.asum = d_asum;
     a.as = d_as;

@@ -575,6 +575,7 @@ int launch_gemm_tc(const GemmTcArgs &a) {
         TQ_CHECK(big_smem(gemm_w4a8_tc_kernel<2, false, true>));
         g_tc.zp_flag = static_cast<int *>(tq_dev_alloc(sizeof(int), "gemm.tc.zero-point.flag"));
     }
+    ProfScope prof(a.M, a.K, a.T, a.aq4 ? 44 : (a.ksh ? 64 : 4));
     const int Tpad = (a.T + kTN - 1) / kTN * kTN;
     const size_t ibytes = (size_t)Kt * (Tpad / kTN) * (kBBytes + kSBytes);
     if (ibytes > g_tc.img_bytes) {

@@ -51,6 +51,7 @@ int launch_gemv_e2m3(const tq_qmma_weight_t *w, const float *d_x, const float *d
     if (w->M != w->Mt * 16 || w->K != w->Kt * 32) return -5;
     const int need_rows = (w->M + 127) >> 7, need_cols = (w->Kt + 3) >> 2;
     if (w->scale_rows < need_rows || (w->scale_cols != w->Kt && w->scale_cols < need_cols)) return -6;
+    ProfScope prof(w->M, w->K, 1, 6);
     launch_pdl(gemv_e2m3_kernel, dim3(w->Mt), dim3(256), 0, (const uint8_t *)w->d_A,
                (const float *)w->d_block_scale_inv, w->scale_cols, w->M, w->K, d_x, d_residual, d_y);
     TQ_LAUNCH_CHECK("gemv_e2m3_kernel");

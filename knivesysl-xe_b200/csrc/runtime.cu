@@ -3,6 +3,8 @@
 // scratch, events. Replaces the SYCL queue layer of xpu/src/decode.cpp:40-130.
 #include "common.cuh"
 
+#include <vector>
+
 #include <string.h>
 
 namespace tq {
@@ -300,3 +302,95 @@ float tq_event_elapsed_ms(void *start, void *stop) {
 }
 
 }  // extern "C"
+
+// ---- per-projection timers (the reference's profile_projection, xpu/src/decode.cpp:156-219) ----
+// The reference waits for the queue and reads the host clock around every projection; here a
+// pair of CUDA events goes onto the stream around the call and nothing waits until the report
+// is asked for, so profiling does not serialise the steps it measures. Off by default
+// (TQ_XPU_PROFILE_PROJ=1 or tq_profile_enable); calls made during stream capture are not timed.
+namespace tq {
+namespace {
+struct ProfSpan {
+    int M, K, T, tier;
+    cudaEvent_t e0, e1;
+};
+std::vector<ProfSpan> g_prof_spans;
+std::vector<cudaEvent_t> g_prof_free;
+int g_prof_on = -1;
+constexpr size_t kProfMaxSpans = 1 << 16;
+
+cudaEvent_t prof_event() {
+    if (!g_prof_free.empty()) {
+        cudaEvent_t e = g_prof_free.back();
+        g_prof_free.pop_back();
+        return e;
+    }
+    cudaEvent_t e = nullptr;
+    TQ_CHECK(cudaEventCreate(&e));
+    return e;
+}
+}  // namespace
+
+bool profile_on() {
+    if (g_prof_on < 0) {
+        const char *e = getenv("TQ_XPU_PROFILE_PROJ");
+        g_prof_on = (e && *e && *e != '0') ? 1 : 0;
+    }
+    return g_prof_on > 0;
+}
+
+ProfScope::ProfScope(int M, int K, int T, int tier) {
+    if (!profile_on() || g_prof_spans.size() >= kProfMaxSpans) return;
+    cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream(), &st) != cudaSuccess || st != cudaStreamCaptureStatusNone) return;
+    g_prof_spans.push_back(ProfSpan{M, K, T, tier, prof_event(), prof_event()});
+    index_ = (int)g_prof_spans.size() - 1;
+    TQ_CHECK(cudaEventRecord(g_prof_spans[index_].e0, stream()));
+}
+ProfScope::~ProfScope() {
+    if (index_ >= 0) TQ_CHECK(cudaEventRecord(g_prof_spans[index_].e1, stream()));
+}
+}  // namespace tq
+
+extern "C" int tq_profile_enable(int on) {
+    const int was = tq::profile_on() ? 1 : 0;
+    tq::g_prof_on = on ? 1 : 0;
+    return was;
+}
+
+// Waits for the stream, adds the recorded spans up per (M, K, T, tier), prints one line per
+// projection and clears the record. rows, when not NULL, receives up to max_rows entries of six
+// doubles {M, K, T, tier, calls, total microseconds}. Returns the number of distinct
+// projections. tier: 4 = W4A8 K32, 64 = K64, 16 = K16, 8 = W8A8, 6 = scalar E2M3, 44 = W4A4.
+extern "C" int tq_profile_report(double *rows, int max_rows) {
+    using namespace tq;
+    tq_sync();
+    struct Agg {
+        int M, K, T, tier;
+        long calls;
+        double us;
+    };
+    std::vector<Agg> agg;
+    for (const ProfSpan &sp : g_prof_spans) {
+        float ms = 0.0f;
+        if (cudaEventElapsedTime(&ms, sp.e0, sp.e1) != cudaSuccess) ms = 0.0f;
+        size_t i = 0;
+        while (i < agg.size() && !(agg[i].M == sp.M && agg[i].K == sp.K && agg[i].T == sp.T && agg[i].tier == sp.tier)) ++i;
+        if (i == agg.size()) agg.push_back(Agg{sp.M, sp.K, sp.T, sp.tier, 0, 0.0});
+        agg[i].calls += 1;
+        agg[i].us += (double)ms * 1e3;
+        g_prof_free.push_back(sp.e0);
+        g_prof_free.push_back(sp.e1);
+    }
+    g_prof_spans.clear();
+    for (size_t i = 0; i < agg.size(); ++i) {
+        printf("projection [%d x %d] T=%d tier %d: %ld calls, %.1f us, %.2f us/call\n", agg[i].M, agg[i].K, agg[i].T,
+               agg[i].tier, agg[i].calls, agg[i].us, agg[i].us / (double)agg[i].calls);
+        if (rows && (int)i < max_rows) {
+            double *r = rows + 6 * i;
+            r[0] = agg[i].M; r[1] = agg[i].K; r[2] = agg[i].T; r[3] = agg[i].tier;
+            r[4] = (double)agg[i].calls; r[5] = agg[i].us;
+        }
+    }
+    return (int)agg.size();
+}
