@@ -158,3 +158,68 @@ def test_two_rank_row_shard_allreduce_within_tolerance():
         p.join(120)
     assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
     assert q.get(timeout=5) <= 1e-3       # the stated fp32 tolerance; not bit-exact by design
+
+
+def _chain_main(rank, world, port, q):
+    """Two column-sharded projections in a row with per-token activation scales, the way the
+    tensor-parallel decode chain runs them: a shard is split like the whole projection
+    (the split count comes from the unsharded row count), every rank ends up with the full
+    output matrix, quantises it per token and multiplies its shard of the next weight."""
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import torch
+    import torch.distributed as dist
+    from oracle import oracle as orc
+    wl = importlib.import_module("knivesysl-xe_b200.workloads")
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        T, K0, N1, N2, ksh = 8, 512, 640, 384, 0
+        w1 = wl.random_packed_weight(N1, K0, seed=21, ksh=ksh)              # same on every rank
+        w2 = wl.random_packed_weight(N2, N1, seed=22, ksh=ksh)
+        x = wl.activations_normal(T, K0, seed=3, outlier_frac=0.01)
+
+        def project(weight, M, K, xin, sharded):
+            codes, scales = weight
+            aq, as_, asum = orc.quantize_act_chunk(xin, per_token=True)
+            as_tok = as_.reshape(K // 32, T)[0].copy()
+            S = orc.choose_pertoken_splits(M // 16, T // 8, K // 32, ksh)   # of the WHOLE projection
+            if not sharded:
+                return orc.gemm_w4a8_pertoken(codes, scales, M, K, ksh, aq, as_tok, asum, T, splits=S)[1].reshape(T, M), S
+            rc, sc, ss = orc.w4_shard_column(codes, scales, M, K, ksh, rank, world, groups=None)
+            assert rc == 0
+            Mn = M // world
+            y = orc.gemm_w4a8_pertoken(sc, ss, Mn, K, ksh, aq, as_tok, asum, T, splits=S)[1].reshape(T, Mn)
+            y = torch.from_numpy(np.ascontiguousarray(y))
+            parts = [torch.empty_like(y) for _ in range(world)]
+            dist.all_gather(parts, y)
+            return np.concatenate([p.numpy() for p in parts], axis=1), S   # columns [r * Mn, (r + 1) * Mn)
+
+        y1, S1 = project(w1, N1, K0, x, True)
+        y2, S2 = project(w2, N2, N1, y1, True)
+        if rank == 0:
+            f1, _ = project(w1, N1, K0, x, False)
+            f2, _ = project(w2, N2, N1, f1, False)
+            # the rule under test matters: a shard on its own would pick another split count
+            own = orc.choose_pertoken_splits(N1 // world // 16, T // 8, K0 // 32, ksh)
+            q.put((y1.tobytes() == f1.tobytes(), y2.tobytes() == f2.tobytes(), S1, own))
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_per_token_chain_bit_identical():
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_chain_main, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(180)
+    assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+    same1, same2, s_full, s_shard = q.get(timeout=5)
+    assert same1 and same2
+    assert s_full != s_shard or s_full == 16, (s_full, s_shard)
