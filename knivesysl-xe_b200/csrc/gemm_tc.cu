@@ -217,7 +217,8 @@ __device__ __forceinline__ uint4 nib8_to_h8(uint32_t w, uint32_t mask, uint32_t 
     uint32_t r[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        const uint32_t t = ((w >> (4 * i)) & mask) ^ bias;
+        uint32_t t;                                        // ((w >> 4i) & mask) ^ bias in one logic op
+        asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(t) : "r"(w >> (4 * i)), "r"(mask), "r"(bias));
         asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(r[i]) : "r"(t), "r"(bias));
     }
     return make_uint4(r[0], r[1], r[2], r[3]);
