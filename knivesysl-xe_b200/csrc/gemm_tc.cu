@@ -43,8 +43,8 @@
 //    operand layout);
 //  * two MMA threads (in two warps, steps in turn): two tcgen05.mma (M=128, N=128, K=16) per
 //    k-tile into accumulator buffer b (the first MMA of a promote group overwrites it);
-//    tcgen05.commit signals the workers. The single-thread roles nap between polls of a
-//    barrier: back-to-back polling took a fifth of the schedulers' issue slots.
+//    tcgen05.commit signals the workers. The single-thread roles wait with a suspend-time
+//    hint: back-to-back polling took a fifth of the schedulers' issue slots.
 //
 // Every mbarrier wait is bounded; on expiry the kernel records a status word, stops
 // issuing work, still frees its TMEM and returns.
@@ -80,7 +80,7 @@ constexpr int kThreads = (kWorkWarps + 1 + kMmaWarps) * 32;    // + the warp tha
 constexpr int kAhead = 3;                 // steps (of two k-tiles) the expansion runs ahead of the
                                           // promote: a slot is rewritten only after the step that
                                           // used it was promoted by the same warp, kAhead <= kSS - 1
-constexpr uint32_t kNapNs = 64;           // nap between polls of the single-thread roles
+constexpr uint32_t kNapNs = 2000;         // suspend-time hint of the single-thread roles' waits
 constexpr int kLoadAhead = 2;             // steps the packed bytes are loaded (into registers) ahead
                                           // of their expansion
 constexpr int kL2Ahead = 8;               // steps their lines are prefetched into L2 ahead of that
@@ -282,10 +282,10 @@ __global__ void __maxnreg__(168) gemm_w4a8_tc_kernel(const TcParams p) {
     const int n_total = my_tiles * spt;                  // steps of this CTA
 
     // A wait that gives up when another role already has: the flag is read on the slow path only.
-    auto wait_on = [&](uint32_t bar, uint32_t parity, int code, uint32_t sleep_ns = 0) -> bool {
+    auto wait_on = [&](uint32_t bar, uint32_t parity, int code, uint32_t suspend_ns = 0) -> bool {
         if (mbar_test_wait(bar, parity)) return true;
         if (*(volatile int *)&dead_s) return false;
-        if (mbar_wait_slow(bar, parity, p.status, code, p.wait_ns, sleep_ns)) return true;
+        if (mbar_wait_slow(bar, parity, p.status, code, p.wait_ns, suspend_ns)) return true;
         dead_s = 1;
         return false;
     };

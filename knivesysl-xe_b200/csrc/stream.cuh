@@ -44,6 +44,20 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
     return ok;
 }
 
+// The same with a suspend-time hint: the thread may stay suspended up to hint_ns while the
+// phase is incomplete.
+__device__ __forceinline__ uint32_t mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(hint_ns)
+        : "memory");
+    return ok;
+}
+
 // Non-blocking test of a phase (mbarrier.test_wait never suspends the thread).
 __device__ __forceinline__ uint32_t mbar_test_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
@@ -70,16 +84,17 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 // loop with its clock arithmetic at each of them multiplies the kernel's code size until its
 // roles evict one another from the instruction cache.
 static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, int *status, int code,
-                                                   uint64_t limit_ns, uint32_t sleep_ns = 0) {
+                                                   uint64_t limit_ns, uint32_t suspend_ns = 0) {
     // mbarrier.try_wait comes back after some tens of clocks while the phase is incomplete, so
     // a warp that polls back to back takes a fifth or more of its scheduler's issue slots
-    // from the warps beside it. A role whose reaction time has slack (a single issuing
-    // thread that runs ahead of its consumers) passes sleep_ns > 0 and naps between polls.
-    // The clock is read every 2048 polls.
+    // from the warps beside it. A single issuing thread that waits beside working warps
+    // passes suspend_ns > 0: the wait then carries that suspend-time hint and the thread
+    // stays off the scheduler until the phase completes or the time is up (measured a little
+    // faster than a nanosleep between polls, which wakes late). The clock is read every 2048
+    // polls, so the limit is noticed within 2048 * suspend_ns.
     uint64_t t0 = 0;
     for (uint32_t polls = 1;; ++polls) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if (sleep_ns) __nanosleep(sleep_ns);
+        if (suspend_ns ? mbar_try_wait_hint(bar, parity, suspend_ns) : mbar_try_wait(bar, parity)) return true;
         if ((polls & 2047u) == 0) {
             const uint64_t now = global_timer_ns();
             if (t0 == 0) t0 = now;
