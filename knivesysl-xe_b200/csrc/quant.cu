@@ -8,6 +8,8 @@
 // scale/sums out.
 #include "common.cuh"
 
+#include <algorithm>
+
 namespace tq {
 
 namespace {
@@ -197,6 +199,63 @@ quant_chunk_kernel(const float *__restrict__ x, int K, int T, size_t blocks,
     }
 }
 
+// Prefill-sized chunk staging: the same blocks and results as quant_chunk_kernel, laid out for
+// bandwidth. Eight lanes own a K32 block (a float4 each: block maximum and code sum are three
+// shuffles), a warp takes 128 consecutive values of a token row per unit and four units per
+// trip of a grid-stride loop, all four loads issued before the first division. One warp per
+// block with a scalar load each, as above, ran 4096 x 5120 at 0.4 TB/s.
+template <bool PER_TOKEN>
+__global__ void __launch_bounds__(256)
+quant_chunk_wide_kernel(const float *__restrict__ x, int K, int T, int8_t *__restrict__ aq,
+                        float *__restrict__ as, int32_t *__restrict__ asum,
+                        const float *__restrict__ as_tok) {
+    pdl_trigger();
+    pdl_wait();
+    constexpr int kU = 4;
+    const int lane = threadIdx.x & 31, sub = lane & 7;
+    const int upr = K >> 7;                                  // units per token row (K % 128 == 0)
+    const size_t units = (size_t)T * (size_t)upr;
+    const size_t nwarps = (size_t)gridDim.x * 8;
+    for (size_t u0 = ((size_t)blockIdx.x * 8 + (threadIdx.x >> 5)) * kU; u0 < units; u0 += nwarps * kU) {
+        float4 v[kU];
+#pragma unroll
+        for (int i = 0; i < kU; ++i)
+            if (u0 + i < units)
+                v[i] = __ldcs(reinterpret_cast<const float4 *>(x + (u0 + i) * 128) + lane);
+#pragma unroll
+        for (int i = 0; i < kU; ++i) {
+            if (u0 + i >= units) break;                      // uniform per warp
+            const size_t tok = (u0 + i) / (size_t)upr;
+            const size_t kt = ((u0 + i) % (size_t)upr) * 4 + (lane >> 3);
+            float s;
+            if (PER_TOKEN) {
+                s = as_tok[tok];
+            } else {
+                float mx = fmaxf(fmaxf(-INFINITY, fabsf(v[i].x)), fabsf(v[i].y));
+                mx = fmaxf(fmaxf(mx, fabsf(v[i].z)), fabsf(v[i].w));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+                s = (mx > 0.0f) ? __fdiv_rn(mx, 127.0f) : 1.0f;
+            }
+            const int q0 = quantise_one(v[i].x, s), q1 = quantise_one(v[i].y, s);
+            const int q2 = quantise_one(v[i].z, s), q3 = quantise_one(v[i].w, s);
+            int sum = q0 + q1 + q2 + q3;
+            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+            const size_t blk = kt * (size_t)T + tok;
+            reinterpret_cast<uint32_t *>(aq + blk * 32)[sub] =
+                (uint32_t)(q0 & 0xFF) | ((uint32_t)(q1 & 0xFF) << 8) | ((uint32_t)(q2 & 0xFF) << 16) |
+                ((uint32_t)(q3 & 0xFF) << 24);
+            if (sub == 0) {
+                as[blk] = s;
+                asum[blk] = sum;
+            }
+        }
+    }
+}
+
 // x_rmsnorm_chunk (xpu/src/kernels_dpas.cpp:1124-1144): one 256-thread block per token row.
 // Thread t adds the squares of elements t, t+256, ... in order; the block sum is a fixed
 // binary tree over the 256 partial sums (the reference leaves that order to the SYCL runtime).
@@ -250,6 +309,53 @@ quant_chunk_s4_kernel(const float *__restrict__ x, int K, int T, size_t blocks,
     if (lane == 0) {
         as4[blk] = s;
         asum4[blk] = sum;
+    }
+}
+
+// The same blocks for prefill-sized calls, laid out like quant_chunk_wide_kernel: sixteen lanes
+// own a K64 block (a float4 each -> two packed bytes), a warp takes 128 consecutive values of
+// a token row per unit and four units per trip.
+__global__ void __launch_bounds__(256)
+quant_chunk_s4_wide_kernel(const float *__restrict__ x, int K, int T, uint8_t *__restrict__ aq4,
+                           float *__restrict__ as4, int32_t *__restrict__ asum4) {
+    pdl_trigger();
+    pdl_wait();
+    constexpr int kU = 4;
+    const int lane = threadIdx.x & 31, sub = lane & 15;
+    const int upr = K >> 7;
+    const size_t units = (size_t)T * (size_t)upr;
+    const size_t nwarps = (size_t)gridDim.x * 8;
+    for (size_t u0 = ((size_t)blockIdx.x * 8 + (threadIdx.x >> 5)) * kU; u0 < units; u0 += nwarps * kU) {
+        float4 v[kU];
+#pragma unroll
+        for (int i = 0; i < kU; ++i)
+            if (u0 + i < units)
+                v[i] = __ldcs(reinterpret_cast<const float4 *>(x + (u0 + i) * 128) + lane);
+#pragma unroll
+        for (int i = 0; i < kU; ++i) {
+            if (u0 + i >= units) break;                      // uniform per warp
+            const size_t tok = (u0 + i) / (size_t)upr;
+            const size_t kt = ((u0 + i) % (size_t)upr) * 2 + (lane >> 4);
+            float mx = fmaxf(fmaxf(-INFINITY, fabsf(v[i].x)), fabsf(v[i].y));
+            mx = fmaxf(fmaxf(mx, fabsf(v[i].z)), fabsf(v[i].w));
+#pragma unroll
+            for (int off = 1; off <= 8; off <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+            const float s = (mx > 0.0f) ? __fdiv_rn(mx, 7.0f) : 1.0f;
+            const int q0 = (int)clampf(rintf(__fdiv_rn(v[i].x, s)), -7.0f, 7.0f);
+            const int q1 = (int)clampf(rintf(__fdiv_rn(v[i].y, s)), -7.0f, 7.0f);
+            const int q2 = (int)clampf(rintf(__fdiv_rn(v[i].z, s)), -7.0f, 7.0f);
+            const int q3 = (int)clampf(rintf(__fdiv_rn(v[i].w, s)), -7.0f, 7.0f);
+            int sum = q0 + q1 + q2 + q3;
+#pragma unroll
+            for (int off = 1; off <= 8; off <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+            const size_t blk = kt * (size_t)T + tok;
+            reinterpret_cast<uint16_t *>(aq4 + blk * 32)[sub] =
+                (uint16_t)((q0 & 0xF) | ((q1 & 0xF) << 4) | ((q2 & 0xF) << 8) | ((q3 & 0xF) << 12));
+            if (sub == 0) {
+                as4[blk] = s;
+                asum4[blk] = sum;
+            }
+        }
     }
 }
 
@@ -327,8 +433,11 @@ quant_chunk_pertoken_fused_kernel(const float *__restrict__ x, int K, int T,
 // The same result in one pass for rows of at most 8192 values: a thread keeps its (up to) two
 // float4 of the row in registers between the maximum and the quantisation, so the kernel is
 // one global round trip, the block reduction and the stores. Eight consecutive lanes hold one
-// K32 block; their code sums are added with three shuffles.
-__global__ void __launch_bounds__(1024)
+// K32 block; their code sums are added with three shuffles. NT threads with NU float4 each:
+// 1024 x 2 for decode batches (shortest chain), 256 x 8 for prefill-sized calls (eight CTAs per
+// SM overlap their round trips: 4096 x 5120 in 40 us against 82 us).
+template <int NT, int NU>
+__global__ void __launch_bounds__(NT)
 quant_chunk_pertoken_regs_kernel(const float *__restrict__ x, int K, int T,
                                  int8_t *__restrict__ aq, float *__restrict__ as,
                                  int32_t *__restrict__ asum, float *__restrict__ as_tok,
@@ -336,17 +445,17 @@ quant_chunk_pertoken_regs_kernel(const float *__restrict__ x, int K, int T,
     pdl_trigger();
     pdl_wait();
     exchange_sync(sync);
-    __shared__ float wmax[32];
+    __shared__ float wmax[NT / 32];
     __shared__ float s_scale;
     const int tok = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const float4 *row4 = reinterpret_cast<const float4 *>(x + (size_t)tok * K);
     const int n4 = K >> 2;
-    float4 v[2];
+    float4 v[NU];
     float m = -INFINITY;
 #pragma unroll
-    for (int u = 0; u < 2; ++u) {
-        const int i = threadIdx.x + u * 1024;
+    for (int u = 0; u < NU; ++u) {
+        const int i = threadIdx.x + u * NT;
         v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
         if (i < n4) {
             v[u] = row4[i];
@@ -357,7 +466,7 @@ quant_chunk_pertoken_regs_kernel(const float *__restrict__ x, int K, int T,
     if (lane == 0) wmax[warp] = m;
     __syncthreads();
     if (warp == 0) {
-        const float t = warp_max(wmax[lane]);
+        const float t = warp_max(lane < NT / 32 ? wmax[lane] : -INFINITY);
         if (lane == 0) {
             const float s = (t > 0.0f) ? __fdiv_rn(t, 127.0f) : 1.0f;
             s_scale = s;
@@ -367,8 +476,8 @@ quant_chunk_pertoken_regs_kernel(const float *__restrict__ x, int K, int T,
     __syncthreads();
     const float s = s_scale;
 #pragma unroll
-    for (int u = 0; u < 2; ++u) {
-        const int i = threadIdx.x + u * 1024;       // float4 index in the row; uniform per warp
+    for (int u = 0; u < NU; ++u) {
+        const int i = threadIdx.x + u * NT;         // float4 index in the row; uniform per warp
         if (i - lane >= n4) break;
         const int q0 = quantise_one(v[u].x, s), q1 = quantise_one(v[u].y, s);
         const int q2 = quantise_one(v[u].z, s), q3 = quantise_one(v[u].w, s);
@@ -586,10 +695,37 @@ namespace {
 const SyncArgs kNoSync = {};
 }
 
+// Prefill-sized calls (64 tokens and more) whose rows split into 128-value units and whose
+// buffers take 16-byte loads and 4-byte stores go to the wide kernels.
+static bool wide_staging(const float *d_x, int K, int T, const int8_t *d_aq) {
+    return T >= 64 && K % 128 == 0 && (reinterpret_cast<uintptr_t>(d_x) & 15) == 0 &&
+           (reinterpret_cast<uintptr_t>(d_aq) & 3) == 0;
+}
+static int sm_count() {
+    static int sms = 0;
+    if (!sms) {
+        int dev = 0;
+        TQ_CHECK(cudaGetDevice(&dev));
+        TQ_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+        if (sms <= 0) sms = 148;
+    }
+    return sms;
+}
+static unsigned wide_grid(int K, int T) {
+    const size_t units = (size_t)T * (size_t)(K >> 7);
+    return (unsigned)std::min<size_t>((units + 31) / 32, (size_t)sm_count() * 8);
+}
+
 void launch_quant_chunk(const float *d_x, int K, int T, int8_t *d_aq, float *d_as,
                         int32_t *d_asum, const SyncArgs *sync) {
     const size_t blocks = (size_t)(K / 32) * (size_t)T;
     if (!blocks) return;
+    if (!sync && wide_staging(d_x, K, T, d_aq)) {
+        launch_pdl(quant_chunk_wide_kernel<false>, dim3(wide_grid(K, T)), dim3(256), 0, d_x, K, T, d_aq, d_as,
+                   d_asum, (const float *)nullptr);
+        TQ_LAUNCH_CHECK("quant_chunk_wide_kernel");
+        return;
+    }
     const unsigned grid = (unsigned)((blocks + kWarpsPerBlock - 1) / kWarpsPerBlock);
     launch_pdl(quant_chunk_kernel<false>, dim3(grid), dim3(kWarpsPerBlock * 32), 0, d_x, K, T,
                blocks, d_aq, d_as, d_asum, (const float *)nullptr, sync ? *sync : kNoSync);
@@ -607,6 +743,12 @@ void launch_quant_chunk_s4(const float *d_x, int K, int T, uint8_t *d_aq4, float
                            int32_t *d_asum4) {
     const size_t blocks = (size_t)(K / 64) * (size_t)T;
     if (!blocks) return;
+    if (wide_staging(d_x, K, T, reinterpret_cast<const int8_t *>(d_aq4))) {
+        launch_pdl(quant_chunk_s4_wide_kernel, dim3(wide_grid(K, T)), dim3(256), 0, d_x, K, T, d_aq4, d_as4,
+                   d_asum4);
+        TQ_LAUNCH_CHECK("quant_chunk_s4_wide_kernel");
+        return;
+    }
     const unsigned grid = (unsigned)((blocks + kWarpsPerBlock - 1) / kWarpsPerBlock);
     launch_pdl(quant_chunk_s4_kernel, dim3(grid), dim3(kWarpsPerBlock * 32), 0, d_x, K, T, blocks,
                d_aq4, d_as4, d_asum4);
@@ -657,7 +799,7 @@ void launch_quant_chunk_pertoken(const float *d_x, int K, int T, int8_t *d_aq, f
                                 d_as_tok, sa))
         return;
     if (T <= 32 && K <= 8192) {
-        launch_pdl(quant_chunk_pertoken_regs_kernel, dim3(T), dim3(1024), 0, d_x, K, T, d_aq, d_as,
+        launch_pdl(quant_chunk_pertoken_regs_kernel<1024, 2>, dim3(T), dim3(1024), 0, d_x, K, T, d_aq, d_as,
                    d_asum, d_as_tok, sa);
         TQ_LAUNCH_CHECK("quant_chunk_pertoken_regs_kernel");
         return;
@@ -668,8 +810,21 @@ void launch_quant_chunk_pertoken(const float *d_x, int K, int T, int8_t *d_aq, f
         TQ_LAUNCH_CHECK("quant_chunk_pertoken_fused_kernel");
         return;
     }
+    if (K <= 8192 && (reinterpret_cast<uintptr_t>(d_x) & 15) == 0 && (reinterpret_cast<uintptr_t>(d_aq) & 3) == 0) {
+        // a row fits the registers of one CTA: one pass whatever the token count
+        launch_pdl(quant_chunk_pertoken_regs_kernel<256, 8>, dim3(T), dim3(256), 0, d_x, K, T, d_aq, d_as,
+                   d_asum, d_as_tok, sa);
+        TQ_LAUNCH_CHECK("quant_chunk_pertoken_regs_kernel");
+        return;
+    }
     launch_pdl(token_scale_kernel, dim3(T), dim3(256), 0, d_x, K, d_as_tok, sa);
     TQ_LAUNCH_CHECK("token_scale_kernel");
+    if (wide_staging(d_x, K, T, d_aq)) {
+        launch_pdl(quant_chunk_wide_kernel<true>, dim3(wide_grid(K, T)), dim3(256), 0, d_x, K, T, d_aq, d_as,
+                   d_asum, (const float *)d_as_tok);
+        TQ_LAUNCH_CHECK("quant_chunk_wide_kernel<pertoken>");
+        return;
+    }
     const unsigned grid = (unsigned)((blocks + kWarpsPerBlock - 1) / kWarpsPerBlock);
     launch_pdl(quant_chunk_kernel<true>, dim3(grid), dim3(kWarpsPerBlock * 32), 0, d_x, K, T,
                blocks, d_aq, d_as, d_asum, (const float *)d_as_tok, kNoSync);

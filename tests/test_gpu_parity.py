@@ -52,7 +52,11 @@ def test_quantize_act_s8(lib, pkg, orc, K):
 
 
 @pytest.mark.parametrize("K,T,exceptional", [(128, 16, True), (128, 16, False), (5120, 8, False),
-                                             (256, 40, True)])
+                                             (256, 40, True),
+                                             # 64 tokens and more: the wide kernel (K % 128 == 0) ...
+                                             (128, 67, True), (5120, 136, False), (17408, 64, False),
+                                             # ... and the block-per-warp one where a row does not split
+                                             (160, 70, True)])
 def test_quantize_act_chunk(lib, pkg, orc, K, T, exceptional):
     x = refgen.chunk_quant_probe_input(K, T, exceptional)
     dx = dev(pkg, x)
@@ -68,9 +72,11 @@ def test_quantize_act_chunk(lib, pkg, orc, K, T, exceptional):
     assert np.array_equal(asum.to_numpy(np.int32), osm)
 
 
-@pytest.mark.parametrize("T", [8, 16, 40])      # one fused launch up to 32 tokens, two above
-def test_quantize_act_chunk_pertoken(lib, pkg, orc, wl, T):
-    K = 5120
+# one fused launch up to 32 tokens; above, one CTA per token with the row in registers (rows up
+# to 8192 values) or the row maxima and then the wide kernel
+@pytest.mark.parametrize("T,K", [(8, 5120), (16, 5120), (40, 5120), (72, 5120), (136, 5120), (65, 17408),
+                                 (70, 8224)])
+def test_quantize_act_chunk_pertoken(lib, pkg, orc, wl, T, K):
     x = wl.activations_normal(T, K, seed=2, outlier_frac=0.01)
     dx = dev(pkg, x)
     n = K // 32 * T
@@ -82,6 +88,29 @@ def test_quantize_act_chunk_pertoken(lib, pkg, orc, wl, T):
     assert as_.to_numpy(np.float32).tobytes() == os_.tobytes()
     assert np.array_equal(asum.to_numpy(np.int32), osm)
     assert at.to_numpy(np.float32).tobytes() == os_.reshape(K // 32, T)[0].tobytes()
+
+
+def test_chunk_staging_from_a_row_that_is_not_16_byte_aligned(lib, pkg, orc, wl):
+    """The wide kernels load 16 bytes per lane; rows that start 4 bytes off go to the kernels
+    that do not, with the same result."""
+    K, T = 256, 80
+    x = wl.activations_normal(T, K, seed=4, outlier_frac=0.01)
+    buf = pkg.DevBuf.from_numpy(np.concatenate([np.zeros(1, np.float32), x.reshape(-1), np.zeros(3, np.float32)]))
+    n = K // 32 * T
+    aq, as_, asum, at = pkg.DevBuf(n * 32), pkg.DevBuf(n * 4), pkg.DevBuf(n * 4), pkg.DevBuf(T * 4)
+    lib.qwn_x_quantize_act_chunk(buf.ptr + 4, K, T, aq.ptr, as_.ptr, asum.ptr)
+    lib.tq_sync()
+    oq, os_, osm = orc.quantize_act_chunk(x)
+    assert np.array_equal(aq.to_numpy(np.int8), oq)
+    assert as_.to_numpy(np.float32).tobytes() == os_.tobytes()
+    assert np.array_equal(asum.to_numpy(np.int32), osm)
+    lib.qwn_x_quantize_act_chunk_pertoken(buf.ptr + 4, K, T, aq.ptr, as_.ptr, asum.ptr, at.ptr)
+    lib.tq_sync()
+    oq, os_, osm = orc.quantize_act_chunk(x, per_token=True)
+    assert np.array_equal(aq.to_numpy(np.int8), oq)
+    assert as_.to_numpy(np.float32).tobytes() == os_.tobytes()
+    assert np.array_equal(asum.to_numpy(np.int32), osm)
+    assert lib.tq_last_error() == 0
 
 
 def test_silu_mul_quant_fused_equals_unfused_and_oracle(lib, pkg, orc):
@@ -544,7 +573,7 @@ def test_gemm_pertoken_tcgen05(lib, pkg, orc, wl, M, K, ksh, T, bf16):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("K,T", [(256, 8), (5120, 40), (128, 136)])
+@pytest.mark.parametrize("K,T", [(256, 8), (5120, 40), (128, 136), (5120, 72), (17408, 64), (192, 70)])
 def test_quantize_act_chunk_s4(lib, pkg, orc, wl, K, T):
     """W4A4 staging: packed int4 codes, scales and sums bit-identical to the oracle."""
     x = wl.activations_normal(T, K, seed=K + T, outlier_frac=0.01)
