@@ -609,6 +609,80 @@ quant_chunk_pertoken_cluster_kernel(const ClusterSrc src, int K, int T,
     }
 }
 
+// The single-row per-token staging (rowmax_partial_kernel + quant_s8_rowscale_kernel) in one
+// launch on a cluster of C CTAs: each CTA keeps K / C values of the row in registers, the
+// maxima meet through distributed shared memory, and each CTA writes its slice of the
+// prepared scratch: linear codes, the permuted tile (a lane's four codes are two even-k and
+// two odd-k neighbours there: two 2-byte stores), the scale in every K32 slot, K16 and K32 sums.
+template <bool SILU>
+__global__ void __launch_bounds__(256)
+quant_s8_rowscale_cluster_kernel(const float *__restrict__ x, const float *__restrict__ up,
+                                 float *__restrict__ hidden, int K, int8_t *__restrict__ q,
+                                 int8_t *__restrict__ qp, float *__restrict__ scale,
+                                 int32_t *__restrict__ sum16, int32_t *__restrict__ sum32) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ float wmax[8];
+    __shared__ float cmax[8];
+    const int C = gridDim.x, c = blockIdx.x;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n4s = (K / C) >> 2;                           // float4 per slice, a multiple of 8
+    const float4 *row4 = reinterpret_cast<const float4 *>(x) + (size_t)c * n4s;
+    float4 v[4];
+    float m = -INFINITY;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        const int i = tid + u * 256;
+        v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (i < n4s) {
+            v[u] = row4[i];
+            if (SILU) {
+                const float4 g = (reinterpret_cast<const float4 *>(up) + (size_t)c * n4s)[i];
+                v[u] = make_float4(silu_mul_f(v[u].x, g.x), silu_mul_f(v[u].y, g.y), silu_mul_f(v[u].z, g.z),
+                                   silu_mul_f(v[u].w, g.w));
+                (reinterpret_cast<float4 *>(hidden) + (size_t)c * n4s)[i] = v[u];
+            }
+            m = fmaxf(m, fmaxf(fmaxf(fabsf(v[u].x), fabsf(v[u].y)), fmaxf(fabsf(v[u].z), fabsf(v[u].w))));
+        }
+    }
+    m = warp_max(m);
+    if (lane == 0) wmax[warp] = m;
+    __syncthreads();
+    if (warp == 0) {
+        const float t = warp_max(lane < 8 ? wmax[lane] : -INFINITY);
+        if (lane < C) st_cluster_f32((uint32_t)__cvta_generic_to_shared(&cmax[c]), (uint32_t)lane, t);
+    }
+    cluster_sync_all();
+    float t = cmax[0];
+    for (int j = 1; j < C; ++j) t = fmaxf(t, cmax[j]);
+    const float s = (t > 0.0f) ? __fdiv_rn(t, 127.0f) : 1.0f;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        const int i = tid + u * 256;                 // float4 index in the slice; uniform per warp
+        if (i - lane >= n4s) break;
+        const int q0 = quantise_one(v[u].x, s), q1 = quantise_one(v[u].y, s);
+        const int q2 = quantise_one(v[u].z, s), q3 = quantise_one(v[u].w, s);
+        int sum = q0 + q1 + q2 + q3;
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);                  // K16 half: four lanes
+        const int other = __shfl_xor_sync(0xffffffffu, sum, 4);
+        if (i < n4s) {
+            const int gi = c * n4s + i;              // float4 index in the row
+            const int b = gi >> 3, j = gi & 7;       // K32 block, float4 inside it (k = 4j .. 4j+3)
+            reinterpret_cast<uint32_t *>(q)[gi] = (uint32_t)(q0 & 0xFF) | ((uint32_t)(q1 & 0xFF) << 8) |
+                                                  ((uint32_t)(q2 & 0xFF) << 16) | ((uint32_t)(q3 & 0xFF) << 24);
+            uint16_t *tile = reinterpret_cast<uint16_t *>(qp + (size_t)b * 32);
+            tile[j] = (uint16_t)((q0 & 0xFF) | ((q2 & 0xFF) << 8));          // permuted_pos(4j), (4j+2)
+            tile[8 + j] = (uint16_t)((q1 & 0xFF) | ((q3 & 0xFF) << 8));      // permuted_pos(4j+1), (4j+3)
+            if ((j & 3) == 0) sum16[b * 2 + (j >> 2)] = sum;
+            if (j == 0) {
+                scale[b] = s;
+                sum32[b] = sum + other;
+            }
+        }
+    }
+}
+
 // K32 code sums of already staged codes (debug helper for the int32 dump).
 __global__ void code_sums_kernel(const int8_t *__restrict__ aq, size_t blocks,
                                  int32_t *__restrict__ asum) {
@@ -668,6 +742,27 @@ void launch_quant_s8_pertoken(const float *d_x, const float *d_up, float *d_hidd
                               int8_t *d_q, int8_t *d_qp, float *d_scale, int32_t *d_sum16,
                               int32_t *d_sum32, float *d_partial, bool silu) {
     if (K < 32) return;
+    // one launch on a cluster of 8, 4 or 2 CTAs when the row divides into K32-aligned slices of
+    // at most 1024 values (one float4 per thread; on longer rows eight SMs are too few and
+    // the two launches below, 68 CTAs at K = 17408, measured faster) and the buffers take
+    // vector accesses
+    const uintptr_t align16 = reinterpret_cast<uintptr_t>(d_x) | reinterpret_cast<uintptr_t>(d_up) |
+                              reinterpret_cast<uintptr_t>(d_hidden);
+    if ((align16 & 15) == 0 && (reinterpret_cast<uintptr_t>(d_q) & 3) == 0 &&
+        (reinterpret_cast<uintptr_t>(d_qp) & 1) == 0) {
+        for (unsigned c = 8; c >= 2; c >>= 1) {
+            if (K % (32 * (int)c) || K / (int)c > 1024) continue;
+            if (silu)
+                launch_pdl_cluster(quant_s8_rowscale_cluster_kernel<true>, dim3(c), dim3(256), c, d_x, d_up,
+                                   d_hidden, K, d_q, d_qp, d_scale, d_sum16, d_sum32);
+            else
+                launch_pdl_cluster(quant_s8_rowscale_cluster_kernel<false>, dim3(c), dim3(256), c, d_x,
+                                   (const float *)nullptr, (float *)nullptr, K, d_q, d_qp, d_scale, d_sum16,
+                                   d_sum32);
+            TQ_LAUNCH_CHECK("quant_s8_rowscale_cluster_kernel");
+            return;
+        }
+    }
     const int nblk = (K + 255) / 256;
     if (silu)
         launch_pdl(rowmax_partial_kernel<true>, dim3(nblk), dim3(256), 0, d_x, d_up, d_hidden, K, d_partial);

@@ -113,6 +113,49 @@ def test_chunk_staging_from_a_row_that_is_not_16_byte_aligned(lib, pkg, orc, wl)
     assert lib.tq_last_error() == 0
 
 
+# a cluster of 8 / 4 / 2 CTAs where the row divides into K32-aligned slices of at most 1024
+# values (one launch), two launches elsewhere (352, 17408). Rows stay below 32768 values: a
+# later test needs the library's staging scratch to be smaller than that.
+@pytest.mark.parametrize("K", [64, 128, 352, 5120, 8192, 17408])
+@pytest.mark.parametrize("silu", [False, True])
+def test_single_row_pertoken_staging_and_gemv(lib, pkg, orc, wl, K, silu):
+    """One scale for the whole row: codes, scale slots and K16 sums against the oracle; the
+    permuted tile and the K32 sums through the GEMV that reads them."""
+    rng = np.random.default_rng(K + silu)
+    x = rng.standard_normal(K).astype(np.float32)
+    x[:32] = 0.0
+    x[K // 2] = -37.5
+    if silu:
+        up = rng.standard_normal(K).astype(np.float32)
+        dg, du, hid = dev(pkg, x), dev(pkg, up), pkg.DevBuf(K * 4)
+        hid.fill(0xFF)
+        lib.qwn_x_silu_mul_quant_pertoken(hid.ptr, dg.ptr, du.ptr, K)
+        row = orc.silu_mul(x, up)
+        lib.tq_sync()
+        assert hid.to_numpy(np.float32).tobytes() == row.tobytes()
+    else:
+        dx = dev(pkg, x)
+        lib.qwn_x_prepare_gemv_act_s8_pertoken(dx.ptr, K)
+        row = x
+    q, s, sm = prepared(lib, pkg, K)
+    oq, os_, _ = orc.quantize_act_chunk(row[None, :], per_token=True)
+    osm = oq.astype(np.int32).reshape(-1, 16).sum(axis=1).astype(np.int32)
+    assert np.array_equal(q, oq.reshape(-1))
+    assert s.tobytes() == os_.tobytes()
+    assert np.array_equal(sm, osm)
+    if K % 128 == 0:
+        M = 32
+        codes, scales = wl.random_packed_weight(M, K, seed=K, ksh=0)
+        w = pkg.PackedWeight(codes, scales, M, K)
+        y = pkg.DevBuf(M * 4)
+        y.fill(0xFF)
+        assert lib.qwn_x_gemv_w4a8_prepared(w.ref, y.ptr, None) == 0
+        lib.tq_sync()
+        _, want = orc.gemv_w4a8(codes, scales, M, K, 0, oq.reshape(-1), os_.reshape(-1), osm, fma=1)
+        assert y.to_numpy(np.float32).tobytes() == want.tobytes()
+    assert lib.tq_last_error() == 0
+
+
 def test_silu_mul_quant_fused_equals_unfused_and_oracle(lib, pkg, orc):
     rng = np.random.default_rng(5)
     K = 17408
