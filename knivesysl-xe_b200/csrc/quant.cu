@@ -852,10 +852,11 @@ void launch_quant_chunk_s4(const float *d_x, int K, int T, uint8_t *d_aq4, float
 
 // Decode batches: a cluster of 8, 4 or 2 CTAs per token when the row divides into K32-aligned
 // slices of at most 4096 values. False: the shape is not covered, nothing was launched.
+constexpr int kClusterMaxT = 64;     // above, the per-token and wide kernels measured faster
 template <int SRC>
 bool launch_quant_cluster(const ClusterSrc &src, int K, int T, int8_t *d_aq, float *d_as, int32_t *d_asum,
                           float *d_as_tok, const SyncArgs &sa) {
-    if (T > 32) return false;
+    if (T > kClusterMaxT) return false;
     for (unsigned c = 8; c >= 2; c >>= 1) {
         if (K % (32 * (int)c) || K / (int)c > 4096) continue;
         launch_pdl_cluster(quant_chunk_pertoken_cluster_kernel<SRC>, dim3(c, T), dim3(256), c, src, K, T, d_aq,

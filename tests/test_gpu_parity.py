@@ -72,7 +72,7 @@ def test_quantize_act_chunk(lib, pkg, orc, K, T, exceptional):
     assert np.array_equal(asum.to_numpy(np.int32), osm)
 
 
-# one fused launch up to 32 tokens; above, one CTA per token with the row in registers (rows up
+# one fused launch up to 64 tokens; above, one CTA per token with the row in registers (rows up
 # to 8192 values) or the row maxima and then the wide kernel
 @pytest.mark.parametrize("T,K", [(8, 5120), (16, 5120), (40, 5120), (72, 5120), (136, 5120), (65, 17408),
                                  (70, 8224)])
@@ -990,7 +990,7 @@ def test_gemm_cases_on_the_tcgen05_decode_kernel():
 # (5120, 8): clusters of 8 CTAs per token; (1280, 16): clusters of 8 over short slices;
 # (96, 8): no K32-aligned split into 2, 4 or 8 - the two separate launches
 @pytest.mark.gpu
-@pytest.mark.parametrize("H,T", [(5120, 8), (1280, 16), (17408, 8), (96, 8), (5120, 40)])
+@pytest.mark.parametrize("H,T", [(5120, 8), (1280, 16), (17408, 8), (96, 8), (5120, 40), (5120, 64), (5120, 72)])
 def test_rmsnorm_quant_chunk_pertoken(lib, pkg, orc, H, T):
     rng = np.random.default_rng(H + T)
     x = (rng.standard_normal((T, H)) * 3).astype(np.float32)
@@ -1015,7 +1015,7 @@ def test_rmsnorm_quant_chunk_pertoken(lib, pkg, orc, H, T):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("K,T", [(17408, 8), (8704, 8), (160, 8), (5120, 40)])
+@pytest.mark.parametrize("K,T", [(17408, 8), (8704, 8), (160, 8), (5120, 40), (17408, 64), (17408, 66)])
 def test_silu_mul_quant_chunk_pertoken(lib, pkg, orc, K, T):
     rng = np.random.default_rng(K + T)
     g = (rng.standard_normal((T, K)) * 2).astype(np.float32)
