@@ -17,34 +17,37 @@
 // Mapping. Weights are the M side of the MMA (128 output rows = 128 TMEM lanes), tokens the
 // N side (128 per CTA tile), a k-tile (K = 32) is two K = 16 instructions, so one accumulator
 // read-out yields exactly the per-k-tile dots the reference promotes. The K loop advances in
-// steps of two k-tiles. A CTA (11 warps, one per SM, persistent over tiles) runs three roles
-// connected by mbarriers (4 step slots in shared memory, 4 accumulator buffers in TMEM):
-//  * workers (8 warps). Each expands weights and promotes accumulators, in one loop:
-//    - expansion, 3 steps ahead of the promote: a warp owns one packed row group (16 rows),
-//      lane = (row, k-tile of the step); the lane's 16 packed bytes were loaded into
-//      registers two steps earlier (and prefetched into L2 eight steps before that); each
-//      32-bit word (8 codes) becomes 8 fp16 values (shift, logic ops that isolate two nibbles
-//      and set the exponent of 1024 with the sign bit flipped, one packed subtract of 1032),
-//      stored as the four 16-byte K-chunks of the row in the canonical no-swizzle K-major
-//      core-matrix layout (inside a chunk the codes sit in the order 0,4,1,5,2,6,3,7: any
-//      fixed permutation of k inside an instruction is exact for a dot, and the activation
-//      image uses the same one);
-//    - promote: thread = weight row x 64 tokens; tcgen05.ld of the thread's 64 columns is
-//      started before the expansion and waited for after it, then per token
-//      f = fma(-z, asum, d) (exact; only in the kernel variant for weights with zero points),
-//      acc = fma(f, ws*as, acc); 64 fp32 accumulators stay in registers for the whole K loop
-//      and are stored at the end (coalesced over rows).
-//    With two or three warps per scheduler the loop's time is close to its instruction count
-//    times a dependent-issue latency, so it is kept short: ring positions are masks of one
-//    step counter, arrivals are predicated instructions, the accumulator barrier of the next
-//    group is tested while this group's load is in flight.
-//  * one thread starts the bulk (TMA) copies of the step's activation images (per k-tile 8 KiB
-//    of fp16 codes and 1 KiB of {as, (float)asum} per token, prepared by a pre-pass in the
-//    operand layout);
+// steps of two k-tiles. Both operands come from images that pre-passes write in the operand
+// layout (canonical no-swizzle K-major core matrices): the activation image (fp16 codes plus
+// as and (float)asum per token) and the weight image - every 4-bit code expanded to fp16 once
+// per call (shift, one logic op that isolates two nibbles and sets the exponent of 1024 with
+// the sign bit flipped, one packed subtract of 1032; inside a 16-byte K-chunk the codes sit in
+// the order 0,4,1,5,2,6,3,7: any fixed permutation of k inside an instruction is exact for a
+// dot, and the activation image uses the same one). The weight image costs 4 bytes per code of
+// scratch, written and read once per call (3 % of the call); with it the GEMM's CUDA cores
+// only promote. Tiles are walked token block fastest, so the CTAs that run together share
+// a few row blocks of the weight image while the whole activation image stays in L2.
+//
+// A CTA (19 warps, one per SM, persistent over tiles) runs three roles connected by
+// mbarriers (6 step slots in shared memory, 4 accumulator buffers in TMEM):
+//  * one thread starts the bulk (TMA) copies of a step: 16 KiB of weights and 18 KiB of
+//    activations, each contiguous in its image;
 //  * two MMA threads (in two warps, steps in turn): two tcgen05.mma (M=128, N=128, K=16) per
 //    k-tile into accumulator buffer b (the first MMA of a promote group overwrites it);
 //    tcgen05.commit signals the workers. The single-thread roles wait with a suspend-time
-//    hint: back-to-back polling took a fifth of the schedulers' issue slots.
+//    hint: back-to-back polling took a fifth of the schedulers' issue slots;
+//  * workers (16 warps): thread = weight row x 32 tokens. Per promote group the thread's 32
+//    accumulator columns are read with two 16-column tcgen05.ld, then per token
+//    f = fma(-z, asum, d) (exact; only in the kernel variant for weights with zero points),
+//    acc = fma(f, ws*as, acc); 32 fp32 accumulators stay in registers for the whole K loop
+//    and are stored at the end (coalesced over rows). The loads of the next group are issued
+//    behind the fma of this one (first half behind the first half's fma, into the registers
+//    just consumed), when that group's barrier has already completed - it nearly always has -
+//    so no load latency is exposed.
+// What bounds it: the workers' per-group sequence (barrier test, loads, fences, arrivals; about
+// 120 instructions besides the fma) - a trace shows the copy and MMA threads waiting on the
+// workers, and neither halving the copied bytes, nor a third MMA thread, nor removing the fma
+// changes the time by more than a tenth.
 //
 // Every mbarrier wait is bounded; on expiry the kernel records a status word, stops
 // issuing work, still frees its TMEM and returns.
@@ -62,30 +65,27 @@ namespace {
 constexpr int kTM = 128;                 // weight rows per tile (TMEM lanes)
 constexpr int kTN = 128;                 // tokens per tile (accumulator columns)
 constexpr int kNB = 4;                   // accumulator buffers in TMEM (4 x 128 columns)
-constexpr int kSS = 4;                   // step slots in shared memory (two k-tile slots each)
+constexpr int kSS = 6;                   // step slots in shared memory (two k-tile slots each)
 constexpr int kABytes = kTM * 64;        // expanded fp16 weights of one k-tile
 constexpr int kBBytes = kTN * 64;        // fp16 activations of one k-tile
 constexpr int kSBytes = kTN * 8;         // as[128] then (float)asum[128] of the tile's tokens
-constexpr int kSlotBytes = kABytes + kBBytes + kSBytes;
-constexpr int kStepBytes = 2 * kSlotBytes;
-// Eleven warps: at most three share a scheduler, so a thread may hold up to 168 registers
-// (a worker's 64 accumulators and two 32-column TMEM loads do not fit the 128 that a fourth
-// warp per scheduler would leave).
-constexpr int kWorkWarps = 8;
+constexpr int kImgBytes = kBBytes + kSBytes;   // activation image of one (k-tile, token block)
+// a step slot: the fp16 weights of its two k-tiles, then their two activation images - the
+// order both lie in memory, so a step is two bulk copies
+constexpr int kStepBytes = 2 * kABytes + 2 * kImgBytes;
+// Nineteen warps: five share a scheduler, whose register file then leaves a thread 96
+// registers (32 accumulators and the 32 loaded columns fit). Eight workers of 64 tokens at 168
+// registers measured the same in per-token mode and 9 % slower in the reference's arithmetic.
+constexpr int kWorkWarps = 16;
+constexpr int kWT = kTN / (kWorkWarps / 4);      // tokens of a tile that one worker thread promotes
+constexpr int kMaxRegs = 96;
 // Two MMA-issuing threads take the promote groups in turn: waits, four tcgen05.mma and the
 // tcgen05.commit of a K64 group cost the issuing thread about 700 clocks (every tcgen05
 // instruction 80 to 110, whatever the MMA's width), more than a group may take.
 constexpr int kMmaWarps = 2;
 constexpr int kThreads = (kWorkWarps + 1 + kMmaWarps) * 32;    // + the warp that starts the image copies
-constexpr int kAhead = 3;                 // steps (of two k-tiles) the expansion runs ahead of the
-                                          // promote: a slot is rewritten only after the step that
-                                          // used it was promoted by the same warp, kAhead <= kSS - 1
 constexpr uint32_t kNapNs = 2000;         // suspend-time hint of the single-thread roles' waits
-constexpr int kLoadAhead = 2;             // steps the packed bytes are loaded (into registers) ahead
-                                          // of their expansion
-constexpr int kL2Ahead = 8;               // steps their lines are prefetched into L2 ahead of that
-static_assert(kAhead <= kSS - 1, "a slot must have been promoted before it is rewritten");
-static_assert((kSS & (kSS - 1)) == 0 && (kNB & (kNB - 1)) == 0, "ring positions are masks of the step counter");
+static_assert((kNB & (kNB - 1)) == 0, "accumulator buffers are a mask of the group counter");
 constexpr int kSmemBytes = kSS * kStepBytes;   // > half an SM's shared
                                          // memory: one CTA per SM, which the 512-column TMEM
                                          // allocation requires
@@ -96,9 +96,9 @@ constexpr uint32_t kLboH = 128, kSboH = 512;
 constexpr uint32_t kIdesc = idesc_f16(kTM, kTN);
 
 struct TcParams {
-    const uint8_t *codes;
+    const uint8_t *wimg;     // per (128-row block, k-tile): kABytes of fp16 weights in operand layout
     const uint16_t *scales;
-    const uint8_t *img;      // per (k-tile, 128-token block): kBBytes of fp16 codes as
+    const uint8_t *img;      // per (128-token block, k-tile): kBBytes of fp16 codes as
                              // [16 token groups][4 K-chunks][8 tokens][16 B], then kSBytes:
                              // as[128], (float)asum[128]
     void *y;
@@ -161,7 +161,7 @@ gemm_tc_prepass_kernel(const int8_t *__restrict__ aq, const float *__restrict__ 
 #pragma unroll
             for (int k = 0; k < 32; ++k) v[k] = (int)(int8_t)(w[k >> 2] >> ((k & 3) * 8));
         }
-        uint8_t *blk = img + ((size_t)kt * (Tpad / kTN) + tok / kTN) * (kBBytes + kSBytes);
+        uint8_t *blk = img + ((size_t)(tok / kTN) * Kt + kt) * kImgBytes;
         const int tl = tok % kTN;
         store_token_chunks(blk, tl, v);
         float *sa = reinterpret_cast<float *>(blk + kBBytes);
@@ -195,7 +195,7 @@ gemm_tc_prepass_s4_kernel(const uint8_t *__restrict__ aq4, const float *__restri
 #pragma unroll
             for (int k = 0; k < 32; ++k) v[k] = ((int)(w[k >> 3] << (28 - (k & 7) * 4))) >> 28;
         }
-        uint8_t *blk = img + ((size_t)kt * (Tpad / kTN) + tok / kTN) * (kBBytes + kSBytes);
+        uint8_t *blk = img + ((size_t)(tok / kTN) * Kt + kt) * kImgBytes;
         const int tl = tok % kTN;
         store_token_chunks(blk, tl, v);
         float *sa = reinterpret_cast<float *>(blk + kBBytes);
@@ -204,8 +204,6 @@ gemm_tc_prepass_s4_kernel(const uint8_t *__restrict__ aq4, const float *__restri
         sa[kTN + tl] = has ? (float)asum4[(size_t)kg * T + tok] : 0.0f;
     }
 }
-
-constexpr int kWaitMma = 21, kWaitEpi = 22, kWaitProd = 23;   // status codes of failed waits
 
 // Eight two's-complement nibbles of w (nibble i = code k = i) -> eight fp16 values, as four
 // words holding the codes (0,4), (1,5), (2,6), (3,7). Per word: the two nibbles land in the
@@ -224,22 +222,56 @@ __device__ __forceinline__ uint4 nib8_to_h8(uint32_t w, uint32_t mask, uint32_t 
     return make_uint4(r[0], r[1], r[2], r[3]);
 }
 
+// Weight pre-pass: packed codes [row group][k-tile][16 rows][16 B] -> per (128-row block,
+// k-tile) the kABytes of fp16 values in the operand layout (row groups of 8 are kSboH apart,
+// a row's four 16-byte K-chunks kLboH apart), so that a tile's weights of a k-tile are one bulk
+// copy. A thread expands one row of one k-tile; 8 consecutive lanes write 128 contiguous bytes
+// per chunk. 4 bytes out per code: 178 MB for 17408 x 5120, written and read once per call.
+__global__ void __launch_bounds__(256)
+gemm_tc_expand_kernel(const uint8_t *__restrict__ codes, int M, int Kt, uint8_t *__restrict__ wimg) {
+    pdl_trigger();
+    const uint32_t mask = 0x000F000Fu, bias = 0x64086408u;
+    const size_t n = (size_t)M * Kt;
+    for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < n; i += (size_t)gridDim.x * 256) {
+        const int kt = (int)(i / M), m = (int)(i % M);
+        const uint4 c4 = ldg_stream_v4(codes + ((size_t)(m >> 4) * Kt + kt) * 256 + (m & 15) * 16);
+        const int r = m & (kTM - 1);
+        uint8_t *dst = wimg + ((size_t)(m / kTM) * Kt + kt) * kABytes + (r >> 3) * kSboH + (r & 7) * 16;
+        *reinterpret_cast<uint4 *>(dst) = nib8_to_h8(c4.x, mask, bias);                 // k 0..7
+        *reinterpret_cast<uint4 *>(dst + kLboH) = nib8_to_h8(c4.y, mask, bias);         // k 8..15
+        *reinterpret_cast<uint4 *>(dst + 2 * kLboH) = nib8_to_h8(c4.z, mask, bias);     // k 16..23
+        *reinterpret_cast<uint4 *>(dst + 3 * kLboH) = nib8_to_h8(c4.w, mask, bias);     // k 24..31
+    }
+}
+
+constexpr int kWaitMma = 21, kWaitEpi = 22, kWaitProd = 23;   // status codes of failed waits
+
+#ifdef TQ_TC_TRACE
+__device__ long long g_tc_trace[20 * 16];
+#define TCT_DECL long long tct_[12] = {}; long long tct_t = clock64();
+#define TCT(i) { const long long t_ = clock64(); tct_[i] += t_ - tct_t; tct_t = t_; }
+#define TCT_CNT(i, v) tct_[i] += (v);
+#define TCT_OUT(slot) if (blockIdx.x == 0 && lane == 0) { for (int i_ = 0; i_ < 12; ++i_) g_tc_trace[(slot) * 16 + i_] = tct_[i_]; }
+#else
+#define TCT_DECL
+#define TCT(i)
+#define TCT_CNT(i, v)
+#define TCT_OUT(slot)
+#endif
+
 // GW = k-tiles accumulated in TMEM before one fp32 promote (1: the reference's arithmetic with
 // a scale per (token, K32); 2: K64 weight groups with per-token activation scales, or - not
 // PERTOK - with one activation scale per (token, K64): the W4A4 arithmetic). PERTOK:
 // the activation scale is applied once at the end (y = acc * as_tok).
 //
 // The K loop advances in steps of two k-tiles (K is a multiple of 64); step n of the CTA
-// (counted across its tiles) uses step slot n % kSS. A worker warp owns 16 weight rows (one
-// packed row group, so its bytes of consecutive k-tiles are contiguous in memory) and 32
-// TMEM lanes; lane l expands row (l & 15) of k-tile (l >> 4) of a step, kAhead steps ahead
-// of the step it promotes. The loop is kept lean on purpose: with two or three warps per
-// scheduler its time is its instruction count times a dependent-issue latency.
+// (counted across its tiles) uses step slot n % kSS. A worker warp owns 32 TMEM lanes (rows)
+// and 32 of the tile's tokens.
 //
 // ZP: the kernel applies the zero-point term f = d - z * asum. Both variants are launched;
 // the one that does not match the pre-pass's flag returns at once.
 template <int GW, bool PERTOK, bool ZP>
-__global__ void __maxnreg__(168) gemm_w4a8_tc_kernel(const TcParams p) {
+__global__ void __maxnreg__(kMaxRegs) gemm_w4a8_tc_kernel(const TcParams p) {
     pdl_trigger();
     pdl_wait();      // everything below reads what earlier kernels wrote (flag, images)
     if ((*p.zp_flag != 0) != ZP) return;
@@ -255,7 +287,7 @@ __global__ void __maxnreg__(168) gemm_w4a8_tc_kernel(const TcParams p) {
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kSS; ++s) {
-            mbar_init(full0 + s * 8, kWorkWarps + 1);    // every worker warp's rows + the image copies
+            mbar_init(full0 + s * 8, 1);                 // the copy thread's arrive with the step's byte count
             mbar_init(empty0 + s * 8, kWorkWarps);       // one arrive per worker warp
         }
         for (int b = 0; b < kNB; ++b) {
@@ -280,6 +312,7 @@ __global__ void __maxnreg__(168) gemm_w4a8_tc_kernel(const TcParams p) {
     const int ntiles = row_blocks * tok_blocks;
     const int my_tiles = (ntiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
     const int n_total = my_tiles * spt;                  // steps of this CTA
+    const int g_total = (GW == 2) ? n_total : 2 * n_total;      // promote groups of this CTA
 
     // A wait that gives up when another role already has: the flag is read on the slow path only.
     auto wait_on = [&](uint32_t bar, uint32_t parity, int code, uint32_t suspend_ns = 0) -> bool {
@@ -291,86 +324,43 @@ __global__ void __maxnreg__(168) gemm_w4a8_tc_kernel(const TcParams p) {
     };
 
     if (warp < kWorkWarps) {
-        // ====================== workers: expand weights, promote accumulators =============
-        const int erow = lane & 15, ehalf = lane >> 4;
-        const int r16 = 16 * warp + erow;                 // the row this lane expands
-        // this lane's four chunks inside a step slot: k-tile ehalf, row r16
-        const uint32_t a_off = (uint32_t)(ehalf * kSlotBytes + (r16 >> 3) * kSboH + (r16 & 7) * 16);
-        uint32_t c_mask, c_bias;                           // see nib8_to_h8
-        asm volatile("mov.b32 %0, 0x000F000F;" : "=r"(c_mask));
-        asm volatile("mov.b32 %0, 0x64086408;" : "=r"(c_bias));
-
-        // ---- load stream (step f_n): this lane's 16 packed bytes of a step, kLoadAhead steps
-        // ahead of their expansion, in registers; the 128-byte lines are pulled into L2
-        // kL2Ahead steps earlier still. A lane's bytes of consecutive steps are 512 bytes apart.
-        auto tile_src = [&](int ti) {
-            const int rb = ((int)blockIdx.x + ti * (int)gridDim.x) % row_blocks;
-            return p.codes + ((size_t)(rb * (kTM / 16) + warp) * Kt + ehalf) * 256 + erow * 16;
-        };
-        int f_n = 0, f_ti = 0, f_left = spt;
-        const uint8_t *f_src = tile_src(0);
-        uint4 pre[kLoadAhead] = {};
-        auto load_next = [&](uint4 &dst) {
-            if (f_n < n_total) {
-                dst = ldg_stream_v4(f_src);
-                // only inside the tile's own run of bytes
-                if (f_left > kL2Ahead && (lane & 7) == 0) prefetch_l2(f_src + kL2Ahead * 512);
-                f_src += 512;
-                if (--f_left == 0) {
-                    f_left = spt;
-                    if (++f_ti < my_tiles) f_src = tile_src(f_ti);
-                }
-            }
-            ++f_n;
-        };
-        // ---- expansion stream (step e_n): registers -> fp16 A operands of the step's slot
-        int e_n = 0;
-        auto expand = [&]() {
-            const uint4 c4 = pre[0];
-#pragma unroll
-            for (int i = 0; i + 1 < kLoadAhead; ++i) pre[i] = pre[i + 1];
-            load_next(pre[kLoadAhead - 1]);
-            if (e_n < n_total) {
-                unsigned char *dst = smem + (size_t)(e_n & (kSS - 1)) * kStepBytes + a_off;
-                *reinterpret_cast<uint4 *>(dst) = nib8_to_h8(c4.x, c_mask, c_bias);                 // k 0..7
-                *reinterpret_cast<uint4 *>(dst + kLboH) = nib8_to_h8(c4.y, c_mask, c_bias);         // k 8..15
-                *reinterpret_cast<uint4 *>(dst + 2 * kLboH) = nib8_to_h8(c4.z, c_mask, c_bias);     // k 16..23
-                *reinterpret_cast<uint4 *>(dst + 3 * kLboH) = nib8_to_h8(c4.w, c_mask, c_bias);     // k 24..31
-                fence_proxy_async_smem();   // generic-proxy stores -> visible to the MMA
-                __syncwarp();
-                mbar_arrive_if(full0 + (e_n & (kSS - 1)) * 8, lane == 0);
-            }
-            ++e_n;
-        };
-#pragma unroll
-        for (int i = 0; i < kLoadAhead; ++i) load_next(pre[i]);
-#pragma unroll 1
-        for (int i = 0; i < kAhead; ++i) expand();
-
-        // ---- promote stream
-        const int q4 = warp & 3, chalf = (warp >> 2) * 64;
+        // ====================== workers: promote the accumulators ==========================
+        const int q4 = warp & 3, chalf = (warp >> 2) * kWT;   // lane quarter, first token
         const int rloc = q4 * 32 + lane;                  // row inside the tile = TMEM lane
         const uint32_t lane_base = tmem_base + ((uint32_t)(q4 * 32) << 16) + chalf;
-        // activation scales of this thread's 64 tokens inside a k-tile slot (as four-token
+        // activation scales of this thread's tokens inside a step slot (as four-token
         // vectors: [0, 16) scales, [32, 48) code sums)
-        const unsigned char *sv_base = smem + kABytes + kBBytes + chalf * 4;
+        const unsigned char *sv_base = smem + 2 * kABytes + kBBytes + chalf * 4;
         int n = 0;                                        // step counter across the CTA's tiles
         bool alive = true;
-        uint32_t acc_ready = 0;
+        // The thread's 64 columns of a group's accumulator, as two 32-column loads. `loaded`:
+        // the loads of the group about to be promoted were already issued, behind the
+        // promotes of the group before it (the load of the second half behind the first
+        // half's fma, and so on around the loop), so that no load's latency is exposed.
+        uint32_t d[kWT];
+        uint32_t (&dlo)[kWT / 2] = *reinterpret_cast<uint32_t (*)[kWT / 2]>(&d[0]);
+        uint32_t (&dhi)[kWT / 2] = *reinterpret_cast<uint32_t (*)[kWT / 2]>(&d[kWT / 2]);
+        auto load_half = [&](uint32_t taddr, uint32_t (&v)[kWT / 2]) {
+            if constexpr (kWT == 64) tmem_ld32(taddr, *reinterpret_cast<uint32_t (*)[32]>(&v[0]));
+            else tmem_ld16(taddr, *reinterpret_cast<uint32_t (*)[16]>(&v[0]));
+        };
+        bool loaded = false;
+        TCT_DECL
 
         for (int ti = 0; ti < my_tiles && alive; ++ti) {
             const int tile = (int)blockIdx.x + ti * (int)gridDim.x;
-            const int rb = tile % row_blocks, tb = tile / row_blocks;
+            const int tb = tile % tok_blocks, rb = tile / tok_blocks;
             const int row = rb * kTM + rloc;
             const uint16_t *sc = p.scales + ((size_t)(row >> 4) * Ktg) * 16 + (row & 15);
-            float acc[64];
+            float acc[kWT];
 #pragma unroll
-            for (int i = 0; i < 64; ++i) acc[i] = 0.0f;
+            for (int i = 0; i < kWT; ++i) acc[i] = 0.0f;
             uint32_t scw = __ldg(sc);
 #pragma unroll 1
             for (int s = 0; s < spt; ++s, ++n) {
 #pragma unroll
                 for (int g = 0; g < (GW == 2 ? 1 : 2); ++g) {
+                    TCT(7)
                     const int kt = 2 * s + g;              // first k-tile of the group
                     const int ig = (GW == 2) ? n : 2 * n + g;      // group counter of the CTA
                     const int b = ig & (kNB - 1);
@@ -380,42 +370,29 @@ __global__ void __maxnreg__(168) gemm_w4a8_tc_kernel(const TcParams p) {
                     if (kt + GW < Kt) scw = __ldg(sc + (size_t)((kt + GW) >> p.ksh) * 16);
                     const f32x2 ws2 = pack2(ws, ws);
                     const float nzf = (float)(-zp);
-                    // acc_ready: the barrier was already tested, with the previous group's
-                    // load in flight (the test's answer takes about a hundred clocks)
-                    if (!__all_sync(0xffffffffu,
-                                    acc_ready || wait_on(acc0 + b * 8, (uint32_t)(ig / kNB) & 1u, kWaitEpi))) {
-                        alive = false;
-                        break;
+                    TCT(0)
+                    TCT_CNT(8, loaded ? 1 : 0) TCT_CNT(9, 1)
+                    if (!loaded) {
+                        if (!__all_sync(0xffffffffu, wait_on(acc0 + b * 8, (uint32_t)(ig / kNB) & 1u, kWaitEpi))) {
+                            alive = false;
+                            break;
+                        }
+                        tc_fence_after();
+                        // the accumulator holds (float)d of the group (the group's first MMA
+                        // overwrites it): nothing has to be converted or stored back
+                        load_half(lane_base + b * kTN, dlo);
+                        load_half(lane_base + b * kTN + kWT / 2, dhi);
                     }
-                    tc_fence_after();
-                    // Two 32-column loads of the thread's share of the accumulator: it holds
-                    // (float)d of the group (the group's first MMA overwrites it), so nothing has
-                    // to be converted or stored back. The loads are in flight while the warp
-                    // expands the weights of a later step (promoting first and expanding
-                    // afterwards, with the load's latency exposed, measured 1.28x slower).
-                    // A group that expands issues the second load only after the expansion,
-                    // behind the first half's promotes: 32 fewer live registers while expanding
-                    // saves more instructions than the shorter cover costs (1.07x faster).
-                    // Exact mode on K32 groups measured 1.13x slower so and keeps both loads
-                    // ahead of the expansion.
-                    const bool kStagger = (g == 0) && (GW == 2 || PERTOK);
-                    uint32_t d[64];
-                    {
-                        uint32_t (&dlo)[32] = *reinterpret_cast<uint32_t (*)[32]>(&d[0]);
-                        uint32_t (&dhi)[32] = *reinterpret_cast<uint32_t (*)[32]>(&d[32]);
-                        tmem_ld32(lane_base + b * kTN, dlo);
-                        if (!kStagger) tmem_ld32(lane_base + b * kTN + 32, dhi);
-                    }
-                    {
-                        const int ign = ig + 1;            // the CTA's next group, also across tiles
-                        acc_ready = mbar_test_wait(acc0 + (ign & (kNB - 1)) * 8, (uint32_t)(ign / kNB) & 1u);
-                    }
-                    if (g == 0) expand();                  // kAhead steps ahead
+                    TCT(1)
+                    // the CTA's next group (also across tiles): is its accumulator complete?
+                    const int ign = ig + 1, bn = ign & (kNB - 1);
+                    const bool next = ign < g_total &&
+                                      __all_sync(0xffffffffu, mbar_test_wait(acc0 + bn * 8, (uint32_t)(ign / kNB) & 1u));
                     const ulonglong2 *sv = reinterpret_cast<const ulonglong2 *>(
-                        sv_base + (size_t)((n & (kSS - 1)) * 2 + g) * kSlotBytes);
+                        sv_base + (size_t)(n % kSS) * kStepBytes + g * kImgBytes);
                     // second k-tile of a K64 group: only its code sums are needed
                     const ulonglong2 *sv1 = reinterpret_cast<const ulonglong2 *>(
-                        sv_base + (size_t)((n & (kSS - 1)) * 2 + 1) * kSlotBytes);
+                        sv_base + (size_t)(n % kSS) * kStepBytes + kImgBytes);
                     // symmetric weights need no zero-point term at all (the weights enter the
                     // MMA as true signed values): ZP is a compile-time choice, a test inside the
                     // unrolled loop would split it into one basic block per token group
@@ -451,32 +428,36 @@ __global__ void __maxnreg__(168) gemm_w4a8_tc_kernel(const TcParams p) {
                             for (int i = 0; i < 4; ++i) acc[4 * j + i] = fmaf(f[i], w[i], acc[4 * j + i]);
                         }
                     };
+                    TCT(2)
                     tmem_wait_ld_all();
-                    if (kStagger) {
-                        uint32_t (&dhi)[32] = *reinterpret_cast<uint32_t (*)[32]>(&d[32]);
-                        tmem_ld32(lane_base + b * kTN + 32, dhi);
-                        promote(0, 8);
-                        tmem_wait_ld_all();
-                        promote(8, 16);
-                    } else {
-                        promote(0, 16);
+                    TCT(3)
+                    promote(0, kWT / 8);
+                    if (next) {
+                        tc_fence_after();
+                        load_half(lane_base + bn * kTN, dlo);          // into the registers just consumed
                     }
+                    promote(kWT / 8, kWT / 4);
+                    if (next) load_half(lane_base + bn * kTN + kWT / 2, dhi);
+                    loaded = next;
+                    TCT(4)
                     tc_fence_before();
                     __syncwarp();
+                    TCT(5)
                     // one instruction, two barriers: lane 0 tells the MMA that it may overwrite
                     // the buffer, lane 1 (after the step's last group) the copy thread that the
                     // slot's images may be replaced
                     if (g == (GW == 2 ? 0 : 1))
-                        mbar_arrive_if(lane == 0 ? accempty0 + b * 8 : empty0 + (n & (kSS - 1)) * 8, lane < 2);
+                        mbar_arrive_if(lane == 0 ? accempty0 + b * 8 : empty0 + (n % kSS) * 8, lane < 2);
                     else
                         mbar_arrive_if(accempty0 + b * 8, lane == 0);
+                    TCT(6)
                 }
                 if (!alive) break;
             }
             if (!alive) break;
-            // store: thread = row, 64 tokens; rows are contiguous in y, so a warp writes 128 B
+            // store: thread = row, its tokens; rows are contiguous in y, so a warp writes 128 B
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
+            for (int i = 0; i < kWT / 2; ++i) {
                 float v0 = acc[2 * i], v1 = acc[2 * i + 1];
                 const int tok = tb * kTN + chalf + 2 * i;
                 if (PERTOK) {
@@ -485,47 +466,61 @@ __global__ void __maxnreg__(168) gemm_w4a8_tc_kernel(const TcParams p) {
                 }
                 if (p.out_bf16) {
                     __nv_bfloat16 *y = static_cast<__nv_bfloat16 *>(p.y);
-                    if (tok < p.T) y[(size_t)tok * p.M + row] = __float2bfloat16_rn(v0);
-                    if (tok + 1 < p.T) y[(size_t)(tok + 1) * p.M + row] = __float2bfloat16_rn(v1);
+                    if (tok < p.T) __stcs(reinterpret_cast<unsigned short *>(y + (size_t)tok * p.M + row), __bfloat16_as_ushort(__float2bfloat16_rn(v0)));
+                    if (tok + 1 < p.T) __stcs(reinterpret_cast<unsigned short *>(y + (size_t)(tok + 1) * p.M + row), __bfloat16_as_ushort(__float2bfloat16_rn(v1)));
                 } else {
                     float *y = static_cast<float *>(p.y);
-                    if (tok < p.T) y[(size_t)tok * p.M + row] = v0;
-                    if (tok + 1 < p.T) y[(size_t)(tok + 1) * p.M + row] = v1;
+                    if (tok < p.T) __stcs(y + (size_t)tok * p.M + row, v0);
+                    if (tok + 1 < p.T) __stcs(y + (size_t)(tok + 1) * p.M + row, v1);
                 }
             }
         }
+        TCT_OUT(warp)
     } else if (warp == kWorkWarps) {
         // ====================== image copies (one thread) =================================
-        // Two bulk copies per step bring the activation images of its k-tiles for the tile's
-        // token block; the slot's previous images must have been read by every worker warp.
+        // Two bulk copies per step: the fp16 weights of the tile's row block and the activation
+        // images of its token block, both k-tiles of the step at once; the slot's previous
+        // contents must have been promoted by every worker warp (their MMAs are then complete).
         if (lane == 0) {
-            const size_t blk = (size_t)(kBBytes + kSBytes), kstride = (size_t)tok_blocks * blk;
+            // every row block reads the activation images again: they should outlive the weight
+            // image and the output, which stream through L2 once
+            const uint64_t keep = l2_policy_evict_last();
             int n = 0;
+            TCT_DECL
             for (int ti = 0; ti < my_tiles; ++ti) {
-                const int tb = ((int)blockIdx.x + ti * (int)gridDim.x) / row_blocks;
-                const uint8_t *src = p.img + (size_t)tb * blk;
+                const int tile = (int)blockIdx.x + ti * (int)gridDim.x;
+                const int tb = tile % tok_blocks, rb = tile / tok_blocks;
+                const uint8_t *src = p.img + (size_t)tb * Kt * kImgBytes;
+                const uint8_t *wsrc = p.wimg + (size_t)rb * Kt * kABytes;
                 bool ok = true;
-                for (int s = 0; s < spt; ++s, ++n, src += 2 * kstride) {
-                    const int ss = n & (kSS - 1);
+                for (int s = 0; s < spt; ++s, ++n, src += 2 * kImgBytes, wsrc += 2 * kABytes) {
+                    const int ss = n % kSS;
+                    TCT(0)
                     ok = wait_on(empty0 + ss * 8, ((uint32_t)(n / kSS) & 1u) ^ 1u, kWaitProd, kNapNs);
+                    TCT(1)
                     if (!ok) break;
                     const uint32_t fb = full0 + ss * 8;
-                    const uint32_t dst = smem_u + ss * kStepBytes + kABytes;
-                    mbar_expect_tx(fb, 2 * (kBBytes + kSBytes));
-                    bulk_g2s_plain(dst, src, kBBytes + kSBytes, fb);
-                    bulk_g2s_plain(dst + kSlotBytes, src + kstride, kBBytes + kSBytes, fb);
+                    const uint32_t dst = smem_u + ss * kStepBytes;
+                    mbar_expect_tx(fb, kStepBytes);
+                    bulk_g2s_plain(dst, wsrc, 2 * kABytes, fb);
+                    bulk_g2s_hint(dst + 2 * kABytes, src, 2 * kImgBytes, fb, keep);
+                    TCT(2)
                 }
                 if (!ok) break;
             }
+            TCT_OUT(16)
         }
     } else {
         // ====================== MMA issuers (one thread per warp, steps in turn) ===========
         if (lane == 0) {
             const int mw = warp - (kWorkWarps + 1);
             const uint64_t desc0 = smem_desc_at(smem_u, kLboH, kSboH);
+            TCT_DECL
             for (int n = mw; n < n_total; n += kMmaWarps) {
-                const int ss = n & (kSS - 1);
+                const int ss = n % kSS;
+                TCT(0)
                 if (!wait_on(full0 + ss * 8, (uint32_t)(n / kSS) & 1u, kWaitMma, kNapNs)) break;
+                TCT(1)
                 bool ok = true;
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {              // the step's two k-tiles
@@ -537,19 +532,23 @@ __global__ void __maxnreg__(168) gemm_w4a8_tc_kernel(const TcParams p) {
                         if (!ok) break;
                         tc_fence_after();
                     }
-                    const uint64_t da = desc0 + (uint64_t)(((ss * 2 + h) * kSlotBytes) >> 4);
-                    const uint64_t db = da + (kABytes >> 4);
+                    TCT(2)
+                    const uint64_t da = desc0 + (uint64_t)((ss * kStepBytes + h * kABytes) >> 4);
+                    const uint64_t db = desc0 + (uint64_t)((ss * kStepBytes + 2 * kABytes + h * kImgBytes) >> 4);
                     // the first MMA of a promote group overwrites the accumulator
                     tc_mma_f16(tmem_base + b * kTN, da, db, kIdesc, (GW == 2 && h == 1) ? 1u : 0u);
                     tc_mma_f16(tmem_base + b * kTN, da + (2 * kLboH >> 4), db + (2 * kLboH >> 4), kIdesc, 1u);
                     if (GW == 1 || h == 1) tc_commit(acc0 + b * 8);
+                    TCT(3)
                 }
                 if (!ok) break;
             }
+            TCT_OUT(17 + mw)
         }
     }
 
     // ---- teardown: every role comes here, also after a failed wait ------------------------
+    if (warp < kWorkWarps) tmem_wait_ld_all();
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -559,6 +558,8 @@ __global__ void __maxnreg__(168) gemm_w4a8_tc_kernel(const TcParams p) {
 struct TcScratch {
     uint8_t *img = nullptr;
     size_t img_bytes = 0;
+    uint8_t *wimg = nullptr;      // fp16 image of the call's weight (4 bytes per code)
+    size_t wimg_bytes = 0;
     int *zp_flag = nullptr;
 } g_tc;
 
@@ -593,11 +594,17 @@ int launch_gemm_tc(const GemmTcArgs &a) {
     }
     ProfScope prof(a.M, a.K, a.T, a.aq4 ? 44 : (a.ksh ? 64 : 4));
     const int Tpad = (a.T + kTN - 1) / kTN * kTN;
-    const size_t ibytes = (size_t)Kt * (Tpad / kTN) * (kBBytes + kSBytes);
+    const size_t ibytes = (size_t)Kt * (Tpad / kTN) * kImgBytes;
     if (ibytes > g_tc.img_bytes) {
         if (g_tc.img) tq_dev_free(g_tc.img);
         g_tc.img = static_cast<uint8_t *>(tq_dev_alloc(ibytes, "gemm.tc.activation.image"));
         g_tc.img_bytes = ibytes;
+    }
+    const size_t wbytes = (size_t)a.M * a.K * 2;
+    if (wbytes > g_tc.wimg_bytes) {
+        if (g_tc.wimg) tq_dev_free(g_tc.wimg);
+        g_tc.wimg = static_cast<uint8_t *>(tq_dev_alloc(wbytes, "gemm.tc.weight.image"));
+        g_tc.wimg_bytes = wbytes;
     }
     const size_t nrow = (size_t)Kt * Tpad;
     const int pgrid = (int)std::min<size_t>((nrow + 255) / 256, (size_t)g_tc_sms * 8);
@@ -610,8 +617,14 @@ int launch_gemm_tc(const GemmTcArgs &a) {
         gemm_tc_prepass_kernel<<<pgrid, 256, 0, stream()>>>(a.aq, a.as, a.asum, a.T, Tpad, Kt, g_tc.img,
                                                            a.scales, nscales, g_tc.zp_flag);
     TQ_LAUNCH_CHECK("gemm_tc_prepass_kernel");
+    {
+        const size_t items = (size_t)a.M * Kt;
+        const int egrid = (int)std::min<size_t>((items + 255) / 256, (size_t)g_tc_sms * 16);
+        gemm_tc_expand_kernel<<<egrid, 256, 0, stream()>>>(a.codes, a.M, Kt, g_tc.wimg);
+        TQ_LAUNCH_CHECK("gemm_tc_expand_kernel");
+    }
     TcParams p{};
-    p.codes = a.codes; p.scales = a.scales; p.img = g_tc.img; p.y = a.y;
+    p.wimg = g_tc.wimg; p.scales = a.scales; p.img = g_tc.img; p.y = a.y;
     p.status = device_status_word();
     p.wait_ns = wait_limit_ns();
     p.M = a.M; p.Kt = Kt; p.ksh = a.ksh; p.T = a.T; p.Tpad = Tpad; p.out_bf16 = a.out_bf16;
@@ -638,3 +651,8 @@ int launch_gemm_tc(const GemmTcArgs &a) {
 
 }  // namespace tq
 
+#ifdef TQ_TC_TRACE
+extern "C" void qwn_dbg_tc_trace(long long *host) {
+    cudaMemcpyFromSymbol(host, tq::g_tc_trace, sizeof(long long) * 320);
+}
+#endif
