@@ -312,7 +312,6 @@ __global__ void __maxnreg__(kMaxRegs) gemm_w4a8_tc_kernel(const TcParams p) {
     const int ntiles = row_blocks * tok_blocks;
     const int my_tiles = (ntiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
     const int n_total = my_tiles * spt;                  // steps of this CTA
-    const int g_total = (GW == 2) ? n_total : 2 * n_total;      // promote groups of this CTA
 
     // A wait that gives up when another role already has: the flag is read on the slow path only.
     auto wait_on = [&](uint32_t bar, uint32_t parity, int code, uint32_t suspend_ns = 0) -> bool {
@@ -332,22 +331,16 @@ __global__ void __maxnreg__(kMaxRegs) gemm_w4a8_tc_kernel(const TcParams p) {
         // vectors: [0, 16) scales, [32, 48) code sums)
         const unsigned char *sv_base = smem + 2 * kABytes + kBBytes + chalf * 4;
         int n = 0;                                        // step counter across the CTA's tiles
-        bool alive = true;
-        // The thread's 64 columns of a group's accumulator, as two 32-column loads. `loaded`:
-        // the loads of the group about to be promoted were already issued, behind the
-        // promotes of the group before it (the load of the second half behind the first
-        // half's fma, and so on around the loop), so that no load's latency is exposed.
+        int ss = 0;                                       // n % kSS, kept as a counter
+        // The thread's 32 columns of a group's accumulator. (Issuing the load of the next
+        // group behind this group's fma, when its barrier had already completed, measured
+        // slower than this plain sequence: with five warps per scheduler the other warps cover
+        // a load's latency, and every instruction saved counts.)
         uint32_t d[kWT];
-        uint32_t (&dlo)[kWT / 2] = *reinterpret_cast<uint32_t (*)[kWT / 2]>(&d[0]);
-        uint32_t (&dhi)[kWT / 2] = *reinterpret_cast<uint32_t (*)[kWT / 2]>(&d[kWT / 2]);
-        auto load_half = [&](uint32_t taddr, uint32_t (&v)[kWT / 2]) {
-            if constexpr (kWT == 64) tmem_ld32(taddr, *reinterpret_cast<uint32_t (*)[32]>(&v[0]));
-            else tmem_ld16(taddr, *reinterpret_cast<uint32_t (*)[16]>(&v[0]));
-        };
-        bool loaded = false;
+        static_assert(kWT == 32, "one 32-column load per group");
         TCT_DECL
 
-        for (int ti = 0; ti < my_tiles && alive; ++ti) {
+        for (int ti = 0; ti < my_tiles; ++ti) {
             const int tile = (int)blockIdx.x + ti * (int)gridDim.x;
             const int tb = tile % tok_blocks, rb = tile / tok_blocks;
             const int row = rb * kTM + rloc;
@@ -356,8 +349,9 @@ __global__ void __maxnreg__(kMaxRegs) gemm_w4a8_tc_kernel(const TcParams p) {
 #pragma unroll
             for (int i = 0; i < kWT; ++i) acc[i] = 0.0f;
             uint32_t scw = __ldg(sc);
+            const uint16_t *scn = sc;                     // the word of the group being promoted
 #pragma unroll 1
-            for (int s = 0; s < spt; ++s, ++n) {
+            for (int s = 0; s < spt; ++s, ++n, ss = (ss + 1 == kSS) ? 0 : ss + 1) {
 #pragma unroll
                 for (int g = 0; g < (GW == 2 ? 1 : 2); ++g) {
                     TCT(7)
@@ -367,32 +361,25 @@ __global__ void __maxnreg__(kMaxRegs) gemm_w4a8_tc_kernel(const TcParams p) {
                     int zp;
                     float ws;
                     unpack_scale(scw, zp, ws);
-                    if (kt + GW < Kt) scw = __ldg(sc + (size_t)((kt + GW) >> p.ksh) * 16);
+                    // the next group's word: the next one in the row's run, except inside a K64
+                    // pair promoted per k-tile, whose second tile shares the first one's
+                    if (GW == 2 || g == 1 || p.ksh == 0) scn += 16;
+                    if (kt + GW < Kt) scw = __ldg(scn);
                     const f32x2 ws2 = pack2(ws, ws);
                     const float nzf = (float)(-zp);
                     TCT(0)
-                    TCT_CNT(8, loaded ? 1 : 0) TCT_CNT(9, 1)
-                    if (!loaded) {
-                        if (!__all_sync(0xffffffffu, wait_on(acc0 + b * 8, (uint32_t)(ig / kNB) & 1u, kWaitEpi))) {
-                            alive = false;
-                            break;
-                        }
-                        tc_fence_after();
-                        // the accumulator holds (float)d of the group (the group's first MMA
-                        // overwrites it): nothing has to be converted or stored back
-                        load_half(lane_base + b * kTN, dlo);
-                        load_half(lane_base + b * kTN + kWT / 2, dhi);
-                    }
+                    if (!__all_sync(0xffffffffu, wait_on(acc0 + b * 8, (uint32_t)(ig / kNB) & 1u, kWaitEpi)))
+                        goto gave_up;
+                    tc_fence_after();
+                    // the accumulator holds (float)d of the group (the group's first MMA
+                    // overwrites it): nothing has to be converted or stored back
+                    tmem_ld32(lane_base + b * kTN, d);
                     TCT(1)
-                    // the CTA's next group (also across tiles): is its accumulator complete?
-                    const int ign = ig + 1, bn = ign & (kNB - 1);
-                    const bool next = ign < g_total &&
-                                      __all_sync(0xffffffffu, mbar_test_wait(acc0 + bn * 8, (uint32_t)(ign / kNB) & 1u));
                     const ulonglong2 *sv = reinterpret_cast<const ulonglong2 *>(
-                        sv_base + (size_t)(n % kSS) * kStepBytes + g * kImgBytes);
+                        sv_base + (size_t)ss * kStepBytes + g * kImgBytes);
                     // second k-tile of a K64 group: only its code sums are needed
                     const ulonglong2 *sv1 = reinterpret_cast<const ulonglong2 *>(
-                        sv_base + (size_t)(n % kSS) * kStepBytes + kImgBytes);
+                        sv_base + (size_t)ss * kStepBytes + kImgBytes);
                     // symmetric weights need no zero-point term at all (the weights enter the
                     // MMA as true signed values): ZP is a compile-time choice, a test inside the
                     // unrolled loop would split it into one basic block per token group
@@ -431,14 +418,7 @@ __global__ void __maxnreg__(kMaxRegs) gemm_w4a8_tc_kernel(const TcParams p) {
                     TCT(2)
                     tmem_wait_ld_all();
                     TCT(3)
-                    promote(0, kWT / 8);
-                    if (next) {
-                        tc_fence_after();
-                        load_half(lane_base + bn * kTN, dlo);          // into the registers just consumed
-                    }
-                    promote(kWT / 8, kWT / 4);
-                    if (next) load_half(lane_base + bn * kTN + kWT / 2, dhi);
-                    loaded = next;
+                    promote(0, kWT / 4);
                     TCT(4)
                     tc_fence_before();
                     __syncwarp();
@@ -447,14 +427,12 @@ __global__ void __maxnreg__(kMaxRegs) gemm_w4a8_tc_kernel(const TcParams p) {
                     // the buffer, lane 1 (after the step's last group) the copy thread that the
                     // slot's images may be replaced
                     if (g == (GW == 2 ? 0 : 1))
-                        mbar_arrive_if(lane == 0 ? accempty0 + b * 8 : empty0 + (n % kSS) * 8, lane < 2);
+                        mbar_arrive_if(lane == 0 ? accempty0 + b * 8 : empty0 + ss * 8, lane < 2);
                     else
                         mbar_arrive_if(accempty0 + b * 8, lane == 0);
                     TCT(6)
                 }
-                if (!alive) break;
             }
-            if (!alive) break;
             // store: thread = row, its tokens; rows are contiguous in y, so a warp writes 128 B
 #pragma unroll
             for (int i = 0; i < kWT / 2; ++i) {
@@ -475,6 +453,7 @@ __global__ void __maxnreg__(kMaxRegs) gemm_w4a8_tc_kernel(const TcParams p) {
                 }
             }
         }
+    gave_up:;
         TCT_OUT(warp)
     } else if (warp == kWorkWarps) {
         // ====================== image copies (one thread) =================================
