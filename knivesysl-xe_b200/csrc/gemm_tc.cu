@@ -368,7 +368,7 @@ __global__ void __maxnreg__(kMaxRegs) gemm_w4a8_tc_kernel(const TcParams p) {
                     const f32x2 ws2 = pack2(ws, ws);
                     const float nzf = (float)(-zp);
                     TCT(0)
-                    if (!__all_sync(0xffffffffu, wait_on(acc0 + b * 8, (uint32_t)(ig / kNB) & 1u, kWaitEpi)))
+                    if (!__all_sync(0xffffffffu, wait_on(acc0 + b * 8, (uint32_t)(ig / kNB) & 1u, kWaitEpi, kNapNs)))
                         goto gave_up;
                     tc_fence_after();
                     // the accumulator holds (float)d of the group (the group's first MMA
@@ -464,7 +464,8 @@ __global__ void __maxnreg__(kMaxRegs) gemm_w4a8_tc_kernel(const TcParams p) {
             // every row block reads the activation images again: they should outlive the weight
             // image and the output, which stream through L2 once
             const uint64_t keep = l2_policy_evict_last();
-            int n = 0;
+            int ss = 0;                    // step slot and the parity of its use, kept as counters
+            uint32_t ph = 0;
             TCT_DECL
             for (int ti = 0; ti < my_tiles; ++ti) {
                 const int tile = (int)blockIdx.x + ti * (int)gridDim.x;
@@ -472,10 +473,9 @@ __global__ void __maxnreg__(kMaxRegs) gemm_w4a8_tc_kernel(const TcParams p) {
                 const uint8_t *src = p.img + (size_t)tb * Kt * kImgBytes;
                 const uint8_t *wsrc = p.wimg + (size_t)rb * Kt * kABytes;
                 bool ok = true;
-                for (int s = 0; s < spt; ++s, ++n, src += 2 * kImgBytes, wsrc += 2 * kABytes) {
-                    const int ss = n % kSS;
+                for (int s = 0; s < spt; ++s, src += 2 * kImgBytes, wsrc += 2 * kABytes) {
                     TCT(0)
-                    ok = wait_on(empty0 + ss * 8, ((uint32_t)(n / kSS) & 1u) ^ 1u, kWaitProd, kNapNs);
+                    ok = wait_on(empty0 + ss * 8, ph ^ 1u, kWaitProd, kNapNs);
                     TCT(1)
                     if (!ok) break;
                     const uint32_t fb = full0 + ss * 8;
@@ -483,6 +483,10 @@ __global__ void __maxnreg__(kMaxRegs) gemm_w4a8_tc_kernel(const TcParams p) {
                     mbar_expect_tx(fb, kStepBytes);
                     bulk_g2s_plain(dst, wsrc, 2 * kABytes, fb);
                     bulk_g2s_hint(dst + 2 * kABytes, src, 2 * kImgBytes, fb, keep);
+                    if (++ss == kSS) {
+                        ss = 0;
+                        ph ^= 1u;
+                    }
                     TCT(2)
                 }
                 if (!ok) break;
@@ -495,10 +499,12 @@ __global__ void __maxnreg__(kMaxRegs) gemm_w4a8_tc_kernel(const TcParams p) {
             const int mw = warp - (kWorkWarps + 1);
             const uint64_t desc0 = smem_desc_at(smem_u, kLboH, kSboH);
             TCT_DECL
+            int ss = mw;                   // step slot and the parity of its use, kept as counters
+            uint32_t ph = 0;
+            static_assert(kMmaWarps < kSS, "the first step of every MMA thread is in the first round of slots");
             for (int n = mw; n < n_total; n += kMmaWarps) {
-                const int ss = n % kSS;
                 TCT(0)
-                if (!wait_on(full0 + ss * 8, (uint32_t)(n / kSS) & 1u, kWaitMma, kNapNs)) break;
+                if (!wait_on(full0 + ss * 8, ph, kWaitMma, kNapNs)) break;
                 TCT(1)
                 bool ok = true;
 #pragma unroll
@@ -521,6 +527,11 @@ __global__ void __maxnreg__(kMaxRegs) gemm_w4a8_tc_kernel(const TcParams p) {
                     TCT(3)
                 }
                 if (!ok) break;
+                ss += kMmaWarps;
+                if (ss >= kSS) {
+                    ss -= kSS;
+                    ph ^= 1u;
+                }
             }
             TCT_OUT(17 + mw)
         }
