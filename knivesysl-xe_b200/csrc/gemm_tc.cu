@@ -36,18 +36,17 @@
 //    k-tile into accumulator buffer b (the first MMA of a promote group overwrites it);
 //    tcgen05.commit signals the workers. The single-thread roles wait with a suspend-time
 //    hint: back-to-back polling took a fifth of the schedulers' issue slots;
-//  * workers (16 warps): thread = weight row x 32 tokens. Per promote group the thread's 32
-//    accumulator columns are read with two 16-column tcgen05.ld, then per token
+//  * workers (16 warps): thread = weight row x 32 tokens. Per promote group: wait for the
+//    group's accumulator, one 32-column tcgen05.ld, then per token
 //    f = fma(-z, asum, d) (exact; only in the kernel variant for weights with zero points),
 //    acc = fma(f, ws*as, acc); 32 fp32 accumulators stay in registers for the whole K loop
-//    and are stored at the end (coalesced over rows). The loads of the next group are issued
-//    behind the fma of this one (first half behind the first half's fma, into the registers
-//    just consumed), when that group's barrier has already completed - it nearly always has -
-//    so no load latency is exposed.
-// What bounds it: the workers' per-group sequence (barrier test, loads, fences, arrivals; about
-// 120 instructions besides the fma) - a trace shows the copy and MMA threads waiting on the
-// workers, and neither halving the copied bytes, nor a third MMA thread, nor removing the fma
-// changes the time by more than a tenth.
+//    and are stored at the end (coalesced over rows). With five warps per scheduler the loop
+//    is bound by issue slots: it is kept to the plain sequence (issuing the next group's
+//    load early, behind this group's fma, cost more instructions than the latency it hid).
+// What bounds it: issue slots of the worker warps (119 instructions per group, 32 of them fma)
+// and the hand-offs between the roles - a trace shows every role busy about half of the time
+// and waiting for another one the other half; neither halving the copied bytes, nor a third
+// MMA thread, nor spinning instead of suspended waits changes the time by more than 2 %.
 //
 // Every mbarrier wait is bounded; on expiry the kernel records a status word, stops
 // issuing work, still frees its TMEM and returns.
