@@ -274,6 +274,8 @@ __global__ void __maxnreg__(kMaxRegs) gemm_w4a8_tc_kernel(const TcParams p) {
     pdl_trigger();
     pdl_wait();      // everything below reads what earlier kernels wrote (flag, images)
     if ((*p.zp_flag != 0) != ZP) return;
+    // per-token scales and no zero points: the promote reads neither as nor asum from the slot
+    constexpr bool kSlotFreedByMma = PERTOK && !ZP;
     extern __shared__ __align__(1024) unsigned char smem[];
     __shared__ uint64_t bars[2 * kSS + 2 * kNB];   // full[kSS], empty[kSS], accfull[kNB], accempty[kNB]
     __shared__ uint32_t tmem_base_s;
@@ -287,7 +289,9 @@ __global__ void __maxnreg__(kMaxRegs) gemm_w4a8_tc_kernel(const TcParams p) {
     if (threadIdx.x == 0) {
         for (int s = 0; s < kSS; ++s) {
             mbar_init(full0 + s * 8, 1);                 // the copy thread's arrive with the step's byte count
-            mbar_init(empty0 + s * 8, kWorkWarps);       // one arrive per worker warp
+            // a slot is free when every worker warp has read its activation scales - or, in
+            // the variant whose workers read nothing from the slot, when its MMAs are complete
+            mbar_init(empty0 + s * 8, kSlotFreedByMma ? 1 : kWorkWarps);
         }
         for (int b = 0; b < kNB; ++b) {
             mbar_init(acc0 + b * 8, 1);                  // tcgen05.commit
@@ -425,7 +429,7 @@ __global__ void __maxnreg__(kMaxRegs) gemm_w4a8_tc_kernel(const TcParams p) {
                     // one instruction, two barriers: lane 0 tells the MMA that it may overwrite
                     // the buffer, lane 1 (after the step's last group) the copy thread that the
                     // slot's images may be replaced
-                    if (g == (GW == 2 ? 0 : 1))
+                    if (g == (GW == 2 ? 0 : 1) && !kSlotFreedByMma)
                         mbar_arrive_if(lane == 0 ? accempty0 + b * 8 : empty0 + ss * 8, lane < 2);
                     else
                         mbar_arrive_if(accempty0 + b * 8, lane == 0);
@@ -523,6 +527,8 @@ __global__ void __maxnreg__(kMaxRegs) gemm_w4a8_tc_kernel(const TcParams p) {
                     tc_mma_f16(tmem_base + b * kTN, da, db, kIdesc, (GW == 2 && h == 1) ? 1u : 0u);
                     tc_mma_f16(tmem_base + b * kTN, da + (2 * kLboH >> 4), db + (2 * kLboH >> 4), kIdesc, 1u);
                     if (GW == 1 || h == 1) tc_commit(acc0 + b * 8);
+                    // the step's operands have been read when its MMAs are complete
+                    if (kSlotFreedByMma && h == 1) tc_commit(empty0 + ss * 8);
                     TCT(3)
                 }
                 if (!ok) break;
