@@ -464,9 +464,6 @@ __global__ void __maxnreg__(kMaxRegs) gemm_w4a8_tc_kernel(const TcParams p) {
         // images of its token block, both k-tiles of the step at once; the slot's previous
         // contents must have been promoted by every worker warp (their MMAs are then complete).
         if (lane == 0) {
-            // every row block reads the activation images again: they should outlive the weight
-            // image and the output, which stream through L2 once
-            const uint64_t keep = l2_policy_evict_last();
             int ss = 0;                    // step slot and the parity of its use, kept as counters
             uint32_t ph = 0;
             TCT_DECL
@@ -485,7 +482,7 @@ __global__ void __maxnreg__(kMaxRegs) gemm_w4a8_tc_kernel(const TcParams p) {
                     const uint32_t dst = smem_u + ss * kStepBytes;
                     mbar_expect_tx(fb, kStepBytes);
                     bulk_g2s_plain(dst, wsrc, 2 * kABytes, fb);
-                    bulk_g2s_hint(dst + 2 * kABytes, src, 2 * kImgBytes, fb, keep);
+                    bulk_g2s_plain(dst + 2 * kABytes, src, 2 * kImgBytes, fb);
                     if (++ss == kSS) {
                         ss = 0;
                         ph ^= 1u;

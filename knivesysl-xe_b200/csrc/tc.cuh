@@ -167,21 +167,6 @@ __device__ __forceinline__ void bulk_g2s_plain(uint32_t dst, const void *src, ui
         : "memory");
 }
 
-// the same with an L2 cache policy (createpolicy) for the lines it reads
-__device__ __forceinline__ void bulk_g2s_hint(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar,
-                                              uint64_t policy) {
-    asm volatile(
-        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::
-            "r"(dst),
-        "l"(src), "r"(bytes), "r"(bar), "l"(policy)
-        : "memory");
-}
-__device__ __forceinline__ uint64_t l2_policy_evict_last() {
-    uint64_t pol;
-    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
-    return pol;
-}
-
 // K-major, no swizzle: core matrix = 8 rows x 16 bytes (128 contiguous bytes); the two
 // 16-byte K-chunks of a row group are kLbo apart, row groups of 8 are kSbo apart.
 constexpr uint32_t kLbo = 128, kSbo = 256;

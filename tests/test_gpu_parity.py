@@ -588,7 +588,9 @@ def _bf16_rne(a):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("M,K,ksh,T,bf16", [(2048, 512, 1, 128, False), (1024, 1024, 0, 256, False),
-                                            (2048, 256, 1, 136, False), (1024, 512, 1, 128, True)])
+                                            (2048, 256, 1, 136, False), (1024, 512, 1, 128, True),
+                                            # one tile of two steps; more tiles than SMs with ragged tokens
+                                            (128, 128, 1, 128, False), (2560, 640, 0, 1000, False)])
 def test_gemm_pertoken_tcgen05(lib, pkg, orc, wl, M, K, ksh, T, bf16):
     """Per-token activation scales: the int32 dot runs over a whole weight-scale group in
     TMEM (two k-tiles under K64) before one fp32 promote; y = acc * as_tok. Bit-identical to
