@@ -359,8 +359,12 @@ __global__ void __maxnreg__(kMaxRegs) gemm_w4a8_tc_kernel(const TcParams p) {
                 for (int g = 0; g < (GW == 2 ? 1 : 2); ++g) {
                     TCT(7)
                     const int kt = 2 * s + g;              // first k-tile of the group
-                    const int ig = (GW == 2) ? n : 2 * n + g;      // group counter of the CTA
-                    const int b = ig & (kNB - 1);
+                    // One barrier round per step: a K64 group per step uses the four 128-column
+                    // buffers in turn; two K32 groups per step share a 256-column buffer pair
+                    // (k-tile g in its half), with one wait and one arrival for both.
+                    const int b = (GW == 2) ? (n & 3) : (n & 1);
+                    const uint32_t par = (GW == 2) ? ((uint32_t)n >> 2) & 1u : ((uint32_t)n >> 1) & 1u;
+                    const uint32_t col = (GW == 2) ? b * kTN : (2 * b + g) * kTN;
                     int zp;
                     float ws;
                     unpack_scale(scw, zp, ws);
@@ -371,12 +375,13 @@ __global__ void __maxnreg__(kMaxRegs) gemm_w4a8_tc_kernel(const TcParams p) {
                     const f32x2 ws2 = pack2(ws, ws);
                     const float nzf = (float)(-zp);
                     TCT(0)
-                    if (!__all_sync(0xffffffffu, wait_on(acc0 + b * 8, (uint32_t)(ig / kNB) & 1u, kWaitEpi, kNapNs)))
-                        goto gave_up;
-                    tc_fence_after();
+                    if (GW == 2 || g == 0) {
+                        if (!__all_sync(0xffffffffu, wait_on(acc0 + b * 8, par, kWaitEpi, kNapNs))) goto gave_up;
+                        tc_fence_after();
+                    }
                     // the accumulator holds (float)d of the group (the group's first MMA
                     // overwrites it): nothing has to be converted or stored back
-                    tmem_ld32(lane_base + b * kTN, d);
+                    tmem_ld32(lane_base + col, d);
                     TCT(1)
                     const ulonglong2 *sv = reinterpret_cast<const ulonglong2 *>(
                         sv_base + (size_t)ss * kStepBytes + g * kImgBytes);
@@ -423,16 +428,17 @@ __global__ void __maxnreg__(kMaxRegs) gemm_w4a8_tc_kernel(const TcParams p) {
                     TCT(3)
                     promote(0, kWT / 4);
                     TCT(4)
-                    tc_fence_before();
-                    __syncwarp();
-                    TCT(5)
-                    // one instruction, two barriers: lane 0 tells the MMA that it may overwrite
-                    // the buffer, lane 1 (after the step's last group) the copy thread that the
-                    // slot's images may be replaced
-                    if (g == (GW == 2 ? 0 : 1) && !kSlotFreedByMma)
-                        mbar_arrive_if(lane == 0 ? accempty0 + b * 8 : empty0 + ss * 8, lane < 2);
-                    else
-                        mbar_arrive_if(accempty0 + b * 8, lane == 0);
+                    if (GW == 2 || g == 1) {
+                        tc_fence_before();
+                        __syncwarp();
+                        TCT(5)
+                        // one instruction, two barriers: lane 0 tells the MMA that it may overwrite
+                        // the buffer, lane 1 the copy thread that the slot's images may be replaced
+                        if (!kSlotFreedByMma)
+                            mbar_arrive_if(lane == 0 ? accempty0 + b * 8 : empty0 + ss * 8, lane < 2);
+                        else
+                            mbar_arrive_if(accempty0 + b * 8, lane == 0);
+                    }
                     TCT(6)
                 }
             }
@@ -509,11 +515,12 @@ __global__ void __maxnreg__(kMaxRegs) gemm_w4a8_tc_kernel(const TcParams p) {
                 bool ok = true;
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {              // the step's two k-tiles
-                    const int ig = (GW == 2) ? n : 2 * n + h;
-                    const int b = ig & (kNB - 1);
-                    // the group's accumulator buffer has been read out
-                    if (GW == 1 || h == 0) {
-                        ok = wait_on(accempty0 + b * 8, ((uint32_t)(ig / kNB) & 1u) ^ 1u, kWaitMma, kNapNs);
+                    const int b = (GW == 2) ? (n & 3) : (n & 1);
+                    const uint32_t par = (GW == 2) ? ((uint32_t)n >> 2) & 1u : ((uint32_t)n >> 1) & 1u;
+                    const uint32_t col = (GW == 2) ? b * kTN : (2 * b + h) * kTN;
+                    // the step's accumulator buffer (or pair) has been read out
+                    if (h == 0) {
+                        ok = wait_on(accempty0 + b * 8, par ^ 1u, kWaitMma, kNapNs);
                         if (!ok) break;
                         tc_fence_after();
                     }
@@ -521,9 +528,9 @@ __global__ void __maxnreg__(kMaxRegs) gemm_w4a8_tc_kernel(const TcParams p) {
                     const uint64_t da = desc0 + (uint64_t)((ss * kStepBytes + h * kABytes) >> 4);
                     const uint64_t db = desc0 + (uint64_t)((ss * kStepBytes + 2 * kABytes + h * kImgBytes) >> 4);
                     // the first MMA of a promote group overwrites the accumulator
-                    tc_mma_f16(tmem_base + b * kTN, da, db, kIdesc, (GW == 2 && h == 1) ? 1u : 0u);
-                    tc_mma_f16(tmem_base + b * kTN, da + (2 * kLboH >> 4), db + (2 * kLboH >> 4), kIdesc, 1u);
-                    if (GW == 1 || h == 1) tc_commit(acc0 + b * 8);
+                    tc_mma_f16(tmem_base + col, da, db, kIdesc, (GW == 2 && h == 1) ? 1u : 0u);
+                    tc_mma_f16(tmem_base + col, da + (2 * kLboH >> 4), db + (2 * kLboH >> 4), kIdesc, 1u);
+                    if (h == 1) tc_commit(acc0 + b * 8);
                     // the step's operands have been read when its MMAs are complete
                     if (kSlotFreedByMma && h == 1) tc_commit(empty0 + ss * 8);
                     TCT(3)
