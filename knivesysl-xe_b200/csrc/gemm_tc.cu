@@ -34,7 +34,8 @@
 //    activations, each contiguous in its image;
 //  * two MMA threads (in two warps, steps in turn): two tcgen05.mma (M=128, N=128, K=16) per
 //    k-tile into accumulator buffer b (the first MMA of a promote group overwrites it);
-//    tcgen05.commit signals the workers. The single-thread roles wait with a suspend-time
+//    tcgen05.commit signals the workers once per step: a step is one K64 group in one of four
+//    128-column buffers, or two K32 groups in the halves of one of two 256-column pairs. The single-thread roles wait with a suspend-time
 //    hint: back-to-back polling took a fifth of the schedulers' issue slots;
 //  * workers (16 warps): thread = weight row x 32 tokens. Per promote group: wait for the
 //    group's accumulator, one 32-column tcgen05.ld, then per token
