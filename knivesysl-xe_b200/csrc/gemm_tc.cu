@@ -246,16 +246,17 @@ gemm_tc_expand_kernel(const uint8_t *__restrict__ codes, int M, int Kt, uint8_t 
 
 constexpr int kWaitMma = 21, kWaitEpi = 22, kWaitProd = 23;   // status codes of failed waits
 
+// Trace build (-DTQ_TC_TRACE): every role of CTA 0 adds up clock64() differences per section
+// of its loop (TCT(i) closes section i); qwn_dbg_tc_trace copies the sums out: rows 0..15
+// the worker warps, 16 the copy thread, 17 and 18 the MMA threads. Compiled out otherwise.
 #ifdef TQ_TC_TRACE
 __device__ long long g_tc_trace[20 * 16];
 #define TCT_DECL long long tct_[12] = {}; long long tct_t = clock64();
 #define TCT(i) { const long long t_ = clock64(); tct_[i] += t_ - tct_t; tct_t = t_; }
-#define TCT_CNT(i, v) tct_[i] += (v);
 #define TCT_OUT(slot) if (blockIdx.x == 0 && lane == 0) { for (int i_ = 0; i_ < 12; ++i_) g_tc_trace[(slot) * 16 + i_] = tct_[i_]; }
 #else
 #define TCT_DECL
 #define TCT(i)
-#define TCT_CNT(i, v)
 #define TCT_OUT(slot)
 #endif
 
