@@ -454,8 +454,9 @@ class Prefill:
         self.off = (C.c_int * 5)(0, self.T // 4, self.T // 2, 3 * self.T // 4, self.T)
         self.weight_bytes = ctx.wl.weight_bytes(self.M, self.K, 64)
         self.ops = 2.0 * self.T * self.M * self.K
-        self.launches_per_step = 4      # staging, activation image pre-pass, the GEMM kernel without and with
-                                        # the zero-point term (the one the weight does not need returns at once)
+        self.launches_per_step = 5      # staging, activation image pre-pass, weight image pre-pass, the GEMM
+                                        # kernel without and with the zero-point term (the one the weight does
+                                        # not need returns at once)
 
     def stage(self, xb):
         lib, x = self.ctx.lib, self.x_dev[xb].ptr
