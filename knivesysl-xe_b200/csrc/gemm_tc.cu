@@ -282,6 +282,9 @@ __global__ void __maxnreg__(kMaxRegs) gemm_w4a8_tc_kernel(const TcParams p) {
     // output, and as packed fma on token pairs it is half as many instructions (5 % faster;
     // in every other mode the packed form measured 8 to 11 % slower than scalar fma).
     constexpr bool kPacked = PERTOK && !ZP && GW == 2;
+    // the step loop of that mode is short enough to gain from two copies (1 to 2 %; four lose 4 %,
+    // and the other modes lose with two)
+    constexpr int kStepUnroll = (PERTOK && GW == 2) ? 2 : 1;
     extern __shared__ __align__(1024) unsigned char smem[];
     __shared__ uint64_t bars[2 * kSS + 2 * kNB];   // full[kSS], empty[kSS], accfull[kNB], accempty[kNB]
     __shared__ uint32_t tmem_base_s;
@@ -362,7 +365,7 @@ __global__ void __maxnreg__(kMaxRegs) gemm_w4a8_tc_kernel(const TcParams p) {
             for (int i = 0; i < kWT / 2; ++i) accp[i] = 0ull;
             uint32_t scw = __ldg(sc);
             const uint16_t *scn = sc;                     // the word of the group being promoted
-#pragma unroll 1
+#pragma unroll kStepUnroll
             for (int s = 0; s < spt; ++s, ++n, ss = (ss + 1 == kSS) ? 0 : ss + 1) {
 #pragma unroll
                 for (int g = 0; g < (GW == 2 ? 1 : 2); ++g) {
