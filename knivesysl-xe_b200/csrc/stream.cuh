@@ -116,11 +116,6 @@ __device__ __forceinline__ uint64_t l2_policy_evict_first() {
     return pol;
 }
 
-// Pulls the 128-byte line at p into L2 (no register, no wait).
-__device__ __forceinline__ void prefetch_l2(const void *p) {
-    asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
-}
-
 // 16-byte asynchronous copy global -> shared that bypasses L1 (per-lane; completion is
 // tracked with commit/wait groups, so there is nothing to spin on).
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint64_t policy) {
