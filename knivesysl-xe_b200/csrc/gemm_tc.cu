@@ -404,39 +404,39 @@ __global__ void __maxnreg__(kMaxRegs) gemm_w4a8_tc_kernel(const TcParams p) {
                     // MMA as true signed values): ZP is a compile-time choice, a test inside the
                     // unrolled loop would split it into one basic block per token group
                     auto promote = [&](int j0, int j1) {
-                        if (kPacked) {
+                        if constexpr (kPacked) {
 #pragma unroll
                             for (int j = 2 * j0; j < 2 * j1; ++j)
                                 fma2_acc(accp[j], pack2(__uint_as_float(d[2 * j]), __uint_as_float(d[2 * j + 1])), ws2);
-                            return;
-                        }
+                        } else {
 #pragma unroll
-                        for (int j = j0; j < j1; ++j) {     // four tokens at a time
-                            // scalar fmas on the loaded registers as they are
-                            float f[4];
+                            for (int j = j0; j < j1; ++j) {     // four tokens at a time
+                                // scalar fmas on the loaded registers as they are
+                                float f[4];
 #pragma unroll
-                            for (int i = 0; i < 4; ++i) f[i] = __uint_as_float(d[4 * j + i]);
-                            if (ZP) {
-                                ulonglong2 sm = sv[32 + j];                        // four code sums
-                                if (GW == 2) {                                     // exact: small integers
-                                    const ulonglong2 sm1 = sv1[32 + j];
-                                    sm.x = add2(sm.x, sm1.x);
-                                    sm.y = add2(sm.y, sm1.y);
+                                for (int i = 0; i < 4; ++i) f[i] = __uint_as_float(d[4 * j + i]);
+                                if (ZP) {
+                                    ulonglong2 sm = sv[32 + j];                        // four code sums
+                                    if (GW == 2) {                                     // exact: small integers
+                                        const ulonglong2 sm1 = sv1[32 + j];
+                                        sm.x = add2(sm.x, sm1.x);
+                                        sm.y = add2(sm.y, sm1.y);
+                                    }
+                                    float m[4];
+                                    unpack2(sm.x, m[0], m[1]);
+                                    unpack2(sm.y, m[2], m[3]);
+#pragma unroll
+                                    for (int i = 0; i < 4; ++i) f[i] = fmaf(nzf, m[i], f[i]);
                                 }
-                                float m[4];
-                                unpack2(sm.x, m[0], m[1]);
-                                unpack2(sm.y, m[2], m[3]);
+                                float w[4] = {ws, ws, ws, ws};
+                                if (!PERTOK) {
+                                    const ulonglong2 a4 = sv[j];                       // four activation scales
+                                    unpack2(mul2(ws2, a4.x), w[0], w[1]);              // ws * as, rounded once
+                                    unpack2(mul2(ws2, a4.y), w[2], w[3]);
+                                }
 #pragma unroll
-                                for (int i = 0; i < 4; ++i) f[i] = fmaf(nzf, m[i], f[i]);
+                                for (int i = 0; i < 4; ++i) acc[4 * j + i] = fmaf(f[i], w[i], acc[4 * j + i]);
                             }
-                            float w[4] = {ws, ws, ws, ws};
-                            if (!PERTOK) {
-                                const ulonglong2 a4 = sv[j];                       // four activation scales
-                                unpack2(mul2(ws2, a4.x), w[0], w[1]);              // ws * as, rounded once
-                                unpack2(mul2(ws2, a4.y), w[2], w[3]);
-                            }
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) acc[4 * j + i] = fmaf(f[i], w[i], acc[4 * j + i]);
                         }
                     };
                     TCT(2)
