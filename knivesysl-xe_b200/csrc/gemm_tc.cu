@@ -514,6 +514,15 @@ __global__ void __maxnreg__(kMaxRegs) gemm_w4a8_tc_kernel(const TcParams p) {
                 }
                 if (!ok) break;
             }
+            // No copy may still be in flight when the CTA gives its shared memory back: wait
+            // (bounded) until the last armed use of every slot has all its bytes. On the normal
+            // path every one of them was consumed long ago and these tests return at once; after
+            // a wait that gave up somewhere, this is where the copies already started drain.
+            for (int s2 = 0; s2 < kSS; ++s2) {
+                const uint32_t last = (s2 < ss) ? ph : (ph ^ 1u);     // this round's use, or the one before
+                if (!mbar_test_wait(full0 + s2 * 8, last))
+                    mbar_wait_slow(full0 + s2 * 8, last, p.status, kWaitProd, p.wait_ns, kNapNs);
+            }
             TCT_OUT(16)
         }
     } else {
